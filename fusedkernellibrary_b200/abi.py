@@ -1,0 +1,99 @@
+"""ctypes mirror of include/fkb/fkb.h and the loader of the CUDA library.
+
+This module is plumbing for the Python test and benchmark harness: it declares the C structs, loads
+``lib/libfkb.so`` (built by :mod:`fusedkernellibrary_b200.build`) and declares every entry point's
+signature.  There is no CPU fallback: if the library is missing, :func:`load` raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+MAX_OPS = 12
+MAX_PLANE_PARAMS = 4
+MAX_CHAINS = 8
+
+OK, ERR_NULL, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_TOO_LARGE, ERR_DEVICE_WAIT = 0, -1, -2, -3, -4, -5, -6
+
+PIX_U8C3, PIX_F32C3, PIX_NV12 = 1, 2, 3
+GEOM_NONE, GEOM_RESIZE_IGNORE_AR, GEOM_RESIZE_PRESERVE_AR = 0, 1, 2
+WRITE_PACKED, WRITE_SPLIT = 1, 2
+OP_CAST_F32, OP_MUL, OP_ADD, OP_SUB, OP_DIV, OP_REORDER_ZYX, OP_YUV2RGB, OP_SATCAST_U8 = 1, 2, 3, 4, 5, 6, 7, 8
+
+
+class Op(C.Structure):
+    _fields_ = [("code", C.c_uint16), ("plane_slot", C.c_int16), ("v", C.c_float * 3)]
+
+
+class ChainDesc(C.Structure):
+    _fields_ = [
+        ("src_format", C.c_uint32), ("geometry", C.c_uint32), ("dst_format", C.c_uint32),
+        ("write_kind", C.c_uint32), ("n_ops", C.c_uint32), ("n_pre_ops", C.c_uint32),
+        ("ops", Op * MAX_OPS), ("ccm", C.c_float * 9), ("yuv_sub", C.c_float * 3),
+    ]
+
+
+class PlaneDesc(C.Structure):
+    _fields_ = [
+        ("src", C.c_void_p), ("src_chroma", C.c_void_p), ("dst", C.c_void_p),
+        ("src_pitch", C.c_uint32), ("src_w", C.c_uint32), ("src_h", C.c_uint32),
+        ("crop_x", C.c_uint32), ("crop_y", C.c_uint32), ("crop_w", C.c_int32), ("crop_h", C.c_int32),
+        ("dst_w", C.c_uint32), ("dst_h", C.c_uint32), ("dst_pitch", C.c_uint32),
+        ("dst_channel_stride", C.c_uint64),
+        ("fx", C.c_float), ("fy", C.c_float),
+        ("x1", C.c_int32), ("y1", C.c_int32), ("x2", C.c_int32), ("y2", C.c_int32),
+        ("bg", C.c_float * 3), ("chain", C.c_uint32),
+        ("params", (C.c_float * 3) * MAX_PLANE_PARAMS),
+    ]
+
+
+assert C.sizeof(Op) == 16 and C.sizeof(ChainDesc) == 264 and C.sizeof(PlaneDesc) == 160
+
+LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libfkb.so")
+
+# name -> (restype, argtypes); every symbol include/fkb/fkb.h declares
+SIGNATURES = {
+    "fkb_resize_params": (C.c_int, [C.c_uint32, C.POINTER(PlaneDesc)]),
+    "fkb_validate": (C.c_int, [C.POINTER(ChainDesc), C.c_uint32, C.POINTER(PlaneDesc), C.c_uint32]),
+    "fkb_launch_transform": (C.c_int, [C.POINTER(ChainDesc), C.POINTER(PlaneDesc), C.c_uint32, C.c_void_p]),
+    "fkb_launch_divergent": (C.c_int, [C.POINTER(ChainDesc), C.c_uint32, C.POINTER(PlaneDesc), C.c_uint32, C.c_void_p]),
+    "fkb_plan_create": (C.c_int, [C.POINTER(ChainDesc), C.c_uint32, C.POINTER(PlaneDesc), C.c_uint32, C.POINTER(C.c_void_p)]),
+    "fkb_plan_launch": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "fkb_plan_destroy": (None, [C.c_void_p]),
+    "fkb_plan_kernel_launches": (C.c_uint32, [C.c_void_p]),
+    "fkb_device_status": (C.c_int, []),
+    "fkb_last_cuda_error": (C.c_int, []),
+    "fkb_status_string": (C.c_char_p, [C.c_int]),
+    "fkb_abi_version": (C.c_uint32, []),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Loads lib/libfkb.so and declares the signatures.  Raises if the library was not built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(f"{LIB_PATH} is missing: run `python -m fusedkernellibrary_b200.build` "
+                               "(there is no CPU fallback)")
+        lib = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib
+
+
+class FkbError(RuntimeError):
+    def __init__(self, status: int):
+        self.status = status
+        msg = load().fkb_status_string(status).decode()
+        if status == ERR_CUDA:
+            msg += f" (cudaError {load().fkb_last_cuda_error()})"
+        super().__init__(f"fkb status {status}: {msg}")
+
+
+def check(status: int) -> None:
+    if status != OK:
+        raise FkbError(status)

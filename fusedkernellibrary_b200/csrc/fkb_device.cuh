@@ -1,0 +1,182 @@
+// Device-side building blocks of the sm_100a transform kernels: the lowered plane record, bulk-async-copy
+// (TMA) and mbarrier wrappers with bounded waits, and the per-pixel op interpreter.
+//
+// Arithmetic contract (matches the FusedKernelLibrary CPU backend built without FMA contraction): every
+// multiply/add/sub/div goes through an explicit round-to-nearest intrinsic, so no FMA is ever formed,
+// division is IEEE, and SaturateCast is cvt.rni.sat.u8.f32 (round half to even, clamp, NaN -> 0), which is
+// what core/constexpr_libs/constexpr_saturate.h:28-150 of the reference computes.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "fkb/fkb.h"
+
+namespace fkb {
+
+enum : uint32_t { KCLASS_GATHER = 0, KCLASS_POINT = 1, KCLASS_RESIZE = 2 };
+
+// One output plane as the kernels see it: the caller's fkb_plane_desc plus what the host lowering derived
+// (which kernel path runs it, its tile shape and its first tile index).
+struct __align__(16) PlaneRec {
+    const uint8_t* src;
+    const uint8_t* src_chroma;
+    uint8_t* dst;
+    uint64_t dst_cstride;
+    uint32_t src_pitch;
+    uint32_t crop_x, crop_y;
+    int32_t crop_w, crop_h;
+    uint32_t dst_w, dst_h, dst_pitch;
+    float fx, fy;
+    int32_t x1, y1, x2, y2;
+    float bg[3];
+    uint32_t chain;
+    uint32_t kclass;
+    uint32_t tile_w, tile_h;    // output pixels per tile
+    uint32_t tiles_x, tiles_y;  // tiles per plane
+    uint32_t tile_base;         // index of this plane's first tile in the launch
+    uint32_t in_stride;         // bytes between staged source rows in shared memory (multiple of 16)
+    uint32_t out_stride;        // bytes between rows of the shared output tile (multiple of 16)
+    float params[FKB_MAX_PLANE_PARAMS][3];
+    uint32_t pad_[2];
+};
+static_assert(sizeof(PlaneRec) == 192, "layout is mirrored by the host lowering");
+static_assert(sizeof(PlaneRec) % 16 == 0, "PlaneRec is copied in 16-byte words");
+
+constexpr uint32_t kInlinePlanes = 8;  // launches of up to this many planes carry their records in the kernel parameters
+
+struct LaunchParams {
+    fkb_chain_desc chains[FKB_MAX_CHAINS];
+    const PlaneRec* table;    // device table, or null when `inline_planes` is used
+    uint32_t n_planes;
+    uint32_t n_tiles;
+    uint32_t tiles_per_plane;  // > 0 when every plane has the same number of tiles; else PlaneRec::tile_base is searched
+    int* status;
+    PlaneRec inline_planes[kInlinePlanes];
+};
+
+// ---------------------------------------------------------------------------------------------------------
+// shared-memory / mbarrier / bulk-copy wrappers
+// ---------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Waits for a phase with an iteration cap.  Returns false when the cap ran out (a lowering bug: the expected
+// byte count never arrived); the caller records it in the status word and leaves without touching the data.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+    for (uint32_t i = 0; i < (1u << 22); ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+// global -> shared bulk copy (the TMA engine, no tensor map, no multicast); completion is signalled on `bar`.
+// Both addresses and the size must be multiples of 16.
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_addr(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_addr(bar)) : "memory");
+}
+// shared -> global bulk copy, tracked by the per-thread bulk group.
+__device__ __forceinline__ void bulk_store(void* gmem_dst, const void* smem_src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                 ::"l"(gmem_dst), "r"(smem_addr(smem_src)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// make this thread's shared-memory writes visible to the async (bulk-copy) proxy
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// ---------------------------------------------------------------------------------------------------------
+// arithmetic
+// ---------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float sat_u8_as_float(float v) {
+    uint32_t r;
+    asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(r) : "f"(v));
+    return static_cast<float>(r);
+}
+
+// Runs ops[first..last) of `ch` on N pixels held in registers.  The op loop is outside the pixel loop so
+// the (uniform) decode cost is paid once per N pixels.
+template <int N>
+__device__ __forceinline__ void apply_ops(float (&v)[N][3], const fkb_chain_desc& ch, const PlaneRec& pl,
+                                          uint32_t first, uint32_t last) {
+    for (uint32_t i = first; i < last; ++i) {
+        const uint32_t code = ch.ops[i].code;
+        const int slot = ch.ops[i].plane_slot;
+        float p0, p1, p2;
+        if (slot >= 0) { p0 = pl.params[slot][0]; p1 = pl.params[slot][1]; p2 = pl.params[slot][2]; }
+        else { p0 = ch.ops[i].v[0]; p1 = ch.ops[i].v[1]; p2 = ch.ops[i].v[2]; }
+        switch (code) {
+        case FKB_OP_MUL:
+#pragma unroll
+            for (int n = 0; n < N; ++n) { v[n][0] = __fmul_rn(v[n][0], p0); v[n][1] = __fmul_rn(v[n][1], p1); v[n][2] = __fmul_rn(v[n][2], p2); }
+            break;
+        case FKB_OP_ADD:
+#pragma unroll
+            for (int n = 0; n < N; ++n) { v[n][0] = __fadd_rn(v[n][0], p0); v[n][1] = __fadd_rn(v[n][1], p1); v[n][2] = __fadd_rn(v[n][2], p2); }
+            break;
+        case FKB_OP_SUB:
+#pragma unroll
+            for (int n = 0; n < N; ++n) { v[n][0] = __fsub_rn(v[n][0], p0); v[n][1] = __fsub_rn(v[n][1], p1); v[n][2] = __fsub_rn(v[n][2], p2); }
+            break;
+        case FKB_OP_DIV:
+#pragma unroll
+            for (int n = 0; n < N; ++n) { v[n][0] = __fdiv_rn(v[n][0], p0); v[n][1] = __fdiv_rn(v[n][1], p1); v[n][2] = __fdiv_rn(v[n][2], p2); }
+            break;
+        case FKB_OP_REORDER_ZYX:
+#pragma unroll
+            for (int n = 0; n < N; ++n) { const float t = v[n][0]; v[n][0] = v[n][2]; v[n][2] = t; }
+            break;
+        case FKB_OP_YUV2RGB:
+#pragma unroll
+            for (int n = 0; n < N; ++n) {
+                const float a = __fsub_rn(v[n][0], ch.yuv_sub[0]), b = __fsub_rn(v[n][1], ch.yuv_sub[1]), d = __fsub_rn(v[n][2], ch.yuv_sub[2]);
+#pragma unroll
+                for (int c = 0; c < 3; ++c)
+                    v[n][c] = __fadd_rn(__fadd_rn(__fmul_rn(a, ch.ccm[3 * c]), __fmul_rn(b, ch.ccm[3 * c + 1])), __fmul_rn(d, ch.ccm[3 * c + 2]));
+            }
+            break;
+        case FKB_OP_SATCAST_U8:
+#pragma unroll
+            for (int n = 0; n < N; ++n) { v[n][0] = sat_u8_as_float(v[n][0]); v[n][1] = sat_u8_as_float(v[n][1]); v[n][2] = sat_u8_as_float(v[n][2]); }
+            break;
+        default: break;  // FKB_OP_CAST_F32: values are already carried as fp32
+        }
+    }
+}
+
+// Bilinear weights and tap indices of one axis, exactly as InterpolateComplete<INTER_LINEAR>::exec
+// (algorithms/image_processing/interpolation.h:70-104): floor, unclamped x2 = x1 + 1 for the weights, the
+// read index clamped to the back operation's extent.
+struct AxisTap {
+    int i0, i1;    // clamped read indices
+    float w0, w1;  // (x2 - s), (s - x1)
+};
+__device__ __forceinline__ AxisTap axis_tap(int t, float f, int extent) {
+    const float s = __fmul_rn(static_cast<float>(t), f);
+    const int a = __float2int_rd(s);
+    AxisTap r;
+    r.w0 = __fsub_rn(static_cast<float>(a + 1), s);
+    r.w1 = __fsub_rn(s, static_cast<float>(a));
+    r.i0 = min(a, extent - 1);
+    r.i1 = min(a + 1, extent - 1);
+    return r;
+}
+__device__ __forceinline__ float bilerp(float p00, float p10, float p01, float p11, float w00, float w10, float w01, float w11) {
+    return __fadd_rn(__fadd_rn(__fadd_rn(__fmul_rn(p00, w00), __fmul_rn(p10, w10)), __fmul_rn(p01, w01)), __fmul_rn(p11, w11));
+}
+
+}  // namespace fkb

@@ -1,0 +1,476 @@
+// Host side of the C ABI (include/fkb/fkb.h): descriptor validation, lowering of a launch to plane records
+// and a tile schedule, the descriptor arena, plans, and the entry points themselves.
+//
+// Reference behaviour mirrored here (paths relative to the reference's include/fused_kernel/):
+//   * executeOperations is asynchronous on the caller's stream, never synchronises, and reports launch
+//     errors right after the launch (core/execution_model/executors.h:316-351).  The reference throws
+//     std::runtime_error (core/utils/utils.h:100-114); a C ABI cannot, so every entry point returns a status.
+//   * Output geometry is the ActiveThreads of the first IOp (executors.h:316-329); here it is dst_w x dst_h of
+//     each plane.
+//   * Resize<>::build computes its parameters on the host in double and stores floats
+//     (algorithms/image_processing/resize.h:164-233, 266-278): fkb_resize_params.
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <vector>
+
+#include "fkb_device.cuh"
+#include "fkb_launch.h"
+
+namespace fkb {
+namespace {
+
+thread_local int t_last_cuda_error = 0;
+
+#define FKB_CUDA(expr)                                              \
+    do {                                                            \
+        const cudaError_t e_ = (expr);                              \
+        if (e_ != cudaSuccess) {                                    \
+            t_last_cuda_error = static_cast<int>(e_);               \
+            (void)cudaGetLastError();                               \
+            return FKB_ERR_CUDA;                                    \
+        }                                                           \
+    } while (0)
+
+enum ValueType { VT_U8 = 0, VT_F32 = 1 };
+
+// -------------------------------------------------------------------------------------------------------
+// validation
+// -------------------------------------------------------------------------------------------------------
+int check_ops(const fkb_chain_desc& ch, uint32_t first, uint32_t last, ValueType& t) {
+    for (uint32_t i = first; i < last; ++i) {
+        const fkb_op& op = ch.ops[i];
+        if (op.plane_slot >= static_cast<int>(FKB_MAX_PLANE_PARAMS) || op.plane_slot < -1) return FKB_ERR_INVALID;
+        switch (op.code) {
+        case FKB_OP_CAST_F32: if (t != VT_U8) return FKB_ERR_INVALID; t = VT_F32; break;
+        case FKB_OP_MUL: case FKB_OP_ADD: case FKB_OP_SUB: case FKB_OP_DIV: if (t != VT_F32) return FKB_ERR_INVALID; break;
+        case FKB_OP_REORDER_ZYX: break;
+        case FKB_OP_YUV2RGB: if (t != VT_U8) return FKB_ERR_INVALID; t = VT_F32; break;
+        case FKB_OP_SATCAST_U8: if (t != VT_F32) return FKB_ERR_INVALID; t = VT_U8; break;
+        default: return FKB_ERR_UNSUPPORTED;
+        }
+    }
+    return FKB_OK;
+}
+
+int check_chain(const fkb_chain_desc& ch) {
+    if (ch.src_format != FKB_PIX_U8C3 && ch.src_format != FKB_PIX_NV12) return FKB_ERR_UNSUPPORTED;
+    if (ch.dst_format != FKB_PIX_U8C3 && ch.dst_format != FKB_PIX_F32C3) return FKB_ERR_UNSUPPORTED;
+    if (ch.geometry > FKB_GEOM_RESIZE_PRESERVE_AR) return FKB_ERR_UNSUPPORTED;
+    if (ch.write_kind != FKB_WRITE_PACKED && ch.write_kind != FKB_WRITE_SPLIT) return FKB_ERR_UNSUPPORTED;
+    if (ch.n_ops > FKB_MAX_OPS || ch.n_pre_ops > ch.n_ops) return FKB_ERR_INVALID;
+    ValueType t = VT_U8;  // both reads produce uchar3
+    int rc;
+    if (ch.geometry == FKB_GEOM_NONE) {
+        if ((rc = check_ops(ch, 0, ch.n_ops, t)) != FKB_OK) return rc;
+    } else {
+        if ((rc = check_ops(ch, 0, ch.n_pre_ops, t)) != FKB_OK) return rc;
+        t = VT_F32;  // the interpolation returns float_<cn> whatever it reads
+        if ((rc = check_ops(ch, ch.n_pre_ops, ch.n_ops, t)) != FKB_OK) return rc;
+    }
+    const ValueType want = ch.dst_format == FKB_PIX_F32C3 ? VT_F32 : VT_U8;
+    return t == want ? FKB_OK : FKB_ERR_INVALID;  // the Write's input type must be the chain's output type
+}
+
+int check_plane(const fkb_chain_desc& ch, const fkb_plane_desc& pl) {
+    if (!pl.src || !pl.dst) return FKB_ERR_NULL;
+    const bool nv12 = ch.src_format == FKB_PIX_NV12;
+    if (nv12 && !pl.src_chroma) return FKB_ERR_NULL;
+    if (pl.src_w == 0 || pl.src_h == 0 || pl.dst_w == 0 || pl.dst_h == 0) return FKB_ERR_INVALID;
+    const uint64_t src_row = nv12 ? ((static_cast<uint64_t>(pl.src_w) + 1) / 2) * 2 : static_cast<uint64_t>(pl.src_w) * 3;
+    if (pl.src_pitch < src_row) return FKB_ERR_INVALID;
+    if (pl.crop_w <= 0 || pl.crop_h <= 0) return FKB_ERR_INVALID;
+    if (static_cast<uint64_t>(pl.crop_x) + static_cast<uint64_t>(pl.crop_w) > pl.src_w ||
+        static_cast<uint64_t>(pl.crop_y) + static_cast<uint64_t>(pl.crop_h) > pl.src_h) return FKB_ERR_INVALID;
+    const bool f32 = ch.dst_format == FKB_PIX_F32C3;
+    const bool split = ch.write_kind == FKB_WRITE_SPLIT;
+    const uint64_t dst_row = static_cast<uint64_t>(pl.dst_w) * (split ? (f32 ? 4 : 1) : (f32 ? 12 : 3));
+    if (pl.dst_pitch < dst_row) return FKB_ERR_INVALID;
+    if (f32 && ((reinterpret_cast<uintptr_t>(pl.dst) & 3) || (pl.dst_pitch & 3) || (pl.dst_channel_stride & 3))) return FKB_ERR_INVALID;
+    if (split && pl.dst_channel_stride < static_cast<uint64_t>(pl.dst_pitch) * (pl.dst_h - 1) + dst_row) return FKB_ERR_INVALID;
+    if (ch.geometry == FKB_GEOM_NONE) {
+        if (pl.dst_w > static_cast<uint32_t>(pl.crop_w) || pl.dst_h > static_cast<uint32_t>(pl.crop_h)) return FKB_ERR_INVALID;
+    } else {
+        if (!(pl.fx > 0.f) || !(pl.fy > 0.f) || !std::isfinite(pl.fx) || !std::isfinite(pl.fy)) return FKB_ERR_INVALID;
+        if (ch.geometry == FKB_GEOM_RESIZE_PRESERVE_AR) {
+            if (pl.x1 < 0 || pl.y1 < 0 || pl.x2 < pl.x1 || pl.y2 < pl.y1 ||
+                pl.x2 >= static_cast<int>(pl.dst_w) || pl.y2 >= static_cast<int>(pl.dst_h)) return FKB_ERR_INVALID;
+        }
+    }
+    return FKB_OK;
+}
+
+int validate(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc* planes, uint32_t n_planes) {
+    if (!chains || !planes) return FKB_ERR_NULL;
+    if (n_chains == 0 || n_chains > FKB_MAX_CHAINS || n_planes == 0) return FKB_ERR_INVALID;
+    for (uint32_t c = 0; c < n_chains; ++c) {
+        const int rc = check_chain(chains[c]);
+        if (rc != FKB_OK) return rc;
+    }
+    for (uint32_t z = 0; z < n_planes; ++z) {
+        if (planes[z].chain >= n_chains) return FKB_ERR_INVALID;
+        const int rc = check_plane(chains[planes[z].chain], planes[z]);
+        if (rc != FKB_OK) return rc;
+    }
+    return FKB_OK;
+}
+
+// -------------------------------------------------------------------------------------------------------
+// lowering
+// -------------------------------------------------------------------------------------------------------
+inline uint32_t up16(uint32_t v) { return (v + 15u) & ~15u; }
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+bool force_gather() {
+    static const bool v = [] { const char* e = std::getenv("FKB_FORCE_GATHER"); return e && e[0] == '1'; }();
+    return v;
+}
+
+// Chooses the kernel path and tile shape of one plane.
+void classify(const fkb_chain_desc& ch, PlaneRec& r) {
+    r.kclass = KCLASS_GATHER;
+    r.tile_w = r.tile_h = r.tiles_x = r.tiles_y = 0;
+    r.in_stride = r.out_stride = 0;
+    if (force_gather()) return;
+    if (ch.src_format != FKB_PIX_U8C3 || ch.write_kind != FKB_WRITE_PACKED) return;
+    if (!aligned16(r.src) || !aligned16(r.dst) || (r.src_pitch & 15) || (r.dst_pitch & 15)) return;
+    const bool f32 = ch.dst_format == FKB_PIX_F32C3;
+    const uint32_t elt = f32 ? 12u : 3u;
+
+    if (ch.geometry == FKB_GEOM_NONE) {
+        if ((r.crop_x * 3u) & 15u) return;
+        const uint32_t chunk_px = f32 ? 4u : 16u;  // pixels per thread step; its output is 48 B either way
+        const uint32_t max_chunks = kOutBytes / 48u;
+        uint32_t chunks = (r.dst_w + chunk_px - 1) / chunk_px;
+        uint32_t n_split = (chunks + max_chunks - 1) / max_chunks;
+        uint32_t tw = r.dst_w;
+        if (n_split > 1) {
+            tw = up16((r.dst_w + n_split - 1) / n_split);
+            chunks = tw / chunk_px;
+        }
+        r.tile_w = tw;
+        r.out_stride = chunks * 48u;
+        r.in_stride = up16(chunks * chunk_px * 3u);
+        uint32_t th = std::min(std::min(kOutBytes / r.out_stride, kInBytes / r.in_stride), 16u);
+        r.tile_h = std::max(1u, std::min(th, r.dst_h));
+        r.kclass = KCLASS_POINT;
+    } else {
+        for (uint32_t i = 0; i < ch.n_pre_ops; ++i)
+            if (ch.ops[i].code != FKB_OP_CAST_F32) return;  // taps are transformed before interpolation: general path
+        if (r.fx > 16.f || r.fy > 16.f) return;             // footprint too sparse to be worth staging
+        uint64_t best_area = 0;
+        for (uint32_t n_split = 1; n_split <= 32; ++n_split) {
+            const uint32_t tw = n_split == 1 ? r.dst_w : up16((r.dst_w + n_split - 1) / n_split);
+            if (n_split > 1 && tw < 32) break;
+            const uint32_t out_stride = up16(tw * elt);
+            const uint32_t cols = std::min<uint32_t>(r.crop_w, static_cast<uint32_t>(std::ceil((tw - 1) * static_cast<double>(r.fx))) + 3u);
+            const uint32_t in_stride = up16(cols * 3u) + 32u;
+            for (uint32_t th : {8u, 4u, 2u, 1u}) {
+                const uint32_t rows = std::min<uint32_t>(r.crop_h, static_cast<uint32_t>(std::ceil((th - 1) * static_cast<double>(r.fy))) + 3u);
+                if (static_cast<uint64_t>(in_stride) * rows > kInBytes || static_cast<uint64_t>(out_stride) * th > kOutBytes) continue;
+                const uint64_t area = static_cast<uint64_t>(tw) * th;
+                if (area > best_area) {
+                    best_area = area;
+                    r.tile_w = tw; r.tile_h = std::min(th, r.dst_h); r.in_stride = in_stride; r.out_stride = out_stride;
+                }
+                break;  // smaller th only shrinks the tile
+            }
+        }
+        if (!best_area) return;
+        r.kclass = KCLASS_RESIZE;
+    }
+    r.tiles_x = (r.dst_w + r.tile_w - 1) / r.tile_w;
+    r.tiles_y = (r.dst_h + r.tile_h - 1) / r.tile_h;
+}
+
+struct Lowered {
+    std::vector<PlaneRec> recs;
+    LaunchParams lp;
+    uint32_t staged_grid = 0;
+    dim3 gather_grid{0, 0, 0};
+    uint32_t kernels = 0;
+};
+
+int device_sm_count(int& sms) {
+    static int cached[64] = {0};
+    int dev = 0;
+    FKB_CUDA(cudaGetDevice(&dev));
+    if (dev < 64 && cached[dev]) { sms = cached[dev]; return FKB_OK; }
+    FKB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    if (dev < 64) cached[dev] = sms;
+    return FKB_OK;
+}
+
+int status_word(int** out) {
+    static std::mutex m;
+    static int* cached[64] = {nullptr};
+    int dev = 0;
+    FKB_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> g(m);
+    if (dev < 64 && cached[dev]) { *out = cached[dev]; return FKB_OK; }
+    int* p = nullptr;
+    FKB_CUDA(status_word_address(&p));
+    if (dev < 64) cached[dev] = p;
+    *out = p;
+    return FKB_OK;
+}
+
+int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc* planes, uint32_t n_planes, Lowered& L) {
+    const int rc = validate(chains, n_chains, planes, n_planes);
+    if (rc != FKB_OK) return rc;
+    L.recs.resize(n_planes);
+    std::memset(&L.lp, 0, sizeof(L.lp));
+    std::memcpy(L.lp.chains, chains, sizeof(fkb_chain_desc) * n_chains);
+    uint32_t n_tiles = 0, gw = 0, gh = 0, n_gather = 0;
+    bool uniform = true;
+    uint32_t first_count = 0;
+    for (uint32_t z = 0; z < n_planes; ++z) {
+        const fkb_plane_desc& s = planes[z];
+        PlaneRec& r = L.recs[z];
+        std::memset(&r, 0, sizeof(r));
+        r.src = static_cast<const uint8_t*>(s.src);
+        r.src_chroma = static_cast<const uint8_t*>(s.src_chroma);
+        r.dst = static_cast<uint8_t*>(s.dst);
+        r.dst_cstride = s.dst_channel_stride;
+        r.src_pitch = s.src_pitch;
+        r.crop_x = s.crop_x; r.crop_y = s.crop_y; r.crop_w = s.crop_w; r.crop_h = s.crop_h;
+        r.dst_w = s.dst_w; r.dst_h = s.dst_h; r.dst_pitch = s.dst_pitch;
+        r.fx = s.fx; r.fy = s.fy; r.x1 = s.x1; r.y1 = s.y1; r.x2 = s.x2; r.y2 = s.y2;
+        std::memcpy(r.bg, s.bg, sizeof(r.bg));
+        r.chain = s.chain;
+        std::memcpy(r.params, s.params, sizeof(r.params));
+        classify(chains[s.chain], r);
+        r.tile_base = n_tiles;
+        const uint32_t count = r.tiles_x * r.tiles_y;
+        if (z == 0) first_count = count; else if (count != first_count) uniform = false;
+        if (static_cast<uint64_t>(n_tiles) + count > 0xfffffff0ull) return FKB_ERR_TOO_LARGE;
+        n_tiles += count;
+        if (r.kclass == KCLASS_GATHER) { ++n_gather; gw = std::max(gw, r.dst_w); gh = std::max(gh, r.dst_h); }
+    }
+    L.lp.n_planes = n_planes;
+    L.lp.n_tiles = n_tiles;
+    L.lp.tiles_per_plane = (uniform && first_count) ? first_count : 0;
+    if (n_tiles) {
+        int sms = 0;
+        const int e = device_sm_count(sms);
+        if (e != FKB_OK) return e;
+        L.staged_grid = std::min<uint32_t>(n_tiles, 2u * static_cast<uint32_t>(sms));
+        ++L.kernels;
+    }
+    if (n_gather) {
+        L.gather_grid = dim3((gw + 127) / 128, (gh + 7) / 8, std::min<uint32_t>(n_planes, 65535u));
+        ++L.kernels;
+    }
+    return status_word(&L.lp.status);
+}
+
+int run(const Lowered& L, const LaunchParams& lp, cudaStream_t stream) {
+    if (L.staged_grid) FKB_CUDA(launch_staged(lp, L.staged_grid, stream));
+    if (L.gather_grid.x) FKB_CUDA(launch_gather(lp, L.gather_grid, stream));
+    return FKB_OK;
+}
+
+// -------------------------------------------------------------------------------------------------------
+// descriptor arena: plane records of launches too large for the kernel parameters travel through a ring of
+// pinned-host / device slots; a slot is reused only after the launch that read it has finished.
+// -------------------------------------------------------------------------------------------------------
+struct Arena {
+    static constexpr int kSlots = 4;
+    std::mutex m;
+    int device = -1;
+    size_t slot_bytes = 0;
+    uint8_t* pinned = nullptr;
+    uint8_t* dev = nullptr;
+    cudaEvent_t ev[kSlots] = {};
+    bool used[kSlots] = {};
+    int next = 0;
+
+    int ensure(size_t bytes) {
+        if (bytes <= slot_bytes) return FKB_OK;
+        for (int i = 0; i < kSlots; ++i)
+            if (used[i]) { FKB_CUDA(cudaEventSynchronize(ev[i])); used[i] = false; }
+        if (pinned) { FKB_CUDA(cudaFreeHost(pinned)); pinned = nullptr; }
+        if (dev) { FKB_CUDA(cudaFree(dev)); dev = nullptr; }
+        size_t want = 1u << 20;
+        while (want < bytes) want <<= 1;
+        FKB_CUDA(cudaMallocHost(reinterpret_cast<void**>(&pinned), want * kSlots));
+        FKB_CUDA(cudaMalloc(reinterpret_cast<void**>(&dev), want * kSlots));
+        if (!ev[0])
+            for (int i = 0; i < kSlots; ++i) FKB_CUDA(cudaEventCreateWithFlags(&ev[i], cudaEventDisableTiming));
+        slot_bytes = want;
+        return FKB_OK;
+    }
+};
+
+Arena& arena_for_current_device(int& rc) {
+    static std::mutex m;
+    static Arena arenas[64];
+    static Arena overflow;
+    int dev = 0;
+    const cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) { t_last_cuda_error = static_cast<int>(e); rc = FKB_ERR_CUDA; return overflow; }
+    rc = FKB_OK;
+    std::lock_guard<std::mutex> g(m);
+    Arena& a = dev < 64 ? arenas[dev] : overflow;
+    a.device = dev;
+    return a;
+}
+
+int launch_once(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc* planes, uint32_t n_planes,
+                cudaStream_t stream) {
+    Lowered L;
+    int rc = lower(chains, n_chains, planes, n_planes, L);
+    if (rc != FKB_OK) return rc;
+    if (n_planes <= kInlinePlanes) {
+        std::memcpy(L.lp.inline_planes, L.recs.data(), sizeof(PlaneRec) * n_planes);
+        L.lp.table = nullptr;
+        return run(L, L.lp, stream);
+    }
+    Arena& a = arena_for_current_device(rc);
+    if (rc != FKB_OK) return rc;
+    std::lock_guard<std::mutex> g(a.m);
+    const size_t bytes = sizeof(PlaneRec) * n_planes;
+    if ((rc = a.ensure(bytes)) != FKB_OK) return rc;
+    const int slot = a.next;
+    a.next = (a.next + 1) % Arena::kSlots;
+    if (a.used[slot]) { FKB_CUDA(cudaEventSynchronize(a.ev[slot])); a.used[slot] = false; }
+    uint8_t* h = a.pinned + static_cast<size_t>(slot) * a.slot_bytes;
+    uint8_t* d = a.dev + static_cast<size_t>(slot) * a.slot_bytes;
+    std::memcpy(h, L.recs.data(), bytes);
+    FKB_CUDA(cudaMemcpyAsync(d, h, bytes, cudaMemcpyHostToDevice, stream));
+    L.lp.table = reinterpret_cast<const PlaneRec*>(d);
+    rc = run(L, L.lp, stream);
+    if (rc != FKB_OK) return rc;
+    FKB_CUDA(cudaEventRecord(a.ev[slot], stream));
+    a.used[slot] = true;
+    return FKB_OK;
+}
+
+}  // namespace
+}  // namespace fkb
+
+struct fkb_plan {
+    fkb::Lowered L;
+    fkb::PlaneRec* table = nullptr;
+    int device = 0;
+};
+
+using namespace fkb;
+
+extern "C" {
+
+int fkb_resize_params(uint32_t geometry, fkb_plane_desc* pl) {
+    if (!pl) return FKB_ERR_NULL;
+    const int sw = pl->crop_w, sh = pl->crop_h;
+    const int dw = static_cast<int>(pl->dst_w), dh = static_cast<int>(pl->dst_h);
+    if (sw <= 0 || sh <= 0 || dw <= 0 || dh <= 0) return FKB_ERR_INVALID;
+    int tw = dw, th = dh;
+    if (geometry == FKB_GEOM_RESIZE_PRESERVE_AR) {
+        // compute_target_size: fit the height first, fall back to fitting the width
+        const float by_height = static_cast<float>(dh) / static_cast<float>(sh);
+        tw = static_cast<int>(std::round(by_height * static_cast<float>(sw)));
+        if (tw > dw) {
+            const float by_width = static_cast<float>(dw) / static_cast<float>(sw);
+            tw = dw;
+            th = static_cast<int>(std::round(by_width * static_cast<float>(sh)));
+        }
+    } else if (geometry != FKB_GEOM_RESIZE_IGNORE_AR) {
+        return FKB_ERR_INVALID;
+    }
+    const double cfx = static_cast<double>(tw) / static_cast<double>(sw);
+    const double cfy = static_cast<double>(th) / static_cast<double>(sh);
+    pl->fx = static_cast<float>(1.0 / cfx);
+    pl->fy = static_cast<float>(1.0 / cfy);
+    pl->x1 = (dw - tw) / 2;
+    pl->y1 = (dh - th) / 2;
+    pl->x2 = pl->x1 + tw - 1;
+    pl->y2 = pl->y1 + th - 1;
+    return FKB_OK;
+}
+
+int fkb_validate(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc* planes, uint32_t n_planes) {
+    return validate(chains, n_chains, planes, n_planes);
+}
+
+int fkb_launch_transform(const fkb_chain_desc* chain, const fkb_plane_desc* planes, uint32_t n_planes, void* cuda_stream) {
+    if (!chain || !planes) return FKB_ERR_NULL;
+    for (uint32_t z = 0; z < n_planes; ++z)
+        if (planes[z].chain != 0) return FKB_ERR_INVALID;
+    return launch_once(chain, 1, planes, n_planes, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int fkb_launch_divergent(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc* planes,
+                         uint32_t n_planes, void* cuda_stream) {
+    return launch_once(chains, n_chains, planes, n_planes, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int fkb_plan_create(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc* planes, uint32_t n_planes,
+                    fkb_plan** out) {
+    if (!out) return FKB_ERR_NULL;
+    *out = nullptr;
+    fkb_plan* plan = new (std::nothrow) fkb_plan();
+    if (!plan) return FKB_ERR_TOO_LARGE;
+    int rc = lower(chains, n_chains, planes, n_planes, plan->L);
+    if (rc != FKB_OK) { delete plan; return rc; }
+    cudaError_t e = cudaGetDevice(&plan->device);
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&plan->table), sizeof(PlaneRec) * n_planes);
+    if (e == cudaSuccess) e = cudaMemcpy(plan->table, plan->L.recs.data(), sizeof(PlaneRec) * n_planes, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        t_last_cuda_error = static_cast<int>(e);
+        (void)cudaGetLastError();
+        if (plan->table) cudaFree(plan->table);
+        delete plan;
+        return FKB_ERR_CUDA;
+    }
+    plan->L.lp.table = plan->table;
+    *out = plan;
+    return FKB_OK;
+}
+
+int fkb_plan_launch(const fkb_plan* plan, void* cuda_stream) {
+    if (!plan) return FKB_ERR_NULL;
+    return run(plan->L, plan->L.lp, static_cast<cudaStream_t>(cuda_stream));
+}
+
+void fkb_plan_destroy(fkb_plan* plan) {
+    if (!plan) return;
+    if (plan->table) cudaFree(plan->table);
+    delete plan;
+}
+
+uint32_t fkb_plan_kernel_launches(const fkb_plan* plan) { return plan ? plan->L.kernels : 0; }
+
+int fkb_device_status(void) {
+    int* w = nullptr;
+    const int rc = status_word(&w);
+    if (rc != FKB_OK) return rc;
+    FKB_CUDA(cudaDeviceSynchronize());
+    int v = 0;
+    FKB_CUDA(cudaMemcpy(&v, w, sizeof(int), cudaMemcpyDeviceToHost));
+    if (v != 0) {
+        const int zero = 0;
+        FKB_CUDA(cudaMemcpy(w, &zero, sizeof(int), cudaMemcpyHostToDevice));
+    }
+    return v;
+}
+
+int fkb_last_cuda_error(void) { return t_last_cuda_error; }
+
+const char* fkb_status_string(int status) {
+    switch (status) {
+    case FKB_OK: return "ok";
+    case FKB_ERR_NULL: return "a required pointer is null";
+    case FKB_ERR_INVALID: return "invalid descriptor";
+    case FKB_ERR_UNSUPPORTED: return "unsupported chain";
+    case FKB_ERR_CUDA: return "CUDA runtime error";
+    case FKB_ERR_TOO_LARGE: return "launch too large";
+    case FKB_ERR_DEVICE_WAIT: return "a bounded device-side wait ran out";
+    default: return "unknown status";
+    }
+}
+
+uint32_t fkb_abi_version(void) { return FKB_ABI_VERSION; }
+
+}  // extern "C"

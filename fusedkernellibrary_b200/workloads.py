@@ -1,0 +1,275 @@
+"""Seeded synthetic workloads in the shapes of the five benchmark configurations, lowered to fkb descriptors.
+
+A :class:`Workload` holds host source buffers (numpy), the chain descriptors and one :class:`PlaneSpec` per
+output plane (which source buffer, which output buffer, byte offsets, geometry).  ``bind`` turns the specs
+into an ``fkb_plane_desc`` array for a given set of buffer base addresses — host addresses for the CPU
+checker, device addresses for the CUDA library — so both run on exactly the same description.
+
+The inputs stand in for the frames the reference's examples read from disk or cameras: no public dataset is
+involved, every byte comes from ``numpy.random.RandomState(seed)``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+
+import numpy as np
+
+from . import abi
+
+BT709_FULL_8BIT = (1.0, 0.0, 1.57480001, 1.0, -0.187324256, -0.46812427, 1.0, 1.8556, 0.0)
+"""YCbCr->RGB matrix of ConvertYUVToRGB<p8bit, Full, bt709> as the reference evaluates it in fp32
+(algorithms/image_processing/itu_color.h:185-258; golden copy in
+utests/algorithm/image_processing/utest_color_conversion.h:441-447)."""
+
+
+def op(code: int, v=(0.0, 0.0, 0.0), slot: int = -1) -> abi.Op:
+    o = abi.Op()
+    o.code, o.plane_slot = code, slot
+    o.v[:] = [float(np.float32(x)) for x in v]
+    return o
+
+
+def chain(src_format, geometry, dst_format, write_kind, ops, n_pre_ops=0, ccm=None, yuv_sub=None) -> abi.ChainDesc:
+    ch = abi.ChainDesc()
+    ch.src_format, ch.geometry, ch.dst_format, ch.write_kind = src_format, geometry, dst_format, write_kind
+    ch.n_ops, ch.n_pre_ops = len(ops), n_pre_ops
+    for i, o in enumerate(ops):
+        ch.ops[i] = o
+    if ccm is not None:
+        ch.ccm[:] = ccm
+    if yuv_sub is not None:
+        ch.yuv_sub[:] = yuv_sub
+    return ch
+
+
+@dataclass
+class PlaneSpec:
+    src: int                     # index into Workload.sources
+    dst: int                     # index into Workload.out_sizes
+    dst_offset: int              # byte offset of this plane inside the output buffer
+    src_w: int
+    src_h: int
+    src_pitch: int
+    crop: tuple                  # (x, y, w, h)
+    dst_w: int
+    dst_h: int
+    dst_pitch: int
+    chain: int = 0
+    dst_channel_stride: int = 0
+    bg: tuple = (0.0, 0.0, 0.0)
+    params: tuple = ()           # up to four float3 operands
+    chroma_offset: int = 0       # NV12: byte offset of the UV rows inside the source buffer
+
+
+@dataclass
+class Workload:
+    name: str
+    chains: list
+    sources: list                # list of np.uint8 arrays (flat)
+    out_sizes: list              # bytes of each output buffer
+    planes: list                 # list of PlaneSpec
+    description: str = ""
+    extra: dict = field(default_factory=dict)
+
+    @property
+    def out_pixels(self) -> int:
+        return sum(p.dst_w * p.dst_h for p in self.planes)
+
+    def chain_array(self):
+        arr = (abi.ChainDesc * len(self.chains))()
+        for i, c in enumerate(self.chains):
+            arr[i] = c
+        return arr
+
+    def bind(self, src_addrs, dst_addrs, resize_params=None):
+        """Returns (fkb_plane_desc * n) with pointers set.  ``resize_params(geometry, plane_ptr)`` fills the
+        resize factors (the library's fkb_resize_params by default)."""
+        if resize_params is None:
+            resize_params = abi.load().fkb_resize_params
+        arr = (abi.PlaneDesc * len(self.planes))()
+        for i, s in enumerate(self.planes):
+            d = arr[i]
+            ch = self.chains[s.chain]
+            d.src = src_addrs[s.src]
+            d.src_chroma = src_addrs[s.src] + s.chroma_offset if ch.src_format == abi.PIX_NV12 else None
+            d.dst = dst_addrs[s.dst] + s.dst_offset
+            d.src_pitch, d.src_w, d.src_h = s.src_pitch, s.src_w, s.src_h
+            d.crop_x, d.crop_y, d.crop_w, d.crop_h = s.crop
+            d.dst_w, d.dst_h, d.dst_pitch = s.dst_w, s.dst_h, s.dst_pitch
+            d.dst_channel_stride = s.dst_channel_stride
+            d.bg[:] = s.bg
+            d.chain = s.chain
+            for k, pv in enumerate(s.params):
+                d.params[k][:] = pv
+            if ch.geometry != abi.GEOM_NONE:
+                rc = resize_params(ch.geometry, C.byref(d))
+                if rc != 0:
+                    raise ValueError(f"resize params failed for plane {i}: {rc}")
+        return arr
+
+    # -- algorithmic bytes ---------------------------------------------------------------------------------
+    def algorithmic_bytes(self) -> dict:
+        """Distinct source bytes addressed by at least one tap of the launch (deduplicated per source buffer)
+        plus output bytes written.  Background pixels address nothing."""
+        lib = abi.load()
+        masks = {}
+        out_bytes = 0
+        for s in self.planes:
+            ch = self.chains[s.chain]
+            nv12 = ch.src_format == abi.PIX_NV12
+            elt = 12 if ch.dst_format == abi.PIX_F32C3 else 3
+            out_bytes += s.dst_w * s.dst_h * elt
+            if s.src not in masks:
+                masks[s.src] = (np.zeros((s.src_h, s.src_w), bool),
+                                np.zeros(((s.src_h + 1) // 2, (s.src_w + 1) // 2), bool) if nv12 else None)
+            cx, cy, cw, chh = s.crop
+            if ch.geometry == abi.GEOM_NONE:
+                cols = np.arange(s.dst_w) + cx
+                rows = np.arange(s.dst_h) + cy
+            else:
+                d = abi.PlaneDesc()
+                d.crop_w, d.crop_h, d.dst_w, d.dst_h = cw, chh, s.dst_w, s.dst_h
+                lib.fkb_resize_params(ch.geometry, C.byref(d))
+                tw, th = d.x2 - d.x1 + 1, d.y2 - d.y1 + 1
+
+                def taps(n, f, extent):
+                    s_ = np.arange(n, dtype=np.float32) * np.float32(f)
+                    a = np.floor(s_).astype(np.int64)
+                    return np.unique(np.concatenate([np.minimum(a, extent - 1), np.minimum(a + 1, extent - 1)]))
+                cols = taps(tw, d.fx, cw) + cx
+                rows = taps(th, d.fy, chh) + cy
+            m, muv = masks[s.src]
+            m[np.ix_(rows, cols)] = True
+            if nv12:
+                muv[np.ix_(np.unique(rows >> 1), np.unique(cols >> 1))] = True
+        src_bytes = 0
+        for m, muv in masks.values():
+            src_bytes += int(m.sum()) * (1 if muv is not None else 3)
+            if muv is not None:
+                src_bytes += int(muv.sum()) * 2
+        return {"src": src_bytes, "dst": out_bytes, "total": src_bytes + out_bytes}
+
+
+def _frame(seed: int, nbytes: int, lo: int = 0, hi: int = 256) -> np.ndarray:
+    return np.random.RandomState(seed).randint(lo, hi, size=nbytes, dtype=np.uint8)
+
+
+def _pitch(row_bytes: int, align: int) -> int:
+    return (row_bytes + align - 1) // align * align
+
+
+# ------------------------------------------------------------------------------------------------------------
+# the five configurations (every size is a parameter so tests can run reduced versions)
+# ------------------------------------------------------------------------------------------------------------
+README_CROPS = ((300, 125, 60, 40), (400, 125, 60, 40), (530, 270, 130, 140), (560, 115, 100, 35), (572, 196, 40, 15))
+
+
+def readme_crops(w=1920, h=1080, crops=README_CROPS, dst=(128, 64), seed=1, pitch_align=16) -> Workload:
+    """Config 1: one uchar3 frame, crops -> Resize PRESERVE_AR (bg 0) -> Mul 2 -> Sub 128 -> SaturateCast ->
+    TensorWrite<uchar3>.  The reference program is tests/examples/readme_test_code.h:26-106."""
+    pitch = _pitch(w * 3, pitch_align)
+    ch = chain(abi.PIX_U8C3, abi.GEOM_RESIZE_PRESERVE_AR, abi.PIX_U8C3, abi.WRITE_PACKED,
+               [op(abi.OP_MUL, (2, 2, 2)), op(abi.OP_SUB, (128, 128, 128)), op(abi.OP_SATCAST_U8)])
+    dw, dh = dst
+    planes = [PlaneSpec(0, 0, i * dw * dh * 3, w, h, pitch, c, dw, dh, dw * 3, bg=(0.0, 0.0, 0.0)) for i, c in enumerate(crops)]
+    return Workload("readme_crops", [ch], [_frame(seed, pitch * h)], [dw * dh * 3 * len(crops)], planes,
+                    f"{len(crops)} crops of one {w}x{h} uchar3 frame -> {dw}x{dh} uchar3 tensor")
+
+
+def vertical_fusion(w=3840, h=2160, seed=2, pitch_align=16, dst_pitch_align=16) -> Workload:
+    """Config 2: Cast -> Mul -> Add -> Div -> BGR2RGB -> SaturateCast on every pixel, uchar3 -> uchar3."""
+    pitch, dpitch = _pitch(w * 3, pitch_align), _pitch(w * 3, dst_pitch_align)
+    ch = chain(abi.PIX_U8C3, abi.GEOM_NONE, abi.PIX_U8C3, abi.WRITE_PACKED,
+               [op(abi.OP_CAST_F32), op(abi.OP_MUL, (0.5, 1.5, 2.0)), op(abi.OP_ADD, (10, -20, 5)),
+                op(abi.OP_DIV, (1.7, 1.7, 1.7)), op(abi.OP_REORDER_ZYX), op(abi.OP_SATCAST_U8)])
+    planes = [PlaneSpec(0, 0, 0, w, h, pitch, (0, 0, w, h), w, h, dpitch)]
+    return Workload("vertical_fusion", [ch], [_frame(seed, pitch * h)], [dpitch * h], planes,
+                    f"{w}x{h} uchar3 -> uchar3, six fused element-wise ops")
+
+
+def nv12_preprocess(w=3840, h=2160, dst=(640, 640), seed=3, pitch_align=16) -> Workload:
+    """Config 3: ReadYUV<NV12> -> ConvertYUVToRGB<p8bit,Full,bt709> -> Resize IGNORE_AR -> Sub mean -> Div std ->
+    TensorSplit<float3> (planar CHW fp32)."""
+    pitch = _pitch(w, pitch_align)
+    dw, dh = dst
+    ch = chain(abi.PIX_NV12, abi.GEOM_RESIZE_IGNORE_AR, abi.PIX_F32C3, abi.WRITE_SPLIT,
+               [op(abi.OP_YUV2RGB), op(abi.OP_SUB, (123.675, 116.28, 103.53)), op(abi.OP_DIV, (58.395, 57.12, 57.375))],
+               n_pre_ops=1, ccm=BT709_FULL_8BIT, yuv_sub=(0.0, 128.0, 128.0))
+    planes = [PlaneSpec(0, 0, 0, w, h, pitch, (0, 0, w, h), dw, dh, dw * 4, dst_channel_stride=dw * dh * 4,
+                        chroma_offset=pitch * h)]
+    return Workload("nv12_preprocess", [ch], [_frame(seed, pitch * (h + h // 2), 16, 236)], [dw * dh * 12], planes,
+                    f"NV12 {w}x{h} -> planar fp32 3x{dh}x{dw}")
+
+
+def random_rects(n, w, h, lo, hi, rs: np.random.RandomState):
+    """x,y uniform in the frame, w,h uniform in [lo,hi], clipped to the frame."""
+    out = []
+    for _ in range(n):
+        x, y = int(rs.randint(0, w)), int(rs.randint(0, h))
+        cw, ch = int(rs.randint(lo, hi + 1)), int(rs.randint(lo, hi + 1))
+        out.append((x, y, min(cw, w - x), min(ch, h - y)))
+    return out
+
+
+def batched_crop_resize(n_frames=64, crops_per_frame=32, w=1920, h=1080, dst=(224, 224), crop_range=(16, 512),
+                        seed=4, pitch_align=16, frame_seed_base=1000) -> Workload:
+    """Config 4: per frame, random crops -> Resize PRESERVE_AR (bg 114) -> Mul 1/255 -> TensorWrite<float3>."""
+    pitch = _pitch(w * 3, pitch_align)
+    dw, dh = dst
+    ch = chain(abi.PIX_U8C3, abi.GEOM_RESIZE_PRESERVE_AR, abi.PIX_F32C3, abi.WRITE_PACKED,
+               [op(abi.OP_MUL, (1.0 / 255.0,) * 3)])
+    rs = np.random.RandomState(seed)
+    rects = random_rects(n_frames * crops_per_frame, w, h, crop_range[0], crop_range[1], rs)
+    planes = [PlaneSpec(i // crops_per_frame, 0, i * dw * dh * 12, w, h, pitch, r, dw, dh, dw * 12, bg=(114.0, 114.0, 114.0))
+              for i, r in enumerate(rects)]
+    sources = [_frame(frame_seed_base + f, pitch * h) for f in range(n_frames)]
+    return Workload("batched_crop_resize", [ch], sources, [dw * dh * 12 * len(planes)], planes,
+                    f"{n_frames} frames {w}x{h} uchar3 x {crops_per_frame} crops -> {dw}x{dh} float3 tensor",
+                    extra={"n_frames": n_frames, "crops_per_frame": crops_per_frame})
+
+
+def divergent_planes(n_per_seq=4, w=3840, h=2160, seed=5, pitch_align=16) -> Workload:
+    """Config 5: one launch over 2n planes.  Planes [0,n): Resize IGNORE_AR to w/2 x h/2 -> SaturateCast -> uchar3
+    tensor.  Planes [n,2n): Cast -> Mul scale_i -> Sub offset_i -> float3 written at the global plane index of a
+    2n-plane tensor (as DivergentBatchTransformDPP passes the global z through)."""
+    pitch = _pitch(w * 3, pitch_align)
+    dw, dh = w // 2, h // 2
+    c0 = chain(abi.PIX_U8C3, abi.GEOM_RESIZE_IGNORE_AR, abi.PIX_U8C3, abi.WRITE_PACKED, [op(abi.OP_SATCAST_U8)])
+    c1 = chain(abi.PIX_U8C3, abi.GEOM_NONE, abi.PIX_F32C3, abi.WRITE_PACKED,
+               [op(abi.OP_CAST_F32), op(abi.OP_MUL, slot=0), op(abi.OP_SUB, slot=1)])
+    rs = np.random.RandomState(seed)
+    scales = rs.uniform(0.5, 2.0, n_per_seq).astype(np.float32)
+    offs = rs.uniform(0.0, 64.0, n_per_seq).astype(np.float32)
+    planes = []
+    for i in range(n_per_seq):
+        planes.append(PlaneSpec(i, 0, i * dw * dh * 3, w, h, pitch, (0, 0, w, h), dw, dh, dw * 3, chain=0))
+    for i in range(n_per_seq):
+        z = n_per_seq + i
+        planes.append(PlaneSpec(z, 1, z * w * h * 12, w, h, pitch, (0, 0, w, h), w, h, w * 12, chain=1,
+                                params=((float(scales[i]),) * 3, (float(offs[i]),) * 3)))
+    sources = [_frame(seed * 100 + f, pitch * h) for f in range(2 * n_per_seq)]
+    return Workload("divergent_planes", [c0, c1], sources, [dw * dh * 3 * n_per_seq, w * h * 12 * 2 * n_per_seq], planes,
+                    f"{2 * n_per_seq} uchar3 {w}x{h} planes, two chains in one launch",
+                    extra={"scales": scales, "offs": offs})
+
+
+def crop_reorder(n=3, w=640, h=360, crop_size=(100, 60), seed=6, pitch_align=16) -> Workload:
+    """Integer-only chain: crops -> BGR2RGB on uchar3 -> TensorWrite<uchar3> (must be bit-exact)."""
+    pitch = _pitch(w * 3, pitch_align)
+    cw, chh = crop_size
+    ch = chain(abi.PIX_U8C3, abi.GEOM_NONE, abi.PIX_U8C3, abi.WRITE_PACKED, [op(abi.OP_REORDER_ZYX)])
+    rs = np.random.RandomState(seed)
+    rects = [(int(rs.randint(0, w - cw + 1)), int(rs.randint(0, h - chh + 1)), cw, chh) for _ in range(n)]
+    planes = [PlaneSpec(0, 0, i * cw * chh * 3, w, h, pitch, r, cw, chh, cw * 3) for i, r in enumerate(rects)]
+    return Workload("crop_reorder", [ch], [_frame(seed, pitch * h)], [cw * chh * 3 * n], planes,
+                    f"{n} crops {cw}x{chh} of a {w}x{h} uchar3 frame, channel reorder only")
+
+
+CONFIGS = {
+    "readme_crops": readme_crops,
+    "vertical_fusion": vertical_fusion,
+    "nv12_preprocess": nv12_preprocess,
+    "batched_crop_resize": batched_crop_resize,
+    "divergent_planes": divergent_planes,
+}

@@ -1,0 +1,171 @@
+/*
+ * fkb.h — C ABI of the B200 (sm_100a) fused image-transform kernels.
+ *
+ * FusedKernelLibrary (FKL) is header-only C++: it has no ABI of its own.  A user lists
+ * `Op::build(...)` objects and calls `fk::executeOperations<TransformDPP<>>(stream, iops...)`
+ * (include/fused_kernel/fused_kernel.h:22-54); the type system turns the list into one templated
+ * kernel (core/execution_model/executor_details/executor_kernels.h:20-30).  This header is the
+ * boundary that sits beneath that source-level API in this library: the C++ front end
+ * (include/fused_kernel_b200/) lowers a built chain to the plain structs below and calls one of the
+ * `fkb_launch_*` entry points.  Every struct is POD, every pointer is a plain device (or host)
+ * address, no C++ or torch type crosses the boundary, and no entry point throws.
+ *
+ * What each piece replaces in the reference (paths relative to include/fused_kernel/):
+ *   fkb_chain_desc   — the *types* of the IOps of one chain, i.e. the template argument list of
+ *                      launchTransformDPP_Kernel (executor_kernels.h:26-30).
+ *   fkb_plane_desc   — the *values*: one OperationData per batch plane as held by BatchRead
+ *                      (core/execution_model/operation_model/batch_operations.h:101-105, 205-212):
+ *                      RawPtr of the frame (core/data/rawptr.h:135-141), Crop rect
+ *                      (algorithms/image_processing/crop.h:36-39), ResizeParams
+ *                      (algorithms/image_processing/resize.h:44-58), and the RawPtr of the write
+ *                      (algorithms/basic_ops/memory_operations.h:85-107, 160-212).
+ *   fkb_launch_transform  — Executor<TransformDPP<GPU_NVIDIA>>::executeOperations_helper
+ *                      (core/execution_model/executors.h:316-351).
+ *   fkb_launch_divergent  — Executor<DivergentBatchTransformDPP<GPU_NVIDIA,Sel>>::executeOperations
+ *                      (executors.h:360-411); the selector result is stored per plane
+ *                      (fkb_plane_desc.chain, 0-based like Selector::at, data_parallel_patterns.h:322-331).
+ *   fkb_resize_params — the host arithmetic of Resize<>::build (resize.h:164-233, 266-278).
+ *
+ * Arithmetic contract: every value inside a chain is carried as three fp32 numbers; the order of
+ * operations is the reference's, without FMA contraction, with IEEE division, and
+ * SaturateCast rounds half to even (core/constexpr_libs/constexpr_saturate.h:28-150).  Results are
+ * bit-identical to the reference CPU backend compiled with -O2 -ffp-contract=off.
+ */
+#ifndef FKB_FKB_H
+#define FKB_FKB_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FKB_ABI_VERSION 1u
+#define FKB_MAX_OPS 12u          /* compute ops per chain */
+#define FKB_MAX_PLANE_PARAMS 4u  /* per-plane float3 operands a chain may refer to */
+#define FKB_MAX_CHAINS 8u        /* chains of one divergent launch */
+
+/* Status codes.  0 is success; everything else is negative.  fkb_status_string() names them. */
+enum {
+    FKB_OK = 0,
+    FKB_ERR_NULL = -1,          /* a required pointer is null */
+    FKB_ERR_INVALID = -2,       /* a descriptor is inconsistent (sizes, pitches, rect outside the frame ...) */
+    FKB_ERR_UNSUPPORTED = -3,   /* well-formed, but not a chain these kernels implement */
+    FKB_ERR_CUDA = -4,          /* a CUDA runtime call failed; fkb_last_cuda_error() has the code */
+    FKB_ERR_TOO_LARGE = -5,     /* more planes / bytes than the entry point accepts */
+    FKB_ERR_DEVICE_WAIT = -6    /* a bounded device-side wait gave up (reported by fkb_device_status) */
+};
+
+/* Pixel formats.  A source is U8C3 (PerThreadRead<_2D,uchar3>, memory_operations.h:27-38) or NV12
+ * (ReadYUV<NV12>, algorithms/image_processing/color_conversion.h:219-238).  A destination is U8C3 or F32C3. */
+enum { FKB_PIX_U8C3 = 1, FKB_PIX_F32C3 = 2, FKB_PIX_NV12 = 3 };
+
+/* Geometry of the ReadBack stage.  The crop rectangle is always applied (a chain without Crop
+ * passes the whole frame as the rectangle).  NONE: output pixel (x,y) reads crop pixel (x,y).
+ * RESIZE_*: bilinear INTER_LINEAR through the parameters of fkb_resize_params. */
+enum { FKB_GEOM_NONE = 0, FKB_GEOM_RESIZE_IGNORE_AR = 1, FKB_GEOM_RESIZE_PRESERVE_AR = 2 };
+
+/* Write kinds.  PACKED: interleaved pixels in pitched rows — PerThreadWrite<_2D,T> and
+ * TensorWrite<T> (memory_operations.h:85-107, 160-179).  SPLIT: TensorSplit<float3>
+ * (memory_operations.h:182-212): channel c of pixel (x,y) at dst + c*dst_channel_stride + y*dst_pitch + x*4. */
+enum { FKB_WRITE_PACKED = 1, FKB_WRITE_SPLIT = 2 };
+
+/* Compute ops.  The value type is tracked like the reference's Input/OutputType: it starts as
+ * uchar3, ops that need float3 are rejected on uchar3 and vice versa. */
+enum {
+    FKB_OP_CAST_F32 = 1,     /* Cast<uchar3,float3>            (basic_ops/cast.h:22-33)            u8 -> f32 */
+    FKB_OP_MUL = 2,          /* Mul<float3>: in * v            (basic_ops/arithmetic.h:23-137)     f32 */
+    FKB_OP_ADD = 3,          /* Add<float3>: in + v                                                f32 */
+    FKB_OP_SUB = 4,          /* Sub<float3>: in - v                                                f32 */
+    FKB_OP_DIV = 5,          /* Div<float3>: in / v, IEEE                                          f32 */
+    FKB_OP_REORDER_ZYX = 6,  /* ColorConversion<COLOR_BGR2RGB|COLOR_RGB2BGR> = VectorReorder<T,2,1,0>
+                                (color_conversion.h:473-476, basic_ops/vector_ops.h:43-56)         any */
+    FKB_OP_YUV2RGB = 7,      /* ConvertYUVToRGB<p8bit,CR,CP> (color_conversion.h:150-174): subtracts
+                                chain.yuv_sub, multiplies by chain.ccm rows, sums (x+y)+z          u8 -> f32 */
+    FKB_OP_SATCAST_U8 = 8    /* SaturateCast<float3,uchar3>    (image_processing/saturate.h:25-36) f32 -> u8 */
+};
+
+typedef struct fkb_op {
+    uint16_t code;       /* FKB_OP_* */
+    int16_t plane_slot;  /* -1: operand is v[]; k >= 0: operand is planes[z].params[k] (per-plane values, as
+                            when the op was fused into each plane's Read with .then()) */
+    float v[3];
+} fkb_op;
+
+typedef struct fkb_chain_desc {
+    uint32_t src_format;  /* FKB_PIX_U8C3 | FKB_PIX_NV12 */
+    uint32_t geometry;    /* FKB_GEOM_* */
+    uint32_t dst_format;  /* FKB_PIX_U8C3 | FKB_PIX_F32C3 */
+    uint32_t write_kind;  /* FKB_WRITE_* */
+    uint32_t n_ops;       /* <= FKB_MAX_OPS */
+    uint32_t n_pre_ops;   /* ops[0..n_pre_ops) were fused into the Read: with a RESIZE geometry they run on each of
+                             the four source taps before the interpolation; the rest run on the interpolated value */
+    fkb_op ops[FKB_MAX_OPS];
+    float ccm[9];         /* FKB_OP_YUV2RGB: row-major 3x3 (algorithms/image_processing/itu_color.h:185-258) */
+    float yuv_sub[3];     /* FKB_OP_YUV2RGB: subtracted from (Y,U,V) first; Full range 8 bit = (0,128,128) */
+} fkb_chain_desc;
+
+typedef struct fkb_plane_desc {
+    const void* src;         /* first byte of the source frame (Y plane for NV12) */
+    const void* src_chroma;  /* NV12: first byte of the interleaved UV rows (reference: src + pitch*height); else null */
+    void* dst;               /* first byte of this plane of the output */
+    uint32_t src_pitch;      /* bytes between source rows (NV12: shared by the Y and the UV rows) */
+    uint32_t src_w, src_h;   /* frame size in pixels */
+    uint32_t crop_x, crop_y; /* Rect (core/data/rect.h:23-32): origin unsigned ... */
+    int32_t crop_w, crop_h;  /* ... extent signed; must lie inside the frame */
+    uint32_t dst_w, dst_h;   /* pixels this plane writes */
+    uint32_t dst_pitch;      /* bytes between destination rows */
+    uint64_t dst_channel_stride; /* FKB_WRITE_SPLIT: bytes between channel planes; else 0 */
+    float fx, fy;            /* ResizeParams::src_conv_factors (resize.h:44-58) */
+    int32_t x1, y1, x2, y2;  /* PRESERVE_AR: inclusive rectangle of the resized image inside dst */
+    float bg[3];             /* PRESERVE_AR: ResizeParams::defaultValue outside that rectangle */
+    uint32_t chain;          /* divergent launch: which chain runs on this plane (0-based); else 0 */
+    float params[FKB_MAX_PLANE_PARAMS][3]; /* operands of ops whose plane_slot >= 0 */
+} fkb_plane_desc;
+
+/* Fills plane->fx, fy, x1, y1, x2, y2 from plane->crop_w/crop_h (the size of the back operation) and
+ * plane->dst_w/dst_h, exactly as Resize<INTER_LINEAR,AR>::build does on the host (resize.h:164-233 for
+ * PRESERVE_AR, 266-278 for IGNORE_AR).  geometry = FKB_GEOM_RESIZE_*. */
+int fkb_resize_params(uint32_t geometry, fkb_plane_desc* plane);
+
+/* Host-only check of a launch: pointer, size, pitch, rectangle, type-flow and chain-index rules.
+ * Launches run it first and return its code.  Needs no GPU. */
+int fkb_validate(const fkb_chain_desc* chains, uint32_t n_chains,
+                 const fkb_plane_desc* planes, uint32_t n_planes);
+
+/* One fused launch of `chain` over n_planes planes (plane z uses planes[z]); replaces
+ * executeOperations<TransformDPP<>> (executors.h:316-351).  `planes` is a host array, copied before the
+ * call returns.  Asynchronous on `cuda_stream` (a cudaStream_t; null = legacy default stream), on the
+ * current device; the caller keeps src/dst alive until the stream has run the work. */
+int fkb_launch_transform(const fkb_chain_desc* chain, const fkb_plane_desc* planes,
+                         uint32_t n_planes, void* cuda_stream);
+
+/* One fused launch where plane z runs chains[planes[z].chain]; replaces
+ * Executor<DivergentBatchTransformDPP<>>::executeOperations (executors.h:360-411). */
+int fkb_launch_divergent(const fkb_chain_desc* chains, uint32_t n_chains,
+                         const fkb_plane_desc* planes, uint32_t n_planes, void* cuda_stream);
+
+/* A plan keeps the lowered launch (descriptor table, tile schedule) resident on the device so that a
+ * pipeline that repeats the same launch pays the lowering once.  fkb_plan_launch is asynchronous.
+ * The reference rebuilds its IOps on every call (executors.h:53-58); a plan is the same launch, cached. */
+typedef struct fkb_plan fkb_plan;
+int fkb_plan_create(const fkb_chain_desc* chains, uint32_t n_chains,
+                    const fkb_plane_desc* planes, uint32_t n_planes, fkb_plan** out);
+int fkb_plan_launch(const fkb_plan* plan, void* cuda_stream);
+void fkb_plan_destroy(fkb_plan* plan);
+/* Kernel launches one fkb_plan_launch issues (for launch accounting). */
+uint32_t fkb_plan_kernel_launches(const fkb_plan* plan);
+
+/* Reads and clears the device-side status word of the current device (synchronises the device).
+ * 0, or FKB_ERR_DEVICE_WAIT when a bounded wait on a bulk copy ran out in some earlier launch. */
+int fkb_device_status(void);
+
+/* cudaError_t of the most recent failing CUDA call on this thread (0 if none). */
+int fkb_last_cuda_error(void);
+const char* fkb_status_string(int status);
+uint32_t fkb_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FKB_FKB_H */

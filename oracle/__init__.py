@@ -1,0 +1,132 @@
+"""TEST INFRASTRUCTURE — Python loaders for the two CPU checkers.  Only tests/, the smoke check and the benchmark's
+CPU-baseline / reference arm may import this package; the product (fusedkernellibrary_b200) never does.
+
+* ``liboracle.so``        — the restatement (oracle/fkb_oracle.cpp); always available (built by oracle/Makefile).
+* ``_ref/libfkl_ref.so``  — the reference's own CPU backend compiled from its headers (oracle/ref_runner.cpp);
+                            present when it was built where the reference is installed.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+from fusedkernellibrary_b200 import abi
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ORACLE_SO = os.path.join(HERE, "liboracle.so")
+REF_SO = os.path.join(HERE, "_ref", "libfkl_ref.so")
+
+_oracle = None
+_ref = None
+
+
+def build() -> None:
+    """Compiles both checkers (the reference one only if its headers are present)."""
+    subprocess.run(["make", "-s", "-C", HERE], check=True)
+
+
+def load_oracle() -> C.CDLL:
+    global _oracle
+    if _oracle is None:
+        if not os.path.exists(ORACLE_SO):
+            build()
+        lib = C.CDLL(ORACLE_SO)
+        lib.fkb_oracle_resize_params.restype = C.c_int
+        lib.fkb_oracle_resize_params.argtypes = [C.c_uint32, C.POINTER(abi.PlaneDesc)]
+        lib.fkb_oracle_run.restype = C.c_int
+        lib.fkb_oracle_run.argtypes = [C.POINTER(abi.ChainDesc), C.c_uint32, C.POINTER(abi.PlaneDesc), C.c_uint32, C.c_uint32]
+        lib.fkb_oracle_saturate_u8.restype = C.c_uint8
+        lib.fkb_oracle_saturate_u8.argtypes = [C.c_float]
+        lib.fkb_oracle_round_half_away.restype = C.c_float
+        lib.fkb_oracle_round_half_away.argtypes = [C.c_float]
+        _oracle = lib
+    return _oracle
+
+
+def have_ref() -> bool:
+    return os.path.exists(REF_SO)
+
+
+def load_ref() -> C.CDLL:
+    global _ref
+    if _ref is None:
+        lib = C.CDLL(REF_SO)
+        u8p, f32p, i32p, pp = C.POINTER(C.c_uint8), C.POINTER(C.c_float), C.POINTER(C.c_int32), C.POINTER(C.c_void_p)
+        lib.fklref_crop_resize_u8.argtypes = [pp, C.c_int, C.c_int, C.c_int, i32p, C.c_int, C.c_int, C.c_int, f32p, f32p, f32p, C.c_void_p, C.c_int]
+        lib.fklref_crop_resize_f32.argtypes = [pp, C.c_int, C.c_int, C.c_int, i32p, C.c_int, C.c_int, C.c_int, f32p, f32p, C.c_void_p, C.c_int]
+        lib.fklref_crop_reorder_u8.argtypes = [pp, C.c_int, C.c_int, C.c_int, i32p, C.c_int, C.c_void_p, C.c_int]
+        lib.fklref_pointwise_u8.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, f32p, f32p, f32p, C.c_void_p, C.c_int]
+        lib.fklref_nv12_resize_split.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, f32p, f32p, C.c_void_p]
+        lib.fklref_divergent.argtypes = [pp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, f32p, f32p, C.c_void_p, C.c_void_p, C.c_int]
+        lib.fklref_bt709_full_matrix.argtypes = [f32p]
+        lib.fklref_saturate_u8.restype = C.c_uint8
+        lib.fklref_saturate_u8.argtypes = [C.c_float]
+        lib.fklref_resize_params.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, f32p, i32p]
+        for name in ("fklref_crop_resize_u8", "fklref_crop_resize_f32", "fklref_crop_reorder_u8", "fklref_pointwise_u8",
+                     "fklref_nv12_resize_split", "fklref_divergent"):
+            getattr(lib, name).restype = C.c_int
+        _ref = lib
+    return _ref
+
+
+def _f3(v):
+    return (C.c_float * 3)(*[float(x) for x in v])
+
+
+def run_oracle(wl, threads: int = 1):
+    """Runs a Workload through the restatement on host memory.  Returns one uint8 array per output buffer."""
+    lib = load_oracle()
+    outs = [np.zeros(n, np.uint8) for n in wl.out_sizes]
+    planes = wl.bind([s.ctypes.data for s in wl.sources], [o.ctypes.data for o in outs],
+                     resize_params=lib.fkb_oracle_resize_params)
+    rc = lib.fkb_oracle_run(wl.chain_array(), len(wl.chains), planes, len(wl.planes), threads)
+    if rc != 0:
+        raise RuntimeError(f"oracle returned {rc}")
+    return outs
+
+
+def run_ref(wl, threads: int = 1):
+    """Runs a Workload of one of the known configuration shapes through the reference CPU backend."""
+    lib = load_ref()
+    outs = [np.zeros(n, np.uint8) for n in wl.out_sizes]
+    p0 = wl.planes[0]
+    n = len(wl.planes)
+
+    def frame_ptrs(specs):
+        return (C.c_void_p * len(specs))(*[wl.sources[s.src].ctypes.data for s in specs])
+
+    def rects(specs):
+        flat = [v for s in specs for v in s.crop]
+        return (C.c_int32 * len(flat))(*flat)
+
+    ch = wl.chains[0]
+    if wl.name == "readme_crops":
+        rc = lib.fklref_crop_resize_u8(frame_ptrs(wl.planes), p0.src_w, p0.src_h, p0.src_pitch, rects(wl.planes), n,
+                                       p0.dst_w, p0.dst_h, _f3(p0.bg), _f3(ch.ops[0].v), _f3(ch.ops[1].v),
+                                       outs[0].ctypes.data, threads)
+    elif wl.name == "batched_crop_resize":
+        rc = lib.fklref_crop_resize_f32(frame_ptrs(wl.planes), p0.src_w, p0.src_h, p0.src_pitch, rects(wl.planes), n,
+                                        p0.dst_w, p0.dst_h, _f3(p0.bg), _f3(ch.ops[0].v), outs[0].ctypes.data, threads)
+    elif wl.name == "crop_reorder":
+        rc = lib.fklref_crop_reorder_u8(frame_ptrs(wl.planes), p0.src_w, p0.src_h, p0.src_pitch, rects(wl.planes), n,
+                                        outs[0].ctypes.data, threads)
+    elif wl.name == "vertical_fusion":
+        rc = lib.fklref_pointwise_u8(wl.sources[0].ctypes.data, p0.src_w, p0.src_h, p0.src_pitch, _f3(ch.ops[1].v),
+                                     _f3(ch.ops[2].v), _f3(ch.ops[3].v), outs[0].ctypes.data, p0.dst_pitch)
+    elif wl.name == "nv12_preprocess":
+        rc = lib.fklref_nv12_resize_split(wl.sources[0].ctypes.data, p0.src_w, p0.src_h, p0.src_pitch, p0.dst_w, p0.dst_h,
+                                          _f3(ch.ops[1].v), _f3(ch.ops[2].v), outs[0].ctypes.data)
+    elif wl.name == "divergent_planes":
+        k = n // 2
+        scales = (C.c_float * k)(*[float(x) for x in wl.extra["scales"]])
+        offs = (C.c_float * k)(*[float(x) for x in wl.extra["offs"]])
+        rc = lib.fklref_divergent(frame_ptrs(wl.planes), p0.src_w, p0.src_h, p0.src_pitch, p0.dst_w, p0.dst_h, scales, offs,
+                                  outs[0].ctypes.data, outs[1].ctypes.data, k)
+    else:
+        raise ValueError(f"no reference runner for workload {wl.name}")
+    if rc != 0:
+        raise RuntimeError(f"reference runner returned {rc}")
+    return outs

@@ -1,0 +1,247 @@
+// TEST INFRASTRUCTURE — not part of the product.  Only tests/, the smoke check and the benchmark's CPU
+// baseline may load this file's library; the CUDA path never does.
+//
+// A plain, scalar CPU restatement of the arithmetic the FusedKernelLibrary CPU backend performs for a
+// fused TransformDPP chain, driven by the same descriptors the CUDA kernels take (include/fkb/fkb.h).
+// Parity status: PINNED.  It is checked bit-for-bit against (1) the reference's own golden values
+// (saturate rounding, BGR<->RGB reorder, bt709 matrix constants) and (2) the outputs of the reference
+// CPU backend itself, compiled from the reference headers by oracle/ref_runner.cpp, on every benchmark
+// configuration and on the fixtures under tests/golden/.
+//
+// Must be compiled with -O2 -ffp-contract=off and without -march=native: an FMA contraction changes the
+// results (also the reference's own).
+//
+// Reference lines restated (paths relative to the reference's include/fused_kernel/):
+//   loop nest z,y,x ............... core/execution_model/data_parallel_patterns.h:271-283
+//   divergent chain selection ...... core/execution_model/data_parallel_patterns.h:322-331
+//   batch plane selection .......... core/execution_model/operation_model/batch_operations.h:205-212
+//   uchar3 read, pitched ........... algorithms/basic_ops/memory_operations.h:34-38, core/data/rawptr.h:203-213
+//   NV12 read ...................... algorithms/image_processing/color_conversion.h:219-238
+//   crop ........................... algorithms/image_processing/crop.h:36-39
+//   resize (host parameters) ....... algorithms/image_processing/resize.h:164-233, 266-278
+//   resize (per pixel) ............. algorithms/image_processing/resize.h:86-98, 117-123
+//   bilinear interpolation ......... algorithms/image_processing/interpolation.h:70-104
+//   YCbCr -> RGB ................... algorithms/image_processing/color_conversion.h:150-174,
+//                                    algorithms/basic_ops/algebraic.h:42-56,
+//                                    core/constexpr_libs/constexpr_vector_exec.h:66-78 (sum order)
+//   Mul/Add/Sub/Div ................ algorithms/basic_ops/arithmetic.h:23-137
+//   Cast ........................... algorithms/basic_ops/cast.h:22-33
+//   channel reorder ................ algorithms/basic_ops/vector_ops.h:43-56
+//   saturate cast .................. core/constexpr_libs/constexpr_saturate.h:28-150
+//   writes ......................... algorithms/basic_ops/memory_operations.h:92-97, 167-170, 189-205
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <thread>
+#include <vector>
+
+#include "fkb/fkb.h"
+
+namespace {
+
+struct V3 {
+    float c[3];
+};
+
+// round-half-away-from-zero, as cxp::round (core/constexpr_libs/constexpr_cmath.h:354-385)
+inline float round_half_away(float v) {
+    if (v != v || v == 0.f) return v;
+    const float a = v < 0.f ? -v : v;
+    if (a >= 8388608.0f) return v;  // already integral
+    const float t = static_cast<float>(static_cast<int>(a));
+    const float r = (a - t) >= 0.5f ? t + 1.f : t;
+    return v < 0.f ? -r : r;
+}
+
+// SaturateCast<float,uchar>: NaN -> 0, ties to even, clamp to [0,255]
+// (constexpr_saturate.h:28-66 banker_round, 97-117 clamp)
+inline uint8_t sat_u8(float s) {
+    if (s != s) return 0;
+    const bool neg = s < 0.f;
+    const float a = neg ? -s : s;
+    float rounded;
+    if (a >= 9007199254740992.0f) {
+        rounded = s;
+    } else {
+        long long i = static_cast<long long>(a);
+        const float diff = a - static_cast<float>(i);
+        if (diff > 0.5f) {
+            i += 1;
+        } else if (diff >= 0.5f) {
+            if (i % 2 != 0) i += 1;
+        }
+        const float r = static_cast<float>(i);
+        rounded = neg ? -r : r;
+    }
+    if (rounded >= 255.f) return 255;
+    if (rounded <= 0.f) return 0;
+    return static_cast<uint8_t>(rounded);
+}
+
+inline void operand(const fkb_op& op, const fkb_plane_desc& pl, float o[3]) {
+    const float* s = op.plane_slot >= 0 ? pl.params[op.plane_slot] : op.v;
+    o[0] = s[0]; o[1] = s[1]; o[2] = s[2];
+}
+
+inline V3 apply_ops(V3 v, const fkb_chain_desc& ch, const fkb_plane_desc& pl, uint32_t first, uint32_t last) {
+    for (uint32_t i = first; i < last; ++i) {
+        const fkb_op& op = ch.ops[i];
+        float p[3];
+        switch (op.code) {
+        case FKB_OP_CAST_F32:  // static_cast<float>(uchar): exact
+            break;
+        case FKB_OP_MUL: operand(op, pl, p); for (int c = 0; c < 3; ++c) v.c[c] = v.c[c] * p[c]; break;
+        case FKB_OP_ADD: operand(op, pl, p); for (int c = 0; c < 3; ++c) v.c[c] = v.c[c] + p[c]; break;
+        case FKB_OP_SUB: operand(op, pl, p); for (int c = 0; c < 3; ++c) v.c[c] = v.c[c] - p[c]; break;
+        case FKB_OP_DIV: operand(op, pl, p); for (int c = 0; c < 3; ++c) v.c[c] = v.c[c] / p[c]; break;
+        case FKB_OP_REORDER_ZYX: { const float t = v.c[0]; v.c[0] = v.c[2]; v.c[2] = t; break; }
+        case FKB_OP_YUV2RGB: {
+            const float a = v.c[0] - ch.yuv_sub[0], b = v.c[1] - ch.yuv_sub[1], d = v.c[2] - ch.yuv_sub[2];
+            V3 r;
+            for (int c = 0; c < 3; ++c)
+                r.c[c] = ((a * ch.ccm[3 * c + 0]) + (b * ch.ccm[3 * c + 1])) + (d * ch.ccm[3 * c + 2]);
+            v = r;
+            break;
+        }
+        case FKB_OP_SATCAST_U8:
+            for (int c = 0; c < 3; ++c) v.c[c] = static_cast<float>(sat_u8(v.c[c]));
+            break;
+        default: break;
+        }
+    }
+    return v;
+}
+
+// Read of crop-relative pixel (cx,cy): Crop adds the rectangle origin (crop.h:36-39), then the Read.
+inline V3 read_tap(const fkb_chain_desc& ch, const fkb_plane_desc& pl, int cx, int cy) {
+    const size_t X = static_cast<size_t>(cx) + pl.crop_x, Y = static_cast<size_t>(cy) + pl.crop_y;
+    const uint8_t* base = static_cast<const uint8_t*>(pl.src);
+    V3 v;
+    if (ch.src_format == FKB_PIX_NV12) {
+        const uint8_t* uv = static_cast<const uint8_t*>(pl.src_chroma) + (Y >> 1) * pl.src_pitch + (X >> 1) * 2;
+        v.c[0] = base[Y * pl.src_pitch + X];
+        v.c[1] = uv[0];
+        v.c[2] = uv[1];
+    } else {
+        const uint8_t* p = base + Y * pl.src_pitch + X * 3;
+        v.c[0] = p[0]; v.c[1] = p[1]; v.c[2] = p[2];
+    }
+    return v;
+}
+
+inline V3 pixel(const fkb_chain_desc& ch, const fkb_plane_desc& pl, int x, int y) {
+    if (ch.geometry == FKB_GEOM_NONE) {
+        return apply_ops(read_tap(ch, pl, x, y), ch, pl, 0, ch.n_ops);
+    }
+    V3 v;
+    int tx = x, ty = y;
+    bool inside = true;
+    if (ch.geometry == FKB_GEOM_RESIZE_PRESERVE_AR) {
+        inside = x >= pl.x1 && x <= pl.x2 && y >= pl.y1 && y <= pl.y2;
+        tx = x - pl.x1; ty = y - pl.y1;
+    }
+    if (!inside) {
+        v.c[0] = pl.bg[0]; v.c[1] = pl.bg[1]; v.c[2] = pl.bg[2];
+    } else {
+        const float sx = tx * pl.fx, sy = ty * pl.fy;
+        int x1 = static_cast<int>(std::floor(sx)), y1 = static_cast<int>(std::floor(sy));
+        const int x2 = x1 + 1, y2 = y1 + 1;
+        const int x2r = x2 < pl.crop_w - 1 ? x2 : pl.crop_w - 1, y2r = y2 < pl.crop_h - 1 ? y2 : pl.crop_h - 1;
+        // The reference reads x1,y1 unclamped; they stay inside the crop for every sane scale.  Clamp the
+        // address only (weights still use the unclamped values) so a degenerate scale cannot read outside.
+        const int x1r = x1 < pl.crop_w - 1 ? x1 : pl.crop_w - 1, y1r = y1 < pl.crop_h - 1 ? y1 : pl.crop_h - 1;
+        const V3 p00 = apply_ops(read_tap(ch, pl, x1r, y1r), ch, pl, 0, ch.n_pre_ops);
+        const V3 p10 = apply_ops(read_tap(ch, pl, x2r, y1r), ch, pl, 0, ch.n_pre_ops);
+        const V3 p01 = apply_ops(read_tap(ch, pl, x1r, y2r), ch, pl, 0, ch.n_pre_ops);
+        const V3 p11 = apply_ops(read_tap(ch, pl, x2r, y2r), ch, pl, 0, ch.n_pre_ops);
+        const float w00 = (x2 - sx) * (y2 - sy), w10 = (sx - x1) * (y2 - sy);
+        const float w01 = (x2 - sx) * (sy - y1), w11 = (sx - x1) * (sy - y1);
+        for (int c = 0; c < 3; ++c)
+            v.c[c] = (p00.c[c] * w00) + (p10.c[c] * w10) + (p01.c[c] * w01) + (p11.c[c] * w11);
+    }
+    return apply_ops(v, ch, pl, ch.n_pre_ops, ch.n_ops);
+}
+
+void run_plane(const fkb_chain_desc& ch, const fkb_plane_desc& pl) {
+    uint8_t* dst = static_cast<uint8_t*>(pl.dst);
+    for (uint32_t y = 0; y < pl.dst_h; ++y) {
+        for (uint32_t x = 0; x < pl.dst_w; ++x) {
+            const V3 v = pixel(ch, pl, static_cast<int>(x), static_cast<int>(y));
+            uint8_t* row = dst + static_cast<size_t>(y) * pl.dst_pitch;
+            if (ch.write_kind == FKB_WRITE_SPLIT) {
+                for (int c = 0; c < 3; ++c) {
+                    uint8_t* q = row + static_cast<size_t>(c) * pl.dst_channel_stride;
+                    if (ch.dst_format == FKB_PIX_F32C3) reinterpret_cast<float*>(q)[x] = v.c[c];
+                    else q[x] = static_cast<uint8_t>(v.c[c]);
+                }
+            } else if (ch.dst_format == FKB_PIX_F32C3) {
+                float* q = reinterpret_cast<float*>(row) + static_cast<size_t>(x) * 3;
+                q[0] = v.c[0]; q[1] = v.c[1]; q[2] = v.c[2];
+            } else {
+                uint8_t* q = row + static_cast<size_t>(x) * 3;
+                q[0] = static_cast<uint8_t>(v.c[0]); q[1] = static_cast<uint8_t>(v.c[1]); q[2] = static_cast<uint8_t>(v.c[2]);
+            }
+        }
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+// Resize<INTER_LINEAR,AR>::build host arithmetic (resize.h:164-205, 208-233, 266-278).
+int fkb_oracle_resize_params(uint32_t geometry, fkb_plane_desc* pl) {
+    const int sw = pl->crop_w, sh = pl->crop_h, dw = static_cast<int>(pl->dst_w), dh = static_cast<int>(pl->dst_h);
+    if (sw <= 0 || sh <= 0 || dw <= 0 || dh <= 0) return FKB_ERR_INVALID;
+    if (geometry == FKB_GEOM_RESIZE_IGNORE_AR) {
+        const double cfx = static_cast<double>(dw) / static_cast<double>(sw);
+        const double cfy = static_cast<double>(dh) / static_cast<double>(sh);
+        pl->fx = static_cast<float>(1.0 / cfx);
+        pl->fy = static_cast<float>(1.0 / cfy);
+        pl->x1 = 0; pl->y1 = 0; pl->x2 = dw - 1; pl->y2 = dh - 1;
+        return FKB_OK;
+    }
+    if (geometry != FKB_GEOM_RESIZE_PRESERVE_AR) return FKB_ERR_INVALID;
+    const float scale = dh / static_cast<float>(sh);
+    int tw = static_cast<int>(round_half_away(scale * sw)), th = dh;
+    if (tw > dw) {
+        const float scale2 = dw / static_cast<float>(sw);
+        tw = dw;
+        th = static_cast<int>(round_half_away(scale2 * sh));
+    }
+    const double cfx = static_cast<double>(tw) / sw, cfy = static_cast<double>(th) / sh;
+    pl->fx = static_cast<float>(1.0 / cfx);
+    pl->fy = static_cast<float>(1.0 / cfy);
+    pl->x1 = (dw - tw) / 2;
+    pl->y1 = (dh - th) / 2;
+    pl->x2 = pl->x1 + tw - 1;
+    pl->y2 = pl->y1 + th - 1;
+    return FKB_OK;
+}
+
+// Runs the launch on host memory: every src/dst pointer in `planes` is a host address.
+// n_threads > 1 splits the planes over std::threads (planes are independent); results do not depend on it.
+int fkb_oracle_run(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc* planes,
+                   uint32_t n_planes, uint32_t n_threads) {
+    if (!chains || !planes) return FKB_ERR_NULL;
+    for (uint32_t z = 0; z < n_planes; ++z)
+        if (planes[z].chain >= n_chains) return FKB_ERR_INVALID;
+    if (n_threads <= 1 || n_planes <= 1) {
+        for (uint32_t z = 0; z < n_planes; ++z) run_plane(chains[planes[z].chain], planes[z]);
+        return FKB_OK;
+    }
+    if (n_threads > n_planes) n_threads = n_planes;
+    std::vector<std::thread> pool;
+    for (uint32_t t = 0; t < n_threads; ++t)
+        pool.emplace_back([=] {
+            for (uint32_t z = t; z < n_planes; z += n_threads) run_plane(chains[planes[z].chain], planes[z]);
+        });
+    for (auto& th : pool) th.join();
+    return FKB_OK;
+}
+
+// Single scalar helpers exported for the golden-value tests.
+uint8_t fkb_oracle_saturate_u8(float v) { return sat_u8(v); }
+float fkb_oracle_round_half_away(float v) { return round_half_away(v); }
+
+}  // extern "C"

@@ -1,0 +1,255 @@
+// TEST INFRASTRUCTURE — not part of the product.  This translation unit contains no arithmetic of its own:
+// it includes the FusedKernelLibrary headers from where they are installed (-I<reference>/include, see
+// oracle/Makefile) and runs the reference's own CPU backend (TransformDPP<ParArch::CPU>,
+// core/execution_model/data_parallel_patterns.h:246-284, executors.h:163-239) on caller-provided host
+// buffers.  The result, oracle/_ref/libfkl_ref.so, pins oracle/fkb_oracle.cpp, produces the fixtures under
+// tests/golden/ and is the timed CPU baseline.  Build flags: -O2 -ffp-contract=off, no -march=native.
+//
+// BATCH is a template parameter in the reference; a batch of n planes is run as independent calls of
+// 32/16/8/4/2/1 planes (planes never interact), optionally spread over std::threads — the reference CPU
+// backend itself is single-threaded.
+#include <fused_kernel/algorithms/basic_ops/arithmetic.h>
+#include <fused_kernel/algorithms/basic_ops/cast.h>
+#include <fused_kernel/algorithms/basic_ops/memory_operations.h>
+#include <fused_kernel/algorithms/image_processing/color_conversion.h>
+#include <fused_kernel/algorithms/image_processing/crop.h>
+#include <fused_kernel/algorithms/image_processing/image.h>
+#include <fused_kernel/algorithms/image_processing/resize.h>
+#include <fused_kernel/algorithms/image_processing/saturate.h>
+#include <fused_kernel/fused_kernel.h>
+
+#include <array>
+#include <cstdint>
+#include <functional>
+#include <thread>
+#include <vector>
+
+using namespace fk;
+
+namespace {
+
+using CpuStream = Stream_<ParArch::CPU>;
+using CpuDPP = TransformDPP<ParArch::CPU>;
+
+struct Chunk { int first; int size; };
+
+std::vector<Chunk> chunks_of(int n) {
+    std::vector<Chunk> out;
+    int at = 0;
+    for (int s : {32, 16, 8, 4, 2, 1})
+        while (n - at >= s) { out.push_back({at, s}); at += s; }
+    return out;
+}
+
+void run_parallel(const std::vector<std::function<void()>>& jobs, int n_threads) {
+    if (n_threads <= 1 || jobs.size() <= 1) { for (auto& j : jobs) j(); return; }
+    const int T = std::min<int>(n_threads, static_cast<int>(jobs.size()));
+    std::vector<std::thread> pool;
+    for (int t = 0; t < T; ++t)
+        pool.emplace_back([&, t] { for (size_t i = t; i < jobs.size(); i += T) jobs[i](); });
+    for (auto& th : pool) th.join();
+}
+
+inline Ptr2D<uchar3> wrap_frame(const uint8_t* p, int w, int h, int pitch) {
+    return Ptr2D<uchar3>(reinterpret_cast<uchar3*>(const_cast<uint8_t*>(p)), w, h, pitch, MemType::Host, 0);
+}
+
+struct BatchArgs {
+    const uint8_t* const* frames; int w, h, pitch; const int32_t* rects; int dw, dh;
+    float3 bg, mul, sub; uint8_t* out;
+};
+
+// Read -> Crop -> Resize(PRESERVE_AR, bg) -> Mul -> Sub -> SaturateCast -> TensorWrite<uchar3>
+template <size_t B>
+void crop_resize_u8(const BatchArgs& a, int first) {
+    CpuStream stream;
+    std::array<Ptr2D<uchar3>, B> ptrs; std::array<Rect, B> rects;
+    for (size_t i = 0; i < B; ++i) {
+        ptrs[i] = wrap_frame(a.frames[first + i], a.w, a.h, a.pitch);
+        const int32_t* r = a.rects + 4 * (first + i);
+        rects[i] = Rect(r[0], r[1], r[2], r[3]);
+    }
+    Tensor<uchar3> out(reinterpret_cast<uchar3*>(a.out) + static_cast<size_t>(first) * a.dw * a.dh, a.dw, a.dh, B, 1, MemType::Host, 0);
+    executeOperations<CpuDPP>(stream, PerThreadRead<ND::_2D, uchar3>::build(ptrs), Crop<>::build(rects),
+        Resize<InterpolationType::INTER_LINEAR, AspectRatio::PRESERVE_AR>::build(Size(a.dw, a.dh), a.bg),
+        Mul<float3>::build(a.mul), Sub<float3>::build(a.sub), SaturateCast<float3, uchar3>::build(),
+        TensorWrite<uchar3>::build(out));
+}
+
+// Read -> Crop -> Resize(PRESERVE_AR, bg) -> Mul -> TensorWrite<float3>
+template <size_t B>
+void crop_resize_f32(const BatchArgs& a, int first) {
+    CpuStream stream;
+    std::array<Ptr2D<uchar3>, B> ptrs; std::array<Rect, B> rects;
+    for (size_t i = 0; i < B; ++i) {
+        ptrs[i] = wrap_frame(a.frames[first + i], a.w, a.h, a.pitch);
+        const int32_t* r = a.rects + 4 * (first + i);
+        rects[i] = Rect(r[0], r[1], r[2], r[3]);
+    }
+    Tensor<float3> out(reinterpret_cast<float3*>(a.out) + static_cast<size_t>(first) * a.dw * a.dh, a.dw, a.dh, B, 1, MemType::Host, 0);
+    executeOperations<CpuDPP>(stream, PerThreadRead<ND::_2D, uchar3>::build(ptrs), Crop<>::build(rects),
+        Resize<InterpolationType::INTER_LINEAR, AspectRatio::PRESERVE_AR>::build(Size(a.dw, a.dh), a.bg),
+        Mul<float3>::build(a.mul), TensorWrite<float3>::build(out));
+}
+
+// Read -> Crop -> ColorConversion<BGR2RGB> on uchar3 -> TensorWrite<uchar3>   (integer only; all rects cw x ch)
+template <size_t B>
+void crop_reorder_u8(const BatchArgs& a, int first) {
+    CpuStream stream;
+    std::array<Ptr2D<uchar3>, B> ptrs; std::array<Rect, B> rects;
+    for (size_t i = 0; i < B; ++i) {
+        ptrs[i] = wrap_frame(a.frames[first + i], a.w, a.h, a.pitch);
+        const int32_t* r = a.rects + 4 * (first + i);
+        rects[i] = Rect(r[0], r[1], r[2], r[3]);
+    }
+    Tensor<uchar3> out(reinterpret_cast<uchar3*>(a.out) + static_cast<size_t>(first) * a.dw * a.dh, a.dw, a.dh, B, 1, MemType::Host, 0);
+    // a chain whose last ReadBack is followed by compute ops only is fused by hand with .then(), as the
+    // reference's own crop tests do (tests/algorithm/test_crop.h:33-37)
+    executeOperations<CpuDPP>(stream, PerThreadRead<ND::_2D, uchar3>::build(ptrs).then(Crop<>::build(rects)),
+        ColorConversion<ColorConversionCodes::COLOR_BGR2RGB, uchar3, uchar3>::build(), TensorWrite<uchar3>::build(out));
+}
+
+#define FKLREF_DISPATCH(fn)                                                               \
+    [](const BatchArgs& a, int n, int n_threads) {                                        \
+        std::vector<std::function<void()>> jobs;                                          \
+        for (const Chunk c : chunks_of(n)) {                                              \
+            switch (c.size) {                                                             \
+            case 32: jobs.push_back([&a, c] { fn<32>(a, c.first); }); break;              \
+            case 16: jobs.push_back([&a, c] { fn<16>(a, c.first); }); break;              \
+            case 8: jobs.push_back([&a, c] { fn<8>(a, c.first); }); break;                \
+            case 4: jobs.push_back([&a, c] { fn<4>(a, c.first); }); break;                \
+            case 2: jobs.push_back([&a, c] { fn<2>(a, c.first); }); break;                \
+            default: jobs.push_back([&a, c] { fn<1>(a, c.first); }); break;               \
+            }                                                                             \
+        }                                                                                 \
+        run_parallel(jobs, n_threads);                                                    \
+    }
+
+template <uint N> struct SelN { FK_HOST_DEVICE_FUSE uint at(const uint& z) { return z < N ? 0u : 1u; } };
+
+// Divergent horizontal fusion over 2N planes of one size: planes [0,N) Resize(IGNORE_AR) -> SaturateCast ->
+// TensorWrite<uchar3>; planes [N,2N) Cast -> Mul(scale_i) -> Sub(off_i) fused into each plane's Read ->
+// TensorWrite<float3> into a 2N-plane tensor addressed by the global plane index.
+template <uint N>
+void divergent(const uint8_t* const* frames, int w, int h, int pitch, int dw, int dh, const float* scales,
+               const float* offs, uint8_t* outA, float* outB) {
+    CpuStream stream;
+    std::array<Ptr2D<uchar3>, N> firstN;
+    for (uint i = 0; i < N; ++i) firstN[i] = wrap_frame(frames[i], w, h, pitch);
+    Tensor<uchar3> tA(reinterpret_cast<uchar3*>(outA), dw, dh, N, 1, MemType::Host, 0);
+    const auto seq0 = buildOperationSequence(PerThreadRead<ND::_2D, uchar3>::build(firstN),
+        Resize<InterpolationType::INTER_LINEAR>::build(Size(dw, dh)), SaturateCast<float3, uchar3>::build(),
+        TensorWrite<uchar3>::build(tA));
+    const Ptr2D<uchar3> f0 = wrap_frame(frames[N], w, h, pitch);
+    using FusedRead = decltype(PerThreadRead<ND::_2D, uchar3>::build(f0).then(Cast<uchar3, float3>::build())
+        .then(Mul<float3>::build(make_set<float3>(1.f))).then(Sub<float3>::build(make_set<float3>(0.f))));
+    std::array<FusedRead, 2 * N> reads;
+    for (uint i = 0; i < 2 * N; ++i) {
+        const uint k = i < N ? 0 : i - N;
+        reads[i] = PerThreadRead<ND::_2D, uchar3>::build(wrap_frame(frames[N + k], w, h, pitch))
+            .then(Cast<uchar3, float3>::build()).then(Mul<float3>::build(make_set<float3>(scales[k])))
+            .then(Sub<float3>::build(make_set<float3>(offs[k])));
+    }
+    auto batchRead = BatchRead<PlanePolicy::PROCESS_ALL>::build(reads);
+    batchRead.params.activeThreads.z = N;  // this sequence owns N planes; indices stay global
+    Tensor<float3> tB(reinterpret_cast<float3*>(outB), w, h, 2 * N, 1, MemType::Host, 0);
+    const auto seq1 = buildOperationSequence(batchRead, TensorWrite<float3>::build(tB));
+    Executor<DivergentBatchTransformDPP<ParArch::CPU, SelN<N>>>::executeOperations(stream, seq0, seq1);
+}
+
+}  // namespace
+
+extern "C" {
+
+int fklref_crop_resize_u8(const uint8_t* const* frames, int w, int h, int pitch, const int32_t* rects, int n,
+                          int dw, int dh, const float* bg, const float* mul, const float* sub, uint8_t* out,
+                          int n_threads) {
+    const BatchArgs a{frames, w, h, pitch, rects, dw, dh, make_<float3>(bg[0], bg[1], bg[2]),
+                      make_<float3>(mul[0], mul[1], mul[2]), make_<float3>(sub[0], sub[1], sub[2]), out};
+    FKLREF_DISPATCH(crop_resize_u8)(a, n, n_threads);
+    return 0;
+}
+
+int fklref_crop_resize_f32(const uint8_t* const* frames, int w, int h, int pitch, const int32_t* rects, int n,
+                           int dw, int dh, const float* bg, const float* mul, float* out, int n_threads) {
+    const BatchArgs a{frames, w, h, pitch, rects, dw, dh, make_<float3>(bg[0], bg[1], bg[2]),
+                      make_<float3>(mul[0], mul[1], mul[2]), make_<float3>(0.f, 0.f, 0.f),
+                      reinterpret_cast<uint8_t*>(out)};
+    FKLREF_DISPATCH(crop_resize_f32)(a, n, n_threads);
+    return 0;
+}
+
+int fklref_crop_reorder_u8(const uint8_t* const* frames, int w, int h, int pitch, const int32_t* rects, int n,
+                           uint8_t* out, int n_threads) {
+    const BatchArgs a{frames, w, h, pitch, rects, rects[2], rects[3], make_<float3>(0.f, 0.f, 0.f),
+                      make_<float3>(0.f, 0.f, 0.f), make_<float3>(0.f, 0.f, 0.f), out};
+    FKLREF_DISPATCH(crop_reorder_u8)(a, n, n_threads);
+    return 0;
+}
+
+// Read -> Cast -> Mul -> Add -> Div -> ColorConversion<BGR2RGB> -> SaturateCast -> PerThreadWrite
+int fklref_pointwise_u8(const uint8_t* src, int w, int h, int spitch, const float* mul, const float* add,
+                        const float* div, uint8_t* dst, int dpitch) {
+    CpuStream stream;
+    const Ptr2D<uchar3> in = wrap_frame(src, w, h, spitch);
+    const Ptr2D<uchar3> out = wrap_frame(dst, w, h, dpitch);
+    executeOperations<CpuDPP>(stream, PerThreadRead<ND::_2D, uchar3>::build(in), Cast<uchar3, float3>::build(),
+        Mul<float3>::build(make_<float3>(mul[0], mul[1], mul[2])),
+        Add<float3>::build(make_<float3>(add[0], add[1], add[2])),
+        Div<float3>::build(make_<float3>(div[0], div[1], div[2])),
+        ColorConversion<ColorConversionCodes::COLOR_BGR2RGB, float3, float3>::build(),
+        SaturateCast<float3, uchar3>::build(), PerThreadWrite<ND::_2D, uchar3>::build(out));
+    return 0;
+}
+
+// ReadYUV<NV12> -> ConvertYUVToRGB<p8bit,Full,bt709> -> Resize(IGNORE_AR) -> Sub -> Div -> TensorSplit<float3>
+int fklref_nv12_resize_split(const uint8_t* nv12, int w, int h, int pitch, int dw, int dh, const float* sub,
+                             const float* div, float* out) {
+    CpuStream stream;
+    const Ptr<ND::_2D, uchar> data(const_cast<uint8_t*>(nv12), PtrDims<ND::_2D>(w, h + h / 2, pitch), MemType::Host, 0);
+    const Image<PixelFormat::NV12> img(data, w, h);
+    Tensor<float> t(out, dw, dh, 1, 3, MemType::Host, 0);
+    executeOperations<CpuDPP>(stream, ReadYUV<PixelFormat::NV12>::build(img),
+        ConvertYUVToRGB<ColorDepth::p8bit, ColorRange::Full, ColorPrimitives::bt709>::build(),
+        Resize<InterpolationType::INTER_LINEAR, AspectRatio::IGNORE_AR>::build(Size(dw, dh)),
+        Sub<float3>::build(make_<float3>(sub[0], sub[1], sub[2])),
+        Div<float3>::build(make_<float3>(div[0], div[1], div[2])), TensorSplit<float3>::build(t));
+    return 0;
+}
+
+// frames: 2*n_per_seq pointers.  outA: n_per_seq planes of dw x dh uchar3.  outB: 2*n_per_seq planes of w x h float3.
+int fklref_divergent(const uint8_t* const* frames, int w, int h, int pitch, int dw, int dh, const float* scales,
+                     const float* offs, uint8_t* outA, float* outB, int n_per_seq) {
+    switch (n_per_seq) {
+    case 1: divergent<1>(frames, w, h, pitch, dw, dh, scales, offs, outA, outB); return 0;
+    case 2: divergent<2>(frames, w, h, pitch, dw, dh, scales, offs, outA, outB); return 0;
+    case 4: divergent<4>(frames, w, h, pitch, dw, dh, scales, offs, outA, outB); return 0;
+    default: return -1;
+    }
+}
+
+// The constexpr bt709 / Full / 8-bit YCbCr->RGB matrix the reference evaluates (itu_color.h:185-258), row-major.
+void fklref_bt709_full_matrix(float* m9) {
+    constexpr M3x3Float m = ccMatrix<ColorRange::Full, ColorPrimitives::bt709, ColorConversionDir::YCbCr2RGB, ColorDepth::p8bit>;
+    m9[0] = m.x.x; m9[1] = m.x.y; m9[2] = m.x.z; m9[3] = m.y.x; m9[4] = m.y.y; m9[5] = m.y.z;
+    m9[6] = m.z.x; m9[7] = m.z.y; m9[8] = m.z.z;
+}
+
+uint8_t fklref_saturate_u8(float v) { return cxp::saturate_cast<uchar>::f(v); }
+
+// Resize<INTER_LINEAR,AR>::build on a w x h source: returns fx, fy, x1, y1, x2, y2 (AR: 0 PRESERVE_AR, 1 IGNORE_AR).
+void fklref_resize_params(int sw, int sh, int dw, int dh, int ignore_ar, float* f2, int32_t* r4) {
+    static uchar3 dummy;
+    const auto read = PerThreadRead<ND::_2D, uchar3>::build(RawPtr<ND::_2D, uchar3>{&dummy, {static_cast<uint>(sw), static_cast<uint>(sh), static_cast<uint>(sw * 3)}});
+    if (ignore_ar) {
+        const auto r = Resize<InterpolationType::INTER_LINEAR, AspectRatio::IGNORE_AR>::build(read, Size(dw, dh));
+        f2[0] = r.params.src_conv_factors.x; f2[1] = r.params.src_conv_factors.y;
+        r4[0] = 0; r4[1] = 0; r4[2] = dw - 1; r4[3] = dh - 1;
+    } else {
+        const auto r = Resize<InterpolationType::INTER_LINEAR, AspectRatio::PRESERVE_AR, float3>::build(read, Size(dw, dh), make_<float3>(0.f, 0.f, 0.f));
+        f2[0] = r.params.src_conv_factors.x; f2[1] = r.params.src_conv_factors.y;
+        r4[0] = r.params.x1; r4[1] = r.params.y1; r4[2] = r.params.x2; r4[3] = r.params.y2;
+    }
+}
+
+}  // extern "C"

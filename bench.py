@@ -1,0 +1,356 @@
+#!/usr/bin/env python
+"""Benchmark of the fused transform hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--scaling weak|strong]
+
+A step is one fused launch of the batched crop -> resize -> normalise workload (64 frames of 1920x1080 uchar3,
+32 random crops per frame, each resized with preserved aspect ratio to 224x224 on a (114,114,114) background, times
+1/255, written as a 224x224x2048 float3 tensor).  With N > 1 (one process per GPU under torch.distributed.run) every
+rank runs that workload on its own frames — no exchange between GPUs — and the value is the pixels of all ranks
+divided by the slowest rank's device time.  Rank 0 prints one JSON line.
+
+``--impl reference`` times the reference library's own CPU backend (compiled from its headers into
+oracle/_ref/libfkl_ref.so; when that file is absent, the CPU restatement in oracle/) on the host cores, on a bounded
+sample of the same workload per step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "fused-pipeline output Gpix/s"
+UNIT = "Gpix/s"
+N_FRAMES, CROPS_PER_FRAME = 64, 32
+FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one staged_kernel launch on this workload (ncu capture summarised
+# in profiles/); None until a capture exists
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def make_workload(rank: int, n_frames: int = N_FRAMES):
+    from fusedkernellibrary_b200 import workloads as W
+    return W.batched_crop_resize(n_frames=n_frames, crops_per_frame=CROPS_PER_FRAME, seed=4 + rank,
+                                 frame_seed_base=1000 + 64 * rank)
+
+
+def workload_config(n_gpus: int, scaling: str, frames_per_gpu: int) -> dict:
+    return {
+        "workload": "batched_crop_resize = BASELINE configs[3]: 1920x1080 uchar3 frames, 32 random crops each "
+                    "(w,h in 16..512, clipped), Resize INTER_LINEAR PRESERVE_AR to 224x224 bg (114,114,114), Mul 1/255, "
+                    "float3 tensor 224x224xplanes",
+        "frames_per_gpu": frames_per_gpu, "crops_per_frame": CROPS_PER_FRAME, "planes_per_gpu": frames_per_gpu * CROPS_PER_FRAME,
+        "sharding": f"by frame over {n_gpus} GPU(s), each GPU owns its frames and its slice of the output, no collective",
+        "l2": "inputs + outputs per launch (1.6 GB per GPU at 64 frames) exceed the 126 MB L2; no flush needed",
+    }
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clock and clock-event reasons of one GPU through NVML (read-only) while the benchmark runs."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
+               0x2: "applications_clocks_setting", 0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting", 0x10: "sync_boost"}
+
+    def __init__(self, cuda_index: int, period_s: float = 0.02):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        self.period = period_s
+        try:
+            import pynvml
+            import torch
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            try:  # the CUDA ordinal is not the NVML index when CUDA_VISIBLE_DEVICES is set: go through the UUID
+                self.h = pynvml.nvmlDeviceGetHandleByUUID("GPU-" + str(torch.cuda.get_device_properties(cuda_index).uuid))
+            except Exception:
+                self.h = pynvml.nvmlDeviceGetHandleByIndex(cuda_index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                util = nv.nvmlDeviceGetUtilizationRates(self.h).gpu
+                mhz = int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+                self.samples.append((mhz, util))
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def start(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+
+    def stop(self) -> dict:
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+        mhz = sorted(m for m, _ in self.samples)
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(mhz)}
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# the reference CPU arm
+# ---------------------------------------------------------------------------------------------------------------
+def host_threads() -> int:
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def cpu_time_sample(sample_frames: int, threads: int, repeats: int):
+    """Times the CPU implementation on `sample_frames` frames of the workload.  Returns (best seconds, pixels, kind)."""
+    import oracle
+    wl = make_workload(0, n_frames=sample_frames)
+    kind = "reference" if oracle.have_ref() else "port"
+    run = (lambda: oracle.run_ref(wl, threads=threads)) if kind == "reference" else (lambda: oracle.run_oracle(wl, threads=threads))
+    run()  # warm: page-faults the output
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        run()
+        best = min(best, time.perf_counter() - t0)
+    return best, wl.out_pixels, kind
+
+
+def reference_arm(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle
+    threads = host_threads()
+    sample_frames = 16
+    wl = make_workload(0, n_frames=sample_frames)
+    kind = "reference" if oracle.have_ref() else "port"
+    run = (lambda: oracle.run_ref(wl, threads=threads)) if kind == "reference" else (lambda: oracle.run_oracle(wl, threads=threads))
+    for _ in range(max(1, args.warmup)):
+        run()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        run()
+    dt = (time.perf_counter() - t0) / args.steps
+    value = wl.out_pixels / dt / 1e9
+    sample = (f"{sample_frames} of the 64 frames ({sample_frames * CROPS_PER_FRAME} planes, {wl.out_pixels} output pixels) per step; "
+              f"the reference CPU backend is single-threaded, so the planes are spread over {threads} threads as independent calls")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": workload_config(args.gpus, args.scaling, N_FRAMES),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------------------------------------------
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback (earlier measurement on this pool)"
+
+
+def time_launches(fn, steps: int, torch) -> float:
+    """Device time in seconds of `steps` calls of fn() on the current stream (CUDA events, synchronised both sides)."""
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(steps):
+        fn()
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) / 1e3
+
+
+def other_configs(torch, steps: int, peak: float) -> dict:
+    """Kernel-only figures of the other four configurations on one GPU (rotating buffer sets defeat the L2)."""
+    from fusedkernellibrary_b200 import runtime, workloads as W
+    out = {}
+    for name, factory in (("readme_crops", W.readme_crops), ("vertical_fusion", W.vertical_fusion),
+                          ("nv12_preprocess", W.nv12_preprocess), ("divergent_planes", W.divergent_planes)):
+        wl = factory()
+        alg = wl.algorithmic_bytes()
+        footprint = sum(s.nbytes for s in wl.sources) + sum(wl.out_sizes)
+        n_sets = max(1, min(8, int(400e6 // footprint) + 1))
+        sets = [runtime.DeviceWorkload(wl, poison=None) for _ in range(n_sets)]
+        for s in sets:
+            s.plan()
+        it = [0]
+
+        def step():
+            sets[it[0] % n_sets].launch_plan()
+            it[0] += 1
+        for _ in range(3 * n_sets):
+            step()
+        dt = time_launches(step, steps, torch) / steps
+        out[name] = {"us_per_launch": dt * 1e6, "gpix_s": wl.out_pixels / dt / 1e9, "alg_bytes": alg["total"],
+                     "hbm_gbs": alg["total"] / dt / 1e9, "frac_of_measured_peak": alg["total"] / dt / 1e9 / peak,
+                     "buffer_sets_rotated": n_sets, "kernels_per_launch": sets[0].kernel_launches()}
+        for s in sets:
+            s.close()
+        del sets
+        torch.cuda.empty_cache()
+    return out
+
+
+def our_arm(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    from fusedkernellibrary_b200 import abi, runtime
+    frames = N_FRAMES if args.scaling == "weak" else max(1, N_FRAMES // world)
+    wl = make_workload(rank if args.scaling == "weak" else 0, n_frames=N_FRAMES)
+    if args.scaling == "strong":  # total work fixed: rank r keeps frames [r*frames, (r+1)*frames)
+        from fusedkernellibrary_b200 import workloads as W
+        lo = rank * frames * CROPS_PER_FRAME
+        keep = wl.planes[lo: lo + frames * CROPS_PER_FRAME]
+        base_src = keep[0].src
+        planes = [W.PlaneSpec(**{**p.__dict__, "src": p.src - base_src, "dst_offset": i * 224 * 224 * 12}) for i, p in enumerate(keep)]
+        wl = W.Workload(wl.name, wl.chains, wl.sources[base_src: base_src + frames], [len(planes) * 224 * 224 * 12], planes,
+                        extra={"n_frames": frames, "crops_per_frame": CROPS_PER_FRAME})
+    alg = wl.algorithmic_bytes()
+    peak, peak_src = measured_peak()
+
+    dw = runtime.DeviceWorkload(wl, poison=None)
+    dw.plan()
+    kernels_per_step = dw.kernel_launches()
+
+    sampler = ClockSampler(torch.cuda.current_device())
+    for _ in range(max(3, args.warmup)):
+        dw.launch_plan()
+    torch.cuda.synchronize()
+    sampler.start()
+    # a sustained stretch of the same launch so that the clock samples are taken under this load
+    t_end = time.perf_counter() + 0.6
+    while time.perf_counter() < t_end:
+        for _ in range(50):
+            dw.launch_plan()
+        torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    dt = time_launches(dw.launch_plan, args.steps, torch)
+    t_end = time.perf_counter() + 0.4
+    while time.perf_counter() < t_end:
+        for _ in range(50):
+            dw.launch_plan()
+        torch.cuda.synchronize()
+    clocks = sampler.stop()
+    abi.check(abi.load().fkb_device_status())
+    if world > 1:
+        t = torch.tensor([dt], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt = float(t.item())
+    ms_per_step = dt / args.steps * 1e3
+    total_pixels = wl.out_pixels * world
+    value = total_pixels / (dt / args.steps) / 1e9
+    achieved = alg["total"] / (dt / args.steps) / 1e9
+
+    # ---- end to end through the public entry point with host buffers: pinned sources up, launch, tensor down ----
+    h_src = [torch.from_numpy(s).pin_memory() for s in wl.sources]
+    h_out = torch.empty(wl.out_sizes[0], dtype=torch.uint8).pin_memory()
+    lib = abi.load()
+
+    def e2e_step():
+        for d, h in zip(dw.src, h_src):
+            d.copy_(h, non_blocking=True)
+        abi.check(lib.fkb_launch_transform(dw.chains, dw.planes, dw.n_planes, runtime.current_stream_ptr()))
+        h_out.copy_(dw.out[0], non_blocking=True)
+
+    e2e_steps = max(2, min(args.steps, 10))
+    for _ in range(2):
+        e2e_step()
+    if world > 1:
+        dist.barrier()
+    e2e_dt = time_launches(e2e_step, e2e_steps, torch)
+    if world > 1:
+        t = torch.tensor([e2e_dt], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_dt = float(t.item())
+    e2e_value = total_pixels / (e2e_dt / e2e_steps) / 1e9
+    h2d = sum(s.nbytes for s in wl.sources) + dw.n_planes * 192
+    d2h = wl.out_sizes[0]
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": workload_config(world, args.scaling, frames),
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_source": peak_src, "kernel": "fkb::staged_kernel",
+                     "algorithmic_bytes_per_launch": alg["total"], "frac_of_nominal_8TBs": achieved / 8000.0},
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": e2e_dt / e2e_steps * 1e3, "steps": e2e_steps,
+                "path": "pinned host frames -> device, fkb_launch_transform (host descriptors), float3 tensor -> pinned host"},
+        "gpu_launches": args.steps * kernels_per_step,
+        "clocks": clocks,
+    }
+    if rank == 0 and world == 1:
+        if not args.no_cpu_baseline:
+            threads = host_threads()
+            sample_frames = 16
+            best, px, kind = cpu_time_sample(sample_frames, threads, repeats=3)
+            line["cpu_baseline"] = {"value": px / best / 1e9, "unit": UNIT, "cores": threads, "kind": kind,
+                                    "sample": f"{sample_frames} of the 64 frames ({sample_frames * CROPS_PER_FRAME} planes), best of 3, "
+                                              f"planes spread over {threads} host threads as independent single-threaded reference calls"}
+        if not args.no_other_configs:
+            dw.close()
+            del dw
+            torch.cuda.empty_cache()
+            line["other_configs"] = other_configs(torch, max(10, min(args.steps, 50)), peak)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-other-configs", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+    else:
+        our_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -93,10 +93,12 @@ int check_plane(const fkb_chain_desc& ch, const fkb_plane_desc& pl) {
     if (ch.geometry == FKB_GEOM_NONE) {
         if (pl.dst_w > static_cast<uint32_t>(pl.crop_w) || pl.dst_h > static_cast<uint32_t>(pl.crop_h)) return FKB_ERR_INVALID;
     } else {
-        if (!(pl.fx > 0.f) || !(pl.fy > 0.f) || !std::isfinite(pl.fx) || !std::isfinite(pl.fy)) return FKB_ERR_INVALID;
-        if (ch.geometry == FKB_GEOM_RESIZE_PRESERVE_AR) {
-            if (pl.x1 < 0 || pl.y1 < 0 || pl.x2 < pl.x1 || pl.y2 < pl.y1 ||
-                pl.x2 >= static_cast<int>(pl.dst_w) || pl.y2 >= static_cast<int>(pl.dst_h)) return FKB_ERR_INVALID;
+        // A PRESERVE_AR target that rounds to zero width or height (x2 < x1 or y2 < y1) is legal in the reference:
+        // no pixel is inside, the whole plane is background, and the scale factors (then infinite) are never used.
+        const bool empty = ch.geometry == FKB_GEOM_RESIZE_PRESERVE_AR && (pl.x2 < pl.x1 || pl.y2 < pl.y1);
+        if (!empty && (!(pl.fx > 0.f) || !(pl.fy > 0.f) || !std::isfinite(pl.fx) || !std::isfinite(pl.fy))) return FKB_ERR_INVALID;
+        if (ch.geometry == FKB_GEOM_RESIZE_PRESERVE_AR && !empty) {
+            if (pl.x1 < 0 || pl.y1 < 0 || pl.x2 >= static_cast<int>(pl.dst_w) || pl.y2 >= static_cast<int>(pl.dst_h)) return FKB_ERR_INVALID;
         }
     }
     return FKB_OK;
@@ -123,9 +125,11 @@ int validate(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_de
 inline uint32_t up16(uint32_t v) { return (v + 15u) & ~15u; }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// FKB_FORCE_GATHER=1 (read at every launch) routes every plane through gather_kernel: a debugging aid that lets
+// the two kernel paths be checked against each other.
 bool force_gather() {
-    static const bool v = [] { const char* e = std::getenv("FKB_FORCE_GATHER"); return e && e[0] == '1'; }();
-    return v;
+    const char* e = std::getenv("FKB_FORCE_GATHER");
+    return e && e[0] == '1';
 }
 
 // Chooses the kernel path and tile shape of one plane.
@@ -159,7 +163,8 @@ void classify(const fkb_chain_desc& ch, PlaneRec& r) {
     } else {
         for (uint32_t i = 0; i < ch.n_pre_ops; ++i)
             if (ch.ops[i].code != FKB_OP_CAST_F32) return;  // taps are transformed before interpolation: general path
-        if (r.fx > 16.f || r.fy > 16.f) return;             // footprint too sparse to be worth staging
+        if (ch.geometry == FKB_GEOM_RESIZE_PRESERVE_AR && (r.x2 < r.x1 || r.y2 < r.y1)) return;  // all background
+        if (!(r.fx <= 16.f) || !(r.fy <= 16.f)) return;     // footprint too sparse to be worth staging
         uint64_t best_area = 0;
         for (uint32_t n_split = 1; n_split <= 32; ++n_split) {
             const uint32_t tw = n_split == 1 ? r.dst_w : up16((r.dst_w + n_split - 1) / n_split);

@@ -273,3 +273,75 @@ CONFIGS = {
     "batched_crop_resize": batched_crop_resize,
     "divergent_planes": divergent_planes,
 }
+
+
+def random_workload(seed: int, max_dim: int = 260) -> Workload:
+    """A random but valid launch: random source format, geometry, op chain (type-correct), write kind, plane count,
+    crops, sizes and pitches (aligned and unaligned).  Used to fuzz the kernels against the CPU checker."""
+    rs = np.random.RandomState(seed)
+    nv12 = rs.rand() < 0.3
+    geometry = int(rs.choice([abi.GEOM_NONE, abi.GEOM_RESIZE_IGNORE_AR, abi.GEOM_RESIZE_PRESERVE_AR]))
+    n_planes = int(rs.randint(1, 6))
+    slots_used = 0
+
+    def arith():
+        nonlocal slots_used
+        code = int(rs.choice([abi.OP_MUL, abi.OP_ADD, abi.OP_SUB, abi.OP_DIV]))
+        vals = tuple(float(v) for v in (rs.uniform(0.3, 3.0, 3) if code in (abi.OP_MUL, abi.OP_DIV) else rs.uniform(-40, 40, 3)))
+        if slots_used < abi.MAX_PLANE_PARAMS and rs.rand() < 0.3:
+            slots_used += 1
+            return op(code, slot=slots_used - 1)
+        return op(code, vals)
+
+    ops, is_f32 = [], False
+    if nv12 and rs.rand() < 0.8:
+        ops.append(op(abi.OP_YUV2RGB)); is_f32 = True
+    elif rs.rand() < 0.4:
+        ops.append(op(abi.OP_CAST_F32)); is_f32 = True
+        if rs.rand() < 0.5:
+            ops.append(arith())
+    if rs.rand() < 0.2:
+        ops.append(op(abi.OP_REORDER_ZYX))
+    n_pre = len(ops) if geometry != abi.GEOM_NONE else 0
+    if geometry != abi.GEOM_NONE:
+        is_f32 = True
+    elif not is_f32 and rs.rand() < 0.7:
+        ops.append(op(abi.OP_CAST_F32)); is_f32 = True
+    if is_f32:
+        for _ in range(int(rs.randint(0, 4))):
+            ops.append(arith() if rs.rand() < 0.8 else op(abi.OP_REORDER_ZYX))
+        if rs.rand() < 0.5:
+            ops.append(op(abi.OP_SATCAST_U8)); is_f32 = False
+    dst_format = abi.PIX_F32C3 if is_f32 else abi.PIX_U8C3
+    split = rs.rand() < 0.25
+    ch = chain(abi.PIX_NV12 if nv12 else abi.PIX_U8C3, geometry, dst_format, abi.WRITE_SPLIT if split else abi.WRITE_PACKED,
+               ops, n_pre_ops=n_pre, ccm=BT709_FULL_8BIT, yuv_sub=(0.0, 128.0, 128.0))
+
+    w, h = int(rs.randint(2, max_dim)), int(rs.randint(2, max_dim))
+    if nv12:
+        w, h = w + (w & 1), h + (h & 1)
+    align = int(rs.choice([1, 4, 16, 64, 512]))
+    pitch = _pitch(w if nv12 else w * 3, max(align, 2 if nv12 else 1))
+    src = _frame(seed + 7, pitch * (h + h // 2 if nv12 else h), 16 if nv12 else 0, 236 if nv12 else 256)
+    elt = (4 if split else 12) if dst_format == abi.PIX_F32C3 else (1 if split else 3)
+    dalign = int(rs.choice([1, 16, 64])) if dst_format == abi.PIX_U8C3 else int(rs.choice([4, 16, 64]))
+    planes, off = [], 0
+    for _ in range(n_planes):
+        cw, chh = int(rs.randint(1, w + 1)), int(rs.randint(1, h + 1))
+        cx, cy = int(rs.randint(0, w - cw + 1)), int(rs.randint(0, h - chh + 1))
+        if rs.rand() < 0.3:
+            cx -= cx % 16
+        if geometry == abi.GEOM_NONE:
+            dw, dh = cw, chh
+        else:
+            dw, dh = int(rs.randint(1, max_dim)), int(rs.randint(1, max_dim))
+        dpitch = _pitch(dw * elt, dalign)
+        plane_bytes = dpitch * dh
+        cstride = _pitch(plane_bytes, 16) if split else 0
+        total = cstride * 3 if split else plane_bytes
+        params = tuple(tuple(float(v) for v in rs.uniform(0.5, 2.5, 3)) for _ in range(slots_used))
+        planes.append(PlaneSpec(0, 0, off, w, h, pitch, (cx, cy, cw, chh), dw, dh, dpitch, dst_channel_stride=cstride,
+                                bg=tuple(float(v) for v in rs.uniform(0, 255, 3)), params=params,
+                                chroma_offset=pitch * h))
+        off += _pitch(total, int(rs.choice([4, 16, 256])))
+    return Workload(f"random_{seed}", [ch], [src], [off], planes, "random launch")

@@ -76,10 +76,11 @@ def _f3(v):
     return (C.c_float * 3)(*[float(x) for x in v])
 
 
-def run_oracle(wl, threads: int = 1):
-    """Runs a Workload through the restatement on host memory.  Returns one uint8 array per output buffer."""
+def run_oracle(wl, threads: int = 1, fill: int = 0):
+    """Runs a Workload through the restatement on host memory.  Returns one uint8 array per output buffer;
+    bytes the launch does not write keep the value ``fill``."""
     lib = load_oracle()
-    outs = [np.zeros(n, np.uint8) for n in wl.out_sizes]
+    outs = [np.full(n, fill, np.uint8) for n in wl.out_sizes]
     planes = wl.bind([s.ctypes.data for s in wl.sources], [o.ctypes.data for o in outs],
                      resize_params=lib.fkb_oracle_resize_params)
     rc = lib.fkb_oracle_run(wl.chain_array(), len(wl.chains), planes, len(wl.planes), threads)

@@ -1,0 +1,61 @@
+"""Generates the golden fixtures in this directory by running the REFERENCE CPU backend
+(oracle/_ref/libfkl_ref.so, compiled from the reference headers by oracle/Makefile) on small seeded workloads.
+
+Run where the reference is installed:  ``make -C oracle && python tests/golden/make_golden.py``.
+Each ``<case>.npz`` stores the workload factory name, its keyword arguments (JSON), a CRC of the generated
+inputs (so a drift of the input generator is caught) and the reference's output bytes.
+"""
+from __future__ import annotations
+
+import json
+import os
+import sys
+import zlib
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+
+import oracle  # noqa: E402
+from fusedkernellibrary_b200 import workloads as W  # noqa: E402
+
+CASES = {
+    "readme_crops_full": ("readme_crops", {}),
+    "readme_crops_pitched": ("readme_crops", {"w": 500, "h": 300, "pitch_align": 512, "seed": 11,
+                                              "crops": [[3, 5, 60, 40], [400, 125, 100, 175], [0, 0, 500, 300], [499, 299, 1, 1], [17, 250, 300, 20]]}),
+    "vertical_fusion_small": ("vertical_fusion", {"w": 333, "h": 41, "seed": 12}),
+    "vertical_fusion_pitched": ("vertical_fusion", {"w": 250, "h": 19, "seed": 13, "pitch_align": 256, "dst_pitch_align": 64}),
+    "nv12_small": ("nv12_preprocess", {"w": 640, "h": 360, "dst": [96, 64], "seed": 14}),
+    "nv12_upscale": ("nv12_preprocess", {"w": 64, "h": 36, "dst": [100, 70], "seed": 15}),
+    "batched_small": ("batched_crop_resize", {"n_frames": 2, "crops_per_frame": 3, "w": 640, "h": 360, "dst": [64, 48],
+                                              "crop_range": [8, 300], "seed": 16}),
+    "divergent_small": ("divergent_planes", {"n_per_seq": 2, "w": 160, "h": 90, "seed": 17}),
+    "crop_reorder_small": ("crop_reorder", {"n": 3, "w": 320, "h": 200, "crop_size": [50, 30], "seed": 18}),
+}
+
+
+def build_case(factory: str, kwargs: dict):
+    kw = {k: (tuple(tuple(x) if isinstance(x, list) else x for x in v) if isinstance(v, list) else v) for k, v in kwargs.items()}
+    return getattr(W, factory)(**kw)
+
+
+def input_crc(wl) -> int:
+    c = 0
+    for s in wl.sources:
+        c = zlib.crc32(s.tobytes(), c)
+    return c
+
+
+def main() -> None:
+    here = os.path.dirname(os.path.abspath(__file__))
+    for name, (factory, kwargs) in CASES.items():
+        wl = build_case(factory, kwargs)
+        outs = oracle.run_ref(wl)
+        np.savez_compressed(os.path.join(here, name + ".npz"), factory=factory, kwargs=json.dumps(kwargs),
+                            input_crc=np.uint32(input_crc(wl)), **{f"out{i}": o for i, o in enumerate(outs)})
+        print(name, [o.size for o in outs])
+
+
+if __name__ == "__main__":
+    main()

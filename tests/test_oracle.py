@@ -1,0 +1,118 @@
+"""CPU tests of the oracle: golden values from the reference's own unit tests, the committed fixtures produced by
+the reference CPU backend, and (where the reference-backed checker was built) a direct comparison with it."""
+import ctypes as C
+import math
+
+import numpy as np
+import pytest
+
+import oracle
+from conftest import GOLDEN_CASES, load_golden
+from fusedkernellibrary_b200 import abi, workloads as W
+
+
+def test_saturate_cast_golden_values():
+    # utests/algorithm/image_processing/utest_saturate/utest_saturate_common.h:60-75 (0.5->0, 1.5->2, 2.5->2, ties to
+    # even), clamping at both ends, and NaN -> 0 (core/constexpr_libs/constexpr_saturate.h:97-100)
+    sat = oracle.load_oracle().fkb_oracle_saturate_u8
+    table = [(0.5, 0), (1.5, 2), (2.5, 2), (3.5, 4), (0.49999997, 0), (0.50000006, 1), (-1.5, 0), (-0.5, 0), (254.5, 254),
+             (254.50002, 255), (255.0, 255), (255.5, 255), (1e9, 255), (-1e9, 0), (127.4, 127), (127.6, 128),
+             (float("nan"), 0), (float("inf"), 255), (float("-inf"), 0)]
+    for v, want in table:
+        assert sat(v) == want, (v, want)
+    if oracle.have_ref():
+        ref = oracle.load_ref().fklref_saturate_u8
+        rs = np.random.RandomState(0)
+        vals = np.concatenate([rs.uniform(-20, 280, 20000), np.arange(-4, 260) + 0.5, np.arange(-4, 260)]).astype(np.float32)
+        for v in vals:
+            assert sat(float(v)) == ref(float(v)), v
+
+
+def test_round_half_away_matches_std_round():
+    f = oracle.load_oracle().fkb_oracle_round_half_away
+    for v in [0.5, 1.5, 2.5, -0.5, -2.5, 0.49999997, 95.99999, 96.0, 58.5, 59.499996, 0.0]:
+        want = math.copysign(math.floor(abs(np.float32(v)) + 0.5), v) if v != 0.49999997 else 0.0
+        assert f(v) == want, v
+
+
+def test_reorder_golden():
+    # utests/algorithm/image_processing/utest_color_conversion.h:91-101: {100,150,200} -> {200,150,100}
+    src = np.array([100, 150, 200] + [0] * 13, np.uint8)
+    ch = W.chain(abi.PIX_U8C3, abi.GEOM_NONE, abi.PIX_U8C3, abi.WRITE_PACKED, [W.op(abi.OP_REORDER_ZYX)])
+    wl = W.Workload("x", [ch], [src], [3], [W.PlaneSpec(0, 0, 0, 1, 1, 16, (0, 0, 1, 1), 1, 1, 3)])
+    assert oracle.run_oracle(wl)[0].tolist() == [200, 150, 100]
+
+
+def test_bt709_matrix_golden():
+    # constants of utests/algorithm/image_processing/utest_color_conversion.h:441-447 (bt709, Full, 8 bit)
+    want = np.array([1.0, 0.0, 1.57480001, 1.0, -0.187324256, -0.46812427, 1.0, 1.8556, 0.0], np.float32)
+    assert np.array_equal(np.array(W.BT709_FULL_8BIT, np.float32), want)
+    if oracle.have_ref():
+        m = (C.c_float * 9)()
+        oracle.load_ref().fklref_bt709_full_matrix(m)
+        assert np.array_equal(np.array(list(m), np.float32), want)
+
+
+# letterbox placement and scale factors the reference computes for the README crops (Resize<>::build run in the
+# reference: resize.h:164-233): crop -> (target w, target h, x1, y1, fx, fy)
+README_KNOWN = [
+    ((60, 40), (96, 64, 16, 0, 0.625, 0.625)),
+    ((130, 140), (59, 64, 34, 0, 2.20338988, 2.1875)),
+    ((100, 35), (128, 45, 0, 9, 0.78125, 0.777777791)),
+    ((40, 15), (128, 48, 0, 8, 0.3125, 0.3125)),
+]
+
+
+def test_resize_params_known_answers():
+    lib = oracle.load_oracle()
+    for (cw, chh), (tw, th, x1, y1, fx, fy) in README_KNOWN:
+        d = abi.PlaneDesc()
+        d.crop_w, d.crop_h, d.dst_w, d.dst_h = cw, chh, 128, 64
+        assert lib.fkb_oracle_resize_params(abi.GEOM_RESIZE_PRESERVE_AR, C.byref(d)) == 0
+        assert (d.x2 - d.x1 + 1, d.y2 - d.y1 + 1, d.x1, d.y1) == (tw, th, x1, y1)
+        assert np.float32(d.fx) == np.float32(fx) and np.float32(d.fy) == np.float32(fy)
+    d = abi.PlaneDesc()
+    d.crop_w, d.crop_h, d.dst_w, d.dst_h = 3840, 2160, 640, 640
+    assert lib.fkb_oracle_resize_params(abi.GEOM_RESIZE_IGNORE_AR, C.byref(d)) == 0
+    assert (d.fx, d.fy) == (6.0, 3.375)
+
+
+@pytest.mark.skipif(not oracle.have_ref(), reason="reference-backed checker not built")
+def test_resize_params_against_reference():
+    lib, ref = oracle.load_oracle(), oracle.load_ref()
+    rs = np.random.RandomState(1)
+    for _ in range(3000):
+        sw, sh, dw, dh = (int(v) for v in rs.randint(1, 700, 4))
+        for ignore in (0, 1):
+            f2, r4 = (C.c_float * 2)(), (C.c_int32 * 4)()
+            ref.fklref_resize_params(sw, sh, dw, dh, ignore, f2, r4)
+            d = abi.PlaneDesc()
+            d.crop_w, d.crop_h, d.dst_w, d.dst_h = sw, sh, dw, dh
+            lib.fkb_oracle_resize_params(abi.GEOM_RESIZE_IGNORE_AR if ignore else abi.GEOM_RESIZE_PRESERVE_AR, C.byref(d))
+            assert (d.fx, d.fy, d.x1, d.y1, d.x2, d.y2) == (f2[0], f2[1], r4[0], r4[1], r4[2], r4[3]), (sw, sh, dw, dh, ignore)
+
+
+@pytest.mark.parametrize("name", GOLDEN_CASES)
+def test_oracle_matches_golden_fixture(name):
+    wl, want = load_golden(name)
+    got = oracle.run_oracle(wl)
+    for g, w in zip(got, want):
+        assert np.array_equal(g, w)  # bit-exact, integer and float outputs alike
+
+
+@pytest.mark.skipif(not oracle.have_ref(), reason="reference-backed checker not built")
+@pytest.mark.parametrize("wl", [
+    W.readme_crops(), W.vertical_fusion(w=1000, h=300), W.nv12_preprocess(w=1280, h=720, dst=(320, 320)),
+    W.batched_crop_resize(n_frames=4, crops_per_frame=8, w=960, h=540), W.divergent_planes(n_per_seq=4, w=480, h=270),
+    W.divergent_planes(n_per_seq=1, w=200, h=100), W.crop_reorder(n=5),
+], ids=lambda w: w.name)
+def test_oracle_matches_reference_backend(wl):
+    got, want = oracle.run_oracle(wl, threads=4), oracle.run_ref(wl, threads=4)
+    for g, w in zip(got, want):
+        assert np.array_equal(g, w)
+
+
+def test_oracle_threads_do_not_change_results():
+    wl = W.batched_crop_resize(n_frames=2, crops_per_frame=5, w=320, h=240, dst=(64, 64))
+    a, b = oracle.run_oracle(wl, threads=1), oracle.run_oracle(wl, threads=4)
+    assert np.array_equal(a[0], b[0])

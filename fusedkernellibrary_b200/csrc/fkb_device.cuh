@@ -6,6 +6,7 @@
 // division is IEEE, and SaturateCast is cvt.rni.sat.u8.f32 (round half to even, clamp, NaN -> 0), which is
 // what core/constexpr_libs/constexpr_saturate.h:28-150 of the reference computes.
 #pragma once
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -51,6 +52,8 @@ struct LaunchParams {
     uint32_t n_tiles;
     uint32_t tiles_per_plane;  // > 0 when every plane has the same number of tiles; else PlaneRec::tile_base is searched
     int* status;
+    uint32_t post_kind[FKB_MAX_CHAINS];  // per chain: bit mask of {Mul, Add|Sub, SaturateCast} when its post-ops have that shape, else 8
+    float neg_zero;           // -0.0f, deliberately opaque to the compiler (see mul2_unfusable)
     PlaneRec inline_planes[kInlinePlanes];
 };
 
@@ -95,6 +98,7 @@ __device__ __forceinline__ void bulk_store(void* gmem_dst, const void* smem_src,
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // make this thread's shared-memory writes visible to the async (bulk-copy) proxy
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -102,10 +106,59 @@ __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.a
 // ---------------------------------------------------------------------------------------------------------
 // arithmetic
 // ---------------------------------------------------------------------------------------------------------
+// Integer <-> float without conversion instructions (those run at a quarter of the FP32 rate).
+// kMagic + n is exactly representable for every integer 0 <= n < 2^23 and its low mantissa bits are n.
+constexpr float kMagic = 8388608.0f;  // 2^23
+// float whose value is 2^23 + (byte `k` of w); sel = 0x7540 | k
+__device__ __forceinline__ float magic_byte(uint32_t w, uint32_t sel) {
+    return __uint_as_float(__byte_perm(w, 0x4B000000u, sel));
+}
+// exact float value of byte k of w
+#define FKB_BYTE_F32(w, k) __fsub_rn(magic_byte((w), 0x7540u | (k)), kMagic)
+// the 8-bit integer held exactly by a float in [0, 255]
+__device__ __forceinline__ uint32_t u8_of_exact(float v) { return __float_as_uint(__fadd_rn(v, kMagic)) & 0xffu; }
+
+// SaturateCast<float,uchar>: NaN -> 0, round half to even, clamp to [0,255].  Clamping first and then adding 2^23
+// (which rounds to nearest-even at unit granularity) gives the same integer as rounding first and clamping after,
+// which is what the reference does (core/constexpr_libs/constexpr_saturate.h:28-66, 97-117).
 __device__ __forceinline__ float sat_u8_as_float(float v) {
-    uint32_t r;
-    asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(r) : "f"(v));
-    return static_cast<float>(r);
+    const float t = fminf(fmaxf(v, 0.f), 255.f);  // fmaxf returns the non-NaN operand
+    return __fsub_rn(__fadd_rn(t, kMagic), kMagic);
+}
+
+// Two fp32 values per instruction (sm_100 f32x2 arithmetic): each lane is rounded to nearest on its own, so the
+// results are bit-identical to two scalar operations at half the issue cost.
+struct f2 { float x, y; };
+#define FKB_F32X2_OP(name, opcode)                                                                              \
+    __device__ __forceinline__ f2 name(f2 a, f2 b) {                                                            \
+        f2 r;                                                                                                   \
+        asm("{\n\t.reg .b64 ra, rb, rc;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t" opcode            \
+            " rc, ra, rb;\n\tmov.b64 {%0, %1}, rc;\n\t}"                                                         \
+            : "=f"(r.x), "=f"(r.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));                                    \
+        return r;                                                                                               \
+    }
+FKB_F32X2_OP(mul2, "mul.rn.f32x2")
+FKB_F32X2_OP(add2, "add.rn.f32x2")
+FKB_F32X2_OP(sub2, "sub.rn.f32x2")
+#undef FKB_F32X2_OP
+// ptxas contracts a packed multiply whose only use is a packed add into one fused multiply-add, even with explicit
+// .rn modifiers and --fmad=false, which changes the rounding.  Products that feed additions are therefore written as
+// fma(a, b, -0.0): adding -0.0 leaves every product (and the sign of a zero product) unchanged, and an FMA result
+// cannot be contracted any further.  The -0.0 comes from a kernel parameter so that it is not folded away.
+__device__ __forceinline__ f2 mul2_unfusable(f2 a, f2 b, float neg_zero) {
+    f2 r;
+    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %6};\n\t"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(r.x), "=f"(r.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(neg_zero));
+    return r;
+}
+
+// Exact fp32 value b * 2^-24 of a byte b: the byte is read as the bit pattern of a subnormal half and widened, which
+// runs on the FP pipe instead of the slow integer->float conversion unit.  Multiplying by a weight that was pre-scaled
+// by 2^24 (exact) gives exactly the correctly rounded product b * w.
+constexpr float kByteScale = 16777216.0f;  // 2^24
+__device__ __forceinline__ float byte_times_2m24(uint32_t b) {
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(b)));
 }
 
 // Runs ops[first..last) of `ch` on N pixels held in registers.  The op loop is outside the pixel loop so
@@ -121,16 +174,40 @@ __device__ __forceinline__ void apply_ops(float (&v)[N][3], const fkb_chain_desc
         else { p0 = ch.ops[i].v[0]; p1 = ch.ops[i].v[1]; p2 = ch.ops[i].v[2]; }
         switch (code) {
         case FKB_OP_MUL:
+            if (N % 2 == 0) {
+                const float pp[3] = {p0, p1, p2};
 #pragma unroll
-            for (int n = 0; n < N; ++n) { v[n][0] = __fmul_rn(v[n][0], p0); v[n][1] = __fmul_rn(v[n][1], p1); v[n][2] = __fmul_rn(v[n][2], p2); }
+                for (int n = 0; n + 1 < N; n += 2)
+#pragma unroll
+                    for (int c = 0; c < 3; ++c) { const f2 r = mul2(f2{v[n][c], v[n + 1][c]}, f2{pp[c], pp[c]}); v[n][c] = r.x; v[n + 1][c] = r.y; }
+            } else {
+#pragma unroll
+                for (int n = 0; n < N; ++n) { v[n][0] = __fmul_rn(v[n][0], p0); v[n][1] = __fmul_rn(v[n][1], p1); v[n][2] = __fmul_rn(v[n][2], p2); }
+            }
             break;
         case FKB_OP_ADD:
+            if (N % 2 == 0) {
+                const float pp[3] = {p0, p1, p2};
 #pragma unroll
-            for (int n = 0; n < N; ++n) { v[n][0] = __fadd_rn(v[n][0], p0); v[n][1] = __fadd_rn(v[n][1], p1); v[n][2] = __fadd_rn(v[n][2], p2); }
+                for (int n = 0; n + 1 < N; n += 2)
+#pragma unroll
+                    for (int c = 0; c < 3; ++c) { const f2 r = add2(f2{v[n][c], v[n + 1][c]}, f2{pp[c], pp[c]}); v[n][c] = r.x; v[n + 1][c] = r.y; }
+            } else {
+#pragma unroll
+                for (int n = 0; n < N; ++n) { v[n][0] = __fadd_rn(v[n][0], p0); v[n][1] = __fadd_rn(v[n][1], p1); v[n][2] = __fadd_rn(v[n][2], p2); }
+            }
             break;
         case FKB_OP_SUB:
+            if (N % 2 == 0) {
+                const float pp[3] = {p0, p1, p2};
 #pragma unroll
-            for (int n = 0; n < N; ++n) { v[n][0] = __fsub_rn(v[n][0], p0); v[n][1] = __fsub_rn(v[n][1], p1); v[n][2] = __fsub_rn(v[n][2], p2); }
+                for (int n = 0; n + 1 < N; n += 2)
+#pragma unroll
+                    for (int c = 0; c < 3; ++c) { const f2 r = sub2(f2{v[n][c], v[n + 1][c]}, f2{pp[c], pp[c]}); v[n][c] = r.x; v[n + 1][c] = r.y; }
+            } else {
+#pragma unroll
+                for (int n = 0; n < N; ++n) { v[n][0] = __fsub_rn(v[n][0], p0); v[n][1] = __fsub_rn(v[n][1], p1); v[n][2] = __fsub_rn(v[n][2], p2); }
+            }
             break;
         case FKB_OP_DIV:
 #pragma unroll

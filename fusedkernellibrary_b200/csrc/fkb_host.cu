@@ -143,51 +143,52 @@ void classify(const fkb_chain_desc& ch, PlaneRec& r) {
     const bool f32 = ch.dst_format == FKB_PIX_F32C3;
     const uint32_t elt = f32 ? 12u : 3u;
 
+    (void)elt;
     if (ch.geometry == FKB_GEOM_NONE) {
-        if ((r.crop_x * 3u) & 15u) return;
-        const uint32_t chunk_px = f32 ? 4u : 16u;  // pixels per thread step; its output is 48 B either way
-        const uint32_t max_chunks = kOutBytes / 48u;
-        uint32_t chunks = (r.dst_w + chunk_px - 1) / chunk_px;
-        uint32_t n_split = (chunks + max_chunks - 1) / max_chunks;
-        uint32_t tw = r.dst_w;
-        if (n_split > 1) {
-            tw = up16((r.dst_w + n_split - 1) / n_split);
-            chunks = tw / chunk_px;
-        }
-        r.tile_w = tw;
-        r.out_stride = chunks * 48u;
-        r.in_stride = up16(chunks * chunk_px * 3u);
-        uint32_t th = std::min(std::min(kOutBytes / r.out_stride, kInBytes / r.in_stride), 16u);
-        r.tile_h = std::max(1u, std::min(th, r.dst_h));
+        if ((r.crop_x * 3u) & 15u) return;  // the staged row must start on a 16-byte boundary
+        // one row segment per step: 16 pixels per lane (uchar3 out) or 4 pixels per lane in two passes (float3 out)
+        r.tile_w = std::min(r.dst_w, f32 ? 256u : 512u);
         r.kclass = KCLASS_POINT;
     } else {
         for (uint32_t i = 0; i < ch.n_pre_ops; ++i)
             if (ch.ops[i].code != FKB_OP_CAST_F32) return;  // taps are transformed before interpolation: general path
         if (ch.geometry == FKB_GEOM_RESIZE_PRESERVE_AR && (r.x2 < r.x1 || r.y2 < r.y1)) return;  // all background
-        if (!(r.fx <= 16.f) || !(r.fy <= 16.f)) return;     // footprint too sparse to be worth staging
-        uint64_t best_area = 0;
-        for (uint32_t n_split = 1; n_split <= 32; ++n_split) {
-            const uint32_t tw = n_split == 1 ? r.dst_w : up16((r.dst_w + n_split - 1) / n_split);
-            if (n_split > 1 && tw < 32) break;
-            const uint32_t out_stride = up16(tw * elt);
+        if (!(r.fx <= 32.f) || !(r.fy <= 4096.f)) return;
+        // widest segment (at most 8 columns per lane) whose source columns fit one staged row
+        uint32_t tw = std::min(r.dst_w, 256u);
+        for (;;) {
             const uint32_t cols = std::min<uint32_t>(r.crop_w, static_cast<uint32_t>(std::ceil((tw - 1) * static_cast<double>(r.fx))) + 3u);
-            const uint32_t in_stride = up16(cols * 3u) + 32u;
-            for (uint32_t th : {8u, 4u, 2u, 1u}) {
-                const uint32_t rows = std::min<uint32_t>(r.crop_h, static_cast<uint32_t>(std::ceil((th - 1) * static_cast<double>(r.fy))) + 3u);
-                if (static_cast<uint64_t>(in_stride) * rows > kInBytes || static_cast<uint64_t>(out_stride) * th > kOutBytes) continue;
-                const uint64_t area = static_cast<uint64_t>(tw) * th;
-                if (area > best_area) {
-                    best_area = area;
-                    r.tile_w = tw; r.tile_h = std::min(th, r.dst_h); r.in_stride = in_stride; r.out_stride = out_stride;
-                }
-                break;  // smaller th only shrinks the tile
-            }
+            if (cols * 3u + 63u <= kInRowBytes) break;
+            if (tw <= 16) return;  // too sparse to stage: general path
+            tw = tw > 32 ? ((tw - 1) & ~15u) : 16u;
         }
-        if (!best_area) return;
+        r.tile_w = tw;
         r.kclass = KCLASS_RESIZE;
     }
-    r.tiles_x = (r.dst_w + r.tile_w - 1) / r.tile_w;
-    r.tiles_y = (r.dst_h + r.tile_h - 1) / r.tile_h;
+    r.in_stride = kInRowBytes;
+    r.out_stride = kOutRowBytes;
+    r.tiles_x = (r.dst_w + r.tile_w - 1) / r.tile_w;  // tile_h / tiles_y are chosen per launch (rows_per_item)
+}
+
+// Output rows a warp processes per item.  Inside an item the next row's footprint is prefetched while the current
+// row is computed, so longer items pipeline better; more items balance better.  Large launches get about eight items
+// per resident warp; launches too small to occupy every warp get one row per item.
+uint32_t rows_per_item(uint64_t row_segments, uint32_t resident_warps) {
+    const uint64_t per = row_segments / (static_cast<uint64_t>(resident_warps) * 8u);
+    uint32_t rpi = static_cast<uint32_t>(std::min<uint64_t>(std::max<uint64_t>(per, 1), kMaxRowsPerItem));
+    if (rpi < 4 && row_segments >= static_cast<uint64_t>(resident_warps) * 4u) rpi = 4;
+    return rpi;
+}
+
+// Shape of the ops that follow the read / the interpolation: bit 0 Mul, bit 1 Add or Sub, bit 2 SaturateCast when the
+// chain is [Cast]* [Mul] [Add|Sub] [SaturateCast] in this order (the kernels specialise those), else 8 (interpreted).
+uint32_t post_kind_of(const fkb_chain_desc& ch) {
+    uint32_t i = ch.geometry == FKB_GEOM_NONE ? 0 : ch.n_pre_ops, kind = 0;
+    while (i < ch.n_ops && ch.ops[i].code == FKB_OP_CAST_F32) ++i;
+    if (i < ch.n_ops && ch.ops[i].code == FKB_OP_MUL) { kind |= 1; ++i; }
+    if (i < ch.n_ops && (ch.ops[i].code == FKB_OP_ADD || ch.ops[i].code == FKB_OP_SUB)) { kind |= 2; ++i; }
+    if (i < ch.n_ops && ch.ops[i].code == FKB_OP_SATCAST_U8) { kind |= 4; ++i; }
+    return i == ch.n_ops ? kind : 8u;
 }
 
 struct Lowered {
@@ -231,6 +232,12 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
     uint32_t n_tiles = 0, gw = 0, gh = 0, n_gather = 0;
     bool uniform = true;
     uint32_t first_count = 0;
+    int sms = 0;
+    {
+        const int e = device_sm_count(sms);
+        if (e != FKB_OK) return e;
+    }
+    uint64_t row_segments = 0;
     for (uint32_t z = 0; z < n_planes; ++z) {
         const fkb_plane_desc& s = planes[z];
         PlaneRec& r = L.recs[z];
@@ -247,6 +254,15 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         r.chain = s.chain;
         std::memcpy(r.params, s.params, sizeof(r.params));
         classify(chains[s.chain], r);
+        if (r.kclass != KCLASS_GATHER) row_segments += static_cast<uint64_t>(r.tiles_x) * r.dst_h;
+    }
+    const uint32_t rpi = rows_per_item(row_segments, 2u * kStagedWarps * static_cast<uint32_t>(sms));
+    for (uint32_t z = 0; z < n_planes; ++z) {
+        PlaneRec& r = L.recs[z];
+        if (r.kclass != KCLASS_GATHER) {
+            r.tile_h = std::min(r.dst_h, rpi);
+            r.tiles_y = (r.dst_h + r.tile_h - 1) / r.tile_h;
+        }
         r.tile_base = n_tiles;
         const uint32_t count = r.tiles_x * r.tiles_y;
         if (z == 0) first_count = count; else if (count != first_count) uniform = false;
@@ -255,12 +271,11 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         if (r.kclass == KCLASS_GATHER) { ++n_gather; gw = std::max(gw, r.dst_w); gh = std::max(gh, r.dst_h); }
     }
     L.lp.n_planes = n_planes;
+    L.lp.neg_zero = -0.0f;
+    for (uint32_t c = 0; c < n_chains; ++c) L.lp.post_kind[c] = post_kind_of(chains[c]);
     L.lp.n_tiles = n_tiles;
     L.lp.tiles_per_plane = (uniform && first_count) ? first_count : 0;
     if (n_tiles) {
-        int sms = 0;
-        const int e = device_sm_count(sms);
-        if (e != FKB_OK) return e;
         L.staged_grid = std::min<uint32_t>(n_tiles, 2u * static_cast<uint32_t>(sms));
         ++L.kernels;
     }

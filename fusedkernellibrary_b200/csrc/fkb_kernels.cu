@@ -1,14 +1,15 @@
 // The two sm_100a kernels behind fkb_launch_*:
 //
-//   staged_kernel  — persistent CTAs (two per SM).  Each CTA walks a strided list of output tiles.  For every
-//                    tile it (1) stages the tile's bounded source footprint into shared memory with
-//                    non-multicast bulk async copies (cp.async.bulk, one per source row, completion on an
-//                    mbarrier), double-buffered so the next tile's footprint is in flight while this one is
-//                    computed, (2) computes the tile from shared memory into a shared output tile and (3)
-//                    writes that tile with bulk async stores (full 16-byte-aligned lines, no partial sectors).
-//                    Two tile kinds: POINT (no resampling, 16 or 4 pixels per thread, 128-bit shared accesses)
-//                    and RESIZE (bilinear from the staged footprint).  The chain of a plane is picked once per
-//                    tile, so a divergent launch never diverges inside a warp.
+//   staged_kernel  — persistent CTAs (two per SM) of autonomous warps.  Each warp walks a strided list of items
+//                    (a block of output rows of one plane) and runs its own pipeline per output row: (1) the
+//                    row's bounded source footprint (one or two source rows) is staged into the warp's slice of
+//                    shared memory with non-multicast bulk async copies (cp.async.bulk, completion on the
+//                    warp's mbarrier), double-buffered so the next row is in flight while this one is computed,
+//                    (2) the row is computed from shared memory into a shared output row and (3) leaves with a
+//                    bulk async store (full 16-byte-aligned lines, no partial sectors).  No __syncthreads
+//                    anywhere: warps never wait for each other.  Two item kinds: POINT (no resampling, 16 or 4
+//                    pixels per lane, 128-bit shared accesses) and RESIZE (bilinear from the staged rows).  The
+//                    chain of a plane is picked once per item, so a divergent launch never diverges in a warp.
 //   gather_kernel  — the general path: any source format (uchar3, NV12), ops before the interpolation, planar
 //                    writes, unaligned buffers, or footprints too sparse/large to stage (heavy decimation).
 //                    Four pixels per thread, read-only global loads, vector stores when aligned.
@@ -146,24 +147,29 @@ __global__ void __launch_bounds__(256) gather_kernel(const __grid_constant__ Lau
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// staged_kernel
+// staged_kernel: every warp runs its own load -> compute -> store pipeline; warps never wait for one another
 // ---------------------------------------------------------------------------------------------------------
-struct TileInfo {
-    uint32_t ox, oy, ow, oh;     // tile origin / extent in output pixels
-    int32_t r_lo, c_lo;          // first staged source row / column, in crop coordinates
-    uint32_t n_rows, row_bytes;  // staged rows and bytes per row
-    uint32_t shift;              // byte offset of column c_lo inside a staged row
-    uint32_t ok;                 // 0 when the footprint did not fit (lowering bug): tile is skipped, status set
-    uint32_t pad_[2];
-};
+// Shared memory of one warp (kSliceBytes): two mbarriers, the plane record of the item being processed, two
+// source stages (two source rows each) and two output rows.
+// All shared-memory accesses go through 32-bit offsets into this array, so that the address arithmetic is 32-bit
+// integer adds and the accesses are plain LDS/STS with immediate offsets.
+extern __shared__ __align__(128) uint8_t smem_raw[];
 
-struct StagedSmem {
-    uint64_t bar[2];
-    TileInfo info[2];
-    PlaneRec plane[2];
+struct WarpSlice {
+    uint32_t base;  // offset of this warp's slice in smem_raw
+    const PlaneRec* pl;
+    __device__ __forceinline__ uint64_t* bar(uint32_t s) const { return reinterpret_cast<uint64_t*>(smem_raw + base) + s; }
+    __device__ __forceinline__ uint32_t in(uint32_t s) const { return base + kSliceHeader + s * (2 * kInRowBytes); }
+    __device__ __forceinline__ uint32_t out(uint32_t s) const { return base + kSliceHeader + 4 * kInRowBytes + s * kOutSlotBytes; }
 };
-constexpr uint32_t kSmemHeader = 1024;
-static_assert(sizeof(StagedSmem) <= kSmemHeader, "header region");
+__device__ __forceinline__ WarpSlice warp_slice(uint32_t base) {
+    WarpSlice w;
+    w.base = base;
+    w.pl = reinterpret_cast<const PlaneRec*>(smem_raw + base + 16);
+    return w;
+}
+static_assert(16 + sizeof(PlaneRec) <= kSliceHeader, "slice header");
+static_assert(kSliceHeader + 4 * kInRowBytes + 2 * kOutSlotBytes == kSliceBytes, "slice layout");
 
 __device__ __forceinline__ uint32_t tile_to_plane(const LaunchParams& p, uint32_t t, uint32_t& local) {
     if (p.tiles_per_plane) { const uint32_t z = t / p.tiles_per_plane; local = t - z * p.tiles_per_plane; return z; }
@@ -177,225 +183,396 @@ __device__ __forceinline__ uint32_t tile_to_plane(const LaunchParams& p, uint32_
     return lo;
 }
 
-// Warp 0 stages tile `t` into buffer `s`: copies the plane record, derives the source footprint, announces the
-// byte count on the mbarrier and issues one bulk copy per footprint row.
-__device__ __forceinline__ void produce_tile(const LaunchParams& p, uint32_t t, uint32_t s, StagedSmem& sm,
-                                             uint8_t* in_buf, uint32_t lane) {
-    uint32_t local;
-    const uint32_t z = tile_to_plane(p, t, local);
-    const PlaneRec* g = plane_table(p) + z;
-    if (lane < sizeof(PlaneRec) / 16)
-        reinterpret_cast<uint4*>(&sm.plane[s])[lane] = reinterpret_cast<const uint4*>(g)[lane];
+// One output row segment leaves through the TMA engine: lane 0 issues a bulk store of the 16-byte multiple,
+// the (row_bytes mod 16) tail bytes go out with plain byte stores.
+__device__ __forceinline__ void store_row(uint8_t* gdst, uint32_t srow, uint32_t row_bytes, uint32_t lane) {
+    const uint32_t bulk = row_bytes & ~15u;
+    fence_async_smem();
     __syncwarp();
-    const PlaneRec& pl = sm.plane[s];
-    const fkb_chain_desc& ch = p.chains[pl.chain];
-    const uint32_t tyi = local / pl.tiles_x, txi = local - tyi * pl.tiles_x;
-    TileInfo ti;
-    ti.ox = txi * pl.tile_w; ti.oy = tyi * pl.tile_h;
-    ti.ow = min(pl.tile_w, pl.dst_w - ti.ox); ti.oh = min(pl.tile_h, pl.dst_h - ti.oy);
-    int r_lo = 0, r_hi = -1, c_lo = 0, c_hi = -1;
-    if (pl.kclass == KCLASS_POINT) {
-        r_lo = ti.oy; r_hi = ti.oy + ti.oh - 1; c_lo = ti.ox; c_hi = ti.ox + ti.ow - 1;
-    } else {
-        const bool par = ch.geometry == FKB_GEOM_RESIZE_PRESERVE_AR;
-        const int X1 = par ? pl.x1 : 0, Y1 = par ? pl.y1 : 0;
-        const int X2 = par ? pl.x2 : static_cast<int>(pl.dst_w) - 1, Y2 = par ? pl.y2 : static_cast<int>(pl.dst_h) - 1;
-        const int xa = max(static_cast<int>(ti.ox), X1), xb = min(static_cast<int>(ti.ox + ti.ow) - 1, X2);
-        const int ya = max(static_cast<int>(ti.oy), Y1), yb = min(static_cast<int>(ti.oy + ti.oh) - 1, Y2);
-        if (xa <= xb && ya <= yb) {
-            c_lo = axis_tap(xa - X1, pl.fx, pl.crop_w).i0; c_hi = axis_tap(xb - X1, pl.fx, pl.crop_w).i1;
-            r_lo = axis_tap(ya - Y1, pl.fy, pl.crop_h).i0; r_hi = axis_tap(yb - Y1, pl.fy, pl.crop_h).i1;
-        }
-    }
-    ti.r_lo = r_lo; ti.c_lo = c_lo;
-    ti.n_rows = r_hi >= r_lo ? static_cast<uint32_t>(r_hi - r_lo + 1) : 0u;
-    const uint32_t g0 = (pl.crop_x + static_cast<uint32_t>(c_lo)) * 3u;
-    const uint32_t g1 = (pl.crop_x + static_cast<uint32_t>(c_hi) + 1u) * 3u;
-    const uint32_t a0 = g0 & ~15u;
-    ti.shift = g0 - a0;
-    ti.row_bytes = ti.n_rows ? ((g1 + 15u) & ~15u) - a0 : 0u;
-    ti.ok = (ti.row_bytes <= pl.in_stride && static_cast<uint64_t>(ti.n_rows) * pl.in_stride <= kInBytes) ? 1u : 0u;
-    if (!ti.ok) { ti.n_rows = 0; ti.row_bytes = 0; }
     if (lane == 0) {
-        sm.info[s] = ti;
-        mbar_arrive_expect_tx(&sm.bar[s], ti.n_rows * ti.row_bytes);
+        if (bulk) bulk_store(gdst, smem_raw + srow, bulk);
+        bulk_commit();
     }
-    __syncwarp();
-    const uint8_t* src0 = pl.src + static_cast<size_t>(pl.crop_y + r_lo) * pl.src_pitch + a0;
-    for (uint32_t r = lane; r < ti.n_rows; r += 32)
-        bulk_load(in_buf + static_cast<size_t>(r) * pl.in_stride, src0 + static_cast<size_t>(r) * pl.src_pitch, ti.row_bytes, &sm.bar[s]);
-}
-
-// --- POINT tiles ------------------------------------------------------------------------------------------
-// uchar3 -> uchar3: 16 pixels (48 B) per thread step, three 128-bit shared loads and stores; thread chunks are
-// 48 B apart, which maps the eight lanes of a quarter-warp onto disjoint bank groups.
-__device__ __forceinline__ void point_tile_u8(const fkb_chain_desc& ch, const PlaneRec& pl, const TileInfo& ti,
-                                              const uint8_t* in, uint8_t* out, uint32_t out_stride) {
-    const uint32_t cpr = (ti.ow + 15) / 16, total = cpr * ti.oh;
-    for (uint32_t c = threadIdx.x; c < total; c += blockDim.x) {
-        const uint32_t ry = c / cpr, k = c - ry * cpr;
-        const uint4* src = reinterpret_cast<const uint4*>(in + static_cast<size_t>(ry) * pl.in_stride + k * 48);
-        uint32_t w[12];
-#pragma unroll
-        for (int i = 0; i < 3; ++i) { const uint4 q = src[i]; w[4 * i] = q.x; w[4 * i + 1] = q.y; w[4 * i + 2] = q.z; w[4 * i + 3] = q.w; }
-        float v[16][3];
-#pragma unroll
-        for (int b = 0; b < 48; ++b) v[b / 3][b % 3] = static_cast<float>((w[b >> 2] >> (8 * (b & 3))) & 0xffu);
-        apply_ops<16>(v, ch, pl, 0, ch.n_ops);
-#pragma unroll
-        for (int i = 0; i < 12; ++i) w[i] = 0;
-#pragma unroll
-        for (int b = 0; b < 48; ++b) w[b >> 2] |= static_cast<uint32_t>(v[b / 3][b % 3]) << (8 * (b & 3));
-        uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(ry) * out_stride + k * 48);
-#pragma unroll
-        for (int i = 0; i < 3; ++i) dst[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
-    }
-}
-// uchar3 -> float3: 4 pixels per thread step: three 32-bit shared loads (12 B apart: conflict-free), three
-// 128-bit shared stores (48 B apart).
-__device__ __forceinline__ void point_tile_f32(const fkb_chain_desc& ch, const PlaneRec& pl, const TileInfo& ti,
-                                               const uint8_t* in, uint8_t* out, uint32_t out_stride) {
-    const uint32_t cpr = (ti.ow + 3) / 4, total = cpr * ti.oh;
-    for (uint32_t c = threadIdx.x; c < total; c += blockDim.x) {
-        const uint32_t ry = c / cpr, k = c - ry * cpr;
-        const uint32_t* src = reinterpret_cast<const uint32_t*>(in + static_cast<size_t>(ry) * pl.in_stride + k * 12);
-        const uint32_t w[3] = {src[0], src[1], src[2]};
-        float v[4][3];
-#pragma unroll
-        for (int b = 0; b < 12; ++b) v[b / 3][b % 3] = static_cast<float>((w[b >> 2] >> (8 * (b & 3))) & 0xffu);
-        apply_ops<4>(v, ch, pl, 0, ch.n_ops);
-        float4* dst = reinterpret_cast<float4*>(out + static_cast<size_t>(ry) * out_stride + k * 48);
-        dst[0] = make_float4(v[0][0], v[0][1], v[0][2], v[1][0]);
-        dst[1] = make_float4(v[1][1], v[1][2], v[2][0], v[2][1]);
-        dst[2] = make_float4(v[2][2], v[3][0], v[3][1], v[3][2]);
+    if (row_bytes != bulk) {  // rare: a row whose byte length is not a multiple of 16
+        if (lane < row_bytes - bulk) gdst[bulk + lane] = smem_raw[srow + bulk + lane];
     }
 }
 
-// --- RESIZE tiles -----------------------------------------------------------------------------------------
-// One warp per output row, lanes along x, four pixels per lane per step (so the op decode is amortised).
-__device__ __forceinline__ void resize_tile(const fkb_chain_desc& ch, const PlaneRec& pl, const TileInfo& ti,
-                                            const uint8_t* in, uint8_t* out, uint32_t out_stride) {
-    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    const bool par = ch.geometry == FKB_GEOM_RESIZE_PRESERVE_AR;
-    const int X1 = par ? pl.x1 : 0, Y1 = par ? pl.y1 : 0;
-    const bool f32 = ch.dst_format == FKB_PIX_F32C3;
-    for (uint32_t ry = warp; ry < ti.oh; ry += nwarps) {
-        const int y = static_cast<int>(ti.oy + ry);
-        const bool row_in = !par || (y >= pl.y1 && y <= pl.y2);
-        const AxisTap ay = axis_tap(row_in ? y - Y1 : 0, pl.fy, pl.crop_h);
-        const uint8_t* row0 = in + static_cast<size_t>(row_in ? ay.i0 - ti.r_lo : 0) * pl.in_stride + ti.shift;
-        const uint8_t* row1 = in + static_cast<size_t>(row_in ? ay.i1 - ti.r_lo : 0) * pl.in_stride + ti.shift;
-        uint8_t* orow = out + static_cast<size_t>(ry) * out_stride;
-        for (uint32_t xb = 0; xb < ti.ow; xb += 128) {
-            float v[4][3];
+// Row pipeline of one item (a block of `nr` output rows of one plane, `ow` pixels wide).  `issue(r, stage)` starts
+// the bulk loads of row r (lane 0 announces the byte count, then issues); `compute(r, stage)` turns the staged bytes
+// into the output row in w.out[stage].  `k` counts this warp's steps: it selects the stage and the mbarrier phase.
+template <typename Issue, typename Compute>
+__device__ __forceinline__ bool run_rows(const WarpSlice& w, uint32_t nr, uint32_t& k, uint32_t lane, uint8_t* gdst,
+                                         uint32_t dst_pitch, uint32_t row_bytes, Issue issue, Compute compute) {
+    issue(0u, k & 1u);
+    for (uint32_t r = 0; r < nr; ++r, ++k) {
+        const uint32_t s = k & 1u;
+        if (r + 1 < nr) issue(r + 1, s ^ 1u);
+        const bool ok = mbar_wait_bounded(w.bar(s), (k >> 1) & 1u);
+        if (__any_sync(0xffffffffu, !ok)) return false;
+        // the bulk store that read w.out(s) two steps ago must have finished reading before the row is overwritten
+        if (lane == 0) bulk_wait_read_1();
+        __syncwarp();
+        compute(r, s);
+        store_row(gdst + static_cast<size_t>(r) * dst_pitch, w.out(s), row_bytes, lane);
+    }
+    return true;
+}
+
+// --- post-ops ---------------------------------------------------------------------------------------------
+// The ops that follow the read (POINT) or the interpolation (RESIZE).  Chains of the shape [Mul] [Add|Sub] [SaturateCast]
+// (each part optional, in this order) are specialised at compile time: KIND is a bit mask of the parts present and the
+// operands sit in registers for the whole item.  x - s is computed as x + (-s), which is the same IEEE operation.  Every
+// other chain runs through the op interpreter (KIND = kPostGeneric).
+constexpr int kPostMul = 1, kPostAdd = 2, kPostSat = 4, kPostGeneric = 8;
+
+struct PostParams {
+    float m[3], a[3];
+};
+__device__ __forceinline__ PostParams load_post(const fkb_chain_desc& ch, const PlaneRec& pl, uint32_t first) {
+    PostParams q;
 #pragma unroll
-            for (int n = 0; n < 4; ++n) {
-                const uint32_t lx = xb + lane + 32 * n;
-                const int x = static_cast<int>(ti.ox + lx);
-                const bool inside = lx < ti.ow && row_in && (!par || (x >= pl.x1 && x <= pl.x2));
-                if (inside) {
-                    const AxisTap ax = axis_tap(x - X1, pl.fx, pl.crop_w);
-                    const uint32_t b0 = static_cast<uint32_t>(ax.i0 - ti.c_lo) * 3u, b1 = static_cast<uint32_t>(ax.i1 - ti.c_lo) * 3u;
-                    const float w00 = __fmul_rn(ax.w0, ay.w0), w10 = __fmul_rn(ax.w1, ay.w0);
-                    const float w01 = __fmul_rn(ax.w0, ay.w1), w11 = __fmul_rn(ax.w1, ay.w1);
+    for (int c = 0; c < 3; ++c) { q.m[c] = 1.f; q.a[c] = 0.f; }
+    for (uint32_t i = first; i < ch.n_ops; ++i) {
+        const fkb_op& op = ch.ops[i];
+        const float* v = op.plane_slot >= 0 ? pl.params[op.plane_slot] : op.v;
+        if (op.code == FKB_OP_MUL) { q.m[0] = v[0]; q.m[1] = v[1]; q.m[2] = v[2]; }
+        else if (op.code == FKB_OP_ADD) { q.a[0] = v[0]; q.a[1] = v[1]; q.a[2] = v[2]; }
+        else if (op.code == FKB_OP_SUB) { q.a[0] = -v[0]; q.a[1] = -v[1]; q.a[2] = -v[2]; }
+    }
+    return q;
+}
+// Applies the post-ops to one channel of a pixel pair.  With a SaturateCast the result is left as 2^23 + n (the
+// integer n sits in the low byte of the bit pattern), ready to be stored as a byte.
+template <int KIND>
+__device__ __forceinline__ f2 post_channel(f2 r, const PostParams& q, int c, float nz) {
+    if (KIND & kPostMul) r = (KIND & kPostAdd) ? mul2_unfusable(r, f2{q.m[c], q.m[c]}, nz) : mul2(r, f2{q.m[c], q.m[c]});
+    if (KIND & kPostAdd) r = add2(r, f2{q.a[c], q.a[c]});
+    if (KIND & kPostSat) {
+        r.x = fminf(fmaxf(r.x, 0.f), 255.f);
+        r.y = fminf(fmaxf(r.y, 0.f), 255.f);
+        r = add2(r, f2{kMagic, kMagic});
+    }
+    return r;
+}
+
+// --- POINT items ------------------------------------------------------------------------------------------
+// uchar3 -> uchar3: each lane owns 16 pixels (48 B): three 128-bit shared loads and stores; lane chunks are 48 B
+// apart, which maps the eight lanes of a quarter-warp onto disjoint bank groups.
+// uchar3 -> float3: each lane owns 4 pixels per pass: three 32-bit shared loads (12 B apart), three 128-bit stores.
+template <bool F32, int KIND>
+__device__ __forceinline__ bool point_item(const LaunchParams& p, const WarpSlice& w, uint32_t ox, uint32_t oy0,
+                                           uint32_t ow, uint32_t nr, uint32_t& k, uint32_t lane) {
+    const PlaneRec& pl = *w.pl;
+    const fkb_chain_desc& ch = p.chains[pl.chain];
+    const float nz = p.neg_zero;
+    // Mul / Add operands in the order the channels appear in a run of byte pairs: (c0,c1) (c2,c0) (c1,c2)
+    const PostParams post = load_post(ch, pl, 0);
+    f2 mp[3], ap[3];
 #pragma unroll
-                    for (int c = 0; c < 3; ++c)
-                        v[n][c] = bilerp(static_cast<float>(row0[b0 + c]), static_cast<float>(row0[b1 + c]),
-                                         static_cast<float>(row1[b0 + c]), static_cast<float>(row1[b1 + c]), w00, w10, w01, w11);
-                } else {
-                    v[n][0] = pl.bg[0]; v[n][1] = pl.bg[1]; v[n][2] = pl.bg[2];
-                }
-            }
-            apply_ops<4>(v, ch, pl, ch.n_pre_ops, ch.n_ops);
+    for (int kk = 0; kk < 3; ++kk) {
+        mp[kk] = f2{__fmul_rn(post.m[(2 * kk) % 3], kByteScale), __fmul_rn(post.m[(2 * kk + 1) % 3], kByteScale)};
+        ap[kk] = f2{post.a[(2 * kk) % 3], post.a[(2 * kk + 1) % 3]};
+    }
+    const uint32_t in_bytes = (ow * 3u + 15u) & ~15u;
+    const uint8_t* gsrc = pl.src + static_cast<size_t>(pl.crop_y + oy0) * pl.src_pitch + static_cast<size_t>(pl.crop_x + ox) * 3u;
+    const uint32_t src_pitch = pl.src_pitch;
+    uint8_t* gdst = pl.dst + static_cast<size_t>(oy0) * pl.dst_pitch + static_cast<size_t>(ox) * (F32 ? 12u : 3u);
+    auto issue = [&](uint32_t r, uint32_t s) {
+        if (lane == 0) {
+            mbar_arrive_expect_tx(w.bar(s), in_bytes);
+            bulk_load(smem_raw + w.in(s), gsrc + static_cast<size_t>(r) * src_pitch, in_bytes, w.bar(s));
+        }
+    };
+    auto compute = [&](uint32_t, uint32_t s) {
+        if (F32) {
+            // 4 pixels = 12 source bytes = 6 byte pairs per lane step.  A pair (two neighbouring bytes of one word)
+            // becomes two half-subnormals with one byte permute, is widened to fp32 (b * 2^-24) and multiplied by the
+            // Mul operand pre-scaled by 2^24 (or by 2^24 alone), all exact; pair k holds channels (2k mod 3, 2k+1 mod 3).
+            for (uint32_t c = lane; c * 4u < ow; c += 32) {
+                const uint32_t* src = reinterpret_cast<const uint32_t*>(smem_raw + w.in(s) + c * 12u);
+                const uint32_t q[3] = {src[0], src[1], src[2]};
+                f2 v[6];
 #pragma unroll
-            for (int n = 0; n < 4; ++n) {
-                const uint32_t lx = xb + lane + 32 * n;
-                if (lx < ti.ow) {
-                    if (f32) {
-                        float* q = reinterpret_cast<float*>(orow) + lx * 3;
-                        q[0] = v[n][0]; q[1] = v[n][1]; q[2] = v[n][2];
-                    } else {
-                        uint8_t* q = orow + lx * 3;
-                        q[0] = static_cast<uint8_t>(v[n][0]); q[1] = static_cast<uint8_t>(v[n][1]); q[2] = static_cast<uint8_t>(v[n][2]);
+                for (int i = 0; i < 3; ++i) {
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const uint32_t two = __byte_perm(q[i], 0u, h ? 0x4342u : 0x4140u);
+                        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&two));
+                        const int kk = (2 * i + h) % 3;
+                        f2 t = {f.x, f.y};
+                        if (KIND == kPostGeneric) t = mul2(t, f2{kByteScale, kByteScale});
+                        else t = (KIND & kPostAdd) ? mul2_unfusable(t, mp[kk], nz) : mul2(t, mp[kk]);
+                        if (KIND != kPostGeneric && (KIND & kPostAdd)) t = add2(t, ap[kk]);
+                        v[2 * i + h] = t;
                     }
                 }
+                if (KIND == kPostGeneric) {
+                    float t[4][3] = {{v[0].x, v[0].y, v[1].x}, {v[1].y, v[2].x, v[2].y}, {v[3].x, v[3].y, v[4].x}, {v[4].y, v[5].x, v[5].y}};
+                    apply_ops<4>(t, ch, pl, 0, ch.n_ops);
+                    v[0] = f2{t[0][0], t[0][1]}; v[1] = f2{t[0][2], t[1][0]}; v[2] = f2{t[1][1], t[1][2]};
+                    v[3] = f2{t[2][0], t[2][1]}; v[4] = f2{t[2][2], t[3][0]}; v[5] = f2{t[3][1], t[3][2]};
+                }
+                float4* dst = reinterpret_cast<float4*>(smem_raw + w.out(s) + c * 48u);
+                dst[0] = make_float4(v[0].x, v[0].y, v[1].x, v[1].y);
+                dst[1] = make_float4(v[2].x, v[2].y, v[3].x, v[3].y);
+                dst[2] = make_float4(v[4].x, v[4].y, v[5].x, v[5].y);
+            }
+        } else {
+            for (uint32_t c = lane; c * 16u < ow; c += 32) {
+                const uint4* src = reinterpret_cast<const uint4*>(smem_raw + w.in(s) + c * 48u);
+                uint32_t q[12];
+#pragma unroll
+                for (int i = 0; i < 3; ++i) { const uint4 t = src[i]; q[4 * i] = t.x; q[4 * i + 1] = t.y; q[4 * i + 2] = t.z; q[4 * i + 3] = t.w; }
+                float v[16][3];
+#pragma unroll
+                for (int b = 0; b < 48; ++b) v[b / 3][b % 3] = FKB_BYTE_F32(q[b >> 2], b & 3);
+                apply_ops<16>(v, ch, pl, 0, ch.n_ops);
+#pragma unroll
+                for (int i = 0; i < 12; ++i) q[i] = 0;
+#pragma unroll
+                for (int b = 0; b < 48; ++b) q[b >> 2] |= u8_of_exact(v[b / 3][b % 3]) << (8 * (b & 3));
+                uint4* dst = reinterpret_cast<uint4*>(smem_raw + w.out(s) + c * 48u);
+#pragma unroll
+                for (int i = 0; i < 3; ++i) dst[i] = make_uint4(q[4 * i], q[4 * i + 1], q[4 * i + 2], q[4 * i + 3]);
             }
         }
+    };
+    return run_rows(w, nr, k, lane, gdst, pl.dst_pitch, ow * (F32 ? 12u : 3u), issue, compute);
+}
+
+// --- RESIZE items -----------------------------------------------------------------------------------------
+// The columns of the item that lie inside the resized image (PRESERVE_AR leaves bars of background left and right)
+// are dealt to the lanes in groups of 32: lane l owns columns xa+l, xa+32+l, ...; the last group is shifted left so
+// that it is full too (a few columns are then computed twice, with identical results).  Everything that depends only
+// on the column — the byte offset of its tap pair in a staged row and the two horizontal weights — is computed once
+// per item and kept in registers for all rows.  A tap pair (x1, x1+1) is six consecutive bytes; the column one past
+// the crop is made a copy of the last column after the row lands, which is exactly the reference's clamp of x2.
+// Bytes become fp32 through the half-subnormal trick (byte_times_2m24), and all arithmetic runs on pixel pairs with
+// packed f32x2 instructions.  The background bars are written into the two output-row buffers once per item.
+template <bool F32, int KIND>
+__device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSlice& w, uint32_t ox, uint32_t oy0,
+                                            uint32_t ow, uint32_t nr, uint32_t& k, uint32_t lane) {
+    constexpr uint32_t ELT = F32 ? 12u : 3u;
+    const PlaneRec& pl = *w.pl;
+    const fkb_chain_desc& ch = p.chains[pl.chain];
+    const bool par = ch.geometry == FKB_GEOM_RESIZE_PRESERVE_AR;
+    const int X1 = par ? pl.x1 : 0, Y1 = par ? pl.y1 : 0;
+    const int X2 = par ? pl.x2 : static_cast<int>(pl.dst_w) - 1, Y2 = par ? pl.y2 : static_cast<int>(pl.dst_h) - 1;
+    const int crop_w = pl.crop_w, crop_h = pl.crop_h;
+    const float fx = pl.fx, fy = pl.fy, nz = p.neg_zero;
+    const int xa = max(static_cast<int>(ox), X1), xb = min(static_cast<int>(ox + ow) - 1, X2);
+    const int n_in = xb >= xa ? xb - xa + 1 : 0;     // columns of this item inside the resized image
+    const int nj = (n_in + 31) >> 5;                 // groups of 32 columns
+    const int c_lo = n_in ? axis_tap(xa - X1, fx, crop_w).i0 : 0;
+    const int c_hi = n_in ? axis_tap(xb - X1, fx, crop_w).i0 + 1 : 0;  // highest column a tap pair touches
+    const bool replicate = c_hi >= crop_w;
+    const uint32_t g0 = (pl.crop_x + static_cast<uint32_t>(c_lo)) * 3u;
+    const uint32_t g1 = (pl.crop_x + static_cast<uint32_t>(min(c_hi, crop_w - 1)) + 1u) * 3u;
+    const uint32_t a0 = g0 & ~15u, shift = g0 - a0;
+    const uint32_t row_bytes = ((g1 + 15u) & ~15u) - a0;
+    if (row_bytes + 32u > kInRowBytes) return false;  // the host lowering guarantees the footprint fits
+
+    // per-column state of this lane: staged-row byte offset of the tap pair, horizontal weights, output offset
+    // (columns that do not exist write to the spare bytes behind the output row)
+    uint32_t boff[8], ooff[8];
+    float wx0[8], wx1[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        int col = 32 * j + static_cast<int>(lane);                 // index among the inside columns
+        if (j == nj - 1 && n_in >= 32) col = n_in - 32 + static_cast<int>(lane);  // last group, shifted to be full
+        const bool live = j < nj && col < n_in;
+        col = min(col, max(n_in - 1, 0));
+        const AxisTap t = axis_tap(xa + col - X1, fx, crop_w);
+        boff[j] = n_in ? static_cast<uint32_t>(t.i0 - c_lo) * 3u + shift : 0u;
+        wx0[j] = t.w0; wx1[j] = t.w1;
+        ooff[j] = live ? static_cast<uint32_t>(xa - static_cast<int>(ox) + col) * ELT : kOutRowBytes;
+    }
+    // Offset (in a staged row) of the crop's last column when a tap pair reaches one past it; that column is then
+    // duplicated into the next three bytes.  Otherwise the copy is aimed at the unused tail of the staged row.
+    const uint32_t rep_off = replicate ? static_cast<uint32_t>(crop_w - 1 - c_lo) * 3u + shift : kInRowBytes - 8u;
+    const uint8_t* gsrc = pl.src + static_cast<size_t>(pl.crop_y) * pl.src_pitch + a0;
+    const uint32_t src_pitch = pl.src_pitch, dst_pitch = pl.dst_pitch;
+    uint8_t* gdst = pl.dst + static_cast<size_t>(oy0) * dst_pitch + static_cast<size_t>(ox) * ELT;
+
+    // what a background pixel becomes, as the bit patterns that are stored
+    const PostParams post = load_post(ch, pl, ch.n_pre_ops);
+    uint32_t bgbits[3];
+    {
+        float b[1][3] = {{pl.bg[0], pl.bg[1], pl.bg[2]}};
+        apply_ops<1>(b, ch, pl, ch.n_pre_ops, ch.n_ops);
+#pragma unroll
+        for (int c = 0; c < 3; ++c) bgbits[c] = F32 ? __float_as_uint(b[0][c]) : u8_of_exact(b[0][c]);
+    }
+    auto put = [&](uint32_t q, uint32_t b0, uint32_t b1, uint32_t b2) {
+        if (F32) { uint32_t* f = reinterpret_cast<uint32_t*>(smem_raw + q); f[0] = b0; f[1] = b1; f[2] = b2; }
+        else { smem_raw[q] = static_cast<uint8_t>(b0); smem_raw[q + 1] = static_cast<uint8_t>(b1); smem_raw[q + 2] = static_cast<uint8_t>(b2); }
+    };
+    // the bars left and right of the image are the same for every row of the item: fill them in both row buffers once
+    // (after the bulk stores that still read those buffers have finished reading)
+    if (lane == 0) bulk_wait_read_all();
+    __syncwarp();
+    if (static_cast<uint32_t>(n_in) < ow) {
+        for (int c = static_cast<int>(lane); c < static_cast<int>(ow); c += 32) {
+            if (n_in == 0 || c < xa - static_cast<int>(ox) || c > xb - static_cast<int>(ox)) {
+                put(w.out(0) + static_cast<uint32_t>(c) * ELT, bgbits[0], bgbits[1], bgbits[2]);
+                put(w.out(1) + static_cast<uint32_t>(c) * ELT, bgbits[0], bgbits[1], bgbits[2]);
+            }
+        }
+    }
+
+    AxisTap ay_next;
+    bool in_next;
+    // Row r's vertical taps, and (lane 0) its bulk loads into stage s.  Always two staged rows (the second repeats the
+    // first where the reference clamps y2), so that the second row sits at a fixed distance from the first.  With
+    // `wait_out`, lane 0 first waits until the bulk store issued two rows ago has finished reading its row buffer.
+    auto issue = [&](uint32_t r, uint32_t s, bool load, bool wait_out) {
+        const int y = static_cast<int>(oy0 + r);
+        in_next = n_in > 0 && y >= Y1 && y <= Y2;
+        ay_next = axis_tap(in_next ? y - Y1 : 0, fy, crop_h);
+        if (lane == 0) {
+            if (wait_out) bulk_wait_read_1();
+            if (load) {
+                mbar_arrive_expect_tx(w.bar(s), in_next ? 2u * row_bytes : 0u);
+                if (in_next) {
+                    bulk_load(smem_raw + w.in(s), gsrc + static_cast<size_t>(ay_next.i0) * src_pitch, row_bytes, w.bar(s));
+                    bulk_load(smem_raw + w.in(s) + kInRowBytes, gsrc + static_cast<size_t>(ay_next.i1) * src_pitch, row_bytes, w.bar(s));
+                }
+            }
+        }
+    };
+
+    // one pair of columns (j, j+1) of the current row
+    auto pair = [&](int j, uint32_t in_s, uint32_t out_s, f2 wy0, f2 wy1) {
+        const uint32_t a0p = in_s + boff[j], a1p = in_s + boff[j + 1];
+        const f2 wx0p = {wx0[j], wx0[j + 1]}, wx1p = {wx1[j], wx1[j + 1]};
+        const f2 w00 = mul2(wx0p, wy0), w10 = mul2(wx1p, wy0), w01 = mul2(wx0p, wy1), w11 = mul2(wx1p, wy1);
+        f2 v[3];
+#pragma unroll
+        for (int c = 0; c < 3; ++c) {
+            // taps of the two columns: (x1,y1) (x1+1,y1) (x1,y2) (x1+1,y2); bytes come back as b * 2^-24
+            const f2 p00 = {byte_times_2m24(smem_raw[a0p + c]), byte_times_2m24(smem_raw[a1p + c])};
+            const f2 p10 = {byte_times_2m24(smem_raw[a0p + 3 + c]), byte_times_2m24(smem_raw[a1p + 3 + c])};
+            const f2 p01 = {byte_times_2m24(smem_raw[a0p + kInRowBytes + c]), byte_times_2m24(smem_raw[a1p + kInRowBytes + c])};
+            const f2 p11 = {byte_times_2m24(smem_raw[a0p + kInRowBytes + 3 + c]), byte_times_2m24(smem_raw[a1p + kInRowBytes + 3 + c])};
+            v[c] = add2(add2(add2(mul2_unfusable(p00, w00, nz), mul2_unfusable(p10, w10, nz)), mul2_unfusable(p01, w01, nz)),
+                        mul2_unfusable(p11, w11, nz));
+        }
+        uint32_t bx[3], by[3];
+        if (KIND == kPostGeneric) {
+            float t[2][3] = {{v[0].x, v[1].x, v[2].x}, {v[0].y, v[1].y, v[2].y}};
+            apply_ops<2>(t, ch, pl, ch.n_pre_ops, ch.n_ops);
+#pragma unroll
+            for (int c = 0; c < 3; ++c) {
+                bx[c] = F32 ? __float_as_uint(t[0][c]) : u8_of_exact(t[0][c]);
+                by[c] = F32 ? __float_as_uint(t[1][c]) : u8_of_exact(t[1][c]);
+            }
+        } else {
+#pragma unroll
+            for (int c = 0; c < 3; ++c) {
+                const f2 t = post_channel<KIND>(v[c], post, c, nz);
+                bx[c] = __float_as_uint(t.x); by[c] = __float_as_uint(t.y);  // with SaturateCast: low byte = value
+            }
+        }
+        put(out_s + ooff[j], bx[0], bx[1], bx[2]);
+        put(out_s + ooff[j + 1], by[0], by[1], by[2]);
+    };
+
+    const int npairs = (nj + 1) >> 1;
+    issue(0u, k & 1u, true, false);
+    for (uint32_t r = 0; r < nr; ++r, ++k) {
+        const uint32_t s = k & 1u;
+        const AxisTap ay = ay_next;
+        const bool row_in = in_next;
+        issue(r + 1, s ^ 1u, r + 1 < nr, true);  // also: the store that read w.out(s) two rows ago is done with it
+        const bool ok = mbar_wait_bounded(w.bar(s), (k >> 1) & 1u);
+        if (__any_sync(0xffffffffu, !ok)) return false;  // (a convergence point for the whole warp, too)
+        const uint32_t in_s = w.in(s), out_s = w.out(s);
+        if (!row_in) {
+            // a row above or below the image: background over the inside columns too
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (j < nj) put(out_s + ooff[j], bgbits[0], bgbits[1], bgbits[2]);
+        } else {
+            {   // every lane writes the same three bytes (even lanes the first staged row, odd lanes the second)
+                const uint32_t q = in_s + (lane & 1u) * kInRowBytes + rep_off;
+                const uint8_t c0 = smem_raw[q], c1 = smem_raw[q + 1], c2 = smem_raw[q + 2];
+                smem_raw[q + 3] = c0; smem_raw[q + 4] = c1; smem_raw[q + 5] = c2;
+                __syncwarp();
+            }
+            const f2 wy0 = {__fmul_rn(ay.w0, kByteScale), __fmul_rn(ay.w0, kByteScale)};  // vertical weights, times 2^24
+            const f2 wy1 = {__fmul_rn(ay.w1, kByteScale), __fmul_rn(ay.w1, kByteScale)};
+            switch (npairs) {  // one uniform jump instead of a test per pair
+            case 4: pair(6, in_s, out_s, wy0, wy1);
+            case 3: pair(4, in_s, out_s, wy0, wy1);
+            case 2: pair(2, in_s, out_s, wy0, wy1);
+            case 1: pair(0, in_s, out_s, wy0, wy1);
+            default: break;
+            }
+        }
+        store_row(gdst + static_cast<size_t>(r) * dst_pitch, out_s, ow * ELT, lane);
+    }
+    return true;
+}
+
+template <bool F32>
+__device__ __forceinline__ bool resize_dispatch(const LaunchParams& p, const WarpSlice& w, uint32_t kind, uint32_t ox,
+                                                uint32_t oy0, uint32_t ow, uint32_t nr, uint32_t& k, uint32_t lane) {
+    constexpr int S = F32 ? 0 : kPostSat;  // a uchar3 destination ends in a SaturateCast, a float3 one cannot
+    switch (kind) {
+    case S: return resize_item<F32, S>(p, w, ox, oy0, ow, nr, k, lane);
+    case S | kPostMul: return resize_item<F32, S | kPostMul>(p, w, ox, oy0, ow, nr, k, lane);
+    case S | kPostAdd: return resize_item<F32, S | kPostAdd>(p, w, ox, oy0, ow, nr, k, lane);
+    case S | kPostMul | kPostAdd: return resize_item<F32, S | kPostMul | kPostAdd>(p, w, ox, oy0, ow, nr, k, lane);
+    default: return resize_item<F32, kPostGeneric>(p, w, ox, oy0, ow, nr, k, lane);
     }
 }
 
 __global__ void __launch_bounds__(kStagedThreads, 2) staged_kernel(const __grid_constant__ LaunchParams p) {
-    extern __shared__ __align__(128) uint8_t smem_raw[];
-    StagedSmem& sm = *reinterpret_cast<StagedSmem*>(smem_raw);
-    uint8_t* in_buf[2] = {smem_raw + kSmemHeader, smem_raw + kSmemHeader + kInBytes};
-    uint8_t* out_buf[2] = {smem_raw + kSmemHeader + 2 * kInBytes, smem_raw + kSmemHeader + 2 * kInBytes + kOutBytes};
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-
-    if (threadIdx.x == 0) {
-        mbar_init(&sm.bar[0], 1);
-        mbar_init(&sm.bar[1], 1);
+    const WarpSlice w = warp_slice(warp * kSliceBytes);
+    if (lane == 0) {
+        mbar_init(w.bar(0), 1);
+        mbar_init(w.bar(1), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    __syncthreads();
-    if (warp == 0 && blockIdx.x < p.n_tiles) produce_tile(p, blockIdx.x, 0, sm, in_buf[0], lane);
-    __syncthreads();
-
-    bool failed = false;
-    uint32_t it = 0;
-    for (uint32_t t = blockIdx.x; t < p.n_tiles; t += gridDim.x, ++it) {
-        const uint32_t s = it & 1;
-        const uint32_t next = t + gridDim.x;
-        if (warp == 0 && next < p.n_tiles) produce_tile(p, next, s ^ 1, sm, in_buf[s ^ 1], lane);
-
-        const TileInfo ti = sm.info[s];
-        const PlaneRec& pl = sm.plane[s];
-        const fkb_chain_desc& ch = p.chains[pl.chain];
-        const bool f32 = ch.dst_format == FKB_PIX_F32C3;
-        const uint32_t elt = f32 ? 12u : 3u;
-        const uint32_t out_stride = pl.out_stride;
-        // everything the store phase needs is read here: after the barrier below warp 0 may already be
-        // overwriting sm.plane / sm.info of the other buffer, and one iteration later this one
-        const uint32_t dst_pitch = pl.dst_pitch;
-        const uint32_t row_bytes = ti.ow * elt, bulk_bytes = row_bytes & ~15u, tail = row_bytes - bulk_bytes;
-        uint8_t* const gdst = pl.dst + static_cast<size_t>(ti.oy) * dst_pitch + static_cast<size_t>(ti.ox) * elt;
-
-        if (!mbar_wait_bounded(&sm.bar[s], (it >> 1) & 1)) failed = true;
-        if (!ti.ok) failed = true;
-        if (!failed) {
-            if (pl.kclass == KCLASS_POINT) {
-                if (f32) point_tile_f32(ch, pl, ti, in_buf[s], out_buf[s], out_stride);
-                else point_tile_u8(ch, pl, ti, in_buf[s], out_buf[s], out_stride);
-            } else {
-                resize_tile(ch, pl, ti, in_buf[s], out_buf[s], out_stride);
+    __syncwarp();
+    const uint32_t warps_per_cta = blockDim.x >> 5;
+    // item i runs on warp (i / gridDim.x) % warps_per_cta of CTA i % gridDim.x: a small launch spreads over all SMs
+    const uint32_t first = warp * gridDim.x + blockIdx.x, stride = gridDim.x * warps_per_cta;
+    const PlaneRec* table = plane_table(p);
+    uint32_t k = 0;
+    bool ok = true;
+    for (uint32_t item = first; item < p.n_tiles && ok; item += stride) {
+        uint32_t local;
+        const uint32_t z = tile_to_plane(p, item, local);
+        __syncwarp();
+        if (lane < sizeof(PlaneRec) / 16)
+            reinterpret_cast<uint4*>(smem_raw + w.base + 16)[lane] = reinterpret_cast<const uint4*>(table + z)[lane];
+        __syncwarp();
+        const PlaneRec& pl = *w.pl;
+        const uint32_t tyi = local / pl.tiles_x, txi = local - tyi * pl.tiles_x;
+        const uint32_t ox = txi * pl.tile_w, oy0 = tyi * pl.tile_h;
+        const uint32_t ow = min(pl.tile_w, pl.dst_w - ox), nr = min(pl.tile_h, pl.dst_h - oy0);
+        const bool f32 = p.chains[pl.chain].dst_format == FKB_PIX_F32C3;
+        if (pl.kclass == KCLASS_POINT) {
+            if (!f32) ok = point_item<false, kPostGeneric>(p, w, ox, oy0, ow, nr, k, lane);
+            else switch (p.post_kind[pl.chain]) {
+                case 0: ok = point_item<true, 0>(p, w, ox, oy0, ow, nr, k, lane); break;
+                case kPostMul: ok = point_item<true, kPostMul>(p, w, ox, oy0, ow, nr, k, lane); break;
+                case kPostAdd: ok = point_item<true, kPostAdd>(p, w, ox, oy0, ow, nr, k, lane); break;
+                case kPostMul | kPostAdd: ok = point_item<true, kPostMul | kPostAdd>(p, w, ox, oy0, ow, nr, k, lane); break;
+                default: ok = point_item<true, kPostGeneric>(p, w, ox, oy0, ow, nr, k, lane); break;
             }
         }
-        fence_async_smem();
-        // the stores issued one iteration ago (from the other output buffer) must have been read out of shared
-        // memory before anybody overwrites that buffer in the next iteration
-        if (warp == 0) bulk_wait_read_all();
-        if (__syncthreads_or(failed ? 1 : 0)) { failed = true; break; }
-
-        if (warp == 0) {
-            if (tail == 0 && row_bytes == out_stride && row_bytes == dst_pitch) {
-                if (lane == 0) bulk_store(gdst, out_buf[s], row_bytes * ti.oh);  // the whole tile is one contiguous run
-            } else if (bulk_bytes) {
-                for (uint32_t r = lane; r < ti.oh; r += 32)
-                    bulk_store(gdst + static_cast<size_t>(r) * dst_pitch, out_buf[s] + static_cast<size_t>(r) * out_stride, bulk_bytes);
-            }
-            bulk_commit();
-        }
-        if (tail) {  // the last (row_bytes mod 16) bytes of each row go out with plain stores
-            for (uint32_t i = threadIdx.x; i < tail * ti.oh; i += blockDim.x) {
-                const uint32_t r = i / tail, b = bulk_bytes + (i - r * tail);
-                gdst[static_cast<size_t>(r) * dst_pitch + b] = out_buf[s][static_cast<size_t>(r) * out_stride + b];
-            }
-        }
+        else ok = f32 ? resize_dispatch<true>(p, w, p.post_kind[pl.chain], ox, oy0, ow, nr, k, lane)
+                      : resize_dispatch<false>(p, w, p.post_kind[pl.chain], ox, oy0, ow, nr, k, lane);
     }
-    if (warp == 0) bulk_wait_all();
-    if (failed) {
-        // give copies that are still in flight into shared memory a bounded chance to land before the CTA retires
-        mbar_wait_bounded(&sm.bar[(it + 1) & 1], ((it + 1) >> 1) & 1);
-        if (threadIdx.x == 0) atomicExch(p.status, FKB_ERR_DEVICE_WAIT);
+    if (lane == 0) bulk_wait_all();  // shared memory must stay valid until the last bulk store has read it
+    if (!ok) {
+        // a copy announced on the other stage may still be in flight: give it a bounded chance to land
+        mbar_wait_bounded(w.bar((k + 1) & 1u), ((k + 1) >> 1) & 1u);
+        if (lane == 0) atomicExch(p.status, FKB_ERR_DEVICE_WAIT);
     }
 }
 

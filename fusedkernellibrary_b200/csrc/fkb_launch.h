@@ -8,11 +8,16 @@ namespace fkb {
 struct LaunchParams;
 
 constexpr uint32_t kStagedThreads = 256;
-// Shared memory of one staged CTA: a 1 KB header (mbarriers, tile infos, plane records), two source buffers
-// and two output buffers.  111 KB in total, so two CTAs fit in the 228 KB of an SM.
-constexpr uint32_t kInBytes = 32 * 1024;
-constexpr uint32_t kOutBytes = 23 * 1024;
-constexpr uint32_t kStagedSmemBytes = 1024 + 2 * (kInBytes + kOutBytes);
+constexpr uint32_t kStagedWarps = kStagedThreads / 32;
+// Shared memory of one warp of a staged CTA: a 256-byte header (two mbarriers, the plane record), two stages of two
+// source rows, and two output rows.  12.5 KB per warp, 100 KB per CTA, so two CTAs fit in the 228 KB of an SM.
+constexpr uint32_t kSliceHeader = 256;
+constexpr uint32_t kInRowBytes = 1600;   // one staged source row segment (512 uchar3 pixels + alignment slack)
+constexpr uint32_t kOutRowBytes = 3072;  // one output row segment (256 float3 pixels, or 512 uchar3 with room to spare)
+constexpr uint32_t kOutSlotBytes = kOutRowBytes + 16;  // the 16 spare bytes take the stores of columns that do not exist
+constexpr uint32_t kSliceBytes = kSliceHeader + 4 * kInRowBytes + 2 * kOutSlotBytes;
+constexpr uint32_t kStagedSmemBytes = kStagedWarps * kSliceBytes;
+constexpr uint32_t kMaxRowsPerItem = 32;  // upper bound of the output rows a warp processes per item
 
 cudaError_t launch_staged(const LaunchParams& p, uint32_t grid, cudaStream_t stream);
 cudaError_t launch_gather(const LaunchParams& p, dim3 grid, cudaStream_t stream);

@@ -14,7 +14,7 @@
 
 namespace fkb {
 
-enum : uint32_t { KCLASS_GATHER = 0, KCLASS_POINT = 1, KCLASS_RESIZE = 2 };
+enum : uint32_t { KCLASS_GATHER = 0, KCLASS_POINT = 1, KCLASS_RESIZE = 2, KCLASS_LUT = 3 };
 
 // One output plane as the kernels see it: the caller's fkb_plane_desc plus what the host lowering derived
 // (which kernel path runs it, its tile shape and its first tile index).
@@ -34,11 +34,12 @@ struct __align__(16) PlaneRec {
     uint32_t kclass;
     uint32_t tile_w, tile_h;    // output pixels per tile
     uint32_t tiles_x, tiles_y;  // tiles per plane
-    uint32_t tile_base;         // index of this plane's first tile in the launch
+    uint32_t tile_base;         // index of this plane's first staged tile in the launch (LUT planes: first LUT unit)
     uint32_t in_stride;         // bytes between staged source rows in shared memory (multiple of 16)
     uint32_t out_stride;        // bytes between rows of the shared output tile (multiple of 16)
     float params[FKB_MAX_PLANE_PARAMS][3];
-    uint32_t pad_[2];
+    uint32_t lut_base;          // LUT units of all earlier planes (monotone over the table, searched by lut_kernel)
+    uint32_t pad_[1];
 };
 static_assert(sizeof(PlaneRec) == 192, "layout is mirrored by the host lowering");
 static_assert(sizeof(PlaneRec) % 16 == 0, "PlaneRec is copied in 16-byte words");
@@ -52,6 +53,8 @@ struct LaunchParams {
     uint32_t n_tiles;
     uint32_t tiles_per_plane;  // > 0 when every plane has the same number of tiles; else PlaneRec::tile_base is searched
     int* status;
+    uint32_t n_lut_units;     // work units of lut_kernel (a block of rows of one LUT plane)
+    uint32_t lut_swap;        // bit c: chain c contains an odd number of channel reorders
     uint32_t post_kind[FKB_MAX_CHAINS];  // per chain: bit mask of {Mul, Add|Sub, SaturateCast} when its post-ops have that shape, else 8
     float neg_zero;           // -0.0f, deliberately opaque to the compiler (see mul2_unfusable)
     PlaneRec inline_planes[kInlinePlanes];

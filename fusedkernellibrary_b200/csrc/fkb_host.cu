@@ -149,6 +149,11 @@ void classify(const fkb_chain_desc& ch, PlaneRec& r) {
         // one row segment per step: 16 pixels per lane (uchar3 out) or 4 pixels per lane in two passes (float3 out)
         r.tile_w = std::min(r.dst_w, f32 ? 256u : 512u);
         r.kclass = KCLASS_POINT;
+        if (!f32) {  // uchar3 -> uchar3 through per-channel ops only: table lookups (lut_kernel)
+            bool per_channel = true;
+            for (uint32_t i = 0; i < ch.n_ops; ++i) per_channel = per_channel && ch.ops[i].code != FKB_OP_YUV2RGB;
+            if (per_channel) r.kclass = KCLASS_LUT;
+        }
     } else {
         for (uint32_t i = 0; i < ch.n_pre_ops; ++i)
             if (ch.ops[i].code != FKB_OP_CAST_F32) return;  // taps are transformed before interpolation: general path
@@ -195,6 +200,7 @@ struct Lowered {
     std::vector<PlaneRec> recs;
     LaunchParams lp;
     uint32_t staged_grid = 0;
+    uint32_t lut_grid = 0;
     dim3 gather_grid{0, 0, 0};
     uint32_t kernels = 0;
 };
@@ -237,7 +243,8 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         const int e = device_sm_count(sms);
         if (e != FKB_OK) return e;
     }
-    uint64_t row_segments = 0;
+    uint64_t row_segments = 0, lut_rows = 0;
+    uint32_t lut_min_tiles_x = 0xffffffffu;
     for (uint32_t z = 0; z < n_planes; ++z) {
         const fkb_plane_desc& s = planes[z];
         PlaneRec& r = L.recs[z];
@@ -254,17 +261,27 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         r.chain = s.chain;
         std::memcpy(r.params, s.params, sizeof(r.params));
         classify(chains[s.chain], r);
-        if (r.kclass != KCLASS_GATHER) row_segments += static_cast<uint64_t>(r.tiles_x) * r.dst_h;
+        if (r.kclass == KCLASS_POINT || r.kclass == KCLASS_RESIZE) row_segments += static_cast<uint64_t>(r.tiles_x) * r.dst_h;
+        if (r.kclass == KCLASS_LUT) { lut_rows += r.dst_h; lut_min_tiles_x = std::min(lut_min_tiles_x, r.tiles_x); }
     }
+    // LUT units: a block of rows of one plane per CTA visit; about one unit per resident CTA, at least eight row segments
+    const uint32_t lut_rpu = lut_rows ? std::max<uint32_t>(static_cast<uint32_t>((lut_rows + 3ull * sms - 1) / (3ull * sms)),
+                                                           (8u + lut_min_tiles_x - 1) / lut_min_tiles_x) : 1u;
+    uint32_t n_lut_units = 0;
     const uint32_t rpi = rows_per_item(row_segments, 2u * kStagedWarps * static_cast<uint32_t>(sms));
     for (uint32_t z = 0; z < n_planes; ++z) {
         PlaneRec& r = L.recs[z];
-        if (r.kclass != KCLASS_GATHER) {
+        r.lut_base = n_lut_units;
+        if (r.kclass == KCLASS_LUT) {
+            r.tile_h = std::min(r.dst_h, lut_rpu);
+            r.tiles_y = (r.dst_h + r.tile_h - 1) / r.tile_h;
+            n_lut_units += r.tiles_y;
+        } else if (r.kclass != KCLASS_GATHER) {
             r.tile_h = std::min(r.dst_h, rpi);
             r.tiles_y = (r.dst_h + r.tile_h - 1) / r.tile_h;
         }
         r.tile_base = n_tiles;
-        const uint32_t count = r.tiles_x * r.tiles_y;
+        const uint32_t count = (r.kclass == KCLASS_POINT || r.kclass == KCLASS_RESIZE) ? r.tiles_x * r.tiles_y : 0u;
         if (z == 0) first_count = count; else if (count != first_count) uniform = false;
         if (static_cast<uint64_t>(n_tiles) + count > 0xfffffff0ull) return FKB_ERR_TOO_LARGE;
         n_tiles += count;
@@ -272,11 +289,21 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
     }
     L.lp.n_planes = n_planes;
     L.lp.neg_zero = -0.0f;
-    for (uint32_t c = 0; c < n_chains; ++c) L.lp.post_kind[c] = post_kind_of(chains[c]);
+    for (uint32_t c = 0; c < n_chains; ++c) {
+        L.lp.post_kind[c] = post_kind_of(chains[c]);
+        uint32_t reorders = 0;
+        for (uint32_t i = 0; i < chains[c].n_ops; ++i) reorders += chains[c].ops[i].code == FKB_OP_REORDER_ZYX;
+        L.lp.lut_swap |= (reorders & 1u) << c;
+    }
     L.lp.n_tiles = n_tiles;
     L.lp.tiles_per_plane = (uniform && first_count) ? first_count : 0;
     if (n_tiles) {
         L.staged_grid = std::min<uint32_t>(n_tiles, 2u * static_cast<uint32_t>(sms));
+        ++L.kernels;
+    }
+    L.lp.n_lut_units = n_lut_units;
+    if (n_lut_units) {
+        L.lut_grid = std::min<uint32_t>(n_lut_units, 3u * static_cast<uint32_t>(sms));
         ++L.kernels;
     }
     if (n_gather) {
@@ -288,6 +315,7 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
 
 int run(const Lowered& L, const LaunchParams& lp, cudaStream_t stream) {
     if (L.staged_grid) FKB_CUDA(launch_staged(lp, L.staged_grid, stream));
+    if (L.lut_grid) FKB_CUDA(launch_lut(lp, L.lut_grid, stream));
     if (L.gather_grid.x) FKB_CUDA(launch_gather(lp, L.gather_grid, stream));
     return FKB_OK;
 }

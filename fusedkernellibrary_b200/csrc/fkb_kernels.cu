@@ -577,6 +577,130 @@ __global__ void __launch_bounds__(kStagedThreads, 2) staged_kernel(const __grid_
 }
 
 // ---------------------------------------------------------------------------------------------------------
+// lut_kernel: uchar3 -> uchar3 chains without resampling
+// ---------------------------------------------------------------------------------------------------------
+// Every op of such a chain acts on one channel at a time (a channel reorder only renames channels), so output channel c
+// is a function of one source byte: out[c] = T_c(in[perm(c)]).  Each CTA evaluates the chain — through the same op
+// interpreter as every other path, so the table is exact by construction — once for the 256 possible bytes, and then
+// every pixel costs three table reads instead of the whole chain (IEEE divisions and saturations included).  The
+// table holds kLutCopies copies of each entry spread over the banks so that the 32 lanes of a load rarely collide.
+// Rows move exactly like in staged_kernel: per-warp bulk loads into shared memory, bulk stores out.
+__device__ __forceinline__ uint32_t unit_to_plane(const LaunchParams& p, uint32_t u, uint32_t& local) {
+    const PlaneRec* table = plane_table(p);
+    uint32_t lo = 0, hi = p.n_planes;
+    while (hi - lo > 1) {
+        const uint32_t mid = (lo + hi) >> 1;
+        if (table[mid].lut_base <= u) lo = mid; else hi = mid;
+    }
+    local = u - table[lo].lut_base;
+    return lo;
+}
+
+template <bool SWAP>
+__device__ __forceinline__ void lut_segment(uint32_t in_s, uint32_t out_s, uint32_t ow, uint32_t lane) {
+    if (lane * 16u >= ow) return;
+    const uint4* src = reinterpret_cast<const uint4*>(smem_raw + in_s + lane * 48u);
+    uint32_t q[12];
+#pragma unroll
+    for (int i = 0; i < 3; ++i) { const uint4 t = src[i]; q[4 * i] = t.x; q[4 * i + 1] = t.y; q[4 * i + 2] = t.z; q[4 * i + 3] = t.w; }
+    const uint32_t lane_off = (lane & (kLutCopies - 1)) * 4u;
+    uint32_t o[12];
+#pragma unroll
+    for (int i = 0; i < 12; ++i) {
+        uint32_t e[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            const int b = 4 * i + t, c = b % 3;          // output byte b is channel c of pixel b / 3
+            const int sb = SWAP ? b - c + (2 - c) : b;   // the source byte it is a function of
+            const uint32_t idx = __byte_perm(q[sb >> 2], 0u, 0x4440u | (sb & 3));
+            e[t] = *reinterpret_cast<const uint32_t*>(smem_raw + idx * (kLutCopies * 4u) + (c * 256u * kLutCopies * 4u) + lane_off);
+        }
+        o[i] = __byte_perm(__byte_perm(e[0], e[1], 0x0040u), __byte_perm(e[2], e[3], 0x0040u), 0x5410u);
+    }
+    uint4* dst = reinterpret_cast<uint4*>(smem_raw + out_s + lane * 48u);
+#pragma unroll
+    for (int i = 0; i < 3; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+}
+
+__global__ void __launch_bounds__(kStagedThreads, 3) lut_kernel(const __grid_constant__ LaunchParams p) {
+    __shared__ PlaneRec s_pl;
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t slice = kLutBytes + warp * kLutSliceBytes;
+    uint64_t* bar = reinterpret_cast<uint64_t*>(smem_raw + slice);
+    const uint32_t in0 = slice + 32, out0 = slice + 32 + 2 * kLutSegBytes;
+    if (lane == 0) {
+        mbar_init(&bar[0], 1);
+        mbar_init(&bar[1], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    const PlaneRec* table = plane_table(p);
+    uint32_t cur_plane = 0xffffffffu, k = 0;
+    bool ok = true;
+    for (uint32_t unit = blockIdx.x; unit < p.n_lut_units; unit += gridDim.x) {
+        uint32_t local;
+        const uint32_t z = unit_to_plane(p, unit, local);
+        if (z != cur_plane) {  // block-uniform
+            if (lane == 0) bulk_wait_read_all();
+            __syncthreads();  // nobody reads the old table or plane record any more
+            if (threadIdx.x < sizeof(PlaneRec) / 16)
+                reinterpret_cast<uint4*>(&s_pl)[threadIdx.x] = reinterpret_cast<const uint4*>(table + z)[threadIdx.x];
+            __syncthreads();
+            const fkb_chain_desc& ch = p.chains[s_pl.chain];
+            for (uint32_t t = threadIdx.x; t < 256; t += blockDim.x) {
+                float v[1][3] = {{static_cast<float>(t), static_cast<float>(t), static_cast<float>(t)}};
+                apply_ops<1>(v, ch, s_pl, 0, ch.n_ops);
+#pragma unroll
+                for (int c = 0; c < 3; ++c) {
+                    const uint32_t e = u8_of_exact(v[0][c]);
+                    uint32_t* row = reinterpret_cast<uint32_t*>(smem_raw) + (c * 256u + t) * kLutCopies;
+#pragma unroll
+                    for (uint32_t r = 0; r < kLutCopies; ++r) row[r] = e;
+                }
+            }
+            __syncthreads();
+            cur_plane = z;
+        }
+        const PlaneRec& pl = s_pl;
+        const bool swap = (p.lut_swap >> pl.chain) & 1u;
+        const uint32_t row0 = local * pl.tile_h, nrows = min(pl.tile_h, pl.dst_h - row0);
+        const uint32_t nseg = nrows * pl.tiles_x;
+        const uint8_t* gsrc = pl.src + static_cast<size_t>(pl.crop_y + row0) * pl.src_pitch + static_cast<size_t>(pl.crop_x) * 3u;
+        uint8_t* gdst = pl.dst + static_cast<size_t>(row0) * pl.dst_pitch;
+        const uint32_t src_pitch = pl.src_pitch, dst_pitch = pl.dst_pitch, tiles_x = pl.tiles_x, tile_w = pl.tile_w, dst_w = pl.dst_w;
+        // segment g of the unit = (row g / tiles_x, column tile g % tiles_x); this warp takes g = warp, warp + 8, ...
+        auto issue = [&](uint32_t g, uint32_t s) {
+            if (lane == 0) {
+                const uint32_t r = g / tiles_x, tx = g - r * tiles_x;
+                const uint32_t ow = min(tile_w, dst_w - tx * tile_w);
+                const uint32_t bytes = (ow * 3u + 15u) & ~15u;
+                mbar_arrive_expect_tx(&bar[s], bytes);
+                bulk_load(smem_raw + in0 + s * kLutSegBytes, gsrc + static_cast<size_t>(r) * src_pitch + static_cast<size_t>(tx) * tile_w * 3u, bytes, &bar[s]);
+            }
+        };
+        if (warp < nseg) issue(warp, k & 1u);
+        for (uint32_t g = warp; g < nseg && ok; g += kStagedWarps, ++k) {
+            const uint32_t s = k & 1u;
+            if (lane == 0) bulk_wait_read_1();  // the store that read this output buffer two segments ago is done
+            if (g + kStagedWarps < nseg) issue(g + kStagedWarps, s ^ 1u);
+            const bool landed = mbar_wait_bounded(&bar[s], (k >> 1) & 1u);
+            if (__any_sync(0xffffffffu, !landed)) { ok = false; break; }
+            const uint32_t r = g / tiles_x, tx = g - r * tiles_x;
+            const uint32_t ow = min(tile_w, dst_w - tx * tile_w);
+            if (swap) lut_segment<true>(in0 + s * kLutSegBytes, out0 + s * kLutSegBytes, ow, lane);
+            else lut_segment<false>(in0 + s * kLutSegBytes, out0 + s * kLutSegBytes, ow, lane);
+            store_row(gdst + static_cast<size_t>(r) * dst_pitch + static_cast<size_t>(tx) * tile_w * 3u, out0 + s * kLutSegBytes, ow * 3u, lane);
+        }
+        if (__syncthreads_or(ok ? 0 : 1)) { ok = false; break; }
+    }
+    if (lane == 0) bulk_wait_all();
+    if (!ok) {
+        mbar_wait_bounded(&bar[(k + 1) & 1u], ((k + 1) >> 1) & 1u);
+        if (threadIdx.x == 0) atomicExch(p.status, FKB_ERR_DEVICE_WAIT);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
 // host-callable launchers (the only symbols the host translation unit needs from this file)
 // ---------------------------------------------------------------------------------------------------------
 cudaError_t launch_staged(const LaunchParams& p, uint32_t grid, cudaStream_t stream) {
@@ -590,6 +714,20 @@ cudaError_t launch_staged(const LaunchParams& p, uint32_t grid, cudaStream_t str
         configured_device = dev;
     }
     staged_kernel<<<grid, kStagedThreads, kStagedSmemBytes, stream>>>(p);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_lut(const LaunchParams& p, uint32_t grid, cudaStream_t stream) {
+    static thread_local int configured_device = -1;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (configured_device != dev) {
+        e = cudaFuncSetAttribute(lut_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kLutSmemBytes));
+        if (e != cudaSuccess) return e;
+        configured_device = dev;
+    }
+    lut_kernel<<<grid, kStagedThreads, kLutSmemBytes, stream>>>(p);
     return cudaGetLastError();
 }
 

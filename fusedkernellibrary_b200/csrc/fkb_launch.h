@@ -17,9 +17,18 @@ constexpr uint32_t kOutRowBytes = 3072;  // one output row segment (256 float3 p
 constexpr uint32_t kOutSlotBytes = kOutRowBytes + 16;  // the 16 spare bytes take the stores of columns that do not exist
 constexpr uint32_t kSliceBytes = kSliceHeader + 4 * kInRowBytes + 2 * kOutSlotBytes;
 constexpr uint32_t kStagedSmemBytes = kStagedWarps * kSliceBytes;
-constexpr uint32_t kMaxRowsPerItem = 32;  // upper bound of the output rows a warp processes per item
+constexpr uint32_t kMaxRowsPerItem = 32;
+// lut_kernel: a CTA-wide table (3 channels x 256 entries x kLutCopies bank-spread copies of one 32-bit word) followed by
+// one slice per warp (two mbarriers, two source and two output row segments of 512 uchar3 pixels).  72 KB per CTA: three
+// CTAs per SM.
+constexpr uint32_t kLutCopies = 8;
+constexpr uint32_t kLutBytes = 3 * 256 * kLutCopies * 4;
+constexpr uint32_t kLutSegBytes = 1536;
+constexpr uint32_t kLutSliceBytes = 32 + 4 * kLutSegBytes;
+constexpr uint32_t kLutSmemBytes = kLutBytes + kStagedWarps * kLutSliceBytes;  // upper bound of the output rows a warp processes per item
 
 cudaError_t launch_staged(const LaunchParams& p, uint32_t grid, cudaStream_t stream);
+cudaError_t launch_lut(const LaunchParams& p, uint32_t grid, cudaStream_t stream);
 cudaError_t launch_gather(const LaunchParams& p, dim3 grid, cudaStream_t stream);
 cudaError_t status_word_address(int** out);
 

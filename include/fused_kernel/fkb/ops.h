@@ -1,0 +1,288 @@
+// Front end, part 3: the operations ("IOps") a chain is built from, with the reference's builder spellings.
+//
+// Reference builders mirrored (paths relative to the reference's include/fused_kernel/):
+//   PerThreadRead<ND::_2D,T>::build(ptr | std::array<Ptr2D,N>) ... algorithms/basic_ops/memory_operations.h:27-67,
+//                                                                 core/execution_model/operation_model/batch_operations.h:523-543
+//   ReadYUV<PixelFormat::NV12>::build(image) ..................... algorithms/image_processing/color_conversion.h:206-294
+//   Crop<>::build(Rect | std::array<Rect,N>) ..................... algorithms/image_processing/crop.h:62-91
+//   Resize<INTER_LINEAR, AR>::build(Size[, background]) .......... algorithms/image_processing/resize.h:159-162, 262-264
+//   Cast / Mul / Add / Sub / Div / SaturateCast / ColorConversion / ConvertYUVToRGB ::build(...)
+//                                                                  core/execution_model/operation_model/parent_operations.h:55, 84-85
+//   PerThreadWrite / TensorWrite / TensorSplit ::build(ptr) ...... algorithms/basic_ops/memory_operations.h:85-212
+//   iop.then(next) ............................................... core/execution_model/operation_model/instantiable_operations.h:43-52
+//   BatchRead<PlanePolicy::PROCESS_ALL>::build(std::array<IOp,N>)  batch_operations.h:395-425
+// In the reference an IOp's type encodes the operation and its value holds the parameters; ill-typed chains fail to
+// compile.  Here the static types carry just enough (value type flowing through the chain, batch size) to keep those
+// compile-time rejections, and the parameters live in a small run-time record that is lowered to include/fkb/fkb.h.
+#pragma once
+#include <array>
+#include <vector>
+
+#include "fkb/fkb.h"
+#include "memory.h"
+
+namespace fk {
+
+enum class InterpolationType { INTER_LINEAR = 1 };
+enum class AspectRatio { PRESERVE_AR = 0, IGNORE_AR = 1 };
+enum class PlanePolicy { PROCESS_ALL = 0 };
+enum class ColorConversionCodes { COLOR_BGR2RGB, COLOR_RGB2BGR };
+
+namespace detail {
+struct SrcPlane { const void* data{nullptr}; uint pitch{0}, w{0}, h{0}; };
+struct OpRec {
+    uint16_t code{0};
+    std::vector<std::array<float, 3>> v;  // one operand per plane, or a single one shared by all planes
+};
+// Everything a chain knows before its Write: the run-time image of the reference's fused Read IOp.
+struct ReadState {
+    uint32_t src_format{FKB_PIX_U8C3};
+    std::vector<SrcPlane> src;   // 1 entry (shared) or one per plane
+    std::vector<Rect> crops;     // empty (whole frame), 1 entry, or one per plane
+    bool has_resize{false};
+    AspectRatio ar{AspectRatio::IGNORE_AR};
+    Size dst_size;
+    float bg[3]{0.f, 0.f, 0.f};
+    std::vector<OpRec> ops;
+    size_t n_pre_ops{0};         // ops that were chained before the Resize run on the taps
+    float ccm[9]{};
+    float yuv_sub[3]{};
+};
+inline std::array<float, 3> f3(const float3& v) { return {v.x, v.y, v.z}; }
+}  // namespace detail
+
+// ---- compute IOps -------------------------------------------------------------------------------------------------
+template <uint16_t CODE, typename I, typename O>
+struct ComputeIOp {
+    using InputType = I;
+    using OutputType = O;
+    static constexpr uint16_t code = CODE;
+    float3 params{0.f, 0.f, 0.f};
+    float ccm[9]{};
+    float yuv_sub[3]{};
+};
+template <typename T> constexpr bool isComputeIOp = false;
+template <uint16_t C, typename I, typename O> constexpr bool isComputeIOp<ComputeIOp<C, I, O>> = true;
+
+template <typename I, typename O>
+struct Cast {
+    static_assert(std::is_same_v<I, uchar3> && std::is_same_v<O, float3>, "the B200 kernels implement Cast<uchar3,float3>");
+    static constexpr auto build() { return ComputeIOp<FKB_OP_CAST_F32, I, O>{}; }
+};
+#define FKB_BINARY_OP(Name, CODE)                                                                                     \
+    template <typename I, typename P = I, typename O = I>                                                             \
+    struct Name {                                                                                                     \
+        static_assert(std::is_same_v<I, float3> && std::is_same_v<P, float3> && std::is_same_v<O, float3>,            \
+                      "the B200 kernels implement " #Name "<float3>");                                                \
+        static constexpr auto build(const float3& params) { return ComputeIOp<CODE, I, O>{params}; }                  \
+    };
+FKB_BINARY_OP(Mul, FKB_OP_MUL)
+FKB_BINARY_OP(Add, FKB_OP_ADD)
+FKB_BINARY_OP(Sub, FKB_OP_SUB)
+FKB_BINARY_OP(Div, FKB_OP_DIV)
+#undef FKB_BINARY_OP
+template <typename I, typename O>
+struct SaturateCast {
+    static_assert(std::is_same_v<I, float3> && std::is_same_v<O, uchar3>, "the B200 kernels implement SaturateCast<float3,uchar3>");
+    static constexpr auto build() { return ComputeIOp<FKB_OP_SATCAST_U8, I, O>{}; }
+};
+template <ColorConversionCodes CODE, typename I, typename O = I>
+struct ColorConversion {
+    static_assert(std::is_same_v<I, O> && (std::is_same_v<I, float3> || std::is_same_v<I, uchar3>),
+                  "BGR<->RGB on uchar3 or float3 is the colour conversion the B200 kernels implement");
+    static constexpr auto build() { return ComputeIOp<FKB_OP_REORDER_ZYX, I, O>{}; }
+};
+// YCbCr -> RGB matrices as the reference evaluates them in fp32 (algorithms/image_processing/itu_color.h:185-258).
+template <ColorDepth CD, ColorRange CR, ColorPrimitives CP>
+struct ConvertYUVToRGB {
+    static_assert(CD == ColorDepth::p8bit && CR == ColorRange::Full && CP == ColorPrimitives::bt709,
+                  "8-bit full-range bt709 is the YCbCr->RGB conversion the B200 kernels implement");
+    static constexpr auto build() {
+        ComputeIOp<FKB_OP_YUV2RGB, uchar3, float3> op{};
+        constexpr float m[9] = {1.f, 0.f, 1.57480001f, 1.f, -0.187324256f, -0.46812427f, 1.f, 1.8556f, 0.f};
+        for (int i = 0; i < 9; ++i) op.ccm[i] = m[i];
+        op.yuv_sub[0] = 0.f; op.yuv_sub[1] = 128.f; op.yuv_sub[2] = 128.f;  // Full range: luma is not offset
+        return op;
+    }
+};
+
+// ---- incomplete ReadBack IOps ----------------------------------------------------------------------------------
+template <size_t BATCH>
+struct CropIOp {
+    std::vector<Rect> rects;
+};
+template <typename BackIOp = void>
+struct Crop {
+    static auto build(const Rect& rect) { return CropIOp<0>{{rect}}; }
+    template <size_t N>
+    static auto build(const std::array<Rect, N>& rects) { return CropIOp<N>{std::vector<Rect>(rects.begin(), rects.end())}; }
+};
+struct ResizeIOp {
+    AspectRatio ar;
+    Size dst_size;
+    float3 bg;
+};
+template <InterpolationType IT = InterpolationType::INTER_LINEAR, AspectRatio AR = AspectRatio::IGNORE_AR, typename DefaultType = void>
+struct Resize {
+    static_assert(IT == InterpolationType::INTER_LINEAR, "INTER_LINEAR is the interpolation the B200 kernels implement");
+    static auto build(const Size& dstSize) {
+        static_assert(AR == AspectRatio::IGNORE_AR, "PRESERVE_AR needs a background value: build(Size, float3)");
+        return ResizeIOp{AR, dstSize, float3{0.f, 0.f, 0.f}};
+    }
+    static auto build(const Size& dstSize, const float3& backgroundValue) { return ResizeIOp{AR, dstSize, backgroundValue}; }
+};
+
+// ---- Read IOps -------------------------------------------------------------------------------------------------
+// OutT: the value type the chain currently produces; BATCH: 0 = not batched, else the number of planes.
+template <typename OutT, size_t BATCH>
+struct ReadIOp {
+    using OutputType = OutT;
+    static constexpr size_t batch = BATCH;
+    detail::ReadState st;
+    struct Params { ActiveThreads activeThreads; } params;  // .activeThreads.z may be narrowed (divergent launches)
+
+    ReadIOp() = default;
+    explicit ReadIOp(detail::ReadState s) : st(std::move(s)) { refresh(); }
+
+    void refresh() {
+        const Size g = geometry();
+        params.activeThreads = {static_cast<uint>(g.width), static_cast<uint>(g.height), static_cast<uint>(BATCH ? BATCH : 1)};
+    }
+    Size geometry() const {
+        if (st.has_resize) return st.dst_size;
+        if (!st.crops.empty()) { int w = 0, h = 0; for (const Rect& r : st.crops) { w = std::max(w, r.width); h = std::max(h, r.height); } return Size(w, h); }
+        if (!st.src.empty()) return Size(static_cast<int>(st.src[0].w), static_cast<int>(st.src[0].h));
+        return Size(0, 0);
+    }
+    ActiveThreads getActiveThreads() const { return params.activeThreads; }
+
+    template <size_t N>
+    auto then(const CropIOp<N>& c) const {
+        static_assert(BATCH == 0 || N == 0 || BATCH == N, "Fusing two batch operations of different BATCH size is not allowed.");
+        if (st.has_resize) throw std::runtime_error("Crop after Resize is not a chain the B200 kernels implement");
+        detail::ReadState s = st;
+        if (s.crops.empty()) s.crops = c.rects;
+        else {  // a crop of a crop: offsets add up
+            std::vector<Rect> out(std::max(s.crops.size(), c.rects.size()));
+            for (size_t i = 0; i < out.size(); ++i) {
+                const Rect& a = s.crops[s.crops.size() == 1 ? 0 : i];
+                const Rect& b = c.rects[c.rects.size() == 1 ? 0 : i];
+                out[i] = Rect(a.x + b.x, a.y + b.y, b.width, b.height);
+            }
+            s.crops = out;
+        }
+        return ReadIOp<OutT, (BATCH ? BATCH : N)>(std::move(s));
+    }
+    auto then(const ResizeIOp& r) const {
+        if (st.has_resize) throw std::runtime_error("two Resize operations in one chain are not implemented by the B200 kernels");
+        detail::ReadState s = st;
+        s.has_resize = true; s.ar = r.ar; s.dst_size = r.dst_size;
+        s.bg[0] = r.bg.x; s.bg[1] = r.bg.y; s.bg[2] = r.bg.z;
+        s.n_pre_ops = s.ops.size();
+        return ReadIOp<float3, BATCH>(std::move(s));  // the interpolation returns float_<cn>
+    }
+    template <uint16_t C, typename I, typename O>
+    auto then(const ComputeIOp<C, I, O>& op) const {
+        static_assert(std::is_same_v<I, OutT>, "the operation's InputType is not the OutputType of the operation before it");
+        detail::ReadState s = st;
+        s.ops.push_back(detail::OpRec{C, {detail::f3(op.params)}});
+        if (C == FKB_OP_YUV2RGB) { for (int i = 0; i < 9; ++i) s.ccm[i] = op.ccm[i]; for (int i = 0; i < 3; ++i) s.yuv_sub[i] = op.yuv_sub[i]; }
+        return ReadIOp<O, BATCH>(std::move(s));
+    }
+};
+template <typename T> constexpr bool isReadIOp = false;
+template <typename O, size_t B> constexpr bool isReadIOp<ReadIOp<O, B>> = true;
+
+template <ND D, typename T>
+struct PerThreadRead {
+    static_assert(D == ND::_2D && std::is_same_v<T, uchar3>, "PerThreadRead<ND::_2D, uchar3> is the read the B200 kernels implement");
+    static auto build(const RawPtr<ND::_2D, T>& p) {
+        detail::ReadState s;
+        s.src.push_back({p.data, p.dims.pitch, p.dims.width, p.dims.height});
+        return ReadIOp<T, 0>(std::move(s));
+    }
+    static auto build(const Ptr<ND::_2D, T>& p) { return build(p.ptr()); }
+    template <size_t N>
+    static auto build(const std::array<Ptr2D<T>, N>& ptrs) {
+        detail::ReadState s;
+        for (const auto& p : ptrs) { const auto r = p.ptr(); s.src.push_back({r.data, r.dims.pitch, r.dims.width, r.dims.height}); }
+        return ReadIOp<T, N>(std::move(s));
+    }
+};
+template <PixelFormat PF>
+struct ReadYUV {
+    static auto build(const Image<PF>& img) { return build(img.ptr()); }
+    static auto build(const RawImage<PF>& raw) {
+        detail::ReadState s;
+        s.src_format = FKB_PIX_NV12;
+        s.src.push_back({raw.data.data, raw.data.dims.pitch, raw.width, raw.height});
+        return ReadIOp<uchar3, 0>(std::move(s));
+    }
+};
+// A batch whose planes are complete read chains of the same shape but different parameters (their own source,
+// their own operands): the operands that differ travel per plane.
+template <PlanePolicy PP = PlanePolicy::PROCESS_ALL>
+struct BatchRead {
+    template <typename O, size_t N>
+    static auto build(const std::array<ReadIOp<O, 0>, N>& iops) {
+        detail::ReadState s = iops[0].st;
+        for (auto& op : s.ops) op.v.resize(N);
+        if (!s.crops.empty()) s.crops.resize(N);
+        s.src.resize(N);
+        for (size_t i = 0; i < N; ++i) {
+            const detail::ReadState& e = iops[i].st;
+            if (e.ops.size() != s.ops.size() || e.src_format != s.src_format || e.has_resize != s.has_resize ||
+                e.n_pre_ops != s.n_pre_ops || e.crops.empty() != iops[0].st.crops.empty() ||
+                (e.has_resize && (e.dst_size.width != s.dst_size.width || e.dst_size.height != s.dst_size.height || e.ar != s.ar)))
+                throw std::runtime_error("BatchRead: the planes are not chains of the same operations");
+            s.src[i] = e.src[0];
+            if (!e.crops.empty()) s.crops[i] = e.crops[0];
+            for (size_t k = 0; k < s.ops.size(); ++k) {
+                if (e.ops[k].code != s.ops[k].code) throw std::runtime_error("BatchRead: the planes are not chains of the same operations");
+                s.ops[k].v[i] = e.ops[k].v[0];
+            }
+        }
+        return ReadIOp<O, N>(std::move(s));
+    }
+};
+
+// ---- Write IOps ------------------------------------------------------------------------------------------------
+template <typename T>
+struct WriteIOp {
+    using InputType = T;
+    uint32_t write_kind{FKB_WRITE_PACKED};
+    void* data{nullptr};
+    uint width{0}, height{0}, pitch{0}, planes{1};
+    size_t plane_stride{0};    // bytes between consecutive planes (tensors)
+    size_t channel_stride{0};  // TensorSplit: bytes between channel planes
+};
+template <typename T> constexpr bool isWriteIOp = false;
+template <typename T> constexpr bool isWriteIOp<WriteIOp<T>> = true;
+
+template <ND D, typename T>
+struct PerThreadWrite {
+    static_assert(D == ND::_2D, "PerThreadWrite<ND::_2D, T> is the 2-D write the B200 kernels implement");
+    static auto build(const RawPtr<ND::_2D, T>& p) { return WriteIOp<T>{FKB_WRITE_PACKED, p.data, p.dims.width, p.dims.height, p.dims.pitch, 1, 0, 0}; }
+    static auto build(const Ptr<ND::_2D, T>& p) { return build(p.ptr()); }
+};
+template <typename T>
+struct TensorWrite {
+    static auto build(const RawPtr<ND::_3D, T>& p) {
+        return WriteIOp<T>{FKB_WRITE_PACKED, p.data, p.dims.width, p.dims.height, p.dims.pitch, p.dims.planes,
+                           static_cast<size_t>(p.dims.plane_pitch) * p.dims.color_planes, 0};
+    }
+    static auto build(const Ptr<ND::_3D, T>& p) { return build(p.ptr()); }
+};
+template <typename T>
+struct TensorSplit {
+    static_assert(std::is_same_v<T, float3>, "TensorSplit<float3> is the planar write the B200 kernels implement");
+    static auto build(const RawPtr<ND::_3D, float>& p) {
+        // memory_operations.h:189-205: channel c of pixel (x,y) lies width*height elements after channel c-1
+        return WriteIOp<T>{FKB_WRITE_SPLIT, p.data, p.dims.width, p.dims.height, p.dims.pitch, p.dims.planes,
+                           static_cast<size_t>(p.dims.plane_pitch) * p.dims.color_planes,
+                           static_cast<size_t>(p.dims.width) * p.dims.height * sizeof(float)};
+    }
+    static auto build(const Ptr<ND::_3D, float>& p) { return build(p.ptr()); }
+};
+
+}  // namespace fk

@@ -1,0 +1,247 @@
+// GPU test of the fk:: front end: the benchmark pipelines written exactly as a FusedKernelLibrary user writes them
+// (compare the reference's tests/examples/readme_test_code.h:26-106, utests/core/execution_model/utest_executors.h:91-134,
+// tests/data_parallel_patterns/test_divergent_batch.h:28-92), executed through the front end -> C ABI -> sm_100a
+// kernels, and compared bit for bit with the CPU oracle run on the same host data (descriptors built by hand here, so
+// the front end's lowering is checked too).  Prints one line per case; exit code 0 = all passed.
+#include <fused_kernel/algorithms/basic_ops/arithmetic.h>
+#include <fused_kernel/algorithms/basic_ops/cast.h>
+#include <fused_kernel/algorithms/basic_ops/memory_operations.h>
+#include <fused_kernel/algorithms/image_processing/color_conversion.h>
+#include <fused_kernel/algorithms/image_processing/crop.h>
+#include <fused_kernel/algorithms/image_processing/image.h>
+#include <fused_kernel/algorithms/image_processing/resize.h>
+#include <fused_kernel/algorithms/image_processing/saturate.h>
+#include <fused_kernel/fused_kernel.h>
+
+#include <cstdio>
+#include <cstring>
+#include <random>
+#include <vector>
+
+using namespace fk;
+
+extern "C" int fkb_oracle_resize_params(uint32_t geometry, fkb_plane_desc* pl);
+extern "C" int fkb_oracle_run(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc* planes, uint32_t n_planes, uint32_t n_threads);
+
+static int g_failed = 0;
+static void report(const char* name, bool ok) {
+    std::printf("%-38s %s\n", name, ok ? "PASS" : "FAIL");
+    if (!ok) ++g_failed;
+}
+template <typename P>
+static void fill_random(P& p, uint32_t seed, int lo = 0, int hi = 255) {
+    std::mt19937 rng(seed);
+    uint8_t* b = reinterpret_cast<uint8_t*>(p.ptrPinned().data);
+    for (size_t i = 0; i < p.sizeInBytes(); ++i) b[i] = static_cast<uint8_t>(lo + rng() % (hi - lo + 1));
+}
+static fkb_op op(uint16_t code, float a = 0, float b = 0, float c = 0, int slot = -1) {
+    fkb_op o{}; o.code = code; o.plane_slot = static_cast<int16_t>(slot); o.v[0] = a; o.v[1] = b; o.v[2] = c; return o;
+}
+static fkb_plane_desc host_plane(const Ptr2D<uchar3>& src, Rect crop, uint32_t dw, uint32_t dh, void* dst, uint32_t dpitch, uint32_t geometry) {
+    fkb_plane_desc d{};
+    const auto r = src.ptrPinned();
+    d.src = r.data; d.src_pitch = r.dims.pitch; d.src_w = r.dims.width; d.src_h = r.dims.height;
+    d.crop_x = crop.x; d.crop_y = crop.y; d.crop_w = crop.width; d.crop_h = crop.height;
+    d.dst = dst; d.dst_w = dw; d.dst_h = dh; d.dst_pitch = dpitch;
+    if (geometry != FKB_GEOM_NONE) fkb_oracle_resize_params(geometry, &d);
+    return d;
+}
+
+// ---- README pipeline: 5 crops of a 1080p frame -> 128x64 uchar3 tensor ------------------------------------------
+static void test_readme() {
+    Stream stream;
+    constexpr int BATCH = 5;
+    Ptr2D<uchar3> inputImage(1920, 1080);  // cudaMallocPitch: the pitch may be padded
+    fill_random(inputImage, 1);
+    inputImage.upload(stream);
+    constexpr std::array<Rect, BATCH> crops{Rect(300, 125, 60, 40), Rect(400, 125, 60, 40), Rect(530, 270, 130, 140), Rect(560, 115, 100, 35), Rect(572, 196, 40, 15)};
+    constexpr Size outputSize(128, 64);
+    Tensor<uchar3> output(outputSize.width, outputSize.height, BATCH);
+    executeOperations<TransformDPP<>>(stream, PerThreadRead<ND::_2D, uchar3>::build(inputImage), Crop<>::build(crops),
+        Resize<InterpolationType::INTER_LINEAR, AspectRatio::PRESERVE_AR>::build(outputSize, make_<float3>(0.f, 0.f, 0.f)),
+        Mul<float3>::build(make_<float3>(2.f, 2.f, 2.f)), Sub<float3>::build(make_set<float3>(128.f)),
+        SaturateCast<float3, uchar3>::build(), TensorWrite<uchar3>::build(output));
+    output.download(stream);
+    // the same chain in .then() form must give the same result (utest_executors.h:91-134)
+    Tensor<uchar3> output2(outputSize.width, outputSize.height, BATCH);
+    const auto sender = PerThreadRead<ND::_2D, uchar3>::build(inputImage).then(Crop<>::build(crops))
+        .then(Resize<InterpolationType::INTER_LINEAR, AspectRatio::PRESERVE_AR>::build(outputSize, make_<float3>(0.f, 0.f, 0.f)))
+        .then(Mul<float3>::build(make_<float3>(2.f, 2.f, 2.f))).then(Sub<float3>::build(make_set<float3>(128.f)))
+        .then(SaturateCast<float3, uchar3>::build());
+    executeOperations<TransformDPP<>>(stream, sender, TensorWrite<uchar3>::build(output2));
+    output2.download(stream);
+    stream.sync();
+
+    fkb_chain_desc ch{};
+    ch.src_format = FKB_PIX_U8C3; ch.geometry = FKB_GEOM_RESIZE_PRESERVE_AR; ch.dst_format = FKB_PIX_U8C3; ch.write_kind = FKB_WRITE_PACKED;
+    ch.n_ops = 3; ch.ops[0] = op(FKB_OP_MUL, 2, 2, 2); ch.ops[1] = op(FKB_OP_SUB, 128, 128, 128); ch.ops[2] = op(FKB_OP_SATCAST_U8);
+    std::vector<uint8_t> want(128 * 64 * 3 * BATCH);
+    std::vector<fkb_plane_desc> planes;
+    for (int i = 0; i < BATCH; ++i) planes.push_back(host_plane(inputImage, crops[i], 128, 64, want.data() + i * 128 * 64 * 3, 128 * 3, ch.geometry));
+    fkb_oracle_run(&ch, 1, planes.data(), BATCH, 1);
+    report("readme crop pipeline (variadic)", std::memcmp(want.data(), output.ptrPinned().data, want.size()) == 0);
+    report("readme crop pipeline (.then form)", std::memcmp(want.data(), output2.ptrPinned().data, want.size()) == 0);
+    report("activeThreads of the fused read", sender.getActiveThreads().x == 128 && sender.getActiveThreads().y == 64 && sender.getActiveThreads().z == 5);
+}
+
+// ---- vertical fusion: Cast, Mul, Add, Div, BGR2RGB, SaturateCast on every pixel ----------------------------------
+static void test_vertical_fusion() {
+    Stream stream;
+    const uint W = 1000, H = 75;
+    Ptr2D<uchar3> in(W, H), out(W, H);
+    fill_random(in, 2);
+    in.upload(stream);
+    executeOperations<TransformDPP<>>(stream, PerThreadRead<ND::_2D, uchar3>::build(in), Cast<uchar3, float3>::build(),
+        Mul<float3>::build(make_<float3>(0.5f, 1.5f, 2.0f)), Add<float3>::build(make_<float3>(10.f, -20.f, 5.f)),
+        Div<float3>::build(make_set<float3>(1.7f)), ColorConversion<ColorConversionCodes::COLOR_BGR2RGB, float3, float3>::build(),
+        SaturateCast<float3, uchar3>::build(), PerThreadWrite<ND::_2D, uchar3>::build(out));
+    out.download(stream);
+    stream.sync();
+    fkb_chain_desc ch{};
+    ch.src_format = FKB_PIX_U8C3; ch.geometry = FKB_GEOM_NONE; ch.dst_format = FKB_PIX_U8C3; ch.write_kind = FKB_WRITE_PACKED;
+    ch.n_ops = 6; ch.ops[0] = op(FKB_OP_CAST_F32); ch.ops[1] = op(FKB_OP_MUL, 0.5f, 1.5f, 2.0f); ch.ops[2] = op(FKB_OP_ADD, 10.f, -20.f, 5.f);
+    ch.ops[3] = op(FKB_OP_DIV, 1.7f, 1.7f, 1.7f); ch.ops[4] = op(FKB_OP_REORDER_ZYX); ch.ops[5] = op(FKB_OP_SATCAST_U8);
+    const uint pitch = out.dims().pitch;
+    std::vector<uint8_t> want(static_cast<size_t>(pitch) * H, 0);
+    fkb_plane_desc d = host_plane(in, Rect(0, 0, W, H), W, H, want.data(), pitch, FKB_GEOM_NONE);
+    fkb_oracle_run(&ch, 1, &d, 1, 1);
+    bool ok = true;
+    for (uint y = 0; y < H && ok; ++y) ok = std::memcmp(want.data() + static_cast<size_t>(y) * pitch, reinterpret_cast<uint8_t*>(out.ptrPinned().data) + static_cast<size_t>(y) * pitch, W * 3) == 0;
+    report("vertical fusion uchar3 -> uchar3", ok);
+}
+
+// ---- NV12 -> RGB -> resize -> normalise -> planar CHW ---------------------------------------------------------------
+static void test_nv12() {
+    Stream stream;
+    const uint W = 640, H = 360, DW = 160, DH = 96;
+    Image<PixelFormat::NV12> img(W, H);
+    auto data = img.getData();
+    fill_random(data, 3, 16, 235);
+    img.upload(stream);
+    Tensor<float> out(DW, DH, 1, 3);
+    executeOperations<TransformDPP<>>(stream, ReadYUV<PixelFormat::NV12>::build(img),
+        ConvertYUVToRGB<ColorDepth::p8bit, ColorRange::Full, ColorPrimitives::bt709>::build(),
+        Resize<InterpolationType::INTER_LINEAR, AspectRatio::IGNORE_AR>::build(Size(DW, DH)),
+        Sub<float3>::build(make_<float3>(123.675f, 116.28f, 103.53f)), Div<float3>::build(make_<float3>(58.395f, 57.12f, 57.375f)),
+        TensorSplit<float3>::build(out));
+    out.download(stream);
+    stream.sync();
+    fkb_chain_desc ch{};
+    ch.src_format = FKB_PIX_NV12; ch.geometry = FKB_GEOM_RESIZE_IGNORE_AR; ch.dst_format = FKB_PIX_F32C3; ch.write_kind = FKB_WRITE_SPLIT;
+    ch.n_ops = 3; ch.n_pre_ops = 1; ch.ops[0] = op(FKB_OP_YUV2RGB); ch.ops[1] = op(FKB_OP_SUB, 123.675f, 116.28f, 103.53f); ch.ops[2] = op(FKB_OP_DIV, 58.395f, 57.12f, 57.375f);
+    const float m[9] = {1.f, 0.f, 1.57480001f, 1.f, -0.187324256f, -0.46812427f, 1.f, 1.8556f, 0.f};
+    std::memcpy(ch.ccm, m, sizeof(m)); ch.yuv_sub[1] = 128.f; ch.yuv_sub[2] = 128.f;
+    std::vector<float> want(DW * DH * 3);
+    fkb_plane_desc d{};
+    const auto r = data.ptrPinned();
+    d.src = r.data; d.src_chroma = reinterpret_cast<uint8_t*>(r.data) + static_cast<size_t>(r.dims.pitch) * H; d.src_pitch = r.dims.pitch; d.src_w = W; d.src_h = H;
+    d.crop_w = W; d.crop_h = H; d.dst = want.data(); d.dst_w = DW; d.dst_h = DH; d.dst_pitch = DW * 4; d.dst_channel_stride = DW * DH * 4;
+    fkb_oracle_resize_params(ch.geometry, &d);
+    fkb_oracle_run(&ch, 1, &d, 1, 1);
+    report("NV12 -> planar float CHW", std::memcmp(want.data(), out.ptrPinned().data, want.size() * 4) == 0);
+}
+
+// ---- batched crop-resize-normalise over several frames --------------------------------------------------------------
+static void test_batched() {
+    Stream stream;
+    constexpr size_t FRAMES = 3, PER = 4, BATCH = FRAMES * PER;
+    std::vector<Ptr2D<uchar3>> frames;
+    for (size_t f = 0; f < FRAMES; ++f) { frames.emplace_back(640, 360); fill_random(frames[f], 100 + f); frames[f].upload(stream); }
+    std::array<Ptr2D<uchar3>, BATCH> ptrs;
+    std::array<Rect, BATCH> rects;
+    std::mt19937 rng(42);
+    for (size_t i = 0; i < BATCH; ++i) {
+        ptrs[i] = frames[i / PER];
+        int x = rng() % 640, y = rng() % 360, w = 8 + rng() % 300, h = 8 + rng() % 300;
+        if (x + w > 640) w = 640 - x;
+        if (y + h > 360) h = 360 - y;
+        rects[i] = Rect(x, y, w, h);
+    }
+    Tensor<float3> out(96, 80, BATCH);
+    executeOperations<TransformDPP<>>(stream, PerThreadRead<ND::_2D, uchar3>::build(ptrs), Crop<>::build(rects),
+        Resize<InterpolationType::INTER_LINEAR, AspectRatio::PRESERVE_AR>::build(Size(96, 80), make_<float3>(114.f, 114.f, 114.f)),
+        Mul<float3>::build(make_set<float3>(1.f / 255.f)), TensorWrite<float3>::build(out));
+    out.download(stream);
+    stream.sync();
+    fkb_chain_desc ch{};
+    ch.src_format = FKB_PIX_U8C3; ch.geometry = FKB_GEOM_RESIZE_PRESERVE_AR; ch.dst_format = FKB_PIX_F32C3; ch.write_kind = FKB_WRITE_PACKED;
+    ch.n_ops = 1; ch.ops[0] = op(FKB_OP_MUL, 1.f / 255.f, 1.f / 255.f, 1.f / 255.f);
+    std::vector<float> want(96 * 80 * 3 * BATCH);
+    std::vector<fkb_plane_desc> planes;
+    for (size_t i = 0; i < BATCH; ++i) {
+        fkb_plane_desc d = host_plane(ptrs[i], rects[i], 96, 80, want.data() + i * 96 * 80 * 3, 96 * 12, ch.geometry);
+        d.bg[0] = d.bg[1] = d.bg[2] = 114.f;
+        planes.push_back(d);
+    }
+    fkb_oracle_run(&ch, 1, planes.data(), BATCH, 1);
+    report("batched crop-resize-normalise", std::memcmp(want.data(), out.ptrPinned().data, want.size() * 4) == 0);
+}
+
+// ---- divergent horizontal fusion: two sequences in one launch, global plane indices ------------------------------------
+struct Sel { static uint at(const uint& z) { return z < 2 ? 0u : 1u; } };
+static void test_divergent() {
+    Stream stream;
+    const uint W = 320, H = 180;
+    std::array<Ptr2D<uchar3>, 4> frames;
+    for (int f = 0; f < 4; ++f) { frames[f] = Ptr2D<uchar3>(W, H); fill_random(frames[f], 7 + f); frames[f].upload(stream); }
+    std::array<Ptr2D<uchar3>, 2> first2{frames[0], frames[1]};
+    Tensor<uchar3> outA(W / 2, H / 2, 2);
+    const auto seq0 = buildOperationSequence(PerThreadRead<ND::_2D, uchar3>::build(first2),
+        Resize<InterpolationType::INTER_LINEAR>::build(Size(W / 2, H / 2)), SaturateCast<float3, uchar3>::build(), TensorWrite<uchar3>::build(outA));
+    using FusedRead = decltype(PerThreadRead<ND::_2D, uchar3>::build(frames[0]).then(Cast<uchar3, float3>::build())
+        .then(Mul<float3>::build(make_set<float3>(1.f))).then(Sub<float3>::build(make_set<float3>(0.f))));
+    std::array<FusedRead, 4> reads;
+    const float scales[4] = {0.f, 0.f, 0.75f, 1.9f}, offs[4] = {0.f, 0.f, 13.5f, 60.f};
+    for (int i = 0; i < 4; ++i)
+        reads[i] = PerThreadRead<ND::_2D, uchar3>::build(frames[i < 2 ? 2 : i]).then(Cast<uchar3, float3>::build())
+            .then(Mul<float3>::build(make_set<float3>(scales[i]))).then(Sub<float3>::build(make_set<float3>(offs[i])));
+    auto batchRead = BatchRead<PlanePolicy::PROCESS_ALL>::build(reads);
+    batchRead.params.activeThreads.z = 2;  // this sequence owns planes 2 and 3; indices stay global
+    Tensor<float3> outB(W, H, 4);
+    std::memset(outB.ptrPinned().data, 0, outB.sizeInBytes());
+    outB.upload(stream);
+    const auto seq1 = buildOperationSequence(batchRead, TensorWrite<float3>::build(outB));
+    Executor<DivergentBatchTransformDPP<ParArch::GPU_NVIDIA, Sel>>::executeOperations(stream, seq0, seq1);
+    outA.download(stream); outB.download(stream);
+    stream.sync();
+    bool ok = true;
+    for (uint z = 0; z < 2; ++z)  // scale exactly 2: the even-pixel subsample
+        for (uint y = 0; y < H / 2; ++y) for (uint x = 0; x < W / 2; ++x) {
+            const uchar3 a = outA.at(x, y, z), b = frames[z].at(2 * x, 2 * y);
+            ok = ok && a.x == b.x && a.y == b.y && a.z == b.z;
+        }
+    for (uint z = 2; z < 4; ++z)
+        for (uint y = 0; y < H; ++y) for (uint x = 0; x < W; ++x) {
+            const float3 a = outB.at(x, y, z); const uchar3 b = frames[z].at(x, y);
+            ok = ok && a.x == b.x * scales[z] - offs[z] && a.y == b.y * scales[z] - offs[z] && a.z == b.z * scales[z] - offs[z];
+        }
+    const float3 untouched = outB.at(5, 5, 0);
+    report("divergent batch (two sequences)", ok && untouched.x == 0.f);
+}
+
+// ---- error behaviour: a bad launch throws std::runtime_error, like the reference's gpuErrchk -------------------------
+static void test_errors() {
+    Stream stream;
+    Ptr2D<uchar3> in(64, 48);
+    Tensor<uchar3> out(32, 32, 1);
+    bool threw = false;
+    try {
+        executeOperations<TransformDPP<>>(stream, PerThreadRead<ND::_2D, uchar3>::build(in), Crop<>::build(Rect(60, 40, 32, 32)),
+            Resize<InterpolationType::INTER_LINEAR>::build(Size(32, 32)), SaturateCast<float3, uchar3>::build(), TensorWrite<uchar3>::build(out));
+    } catch (const std::runtime_error&) { threw = true; }
+    report("rectangle outside the frame throws", threw);
+    threw = false;
+    try { Ptr2D<uchar3> bad(0, 10); } catch (const std::runtime_error&) { threw = true; }
+    report("zero-sized Ptr2D throws", threw);
+}
+
+int main() {
+    test_readme();
+    test_vertical_fusion();
+    test_nv12();
+    test_batched();
+    test_divergent();
+    test_errors();
+    std::printf("%s\n", g_failed ? "FAILED" : "ALL PASSED");
+    return g_failed ? 1 : 0;
+}

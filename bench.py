@@ -34,10 +34,30 @@ FALLBACK_HBM_GBS = 6650.0
 NCU_TRAFFIC_BYTES_PER_LAUNCH = None
 
 
-def make_workload(rank: int, n_frames: int = N_FRAMES):
+def make_workload(rank: int, n_frames: int = N_FRAMES, frame_w: int = 1920, frame_h: int = 1080):
     from fusedkernellibrary_b200 import workloads as W
-    return W.batched_crop_resize(n_frames=n_frames, crops_per_frame=CROPS_PER_FRAME, seed=4 + rank,
+    return W.batched_crop_resize(n_frames=n_frames, crops_per_frame=CROPS_PER_FRAME, w=frame_w, h=frame_h, seed=4 + rank,
                                  frame_seed_base=1000 + 64 * rank)
+
+
+def shard_workload(rank: int, world: int, scaling: str, n_frames: int = N_FRAMES, frame_w: int = 1920, frame_h: int = 1080):
+    """The part of the job rank `rank` of `world` processes.  Returns (workload, frames of this rank).
+    weak: every rank runs the whole n_frames workload on its own seeded frames (per-GPU work fixed).
+    strong: one n_frames job, rank r keeps frames [r*n/world, (r+1)*n/world) and their planes (total work fixed).
+    Either way a rank reads only its own frames and writes only its own output: there is no exchange."""
+    from fusedkernellibrary_b200 import workloads as W
+    if scaling == "weak":
+        return make_workload(rank, n_frames, frame_w, frame_h), n_frames
+    frames = max(1, n_frames // world)
+    wl = make_workload(0, n_frames, frame_w, frame_h)
+    lo = rank * frames * CROPS_PER_FRAME
+    keep = wl.planes[lo: lo + frames * CROPS_PER_FRAME]
+    base_src = keep[0].src
+    plane_bytes = keep[0].dst_w * keep[0].dst_h * 12
+    planes = [W.PlaneSpec(**{**p.__dict__, "src": p.src - base_src, "dst_offset": i * plane_bytes}) for i, p in enumerate(keep)]
+    shard = W.Workload(wl.name, wl.chains, wl.sources[base_src: base_src + frames], [len(planes) * plane_bytes], planes,
+                       extra={"n_frames": frames, "crops_per_frame": CROPS_PER_FRAME})
+    return shard, frames
 
 
 def workload_config(n_gpus: int, scaling: str, frames_per_gpu: int) -> dict:
@@ -231,16 +251,7 @@ def our_arm(args) -> None:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     from fusedkernellibrary_b200 import abi, runtime
-    frames = N_FRAMES if args.scaling == "weak" else max(1, N_FRAMES // world)
-    wl = make_workload(rank if args.scaling == "weak" else 0, n_frames=N_FRAMES)
-    if args.scaling == "strong":  # total work fixed: rank r keeps frames [r*frames, (r+1)*frames)
-        from fusedkernellibrary_b200 import workloads as W
-        lo = rank * frames * CROPS_PER_FRAME
-        keep = wl.planes[lo: lo + frames * CROPS_PER_FRAME]
-        base_src = keep[0].src
-        planes = [W.PlaneSpec(**{**p.__dict__, "src": p.src - base_src, "dst_offset": i * 224 * 224 * 12}) for i, p in enumerate(keep)]
-        wl = W.Workload(wl.name, wl.chains, wl.sources[base_src: base_src + frames], [len(planes) * 224 * 224 * 12], planes,
-                        extra={"n_frames": frames, "crops_per_frame": CROPS_PER_FRAME})
+    wl, frames = shard_workload(rank, world, args.scaling)
     alg = wl.algorithmic_bytes()
     peak, peak_src = measured_peak()
 

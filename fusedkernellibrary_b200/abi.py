@@ -12,6 +12,7 @@ import os
 MAX_OPS = 12
 MAX_PLANE_PARAMS = 4
 MAX_CHAINS = 8
+NOALLOC_MAX_PLANES = 4096
 
 OK, ERR_NULL, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_TOO_LARGE, ERR_DEVICE_WAIT = 0, -1, -2, -3, -4, -5, -6
 
@@ -56,6 +57,7 @@ SIGNATURES = {
     "fkb_resize_params": (C.c_int, [C.c_uint32, C.POINTER(PlaneDesc)]),
     "fkb_validate": (C.c_int, [C.POINTER(ChainDesc), C.c_uint32, C.POINTER(PlaneDesc), C.c_uint32]),
     "fkb_launch_transform": (C.c_int, [C.POINTER(ChainDesc), C.POINTER(PlaneDesc), C.c_uint32, C.c_void_p]),
+    "fkb_launch_transform_noalloc": (C.c_int, [C.POINTER(ChainDesc), C.POINTER(PlaneDesc), C.c_uint32, C.c_void_p]),
     "fkb_launch_divergent": (C.c_int, [C.POINTER(ChainDesc), C.c_uint32, C.POINTER(PlaneDesc), C.c_uint32, C.c_void_p]),
     "fkb_plan_create": (C.c_int, [C.POINTER(ChainDesc), C.c_uint32, C.POINTER(PlaneDesc), C.c_uint32, C.POINTER(C.c_void_p)]),
     "fkb_plan_launch": (C.c_int, [C.c_void_p, C.c_void_p]),

@@ -396,6 +396,126 @@ int launch_once(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane
     return FKB_OK;
 }
 
+// -------------------------------------------------------------------------------------------------------
+// fkb_launch_transform_noalloc: the plane-record table lives in a fixed array inside the library image
+// -------------------------------------------------------------------------------------------------------
+// Device-side table of the allocation-free entry point.  Every GPU that loads this library carries these
+// FKB_NOALLOC_MAX_PLANES * sizeof(PlaneRec) bytes (768 KB) until the process exits.  In host code this name is only a
+// handle for cudaGetSymbolAddress, never an address a kernel may be given.
+static __device__ __align__(256) unsigned char g_noalloc_table[FKB_NOALLOC_MAX_PLANES * sizeof(PlaneRec)];
+
+struct NoAllocState {
+    std::mutex m;
+    PlaneRec* device_table[64] = {nullptr};  // per device: where g_noalloc_table lives on that device
+    PlaneRec host_recs[FKB_NOALLOC_MAX_PLANES];  // lowering target; ordinary (pageable) memory of the library image
+};
+NoAllocState& noalloc_state() {
+    static NoAllocState s;
+    return s;
+}
+
+// The lowering of lower(), writing into a caller-provided array instead of a growing vector.
+int lower_fixed(const fkb_chain_desc* chain, const fkb_plane_desc* planes, uint32_t n_planes, PlaneRec* recs,
+                LaunchParams& lp, uint32_t& staged_grid, uint32_t& lut_grid, dim3& gather_grid) {
+    const int rc = validate(chain, 1, planes, n_planes);
+    if (rc != FKB_OK) return rc;
+    std::memset(&lp, 0, sizeof(lp));
+    lp.chains[0] = *chain;
+    int sms = 0;
+    {
+        const int e = device_sm_count(sms);
+        if (e != FKB_OK) return e;
+    }
+    uint64_t row_segments = 0, lut_rows = 0;
+    uint32_t lut_min_tiles_x = 0xffffffffu;
+    for (uint32_t z = 0; z < n_planes; ++z) {
+        const fkb_plane_desc& s = planes[z];
+        PlaneRec& r = recs[z];
+        std::memset(&r, 0, sizeof(r));
+        r.src = static_cast<const uint8_t*>(s.src);
+        r.src_chroma = static_cast<const uint8_t*>(s.src_chroma);
+        r.dst = static_cast<uint8_t*>(s.dst);
+        r.dst_cstride = s.dst_channel_stride;
+        r.src_pitch = s.src_pitch;
+        r.crop_x = s.crop_x; r.crop_y = s.crop_y; r.crop_w = s.crop_w; r.crop_h = s.crop_h;
+        r.dst_w = s.dst_w; r.dst_h = s.dst_h; r.dst_pitch = s.dst_pitch;
+        r.fx = s.fx; r.fy = s.fy; r.x1 = s.x1; r.y1 = s.y1; r.x2 = s.x2; r.y2 = s.y2;
+        std::memcpy(r.bg, s.bg, sizeof(r.bg));
+        r.chain = 0;
+        std::memcpy(r.params, s.params, sizeof(r.params));
+        classify(*chain, r);
+        if (r.kclass == KCLASS_POINT || r.kclass == KCLASS_RESIZE) row_segments += static_cast<uint64_t>(r.tiles_x) * r.dst_h;
+        if (r.kclass == KCLASS_LUT) { lut_rows += r.dst_h; lut_min_tiles_x = std::min(lut_min_tiles_x, r.tiles_x); }
+    }
+    const uint32_t rpi = rows_per_item(row_segments, 2u * kStagedWarps * static_cast<uint32_t>(sms));
+    const uint32_t lut_rpu = lut_rows ? std::max<uint32_t>(static_cast<uint32_t>((lut_rows + 3ull * sms - 1) / (3ull * sms)),
+                                                           (8u + lut_min_tiles_x - 1) / lut_min_tiles_x) : 1u;
+    uint32_t n_tiles = 0, n_lut_units = 0, n_gather = 0, gw = 0, gh = 0, first_count = 0;
+    bool uniform = true;
+    for (uint32_t z = 0; z < n_planes; ++z) {
+        PlaneRec& r = recs[z];
+        r.lut_base = n_lut_units;
+        if (r.kclass == KCLASS_LUT) {
+            r.tile_h = std::min(r.dst_h, lut_rpu);
+            r.tiles_y = (r.dst_h + r.tile_h - 1) / r.tile_h;
+            n_lut_units += r.tiles_y;
+        } else if (r.kclass != KCLASS_GATHER) {
+            r.tile_h = std::min(r.dst_h, rpi);
+            r.tiles_y = (r.dst_h + r.tile_h - 1) / r.tile_h;
+        }
+        r.tile_base = n_tiles;
+        const uint32_t count = (r.kclass == KCLASS_POINT || r.kclass == KCLASS_RESIZE) ? r.tiles_x * r.tiles_y : 0u;
+        if (z == 0) first_count = count; else if (count != first_count) uniform = false;
+        if (static_cast<uint64_t>(n_tiles) + count > 0xfffffff0ull) return FKB_ERR_TOO_LARGE;
+        n_tiles += count;
+        if (r.kclass == KCLASS_GATHER) { ++n_gather; gw = std::max(gw, r.dst_w); gh = std::max(gh, r.dst_h); }
+    }
+    lp.n_planes = n_planes;
+    lp.neg_zero = -0.0f;
+    lp.post_kind[0] = post_kind_of(*chain);
+    uint32_t reorders = 0;
+    for (uint32_t i = 0; i < chain->n_ops; ++i) reorders += chain->ops[i].code == FKB_OP_REORDER_ZYX;
+    lp.lut_swap = reorders & 1u;
+    lp.n_tiles = n_tiles;
+    lp.tiles_per_plane = (uniform && first_count) ? first_count : 0;
+    lp.n_lut_units = n_lut_units;
+    staged_grid = n_tiles ? std::min<uint32_t>(n_tiles, 2u * static_cast<uint32_t>(sms)) : 0u;
+    lut_grid = n_lut_units ? std::min<uint32_t>(n_lut_units, 3u * static_cast<uint32_t>(sms)) : 0u;
+    gather_grid = n_gather ? dim3((gw + 127) / 128, (gh + 7) / 8, std::min<uint32_t>(n_planes, 65535u)) : dim3(0, 0, 0);
+    return status_word(&lp.status);
+}
+
+int launch_noalloc(const fkb_chain_desc* chain, const fkb_plane_desc* planes, uint32_t n_planes, cudaStream_t stream) {
+    if (!chain || !planes) return FKB_ERR_NULL;
+    if (n_planes > FKB_NOALLOC_MAX_PLANES) return FKB_ERR_TOO_LARGE;  // the fixed table holds no more
+    for (uint32_t z = 0; z < n_planes; ++z)
+        if (planes[z].chain != 0) return FKB_ERR_INVALID;
+    NoAllocState& st = noalloc_state();
+    std::lock_guard<std::mutex> g(st.m);
+    int dev = 0;
+    FKB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return FKB_ERR_UNSUPPORTED;
+    if (!st.device_table[dev]) {
+        // set-up, once per device, with that device current: ask the runtime where the array lives on it
+        PlaneRec* ptr = nullptr;
+        FKB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_table));
+        st.device_table[dev] = ptr;
+    }
+    LaunchParams lp;
+    uint32_t staged_grid = 0, lut_grid = 0;
+    dim3 gather_grid(0, 0, 0);
+    const int rc = lower_fixed(chain, planes, n_planes, st.host_recs, lp, staged_grid, lut_grid, gather_grid);
+    if (rc != FKB_OK) return rc;
+    // Every record the kernels will read is rewritten by this copy; nothing in the table has to start at zero.  The
+    // source is pageable memory, so the call returns only after the records have left st.host_recs.
+    FKB_CUDA(cudaMemcpyAsync(st.device_table[dev], st.host_recs, sizeof(PlaneRec) * n_planes, cudaMemcpyHostToDevice, stream));
+    lp.table = st.device_table[dev];
+    if (staged_grid) FKB_CUDA(launch_staged(lp, staged_grid, stream));
+    if (lut_grid) FKB_CUDA(launch_lut(lp, lut_grid, stream));
+    if (gather_grid.x) FKB_CUDA(launch_gather(lp, gather_grid, stream));
+    return FKB_OK;
+}
+
 }  // namespace
 }  // namespace fkb
 
@@ -447,6 +567,10 @@ int fkb_launch_transform(const fkb_chain_desc* chain, const fkb_plane_desc* plan
     for (uint32_t z = 0; z < n_planes; ++z)
         if (planes[z].chain != 0) return FKB_ERR_INVALID;
     return launch_once(chain, 1, planes, n_planes, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int fkb_launch_transform_noalloc(const fkb_chain_desc* chain, const fkb_plane_desc* planes, uint32_t n_planes, void* cuda_stream) {
+    return launch_noalloc(chain, planes, n_planes, static_cast<cudaStream_t>(cuda_stream));
 }
 
 int fkb_launch_divergent(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc* planes,

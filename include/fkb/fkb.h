@@ -6,7 +6,7 @@
  * (include/fused_kernel/fused_kernel.h:22-54); the type system turns the list into one templated
  * kernel (core/execution_model/executor_details/executor_kernels.h:20-30).  This header is the
  * boundary that sits beneath that source-level API in this library: the C++ front end
- * (include/fused_kernel_b200/) lowers a built chain to the plain structs below and calls one of the
+ * (include/fused_kernel/) lowers a built chain to the plain structs below and calls one of the
  * `fkb_launch_*` entry points.  Every struct is POD, every pointer is a plain device (or host)
  * address, no C++ or torch type crosses the boundary, and no entry point throws.
  *
@@ -139,6 +139,26 @@ int fkb_validate(const fkb_chain_desc* chains, uint32_t n_chains,
  * current device; the caller keeps src/dst alive until the stream has run the work. */
 int fkb_launch_transform(const fkb_chain_desc* chain, const fkb_plane_desc* planes,
                          uint32_t n_planes, void* cuda_stream);
+
+/* The same launch as fkb_launch_transform for callers that must not allocate.  (No counterpart in the reference: it is
+ * an addition of this library.)  Some users of these kernels run where creating memory is off the table once start-up
+ * is over: a process whose GPU memory was handed out in full to a pool or to other tenants, a service with a
+ * no-allocation rule on its steady-state path, code between two points where the CUDA runtime refuses allocation calls.
+ * fkb_launch_transform keeps its plane records in device and pinned buffers that it creates and grows on demand; this
+ * entry point instead keeps them in a fixed array that is part of the library image on every GPU, and calls neither
+ * cudaMalloc / cudaMallocHost / cudaFree nor any other allocating routine, on the device or on the host.
+ *   - Limit: at most FKB_NOALLOC_MAX_PLANES planes per call; more returns FKB_ERR_TOO_LARGE and launches nothing.
+ *   - Cost: FKB_NOALLOC_MAX_PLANES * 192 bytes (768 KB) of device memory on each GPU that loads the library, and the
+ *     same again in host memory, until the process exits, whether or not this entry point is ever called.
+ *   - The first call on a device looks up the array's device address (one cudaGetSymbolAddress, with that device
+ *     current).  Make that first call before any stream capture begins.
+ *   - All calls share the one array.  A call overwrites every record it uses, so nothing has to be cleared, but two
+ *     calls whose GPU work can overlap (different streams, no dependency between them) race on it: keep calls to this
+ *     entry point ordered on the GPU, or use fkb_launch_transform / a plan for concurrent launches.
+ * Source and destination buffers are still the caller's, as everywhere else in this header. */
+#define FKB_NOALLOC_MAX_PLANES 4096u
+int fkb_launch_transform_noalloc(const fkb_chain_desc* chain, const fkb_plane_desc* planes,
+                                 uint32_t n_planes, void* cuda_stream);
 
 /* One fused launch where plane z runs chains[planes[z].chain]; replaces
  * Executor<DivergentBatchTransformDPP<>>::executeOperations (executors.h:360-411). */

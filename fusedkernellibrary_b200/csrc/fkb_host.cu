@@ -132,6 +132,13 @@ bool force_gather() {
     return e && e[0] == '1';
 }
 
+// Launches below this many output pixels take the general kernel.  FKB_TINY_PIXELS (read at every launch) overrides the
+// default; 0 switches the routing off, which the tests use to drive small cases through the pipelined kernels.
+uint64_t tiny_launch_pixels() {
+    const char* e = std::getenv("FKB_TINY_PIXELS");
+    return e && e[0] ? std::strtoull(e, nullptr, 10) : kTinyLaunchPixels;
+}
+
 // Chooses the kernel path and tile shape of one plane.
 void classify(const fkb_chain_desc& ch, PlaneRec& r) {
     r.kclass = KCLASS_GATHER;
@@ -202,6 +209,7 @@ struct Lowered {
     uint32_t staged_grid = 0;
     uint32_t lut_grid = 0;
     dim3 gather_grid{0, 0, 0};
+    int gather_ppt = 4;
     uint32_t kernels = 0;
 };
 
@@ -243,7 +251,7 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         const int e = device_sm_count(sms);
         if (e != FKB_OK) return e;
     }
-    uint64_t row_segments = 0, lut_rows = 0;
+    uint64_t row_segments = 0, lut_rows = 0, total_pixels = 0, gather_pixels = 0;
     uint32_t lut_min_tiles_x = 0xffffffffu;
     for (uint32_t z = 0; z < n_planes; ++z) {
         const fkb_plane_desc& s = planes[z];
@@ -261,11 +269,20 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         r.chain = s.chain;
         std::memcpy(r.params, s.params, sizeof(r.params));
         classify(chains[s.chain], r);
+        total_pixels += static_cast<uint64_t>(r.dst_w) * r.dst_h;
+    }
+    // A launch of a few ten thousand pixels is pure latency: the pipelined paths would spend it filling their stages,
+    // so it goes through the general kernel, one pixel per thread.
+    if (total_pixels < tiny_launch_pixels())
+        for (uint32_t z = 0; z < n_planes; ++z) { L.recs[z].kclass = KCLASS_GATHER; L.recs[z].tiles_x = 0; }
+    for (uint32_t z = 0; z < n_planes; ++z) {
+        const PlaneRec& r = L.recs[z];
         if (r.kclass == KCLASS_POINT || r.kclass == KCLASS_RESIZE) row_segments += static_cast<uint64_t>(r.tiles_x) * r.dst_h;
         if (r.kclass == KCLASS_LUT) { lut_rows += r.dst_h; lut_min_tiles_x = std::min(lut_min_tiles_x, r.tiles_x); }
+        if (r.kclass == KCLASS_GATHER) gather_pixels += static_cast<uint64_t>(r.dst_w) * r.dst_h;
     }
     // LUT units: a block of rows of one plane per CTA visit; about one unit per resident CTA, at least eight row segments
-    const uint32_t lut_rpu = lut_rows ? std::max<uint32_t>(static_cast<uint32_t>((lut_rows + 3ull * sms - 1) / (3ull * sms)),
+    const uint32_t lut_rpu = lut_rows ? std::max<uint32_t>(static_cast<uint32_t>((lut_rows + 2ull * sms - 1) / (2ull * sms)),
                                                            (8u + lut_min_tiles_x - 1) / lut_min_tiles_x) : 1u;
     uint32_t n_lut_units = 0;
     const uint32_t rpi = rows_per_item(row_segments, 2u * kStagedWarps * static_cast<uint32_t>(sms));
@@ -303,11 +320,13 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
     }
     L.lp.n_lut_units = n_lut_units;
     if (n_lut_units) {
-        L.lut_grid = std::min<uint32_t>(n_lut_units, 3u * static_cast<uint32_t>(sms));
+        L.lut_grid = std::min<uint32_t>(n_lut_units, 2u * static_cast<uint32_t>(sms));
         ++L.kernels;
     }
     if (n_gather) {
-        L.gather_grid = dim3((gw + 127) / 128, (gh + 7) / 8, std::min<uint32_t>(n_planes, 65535u));
+        // small launches are latency-bound: one pixel per thread puts four times as many threads on the taps
+        L.gather_ppt = gather_pixels < (2u << 20) ? 1 : 4;
+        L.gather_grid = dim3((gw + 32 * L.gather_ppt - 1) / (32 * L.gather_ppt), (gh + 7) / 8, std::min<uint32_t>(n_planes, 65535u));
         ++L.kernels;
     }
     return status_word(&L.lp.status);
@@ -316,7 +335,7 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
 int run(const Lowered& L, const LaunchParams& lp, cudaStream_t stream) {
     if (L.staged_grid) FKB_CUDA(launch_staged(lp, L.staged_grid, stream));
     if (L.lut_grid) FKB_CUDA(launch_lut(lp, L.lut_grid, stream));
-    if (L.gather_grid.x) FKB_CUDA(launch_gather(lp, L.gather_grid, stream));
+    if (L.gather_grid.x) FKB_CUDA(launch_gather(lp, L.gather_grid, L.gather_ppt, stream));
     return FKB_OK;
 }
 
@@ -448,7 +467,7 @@ int lower_fixed(const fkb_chain_desc* chain, const fkb_plane_desc* planes, uint3
         if (r.kclass == KCLASS_LUT) { lut_rows += r.dst_h; lut_min_tiles_x = std::min(lut_min_tiles_x, r.tiles_x); }
     }
     const uint32_t rpi = rows_per_item(row_segments, 2u * kStagedWarps * static_cast<uint32_t>(sms));
-    const uint32_t lut_rpu = lut_rows ? std::max<uint32_t>(static_cast<uint32_t>((lut_rows + 3ull * sms - 1) / (3ull * sms)),
+    const uint32_t lut_rpu = lut_rows ? std::max<uint32_t>(static_cast<uint32_t>((lut_rows + 2ull * sms - 1) / (2ull * sms)),
                                                            (8u + lut_min_tiles_x - 1) / lut_min_tiles_x) : 1u;
     uint32_t n_tiles = 0, n_lut_units = 0, n_gather = 0, gw = 0, gh = 0, first_count = 0;
     bool uniform = true;
@@ -480,7 +499,7 @@ int lower_fixed(const fkb_chain_desc* chain, const fkb_plane_desc* planes, uint3
     lp.tiles_per_plane = (uniform && first_count) ? first_count : 0;
     lp.n_lut_units = n_lut_units;
     staged_grid = n_tiles ? std::min<uint32_t>(n_tiles, 2u * static_cast<uint32_t>(sms)) : 0u;
-    lut_grid = n_lut_units ? std::min<uint32_t>(n_lut_units, 3u * static_cast<uint32_t>(sms)) : 0u;
+    lut_grid = n_lut_units ? std::min<uint32_t>(n_lut_units, 2u * static_cast<uint32_t>(sms)) : 0u;
     gather_grid = n_gather ? dim3((gw + 127) / 128, (gh + 7) / 8, std::min<uint32_t>(n_planes, 65535u)) : dim3(0, 0, 0);
     return status_word(&lp.status);
 }
@@ -512,7 +531,7 @@ int launch_noalloc(const fkb_chain_desc* chain, const fkb_plane_desc* planes, ui
     lp.table = st.device_table[dev];
     if (staged_grid) FKB_CUDA(launch_staged(lp, staged_grid, stream));
     if (lut_grid) FKB_CUDA(launch_lut(lp, lut_grid, stream));
-    if (gather_grid.x) FKB_CUDA(launch_gather(lp, gather_grid, stream));
+    if (gather_grid.x) FKB_CUDA(launch_gather(lp, gather_grid, 4, stream));
     return FKB_OK;
 }
 

@@ -47,6 +47,8 @@ __device__ __forceinline__ void read_tap_global(const fkb_chain_desc& ch, const 
 // ---------------------------------------------------------------------------------------------------------
 // gather_kernel
 // ---------------------------------------------------------------------------------------------------------
+// PPT pixels per thread: 4 for large launches (vector stores), 1 for small ones (more threads hide the tap latency).
+template <int PPT>
 __global__ void __launch_bounds__(256) gather_kernel(const __grid_constant__ LaunchParams p) {
     __shared__ PlaneRec s_pl;
     const PlaneRec* table = plane_table(p);
@@ -60,25 +62,25 @@ __global__ void __launch_bounds__(256) gather_kernel(const __grid_constant__ Lau
         if (pl.kclass != KCLASS_GATHER) continue;
         const fkb_chain_desc& ch = p.chains[pl.chain];
         const uint32_t y = blockIdx.y * 8 + ty;
-        const uint32_t x0 = (blockIdx.x * 32 + tx) * 4;
+        const uint32_t x0 = (blockIdx.x * 32 + tx) * PPT;
         if (y >= pl.dst_h || x0 >= pl.dst_w) continue;
-        const uint32_t nvalid = min(4u, pl.dst_w - x0);
+        const uint32_t nvalid = min(static_cast<uint32_t>(PPT), pl.dst_w - x0);
 
-        float v[4][3];
+        float v[PPT][3];
         if (ch.geometry == FKB_GEOM_NONE) {
 #pragma unroll
-            for (int n = 0; n < 4; ++n) {
+            for (int n = 0; n < PPT; ++n) {
                 if (n < nvalid) read_tap_global(ch, pl, x0 + n, y, v[n]);
                 else { v[n][0] = v[n][1] = v[n][2] = 0.f; }
             }
-            apply_ops<4>(v, ch, pl, 0, ch.n_ops);
+            apply_ops<PPT>(v, ch, pl, 0, ch.n_ops);
         } else {
             const bool par = ch.geometry == FKB_GEOM_RESIZE_PRESERVE_AR;
             const int ox = par ? pl.x1 : 0, oy = par ? pl.y1 : 0;
             const bool row_in = !par || (static_cast<int>(y) >= pl.y1 && static_cast<int>(y) <= pl.y2);
             const AxisTap ay = axis_tap(row_in ? static_cast<int>(y) - oy : 0, pl.fy, pl.crop_h);
 #pragma unroll
-            for (int n = 0; n < 4; ++n) {
+            for (int n = 0; n < PPT; ++n) {
                 const int x = static_cast<int>(x0) + n;
                 const bool inside = n < nvalid && row_in && (!par || (x >= pl.x1 && x <= pl.x2));
                 if (inside) {
@@ -97,7 +99,7 @@ __global__ void __launch_bounds__(256) gather_kernel(const __grid_constant__ Lau
                     v[n][0] = pl.bg[0]; v[n][1] = pl.bg[1]; v[n][2] = pl.bg[2];
                 }
             }
-            apply_ops<4>(v, ch, pl, ch.n_pre_ops, ch.n_ops);
+            apply_ops<PPT>(v, ch, pl, ch.n_pre_ops, ch.n_ops);
         }
 
         uint8_t* row = pl.dst + static_cast<size_t>(y) * pl.dst_pitch;
@@ -107,8 +109,8 @@ __global__ void __launch_bounds__(256) gather_kernel(const __grid_constant__ Lau
                 uint8_t* q = row + static_cast<size_t>(c) * pl.dst_cstride;
                 if (ch.dst_format == FKB_PIX_F32C3) {
                     float* f = reinterpret_cast<float*>(q) + x0;
-                    if (nvalid == 4 && (reinterpret_cast<uintptr_t>(f) & 15) == 0) {
-                        *reinterpret_cast<float4*>(f) = make_float4(v[0][c], v[1][c], v[2][c], v[3][c]);
+                    if (PPT == 4 && nvalid == 4 && (reinterpret_cast<uintptr_t>(f) & 15) == 0) {
+                        *reinterpret_cast<float4*>(f) = make_float4(v[0][c], v[1 % PPT][c], v[2 % PPT][c], v[3 % PPT][c]);
                     } else {
                         for (uint32_t n = 0; n < nvalid; ++n) f[n] = v[n][c];
                     }
@@ -118,22 +120,22 @@ __global__ void __launch_bounds__(256) gather_kernel(const __grid_constant__ Lau
             }
         } else if (ch.dst_format == FKB_PIX_F32C3) {
             float* f = reinterpret_cast<float*>(row) + static_cast<size_t>(x0) * 3;
-            if (nvalid == 4 && (reinterpret_cast<uintptr_t>(f) & 15) == 0) {
+            if (PPT == 4 && nvalid == 4 && (reinterpret_cast<uintptr_t>(f) & 15) == 0) {
                 float4* f4 = reinterpret_cast<float4*>(f);
-                f4[0] = make_float4(v[0][0], v[0][1], v[0][2], v[1][0]);
-                f4[1] = make_float4(v[1][1], v[1][2], v[2][0], v[2][1]);
-                f4[2] = make_float4(v[2][2], v[3][0], v[3][1], v[3][2]);
+                f4[0] = make_float4(v[0][0], v[0][1], v[0][2], v[1 % PPT][0]);
+                f4[1] = make_float4(v[1 % PPT][1], v[1 % PPT][2], v[2 % PPT][0], v[2 % PPT][1]);
+                f4[2] = make_float4(v[2 % PPT][2], v[3 % PPT][0], v[3 % PPT][1], v[3 % PPT][2]);
             } else {
                 for (uint32_t n = 0; n < nvalid; ++n) { f[3 * n] = v[n][0]; f[3 * n + 1] = v[n][1]; f[3 * n + 2] = v[n][2]; }
             }
         } else {
             uint8_t* q = row + static_cast<size_t>(x0) * 3;
-            if (nvalid == 4 && (reinterpret_cast<uintptr_t>(q) & 3) == 0) {
+            if (PPT == 4 && nvalid == 4 && (reinterpret_cast<uintptr_t>(q) & 3) == 0) {
                 uint32_t b[12];
 #pragma unroll
                 for (int n = 0; n < 4; ++n)
 #pragma unroll
-                    for (int c = 0; c < 3; ++c) b[3 * n + c] = static_cast<uint32_t>(v[n][c]);
+                    for (int c = 0; c < 3; ++c) b[3 * n + c] = static_cast<uint32_t>(v[n % PPT][c]);
                 uint32_t* q4 = reinterpret_cast<uint32_t*>(q);
 #pragma unroll
                 for (int k = 0; k < 3; ++k) q4[k] = b[4 * k] | (b[4 * k + 1] << 8) | (b[4 * k + 2] << 16) | (b[4 * k + 3] << 24);
@@ -158,17 +160,19 @@ extern __shared__ __align__(128) uint8_t smem_raw[];
 struct WarpSlice {
     uint32_t base;  // offset of this warp's slice in smem_raw
     const PlaneRec* pl;
+    // mbarriers 0,1: the two stages of RESIZE items; 2..5: the four stages of POINT items (separate phase counters)
     __device__ __forceinline__ uint64_t* bar(uint32_t s) const { return reinterpret_cast<uint64_t*>(smem_raw + base) + s; }
     __device__ __forceinline__ uint32_t in(uint32_t s) const { return base + kSliceHeader + s * (2 * kInRowBytes); }
+    __device__ __forceinline__ uint32_t in4(uint32_t s) const { return base + kSliceHeader + s * kInRowBytes; }
     __device__ __forceinline__ uint32_t out(uint32_t s) const { return base + kSliceHeader + 4 * kInRowBytes + s * kOutSlotBytes; }
 };
 __device__ __forceinline__ WarpSlice warp_slice(uint32_t base) {
     WarpSlice w;
     w.base = base;
-    w.pl = reinterpret_cast<const PlaneRec*>(smem_raw + base + 16);
+    w.pl = reinterpret_cast<const PlaneRec*>(smem_raw + base + 48);
     return w;
 }
-static_assert(16 + sizeof(PlaneRec) <= kSliceHeader, "slice header");
+static_assert(48 + sizeof(PlaneRec) <= kSliceHeader, "slice header");
 static_assert(kSliceHeader + 4 * kInRowBytes + 2 * kOutSlotBytes == kSliceBytes, "slice layout");
 
 __device__ __forceinline__ uint32_t tile_to_plane(const LaunchParams& p, uint32_t t, uint32_t& local) {
@@ -196,27 +200,6 @@ __device__ __forceinline__ void store_row(uint8_t* gdst, uint32_t srow, uint32_t
     if (row_bytes != bulk) {  // rare: a row whose byte length is not a multiple of 16
         if (lane < row_bytes - bulk) gdst[bulk + lane] = smem_raw[srow + bulk + lane];
     }
-}
-
-// Row pipeline of one item (a block of `nr` output rows of one plane, `ow` pixels wide).  `issue(r, stage)` starts
-// the bulk loads of row r (lane 0 announces the byte count, then issues); `compute(r, stage)` turns the staged bytes
-// into the output row in w.out[stage].  `k` counts this warp's steps: it selects the stage and the mbarrier phase.
-template <typename Issue, typename Compute>
-__device__ __forceinline__ bool run_rows(const WarpSlice& w, uint32_t nr, uint32_t& k, uint32_t lane, uint8_t* gdst,
-                                         uint32_t dst_pitch, uint32_t row_bytes, Issue issue, Compute compute) {
-    issue(0u, k & 1u);
-    for (uint32_t r = 0; r < nr; ++r, ++k) {
-        const uint32_t s = k & 1u;
-        if (r + 1 < nr) issue(r + 1, s ^ 1u);
-        const bool ok = mbar_wait_bounded(w.bar(s), (k >> 1) & 1u);
-        if (__any_sync(0xffffffffu, !ok)) return false;
-        // the bulk store that read w.out(s) two steps ago must have finished reading before the row is overwritten
-        if (lane == 0) bulk_wait_read_1();
-        __syncwarp();
-        compute(r, s);
-        store_row(gdst + static_cast<size_t>(r) * dst_pitch, w.out(s), row_bytes, lane);
-    }
-    return true;
 }
 
 // --- post-ops ---------------------------------------------------------------------------------------------
@@ -260,6 +243,7 @@ __device__ __forceinline__ f2 post_channel(f2 r, const PostParams& q, int c, flo
 // uchar3 -> uchar3: each lane owns 16 pixels (48 B): three 128-bit shared loads and stores; lane chunks are 48 B
 // apart, which maps the eight lanes of a quarter-warp onto disjoint bank groups.
 // uchar3 -> float3: each lane owns 4 pixels per pass: three 32-bit shared loads (12 B apart), three 128-bit stores.
+// Their rows are short (at most 1.5 KB in), so three rows are kept in flight ahead of the one being computed.
 template <bool F32, int KIND>
 __device__ __forceinline__ bool point_item(const LaunchParams& p, const WarpSlice& w, uint32_t ox, uint32_t oy0,
                                            uint32_t ow, uint32_t nr, uint32_t& k, uint32_t lane) {
@@ -280,17 +264,17 @@ __device__ __forceinline__ bool point_item(const LaunchParams& p, const WarpSlic
     uint8_t* gdst = pl.dst + static_cast<size_t>(oy0) * pl.dst_pitch + static_cast<size_t>(ox) * (F32 ? 12u : 3u);
     auto issue = [&](uint32_t r, uint32_t s) {
         if (lane == 0) {
-            mbar_arrive_expect_tx(w.bar(s), in_bytes);
-            bulk_load(smem_raw + w.in(s), gsrc + static_cast<size_t>(r) * src_pitch, in_bytes, w.bar(s));
+            mbar_arrive_expect_tx(w.bar(2 + s), in_bytes);
+            bulk_load(smem_raw + w.in4(s), gsrc + static_cast<size_t>(r) * src_pitch, in_bytes, w.bar(2 + s));
         }
     };
-    auto compute = [&](uint32_t, uint32_t s) {
+    auto compute = [&](uint32_t in_s, uint32_t out_s) {
         if (F32) {
             // 4 pixels = 12 source bytes = 6 byte pairs per lane step.  A pair (two neighbouring bytes of one word)
             // becomes two half-subnormals with one byte permute, is widened to fp32 (b * 2^-24) and multiplied by the
             // Mul operand pre-scaled by 2^24 (or by 2^24 alone), all exact; pair k holds channels (2k mod 3, 2k+1 mod 3).
             for (uint32_t c = lane; c * 4u < ow; c += 32) {
-                const uint32_t* src = reinterpret_cast<const uint32_t*>(smem_raw + w.in(s) + c * 12u);
+                const uint32_t* src = reinterpret_cast<const uint32_t*>(smem_raw + in_s + c * 12u);
                 const uint32_t q[3] = {src[0], src[1], src[2]};
                 f2 v[6];
 #pragma unroll
@@ -313,14 +297,14 @@ __device__ __forceinline__ bool point_item(const LaunchParams& p, const WarpSlic
                     v[0] = f2{t[0][0], t[0][1]}; v[1] = f2{t[0][2], t[1][0]}; v[2] = f2{t[1][1], t[1][2]};
                     v[3] = f2{t[2][0], t[2][1]}; v[4] = f2{t[2][2], t[3][0]}; v[5] = f2{t[3][1], t[3][2]};
                 }
-                float4* dst = reinterpret_cast<float4*>(smem_raw + w.out(s) + c * 48u);
+                float4* dst = reinterpret_cast<float4*>(smem_raw + out_s + c * 48u);
                 dst[0] = make_float4(v[0].x, v[0].y, v[1].x, v[1].y);
                 dst[1] = make_float4(v[2].x, v[2].y, v[3].x, v[3].y);
                 dst[2] = make_float4(v[4].x, v[4].y, v[5].x, v[5].y);
             }
         } else {
             for (uint32_t c = lane; c * 16u < ow; c += 32) {
-                const uint4* src = reinterpret_cast<const uint4*>(smem_raw + w.in(s) + c * 48u);
+                const uint4* src = reinterpret_cast<const uint4*>(smem_raw + in_s + c * 48u);
                 uint32_t q[12];
 #pragma unroll
                 for (int i = 0; i < 3; ++i) { const uint4 t = src[i]; q[4 * i] = t.x; q[4 * i + 1] = t.y; q[4 * i + 2] = t.z; q[4 * i + 3] = t.w; }
@@ -332,13 +316,28 @@ __device__ __forceinline__ bool point_item(const LaunchParams& p, const WarpSlic
                 for (int i = 0; i < 12; ++i) q[i] = 0;
 #pragma unroll
                 for (int b = 0; b < 48; ++b) q[b >> 2] |= u8_of_exact(v[b / 3][b % 3]) << (8 * (b & 3));
-                uint4* dst = reinterpret_cast<uint4*>(smem_raw + w.out(s) + c * 48u);
+                uint4* dst = reinterpret_cast<uint4*>(smem_raw + out_s + c * 48u);
 #pragma unroll
                 for (int i = 0; i < 3; ++i) dst[i] = make_uint4(q[4 * i], q[4 * i + 1], q[4 * i + 2], q[4 * i + 3]);
             }
         }
     };
-    return run_rows(w, nr, k, lane, gdst, pl.dst_pitch, ow * (F32 ? 12u : 3u), issue, compute);
+    constexpr uint32_t AHEAD = 3;
+    const uint32_t dst_pitch = pl.dst_pitch, row_bytes = ow * (F32 ? 12u : 3u);
+    // the previous item may have ended on either output buffer: start from a state where no store reads them
+    if (lane == 0) bulk_wait_read_all();
+    __syncwarp();
+    for (uint32_t i = 0; i < AHEAD && i < nr; ++i) issue(i, (k + i) & 3u);
+    for (uint32_t r = 0; r < nr; ++r, ++k) {
+        const uint32_t s = k & 3u, o = k & 1u;
+        if (lane == 0) bulk_wait_read_1();  // the store that read w.out(o) two rows ago is done with it
+        if (r + AHEAD < nr) issue(r + AHEAD, (k + AHEAD) & 3u);  // into the stage of the row computed just before
+        const bool landed = mbar_wait_bounded(w.bar(2 + s), (k >> 2) & 1u);
+        if (__any_sync(0xffffffffu, !landed)) return false;
+        compute(w.in4(s), w.out(o));
+        store_row(gdst + static_cast<size_t>(r) * dst_pitch, w.out(o), row_bytes, lane);
+    }
+    return true;
 }
 
 // --- RESIZE items -----------------------------------------------------------------------------------------
@@ -532,8 +531,7 @@ __global__ void __launch_bounds__(kStagedThreads, 2) staged_kernel(const __grid_
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const WarpSlice w = warp_slice(warp * kSliceBytes);
     if (lane == 0) {
-        mbar_init(w.bar(0), 1);
-        mbar_init(w.bar(1), 1);
+        for (uint32_t i = 0; i < 6; ++i) mbar_init(w.bar(i), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncwarp();
@@ -541,14 +539,14 @@ __global__ void __launch_bounds__(kStagedThreads, 2) staged_kernel(const __grid_
     // item i runs on warp (i / gridDim.x) % warps_per_cta of CTA i % gridDim.x: a small launch spreads over all SMs
     const uint32_t first = warp * gridDim.x + blockIdx.x, stride = gridDim.x * warps_per_cta;
     const PlaneRec* table = plane_table(p);
-    uint32_t k = 0;
+    uint32_t k = 0, k4 = 0;  // steps done so far by RESIZE items (two stages) and by POINT items (four stages)
     bool ok = true;
     for (uint32_t item = first; item < p.n_tiles && ok; item += stride) {
         uint32_t local;
         const uint32_t z = tile_to_plane(p, item, local);
         __syncwarp();
         if (lane < sizeof(PlaneRec) / 16)
-            reinterpret_cast<uint4*>(smem_raw + w.base + 16)[lane] = reinterpret_cast<const uint4*>(table + z)[lane];
+            reinterpret_cast<uint4*>(smem_raw + w.base + 48)[lane] = reinterpret_cast<const uint4*>(table + z)[lane];
         __syncwarp();
         const PlaneRec& pl = *w.pl;
         const uint32_t tyi = local / pl.tiles_x, txi = local - tyi * pl.tiles_x;
@@ -556,13 +554,13 @@ __global__ void __launch_bounds__(kStagedThreads, 2) staged_kernel(const __grid_
         const uint32_t ow = min(pl.tile_w, pl.dst_w - ox), nr = min(pl.tile_h, pl.dst_h - oy0);
         const bool f32 = p.chains[pl.chain].dst_format == FKB_PIX_F32C3;
         if (pl.kclass == KCLASS_POINT) {
-            if (!f32) ok = point_item<false, kPostGeneric>(p, w, ox, oy0, ow, nr, k, lane);
+            if (!f32) ok = point_item<false, kPostGeneric>(p, w, ox, oy0, ow, nr, k4, lane);
             else switch (p.post_kind[pl.chain]) {
-                case 0: ok = point_item<true, 0>(p, w, ox, oy0, ow, nr, k, lane); break;
-                case kPostMul: ok = point_item<true, kPostMul>(p, w, ox, oy0, ow, nr, k, lane); break;
-                case kPostAdd: ok = point_item<true, kPostAdd>(p, w, ox, oy0, ow, nr, k, lane); break;
-                case kPostMul | kPostAdd: ok = point_item<true, kPostMul | kPostAdd>(p, w, ox, oy0, ow, nr, k, lane); break;
-                default: ok = point_item<true, kPostGeneric>(p, w, ox, oy0, ow, nr, k, lane); break;
+                case 0: ok = point_item<true, 0>(p, w, ox, oy0, ow, nr, k4, lane); break;
+                case kPostMul: ok = point_item<true, kPostMul>(p, w, ox, oy0, ow, nr, k4, lane); break;
+                case kPostAdd: ok = point_item<true, kPostAdd>(p, w, ox, oy0, ow, nr, k4, lane); break;
+                case kPostMul | kPostAdd: ok = point_item<true, kPostMul | kPostAdd>(p, w, ox, oy0, ow, nr, k4, lane); break;
+                default: ok = point_item<true, kPostGeneric>(p, w, ox, oy0, ow, nr, k4, lane); break;
             }
         }
         else ok = f32 ? resize_dispatch<true>(p, w, p.post_kind[pl.chain], ox, oy0, ow, nr, k, lane)
@@ -570,8 +568,9 @@ __global__ void __launch_bounds__(kStagedThreads, 2) staged_kernel(const __grid_
     }
     if (lane == 0) bulk_wait_all();  // shared memory must stay valid until the last bulk store has read it
     if (!ok) {
-        // a copy announced on the other stage may still be in flight: give it a bounded chance to land
+        // copies announced on the other stages may still be in flight: give them a bounded chance to land
         mbar_wait_bounded(w.bar((k + 1) & 1u), ((k + 1) >> 1) & 1u);
+        for (uint32_t i = 1; i <= 3; ++i) mbar_wait_bounded(w.bar(2 + ((k4 + i) & 3u)), ((k4 + i) >> 2) & 1u);
         if (lane == 0) atomicExch(p.status, FKB_ERR_DEVICE_WAIT);
     }
 }
@@ -582,8 +581,9 @@ __global__ void __launch_bounds__(kStagedThreads, 2) staged_kernel(const __grid_
 // Every op of such a chain acts on one channel at a time (a channel reorder only renames channels), so output channel c
 // is a function of one source byte: out[c] = T_c(in[perm(c)]).  Each CTA evaluates the chain — through the same op
 // interpreter as every other path, so the table is exact by construction — once for the 256 possible bytes, and then
-// every pixel costs three table reads instead of the whole chain (IEEE divisions and saturations included).  The
-// table holds kLutCopies copies of each entry spread over the banks so that the 32 lanes of a load rarely collide.
+// every pixel costs three table reads instead of the whole chain (IEEE divisions and saturations included).  An entry
+// is one 32-bit word holding the three channels' results for that byte value, and every lane reads its own copy of the
+// table (copy l lives in bank l), so a table read is free of bank conflicts whatever the pixel values are.
 // Rows move exactly like in staged_kernel: per-warp bulk loads into shared memory, bulk stores out.
 __device__ __forceinline__ uint32_t unit_to_plane(const LaunchParams& p, uint32_t u, uint32_t& local) {
     const PlaneRec* table = plane_table(p);
@@ -603,7 +603,7 @@ __device__ __forceinline__ void lut_segment(uint32_t in_s, uint32_t out_s, uint3
     uint32_t q[12];
 #pragma unroll
     for (int i = 0; i < 3; ++i) { const uint4 t = src[i]; q[4 * i] = t.x; q[4 * i + 1] = t.y; q[4 * i + 2] = t.z; q[4 * i + 3] = t.w; }
-    const uint32_t lane_off = (lane & (kLutCopies - 1)) * 4u;
+    const uint32_t lane_off = lane * 4u;
     uint32_t o[12];
 #pragma unroll
     for (int i = 0; i < 12; ++i) {
@@ -613,24 +613,25 @@ __device__ __forceinline__ void lut_segment(uint32_t in_s, uint32_t out_s, uint3
             const int b = 4 * i + t, c = b % 3;          // output byte b is channel c of pixel b / 3
             const int sb = SWAP ? b - c + (2 - c) : b;   // the source byte it is a function of
             const uint32_t idx = __byte_perm(q[sb >> 2], 0u, 0x4440u | (sb & 3));
-            e[t] = *reinterpret_cast<const uint32_t*>(smem_raw + idx * (kLutCopies * 4u) + (c * 256u * kLutCopies * 4u) + lane_off);
+            e[t] = *reinterpret_cast<const uint32_t*>(smem_raw + idx * 128u + lane_off);
         }
-        o[i] = __byte_perm(__byte_perm(e[0], e[1], 0x0040u), __byte_perm(e[2], e[3], 0x0040u), 0x5410u);
+        // byte (4i+t) % 3 of entry t is the channel this output byte wants
+        const uint32_t c0 = (4 * i) % 3, c1 = (4 * i + 1) % 3, c2 = (4 * i + 2) % 3, c3 = (4 * i + 3) % 3;  // constants once unrolled
+        o[i] = __byte_perm(__byte_perm(e[0], e[1], c0 | ((4u + c1) << 4)), __byte_perm(e[2], e[3], c2 | ((4u + c3) << 4)), 0x5410u);
     }
     uint4* dst = reinterpret_cast<uint4*>(smem_raw + out_s + lane * 48u);
 #pragma unroll
     for (int i = 0; i < 3; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
 }
 
-__global__ void __launch_bounds__(kStagedThreads, 3) lut_kernel(const __grid_constant__ LaunchParams p) {
+__global__ void __launch_bounds__(kLutThreads, 2) lut_kernel(const __grid_constant__ LaunchParams p) {
     __shared__ PlaneRec s_pl;
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t slice = kLutBytes + warp * kLutSliceBytes;
     uint64_t* bar = reinterpret_cast<uint64_t*>(smem_raw + slice);
-    const uint32_t in0 = slice + 32, out0 = slice + 32 + 2 * kLutSegBytes;
+    const uint32_t in0 = slice + 64, out0 = slice + 64 + kLutInStages * kLutSegBytes;
     if (lane == 0) {
-        mbar_init(&bar[0], 1);
-        mbar_init(&bar[1], 1);
+        for (uint32_t i = 0; i < kLutInStages; ++i) mbar_init(&bar[i], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncwarp();
@@ -640,26 +641,13 @@ __global__ void __launch_bounds__(kStagedThreads, 3) lut_kernel(const __grid_con
     for (uint32_t unit = blockIdx.x; unit < p.n_lut_units; unit += gridDim.x) {
         uint32_t local;
         const uint32_t z = unit_to_plane(p, unit, local);
-        if (z != cur_plane) {  // block-uniform
+        const bool rebuild = z != cur_plane;  // block-uniform
+        if (rebuild) {
             if (lane == 0) bulk_wait_read_all();
             __syncthreads();  // nobody reads the old table or plane record any more
             if (threadIdx.x < sizeof(PlaneRec) / 16)
                 reinterpret_cast<uint4*>(&s_pl)[threadIdx.x] = reinterpret_cast<const uint4*>(table + z)[threadIdx.x];
             __syncthreads();
-            const fkb_chain_desc& ch = p.chains[s_pl.chain];
-            for (uint32_t t = threadIdx.x; t < 256; t += blockDim.x) {
-                float v[1][3] = {{static_cast<float>(t), static_cast<float>(t), static_cast<float>(t)}};
-                apply_ops<1>(v, ch, s_pl, 0, ch.n_ops);
-#pragma unroll
-                for (int c = 0; c < 3; ++c) {
-                    const uint32_t e = u8_of_exact(v[0][c]);
-                    uint32_t* row = reinterpret_cast<uint32_t*>(smem_raw) + (c * 256u + t) * kLutCopies;
-#pragma unroll
-                    for (uint32_t r = 0; r < kLutCopies; ++r) row[r] = e;
-                }
-            }
-            __syncthreads();
-            cur_plane = z;
         }
         const PlaneRec& pl = s_pl;
         const bool swap = (p.lut_swap >> pl.chain) & 1u;
@@ -668,34 +656,57 @@ __global__ void __launch_bounds__(kStagedThreads, 3) lut_kernel(const __grid_con
         const uint8_t* gsrc = pl.src + static_cast<size_t>(pl.crop_y + row0) * pl.src_pitch + static_cast<size_t>(pl.crop_x) * 3u;
         uint8_t* gdst = pl.dst + static_cast<size_t>(row0) * pl.dst_pitch;
         const uint32_t src_pitch = pl.src_pitch, dst_pitch = pl.dst_pitch, tiles_x = pl.tiles_x, tile_w = pl.tile_w, dst_w = pl.dst_w;
-        // segment g of the unit = (row g / tiles_x, column tile g % tiles_x); this warp takes g = warp, warp + 8, ...
-        auto issue = [&](uint32_t g, uint32_t s) {
+        // Segment g of the unit is (row g / tiles_x, column tile g % tiles_x); this warp takes g = warp, warp + 8, ...
+        // Two cursors walk that list without dividing: `pf` for the prefetches, `cu` for the segment being computed.
+        struct Cursor { uint32_t g, r, tx; };
+        auto advance = [&](Cursor& c) {
+            c.g += kLutWarps; c.tx += kLutWarps;
+            while (c.tx >= tiles_x) { c.tx -= tiles_x; ++c.r; }
+        };
+        auto issue = [&](const Cursor& c, uint32_t s) {
             if (lane == 0) {
-                const uint32_t r = g / tiles_x, tx = g - r * tiles_x;
-                const uint32_t ow = min(tile_w, dst_w - tx * tile_w);
+                const uint32_t ow = min(tile_w, dst_w - c.tx * tile_w);
                 const uint32_t bytes = (ow * 3u + 15u) & ~15u;
                 mbar_arrive_expect_tx(&bar[s], bytes);
-                bulk_load(smem_raw + in0 + s * kLutSegBytes, gsrc + static_cast<size_t>(r) * src_pitch + static_cast<size_t>(tx) * tile_w * 3u, bytes, &bar[s]);
+                bulk_load(smem_raw + in0 + s * kLutSegBytes, gsrc + static_cast<size_t>(c.r) * src_pitch + static_cast<size_t>(c.tx) * tile_w * 3u, bytes, &bar[s]);
             }
         };
-        if (warp < nseg) issue(warp, k & 1u);
-        for (uint32_t g = warp; g < nseg && ok; g += kStagedWarps, ++k) {
-            const uint32_t s = k & 1u;
+        Cursor cu{warp, warp / tiles_x, warp % tiles_x}, pf = cu;
+        constexpr uint32_t AHEAD = kLutInStages - 1;
+        for (uint32_t i = 0; i < AHEAD; ++i) {  // the first loads fly while the table is built
+            if (pf.g < nseg) issue(pf, (k + i) % kLutInStages);
+            advance(pf);
+        }
+        if (rebuild) {
+            const fkb_chain_desc& ch = p.chains[pl.chain];
+            for (uint32_t t = threadIdx.x; t < 256; t += blockDim.x) {
+                float v[1][3] = {{static_cast<float>(t), static_cast<float>(t), static_cast<float>(t)}};
+                apply_ops<1>(v, ch, pl, 0, ch.n_ops);
+                const uint32_t e = u8_of_exact(v[0][0]) | (u8_of_exact(v[0][1]) << 8) | (u8_of_exact(v[0][2]) << 16);
+                uint32_t* row = reinterpret_cast<uint32_t*>(smem_raw) + t * 32u;
+#pragma unroll
+                for (uint32_t r = 0; r < 32; ++r) row[r] = e;
+            }
+            __syncthreads();
+            cur_plane = z;
+        }
+        for (; cu.g < nseg && ok; advance(cu), ++k) {
+            const uint32_t s = k % kLutInStages, o = k & 1u;
             if (lane == 0) bulk_wait_read_1();  // the store that read this output buffer two segments ago is done
-            if (g + kStagedWarps < nseg) issue(g + kStagedWarps, s ^ 1u);
-            const bool landed = mbar_wait_bounded(&bar[s], (k >> 1) & 1u);
+            if (pf.g < nseg) issue(pf, (k + AHEAD) % kLutInStages);
+            advance(pf);
+            const bool landed = mbar_wait_bounded(&bar[s], (k / kLutInStages) & 1u);
             if (__any_sync(0xffffffffu, !landed)) { ok = false; break; }
-            const uint32_t r = g / tiles_x, tx = g - r * tiles_x;
-            const uint32_t ow = min(tile_w, dst_w - tx * tile_w);
-            if (swap) lut_segment<true>(in0 + s * kLutSegBytes, out0 + s * kLutSegBytes, ow, lane);
-            else lut_segment<false>(in0 + s * kLutSegBytes, out0 + s * kLutSegBytes, ow, lane);
-            store_row(gdst + static_cast<size_t>(r) * dst_pitch + static_cast<size_t>(tx) * tile_w * 3u, out0 + s * kLutSegBytes, ow * 3u, lane);
+            const uint32_t ow = min(tile_w, dst_w - cu.tx * tile_w);
+            if (swap) lut_segment<true>(in0 + s * kLutSegBytes, out0 + o * kLutSegBytes, ow, lane);
+            else lut_segment<false>(in0 + s * kLutSegBytes, out0 + o * kLutSegBytes, ow, lane);
+            store_row(gdst + static_cast<size_t>(cu.r) * dst_pitch + static_cast<size_t>(cu.tx) * tile_w * 3u, out0 + o * kLutSegBytes, ow * 3u, lane);
         }
         if (__syncthreads_or(ok ? 0 : 1)) { ok = false; break; }
     }
     if (lane == 0) bulk_wait_all();
     if (!ok) {
-        mbar_wait_bounded(&bar[(k + 1) & 1u], ((k + 1) >> 1) & 1u);
+        for (uint32_t i = 1; i < kLutInStages; ++i) mbar_wait_bounded(&bar[(k + i) % kLutInStages], ((k + i) / kLutInStages) & 1u);
         if (threadIdx.x == 0) atomicExch(p.status, FKB_ERR_DEVICE_WAIT);
     }
 }
@@ -727,12 +738,13 @@ cudaError_t launch_lut(const LaunchParams& p, uint32_t grid, cudaStream_t stream
         if (e != cudaSuccess) return e;
         configured_device = dev;
     }
-    lut_kernel<<<grid, kStagedThreads, kLutSmemBytes, stream>>>(p);
+    lut_kernel<<<grid, kLutThreads, kLutSmemBytes, stream>>>(p);
     return cudaGetLastError();
 }
 
-cudaError_t launch_gather(const LaunchParams& p, dim3 grid, cudaStream_t stream) {
-    gather_kernel<<<grid, 256, 0, stream>>>(p);
+cudaError_t launch_gather(const LaunchParams& p, dim3 grid, int pixels_per_thread, cudaStream_t stream) {
+    if (pixels_per_thread == 1) gather_kernel<1><<<grid, 256, 0, stream>>>(p);
+    else gather_kernel<4><<<grid, 256, 0, stream>>>(p);
     return cudaGetLastError();
 }
 

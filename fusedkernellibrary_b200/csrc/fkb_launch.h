@@ -18,18 +18,23 @@ constexpr uint32_t kOutSlotBytes = kOutRowBytes + 16;  // the 16 spare bytes tak
 constexpr uint32_t kSliceBytes = kSliceHeader + 4 * kInRowBytes + 2 * kOutSlotBytes;
 constexpr uint32_t kStagedSmemBytes = kStagedWarps * kSliceBytes;
 constexpr uint32_t kMaxRowsPerItem = 32;
-// lut_kernel: a CTA-wide table (3 channels x 256 entries x kLutCopies bank-spread copies of one 32-bit word) followed by
-// one slice per warp (two mbarriers, two source and two output row segments of 512 uchar3 pixels).  72 KB per CTA: three
-// CTAs per SM.
-constexpr uint32_t kLutCopies = 8;
-constexpr uint32_t kLutBytes = 3 * 256 * kLutCopies * 4;
+// lut_kernel: a CTA-wide table of 256 entries x 32 copies of one 32-bit word {T0[i], T1[i], T2[i], 0} (copy l belongs to
+// lane l and sits in bank l, so a table read never has a bank conflict), followed by one slice per warp (four mbarriers, four
+// source and two output row segments of 512 uchar3 pixels; three segments are kept in flight ahead of the one being
+// computed).  8 warps, 104 KB per CTA: two CTAs per SM.
+constexpr uint32_t kLutThreads = 256;
+constexpr uint32_t kLutWarps = kLutThreads / 32;
+constexpr uint32_t kLutBytes = 256 * 32 * 4;
 constexpr uint32_t kLutSegBytes = 1536;
-constexpr uint32_t kLutSliceBytes = 32 + 4 * kLutSegBytes;
-constexpr uint32_t kLutSmemBytes = kLutBytes + kStagedWarps * kLutSliceBytes;  // upper bound of the output rows a warp processes per item
+constexpr uint32_t kLutInStages = 4;
+constexpr uint32_t kLutSliceBytes = 64 + (kLutInStages + 2) * kLutSegBytes;
+constexpr uint32_t kLutSmemBytes = kLutBytes + kLutWarps * kLutSliceBytes;
+
+constexpr uint64_t kTinyLaunchPixels = 100000;  // launches below this many output pixels take the general kernel
 
 cudaError_t launch_staged(const LaunchParams& p, uint32_t grid, cudaStream_t stream);
 cudaError_t launch_lut(const LaunchParams& p, uint32_t grid, cudaStream_t stream);
-cudaError_t launch_gather(const LaunchParams& p, dim3 grid, cudaStream_t stream);
+cudaError_t launch_gather(const LaunchParams& p, dim3 grid, int pixels_per_thread, cudaStream_t stream);
 cudaError_t status_word_address(int** out);
 
 }  // namespace fkb

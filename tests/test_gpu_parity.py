@@ -28,9 +28,15 @@ def _needs_gpu():
     assert os.path.exists(abi.LIB_PATH), "libfkb.so missing: the CUDA path cannot run (no fallback exists)"
 
 
-def gpu_run(wl, use_plan=False, force_gather=False, fill=FILL):
+def gpu_run(wl, use_plan=False, force_gather=False, fill=FILL, tiny_route=False):
+    """tiny_route=False switches off the routing of very small launches to the general kernel, so that small test
+    cases still exercise the pipelined kernels; test_tiny_launch_routing covers the default behaviour."""
     from fusedkernellibrary_b200 import runtime
     os.environ["FKB_FORCE_GATHER"] = "1" if force_gather else "0"
+    if tiny_route:
+        os.environ.pop("FKB_TINY_PIXELS", None)
+    else:
+        os.environ["FKB_TINY_PIXELS"] = "0"
     try:
         dw = runtime.DeviceWorkload(wl, poison=fill)
         try:
@@ -40,6 +46,7 @@ def gpu_run(wl, use_plan=False, force_gather=False, fill=FILL):
             dw.close()
     finally:
         os.environ["FKB_FORCE_GATHER"] = "0"
+        os.environ.pop("FKB_TINY_PIXELS", None)
 
 
 def assert_same(wl, got, want):
@@ -91,6 +98,13 @@ def test_random_launches(seed):
     check(wl)
     if seed % 4 == 0:
         check(wl, force_gather=True)
+
+
+def test_tiny_launch_routing():
+    # default behaviour: launches of fewer than 100 000 output pixels run through the general kernel
+    for wl in [W.readme_crops(), W.vertical_fusion(w=200, h=100), W.divergent_planes(n_per_seq=1, w=128, h=72)]:
+        check(wl, tiny_route=True)
+        check(wl, tiny_route=True, use_plan=True)
 
 
 def test_edge_shapes():

@@ -29,9 +29,11 @@ METRIC = "fused-pipeline output Gpix/s"
 UNIT = "Gpix/s"
 N_FRAMES, CROPS_PER_FRAME = 64, 32
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one staged_kernel launch on this workload (ncu capture summarised
-# in profiles/); None until a capture exists
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one staged_kernel launch on this workload, from the ncu capture of the
+# 8-frame case (28.46 MB read + 95.10 MB written for 256 planes; profiles/staged_kernel_batched_crop_resize.md) scaled by
+# planes to the 64-frame launch.  A lower bound: in the small case a third of the output is still in the write-back L2
+# when the kernel ends, at full size all 1.233 GB of output reach DRAM.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = int((28.460032e6 + 95.097600e6) * 8)
 
 
 def make_workload(rank: int, n_frames: int = N_FRAMES, frame_w: int = 1920, frame_h: int = 1080):
@@ -303,11 +305,40 @@ def our_arm(args) -> None:
     h_out = torch.empty(wl.out_sizes[0], dtype=torch.uint8).pin_memory()
     lib = abi.load()
 
+    # The step is pipelined by groups of frames on three streams, as a user feeding a camera batch would: upload the
+    # frames of group g, launch the fused kernel over that group's planes (fkb_launch_transform with host descriptors),
+    # download its planes of the tensor.  PCIe runs in both directions at once; every byte still crosses it every step.
+    group = 4  # frames per group
+    n_groups = (len(h_src) + group - 1) // group
+    planes_per_frame = dw.n_planes // len(h_src)
+    plane_bytes = wl.out_sizes[0] // dw.n_planes
+    s_up, s_run, s_down = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+    sub_planes = []
+    for g in range(n_groups):
+        lo, hi = g * group * planes_per_frame, min((g + 1) * group, len(h_src)) * planes_per_frame
+        arr = (abi.PlaneDesc * (hi - lo))()
+        for i in range(hi - lo):
+            arr[i] = dw.planes[lo + i]
+        sub_planes.append((lo, hi, arr))
+
     def e2e_step():
-        for d, h in zip(dw.src, h_src):
-            d.copy_(h, non_blocking=True)
-        abi.check(lib.fkb_launch_transform(dw.chains, dw.planes, dw.n_planes, runtime.current_stream_ptr()))
-        h_out.copy_(dw.out[0], non_blocking=True)
+        cur = torch.cuda.current_stream()
+        for st in (s_up, s_run, s_down):
+            st.wait_stream(cur)
+        for g, (lo, hi, arr) in enumerate(sub_planes):
+            with torch.cuda.stream(s_up):
+                for f in range(g * group, min((g + 1) * group, len(h_src))):
+                    dw.src[f].copy_(h_src[f], non_blocking=True)
+                up = s_up.record_event()
+            with torch.cuda.stream(s_run):
+                s_run.wait_event(up)
+                abi.check(lib.fkb_launch_transform(dw.chains, arr, hi - lo, s_run.cuda_stream))
+                ran = s_run.record_event()
+            with torch.cuda.stream(s_down):
+                s_down.wait_event(ran)
+                h_out[lo * plane_bytes: hi * plane_bytes].copy_(dw.out[0][lo * plane_bytes: hi * plane_bytes], non_blocking=True)
+        for st in (s_up, s_run, s_down):
+            cur.wait_stream(st)
 
     e2e_steps = max(2, min(args.steps, 10))
     for _ in range(2):
@@ -332,7 +363,8 @@ def our_arm(args) -> None:
                      "algorithmic_bytes_per_launch": alg["total"], "frac_of_nominal_8TBs": achieved / 8000.0},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_dt / e2e_steps * 1e3, "steps": e2e_steps,
-                "path": "pinned host frames -> device, fkb_launch_transform (host descriptors), float3 tensor -> pinned host"},
+                "path": "per group of 4 frames on three streams: pinned host frames -> device, fkb_launch_transform (host "
+                        "descriptors) over the group's planes, its planes of the float3 tensor -> pinned host"},
         "gpu_launches": args.steps * kernels_per_step,
         "clocks": clocks,
     }

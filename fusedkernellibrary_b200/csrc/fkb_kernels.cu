@@ -175,9 +175,18 @@ __device__ __forceinline__ WarpSlice warp_slice(uint32_t base) {
 static_assert(48 + sizeof(PlaneRec) <= kSliceHeader, "slice header");
 static_assert(kSliceHeader + 4 * kInRowBytes + 2 * kOutSlotBytes == kSliceBytes, "slice layout");
 
+// Plane of staged tile t (warp-uniform t; called by all lanes of a warp).
 __device__ __forceinline__ uint32_t tile_to_plane(const LaunchParams& p, uint32_t t, uint32_t& local) {
     if (p.tiles_per_plane) { const uint32_t z = t / p.tiles_per_plane; local = t - z * p.tiles_per_plane; return z; }
     const PlaneRec* table = plane_table(p);
+    if (p.n_planes <= 32) {
+        // lane i looks at plane i; first tiles never decrease, so the planes starting at or before t form a prefix
+        const uint32_t lane = threadIdx.x & 31;
+        const uint32_t base = lane < p.n_planes ? table[lane].tile_base : 0xffffffffu;
+        const uint32_t z = __popc(__ballot_sync(0xffffffffu, base <= t)) - 1u;
+        local = t - __shfl_sync(0xffffffffu, base, z);
+        return z;
+    }
     uint32_t lo = 0, hi = p.n_planes;  // the last plane whose first tile is <= t (planes without tiles are skipped over)
     while (hi - lo > 1) {
         const uint32_t mid = (lo + hi) >> 1;
@@ -541,15 +550,26 @@ __global__ void __launch_bounds__(kStagedThreads, 2) staged_kernel(const __grid_
     const PlaneRec* table = plane_table(p);
     uint32_t k = 0, k4 = 0;  // steps done so far by RESIZE items (two stages) and by POINT items (four stages)
     bool ok = true;
+    // The plane record of the next item is fetched (12 lanes x 16 bytes, into registers) while the current item is
+    // processed, so its global-memory latency is off the critical path.
+    constexpr uint32_t kRecLanes = sizeof(PlaneRec) / 16;
+    uint32_t local = 0;
+    uint4 rec = make_uint4(0, 0, 0, 0);
+    if (first < p.n_tiles) {
+        const uint32_t z = tile_to_plane(p, first, local);
+        if (lane < kRecLanes) rec = reinterpret_cast<const uint4*>(table + z)[lane];
+    }
     for (uint32_t item = first; item < p.n_tiles && ok; item += stride) {
-        uint32_t local;
-        const uint32_t z = tile_to_plane(p, item, local);
         __syncwarp();
-        if (lane < sizeof(PlaneRec) / 16)
-            reinterpret_cast<uint4*>(smem_raw + w.base + 48)[lane] = reinterpret_cast<const uint4*>(table + z)[lane];
+        if (lane < kRecLanes) reinterpret_cast<uint4*>(smem_raw + w.base + 48)[lane] = rec;
         __syncwarp();
+        const uint32_t cur_local = local;
+        if (item + stride < p.n_tiles) {
+            const uint32_t z = tile_to_plane(p, item + stride, local);
+            if (lane < kRecLanes) rec = reinterpret_cast<const uint4*>(table + z)[lane];
+        }
         const PlaneRec& pl = *w.pl;
-        const uint32_t tyi = local / pl.tiles_x, txi = local - tyi * pl.tiles_x;
+        const uint32_t tyi = cur_local / pl.tiles_x, txi = cur_local - tyi * pl.tiles_x;
         const uint32_t ox = txi * pl.tile_w, oy0 = tyi * pl.tile_h;
         const uint32_t ow = min(pl.tile_w, pl.dst_w - ox), nr = min(pl.tile_h, pl.dst_h - oy0);
         const bool f32 = p.chains[pl.chain].dst_format == FKB_PIX_F32C3;

@@ -236,7 +236,26 @@ def other_configs(torch, steps: int, peak: float) -> dict:
         rounds = max(3, steps // n_sets)
         graph.replay()
         dt = time_launches(graph.replay, rounds, torch) / (rounds * n_sets)
-        out[name] = {"us_per_launch": dt * 1e6, "gpix_s": wl.out_pixels / dt / 1e9, "alg_bytes": alg["total"],
+        ref_us = None
+        try:
+            import oracle
+            if oracle.have_ref_cuda():
+                launchers = [oracle.ref_cuda_launcher(wl, [t.data_ptr() for t in s.src], [t.data_ptr() for t in s.out], side.cuda_stream) for s in sets]
+                if launchers[0] is not None:
+                    for fn in launchers:
+                        fn()
+                    torch.cuda.synchronize()
+                    ref_graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.stream(side):
+                        with torch.cuda.graph(ref_graph, stream=side):
+                            for fn in launchers:
+                                fn()
+                    ref_graph.replay()
+                    ref_us = time_launches(ref_graph.replay, rounds, torch) / (rounds * n_sets) * 1e6
+                    del ref_graph
+        except Exception as exc:  # the comparison is optional; the product's figures never depend on it
+            ref_us = f"failed: {exc}"
+        out[name] = {"us_per_launch": dt * 1e6, "reference_cuda_us_per_launch": ref_us, "gpix_s": wl.out_pixels / dt / 1e9, "alg_bytes": alg["total"],
                      "hbm_gbs": alg["total"] / dt / 1e9, "frac_of_measured_peak": alg["total"] / dt / 1e9 / peak,
                      "buffer_sets_rotated": n_sets, "kernels_per_launch": sets[0].kernel_launches(),
                      "timing": "CUDA graph of one round over the buffer sets, replayed"}
@@ -246,6 +265,29 @@ def other_configs(torch, steps: int, peak: float) -> dict:
         del sets
         torch.cuda.empty_cache()
     return out
+
+
+def reference_cuda_main(torch, wl, dw, steps: int, our_ms: float) -> dict:
+    """The reference library's own CUDA backend (its generic templated kernel compiled for sm_100a, oracle/_ref) on the
+    same resident buffers: a comparison figure beside the product's, not part of the product's path.  Its output is
+    compared with ours (the reference contracts to FMA, so the last bit may differ; tolerance 1e-5 relative)."""
+    import oracle
+    if not oracle.have_ref_cuda():
+        return {"unavailable": "oracle/_ref/libfkl_ref_cuda.so was not built (reference headers or nvcc absent at build time)"}
+    from fusedkernellibrary_b200 import runtime
+    ours = dw.out[0].view(torch.float32).clone()
+    launch = oracle.ref_cuda_launcher(wl, [t.data_ptr() for t in dw.src], [t.data_ptr() for t in dw.out], runtime.current_stream_ptr())
+    kernels = launch()
+    torch.cuda.synchronize()
+    theirs = dw.out[0].view(torch.float32)
+    rel = ((theirs - ours).abs() / ours.abs().clamp_min(1e-30)).max().item()
+    for _ in range(2):
+        launch()
+    dt = time_launches(launch, steps, torch) / steps
+    del ours
+    return {"ms_per_step": dt * 1e3, "value": wl.out_pixels / dt / 1e9, "unit": UNIT, "kernel_launches_per_step": kernels,
+            "max_rel_diff_vs_ours": rel, "speedup_of_ours": dt * 1e3 / our_ms,
+            "note": "reference templated kernel, nvcc 12.9 sm_100a, 256 planes per launch (kernel-parameter limit)"}
 
 
 def our_arm(args) -> None:
@@ -376,6 +418,7 @@ def our_arm(args) -> None:
             line["cpu_baseline"] = {"value": px / best / 1e9, "unit": UNIT, "cores": threads, "kind": kind,
                                     "sample": f"{sample_frames} of the 64 frames ({sample_frames * CROPS_PER_FRAME} planes), best of 3, "
                                               f"planes spread over {threads} host threads as independent single-threaded reference calls"}
+        line["reference_cuda_backend"] = reference_cuda_main(torch, wl, dw, max(5, min(args.steps, 20)), ms_per_step)
         if not args.no_other_configs:
             dw.close()
             del dw

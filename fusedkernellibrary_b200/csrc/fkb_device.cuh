@@ -14,7 +14,7 @@
 
 namespace fkb {
 
-enum : uint32_t { KCLASS_GATHER = 0, KCLASS_POINT = 1, KCLASS_RESIZE = 2, KCLASS_LUT = 3 };
+enum : uint32_t { KCLASS_GATHER = 0, KCLASS_POINT = 1, KCLASS_RESIZE = 2, KCLASS_LUT = 3, KCLASS_NV12 = 4 };
 
 // One output plane as the kernels see it: the caller's fkb_plane_desc plus what the host lowering derived
 // (which kernel path runs it, its tile shape and its first tile index).
@@ -46,6 +46,22 @@ static_assert(sizeof(PlaneRec) % 16 == 0, "PlaneRec is copied in 16-byte words")
 
 constexpr uint32_t kInlinePlanes = 8;  // launches of up to this many planes carry their records in the kernel parameters
 
+// Operands of a chain's specialised post-ops [Mul][Add|Sub][Div], resolved on the host when none of them is a per-plane
+// operand (slots = 0); x - s is stored as x + (-s).
+struct PostImm {
+    float m[3], a[3], d[3];
+    uint32_t slots;  // non-zero: some operand lives in the plane record, read it there instead
+};
+
+// Everything nv12_kernel needs to know about its chain, flattened so that every read has a fixed parameter offset.
+struct Nv12Consts {
+    float ccm[9], sub[3];
+    float m[3], a[3], d[3];  // post-op operands (Mul, Add or negated Sub, Div)
+    uint32_t kind;           // post-op shape bits
+    uint32_t chain;          // the one chain whose planes take nv12_kernel
+    uint32_t preserve_ar, f32, split, slots;
+};
+
 struct LaunchParams {
     fkb_chain_desc chains[FKB_MAX_CHAINS];
     const PlaneRec* table;    // device table, or null when `inline_planes` is used
@@ -55,10 +71,14 @@ struct LaunchParams {
     int* status;
     uint32_t n_lut_units;     // work units of lut_kernel (a block of rows of one LUT plane)
     uint32_t lut_swap;        // bit c: chain c contains an odd number of channel reorders
-    uint32_t post_kind[FKB_MAX_CHAINS];  // per chain: bit mask of {Mul, Add|Sub, SaturateCast} when its post-ops have that shape, else 8
+    uint32_t post_kind[FKB_MAX_CHAINS];
+    PostImm post_imm[FKB_MAX_CHAINS];
+    Nv12Consts nv12;  // per chain: bit mask of {Mul, Add|Sub, SaturateCast} when its post-ops have that shape, else 8
     float neg_zero;           // -0.0f, deliberately opaque to the compiler (see mul2_unfusable)
     PlaneRec inline_planes[kInlinePlanes];
 };
+
+static_assert(sizeof(LaunchParams) <= 8192, "kernel parameters (CUDA 12.1+ allows up to 32 764 bytes on sm_70 and later)");
 
 // ---------------------------------------------------------------------------------------------------------
 // shared-memory / mbarrier / bulk-copy wrappers

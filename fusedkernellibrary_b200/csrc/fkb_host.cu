@@ -139,12 +139,20 @@ uint64_t tiny_launch_pixels() {
     return e && e[0] ? std::strtoull(e, nullptr, 10) : kTinyLaunchPixels;
 }
 
+uint32_t post_kind_of(const fkb_chain_desc& ch);
+
 // Chooses the kernel path and tile shape of one plane.
 void classify(const fkb_chain_desc& ch, PlaneRec& r) {
     r.kclass = KCLASS_GATHER;
     r.tile_w = r.tile_h = r.tiles_x = r.tiles_y = 0;
     r.in_stride = r.out_stride = 0;
     if (force_gather()) return;
+    if (ch.src_format == FKB_PIX_NV12 && ch.geometry != FKB_GEOM_NONE && ch.n_pre_ops == 1 && ch.ops[0].code == FKB_OP_YUV2RGB &&
+        post_kind_of(ch) != 8u && !(ch.geometry == FKB_GEOM_RESIZE_PRESERVE_AR && (r.x2 < r.x1 || r.y2 < r.y1)) &&
+        (reinterpret_cast<uintptr_t>(r.src_chroma) & 1) == 0 && (r.src_pitch & 1) == 0) {  // UV pairs are read as 16-bit words
+        r.kclass = KCLASS_NV12;  // NV12 -> RGB on the taps -> resize -> [Mul][Add|Sub][Div][SaturateCast]: nv12_kernel
+        return;
+    }
     if (ch.src_format != FKB_PIX_U8C3 || ch.write_kind != FKB_WRITE_PACKED) return;
     if (!aligned16(r.src) || !aligned16(r.dst) || (r.src_pitch & 15) || (r.dst_pitch & 15)) return;
     const bool f32 = ch.dst_format == FKB_PIX_F32C3;
@@ -193,14 +201,34 @@ uint32_t rows_per_item(uint64_t row_segments, uint32_t resident_warps) {
 }
 
 // Shape of the ops that follow the read / the interpolation: bit 0 Mul, bit 1 Add or Sub, bit 2 SaturateCast when the
-// chain is [Cast]* [Mul] [Add|Sub] [SaturateCast] in this order (the kernels specialise those), else 8 (interpreted).
+// chain is [Cast]* [Mul] [Add|Sub] [Div] [SaturateCast] in this order (bit 4 = Div; the kernels specialise those shapes),
+// else 8 (interpreted).
 uint32_t post_kind_of(const fkb_chain_desc& ch) {
     uint32_t i = ch.geometry == FKB_GEOM_NONE ? 0 : ch.n_pre_ops, kind = 0;
     while (i < ch.n_ops && ch.ops[i].code == FKB_OP_CAST_F32) ++i;
     if (i < ch.n_ops && ch.ops[i].code == FKB_OP_MUL) { kind |= 1; ++i; }
     if (i < ch.n_ops && (ch.ops[i].code == FKB_OP_ADD || ch.ops[i].code == FKB_OP_SUB)) { kind |= 2; ++i; }
+    if (i < ch.n_ops && ch.ops[i].code == FKB_OP_DIV) { kind |= 16; ++i; }  // only nv12_kernel specialises this part
     if (i < ch.n_ops && ch.ops[i].code == FKB_OP_SATCAST_U8) { kind |= 4; ++i; }
     return i == ch.n_ops ? kind : 8u;
+}
+
+// Immediate operands of a chain's [Mul][Add|Sub][Div] post-ops (see PostImm).
+PostImm post_imm_of(const fkb_chain_desc& ch) {
+    PostImm q{};
+    for (int c = 0; c < 3; ++c) { q.m[c] = 1.f; q.a[c] = 0.f; q.d[c] = 1.f; }
+    for (uint32_t i = ch.geometry == FKB_GEOM_NONE ? 0 : ch.n_pre_ops; i < ch.n_ops; ++i) {
+        const fkb_op& op = ch.ops[i];
+        if (op.code != FKB_OP_MUL && op.code != FKB_OP_ADD && op.code != FKB_OP_SUB && op.code != FKB_OP_DIV) continue;
+        if (op.plane_slot >= 0) q.slots = 1;
+        for (int c = 0; c < 3; ++c) {
+            if (op.code == FKB_OP_MUL) q.m[c] = op.v[c];
+            if (op.code == FKB_OP_ADD) q.a[c] = op.v[c];
+            if (op.code == FKB_OP_SUB) q.a[c] = -op.v[c];
+            if (op.code == FKB_OP_DIV) q.d[c] = op.v[c];
+        }
+    }
+    return q;
 }
 
 struct Lowered {
@@ -209,6 +237,7 @@ struct Lowered {
     uint32_t staged_grid = 0;
     uint32_t lut_grid = 0;
     dim3 gather_grid{0, 0, 0};
+    dim3 nv12_grid{0, 0, 0};
     int gather_ppt = 4;
     uint32_t kernels = 0;
 };
@@ -252,6 +281,7 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         if (e != FKB_OK) return e;
     }
     uint64_t row_segments = 0, lut_rows = 0, total_pixels = 0, gather_pixels = 0;
+    uint32_t n_nv12 = 0, nw = 0, nh = 0, nv12_chain = 0xffffffffu;
     uint32_t lut_min_tiles_x = 0xffffffffu;
     for (uint32_t z = 0; z < n_planes; ++z) {
         const fkb_plane_desc& s = planes[z];
@@ -274,12 +304,18 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
     // A launch of a few ten thousand pixels is pure latency: the pipelined paths would spend it filling their stages,
     // so it goes through the general kernel, one pixel per thread.
     if (total_pixels < tiny_launch_pixels())
-        for (uint32_t z = 0; z < n_planes; ++z) { L.recs[z].kclass = KCLASS_GATHER; L.recs[z].tiles_x = 0; }
+        for (uint32_t z = 0; z < n_planes; ++z)
+            if (L.recs[z].kclass != KCLASS_NV12) { L.recs[z].kclass = KCLASS_GATHER; L.recs[z].tiles_x = 0; }
     for (uint32_t z = 0; z < n_planes; ++z) {
         const PlaneRec& r = L.recs[z];
         if (r.kclass == KCLASS_POINT || r.kclass == KCLASS_RESIZE) row_segments += static_cast<uint64_t>(r.tiles_x) * r.dst_h;
         if (r.kclass == KCLASS_LUT) { lut_rows += r.dst_h; lut_min_tiles_x = std::min(lut_min_tiles_x, r.tiles_x); }
         if (r.kclass == KCLASS_GATHER) gather_pixels += static_cast<uint64_t>(r.dst_w) * r.dst_h;
+        if (r.kclass == KCLASS_NV12) {
+            if (nv12_chain == 0xffffffffu) nv12_chain = r.chain;
+            if (r.chain == nv12_chain) { ++n_nv12; nw = std::max(nw, r.dst_w); nh = std::max(nh, r.dst_h); }
+            else { L.recs[z].kclass = KCLASS_GATHER; gather_pixels += static_cast<uint64_t>(r.dst_w) * r.dst_h; }
+        }
     }
     // LUT units: a block of rows of one plane per CTA visit; about one unit per resident CTA, at least eight row segments
     const uint32_t lut_rpu = lut_rows ? std::max<uint32_t>(static_cast<uint32_t>((lut_rows + 2ull * sms - 1) / (2ull * sms)),
@@ -308,6 +344,7 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
     L.lp.neg_zero = -0.0f;
     for (uint32_t c = 0; c < n_chains; ++c) {
         L.lp.post_kind[c] = post_kind_of(chains[c]);
+        L.lp.post_imm[c] = post_imm_of(chains[c]);
         uint32_t reorders = 0;
         for (uint32_t i = 0; i < chains[c].n_ops; ++i) reorders += chains[c].ops[i].code == FKB_OP_REORDER_ZYX;
         L.lp.lut_swap |= (reorders & 1u) << c;
@@ -323,6 +360,20 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         L.lut_grid = std::min<uint32_t>(n_lut_units, 2u * static_cast<uint32_t>(sms));
         ++L.kernels;
     }
+    if (n_nv12) {
+        // nv12_kernel is specialised on one chain; planes of any other NV12 chain of the launch take the general kernel
+        const uint32_t c = nv12_chain;
+        const fkb_chain_desc& ch = chains[c];
+        Nv12Consts& k = L.lp.nv12;
+        std::memcpy(k.ccm, ch.ccm, sizeof(k.ccm));
+        std::memcpy(k.sub, ch.yuv_sub, sizeof(k.sub));
+        const PostImm imm = post_imm_of(ch);
+        std::memcpy(k.m, imm.m, sizeof(k.m)); std::memcpy(k.a, imm.a, sizeof(k.a)); std::memcpy(k.d, imm.d, sizeof(k.d));
+        k.kind = post_kind_of(ch); k.chain = c; k.slots = imm.slots;
+        k.preserve_ar = ch.geometry == FKB_GEOM_RESIZE_PRESERVE_AR; k.f32 = ch.dst_format == FKB_PIX_F32C3; k.split = ch.write_kind == FKB_WRITE_SPLIT;
+        L.nv12_grid = dim3((nw + 31) / 32, (nh + 7) / 8, std::min<uint32_t>(n_planes, 65535u));
+        ++L.kernels;
+    }
     if (n_gather) {
         // small launches are latency-bound: one pixel per thread puts four times as many threads on the taps
         L.gather_ppt = gather_pixels < (2u << 20) ? 1 : 4;
@@ -335,6 +386,7 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
 int run(const Lowered& L, const LaunchParams& lp, cudaStream_t stream) {
     if (L.staged_grid) FKB_CUDA(launch_staged(lp, L.staged_grid, stream));
     if (L.lut_grid) FKB_CUDA(launch_lut(lp, L.lut_grid, stream));
+    if (L.nv12_grid.x) FKB_CUDA(launch_nv12(lp, L.nv12_grid, stream));
     if (L.gather_grid.x) FKB_CUDA(launch_gather(lp, L.gather_grid, L.gather_ppt, stream));
     return FKB_OK;
 }
@@ -463,6 +515,7 @@ int lower_fixed(const fkb_chain_desc* chain, const fkb_plane_desc* planes, uint3
         r.chain = 0;
         std::memcpy(r.params, s.params, sizeof(r.params));
         classify(*chain, r);
+        if (r.kclass == KCLASS_NV12) r.kclass = KCLASS_GATHER;  // this entry point keeps to the three general-purpose kernels
         if (r.kclass == KCLASS_POINT || r.kclass == KCLASS_RESIZE) row_segments += static_cast<uint64_t>(r.tiles_x) * r.dst_h;
         if (r.kclass == KCLASS_LUT) { lut_rows += r.dst_h; lut_min_tiles_x = std::min(lut_min_tiles_x, r.tiles_x); }
     }
@@ -492,6 +545,7 @@ int lower_fixed(const fkb_chain_desc* chain, const fkb_plane_desc* planes, uint3
     lp.n_planes = n_planes;
     lp.neg_zero = -0.0f;
     lp.post_kind[0] = post_kind_of(*chain);
+    lp.post_imm[0] = post_imm_of(*chain);
     uint32_t reorders = 0;
     for (uint32_t i = 0; i < chain->n_ops; ++i) reorders += chain->ops[i].code == FKB_OP_REORDER_ZYX;
     lp.lut_swap = reorders & 1u;

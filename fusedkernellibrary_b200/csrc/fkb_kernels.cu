@@ -216,21 +216,22 @@ __device__ __forceinline__ void store_row(uint8_t* gdst, uint32_t srow, uint32_t
 // (each part optional, in this order) are specialised at compile time: KIND is a bit mask of the parts present and the
 // operands sit in registers for the whole item.  x - s is computed as x + (-s), which is the same IEEE operation.  Every
 // other chain runs through the op interpreter (KIND = kPostGeneric).
-constexpr int kPostMul = 1, kPostAdd = 2, kPostSat = 4, kPostGeneric = 8;
+constexpr int kPostMul = 1, kPostAdd = 2, kPostSat = 4, kPostGeneric = 8, kPostDiv = 16;  // Div: nv12_kernel only
 
 struct PostParams {
-    float m[3], a[3];
+    float m[3], a[3], d[3];
 };
 __device__ __forceinline__ PostParams load_post(const fkb_chain_desc& ch, const PlaneRec& pl, uint32_t first) {
     PostParams q;
 #pragma unroll
-    for (int c = 0; c < 3; ++c) { q.m[c] = 1.f; q.a[c] = 0.f; }
+    for (int c = 0; c < 3; ++c) { q.m[c] = 1.f; q.a[c] = 0.f; q.d[c] = 1.f; }
     for (uint32_t i = first; i < ch.n_ops; ++i) {
         const fkb_op& op = ch.ops[i];
         const float* v = op.plane_slot >= 0 ? pl.params[op.plane_slot] : op.v;
         if (op.code == FKB_OP_MUL) { q.m[0] = v[0]; q.m[1] = v[1]; q.m[2] = v[2]; }
         else if (op.code == FKB_OP_ADD) { q.a[0] = v[0]; q.a[1] = v[1]; q.a[2] = v[2]; }
         else if (op.code == FKB_OP_SUB) { q.a[0] = -v[0]; q.a[1] = -v[1]; q.a[2] = -v[2]; }
+        else if (op.code == FKB_OP_DIV) { q.d[0] = v[0]; q.d[1] = v[1]; q.d[2] = v[2]; }
     }
     return q;
 }
@@ -596,6 +597,100 @@ __global__ void __launch_bounds__(kStagedThreads, 2) staged_kernel(const __grid_
 }
 
 // ---------------------------------------------------------------------------------------------------------
+// nv12_kernel: NV12 -> RGB on the taps -> bilinear resize -> [Mul][Add|Sub][Div][SaturateCast] -> any write
+// ---------------------------------------------------------------------------------------------------------
+// The DNN-preprocessing shape.  Such launches are small and decimate heavily (a 4K frame to 640x640 moves 8 MB), so they
+// are bound by latency, not bandwidth: one thread per output pixel, all twelve tap bytes requested before any is used,
+// the colour matrix and the chain's operands held in registers, no interpretation.  The conversion runs on each tap
+// before the interpolation, which is what the reference computes when ConvertYUVToRGB is fused into the Read under the
+// Resize (algorithms/image_processing/color_conversion.h:150-174, interpolation.h:70-104).
+__device__ __forceinline__ void nv12_pixel(const LaunchParams& p, const PlaneRec& pl, uint32_t x, uint32_t y) {
+    if (pl.kclass != KCLASS_NV12) return;
+    if (x >= pl.dst_w || y >= pl.dst_h) return;
+    const Nv12Consts& k = p.nv12;
+    const bool par = k.preserve_ar != 0;
+    const bool inside = !par || (static_cast<int>(x) >= pl.x1 && static_cast<int>(x) <= pl.x2 &&
+                                 static_cast<int>(y) >= pl.y1 && static_cast<int>(y) <= pl.y2);
+    float v[3] = {pl.bg[0], pl.bg[1], pl.bg[2]};
+    if (inside) {
+        const AxisTap ax = axis_tap(static_cast<int>(x) - (par ? pl.x1 : 0), pl.fx, pl.crop_w);
+        const AxisTap ay = axis_tap(static_cast<int>(y) - (par ? pl.y1 : 0), pl.fy, pl.crop_h);
+        const uint32_t X0 = ax.i0 + pl.crop_x, X1 = ax.i1 + pl.crop_x, Y0 = ay.i0 + pl.crop_y, Y1 = ay.i1 + pl.crop_y;
+        const uint32_t pitch = pl.src_pitch;
+        const uint8_t* yr0 = pl.src + static_cast<size_t>(Y0 * pitch);
+        const uint8_t* yr1 = pl.src + static_cast<size_t>(Y1 * pitch);
+        const uint8_t* cr0 = pl.src_chroma + static_cast<size_t>((Y0 >> 1) * pitch);
+        const uint8_t* cr1 = pl.src_chroma + static_cast<size_t>((Y1 >> 1) * pitch);
+        const uint32_t u0 = X0 & ~1u, u1 = X1 & ~1u;
+        // all eight loads first (a UV pair is one aligned 16-bit word)
+        const uint32_t l00 = __ldg(yr0 + X0), l10 = __ldg(yr0 + X1), l01 = __ldg(yr1 + X0), l11 = __ldg(yr1 + X1);
+        const uint32_t c00 = __ldg(reinterpret_cast<const unsigned short*>(cr0 + u0)), c10 = __ldg(reinterpret_cast<const unsigned short*>(cr0 + u1));
+        const uint32_t c01 = __ldg(reinterpret_cast<const unsigned short*>(cr1 + u0)), c11 = __ldg(reinterpret_cast<const unsigned short*>(cr1 + u1));
+        const float w00 = __fmul_rn(ax.w0, ay.w0), w10 = __fmul_rn(ax.w1, ay.w0);
+        const float w01 = __fmul_rn(ax.w0, ay.w1), w11 = __fmul_rn(ax.w1, ay.w1);
+        const uint32_t lum[4] = {l00, l10, l01, l11}, chr[4] = {c00, c10, c01, c11};
+        const float w[4] = {w00, w10, w01, w11};
+        float acc[3];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            const float yy = static_cast<float>(lum[t]);
+            const float a = k.sub[0] != 0.f ? __fsub_rn(yy, k.sub[0]) : yy;  // x - 0 is x
+            const float b = __fsub_rn(static_cast<float>(chr[t] & 0xffu), k.sub[1]);
+            const float d = __fsub_rn(static_cast<float>(chr[t] >> 8), k.sub[2]);
+#pragma unroll
+            for (int c = 0; c < 3; ++c) {
+                const float rgb = __fadd_rn(__fadd_rn(__fmul_rn(a, k.ccm[3 * c]), __fmul_rn(b, k.ccm[3 * c + 1])), __fmul_rn(d, k.ccm[3 * c + 2]));
+                const float term = __fmul_rn(rgb, w[t]);
+                acc[c] = t == 0 ? term : __fadd_rn(acc[c], term);  // ((t0 + t1) + t2) + t3, the reference's order
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < 3; ++c) v[c] = acc[c];
+    }
+    float m[3], a[3], d[3];
+    if (k.slots) {
+        const PostParams q = load_post(p.chains[k.chain], pl, p.chains[k.chain].n_pre_ops);
+#pragma unroll
+        for (int c = 0; c < 3; ++c) { m[c] = q.m[c]; a[c] = q.a[c]; d[c] = q.d[c]; }
+    } else {
+#pragma unroll
+        for (int c = 0; c < 3; ++c) { m[c] = k.m[c]; a[c] = k.a[c]; d[c] = k.d[c]; }
+    }
+#pragma unroll
+    for (int c = 0; c < 3; ++c) {
+        if (k.kind & kPostMul) v[c] = __fmul_rn(v[c], m[c]);
+        if (k.kind & kPostAdd) v[c] = __fadd_rn(v[c], a[c]);
+        if (k.kind & kPostDiv) v[c] = __fdiv_rn(v[c], d[c]);
+        if (k.kind & kPostSat) v[c] = sat_u8_as_float(v[c]);
+    }
+    uint8_t* row = pl.dst + static_cast<size_t>(y * pl.dst_pitch);
+    if (k.split) {
+#pragma unroll
+        for (int c = 0; c < 3; ++c) {
+            uint8_t* q8 = row + static_cast<size_t>(c) * pl.dst_cstride;
+            if (k.f32) reinterpret_cast<float*>(q8)[x] = v[c]; else q8[x] = static_cast<uint8_t>(u8_of_exact(v[c]));
+        }
+    } else if (k.f32) {
+        float* f = reinterpret_cast<float*>(row) + static_cast<size_t>(x) * 3;
+        f[0] = v[0]; f[1] = v[1]; f[2] = v[2];
+    } else {
+        uint8_t* q8 = row + static_cast<size_t>(x) * 3;
+        q8[0] = static_cast<uint8_t>(u8_of_exact(v[0])); q8[1] = static_cast<uint8_t>(u8_of_exact(v[1])); q8[2] = static_cast<uint8_t>(u8_of_exact(v[2]));
+    }
+}
+
+__global__ void __launch_bounds__(256, 8) nv12_kernel(const __grid_constant__ LaunchParams p) {
+    const uint32_t x = blockIdx.x * 32 + (threadIdx.x & 31), y = blockIdx.y * 8 + (threadIdx.x >> 5);
+    // Two copies of the body so that each knows where its plane records live: in the kernel parameters (constant-bank
+    // reads, shared by all threads) for launches of a few planes, in the global table otherwise.
+    if (p.table == nullptr) {
+        for (uint32_t z = blockIdx.z; z < p.n_planes; z += gridDim.z) nv12_pixel(p, p.inline_planes[z], x, y);
+    } else {
+        for (uint32_t z = blockIdx.z; z < p.n_planes; z += gridDim.z) nv12_pixel(p, p.table[z], x, y);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
 // lut_kernel: uchar3 -> uchar3 chains without resampling
 // ---------------------------------------------------------------------------------------------------------
 // Every op of such a chain acts on one channel at a time (a channel reorder only renames channels), so output channel c
@@ -759,6 +854,11 @@ cudaError_t launch_lut(const LaunchParams& p, uint32_t grid, cudaStream_t stream
         configured_device = dev;
     }
     lut_kernel<<<grid, kLutThreads, kLutSmemBytes, stream>>>(p);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_nv12(const LaunchParams& p, dim3 grid, cudaStream_t stream) {
+    nv12_kernel<<<grid, 256, 0, stream>>>(p);
     return cudaGetLastError();
 }
 

@@ -34,6 +34,7 @@ constexpr uint64_t kTinyLaunchPixels = 100000;  // launches below this many outp
 
 cudaError_t launch_staged(const LaunchParams& p, uint32_t grid, cudaStream_t stream);
 cudaError_t launch_lut(const LaunchParams& p, uint32_t grid, cudaStream_t stream);
+cudaError_t launch_nv12(const LaunchParams& p, dim3 grid, cudaStream_t stream);
 cudaError_t launch_gather(const LaunchParams& p, dim3 grid, int pixels_per_thread, cudaStream_t stream);
 cudaError_t status_word_address(int** out);
 

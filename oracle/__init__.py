@@ -18,6 +18,7 @@ from fusedkernellibrary_b200 import abi
 HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(HERE, "liboracle.so")
 REF_SO = os.path.join(HERE, "_ref", "libfkl_ref.so")
+REF_CUDA_SO = os.path.join(HERE, "_ref", "libfkl_ref_cuda.so")
 
 _oracle = None
 _ref = None
@@ -70,6 +71,51 @@ def load_ref() -> C.CDLL:
             getattr(lib, name).restype = C.c_int
         _ref = lib
     return _ref
+
+
+_ref_cuda = None
+
+
+def have_ref_cuda() -> bool:
+    return os.path.exists(REF_CUDA_SO)
+
+
+def load_ref_cuda() -> C.CDLL:
+    """The reference's own CUDA backend compiled for sm_100a (oracle/ref_cuda_runner.cu); device pointers in, no timing inside."""
+    global _ref_cuda
+    if _ref_cuda is None:
+        lib = C.CDLL(REF_CUDA_SO)
+        f32p, i32p, pp = C.POINTER(C.c_float), C.POINTER(C.c_int32), C.POINTER(C.c_void_p)
+        lib.fklrefcuda_crop_resize_f32.restype = C.c_int
+        lib.fklrefcuda_crop_resize_f32.argtypes = [pp, C.c_int, C.c_int, C.c_int, i32p, C.c_int, C.c_int, C.c_int, f32p, f32p, C.c_void_p, C.c_void_p]
+        lib.fklrefcuda_pointwise_u8.restype = C.c_int
+        lib.fklrefcuda_pointwise_u8.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, f32p, f32p, f32p, C.c_void_p, C.c_int, C.c_void_p]
+        lib.fklrefcuda_nv12_resize_split.restype = C.c_int
+        lib.fklrefcuda_nv12_resize_split.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, f32p, f32p, C.c_void_p, C.c_void_p]
+        _ref_cuda = lib
+    return _ref_cuda
+
+
+def ref_cuda_launcher(wl, src_addrs, dst_addrs, stream_ptr):
+    """Returns a zero-argument function that launches workload `wl` (device buffers at the given addresses) once through
+    the reference CUDA backend on the given stream, or None when the workload has no reference CUDA runner."""
+    lib = load_ref_cuda()
+    p0, n, ch = wl.planes[0], len(wl.planes), wl.chains[0]
+    if wl.name == "batched_crop_resize" and n % 32 == 0:
+        frames = (C.c_void_p * n)(*[src_addrs[s.src] for s in wl.planes])
+        flat = [v for s in wl.planes for v in s.crop]
+        rects = (C.c_int32 * len(flat))(*flat)
+        bg, mul = _f3(p0.bg), _f3(ch.ops[0].v)
+        return lambda: lib.fklrefcuda_crop_resize_f32(frames, p0.src_w, p0.src_h, p0.src_pitch, rects, n, p0.dst_w, p0.dst_h, bg, mul,
+                                                      dst_addrs[0], stream_ptr)
+    if wl.name == "vertical_fusion":
+        a, b, c = _f3(ch.ops[1].v), _f3(ch.ops[2].v), _f3(ch.ops[3].v)
+        return lambda: lib.fklrefcuda_pointwise_u8(src_addrs[0], p0.src_w, p0.src_h, p0.src_pitch, a, b, c, dst_addrs[0], p0.dst_pitch, stream_ptr)
+    if wl.name == "nv12_preprocess":
+        a, b = _f3(ch.ops[1].v), _f3(ch.ops[2].v)
+        return lambda: lib.fklrefcuda_nv12_resize_split(src_addrs[0], p0.src_w, p0.src_h, p0.src_pitch, p0.dst_w, p0.dst_h, a, b,
+                                                        dst_addrs[0], stream_ptr)
+    return None
 
 
 def _f3(v):

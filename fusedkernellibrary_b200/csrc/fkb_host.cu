@@ -371,7 +371,25 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         std::memcpy(k.m, imm.m, sizeof(k.m)); std::memcpy(k.a, imm.a, sizeof(k.a)); std::memcpy(k.d, imm.d, sizeof(k.d));
         k.kind = post_kind_of(ch); k.chain = c; k.slots = imm.slots;
         k.preserve_ar = ch.geometry == FKB_GEOM_RESIZE_PRESERVE_AR; k.f32 = ch.dst_format == FKB_PIX_F32C3; k.split = ch.write_kind == FKB_WRITE_SPLIT;
-        L.nv12_grid = dim3((nw + 31) / 32, (nh + 7) / 8, std::min<uint32_t>(n_planes, 65535u));
+        // nv12_pair_kernel's conditions: the colour matrix of the YCbCr standards ([1 0 r; 1 g1 g2; 1 b 0]), integer
+        // offsets, immediate operands, and plane offsets that fit 32 bits
+        bool pair = !imm.slots && k.ccm[0] == 1.f && k.ccm[3] == 1.f && k.ccm[6] == 1.f && k.ccm[1] == 0.f && k.ccm[8] == 0.f;
+        for (int i = 0; i < 3; ++i) {
+            pair = pair && k.sub[i] >= 0.f && k.sub[i] <= 255.f && k.sub[i] == std::floor(k.sub[i]);
+            k.kmag[i] = 8388608.f + (pair ? k.sub[i] : 0.f);
+        }
+        for (int i : {2, 4, 5, 7}) pair = pair && std::isfinite(k.ccm[i]);
+        bool wide = true;
+        for (uint32_t z = 0; z < n_planes && pair; ++z) {
+            const PlaneRec& r = L.recs[z];
+            if (r.kclass != KCLASS_NV12) continue;
+            const uint64_t src_end = static_cast<uint64_t>(r.src_pitch) * (static_cast<uint64_t>(r.crop_y) + r.crop_h) + r.crop_x + r.crop_w;
+            const uint64_t dst_end = static_cast<uint64_t>(r.dst_pitch) * r.dst_h;
+            pair = src_end < (1ull << 31) && dst_end < (1ull << 31);
+            wide = wide && (reinterpret_cast<uintptr_t>(r.dst) & 7) == 0 && (r.dst_pitch & 7) == 0 && (r.dst_cstride & 7) == 0;
+        }
+        k.pair = pair; k.wide_store = wide;
+        L.nv12_grid = dim3((nw + (pair ? 63 : 31)) / (pair ? 64 : 32), (nh + 7) / 8, std::min<uint32_t>(n_planes, 65535u));
         ++L.kernels;
     }
     if (n_gather) {
@@ -660,6 +678,14 @@ int fkb_plan_create(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_p
     int rc = lower(chains, n_chains, planes, n_planes, plan->L);
     if (rc != FKB_OK) { delete plan; return rc; }
     cudaError_t e = cudaGetDevice(&plan->device);
+    if (n_planes <= kInlinePlanes) {
+        // a few planes travel in the kernel parameters, as in fkb_launch_transform: no table read before the first tap
+        if (e != cudaSuccess) { t_last_cuda_error = static_cast<int>(e); delete plan; return FKB_ERR_CUDA; }
+        std::memcpy(plan->L.lp.inline_planes, plan->L.recs.data(), sizeof(PlaneRec) * n_planes);
+        plan->L.lp.table = nullptr;
+        *out = plan;
+        return FKB_OK;
+    }
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&plan->table), sizeof(PlaneRec) * n_planes);
     if (e == cudaSuccess) e = cudaMemcpy(plan->table, plan->L.recs.data(), sizeof(PlaneRec) * n_planes, cudaMemcpyHostToDevice);
     if (e != cudaSuccess) {

@@ -17,6 +17,7 @@
 // Replaces launchTransformDPP_Kernel / launchDivergentBatchTransformDPP_Kernel of the reference
 // (core/execution_model/executor_details/executor_kernels.h:20-30).  No tensor cores: nothing here is a
 // contraction; the bound is HBM bandwidth.
+#include <cstdlib>
 #include "fkb_device.cuh"
 #include "fkb_launch.h"
 
@@ -690,6 +691,129 @@ __global__ void __launch_bounds__(256, 8) nv12_kernel(const __grid_constant__ La
     }
 }
 
+// nv12_pair_kernel: the same chain for the colour matrices every YCbCr standard uses, two output pixels per thread.
+// Conditions (checked on the host): the matrix has the shape [1 0 r; 1 g1 g2; 1 b 0], the offsets are integers in
+// [0,255], the operands are immediates, and every offset into a plane fits 32 bits.  Under them
+//   * (Y*1 + Cb*0) + Cr*r == Y + Cr*r bit for bit (x*1 is x; a finite x times 0 is a zero, and adding a zero of either
+//     sign to a value that is never -0 changes nothing; Y - offset is an exact integer difference, so its zero is +0),
+//     and likewise for the blue row, which drops seven of the fifteen operations per tap;
+//   * byte - offset is computed as (2^23 + byte) - (2^23 + offset): one byte-permute and one exact subtraction;
+//   * the two pixels of a thread share every coefficient, so the arithmetic runs as packed f32x2 operations.
+// A product that feeds only a sum is written as fma(a, b, -0), which the assembler cannot contract with the sum.
+struct PairTaps {
+    uint32_t x0, x1;
+    float w0, w1;
+};
+__device__ __forceinline__ f2 magic_pair(uint32_t wa, uint32_t wb, uint32_t sel) {
+    return f2{__uint_as_float(__byte_perm(wa, 0x4B000000u, sel)), __uint_as_float(__byte_perm(wb, 0x4B000000u, sel))};
+}
+template <bool INLINE>
+__device__ __forceinline__ void nv12_pair(const LaunchParams& p, const PlaneRec& pl, uint32_t xa, uint32_t y) {
+    if (pl.kclass != KCLASS_NV12) return;
+    if (xa >= pl.dst_w || y >= pl.dst_h) return;
+    const Nv12Consts& k = p.nv12;
+    const float nz = p.neg_zero;
+    const bool par = k.preserve_ar != 0;
+    const uint32_t xb = xa + 1;
+    const bool has_b = xb < pl.dst_w;
+    const int ox = par ? pl.x1 : 0, oy = par ? pl.y1 : 0;
+    // taps are computed for clamped coordinates, so that every address is valid; letterbox pixels are replaced below
+    const AxisTap ta = axis_tap(max(static_cast<int>(xa) - ox, 0), pl.fx, pl.crop_w);
+    const AxisTap tb = axis_tap(max(static_cast<int>(xb) - ox, 0), pl.fx, pl.crop_w);
+    const AxisTap ty = axis_tap(max(static_cast<int>(y) - oy, 0), pl.fy, pl.crop_h);
+    const uint32_t pitch = pl.src_pitch;
+    const uint32_t Y0 = ty.i0 + pl.crop_y, Y1 = ty.i1 + pl.crop_y;
+    const uint32_t ry0 = Y0 * pitch + pl.crop_x, ry1 = Y1 * pitch + pl.crop_x;
+    const uint32_t rc0 = (Y0 >> 1) * pitch, rc1 = (Y1 >> 1) * pitch;
+    const uint32_t ua0 = (ta.i0 + pl.crop_x) & ~1u, ua1 = (ta.i1 + pl.crop_x) & ~1u;
+    const uint32_t ub0 = (tb.i0 + pl.crop_x) & ~1u, ub1 = (tb.i1 + pl.crop_x) & ~1u;
+    const uint8_t* __restrict__ lum = pl.src;
+    const uint8_t* __restrict__ chr = pl.src_chroma;
+    // tap order: (x0,y0) (x1,y0) (x0,y1) (x1,y1); all sixteen loads are requested before any is used
+    uint32_t la[4], lb[4], ca[4], cb[4];
+    la[0] = __ldg(lum + (ry0 + ta.i0)); la[1] = __ldg(lum + (ry0 + ta.i1)); la[2] = __ldg(lum + (ry1 + ta.i0)); la[3] = __ldg(lum + (ry1 + ta.i1));
+    lb[0] = __ldg(lum + (ry0 + tb.i0)); lb[1] = __ldg(lum + (ry0 + tb.i1)); lb[2] = __ldg(lum + (ry1 + tb.i0)); lb[3] = __ldg(lum + (ry1 + tb.i1));
+    ca[0] = __ldg(reinterpret_cast<const unsigned short*>(chr + (rc0 + ua0))); ca[1] = __ldg(reinterpret_cast<const unsigned short*>(chr + (rc0 + ua1)));
+    ca[2] = __ldg(reinterpret_cast<const unsigned short*>(chr + (rc1 + ua0))); ca[3] = __ldg(reinterpret_cast<const unsigned short*>(chr + (rc1 + ua1)));
+    cb[0] = __ldg(reinterpret_cast<const unsigned short*>(chr + (rc0 + ub0))); cb[1] = __ldg(reinterpret_cast<const unsigned short*>(chr + (rc0 + ub1)));
+    cb[2] = __ldg(reinterpret_cast<const unsigned short*>(chr + (rc1 + ub0))); cb[3] = __ldg(reinterpret_cast<const unsigned short*>(chr + (rc1 + ub1)));
+    const f2 wy0{ty.w0, ty.w0}, wy1{ty.w1, ty.w1};
+    const f2 wx0{ta.w0, tb.w0}, wx1{ta.w1, tb.w1};
+    const f2 w[4] = {mul2(wx0, wy0), mul2(wx1, wy0), mul2(wx0, wy1), mul2(wx1, wy1)};
+    const f2 ky{-k.kmag[0], -k.kmag[0]}, ku{-k.kmag[1], -k.kmag[1]}, kv{-k.kmag[2], -k.kmag[2]};
+    const f2 cr{k.ccm[2], k.ccm[2]}, cg1{k.ccm[4], k.ccm[4]}, cg2{k.ccm[5], k.ccm[5]}, cbl{k.ccm[7], k.ccm[7]};
+    f2 acc[3];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+        const f2 yy = add2(magic_pair(la[t], lb[t], 0x7440u), ky);
+        const f2 uu = add2(magic_pair(ca[t], cb[t], 0x7440u), ku);
+        const f2 vv = add2(magic_pair(ca[t], cb[t], 0x7441u), kv);
+        const f2 r = add2(yy, mul2_unfusable(vv, cr, nz));
+        const f2 g = add2(add2(yy, mul2_unfusable(uu, cg1, nz)), mul2_unfusable(vv, cg2, nz));
+        const f2 b = add2(yy, mul2_unfusable(uu, cbl, nz));
+        const f2 tr = mul2_unfusable(r, w[t], nz), tg = mul2_unfusable(g, w[t], nz), tbb = mul2_unfusable(b, w[t], nz);
+        acc[0] = t == 0 ? tr : add2(acc[0], tr);
+        acc[1] = t == 0 ? tg : add2(acc[1], tg);
+        acc[2] = t == 0 ? tbb : add2(acc[2], tbb);
+    }
+    if (par) {
+        const bool row_in = static_cast<int>(y) >= pl.y1 && static_cast<int>(y) <= pl.y2;
+        const bool in_a = row_in && static_cast<int>(xa) >= pl.x1 && static_cast<int>(xa) <= pl.x2;
+        const bool in_b = row_in && static_cast<int>(xb) >= pl.x1 && static_cast<int>(xb) <= pl.x2;
+#pragma unroll
+        for (int c = 0; c < 3; ++c) {
+            if (!in_a) acc[c].x = pl.bg[c];
+            if (!in_b) acc[c].y = pl.bg[c];
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < 3; ++c) {
+        if (k.kind & kPostMul) acc[c] = mul2_unfusable(acc[c], f2{k.m[c], k.m[c]}, nz);
+        if (k.kind & kPostAdd) acc[c] = add2(acc[c], f2{k.a[c], k.a[c]});
+        if (k.kind & kPostDiv) { acc[c].x = __fdiv_rn(acc[c].x, k.d[c]); acc[c].y = __fdiv_rn(acc[c].y, k.d[c]); }
+        if (k.kind & kPostSat) { acc[c].x = sat_u8_as_float(acc[c].x); acc[c].y = sat_u8_as_float(acc[c].y); }
+    }
+    uint8_t* __restrict__ row = pl.dst + y * pl.dst_pitch;
+    if (k.f32) {
+        if (k.split) {
+#pragma unroll
+            for (int c = 0; c < 3; ++c) {
+                float* q = reinterpret_cast<float*>(row + c * pl.dst_cstride) + xa;
+                if (has_b && k.wide_store) *reinterpret_cast<float2*>(q) = make_float2(acc[c].x, acc[c].y);
+                else { q[0] = acc[c].x; if (has_b) q[1] = acc[c].y; }
+            }
+        } else {
+            float* q = reinterpret_cast<float*>(row) + xa * 3u;
+            if (has_b && k.wide_store) {
+                reinterpret_cast<float2*>(q)[0] = make_float2(acc[0].x, acc[1].x);
+                reinterpret_cast<float2*>(q)[1] = make_float2(acc[2].x, acc[0].y);
+                reinterpret_cast<float2*>(q)[2] = make_float2(acc[1].y, acc[2].y);
+            } else {
+                q[0] = acc[0].x; q[1] = acc[1].x; q[2] = acc[2].x;
+                if (has_b) { q[3] = acc[0].y; q[4] = acc[1].y; q[5] = acc[2].y; }
+            }
+        }
+    } else {
+#pragma unroll
+        for (int c = 0; c < 3; ++c) {
+            uint8_t* q = k.split ? row + c * pl.dst_cstride + xa : row + xa * 3u + c;
+            const uint32_t step = k.split ? 1u : 3u;
+            q[0] = static_cast<uint8_t>(u8_of_exact(acc[c].x));
+            if (has_b) q[step] = static_cast<uint8_t>(u8_of_exact(acc[c].y));
+        }
+    }
+}
+
+template <int THREADS, int MINB>
+__global__ void __launch_bounds__(THREADS, MINB) nv12_pair_kernel(const __grid_constant__ LaunchParams p) {
+    const uint32_t x = (blockIdx.x * 32 + (threadIdx.x & 31)) * 2, y = blockIdx.y * (THREADS / 32) + (threadIdx.x >> 5);
+    if (p.table == nullptr) {
+        for (uint32_t z = blockIdx.z; z < p.n_planes; z += gridDim.z) nv12_pair<true>(p, p.inline_planes[z], x, y);
+    } else {
+        for (uint32_t z = blockIdx.z; z < p.n_planes; z += gridDim.z) nv12_pair<false>(p, p.table[z], x, y);
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------------
 // lut_kernel: uchar3 -> uchar3 chains without resampling
 // ---------------------------------------------------------------------------------------------------------
@@ -858,7 +982,9 @@ cudaError_t launch_lut(const LaunchParams& p, uint32_t grid, cudaStream_t stream
 }
 
 cudaError_t launch_nv12(const LaunchParams& p, dim3 grid, cudaStream_t stream) {
-    nv12_kernel<<<grid, 256, 0, stream>>>(p);
+    // the pair kernel runs 128-thread CTAs (four rows of 64 pixels), ten per SM: more, smaller CTAs shorten the tail
+    if (p.nv12.pair) nv12_pair_kernel<128, 10><<<dim3(grid.x, grid.y * 2, grid.z), 128, 0, stream>>>(p);
+    else nv12_kernel<<<grid, 256, 0, stream>>>(p);
     return cudaGetLastError();
 }
 

@@ -188,14 +188,14 @@ def vertical_fusion(w=3840, h=2160, seed=2, pitch_align=16, dst_pitch_align=16) 
                     f"{w}x{h} uchar3 -> uchar3, six fused element-wise ops")
 
 
-def nv12_preprocess(w=3840, h=2160, dst=(640, 640), seed=3, pitch_align=16) -> Workload:
+def nv12_preprocess(w=3840, h=2160, dst=(640, 640), seed=3, pitch_align=16, ccm=None, yuv_sub=(0.0, 128.0, 128.0)) -> Workload:
     """Config 3: ReadYUV<NV12> -> ConvertYUVToRGB<p8bit,Full,bt709> -> Resize IGNORE_AR -> Sub mean -> Div std ->
     TensorSplit<float3> (planar CHW fp32)."""
     pitch = _pitch(w, pitch_align)
     dw, dh = dst
     ch = chain(abi.PIX_NV12, abi.GEOM_RESIZE_IGNORE_AR, abi.PIX_F32C3, abi.WRITE_SPLIT,
                [op(abi.OP_YUV2RGB), op(abi.OP_SUB, (123.675, 116.28, 103.53)), op(abi.OP_DIV, (58.395, 57.12, 57.375))],
-               n_pre_ops=1, ccm=BT709_FULL_8BIT, yuv_sub=(0.0, 128.0, 128.0))
+               n_pre_ops=1, ccm=BT709_FULL_8BIT if ccm is None else ccm, yuv_sub=yuv_sub)
     planes = [PlaneSpec(0, 0, 0, w, h, pitch, (0, 0, w, h), dw, dh, dw * 4, dst_channel_stride=dw * dh * 4,
                         chroma_offset=pitch * h)]
     return Workload("nv12_preprocess", [ch], [_frame(seed, pitch * (h + h // 2), 16, 236)], [dw * dh * 12], planes,

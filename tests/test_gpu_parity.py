@@ -122,6 +122,19 @@ def test_edge_shapes():
         check(wl, force_gather=True)
 
 
+def test_nv12_colour_matrices():
+    # limited-range bt601 (luma offset 16: the two-pixel kernel with a non-zero luma offset), then two matrices outside
+    # that kernel's conditions (a Cb term in the red row; a fractional offset), which take the one-pixel NV12 kernel
+    bt601_limited = (1.0, 0.0, 1.402, 1.0, -0.344136, -0.714136, 1.0, 1.772, 0.0)
+    odd = (1.164, 0.25, 1.596, 1.164, -0.392, -0.813, 1.164, 2.017, 0.125)
+    for kw in [dict(ccm=bt601_limited, yuv_sub=(16.0, 128.0, 128.0)), dict(ccm=odd, yuv_sub=(16.0, 128.0, 128.0)),
+               dict(yuv_sub=(0.0, 127.5, 128.0))]:
+        for shape in [dict(w=1280, h=720, dst=(321, 203)), dict(w=64, h=48, dst=(7, 5)), dict(w=66, h=50, dst=(300, 301))]:
+            wl = W.nv12_preprocess(**shape, **kw)
+            check(wl)
+            check(wl, use_plan=True)
+
+
 def test_many_planes_use_the_descriptor_arena():
     # more planes than fit in the kernel parameters: descriptors travel through the pinned/device ring
     wl = W.batched_crop_resize(n_frames=3, crops_per_frame=100, w=320, h=240, dst=(32, 24), crop_range=(4, 100))

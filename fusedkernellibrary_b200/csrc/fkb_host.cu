@@ -318,8 +318,8 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         }
     }
     // LUT units: a block of rows of one plane per CTA visit; about one unit per resident CTA, at least eight row segments
-    const uint32_t lut_rpu = lut_rows ? std::max<uint32_t>(static_cast<uint32_t>((lut_rows + 2ull * sms - 1) / (2ull * sms)),
-                                                           (8u + lut_min_tiles_x - 1) / lut_min_tiles_x) : 1u;
+    const uint32_t lut_rpu = lut_rows ? std::max<uint32_t>(static_cast<uint32_t>((lut_rows + 1ull * kLutCtasPerSm * sms - 1) / (1ull * kLutCtasPerSm * sms)),
+                                                           (kLutWarps + lut_min_tiles_x - 1) / lut_min_tiles_x) : 1u;
     uint32_t n_lut_units = 0;
     const uint32_t rpi = rows_per_item(row_segments, 2u * kStagedWarps * static_cast<uint32_t>(sms));
     for (uint32_t z = 0; z < n_planes; ++z) {
@@ -357,7 +357,7 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
     }
     L.lp.n_lut_units = n_lut_units;
     if (n_lut_units) {
-        L.lut_grid = std::min<uint32_t>(n_lut_units, 2u * static_cast<uint32_t>(sms));
+        L.lut_grid = std::min<uint32_t>(n_lut_units, kLutCtasPerSm * static_cast<uint32_t>(sms));
         ++L.kernels;
     }
     if (n_nv12) {
@@ -538,8 +538,8 @@ int lower_fixed(const fkb_chain_desc* chain, const fkb_plane_desc* planes, uint3
         if (r.kclass == KCLASS_LUT) { lut_rows += r.dst_h; lut_min_tiles_x = std::min(lut_min_tiles_x, r.tiles_x); }
     }
     const uint32_t rpi = rows_per_item(row_segments, 2u * kStagedWarps * static_cast<uint32_t>(sms));
-    const uint32_t lut_rpu = lut_rows ? std::max<uint32_t>(static_cast<uint32_t>((lut_rows + 2ull * sms - 1) / (2ull * sms)),
-                                                           (8u + lut_min_tiles_x - 1) / lut_min_tiles_x) : 1u;
+    const uint32_t lut_rpu = lut_rows ? std::max<uint32_t>(static_cast<uint32_t>((lut_rows + 1ull * kLutCtasPerSm * sms - 1) / (1ull * kLutCtasPerSm * sms)),
+                                                           (kLutWarps + lut_min_tiles_x - 1) / lut_min_tiles_x) : 1u;
     uint32_t n_tiles = 0, n_lut_units = 0, n_gather = 0, gw = 0, gh = 0, first_count = 0;
     bool uniform = true;
     for (uint32_t z = 0; z < n_planes; ++z) {
@@ -571,7 +571,7 @@ int lower_fixed(const fkb_chain_desc* chain, const fkb_plane_desc* planes, uint3
     lp.tiles_per_plane = (uniform && first_count) ? first_count : 0;
     lp.n_lut_units = n_lut_units;
     staged_grid = n_tiles ? std::min<uint32_t>(n_tiles, 2u * static_cast<uint32_t>(sms)) : 0u;
-    lut_grid = n_lut_units ? std::min<uint32_t>(n_lut_units, 2u * static_cast<uint32_t>(sms)) : 0u;
+    lut_grid = n_lut_units ? std::min<uint32_t>(n_lut_units, kLutCtasPerSm * static_cast<uint32_t>(sms)) : 0u;
     gather_grid = n_gather ? dim3((gw + 127) / 128, (gh + 7) / 8, std::min<uint32_t>(n_planes, 65535u)) : dim3(0, 0, 0);
     return status_word(&lp.status);
 }

@@ -822,8 +822,12 @@ __global__ void __launch_bounds__(THREADS, MINB) nv12_pair_kernel(const __grid_c
 // interpreter as every other path, so the table is exact by construction — once for the 256 possible bytes, and then
 // every pixel costs three table reads instead of the whole chain (IEEE divisions and saturations included).  An entry
 // is one 32-bit word holding the three channels' results for that byte value, and every lane reads its own copy of the
-// table (copy l lives in bank l), so a table read is free of bank conflicts whatever the pixel values are.
-// Rows move exactly like in staged_kernel: per-warp bulk loads into shared memory, bulk stores out.
+// table (copy l lives in bank l), so a table read is free of bank conflicts whatever the pixel values are.  The rows of
+// the table are 256 bytes apart (the copies fill the first 128), so the address of a read — value * 256 + lane * 4 — is
+// one byte-permute that drops the source byte into byte 1 of a word whose byte 0 is lane * 4.
+// One CTA of 24 warps per SM.  Rows move like in staged_kernel — per-warp bulk loads into shared memory, bulk stores out —
+// but a segment is transformed in place (a lane reads its 16 pixels, then writes them back), so each warp needs only one
+// ring of four buffers: one being computed, two loads in flight, one store still being read.
 __device__ __forceinline__ uint32_t unit_to_plane(const LaunchParams& p, uint32_t u, uint32_t& local) {
     const PlaneRec* table = plane_table(p);
     uint32_t lo = 0, hi = p.n_planes;
@@ -836,13 +840,13 @@ __device__ __forceinline__ uint32_t unit_to_plane(const LaunchParams& p, uint32_
 }
 
 template <bool SWAP>
-__device__ __forceinline__ void lut_segment(uint32_t in_s, uint32_t out_s, uint32_t ow, uint32_t lane) {
+__device__ __forceinline__ void lut_segment(uint32_t seg, uint32_t ow, uint32_t lane) {
     if (lane * 16u >= ow) return;
-    const uint4* src = reinterpret_cast<const uint4*>(smem_raw + in_s + lane * 48u);
+    uint4* buf = reinterpret_cast<uint4*>(smem_raw + seg + lane * 48u);
     uint32_t q[12];
 #pragma unroll
-    for (int i = 0; i < 3; ++i) { const uint4 t = src[i]; q[4 * i] = t.x; q[4 * i + 1] = t.y; q[4 * i + 2] = t.z; q[4 * i + 3] = t.w; }
-    const uint32_t lane_off = lane * 4u;
+    for (int i = 0; i < 3; ++i) { const uint4 t = buf[i]; q[4 * i] = t.x; q[4 * i + 1] = t.y; q[4 * i + 2] = t.z; q[4 * i + 3] = t.w; }
+    const uint32_t lane_word = lane * 4u;  // byte 0 of every table address
     uint32_t o[12];
 #pragma unroll
     for (int i = 0; i < 12; ++i) {
@@ -851,26 +855,27 @@ __device__ __forceinline__ void lut_segment(uint32_t in_s, uint32_t out_s, uint3
         for (int t = 0; t < 4; ++t) {
             const int b = 4 * i + t, c = b % 3;          // output byte b is channel c of pixel b / 3
             const int sb = SWAP ? b - c + (2 - c) : b;   // the source byte it is a function of
-            const uint32_t idx = __byte_perm(q[sb >> 2], 0u, 0x4440u | (sb & 3));
-            e[t] = *reinterpret_cast<const uint32_t*>(smem_raw + idx * 128u + lane_off);
+            const uint32_t at = __byte_perm(q[sb >> 2], lane_word, 0x5504u | ((sb & 3) << 4));  // value * 256 + lane * 4
+            e[t] = *reinterpret_cast<const uint32_t*>(smem_raw + at);
         }
         // byte (4i+t) % 3 of entry t is the channel this output byte wants
         const uint32_t c0 = (4 * i) % 3, c1 = (4 * i + 1) % 3, c2 = (4 * i + 2) % 3, c3 = (4 * i + 3) % 3;  // constants once unrolled
         o[i] = __byte_perm(__byte_perm(e[0], e[1], c0 | ((4u + c1) << 4)), __byte_perm(e[2], e[3], c2 | ((4u + c3) << 4)), 0x5410u);
     }
-    uint4* dst = reinterpret_cast<uint4*>(smem_raw + out_s + lane * 48u);
 #pragma unroll
-    for (int i = 0; i < 3; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+    for (int i = 0; i < 3; ++i) buf[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
 }
 
-__global__ void __launch_bounds__(kLutThreads, 2) lut_kernel(const __grid_constant__ LaunchParams p) {
+__global__ void __launch_bounds__(kLutThreads, 1) lut_kernel(const __grid_constant__ LaunchParams p) {
     __shared__ PlaneRec s_pl;
-    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __shared__ uint32_t s_entry[256];
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);  // tells the compiler the value is warp-uniform
     const uint32_t slice = kLutBytes + warp * kLutSliceBytes;
     uint64_t* bar = reinterpret_cast<uint64_t*>(smem_raw + slice);
-    const uint32_t in0 = slice + 64, out0 = slice + 64 + kLutInStages * kLutSegBytes;
+    const uint32_t buf0 = slice + 64;
     if (lane == 0) {
-        for (uint32_t i = 0; i < kLutInStages; ++i) mbar_init(&bar[i], 1);
+        for (uint32_t i = 0; i < kLutStages; ++i) mbar_init(&bar[i], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncwarp();
@@ -882,7 +887,6 @@ __global__ void __launch_bounds__(kLutThreads, 2) lut_kernel(const __grid_consta
         const uint32_t z = unit_to_plane(p, unit, local);
         const bool rebuild = z != cur_plane;  // block-uniform
         if (rebuild) {
-            if (lane == 0) bulk_wait_read_all();
             __syncthreads();  // nobody reads the old table or plane record any more
             if (threadIdx.x < sizeof(PlaneRec) / 16)
                 reinterpret_cast<uint4*>(&s_pl)[threadIdx.x] = reinterpret_cast<const uint4*>(table + z)[threadIdx.x];
@@ -895,57 +899,63 @@ __global__ void __launch_bounds__(kLutThreads, 2) lut_kernel(const __grid_consta
         const uint8_t* gsrc = pl.src + static_cast<size_t>(pl.crop_y + row0) * pl.src_pitch + static_cast<size_t>(pl.crop_x) * 3u;
         uint8_t* gdst = pl.dst + static_cast<size_t>(row0) * pl.dst_pitch;
         const uint32_t src_pitch = pl.src_pitch, dst_pitch = pl.dst_pitch, tiles_x = pl.tiles_x, tile_w = pl.tile_w, dst_w = pl.dst_w;
-        // Segment g of the unit is (row g / tiles_x, column tile g % tiles_x); this warp takes g = warp, warp + 8, ...
+        // Segment g of the unit is (row g / tiles_x, column tile g % tiles_x); this warp takes g = warp, warp + 24, ...
         // Two cursors walk that list without dividing: `pf` for the prefetches, `cu` for the segment being computed.
         struct Cursor { uint32_t g, r, tx; };
+        const uint32_t step_r = kLutWarps / tiles_x, step_tx = kLutWarps % tiles_x;
         auto advance = [&](Cursor& c) {
-            c.g += kLutWarps; c.tx += kLutWarps;
-            while (c.tx >= tiles_x) { c.tx -= tiles_x; ++c.r; }
+            c.g += kLutWarps; c.tx += step_tx; c.r += step_r;
+            if (c.tx >= tiles_x) { c.tx -= tiles_x; ++c.r; }
         };
         auto issue = [&](const Cursor& c, uint32_t s) {
-            if (lane == 0) {
-                const uint32_t ow = min(tile_w, dst_w - c.tx * tile_w);
-                const uint32_t bytes = (ow * 3u + 15u) & ~15u;
-                mbar_arrive_expect_tx(&bar[s], bytes);
-                bulk_load(smem_raw + in0 + s * kLutSegBytes, gsrc + static_cast<size_t>(c.r) * src_pitch + static_cast<size_t>(c.tx) * tile_w * 3u, bytes, &bar[s]);
-            }
+            const uint32_t ow = min(tile_w, dst_w - c.tx * tile_w);
+            const uint32_t bytes = (ow * 3u + 15u) & ~15u;
+            mbar_arrive_expect_tx(&bar[s], bytes);
+            bulk_load(smem_raw + buf0 + s * kLutSegBytes, gsrc + static_cast<size_t>(c.r) * src_pitch + static_cast<size_t>(c.tx) * tile_w * 3u, bytes, &bar[s]);
         };
         Cursor cu{warp, warp / tiles_x, warp % tiles_x}, pf = cu;
-        constexpr uint32_t AHEAD = kLutInStages - 1;
+        constexpr uint32_t AHEAD = kLutStages - 2;
+        if (lane == 0) bulk_wait_read_all();  // the ring's earlier stores have been read out of their buffers
         for (uint32_t i = 0; i < AHEAD; ++i) {  // the first loads fly while the table is built
-            if (pf.g < nseg) issue(pf, (k + i) % kLutInStages);
+            if (lane == 0 && pf.g < nseg) issue(pf, (k + i) % kLutStages);
             advance(pf);
         }
         if (rebuild) {
             const fkb_chain_desc& ch = p.chains[pl.chain];
-            for (uint32_t t = threadIdx.x; t < 256; t += blockDim.x) {
-                float v[1][3] = {{static_cast<float>(t), static_cast<float>(t), static_cast<float>(t)}};
+            if (threadIdx.x < 256) {
+                const float t = static_cast<float>(threadIdx.x);
+                float v[1][3] = {{t, t, t}};
                 apply_ops<1>(v, ch, pl, 0, ch.n_ops);
-                const uint32_t e = u8_of_exact(v[0][0]) | (u8_of_exact(v[0][1]) << 8) | (u8_of_exact(v[0][2]) << 16);
-                uint32_t* row = reinterpret_cast<uint32_t*>(smem_raw) + t * 32u;
-#pragma unroll
-                for (uint32_t r = 0; r < 32; ++r) row[r] = e;
+                s_entry[threadIdx.x] = u8_of_exact(v[0][0]) | (u8_of_exact(v[0][1]) << 8) | (u8_of_exact(v[0][2]) << 16);
             }
+            __syncthreads();
+            // copy l of value v sits at v * 256 + l * 4: consecutive threads write consecutive words of a row
+            for (uint32_t w = threadIdx.x; w < 256u * 32u; w += kLutThreads)
+                *reinterpret_cast<uint32_t*>(smem_raw + (w >> 5) * 256u + (w & 31u) * 4u) = s_entry[w >> 5];
             __syncthreads();
             cur_plane = z;
         }
         for (; cu.g < nseg && ok; advance(cu), ++k) {
-            const uint32_t s = k % kLutInStages, o = k & 1u;
-            if (lane == 0) bulk_wait_read_1();  // the store that read this output buffer two segments ago is done
-            if (pf.g < nseg) issue(pf, (k + AHEAD) % kLutInStages);
+            const uint32_t s = k % kLutStages;
+            // the buffer two segments back is free once its store has read it; the load two ahead goes there
+            if (lane == 0) {
+                bulk_wait_read_1();
+                if (pf.g < nseg) issue(pf, (k + AHEAD) % kLutStages);
+            }
             advance(pf);
-            const bool landed = mbar_wait_bounded(&bar[s], (k / kLutInStages) & 1u);
+            const bool landed = mbar_wait_bounded(&bar[s], (k / kLutStages) & 1u);
             if (__any_sync(0xffffffffu, !landed)) { ok = false; break; }
             const uint32_t ow = min(tile_w, dst_w - cu.tx * tile_w);
-            if (swap) lut_segment<true>(in0 + s * kLutSegBytes, out0 + o * kLutSegBytes, ow, lane);
-            else lut_segment<false>(in0 + s * kLutSegBytes, out0 + o * kLutSegBytes, ow, lane);
-            store_row(gdst + static_cast<size_t>(cu.r) * dst_pitch + static_cast<size_t>(cu.tx) * tile_w * 3u, out0 + o * kLutSegBytes, ow * 3u, lane);
+            const uint32_t seg = buf0 + s * kLutSegBytes;
+            if (swap) lut_segment<true>(seg, ow, lane);
+            else lut_segment<false>(seg, ow, lane);
+            store_row(gdst + static_cast<size_t>(cu.r) * dst_pitch + static_cast<size_t>(cu.tx) * tile_w * 3u, seg, ow * 3u, lane);
         }
         if (__syncthreads_or(ok ? 0 : 1)) { ok = false; break; }
     }
     if (lane == 0) bulk_wait_all();
     if (!ok) {
-        for (uint32_t i = 1; i < kLutInStages; ++i) mbar_wait_bounded(&bar[(k + i) % kLutInStages], ((k + i) / kLutInStages) & 1u);
+        for (uint32_t i = 1; i < kLutStages; ++i) mbar_wait_bounded(&bar[(k + i) % kLutStages], ((k + i) / kLutStages) & 1u);
         if (threadIdx.x == 0) atomicExch(p.status, FKB_ERR_DEVICE_WAIT);
     }
 }

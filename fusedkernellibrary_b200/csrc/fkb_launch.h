@@ -18,16 +18,17 @@ constexpr uint32_t kOutSlotBytes = kOutRowBytes + 16;  // the 16 spare bytes tak
 constexpr uint32_t kSliceBytes = kSliceHeader + 4 * kInRowBytes + 2 * kOutSlotBytes;
 constexpr uint32_t kStagedSmemBytes = kStagedWarps * kSliceBytes;
 constexpr uint32_t kMaxRowsPerItem = 32;
-// lut_kernel: a CTA-wide table of 256 entries x 32 copies of one 32-bit word {T0[i], T1[i], T2[i], 0} (copy l belongs to
-// lane l and sits in bank l, so a table read never has a bank conflict), followed by one slice per warp (four mbarriers, four
-// source and two output row segments of 512 uchar3 pixels; three segments are kept in flight ahead of the one being
-// computed).  8 warps, 104 KB per CTA: two CTAs per SM.
-constexpr uint32_t kLutThreads = 256;
+// lut_kernel: a CTA-wide table of 256 rows, 256 bytes apart, each holding 32 copies of one 32-bit word
+// {T0[i], T1[i], T2[i], 0} (copy l belongs to lane l and sits in bank l, so a table read never has a bank conflict),
+// followed by one slice per warp: four mbarriers and a ring of four row segments of 512 uchar3 pixels that are transformed
+// in place.  24 warps, 210 KB: one CTA per SM.
+constexpr uint32_t kLutThreads = 768;
 constexpr uint32_t kLutWarps = kLutThreads / 32;
-constexpr uint32_t kLutBytes = 256 * 32 * 4;
+constexpr uint32_t kLutCtasPerSm = 1;
+constexpr uint32_t kLutBytes = 256 * 256;  // 256 values, rows 256 bytes apart (32 lane copies of a 4-byte entry, then unused)
 constexpr uint32_t kLutSegBytes = 1536;
-constexpr uint32_t kLutInStages = 4;
-constexpr uint32_t kLutSliceBytes = 64 + (kLutInStages + 2) * kLutSegBytes;
+constexpr uint32_t kLutStages = 4;
+constexpr uint32_t kLutSliceBytes = 64 + kLutStages * kLutSegBytes;
 constexpr uint32_t kLutSmemBytes = kLutBytes + kLutWarps * kLutSliceBytes;
 
 constexpr uint64_t kTinyLaunchPixels = 100000;  // launches below this many output pixels take the general kernel

@@ -18,6 +18,8 @@ OK, ERR_NULL, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_TOO_LARGE, ERR_DEVICE_
 
 PIX_U8C3, PIX_F32C3, PIX_NV12 = 1, 2, 3
 GEOM_NONE, GEOM_RESIZE_IGNORE_AR, GEOM_RESIZE_PRESERVE_AR = 0, 1, 2
+GEOM_RESIZE_PRESERVE_AR_RN_EVEN, GEOM_RESIZE_PRESERVE_AR_LEFT = 3, 4
+PLANE_DEFAULT = 0x80000000  # fkb_plane_desc.chain bit: the plane's read yields bg (conditional batch read)
 WRITE_PACKED, WRITE_SPLIT = 1, 2
 OP_CAST_F32, OP_MUL, OP_ADD, OP_SUB, OP_DIV, OP_REORDER_ZYX, OP_YUV2RGB, OP_SATCAST_U8 = 1, 2, 3, 4, 5, 6, 7, 8
 

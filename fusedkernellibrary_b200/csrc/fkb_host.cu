@@ -58,7 +58,7 @@ int check_ops(const fkb_chain_desc& ch, uint32_t first, uint32_t last, ValueType
 int check_chain(const fkb_chain_desc& ch) {
     if (ch.src_format != FKB_PIX_U8C3 && ch.src_format != FKB_PIX_NV12) return FKB_ERR_UNSUPPORTED;
     if (ch.dst_format != FKB_PIX_U8C3 && ch.dst_format != FKB_PIX_F32C3) return FKB_ERR_UNSUPPORTED;
-    if (ch.geometry > FKB_GEOM_RESIZE_PRESERVE_AR) return FKB_ERR_UNSUPPORTED;
+    if (ch.geometry > FKB_GEOM_RESIZE_PRESERVE_AR_LEFT) return FKB_ERR_UNSUPPORTED;
     if (ch.write_kind != FKB_WRITE_PACKED && ch.write_kind != FKB_WRITE_SPLIT) return FKB_ERR_UNSUPPORTED;
     if (ch.n_ops > FKB_MAX_OPS || ch.n_pre_ops > ch.n_ops) return FKB_ERR_INVALID;
     ValueType t = VT_U8;  // both reads produce uchar3
@@ -75,29 +75,37 @@ int check_chain(const fkb_chain_desc& ch) {
 }
 
 int check_plane(const fkb_chain_desc& ch, const fkb_plane_desc& pl) {
-    if (!pl.src || !pl.dst) return FKB_ERR_NULL;
+    const bool dflt = (pl.chain & FKB_PLANE_DEFAULT) != 0;  // the read yields bg: no source is touched
+    if ((!dflt && !pl.src) || !pl.dst) return FKB_ERR_NULL;
     const bool nv12 = ch.src_format == FKB_PIX_NV12;
-    if (nv12 && !pl.src_chroma) return FKB_ERR_NULL;
-    if (pl.src_w == 0 || pl.src_h == 0 || pl.dst_w == 0 || pl.dst_h == 0) return FKB_ERR_INVALID;
-    const uint64_t src_row = nv12 ? ((static_cast<uint64_t>(pl.src_w) + 1) / 2) * 2 : static_cast<uint64_t>(pl.src_w) * 3;
-    if (pl.src_pitch < src_row) return FKB_ERR_INVALID;
-    if (pl.crop_w <= 0 || pl.crop_h <= 0) return FKB_ERR_INVALID;
-    if (static_cast<uint64_t>(pl.crop_x) + static_cast<uint64_t>(pl.crop_w) > pl.src_w ||
-        static_cast<uint64_t>(pl.crop_y) + static_cast<uint64_t>(pl.crop_h) > pl.src_h) return FKB_ERR_INVALID;
+    if (!dflt) {
+        if (nv12 && !pl.src_chroma) return FKB_ERR_NULL;
+        if (pl.src_w == 0 || pl.src_h == 0) return FKB_ERR_INVALID;
+        const uint64_t src_row = nv12 ? ((static_cast<uint64_t>(pl.src_w) + 1) / 2) * 2 : static_cast<uint64_t>(pl.src_w) * 3;
+        if (pl.src_pitch < src_row) return FKB_ERR_INVALID;
+        if (pl.crop_w <= 0 || pl.crop_h <= 0) return FKB_ERR_INVALID;
+        if (static_cast<uint64_t>(pl.crop_x) + static_cast<uint64_t>(pl.crop_w) > pl.src_w ||
+            static_cast<uint64_t>(pl.crop_y) + static_cast<uint64_t>(pl.crop_h) > pl.src_h) return FKB_ERR_INVALID;
+    } else if (ch.geometry == FKB_GEOM_NONE) {
+        for (int c = 0; c < 3; ++c)  // a uchar3 default
+            if (!(pl.bg[c] >= 0.f && pl.bg[c] <= 255.f) || pl.bg[c] != std::floor(pl.bg[c])) return FKB_ERR_INVALID;
+    }
+    if (pl.dst_w == 0 || pl.dst_h == 0) return FKB_ERR_INVALID;
     const bool f32 = ch.dst_format == FKB_PIX_F32C3;
     const bool split = ch.write_kind == FKB_WRITE_SPLIT;
     const uint64_t dst_row = static_cast<uint64_t>(pl.dst_w) * (split ? (f32 ? 4 : 1) : (f32 ? 12 : 3));
     if (pl.dst_pitch < dst_row) return FKB_ERR_INVALID;
     if (f32 && ((reinterpret_cast<uintptr_t>(pl.dst) & 3) || (pl.dst_pitch & 3) || (pl.dst_channel_stride & 3))) return FKB_ERR_INVALID;
     if (split && pl.dst_channel_stride < static_cast<uint64_t>(pl.dst_pitch) * (pl.dst_h - 1) + dst_row) return FKB_ERR_INVALID;
+    if (dflt) return FKB_OK;
     if (ch.geometry == FKB_GEOM_NONE) {
         if (pl.dst_w > static_cast<uint32_t>(pl.crop_w) || pl.dst_h > static_cast<uint32_t>(pl.crop_h)) return FKB_ERR_INVALID;
     } else {
         // A PRESERVE_AR target that rounds to zero width or height (x2 < x1 or y2 < y1) is legal in the reference:
         // no pixel is inside, the whole plane is background, and the scale factors (then infinite) are never used.
-        const bool empty = ch.geometry == FKB_GEOM_RESIZE_PRESERVE_AR && (pl.x2 < pl.x1 || pl.y2 < pl.y1);
+        const bool empty = ch.geometry >= FKB_GEOM_RESIZE_PRESERVE_AR && (pl.x2 < pl.x1 || pl.y2 < pl.y1);
         if (!empty && (!(pl.fx > 0.f) || !(pl.fy > 0.f) || !std::isfinite(pl.fx) || !std::isfinite(pl.fy))) return FKB_ERR_INVALID;
-        if (ch.geometry == FKB_GEOM_RESIZE_PRESERVE_AR && !empty) {
+        if (ch.geometry >= FKB_GEOM_RESIZE_PRESERVE_AR && !empty) {
             if (pl.x1 < 0 || pl.y1 < 0 || pl.x2 >= static_cast<int>(pl.dst_w) || pl.y2 >= static_cast<int>(pl.dst_h)) return FKB_ERR_INVALID;
         }
     }
@@ -112,8 +120,8 @@ int validate(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_de
         if (rc != FKB_OK) return rc;
     }
     for (uint32_t z = 0; z < n_planes; ++z) {
-        if (planes[z].chain >= n_chains) return FKB_ERR_INVALID;
-        const int rc = check_plane(chains[planes[z].chain], planes[z]);
+        if ((planes[z].chain & ~FKB_PLANE_DEFAULT) >= n_chains) return FKB_ERR_INVALID;
+        const int rc = check_plane(chains[planes[z].chain & ~FKB_PLANE_DEFAULT], planes[z]);
         if (rc != FKB_OK) return rc;
     }
     return FKB_OK;
@@ -148,7 +156,7 @@ void classify(const fkb_chain_desc& ch, PlaneRec& r) {
     r.in_stride = r.out_stride = 0;
     if (force_gather()) return;
     if (ch.src_format == FKB_PIX_NV12 && ch.geometry != FKB_GEOM_NONE && ch.n_pre_ops == 1 && ch.ops[0].code == FKB_OP_YUV2RGB &&
-        post_kind_of(ch) != 8u && !(ch.geometry == FKB_GEOM_RESIZE_PRESERVE_AR && (r.x2 < r.x1 || r.y2 < r.y1)) &&
+        post_kind_of(ch) != 8u && !(ch.geometry >= FKB_GEOM_RESIZE_PRESERVE_AR && (r.x2 < r.x1 || r.y2 < r.y1)) &&
         (reinterpret_cast<uintptr_t>(r.src_chroma) & 1) == 0 && (r.src_pitch & 1) == 0) {  // UV pairs are read as 16-bit words
         r.kclass = KCLASS_NV12;  // NV12 -> RGB on the taps -> resize -> [Mul][Add|Sub][Div][SaturateCast]: nv12_kernel
         return;
@@ -172,7 +180,7 @@ void classify(const fkb_chain_desc& ch, PlaneRec& r) {
     } else {
         for (uint32_t i = 0; i < ch.n_pre_ops; ++i)
             if (ch.ops[i].code != FKB_OP_CAST_F32) return;  // taps are transformed before interpolation: general path
-        if (ch.geometry == FKB_GEOM_RESIZE_PRESERVE_AR && (r.x2 < r.x1 || r.y2 < r.y1)) return;  // all background
+        if (ch.geometry >= FKB_GEOM_RESIZE_PRESERVE_AR && (r.x2 < r.x1 || r.y2 < r.y1)) return;  // all background
         if (!(r.fx <= 32.f) || !(r.fy <= 4096.f)) return;
         // widest segment (at most 8 columns per lane) whose source columns fit one staged row
         uint32_t tw = std::min(r.dst_w, 256u);
@@ -296,9 +304,14 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         r.dst_w = s.dst_w; r.dst_h = s.dst_h; r.dst_pitch = s.dst_pitch;
         r.fx = s.fx; r.fy = s.fy; r.x1 = s.x1; r.y1 = s.y1; r.x2 = s.x2; r.y2 = s.y2;
         std::memcpy(r.bg, s.bg, sizeof(r.bg));
-        r.chain = s.chain;
+        r.chain = s.chain & ~FKB_PLANE_DEFAULT;
         std::memcpy(r.params, s.params, sizeof(r.params));
-        classify(chains[s.chain], r);
+        if (s.chain & FKB_PLANE_DEFAULT) {  // the kernels know such a plane by its null source; the general kernel fills it
+            r.src = r.src_chroma = nullptr;
+            r.kclass = KCLASS_GATHER;
+        } else {
+            classify(chains[r.chain], r);
+        }
         total_pixels += static_cast<uint64_t>(r.dst_w) * r.dst_h;
     }
     // A launch of a few ten thousand pixels is pure latency: the pipelined paths would spend it filling their stages,
@@ -370,7 +383,7 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         const PostImm imm = post_imm_of(ch);
         std::memcpy(k.m, imm.m, sizeof(k.m)); std::memcpy(k.a, imm.a, sizeof(k.a)); std::memcpy(k.d, imm.d, sizeof(k.d));
         k.kind = post_kind_of(ch); k.chain = c; k.slots = imm.slots;
-        k.preserve_ar = ch.geometry == FKB_GEOM_RESIZE_PRESERVE_AR; k.f32 = ch.dst_format == FKB_PIX_F32C3; k.split = ch.write_kind == FKB_WRITE_SPLIT;
+        k.preserve_ar = ch.geometry >= FKB_GEOM_RESIZE_PRESERVE_AR; k.f32 = ch.dst_format == FKB_PIX_F32C3; k.split = ch.write_kind == FKB_WRITE_SPLIT;
         // nv12_pair_kernel's conditions: the colour matrix of the YCbCr standards ([1 0 r; 1 g1 g2; 1 b 0]), integer
         // offsets, immediate operands, and plane offsets that fit 32 bits
         bool pair = !imm.slots && k.ccm[0] == 1.f && k.ccm[3] == 1.f && k.ccm[6] == 1.f && k.ccm[1] == 0.f && k.ccm[8] == 0.f;
@@ -626,14 +639,18 @@ int fkb_resize_params(uint32_t geometry, fkb_plane_desc* pl) {
     const int dw = static_cast<int>(pl->dst_w), dh = static_cast<int>(pl->dst_h);
     if (sw <= 0 || sh <= 0 || dw <= 0 || dh <= 0) return FKB_ERR_INVALID;
     int tw = dw, th = dh;
-    if (geometry == FKB_GEOM_RESIZE_PRESERVE_AR) {
-        // compute_target_size: fit the height first, fall back to fitting the width
+    if (geometry >= FKB_GEOM_RESIZE_PRESERVE_AR && geometry <= FKB_GEOM_RESIZE_PRESERVE_AR_LEFT) {
+        // compute_target_size: fit the height first, fall back to fitting the width; RN_EVEN rounds the fitted
+        // dimension down to an even number (and tests the evened width against the destination)
+        const bool even = geometry == FKB_GEOM_RESIZE_PRESERVE_AR_RN_EVEN;
         const float by_height = static_cast<float>(dh) / static_cast<float>(sh);
         tw = static_cast<int>(std::round(by_height * static_cast<float>(sw)));
+        if (even) tw -= tw % 2;
         if (tw > dw) {
             const float by_width = static_cast<float>(dw) / static_cast<float>(sw);
             tw = dw;
             th = static_cast<int>(std::round(by_width * static_cast<float>(sh)));
+            if (even) th -= th % 2;
         }
     } else if (geometry != FKB_GEOM_RESIZE_IGNORE_AR) {
         return FKB_ERR_INVALID;
@@ -642,7 +659,7 @@ int fkb_resize_params(uint32_t geometry, fkb_plane_desc* pl) {
     const double cfy = static_cast<double>(th) / static_cast<double>(sh);
     pl->fx = static_cast<float>(1.0 / cfx);
     pl->fy = static_cast<float>(1.0 / cfy);
-    pl->x1 = (dw - tw) / 2;
+    pl->x1 = geometry == FKB_GEOM_RESIZE_PRESERVE_AR_LEFT ? 0 : (dw - tw) / 2;
     pl->y1 = (dh - th) / 2;
     pl->x2 = pl->x1 + tw - 1;
     pl->y2 = pl->y1 + th - 1;
@@ -656,7 +673,7 @@ int fkb_validate(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plan
 int fkb_launch_transform(const fkb_chain_desc* chain, const fkb_plane_desc* planes, uint32_t n_planes, void* cuda_stream) {
     if (!chain || !planes) return FKB_ERR_NULL;
     for (uint32_t z = 0; z < n_planes; ++z)
-        if (planes[z].chain != 0) return FKB_ERR_INVALID;
+        if ((planes[z].chain & ~FKB_PLANE_DEFAULT) != 0) return FKB_ERR_INVALID;
     return launch_once(chain, 1, planes, n_planes, static_cast<cudaStream_t>(cuda_stream));
 }
 

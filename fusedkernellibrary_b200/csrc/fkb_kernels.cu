@@ -68,7 +68,12 @@ __global__ void __launch_bounds__(256) gather_kernel(const __grid_constant__ Lau
         const uint32_t nvalid = min(static_cast<uint32_t>(PPT), pl.dst_w - x0);
 
         float v[PPT][3];
-        if (ch.geometry == FKB_GEOM_NONE) {
+        if (pl.src == nullptr) {
+            // a plane whose read yields its default value (beyond usedPlanes of a conditional batch read)
+#pragma unroll
+            for (int n = 0; n < PPT; ++n) { v[n][0] = pl.bg[0]; v[n][1] = pl.bg[1]; v[n][2] = pl.bg[2]; }
+            apply_ops<PPT>(v, ch, pl, ch.geometry == FKB_GEOM_NONE ? 0 : ch.n_pre_ops, ch.n_ops);
+        } else if (ch.geometry == FKB_GEOM_NONE) {
 #pragma unroll
             for (int n = 0; n < PPT; ++n) {
                 if (n < nvalid) read_tap_global(ch, pl, x0 + n, y, v[n]);
@@ -76,7 +81,7 @@ __global__ void __launch_bounds__(256) gather_kernel(const __grid_constant__ Lau
             }
             apply_ops<PPT>(v, ch, pl, 0, ch.n_ops);
         } else {
-            const bool par = ch.geometry == FKB_GEOM_RESIZE_PRESERVE_AR;
+            const bool par = ch.geometry >= FKB_GEOM_RESIZE_PRESERVE_AR;
             const int ox = par ? pl.x1 : 0, oy = par ? pl.y1 : 0;
             const bool row_in = !par || (static_cast<int>(y) >= pl.y1 && static_cast<int>(y) <= pl.y2);
             const AxisTap ay = axis_tap(row_in ? static_cast<int>(y) - oy : 0, pl.fy, pl.crop_h);
@@ -366,7 +371,7 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
     constexpr uint32_t ELT = F32 ? 12u : 3u;
     const PlaneRec& pl = *w.pl;
     const fkb_chain_desc& ch = p.chains[pl.chain];
-    const bool par = ch.geometry == FKB_GEOM_RESIZE_PRESERVE_AR;
+    const bool par = ch.geometry >= FKB_GEOM_RESIZE_PRESERVE_AR;
     const int X1 = par ? pl.x1 : 0, Y1 = par ? pl.y1 : 0;
     const int X2 = par ? pl.x2 : static_cast<int>(pl.dst_w) - 1, Y2 = par ? pl.y2 : static_cast<int>(pl.dst_h) - 1;
     const int crop_w = pl.crop_w, crop_h = pl.crop_h;

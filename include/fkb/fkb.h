@@ -41,6 +41,7 @@ extern "C" {
 #endif
 
 #define FKB_ABI_VERSION 1u
+#define FKB_PLANE_DEFAULT 0x80000000u
 #define FKB_MAX_OPS 12u          /* compute ops per chain */
 #define FKB_MAX_PLANE_PARAMS 4u  /* per-plane float3 operands a chain may refer to */
 #define FKB_MAX_CHAINS 8u        /* chains of one divergent launch */
@@ -63,7 +64,11 @@ enum { FKB_PIX_U8C3 = 1, FKB_PIX_F32C3 = 2, FKB_PIX_NV12 = 3 };
 /* Geometry of the ReadBack stage.  The crop rectangle is always applied (a chain without Crop
  * passes the whole frame as the rectangle).  NONE: output pixel (x,y) reads crop pixel (x,y).
  * RESIZE_*: bilinear INTER_LINEAR through the parameters of fkb_resize_params. */
-enum { FKB_GEOM_NONE = 0, FKB_GEOM_RESIZE_IGNORE_AR = 1, FKB_GEOM_RESIZE_PRESERVE_AR = 2 };
+enum { FKB_GEOM_NONE = 0, FKB_GEOM_RESIZE_IGNORE_AR = 1, FKB_GEOM_RESIZE_PRESERVE_AR = 2,
+       /* the two other letterbox placements of the reference (resize.h:42): the target width rounded down to an even
+        * number (resize.h:212-222), and the image flush with the left edge (resize.h:176-189).  On the device they are
+        * PRESERVE_AR with other x1..y2; only fkb_resize_params tells them apart. */
+       FKB_GEOM_RESIZE_PRESERVE_AR_RN_EVEN = 3, FKB_GEOM_RESIZE_PRESERVE_AR_LEFT = 4 };
 
 /* Write kinds.  PACKED: interleaved pixels in pitched rows — PerThreadWrite<_2D,T> and
  * TensorWrite<T> (memory_operations.h:85-107, 160-179).  SPLIT: TensorSplit<float3>
@@ -119,13 +124,19 @@ typedef struct fkb_plane_desc {
     float fx, fy;            /* ResizeParams::src_conv_factors (resize.h:44-58) */
     int32_t x1, y1, x2, y2;  /* PRESERVE_AR: inclusive rectangle of the resized image inside dst */
     float bg[3];             /* PRESERVE_AR: ResizeParams::defaultValue outside that rectangle */
-    uint32_t chain;          /* divergent launch: which chain runs on this plane (0-based); else 0 */
+    uint32_t chain;          /* bits 0..30: divergent launch: which chain runs on this plane (0-based); else 0.
+                                bit 31 (FKB_PLANE_DEFAULT): a plane beyond usedPlanes of
+                                BatchRead<CONDITIONAL_WITH_DEFAULT> (batch_operations.h:221-281): its read — with a
+                                RESIZE geometry, the resized read — yields bg for every pixel and the remaining ops
+                                (all ops without a Resize, ops[n_pre_ops..) with one) run on that value; src, crop and
+                                the resize parameters are ignored.  Without a Resize the read is uchar3, so bg must
+                                hold integers in [0,255]. */
     float params[FKB_MAX_PLANE_PARAMS][3]; /* operands of ops whose plane_slot >= 0 */
 } fkb_plane_desc;
 
 /* Fills plane->fx, fy, x1, y1, x2, y2 from plane->crop_w/crop_h (the size of the back operation) and
  * plane->dst_w/dst_h, exactly as Resize<INTER_LINEAR,AR>::build does on the host (resize.h:164-233 for
- * PRESERVE_AR, 266-278 for IGNORE_AR).  geometry = FKB_GEOM_RESIZE_*. */
+ * the PRESERVE_AR family, 266-278 for IGNORE_AR).  geometry = FKB_GEOM_RESIZE_*. */
 int fkb_resize_params(uint32_t geometry, fkb_plane_desc* plane);
 
 /* Host-only check of a launch: pointer, size, pitch, rectangle, type-flow and chain-index rules.

@@ -48,7 +48,13 @@ inline void check(int status) {
 template <typename R>
 auto fold_chain(const R& read) { return read; }
 template <typename R, typename Next, typename... Rest>
-auto fold_chain(const R& read, const Next& next, const Rest&... rest) { return fold_chain(read.then(next), rest...); }
+auto fold_chain(const R& read, const Next& next, const Rest&... rest) {
+    // operations listed after the read keep a conditional batch read conditional; only an explicit .then(compute) by
+    // the caller re-batches the read with PROCESS_ALL, as the reference's fuser does
+    auto fused = read.then(next);
+    fused.st.used_planes = read.st.used_planes;
+    return fold_chain(fused, rest...);
+}
 
 template <typename Tuple, size_t... I>
 auto fold_all_but_last(const Tuple& t, std::index_sequence<I...>) { return fold_chain(std::get<I>(t)...); }
@@ -67,7 +73,10 @@ struct Lowered {
         static_assert(std::is_same_v<WT, uchar3> || std::is_same_v<WT, float3>, "uchar3 and float3 are the pixel types the B200 kernels write");
         n_planes = r.params.activeThreads.z;
         chain.src_format = st.src_format;
-        chain.geometry = !st.has_resize ? FKB_GEOM_NONE : (st.ar == AspectRatio::PRESERVE_AR ? FKB_GEOM_RESIZE_PRESERVE_AR : FKB_GEOM_RESIZE_IGNORE_AR);
+        chain.geometry = !st.has_resize ? FKB_GEOM_NONE
+                       : st.ar == AspectRatio::IGNORE_AR ? FKB_GEOM_RESIZE_IGNORE_AR
+                       : st.ar == AspectRatio::PRESERVE_AR_RN_EVEN ? FKB_GEOM_RESIZE_PRESERVE_AR_RN_EVEN
+                       : st.ar == AspectRatio::PRESERVE_AR_LEFT ? FKB_GEOM_RESIZE_PRESERVE_AR_LEFT : FKB_GEOM_RESIZE_PRESERVE_AR;
         chain.dst_format = std::is_same_v<WT, float3> ? FKB_PIX_F32C3 : FKB_PIX_U8C3;
         chain.write_kind = wr.write_kind;
         if (st.ops.size() > FKB_MAX_OPS) check(FKB_ERR_UNSUPPORTED);
@@ -114,9 +123,13 @@ struct Lowered {
         d.dst_channel_stride = wr.channel_stride;
         d.bg[0] = st.bg[0]; d.bg[1] = st.bg[1]; d.bg[2] = st.bg[2];
         d.chain = chain_index;
+        if (st.used_planes >= 0 && z >= static_cast<uint32_t>(st.used_planes)) {
+            d.chain |= FKB_PLANE_DEFAULT;
+            d.bg[0] = st.dflt[0]; d.bg[1] = st.dflt[1]; d.bg[2] = st.dflt[2];
+        }
         for (size_t k = 0; k < st.ops.size(); ++k)
             if (op_slot[k] >= 0) { const auto& v = pick(st.ops[k].v); for (int c = 0; c < 3; ++c) d.params[op_slot[k]][c] = v[c]; }
-        if (st.has_resize) check(fkb_resize_params(chain.geometry, &d));
+        if (st.has_resize && !(d.chain & FKB_PLANE_DEFAULT)) check(fkb_resize_params(chain.geometry, &d));
         return d;
     }
 };
@@ -176,6 +189,27 @@ struct Executor<DivergentBatchTransformDPP<PA, Selector>> {
 template <typename DPPType, typename... Args>
 inline void executeOperations(Stream_<DPPType::PAR_ARCH>& stream, const Args&... args) {
     Executor<DPPType>::executeOperations(stream, args...);
+}
+// the batch conveniences of core/execution_model/executors.h:80-114
+template <typename DPPType, typename I, size_t BATCH, typename... IOps>
+inline void executeOperations(const std::array<Ptr2D<I>, BATCH>& input, const int& activeBatch, const I& defaultValue,
+                              Stream_<DPPType::PAR_ARCH>& stream, const IOps&... iOps) {
+    Executor<DPPType>::executeOperations(stream, PerThreadRead<ND::_2D, I>::build(activeBatch, defaultValue, input), iOps...);
+}
+template <typename DPPType, typename I, size_t BATCH, typename... IOps>
+inline void executeOperations(const std::array<Ptr2D<I>, BATCH>& input, Stream_<DPPType::PAR_ARCH>& stream, const IOps&... iOps) {
+    Executor<DPPType>::executeOperations(stream, PerThreadRead<ND::_2D, I>::build(input), iOps...);
+}
+template <typename DPPType, typename I, typename O, size_t BATCH, typename... IOps>
+inline void executeOperations(const std::array<Ptr2D<I>, BATCH>& input, const int& activeBatch, const I& defaultValue,
+                              const Tensor<O>& output, Stream_<DPPType::PAR_ARCH>& stream, const IOps&... iOps) {
+    Executor<DPPType>::executeOperations(stream, PerThreadRead<ND::_2D, I>::build(activeBatch, defaultValue, input), iOps...,
+                                         TensorWrite<O>::build(output));
+}
+template <typename DPPType, typename I, typename O, size_t BATCH, typename... IOps>
+inline void executeOperations(const std::array<Ptr2D<I>, BATCH>& input, const Tensor<O>& output, Stream_<DPPType::PAR_ARCH>& stream,
+                              const IOps&... iOps) {
+    Executor<DPPType>::executeOperations(stream, PerThreadRead<ND::_2D, I>::build(input), iOps..., TensorWrite<O>::build(output));
 }
 
 }  // namespace fk

@@ -24,8 +24,8 @@
 namespace fk {
 
 enum class InterpolationType { INTER_LINEAR = 1 };
-enum class AspectRatio { PRESERVE_AR = 0, IGNORE_AR = 1 };
-enum class PlanePolicy { PROCESS_ALL = 0 };
+enum class AspectRatio { PRESERVE_AR = 0, IGNORE_AR = 1, PRESERVE_AR_RN_EVEN = 2, PRESERVE_AR_LEFT = 3 };  // resize.h:42
+enum class PlanePolicy { PROCESS_ALL = 0, CONDITIONAL_WITH_DEFAULT = 1 };  // batch_operations.h:75
 enum class ColorConversionCodes { COLOR_BGR2RGB, COLOR_RGB2BGR };
 
 namespace detail {
@@ -47,6 +47,9 @@ struct ReadState {
     size_t n_pre_ops{0};         // ops that were chained before the Resize run on the taps
     float ccm[9]{};
     float yuv_sub[3]{};
+    // BatchRead<CONDITIONAL_WITH_DEFAULT>: planes >= used_planes yield dflt instead of reading (-1: every plane reads)
+    int used_planes{-1};
+    float dflt[3]{0.f, 0.f, 0.f};
 };
 inline std::array<float, 3> f3(const float3& v) { return {v.x, v.y, v.z}; }
 }  // namespace detail
@@ -185,6 +188,9 @@ struct ReadIOp {
     auto then(const ComputeIOp<C, I, O>& op) const {
         static_assert(std::is_same_v<I, OutT>, "the operation's InputType is not the OutputType of the operation before it");
         detail::ReadState s = st;
+        // the reference's fuser rebuilds a batch of fused per-plane reads here with PROCESS_ALL (iop_fuser.h:89-95):
+        // a conditional batch read stops being conditional when a compute operation is fused into it
+        s.used_planes = -1;
         s.ops.push_back(detail::OpRec{C, {detail::f3(op.params)}});
         if (C == FKB_OP_YUV2RGB) { for (int i = 0; i < 9; ++i) s.ccm[i] = op.ccm[i]; for (int i = 0; i < 3; ++i) s.yuv_sub[i] = op.yuv_sub[i]; }
         return ReadIOp<O, BATCH>(std::move(s));
@@ -207,6 +213,15 @@ struct PerThreadRead {
         detail::ReadState s;
         for (const auto& p : ptrs) { const auto r = p.ptr(); s.src.push_back({r.data, r.dims.pitch, r.dims.width, r.dims.height}); }
         return ReadIOp<T, N>(std::move(s));
+    }
+    // BatchRead<CONDITIONAL_WITH_DEFAULT> (batch_operations.h:221-281, builder :530-534): planes >= usedPlanes yield
+    // defaultValue; a Resize fused behind it passes the value on as its float3 cast (iop_fuser.h:71-88)
+    template <size_t N>
+    static auto build(const int& usedPlanes, const T& defaultValue, const std::array<Ptr2D<T>, N>& ptrs) {
+        auto r = build(ptrs);
+        r.st.used_planes = usedPlanes;
+        r.st.dflt[0] = static_cast<float>(defaultValue.x); r.st.dflt[1] = static_cast<float>(defaultValue.y); r.st.dflt[2] = static_cast<float>(defaultValue.z);
+        return r;
     }
 };
 template <PixelFormat PF>

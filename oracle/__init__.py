@@ -66,8 +66,12 @@ def load_ref() -> C.CDLL:
         lib.fklref_saturate_u8.restype = C.c_uint8
         lib.fklref_saturate_u8.argtypes = [C.c_float]
         lib.fklref_resize_params.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, f32p, i32p]
+        u8p = C.POINTER(C.c_uint8)
+        lib.fklref_conditional_resize_f32.argtypes = [pp, C.c_int, C.c_int, C.c_int, C.c_int, u8p, C.c_int, C.c_int, f32p, C.c_void_p]
+        lib.fklref_conditional_pointwise_u8.argtypes = [pp, C.c_int, C.c_int, C.c_int, C.c_int, u8p, f32p, C.c_void_p]
         for name in ("fklref_crop_resize_u8", "fklref_crop_resize_f32", "fklref_crop_reorder_u8", "fklref_pointwise_u8",
-                     "fklref_nv12_resize_split", "fklref_divergent"):
+                     "fklref_nv12_resize_split", "fklref_divergent", "fklref_conditional_resize_f32",
+                     "fklref_conditional_pointwise_u8"):
             getattr(lib, name).restype = C.c_int
         _ref = lib
     return _ref
@@ -172,6 +176,15 @@ def run_ref(wl, threads: int = 1):
         offs = (C.c_float * k)(*[float(x) for x in wl.extra["offs"]])
         rc = lib.fklref_divergent(frame_ptrs(wl.planes), p0.src_w, p0.src_h, p0.src_pitch, p0.dst_w, p0.dst_h, scales, offs,
                                   outs[0].ctypes.data, outs[1].ctypes.data, k)
+    elif wl.name in ("conditional_resize", "conditional_pointwise"):
+        dflt = (C.c_uint8 * 3)(*[int(v) for v in wl.extra["default"]])
+        every = list(wl.planes)
+        if wl.name == "conditional_resize":
+            rc = lib.fklref_conditional_resize_f32(frame_ptrs(every), p0.src_w, p0.src_h, p0.src_pitch, wl.extra["used"], dflt,
+                                                   p0.dst_w, p0.dst_h, _f3(ch.ops[0].v), outs[0].ctypes.data)
+        else:
+            rc = lib.fklref_conditional_pointwise_u8(frame_ptrs(every), p0.src_w, p0.src_h, p0.src_pitch, wl.extra["used"], dflt,
+                                                     _f3(ch.ops[1].v), outs[0].ctypes.data)
     else:
         raise ValueError(f"no reference runner for workload {wl.name}")
     if rc != 0:

@@ -130,13 +130,20 @@ inline V3 read_tap(const fkb_chain_desc& ch, const fkb_plane_desc& pl, int cx, i
 }
 
 inline V3 pixel(const fkb_chain_desc& ch, const fkb_plane_desc& pl, int x, int y) {
+    if (pl.chain & FKB_PLANE_DEFAULT) {
+        // a plane beyond usedPlanes of BatchRead<CONDITIONAL_WITH_DEFAULT> (batch_operations.h:262-266): the read —
+        // including a Resize fused into it (iop_fuser.h:71-88) — yields the default value; the later ops still run
+        V3 d;
+        d.c[0] = pl.bg[0]; d.c[1] = pl.bg[1]; d.c[2] = pl.bg[2];
+        return apply_ops(d, ch, pl, ch.geometry == FKB_GEOM_NONE ? 0 : ch.n_pre_ops, ch.n_ops);
+    }
     if (ch.geometry == FKB_GEOM_NONE) {
         return apply_ops(read_tap(ch, pl, x, y), ch, pl, 0, ch.n_ops);
     }
     V3 v;
     int tx = x, ty = y;
     bool inside = true;
-    if (ch.geometry == FKB_GEOM_RESIZE_PRESERVE_AR) {
+    if (ch.geometry >= FKB_GEOM_RESIZE_PRESERVE_AR) {
         inside = x >= pl.x1 && x <= pl.x2 && y >= pl.y1 && y <= pl.y2;
         tx = x - pl.x1; ty = y - pl.y1;
     }
@@ -201,18 +208,22 @@ int fkb_oracle_resize_params(uint32_t geometry, fkb_plane_desc* pl) {
         pl->x1 = 0; pl->y1 = 0; pl->x2 = dw - 1; pl->y2 = dh - 1;
         return FKB_OK;
     }
-    if (geometry != FKB_GEOM_RESIZE_PRESERVE_AR) return FKB_ERR_INVALID;
+    if (geometry < FKB_GEOM_RESIZE_PRESERVE_AR || geometry > FKB_GEOM_RESIZE_PRESERVE_AR_LEFT) return FKB_ERR_INVALID;
+    // compute_target_size (resize.h:206-233); RN_EVEN (resize.h:212-222) evens the fitted dimension
+    const bool even = geometry == FKB_GEOM_RESIZE_PRESERVE_AR_RN_EVEN;
     const float scale = dh / static_cast<float>(sh);
     int tw = static_cast<int>(round_half_away(scale * sw)), th = dh;
+    if (even) tw = tw - (tw % 2);
     if (tw > dw) {
         const float scale2 = dw / static_cast<float>(sw);
         tw = dw;
         th = static_cast<int>(round_half_away(scale2 * sh));
+        if (even) th = th - (th % 2);
     }
     const double cfx = static_cast<double>(tw) / sw, cfy = static_cast<double>(th) / sh;
     pl->fx = static_cast<float>(1.0 / cfx);
     pl->fy = static_cast<float>(1.0 / cfy);
-    pl->x1 = (dw - tw) / 2;
+    pl->x1 = geometry == FKB_GEOM_RESIZE_PRESERVE_AR_LEFT ? 0 : (dw - tw) / 2;  // resize.h:176-178
     pl->y1 = (dh - th) / 2;
     pl->x2 = pl->x1 + tw - 1;
     pl->y2 = pl->y1 + th - 1;
@@ -225,16 +236,16 @@ int fkb_oracle_run(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_pl
                    uint32_t n_planes, uint32_t n_threads) {
     if (!chains || !planes) return FKB_ERR_NULL;
     for (uint32_t z = 0; z < n_planes; ++z)
-        if (planes[z].chain >= n_chains) return FKB_ERR_INVALID;
+        if ((planes[z].chain & ~FKB_PLANE_DEFAULT) >= n_chains) return FKB_ERR_INVALID;
     if (n_threads <= 1 || n_planes <= 1) {
-        for (uint32_t z = 0; z < n_planes; ++z) run_plane(chains[planes[z].chain], planes[z]);
+        for (uint32_t z = 0; z < n_planes; ++z) run_plane(chains[planes[z].chain & ~FKB_PLANE_DEFAULT], planes[z]);
         return FKB_OK;
     }
     if (n_threads > n_planes) n_threads = n_planes;
     std::vector<std::thread> pool;
     for (uint32_t t = 0; t < n_threads; ++t)
         pool.emplace_back([=] {
-            for (uint32_t z = t; z < n_planes; z += n_threads) run_plane(chains[planes[z].chain], planes[z]);
+            for (uint32_t z = t; z < n_planes; z += n_threads) run_plane(chains[planes[z].chain & ~FKB_PLANE_DEFAULT], planes[z]);
         });
     for (auto& th : pool) th.join();
     return FKB_OK;

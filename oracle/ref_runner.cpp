@@ -159,6 +159,13 @@ void divergent(const uint8_t* const* frames, int w, int h, int pitch, int dw, in
 
 }  // namespace
 
+template <AspectRatio AR, typename Read>
+static void letterbox_params(const Read& read, int dw, int dh, float* f2, int32_t* r4) {
+    const auto r = Resize<InterpolationType::INTER_LINEAR, AR, float3>::build(read, Size(dw, dh), make_<float3>(0.f, 0.f, 0.f));
+    f2[0] = r.params.src_conv_factors.x; f2[1] = r.params.src_conv_factors.y;
+    r4[0] = r.params.x1; r4[1] = r.params.y1; r4[2] = r.params.x2; r4[3] = r.params.y2;
+}
+
 extern "C" {
 
 int fklref_crop_resize_u8(const uint8_t* const* frames, int w, int h, int pitch, const int32_t* rects, int n,
@@ -184,6 +191,32 @@ int fklref_crop_reorder_u8(const uint8_t* const* frames, int w, int h, int pitch
     const BatchArgs a{frames, w, h, pitch, rects, rects[2], rects[3], make_<float3>(0.f, 0.f, 0.f),
                       make_<float3>(0.f, 0.f, 0.f), make_<float3>(0.f, 0.f, 0.f), out};
     FKLREF_DISPATCH(crop_reorder_u8)(a, n, n_threads);
+    return 0;
+}
+
+// BatchRead<CONDITIONAL_WITH_DEFAULT> (batch_operations.h:221-281): eight planes of which the first `used` are read;
+// the others yield `dflt`.  Two chains: with a Resize (the default value passes through the fused ReadBack as its
+// float3 cast, then Mul), and without (Cast -> Mul -> SaturateCast on the uchar3 default).
+int fklref_conditional_resize_f32(const uint8_t* const* frames, int w, int h, int pitch, int used, const uint8_t* dflt,
+                                  int dw, int dh, const float* mul, float* out) {
+    CpuStream stream;
+    std::array<Ptr2D<uchar3>, 8> ptrs;
+    for (size_t i = 0; i < 8; ++i) ptrs[i] = wrap_frame(frames[i], w, h, pitch);
+    Tensor<float3> t(reinterpret_cast<float3*>(out), dw, dh, 8, 1, MemType::Host, 0);
+    executeOperations<CpuDPP>(stream, PerThreadRead<ND::_2D, uchar3>::build(used, make_<uchar3>(dflt[0], dflt[1], dflt[2]), ptrs),
+        Resize<InterpolationType::INTER_LINEAR, AspectRatio::IGNORE_AR>::build(Size(dw, dh)),
+        Mul<float3>::build(make_<float3>(mul[0], mul[1], mul[2])), TensorWrite<float3>::build(t));
+    return 0;
+}
+int fklref_conditional_pointwise_u8(const uint8_t* const* frames, int w, int h, int pitch, int used, const uint8_t* dflt,
+                                    const float* mul, uint8_t* out) {
+    CpuStream stream;
+    std::array<Ptr2D<uchar3>, 8> ptrs;
+    for (size_t i = 0; i < 8; ++i) ptrs[i] = wrap_frame(frames[i], w, h, pitch);
+    Tensor<uchar3> t(reinterpret_cast<uchar3*>(out), w, h, 8, 1, MemType::Host, 0);
+    executeOperations<CpuDPP>(stream, PerThreadRead<ND::_2D, uchar3>::build(used, make_<uchar3>(dflt[0], dflt[1], dflt[2]), ptrs),
+        Cast<uchar3, float3>::build(), Mul<float3>::build(make_<float3>(mul[0], mul[1], mul[2])),
+        SaturateCast<float3, uchar3>::build(), TensorWrite<uchar3>::build(t));
     return 0;
 }
 
@@ -237,18 +270,21 @@ void fklref_bt709_full_matrix(float* m9) {
 
 uint8_t fklref_saturate_u8(float v) { return cxp::saturate_cast<uchar>::f(v); }
 
-// Resize<INTER_LINEAR,AR>::build on a w x h source: returns fx, fy, x1, y1, x2, y2 (AR: 0 PRESERVE_AR, 1 IGNORE_AR).
-void fklref_resize_params(int sw, int sh, int dw, int dh, int ignore_ar, float* f2, int32_t* r4) {
+// Resize<INTER_LINEAR,AR>::build on a w x h source: returns fx, fy, x1, y1, x2, y2.  `ar` is the reference's own
+// AspectRatio value: 0 PRESERVE_AR, 1 IGNORE_AR, 2 PRESERVE_AR_RN_EVEN, 3 PRESERVE_AR_LEFT.
+void fklref_resize_params(int sw, int sh, int dw, int dh, int ar, float* f2, int32_t* r4) {
     static uchar3 dummy;
     const auto read = PerThreadRead<ND::_2D, uchar3>::build(RawPtr<ND::_2D, uchar3>{&dummy, {static_cast<uint>(sw), static_cast<uint>(sh), static_cast<uint>(sw * 3)}});
-    if (ignore_ar) {
+    if (ar == 1) {
         const auto r = Resize<InterpolationType::INTER_LINEAR, AspectRatio::IGNORE_AR>::build(read, Size(dw, dh));
         f2[0] = r.params.src_conv_factors.x; f2[1] = r.params.src_conv_factors.y;
         r4[0] = 0; r4[1] = 0; r4[2] = dw - 1; r4[3] = dh - 1;
+    } else if (ar == 2) {
+        letterbox_params<AspectRatio::PRESERVE_AR_RN_EVEN>(read, dw, dh, f2, r4);
+    } else if (ar == 3) {
+        letterbox_params<AspectRatio::PRESERVE_AR_LEFT>(read, dw, dh, f2, r4);
     } else {
-        const auto r = Resize<InterpolationType::INTER_LINEAR, AspectRatio::PRESERVE_AR, float3>::build(read, Size(dw, dh), make_<float3>(0.f, 0.f, 0.f));
-        f2[0] = r.params.src_conv_factors.x; f2[1] = r.params.src_conv_factors.y;
-        r4[0] = r.params.x1; r4[1] = r.params.y1; r4[2] = r.params.x2; r4[3] = r.params.y2;
+        letterbox_params<AspectRatio::PRESERVE_AR>(read, dw, dh, f2, r4);
     }
 }
 

@@ -142,7 +142,8 @@ static void test_nv12() {
 }
 
 // ---- batched crop-resize-normalise over several frames --------------------------------------------------------------
-static void test_batched() {
+template <AspectRatio AR>
+static void test_batched(const char* what, uint32_t geometry) {
     Stream stream;
     constexpr size_t FRAMES = 3, PER = 4, BATCH = FRAMES * PER;
     std::vector<Ptr2D<uchar3>> frames;
@@ -159,12 +160,12 @@ static void test_batched() {
     }
     Tensor<float3> out(96, 80, BATCH);
     executeOperations<TransformDPP<>>(stream, PerThreadRead<ND::_2D, uchar3>::build(ptrs), Crop<>::build(rects),
-        Resize<InterpolationType::INTER_LINEAR, AspectRatio::PRESERVE_AR>::build(Size(96, 80), make_<float3>(114.f, 114.f, 114.f)),
+        Resize<InterpolationType::INTER_LINEAR, AR>::build(Size(96, 80), make_<float3>(114.f, 114.f, 114.f)),
         Mul<float3>::build(make_set<float3>(1.f / 255.f)), TensorWrite<float3>::build(out));
     out.download(stream);
     stream.sync();
     fkb_chain_desc ch{};
-    ch.src_format = FKB_PIX_U8C3; ch.geometry = FKB_GEOM_RESIZE_PRESERVE_AR; ch.dst_format = FKB_PIX_F32C3; ch.write_kind = FKB_WRITE_PACKED;
+    ch.src_format = FKB_PIX_U8C3; ch.geometry = geometry; ch.dst_format = FKB_PIX_F32C3; ch.write_kind = FKB_WRITE_PACKED;
     ch.n_ops = 1; ch.ops[0] = op(FKB_OP_MUL, 1.f / 255.f, 1.f / 255.f, 1.f / 255.f);
     std::vector<float> want(96 * 80 * 3 * BATCH);
     std::vector<fkb_plane_desc> planes;
@@ -174,7 +175,34 @@ static void test_batched() {
         planes.push_back(d);
     }
     fkb_oracle_run(&ch, 1, planes.data(), BATCH, 1);
-    report("batched crop-resize-normalise", std::memcmp(want.data(), out.ptrPinned().data, want.size() * 4) == 0);
+    report(what, std::memcmp(want.data(), out.ptrPinned().data, want.size() * 4) == 0);
+}
+
+// ---- conditional batch read: planes beyond activeBatch come out as the operations applied to the default value -----
+static void test_conditional_batch() {
+    Stream stream;
+    constexpr size_t BATCH = 6;
+    const int used = 4;
+    std::array<Ptr2D<uchar3>, BATCH> ptrs;
+    for (size_t i = 0; i < BATCH; ++i) { ptrs[i] = Ptr2D<uchar3>(200, 120); fill_random(ptrs[i], 300 + i); ptrs[i].upload(stream); }
+    Tensor<float3> out(64, 48, BATCH);
+    const uchar3 dflt = make_<uchar3>(9, 250, 77);
+    executeOperations<TransformDPP<>>(ptrs, used, dflt, out, stream, Resize<InterpolationType::INTER_LINEAR>::build(Size(64, 48)),
+                                      Mul<float3>::build(make_<float3>(0.5f, 2.f, 1.f / 3.f)));
+    out.download(stream);
+    stream.sync();
+    fkb_chain_desc ch{};
+    ch.src_format = FKB_PIX_U8C3; ch.geometry = FKB_GEOM_RESIZE_IGNORE_AR; ch.dst_format = FKB_PIX_F32C3; ch.write_kind = FKB_WRITE_PACKED;
+    ch.n_ops = 1; ch.ops[0] = op(FKB_OP_MUL, 0.5f, 2.f, 1.f / 3.f);
+    std::vector<float> want(64 * 48 * 3 * BATCH);
+    std::vector<fkb_plane_desc> planes;
+    for (size_t i = 0; i < BATCH; ++i) {
+        fkb_plane_desc d = host_plane(ptrs[i], Rect(0, 0, 200, 120), 64, 48, want.data() + i * 64 * 48 * 3, 64 * 12, ch.geometry);
+        if (static_cast<int>(i) >= used) { d.chain |= FKB_PLANE_DEFAULT; d.bg[0] = 9.f; d.bg[1] = 250.f; d.bg[2] = 77.f; }
+        planes.push_back(d);
+    }
+    fkb_oracle_run(&ch, 1, planes.data(), BATCH, 1);
+    report("conditional batch read (activeBatch, defaultValue)", std::memcmp(want.data(), out.ptrPinned().data, want.size() * 4) == 0);
 }
 
 // ---- divergent horizontal fusion: two sequences in one launch, global plane indices ------------------------------------
@@ -239,7 +267,10 @@ int main() {
     test_readme();
     test_vertical_fusion();
     test_nv12();
-    test_batched();
+    test_batched<AspectRatio::PRESERVE_AR>("batched crop-resize-normalise", FKB_GEOM_RESIZE_PRESERVE_AR);
+    test_batched<AspectRatio::PRESERVE_AR_RN_EVEN>("batched crop-resize-normalise, PRESERVE_AR_RN_EVEN", FKB_GEOM_RESIZE_PRESERVE_AR_RN_EVEN);
+    test_batched<AspectRatio::PRESERVE_AR_LEFT>("batched crop-resize-normalise, PRESERVE_AR_LEFT", FKB_GEOM_RESIZE_PRESERVE_AR_LEFT);
+    test_conditional_batch();
     test_divergent();
     test_errors();
     std::printf("%s\n", g_failed ? "FAILED" : "ALL PASSED");

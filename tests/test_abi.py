@@ -61,7 +61,7 @@ def test_resize_params_match_oracle():
     rs = np.random.RandomState(2)
     for _ in range(5000):
         sw, sh, dw, dh = (int(v) for v in rs.randint(1, 2000, 4))
-        for geom in (abi.GEOM_RESIZE_IGNORE_AR, abi.GEOM_RESIZE_PRESERVE_AR):
+        for geom in (abi.GEOM_RESIZE_IGNORE_AR, abi.GEOM_RESIZE_PRESERVE_AR, abi.GEOM_RESIZE_PRESERVE_AR_RN_EVEN, abi.GEOM_RESIZE_PRESERVE_AR_LEFT):
             a, b = abi.PlaneDesc(), abi.PlaneDesc()
             for d in (a, b):
                 d.crop_w, d.crop_h, d.dst_w, d.dst_h = sw, sh, dw, dh

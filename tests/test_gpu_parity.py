@@ -76,6 +76,8 @@ SMALL = {
     "divergent": lambda: W.divergent_planes(n_per_seq=4, w=480, h=270),
     "divergent_odd": lambda: W.divergent_planes(n_per_seq=3, w=330, h=190),
     "crop_reorder": lambda: W.crop_reorder(n=5),
+    "conditional_resize": lambda: W.conditional_resize(),
+    "conditional_pointwise": lambda: W.conditional_pointwise(),
 }
 
 

@@ -83,13 +83,18 @@ def test_resize_params_against_reference():
     rs = np.random.RandomState(1)
     for _ in range(3000):
         sw, sh, dw, dh = (int(v) for v in rs.randint(1, 700, 4))
-        for ignore in (0, 1):
+        # the reference's AspectRatio value -> this library's geometry code
+        for ar, geom in ((0, abi.GEOM_RESIZE_PRESERVE_AR), (1, abi.GEOM_RESIZE_IGNORE_AR),
+                         (2, abi.GEOM_RESIZE_PRESERVE_AR_RN_EVEN), (3, abi.GEOM_RESIZE_PRESERVE_AR_LEFT)):
             f2, r4 = (C.c_float * 2)(), (C.c_int32 * 4)()
-            ref.fklref_resize_params(sw, sh, dw, dh, ignore, f2, r4)
+            ref.fklref_resize_params(sw, sh, dw, dh, ar, f2, r4)
             d = abi.PlaneDesc()
             d.crop_w, d.crop_h, d.dst_w, d.dst_h = sw, sh, dw, dh
-            lib.fkb_oracle_resize_params(abi.GEOM_RESIZE_IGNORE_AR if ignore else abi.GEOM_RESIZE_PRESERVE_AR, C.byref(d))
-            assert (d.fx, d.fy, d.x1, d.y1, d.x2, d.y2) == (f2[0], f2[1], r4[0], r4[1], r4[2], r4[3]), (sw, sh, dw, dh, ignore)
+            lib.fkb_oracle_resize_params(geom, C.byref(d))
+            got = (d.fx, d.fy, d.x1, d.y1, d.x2, d.y2)
+            want = (f2[0], f2[1], r4[0], r4[1], r4[2], r4[3])
+            # a target that rounds to zero divides by zero in both (inf, or nan for 0/0): compare those by class
+            assert all(g == w or (np.isnan(g) and np.isnan(w)) for g, w in zip(got, want)), (sw, sh, dw, dh, ar, got, want)
 
 
 @pytest.mark.parametrize("name", GOLDEN_CASES)
@@ -105,6 +110,7 @@ def test_oracle_matches_golden_fixture(name):
     W.readme_crops(), W.vertical_fusion(w=1000, h=300), W.nv12_preprocess(w=1280, h=720, dst=(320, 320)),
     W.batched_crop_resize(n_frames=4, crops_per_frame=8, w=960, h=540), W.divergent_planes(n_per_seq=4, w=480, h=270),
     W.divergent_planes(n_per_seq=1, w=200, h=100), W.crop_reorder(n=5),
+    W.conditional_resize(), W.conditional_resize(used=0), W.conditional_resize(used=8), W.conditional_pointwise(),
 ], ids=lambda w: w.name)
 def test_oracle_matches_reference_backend(wl):
     got, want = oracle.run_oracle(wl, threads=4), oracle.run_ref(wl, threads=4)

@@ -233,9 +233,12 @@ def other_configs(torch, steps: int, peak: float) -> dict:
             with torch.cuda.graph(graph, stream=side):
                 for s in sets:
                     s.launch_plan()
-        rounds = max(3, steps // n_sets)
+        rounds = max(30, steps)  # these launches last microseconds: many replays, and the median of five measurements
         graph.replay()
-        dt = time_launches(graph.replay, rounds, torch) / (rounds * n_sets)
+
+        def median_time(replay):
+            return sorted(time_launches(replay, rounds, torch) / (rounds * n_sets) for _ in range(5))[2]
+        dt = median_time(graph.replay)
         ref_us = None
         try:
             import oracle
@@ -251,14 +254,14 @@ def other_configs(torch, steps: int, peak: float) -> dict:
                             for fn in launchers:
                                 fn()
                     ref_graph.replay()
-                    ref_us = time_launches(ref_graph.replay, rounds, torch) / (rounds * n_sets) * 1e6
+                    ref_us = median_time(ref_graph.replay) * 1e6
                     del ref_graph
         except Exception as exc:  # the comparison is optional; the product's figures never depend on it
             ref_us = f"failed: {exc}"
         out[name] = {"us_per_launch": dt * 1e6, "reference_cuda_us_per_launch": ref_us, "gpix_s": wl.out_pixels / dt / 1e9, "alg_bytes": alg["total"],
                      "hbm_gbs": alg["total"] / dt / 1e9, "frac_of_measured_peak": alg["total"] / dt / 1e9 / peak,
                      "buffer_sets_rotated": n_sets, "kernels_per_launch": sets[0].kernel_launches(),
-                     "timing": "CUDA graph of one round over the buffer sets, replayed"}
+                     "timing": "CUDA graph of one round over the buffer sets, replayed; median of five measurements"}
         del graph
         for s in sets:
             s.close()

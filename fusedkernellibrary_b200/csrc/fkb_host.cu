@@ -56,7 +56,8 @@ int check_ops(const fkb_chain_desc& ch, uint32_t first, uint32_t last, ValueType
 }
 
 int check_chain(const fkb_chain_desc& ch) {
-    if (ch.src_format != FKB_PIX_U8C3 && ch.src_format != FKB_PIX_NV12) return FKB_ERR_UNSUPPORTED;
+    if (ch.src_format != FKB_PIX_U8C3 && ch.src_format != FKB_PIX_NV12 && ch.src_format != FKB_PIX_NV21 &&
+        ch.src_format != FKB_PIX_UYVY) return FKB_ERR_UNSUPPORTED;
     if (ch.dst_format != FKB_PIX_U8C3 && ch.dst_format != FKB_PIX_F32C3) return FKB_ERR_UNSUPPORTED;
     if (ch.geometry > FKB_GEOM_RESIZE_PRESERVE_AR_LEFT) return FKB_ERR_UNSUPPORTED;
     if (ch.write_kind != FKB_WRITE_PACKED && ch.write_kind != FKB_WRITE_SPLIT) return FKB_ERR_UNSUPPORTED;
@@ -77,11 +78,13 @@ int check_chain(const fkb_chain_desc& ch) {
 int check_plane(const fkb_chain_desc& ch, const fkb_plane_desc& pl) {
     const bool dflt = (pl.chain & FKB_PLANE_DEFAULT) != 0;  // the read yields bg: no source is touched
     if ((!dflt && !pl.src) || !pl.dst) return FKB_ERR_NULL;
-    const bool nv12 = ch.src_format == FKB_PIX_NV12;
+    const bool nv12 = ch.src_format == FKB_PIX_NV12 || ch.src_format == FKB_PIX_NV21;  // luma plane + interleaved chroma rows
+    const bool uyvy = ch.src_format == FKB_PIX_UYVY;
     if (!dflt) {
         if (nv12 && !pl.src_chroma) return FKB_ERR_NULL;
         if (pl.src_w == 0 || pl.src_h == 0) return FKB_ERR_INVALID;
-        const uint64_t src_row = nv12 ? ((static_cast<uint64_t>(pl.src_w) + 1) / 2) * 2 : static_cast<uint64_t>(pl.src_w) * 3;
+        const uint64_t src_row = nv12 ? ((static_cast<uint64_t>(pl.src_w) + 1) / 2) * 2
+                                 : uyvy ? ((static_cast<uint64_t>(pl.src_w) + 1) / 2) * 4 : static_cast<uint64_t>(pl.src_w) * 3;
         if (pl.src_pitch < src_row) return FKB_ERR_INVALID;
         if (pl.crop_w <= 0 || pl.crop_h <= 0) return FKB_ERR_INVALID;
         if (static_cast<uint64_t>(pl.crop_x) + static_cast<uint64_t>(pl.crop_w) > pl.src_w ||
@@ -155,7 +158,7 @@ void classify(const fkb_chain_desc& ch, PlaneRec& r) {
     r.tile_w = r.tile_h = r.tiles_x = r.tiles_y = 0;
     r.in_stride = r.out_stride = 0;
     if (force_gather()) return;
-    if (ch.src_format == FKB_PIX_NV12 && ch.geometry != FKB_GEOM_NONE && ch.n_pre_ops == 1 && ch.ops[0].code == FKB_OP_YUV2RGB &&
+    if ((ch.src_format == FKB_PIX_NV12 || ch.src_format == FKB_PIX_NV21) && ch.geometry != FKB_GEOM_NONE && ch.n_pre_ops == 1 && ch.ops[0].code == FKB_OP_YUV2RGB &&
         post_kind_of(ch) != 8u && !(ch.geometry >= FKB_GEOM_RESIZE_PRESERVE_AR && (r.x2 < r.x1 || r.y2 < r.y1)) &&
         (reinterpret_cast<uintptr_t>(r.src_chroma) & 1) == 0 && (r.src_pitch & 1) == 0) {  // UV pairs are read as 16-bit words
         r.kclass = KCLASS_NV12;  // NV12 -> RGB on the taps -> resize -> [Mul][Add|Sub][Div][SaturateCast]: nv12_kernel
@@ -384,9 +387,11 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         std::memcpy(k.m, imm.m, sizeof(k.m)); std::memcpy(k.a, imm.a, sizeof(k.a)); std::memcpy(k.d, imm.d, sizeof(k.d));
         k.kind = post_kind_of(ch); k.chain = c; k.slots = imm.slots;
         k.preserve_ar = ch.geometry >= FKB_GEOM_RESIZE_PRESERVE_AR; k.f32 = ch.dst_format == FKB_PIX_F32C3; k.split = ch.write_kind == FKB_WRITE_SPLIT;
-        // nv12_pair_kernel's conditions: the colour matrix of the YCbCr standards ([1 0 r; 1 g1 g2; 1 b 0]), integer
+        // nv12_pair_kernel's conditions: the colour matrix of the YCbCr standards ([s 0 r; s g1 g2; s b 0]), integer
         // offsets, immediate operands, and plane offsets that fit 32 bits
-        bool pair = !imm.slots && k.ccm[0] == 1.f && k.ccm[3] == 1.f && k.ccm[6] == 1.f && k.ccm[1] == 0.f && k.ccm[8] == 0.f;
+        k.vu = ch.src_format == FKB_PIX_NV21;
+        bool pair = !imm.slots && k.ccm[0] > 0.f && std::isfinite(k.ccm[0]) && k.ccm[3] == k.ccm[0] && k.ccm[6] == k.ccm[0] &&
+                    k.ccm[1] == 0.f && k.ccm[8] == 0.f;
         for (int i = 0; i < 3; ++i) {
             pair = pair && k.sub[i] >= 0.f && k.sub[i] <= 255.f && k.sub[i] == std::floor(k.sub[i]);
             k.kmag[i] = 8388608.f + (pair ? k.sub[i] : 0.f);
@@ -663,6 +668,26 @@ int fkb_resize_params(uint32_t geometry, fkb_plane_desc* pl) {
     pl->y1 = (dh - th) / 2;
     pl->x2 = pl->x1 + tw - 1;
     pl->y2 = pl->y1 + th - 1;
+    return FKB_OK;
+}
+
+int fkb_ycbcr_to_rgb(uint32_t range, uint32_t primitives, float ccm[9], float yuv_sub[3]) {
+    if (!ccm || !yuv_sub) return FKB_ERR_NULL;
+    if (range > FKB_RANGE_FULL || primitives > FKB_PRIMITIVES_BT2020) return FKB_ERR_INVALID;
+    // luma weights of Rec. BT.601 / BT.709 / BT.2020; every step below is an fp32 operation, in this order
+    static const float kKr[3] = {0.299f, 0.2126f, 0.2627f}, kKb[3] = {0.114f, 0.0722f, 0.0593f};
+    const float Kr = kKr[primitives], Kb = kKb[primitives];
+    const float Kg = 1.0f - Kr - Kb;
+    float m[3][3] = {{1.0f, 0.0f, 2.0f * (1.0f - Kr)},
+                     {1.0f, -2.0f * Kb * (1.0f - Kb) / Kg, -2.0f * Kr * (1.0f - Kr) / Kg},
+                     {1.0f, 2.0f * (1.0f - Kb), 0.0f}};
+    if (range == FKB_RANGE_LIMITED) {  // 8 bit: luma spans 219 codes from 16, chroma 224 around 128
+        const float scale_y = 255.f / 219.f, scale_c = 255.f / 224.f;
+        for (int i = 0; i < 3; ++i) { m[i][0] *= scale_y; m[i][1] *= scale_c; m[i][2] *= scale_c; }
+    }
+    for (int i = 0; i < 9; ++i) ccm[i] = m[i / 3][i % 3];
+    yuv_sub[0] = range == FKB_RANGE_LIMITED ? 16.f : 0.f;  // full range subtracts nothing from the luma
+    yuv_sub[1] = yuv_sub[2] = 128.f;
     return FKB_OK;
 }
 

@@ -32,11 +32,17 @@ __device__ __forceinline__ const PlaneRec* plane_table(const LaunchParams& p) {
 
 __device__ __forceinline__ void read_tap_global(const fkb_chain_desc& ch, const PlaneRec& pl, int cx, int cy, float (&o)[3]) {
     const size_t X = static_cast<size_t>(cx) + pl.crop_x, Y = static_cast<size_t>(cy) + pl.crop_y;
-    if (ch.src_format == FKB_PIX_NV12) {
+    if (ch.src_format == FKB_PIX_NV12 || ch.src_format == FKB_PIX_NV21) {
         const uint8_t* uv = pl.src_chroma + (Y >> 1) * pl.src_pitch + (X >> 1) * 2;
+        const uint32_t vu = ch.src_format == FKB_PIX_NV21;  // V first
         o[0] = static_cast<float>(__ldg(pl.src + Y * pl.src_pitch + X));
-        o[1] = static_cast<float>(__ldg(uv));
-        o[2] = static_cast<float>(__ldg(uv + 1));
+        o[1] = static_cast<float>(__ldg(uv + vu));
+        o[2] = static_cast<float>(__ldg(uv + (vu ^ 1u)));
+    } else if (ch.src_format == FKB_PIX_UYVY) {
+        const uint8_t* g = pl.src + Y * pl.src_pitch + (X >> 1) * 4;  // U Y0 V Y1
+        o[0] = static_cast<float>(__ldg(g + 1 + 2 * (X & 1)));
+        o[1] = static_cast<float>(__ldg(g));
+        o[2] = static_cast<float>(__ldg(g + 2));
     } else {
         const uint8_t* q = pl.src + Y * pl.src_pitch + X * 3;
         o[0] = static_cast<float>(__ldg(q));
@@ -641,8 +647,8 @@ __device__ __forceinline__ void nv12_pixel(const LaunchParams& p, const PlaneRec
         for (int t = 0; t < 4; ++t) {
             const float yy = static_cast<float>(lum[t]);
             const float a = k.sub[0] != 0.f ? __fsub_rn(yy, k.sub[0]) : yy;  // x - 0 is x
-            const float b = __fsub_rn(static_cast<float>(chr[t] & 0xffu), k.sub[1]);
-            const float d = __fsub_rn(static_cast<float>(chr[t] >> 8), k.sub[2]);
+            const float b = __fsub_rn(static_cast<float>(k.vu ? chr[t] >> 8 : chr[t] & 0xffu), k.sub[1]);
+            const float d = __fsub_rn(static_cast<float>(k.vu ? chr[t] & 0xffu : chr[t] >> 8), k.sub[2]);
 #pragma unroll
             for (int c = 0; c < 3; ++c) {
                 const float rgb = __fadd_rn(__fadd_rn(__fmul_rn(a, k.ccm[3 * c]), __fmul_rn(b, k.ccm[3 * c + 1])), __fmul_rn(d, k.ccm[3 * c + 2]));
@@ -697,11 +703,11 @@ __global__ void __launch_bounds__(256, 8) nv12_kernel(const __grid_constant__ La
 }
 
 // nv12_pair_kernel: the same chain for the colour matrices every YCbCr standard uses, two output pixels per thread.
-// Conditions (checked on the host): the matrix has the shape [1 0 r; 1 g1 g2; 1 b 0], the offsets are integers in
-// [0,255], the operands are immediates, and every offset into a plane fits 32 bits.  Under them
-//   * (Y*1 + Cb*0) + Cr*r == Y + Cr*r bit for bit (x*1 is x; a finite x times 0 is a zero, and adding a zero of either
-//     sign to a value that is never -0 changes nothing; Y - offset is an exact integer difference, so its zero is +0),
-//     and likewise for the blue row, which drops seven of the fifteen operations per tap;
+// Conditions (checked on the host): the matrix has the shape [s 0 r; s g1 g2; s b 0] with s > 0, the offsets are
+// integers in [0,255], the operands are immediates, and every offset into a plane fits 32 bits.  Under them
+//   * (Y*s + Cb*0) + Cr*r == Y*s + Cr*r bit for bit (a finite x times 0 is a zero, and adding a zero of either sign to
+//     a value that is never -0 changes nothing: Y - offset is an exact integer difference, so its zero is +0, and so
+//     is that zero times a positive s), and likewise for the blue row, which drops six of the fifteen operations per tap;
 //   * byte - offset is computed as (2^23 + byte) - (2^23 + offset): one byte-permute and one exact subtraction;
 //   * the two pixels of a thread share every coefficient, so the arithmetic runs as packed f32x2 operations.
 // A product that feeds only a sum is written as fma(a, b, -0), which the assembler cannot contract with the sum.
@@ -712,7 +718,7 @@ struct PairTaps {
 __device__ __forceinline__ f2 magic_pair(uint32_t wa, uint32_t wb, uint32_t sel) {
     return f2{__uint_as_float(__byte_perm(wa, 0x4B000000u, sel)), __uint_as_float(__byte_perm(wb, 0x4B000000u, sel))};
 }
-template <bool INLINE>
+template <bool SCALED_LUMA, bool VU>
 __device__ __forceinline__ void nv12_pair(const LaunchParams& p, const PlaneRec& pl, uint32_t xa, uint32_t y) {
     if (pl.kclass != KCLASS_NV12) return;
     if (xa >= pl.dst_w || y >= pl.dst_h) return;
@@ -746,16 +752,18 @@ __device__ __forceinline__ void nv12_pair(const LaunchParams& p, const PlaneRec&
     const f2 wx0{ta.w0, tb.w0}, wx1{ta.w1, tb.w1};
     const f2 w[4] = {mul2(wx0, wy0), mul2(wx1, wy0), mul2(wx0, wy1), mul2(wx1, wy1)};
     const f2 ky{-k.kmag[0], -k.kmag[0]}, ku{-k.kmag[1], -k.kmag[1]}, kv{-k.kmag[2], -k.kmag[2]};
-    const f2 cr{k.ccm[2], k.ccm[2]}, cg1{k.ccm[4], k.ccm[4]}, cg2{k.ccm[5], k.ccm[5]}, cbl{k.ccm[7], k.ccm[7]};
+    const f2 cr{k.ccm[2], k.ccm[2]}, cg1{k.ccm[4], k.ccm[4]}, cg2{k.ccm[5], k.ccm[5]}, cbl{k.ccm[7], k.ccm[7]}, cy{k.ccm[0], k.ccm[0]};
+    constexpr uint32_t sel_u = VU ? 0x7441u : 0x7440u, sel_v = VU ? 0x7440u : 0x7441u;  // which byte of a chroma pair is Cb
     f2 acc[3];
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
         const f2 yy = add2(magic_pair(la[t], lb[t], 0x7440u), ky);
-        const f2 uu = add2(magic_pair(ca[t], cb[t], 0x7440u), ku);
-        const f2 vv = add2(magic_pair(ca[t], cb[t], 0x7441u), kv);
-        const f2 r = add2(yy, mul2_unfusable(vv, cr, nz));
-        const f2 g = add2(add2(yy, mul2_unfusable(uu, cg1, nz)), mul2_unfusable(vv, cg2, nz));
-        const f2 b = add2(yy, mul2_unfusable(uu, cbl, nz));
+        const f2 uu = add2(magic_pair(ca[t], cb[t], sel_u), ku);
+        const f2 vv = add2(magic_pair(ca[t], cb[t], sel_v), kv);
+        const f2 ys = SCALED_LUMA ? mul2_unfusable(yy, cy, nz) : yy;  // the luma column is 1 for full range, and x * 1 is x
+        const f2 r = add2(ys, mul2_unfusable(vv, cr, nz));
+        const f2 g = add2(add2(ys, mul2_unfusable(uu, cg1, nz)), mul2_unfusable(vv, cg2, nz));
+        const f2 b = add2(ys, mul2_unfusable(uu, cbl, nz));
         const f2 tr = mul2_unfusable(r, w[t], nz), tg = mul2_unfusable(g, w[t], nz), tbb = mul2_unfusable(b, w[t], nz);
         acc[0] = t == 0 ? tr : add2(acc[0], tr);
         acc[1] = t == 0 ? tg : add2(acc[1], tg);
@@ -809,13 +817,16 @@ __device__ __forceinline__ void nv12_pair(const LaunchParams& p, const PlaneRec&
     }
 }
 
-template <int THREADS, int MINB>
+template <int THREADS, int MINB, bool SCALED_LUMA, bool VU>
 __global__ void __launch_bounds__(THREADS, MINB) nv12_pair_kernel(const __grid_constant__ LaunchParams p) {
     const uint32_t x = (blockIdx.x * 32 + (threadIdx.x & 31)) * 2, y = blockIdx.y * (THREADS / 32) + (threadIdx.x >> 5);
+    // three copies of the body, so that each knows where its plane record lives: the single plane of a one-plane launch
+    // (every field a constant-bank operand, the pointers uniform), one of a few kernel-parameter records, or a table entry
     if (p.table == nullptr) {
-        for (uint32_t z = blockIdx.z; z < p.n_planes; z += gridDim.z) nv12_pair<true>(p, p.inline_planes[z], x, y);
+        if (p.n_planes == 1) nv12_pair<SCALED_LUMA, VU>(p, p.inline_planes[0], x, y);
+        else for (uint32_t z = blockIdx.z; z < p.n_planes; z += gridDim.z) nv12_pair<SCALED_LUMA, VU>(p, p.inline_planes[z], x, y);
     } else {
-        for (uint32_t z = blockIdx.z; z < p.n_planes; z += gridDim.z) nv12_pair<false>(p, p.table[z], x, y);
+        for (uint32_t z = blockIdx.z; z < p.n_planes; z += gridDim.z) nv12_pair<SCALED_LUMA, VU>(p, p.table[z], x, y);
     }
 }
 
@@ -998,7 +1009,14 @@ cudaError_t launch_lut(const LaunchParams& p, uint32_t grid, cudaStream_t stream
 
 cudaError_t launch_nv12(const LaunchParams& p, dim3 grid, cudaStream_t stream) {
     // the pair kernel runs 128-thread CTAs (four rows of 64 pixels), ten per SM: more, smaller CTAs shorten the tail
-    if (p.nv12.pair) nv12_pair_kernel<128, 10><<<dim3(grid.x, grid.y * 2, grid.z), 128, 0, stream>>>(p);
+    if (p.nv12.pair) {
+        const dim3 g(grid.x, grid.y * 2, grid.z);
+        const bool scaled = p.nv12.ccm[0] != 1.f;
+        if (scaled && p.nv12.vu) nv12_pair_kernel<128, 10, true, true><<<g, 128, 0, stream>>>(p);
+        else if (scaled) nv12_pair_kernel<128, 10, true, false><<<g, 128, 0, stream>>>(p);
+        else if (p.nv12.vu) nv12_pair_kernel<128, 10, false, true><<<g, 128, 0, stream>>>(p);
+        else nv12_pair_kernel<128, 10, false, false><<<g, 128, 0, stream>>>(p);
+    }
     else nv12_kernel<<<grid, 256, 0, stream>>>(p);
     return cudaGetLastError();
 }

@@ -93,7 +93,7 @@ class Workload:
             d = arr[i]
             ch = self.chains[s.chain]
             d.src = src_addrs[s.src]
-            d.src_chroma = src_addrs[s.src] + s.chroma_offset if ch.src_format == abi.PIX_NV12 else None
+            d.src_chroma = src_addrs[s.src] + s.chroma_offset if ch.src_format in (abi.PIX_NV12, abi.PIX_NV21) else None
             d.dst = dst_addrs[s.dst] + s.dst_offset
             d.src_pitch, d.src_w, d.src_h = s.src_pitch, s.src_w, s.src_h
             d.crop_x, d.crop_y, d.crop_w, d.crop_h = s.crop
@@ -120,14 +120,15 @@ class Workload:
         out_bytes = 0
         for s in self.planes:
             ch = self.chains[s.chain]
-            nv12 = ch.src_format == abi.PIX_NV12
+            uyvy = ch.src_format == abi.PIX_UYVY
+            nv12 = ch.src_format in (abi.PIX_NV12, abi.PIX_NV21) or uyvy  # one luma byte per pixel, one chroma pair per 2 (x2) pixels
             elt = 12 if ch.dst_format == abi.PIX_F32C3 else 3
             out_bytes += s.dst_w * s.dst_h * elt
             if s.default:
                 continue
             if s.src not in masks:
                 masks[s.src] = (np.zeros((s.src_h, s.src_w), bool),
-                                np.zeros(((s.src_h + 1) // 2, (s.src_w + 1) // 2), bool) if nv12 else None)
+                                np.zeros((s.src_h if uyvy else (s.src_h + 1) // 2, (s.src_w + 1) // 2), bool) if nv12 else None)
             cx, cy, cw, chh = s.crop
             if ch.geometry == abi.GEOM_NONE:
                 cols = np.arange(s.dst_w) + cx
@@ -147,7 +148,7 @@ class Workload:
             m, muv = masks[s.src]
             m[np.ix_(rows, cols)] = True
             if nv12:
-                muv[np.ix_(np.unique(rows >> 1), np.unique(cols >> 1))] = True
+                muv[np.ix_(rows if uyvy else np.unique(rows >> 1), np.unique(cols >> 1))] = True
         src_bytes = 0
         for m, muv in masks.values():
             src_bytes += int(m.sum()) * (1 if muv is not None else 3)
@@ -193,18 +194,27 @@ def vertical_fusion(w=3840, h=2160, seed=2, pitch_align=16, dst_pitch_align=16) 
                     f"{w}x{h} uchar3 -> uchar3, six fused element-wise ops")
 
 
-def nv12_preprocess(w=3840, h=2160, dst=(640, 640), seed=3, pitch_align=16, ccm=None, yuv_sub=(0.0, 128.0, 128.0)) -> Workload:
+def nv12_preprocess(w=3840, h=2160, dst=(640, 640), seed=3, pitch_align=16, ccm=None, yuv_sub=(0.0, 128.0, 128.0),
+                    src_format=abi.PIX_NV12, colour=None) -> Workload:
     """Config 3: ReadYUV<NV12> -> ConvertYUVToRGB<p8bit,Full,bt709> -> Resize IGNORE_AR -> Sub mean -> Div std ->
-    TensorSplit<float3> (planar CHW fp32)."""
-    pitch = _pitch(w, pitch_align)
+    TensorSplit<float3> (planar CHW fp32).  ``src_format`` selects NV21 or UYVY instead; ``colour=(range, primitives)``
+    takes the matrix and offsets from fkb_ycbcr_to_rgb."""
+    uyvy = src_format == abi.PIX_UYVY
+    pitch = _pitch(w * 2 if uyvy else w, pitch_align)
     dw, dh = dst
-    ch = chain(abi.PIX_NV12, abi.GEOM_RESIZE_IGNORE_AR, abi.PIX_F32C3, abi.WRITE_SPLIT,
+    if colour is not None:
+        m, sub = (C.c_float * 9)(), (C.c_float * 3)()
+        if abi.load().fkb_ycbcr_to_rgb(colour[0], colour[1], m, sub) != 0:
+            raise ValueError("fkb_ycbcr_to_rgb refused the colour description")
+        ccm, yuv_sub = tuple(m), tuple(sub)
+    ch = chain(src_format, abi.GEOM_RESIZE_IGNORE_AR, abi.PIX_F32C3, abi.WRITE_SPLIT,
                [op(abi.OP_YUV2RGB), op(abi.OP_SUB, (123.675, 116.28, 103.53)), op(abi.OP_DIV, (58.395, 57.12, 57.375))],
                n_pre_ops=1, ccm=BT709_FULL_8BIT if ccm is None else ccm, yuv_sub=yuv_sub)
     planes = [PlaneSpec(0, 0, 0, w, h, pitch, (0, 0, w, h), dw, dh, dw * 4, dst_channel_stride=dw * dh * 4,
                         chroma_offset=pitch * h)]
-    return Workload("nv12_preprocess", [ch], [_frame(seed, pitch * (h + h // 2), 16, 236)], [dw * dh * 12], planes,
-                    f"NV12 {w}x{h} -> planar fp32 3x{dh}x{dw}")
+    name = {abi.PIX_NV12: "nv12_preprocess", abi.PIX_NV21: "nv21_preprocess", abi.PIX_UYVY: "uyvy_preprocess"}[src_format]
+    return Workload(name, [ch], [_frame(seed, pitch * h if uyvy else pitch * (h + h // 2), 16, 236)], [dw * dh * 12], planes,
+                    f"{name[:4].upper()} {w}x{h} -> planar fp32 3x{dh}x{dw}", extra={"colour": colour})
 
 
 def conditional_resize(used=5, w=320, h=180, dst=(96, 64), default=(7, 200, 33), seed=11) -> Workload:

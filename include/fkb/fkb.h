@@ -59,7 +59,10 @@ enum {
 
 /* Pixel formats.  A source is U8C3 (PerThreadRead<_2D,uchar3>, memory_operations.h:27-38) or NV12
  * (ReadYUV<NV12>, algorithms/image_processing/color_conversion.h:219-238).  A destination is U8C3 or F32C3. */
-enum { FKB_PIX_U8C3 = 1, FKB_PIX_F32C3 = 2, FKB_PIX_NV12 = 3 };
+enum { FKB_PIX_U8C3 = 1, FKB_PIX_F32C3 = 2, FKB_PIX_NV12 = 3,
+       /* two more 8-bit sources of ReadYUV (color_conversion.h:240-268): NV21 is NV12 with the chroma bytes in the
+        * order V,U; UYVY is one plane of 4-byte groups U Y0 V Y1 (two pixels), 2*width bytes per row, no src_chroma */
+       FKB_PIX_NV21 = 4, FKB_PIX_UYVY = 5 };
 
 /* Geometry of the ReadBack stage.  The crop rectangle is always applied (a chain without Crop
  * passes the whole frame as the rectangle).  NONE: output pixel (x,y) reads crop pixel (x,y).
@@ -138,6 +141,13 @@ typedef struct fkb_plane_desc {
  * plane->dst_w/dst_h, exactly as Resize<INTER_LINEAR,AR>::build does on the host (resize.h:164-233 for
  * the PRESERVE_AR family, 266-278 for IGNORE_AR).  geometry = FKB_GEOM_RESIZE_*. */
 int fkb_resize_params(uint32_t geometry, fkb_plane_desc* plane);
+
+/* The 8-bit YCbCr -> RGB matrix (row-major) and the offsets subtracted from (Y,Cb,Cr) first, as ConvertYUVToRGB
+ * <p8bit, range, primitives> evaluates them in fp32 (itu_color.h:112-124, 142-153, 185-258; color_conversion.h:150-174):
+ * goes into fkb_chain_desc.ccm / yuv_sub of a chain with FKB_OP_YUV2RGB. */
+enum { FKB_RANGE_LIMITED = 0, FKB_RANGE_FULL = 1 };
+enum { FKB_PRIMITIVES_BT601 = 0, FKB_PRIMITIVES_BT709 = 1, FKB_PRIMITIVES_BT2020 = 2 };
+int fkb_ycbcr_to_rgb(uint32_t range, uint32_t primitives, float ccm[9], float yuv_sub[3]);
 
 /* Host-only check of a launch: pointer, size, pitch, rectangle, type-flow and chain-index rules.
  * Launches run it first and return its code.  Needs no GPU. */

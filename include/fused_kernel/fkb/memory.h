@@ -182,8 +182,9 @@ public:
         : Ptr<ND::_3D, T>(data, PtrDims<ND::_3D>(width_, height_, planes_, color_planes_, sizeof(T) * width_), type_, deviceID_) {}
 };
 
-enum class PixelFormat { NV12 };
-enum class ColorDepth { p8bit };
+// The reference's enumerators (itu_color.h:30, 53); the 8-bit formats NV12, NV21 and UYVY are the ones these kernels read.
+enum class PixelFormat { NV12, NV21, YV12, P010, P016, P216, P210, Y216, Y210, Y416, UYVY };
+enum class ColorDepth { p8bit, p10bit, p12bit, fn8bit, fn10bit, fn12bit };
 enum class ColorRange { Limited, Full };
 enum class ColorPrimitives { bt601, bt709, bt2020 };
 
@@ -195,7 +196,10 @@ struct RawImage {
 
 template <PixelFormat PF>
 class Image {
-    static_assert(PF == PixelFormat::NV12, "only NV12 images are implemented by the B200 kernels");
+    static_assert(PF == PixelFormat::NV12 || PF == PixelFormat::NV21 || PF == PixelFormat::UYVY,
+                  "NV12, NV21 and UYVY are the image formats the B200 kernels read");
+    // bytes per row and rows of the one buffer that holds the image (PixelFormatTraits<PF>::rf, itu_color.h:57-102)
+    static constexpr bool packed422 = PF == PixelFormat::UYVY;
     Ptr<ND::_2D, uchar> data;
     uint width{0}, height{0};
 
@@ -203,7 +207,8 @@ public:
     Image(const Ptr<ND::_2D, uchar>& data_, const uint& width_, const uint& height_) : data(data_), width(width_), height(height_) {}
     Image(const uint width_, const uint height_, const MemType memType = defaultMemType, const uint deviceID = 0)
         : width(width_), height(height_) {
-        data = Ptr<ND::_2D, uchar>(PtrDims<ND::_2D>(width_, height_ + height_ / 2, 0), memType, static_cast<int>(deviceID));
+        data = Ptr<ND::_2D, uchar>(packed422 ? PtrDims<ND::_2D>(width_ * 2, height_, 0) : PtrDims<ND::_2D>(width_, height_ + height_ / 2, 0),
+                                   memType, static_cast<int>(deviceID));
     }
     uint imageWidth() const { return width; }
     uint imageHeight() const { return height; }

@@ -95,16 +95,16 @@ struct ColorConversion {
                   "BGR<->RGB on uchar3 or float3 is the colour conversion the B200 kernels implement");
     static constexpr auto build() { return ComputeIOp<FKB_OP_REORDER_ZYX, I, O>{}; }
 };
-// YCbCr -> RGB matrices as the reference evaluates them in fp32 (algorithms/image_processing/itu_color.h:185-258).
+// YCbCr -> RGB: the matrix and offsets of <range, primitives> as the reference evaluates them in fp32
+// (algorithms/image_processing/itu_color.h:185-258, color_conversion.h:150-174), from fkb_ycbcr_to_rgb.
 template <ColorDepth CD, ColorRange CR, ColorPrimitives CP>
 struct ConvertYUVToRGB {
-    static_assert(CD == ColorDepth::p8bit && CR == ColorRange::Full && CP == ColorPrimitives::bt709,
-                  "8-bit full-range bt709 is the YCbCr->RGB conversion the B200 kernels implement");
-    static constexpr auto build() {
+    static_assert(CD == ColorDepth::p8bit, "8-bit YCbCr is the depth the B200 kernels convert");
+    static auto build() {
         ComputeIOp<FKB_OP_YUV2RGB, uchar3, float3> op{};
-        constexpr float m[9] = {1.f, 0.f, 1.57480001f, 1.f, -0.187324256f, -0.46812427f, 1.f, 1.8556f, 0.f};
-        for (int i = 0; i < 9; ++i) op.ccm[i] = m[i];
-        op.yuv_sub[0] = 0.f; op.yuv_sub[1] = 128.f; op.yuv_sub[2] = 128.f;  // Full range: luma is not offset
+        const uint32_t prim = CP == ColorPrimitives::bt601 ? FKB_PRIMITIVES_BT601 : CP == ColorPrimitives::bt709 ? FKB_PRIMITIVES_BT709 : FKB_PRIMITIVES_BT2020;
+        if (fkb_ycbcr_to_rgb(CR == ColorRange::Full ? FKB_RANGE_FULL : FKB_RANGE_LIMITED, prim, op.ccm, op.yuv_sub) != FKB_OK)
+            throw std::runtime_error("ConvertYUVToRGB: colour description refused");
         return op;
     }
 };
@@ -229,7 +229,9 @@ struct ReadYUV {
     static auto build(const Image<PF>& img) { return build(img.ptr()); }
     static auto build(const RawImage<PF>& raw) {
         detail::ReadState s;
-        s.src_format = FKB_PIX_NV12;
+        static_assert(PF == PixelFormat::NV12 || PF == PixelFormat::NV21 || PF == PixelFormat::UYVY,
+                      "NV12, NV21 and UYVY are the formats the B200 kernels read");
+        s.src_format = PF == PixelFormat::NV12 ? FKB_PIX_NV12 : PF == PixelFormat::NV21 ? FKB_PIX_NV21 : FKB_PIX_UYVY;
         s.src.push_back({raw.data.data, raw.data.dims.pitch, raw.width, raw.height});
         return ReadIOp<uchar3, 0>(std::move(s));
     }

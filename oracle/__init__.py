@@ -39,6 +39,8 @@ def load_oracle() -> C.CDLL:
         lib.fkb_oracle_resize_params.argtypes = [C.c_uint32, C.POINTER(abi.PlaneDesc)]
         lib.fkb_oracle_run.restype = C.c_int
         lib.fkb_oracle_run.argtypes = [C.POINTER(abi.ChainDesc), C.c_uint32, C.POINTER(abi.PlaneDesc), C.c_uint32, C.c_uint32]
+        lib.fkb_oracle_ycbcr_to_rgb.restype = C.c_int
+        lib.fkb_oracle_ycbcr_to_rgb.argtypes = [C.c_uint32, C.c_uint32, C.POINTER(C.c_float), C.POINTER(C.c_float)]
         lib.fkb_oracle_saturate_u8.restype = C.c_uint8
         lib.fkb_oracle_saturate_u8.argtypes = [C.c_float]
         lib.fkb_oracle_round_half_away.restype = C.c_float
@@ -67,6 +69,10 @@ def load_ref() -> C.CDLL:
         lib.fklref_saturate_u8.argtypes = [C.c_float]
         lib.fklref_resize_params.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, f32p, i32p]
         u8p = C.POINTER(C.c_uint8)
+        lib.fklref_ycbcr_matrix.restype = C.c_int
+        lib.fklref_ycbcr_matrix.argtypes = [C.c_int, C.c_int, f32p]
+        lib.fklref_yuv_resize_split.restype = C.c_int
+        lib.fklref_yuv_resize_split.argtypes = [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, f32p, f32p, C.c_void_p]
         lib.fklref_conditional_resize_f32.argtypes = [pp, C.c_int, C.c_int, C.c_int, C.c_int, u8p, C.c_int, C.c_int, f32p, C.c_void_p]
         lib.fklref_conditional_pointwise_u8.argtypes = [pp, C.c_int, C.c_int, C.c_int, C.c_int, u8p, f32p, C.c_void_p]
         for name in ("fklref_crop_resize_u8", "fklref_crop_resize_f32", "fklref_crop_reorder_u8", "fklref_pointwise_u8",
@@ -167,6 +173,12 @@ def run_ref(wl, threads: int = 1):
     elif wl.name == "vertical_fusion":
         rc = lib.fklref_pointwise_u8(wl.sources[0].ctypes.data, p0.src_w, p0.src_h, p0.src_pitch, _f3(ch.ops[1].v),
                                      _f3(ch.ops[2].v), _f3(ch.ops[3].v), outs[0].ctypes.data, p0.dst_pitch)
+    elif wl.name.endswith("_preprocess") and wl.extra.get("colour") is not None:
+        rng, prim = wl.extra["colour"]
+        rc = lib.fklref_yuv_resize_split(ch.src_format, rng, prim, wl.sources[0].ctypes.data, p0.src_w, p0.src_h, p0.src_pitch,
+                                         p0.dst_w, p0.dst_h, _f3(ch.ops[1].v), _f3(ch.ops[2].v), outs[0].ctypes.data)
+        if rc == -1:
+            raise ValueError("the reference runner has no instantiation for this format / range / primitives")
     elif wl.name == "nv12_preprocess":
         rc = lib.fklref_nv12_resize_split(wl.sources[0].ctypes.data, p0.src_w, p0.src_h, p0.src_pitch, p0.dst_w, p0.dst_h,
                                           _f3(ch.ops[1].v), _f3(ch.ops[2].v), outs[0].ctypes.data)

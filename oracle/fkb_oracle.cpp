@@ -122,6 +122,16 @@ inline V3 read_tap(const fkb_chain_desc& ch, const fkb_plane_desc& pl, int cx, i
         v.c[0] = base[Y * pl.src_pitch + X];
         v.c[1] = uv[0];
         v.c[2] = uv[1];
+    } else if (ch.src_format == FKB_PIX_NV21) {  // color_conversion.h:240-254: the pair is (V,U)
+        const uint8_t* vu = static_cast<const uint8_t*>(pl.src_chroma) + (Y >> 1) * pl.src_pitch + (X >> 1) * 2;
+        v.c[0] = base[Y * pl.src_pitch + X];
+        v.c[1] = vu[1];
+        v.c[2] = vu[0];
+    } else if (ch.src_format == FKB_PIX_UYVY) {  // color_conversion.h:255-265: one uchar4 (U, Y0, V, Y1) per two pixels
+        const uint8_t* g = base + Y * pl.src_pitch + (X >> 1) * 4;
+        v.c[0] = (X & 1) ? g[3] : g[1];
+        v.c[1] = g[0];
+        v.c[2] = g[2];
     } else {
         const uint8_t* p = base + Y * pl.src_pitch + X * 3;
         v.c[0] = p[0]; v.c[1] = p[1]; v.c[2] = p[2];
@@ -227,6 +237,31 @@ int fkb_oracle_resize_params(uint32_t geometry, fkb_plane_desc* pl) {
     pl->y1 = (dh - th) / 2;
     pl->x2 = pl->x1 + tw - 1;
     pl->y2 = pl->y1 + th - 1;
+    return FKB_OK;
+}
+
+// ccMatrix<CR, CP, YCbCr2RGB, p8bit> and subCoefficients<p8bit> (itu_color.h:112-124, 142-153, 185-258), with the
+// luma offset dropped for Full range as ConvertYUVToRGB::exec does (color_conversion.h:163-171).
+int fkb_oracle_ycbcr_to_rgb(uint32_t range, uint32_t primitives, float* ccm, float* yuv_sub) {
+    float kr, kb;
+    switch (primitives) {
+    case FKB_PRIMITIVES_BT601: kr = 0.299f; kb = 0.114f; break;
+    case FKB_PRIMITIVES_BT709: kr = 0.2126f; kb = 0.0722f; break;
+    case FKB_PRIMITIVES_BT2020: kr = 0.2627f; kb = 0.0593f; break;
+    default: return FKB_ERR_INVALID;
+    }
+    const float kg = 1.0f - kr - kb;
+    ccm[0] = 1.0f; ccm[1] = 0.0f; ccm[2] = 2.0f * (1.0f - kr);
+    ccm[3] = 1.0f; ccm[4] = -2.0f * kb * (1.0f - kb) / kg; ccm[5] = -2.0f * kr * (1.0f - kr) / kg;
+    ccm[6] = 1.0f; ccm[7] = 2.0f * (1.0f - kb); ccm[8] = 0.0f;
+    if (range == FKB_RANGE_LIMITED) {
+        const float sy = 255.f / 219.f, sc = 255.f / 224.f;
+        for (int r = 0; r < 3; ++r) { ccm[3 * r] *= sy; ccm[3 * r + 1] *= sc; ccm[3 * r + 2] *= sc; }
+    } else if (range != FKB_RANGE_FULL) {
+        return FKB_ERR_INVALID;
+    }
+    yuv_sub[0] = range == FKB_RANGE_LIMITED ? 16.f : 0.f;
+    yuv_sub[1] = 128.f; yuv_sub[2] = 128.f;
     return FKB_OK;
 }
 

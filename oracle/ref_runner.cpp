@@ -268,6 +268,59 @@ void fklref_bt709_full_matrix(float* m9) {
     m9[6] = m.z.x; m9[7] = m.z.y; m9[8] = m.z.z;
 }
 
+}  // extern "C"
+
+// ccMatrix<range, primitives, YCbCr2RGB, p8bit> for range 0 Limited / 1 Full, primitives 0 bt601 / 1 bt709 / 2 bt2020
+template <ColorRange CR, ColorPrimitives CP>
+static void matrix_of(float* m9) {
+    constexpr M3x3Float m = ccMatrix<CR, CP, ColorConversionDir::YCbCr2RGB, ColorDepth::p8bit>;
+    m9[0] = m.x.x; m9[1] = m.x.y; m9[2] = m.x.z; m9[3] = m.y.x; m9[4] = m.y.y; m9[5] = m.y.z;
+    m9[6] = m.z.x; m9[7] = m.z.y; m9[8] = m.z.z;
+}
+extern "C" int fklref_ycbcr_matrix(int range, int primitives, float* m9) {
+    switch (range * 3 + primitives) {
+    case 0: matrix_of<ColorRange::Limited, ColorPrimitives::bt601>(m9); return 0;
+    case 1: matrix_of<ColorRange::Limited, ColorPrimitives::bt709>(m9); return 0;
+    case 2: matrix_of<ColorRange::Limited, ColorPrimitives::bt2020>(m9); return 0;
+    case 3: matrix_of<ColorRange::Full, ColorPrimitives::bt601>(m9); return 0;
+    case 4: matrix_of<ColorRange::Full, ColorPrimitives::bt709>(m9); return 0;
+    case 5: matrix_of<ColorRange::Full, ColorPrimitives::bt2020>(m9); return 0;
+    default: return -1;
+    }
+}
+
+// ReadYUV<PF> -> ConvertYUVToRGB<p8bit, CR, CP> -> Resize(IGNORE_AR) -> Sub -> Div -> TensorSplit<float3>
+template <PixelFormat PF, ColorRange CR, ColorPrimitives CP>
+static int yuv_resize_split(const uint8_t* data, int w, int h, int pitch, int dw, int dh, const float* sub, const float* div, float* out) {
+    CpuStream stream;
+    constexpr bool packed = PF == PixelFormat::UYVY;
+    const Ptr<ND::_2D, uchar> buf(const_cast<uint8_t*>(data), packed ? PtrDims<ND::_2D>(w * 2, h, pitch) : PtrDims<ND::_2D>(w, h + h / 2, pitch),
+                                  MemType::Host, 0);
+    const Image<PF> img(buf, w, h);
+    Tensor<float> t(out, dw, dh, 1, 3, MemType::Host, 0);
+    executeOperations<CpuDPP>(stream, ReadYUV<PF>::build(img), ConvertYUVToRGB<ColorDepth::p8bit, CR, CP>::build(),
+        Resize<InterpolationType::INTER_LINEAR, AspectRatio::IGNORE_AR>::build(Size(dw, dh)),
+        Sub<float3>::build(make_<float3>(sub[0], sub[1], sub[2])), Div<float3>::build(make_<float3>(div[0], div[1], div[2])),
+        TensorSplit<float3>::build(t));
+    return 0;
+}
+// format: 3 NV12, 4 NV21, 5 UYVY (this library's source-format codes); a spread of range / primitives per format
+extern "C" int fklref_yuv_resize_split(int format, int range, int primitives, const uint8_t* data, int w, int h, int pitch, int dw,
+                                       int dh, const float* sub, const float* div, float* out) {
+    const int key = format * 100 + range * 10 + primitives;
+    switch (key) {
+    case 311: return yuv_resize_split<PixelFormat::NV12, ColorRange::Full, ColorPrimitives::bt709>(data, w, h, pitch, dw, dh, sub, div, out);
+    case 300: return yuv_resize_split<PixelFormat::NV12, ColorRange::Limited, ColorPrimitives::bt601>(data, w, h, pitch, dw, dh, sub, div, out);
+    case 302: return yuv_resize_split<PixelFormat::NV12, ColorRange::Limited, ColorPrimitives::bt2020>(data, w, h, pitch, dw, dh, sub, div, out);
+    case 410: return yuv_resize_split<PixelFormat::NV21, ColorRange::Full, ColorPrimitives::bt601>(data, w, h, pitch, dw, dh, sub, div, out);
+    case 401: return yuv_resize_split<PixelFormat::NV21, ColorRange::Limited, ColorPrimitives::bt709>(data, w, h, pitch, dw, dh, sub, div, out);
+    case 512: return yuv_resize_split<PixelFormat::UYVY, ColorRange::Full, ColorPrimitives::bt2020>(data, w, h, pitch, dw, dh, sub, div, out);
+    case 500: return yuv_resize_split<PixelFormat::UYVY, ColorRange::Limited, ColorPrimitives::bt601>(data, w, h, pitch, dw, dh, sub, div, out);
+    default: return -1;
+    }
+}
+
+extern "C" {
 uint8_t fklref_saturate_u8(float v) { return cxp::saturate_cast<uchar>::f(v); }
 
 // Resize<INTER_LINEAR,AR>::build on a w x h source: returns fx, fy, x1, y1, x2, y2.  `ar` is the reference's own

@@ -72,6 +72,17 @@ def test_resize_params_match_oracle():
     assert lib.fkb_resize_params(abi.GEOM_RESIZE_IGNORE_AR, None) == abi.ERR_NULL
 
 
+def test_ycbcr_matrices_match_oracle():
+    lib, orc = abi.load(), oracle.load_oracle()
+    for rng in (abi.RANGE_LIMITED, abi.RANGE_FULL):
+        for prim in (abi.PRIMITIVES_BT601, abi.PRIMITIVES_BT709, abi.PRIMITIVES_BT2020):
+            a, b, sa, sb = (C.c_float * 9)(), (C.c_float * 9)(), (C.c_float * 3)(), (C.c_float * 3)()
+            assert lib.fkb_ycbcr_to_rgb(rng, prim, a, sa) == 0 and orc.fkb_oracle_ycbcr_to_rgb(rng, prim, b, sb) == 0
+            assert list(a) == list(b) and list(sa) == list(sb)
+    assert lib.fkb_ycbcr_to_rgb(2, 0, a, sa) == abi.ERR_INVALID and lib.fkb_ycbcr_to_rgb(0, 3, a, sa) == abi.ERR_INVALID
+    assert lib.fkb_ycbcr_to_rgb(0, 0, None, sa) == abi.ERR_NULL
+
+
 def _bound(wl):
     """Planes bound to fake, well-aligned addresses: enough for the host-only validator."""
     return wl.bind([0x10000000 + i * 0x10000000 for i in range(len(wl.sources))],

@@ -137,6 +137,16 @@ def test_nv12_colour_matrices():
             check(wl, use_plan=True)
 
 
+@pytest.mark.parametrize("fmt", [abi.PIX_NV12, abi.PIX_NV21, abi.PIX_UYVY])
+@pytest.mark.parametrize("rng", [abi.RANGE_LIMITED, abi.RANGE_FULL])
+@pytest.mark.parametrize("prim", [abi.PRIMITIVES_BT601, abi.PRIMITIVES_BT709, abi.PRIMITIVES_BT2020])
+def test_yuv_formats_ranges_primitives(fmt, rng, prim):
+    for shape in [dict(w=1280, h=720, dst=(321, 203)), dict(w=66, h=50, dst=(300, 301))]:
+        wl = W.nv12_preprocess(**shape, src_format=fmt, colour=(rng, prim))
+        check(wl)
+        check(wl, force_gather=True)
+
+
 def test_many_planes_use_the_descriptor_arena():
     # more planes than fit in the kernel parameters: descriptors travel through the pinned/device ring
     wl = W.batched_crop_resize(n_frames=3, crops_per_frame=100, w=320, h=240, dst=(32, 24), crop_range=(4, 100))

@@ -97,6 +97,32 @@ def test_resize_params_against_reference():
             assert all(g == w or (np.isnan(g) and np.isnan(w)) for g, w in zip(got, want)), (sw, sh, dw, dh, ar, got, want)
 
 
+@pytest.mark.skipif(not oracle.have_ref(), reason="reference-backed checker not built")
+def test_ycbcr_matrices_against_reference():
+    lib, ref = oracle.load_oracle(), oracle.load_ref()
+    for rng in (abi.RANGE_LIMITED, abi.RANGE_FULL):
+        for prim in (abi.PRIMITIVES_BT601, abi.PRIMITIVES_BT709, abi.PRIMITIVES_BT2020):
+            want, got, sub = (C.c_float * 9)(), (C.c_float * 9)(), (C.c_float * 3)()
+            assert ref.fklref_ycbcr_matrix(rng, prim, want) == 0
+            assert lib.fkb_oracle_ycbcr_to_rgb(rng, prim, got, sub) == 0
+            assert list(got) == list(want), (rng, prim)  # bit for bit
+            assert list(sub) == [16.0 if rng == abi.RANGE_LIMITED else 0.0, 128.0, 128.0]
+
+
+YUV_CASES = [(abi.PIX_NV12, abi.RANGE_FULL, abi.PRIMITIVES_BT709), (abi.PIX_NV12, abi.RANGE_LIMITED, abi.PRIMITIVES_BT601),
+             (abi.PIX_NV12, abi.RANGE_LIMITED, abi.PRIMITIVES_BT2020), (abi.PIX_NV21, abi.RANGE_FULL, abi.PRIMITIVES_BT601),
+             (abi.PIX_NV21, abi.RANGE_LIMITED, abi.PRIMITIVES_BT709), (abi.PIX_UYVY, abi.RANGE_FULL, abi.PRIMITIVES_BT2020),
+             (abi.PIX_UYVY, abi.RANGE_LIMITED, abi.PRIMITIVES_BT601)]
+
+
+@pytest.mark.skipif(not oracle.have_ref(), reason="reference-backed checker not built")
+@pytest.mark.parametrize("fmt,rng,prim", YUV_CASES)
+def test_oracle_yuv_formats_match_reference_backend(fmt, rng, prim):
+    wl = W.nv12_preprocess(w=640, h=360, dst=(200, 150), src_format=fmt, colour=(rng, prim))
+    got, want = oracle.run_oracle(wl, threads=4), oracle.run_ref(wl)
+    assert np.array_equal(got[0], want[0])
+
+
 @pytest.mark.parametrize("name", GOLDEN_CASES)
 def test_oracle_matches_golden_fixture(name):
     wl, want = load_golden(name)

@@ -23,6 +23,7 @@ GEOM_NONE, GEOM_RESIZE_IGNORE_AR, GEOM_RESIZE_PRESERVE_AR = 0, 1, 2
 GEOM_RESIZE_PRESERVE_AR_RN_EVEN, GEOM_RESIZE_PRESERVE_AR_LEFT = 3, 4
 PLANE_DEFAULT = 0x80000000  # fkb_plane_desc.chain bit: the plane's read yields bg (conditional batch read)
 WRITE_PACKED, WRITE_SPLIT = 1, 2
+BORDER_NONE, BORDER_CONSTANT, BORDER_REPLICATE, BORDER_REFLECT, BORDER_WRAP, BORDER_REFLECT_101 = 0, 1, 2, 3, 4, 5
 OP_CAST_F32, OP_MUL, OP_ADD, OP_SUB, OP_DIV, OP_REORDER_ZYX, OP_YUV2RGB, OP_SATCAST_U8 = 1, 2, 3, 4, 5, 6, 7, 8
 
 
@@ -35,6 +36,7 @@ class ChainDesc(C.Structure):
         ("src_format", C.c_uint32), ("geometry", C.c_uint32), ("dst_format", C.c_uint32),
         ("write_kind", C.c_uint32), ("n_ops", C.c_uint32), ("n_pre_ops", C.c_uint32),
         ("ops", Op * MAX_OPS), ("ccm", C.c_float * 9), ("yuv_sub", C.c_float * 3),
+        ("border", C.c_uint32), ("border_at", C.c_uint32), ("border_value", C.c_float * 3),
     ]
 
 
@@ -52,7 +54,7 @@ class PlaneDesc(C.Structure):
     ]
 
 
-assert C.sizeof(Op) == 16 and C.sizeof(ChainDesc) == 264 and C.sizeof(PlaneDesc) == 160
+assert C.sizeof(Op) == 16 and C.sizeof(ChainDesc) == 284 and C.sizeof(PlaneDesc) == 160
 
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libfkb.so")
 

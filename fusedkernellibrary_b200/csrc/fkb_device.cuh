@@ -35,8 +35,7 @@ struct __align__(16) PlaneRec {
     uint32_t tile_w, tile_h;    // output pixels per tile
     uint32_t tiles_x, tiles_y;  // tiles per plane
     uint32_t tile_base;         // index of this plane's first staged tile in the launch (LUT planes: first LUT unit)
-    uint32_t in_stride;         // bytes between staged source rows in shared memory (multiple of 16)
-    uint32_t out_stride;        // bytes between rows of the shared output tile (multiple of 16)
+    uint32_t src_w, src_h;      // frame size in pixels (what a BorderReader maps coordinates into)
     float params[FKB_MAX_PLANE_PARAMS][3];
     uint32_t lut_base;          // LUT units of all earlier planes (monotone over the table, searched by lut_kernel)
     uint32_t pad_[1];

@@ -62,6 +62,8 @@ int check_chain(const fkb_chain_desc& ch) {
     if (ch.geometry > FKB_GEOM_RESIZE_PRESERVE_AR_LEFT) return FKB_ERR_UNSUPPORTED;
     if (ch.write_kind != FKB_WRITE_PACKED && ch.write_kind != FKB_WRITE_SPLIT) return FKB_ERR_UNSUPPORTED;
     if (ch.n_ops > FKB_MAX_OPS || ch.n_pre_ops > ch.n_ops) return FKB_ERR_INVALID;
+    if (ch.border > FKB_BORDER_REFLECT_101) return FKB_ERR_UNSUPPORTED;
+    if (ch.border && ch.border_at > (ch.geometry == FKB_GEOM_NONE ? ch.n_ops : ch.n_pre_ops)) return FKB_ERR_INVALID;
     ValueType t = VT_U8;  // both reads produce uchar3
     int rc;
     if (ch.geometry == FKB_GEOM_NONE) {
@@ -87,8 +89,17 @@ int check_plane(const fkb_chain_desc& ch, const fkb_plane_desc& pl) {
                                  : uyvy ? ((static_cast<uint64_t>(pl.src_w) + 1) / 2) * 4 : static_cast<uint64_t>(pl.src_w) * 3;
         if (pl.src_pitch < src_row) return FKB_ERR_INVALID;
         if (pl.crop_w <= 0 || pl.crop_h <= 0) return FKB_ERR_INVALID;
-        if (static_cast<uint64_t>(pl.crop_x) + static_cast<uint64_t>(pl.crop_w) > pl.src_w ||
-            static_cast<uint64_t>(pl.crop_y) + static_cast<uint64_t>(pl.crop_h) > pl.src_h) return FKB_ERR_INVALID;
+        if (ch.border) {
+            // the rectangle may leave the frame; its origin is signed (crop.h:36-39).  Bounded so that the index maps
+            // of the border modes cannot overflow.
+            const int64_t lim = 1 << 24;
+            const int64_t x = static_cast<int32_t>(pl.crop_x), y = static_cast<int32_t>(pl.crop_y);
+            if (x < -lim || x > lim || y < -lim || y > lim || pl.crop_w > lim || pl.crop_h > lim || pl.src_w > lim || pl.src_h > lim)
+                return FKB_ERR_INVALID;
+        } else if (static_cast<uint64_t>(pl.crop_x) + static_cast<uint64_t>(pl.crop_w) > pl.src_w ||
+                   static_cast<uint64_t>(pl.crop_y) + static_cast<uint64_t>(pl.crop_h) > pl.src_h) {
+            return FKB_ERR_INVALID;
+        }
     } else if (ch.geometry == FKB_GEOM_NONE) {
         for (int c = 0; c < 3; ++c)  // a uchar3 default
             if (!(pl.bg[c] >= 0.f && pl.bg[c] <= 255.f) || pl.bg[c] != std::floor(pl.bg[c])) return FKB_ERR_INVALID;
@@ -156,8 +167,13 @@ uint32_t post_kind_of(const fkb_chain_desc& ch);
 void classify(const fkb_chain_desc& ch, PlaneRec& r) {
     r.kclass = KCLASS_GATHER;
     r.tile_w = r.tile_h = r.tiles_x = r.tiles_y = 0;
-    r.in_stride = r.out_stride = 0;
     if (force_gather()) return;
+    if (ch.border) {
+        // a rectangle inside the frame never meets the border: it takes the usual paths; one that leaves it is
+        // remapped tap by tap in the general kernel
+        const int64_t x = static_cast<int32_t>(r.crop_x), y = static_cast<int32_t>(r.crop_y);
+        if (x < 0 || y < 0 || x + r.crop_w > static_cast<int64_t>(r.src_w) || y + r.crop_h > static_cast<int64_t>(r.src_h)) return;
+    }
     if ((ch.src_format == FKB_PIX_NV12 || ch.src_format == FKB_PIX_NV21) && ch.geometry != FKB_GEOM_NONE && ch.n_pre_ops == 1 && ch.ops[0].code == FKB_OP_YUV2RGB &&
         post_kind_of(ch) != 8u && !(ch.geometry >= FKB_GEOM_RESIZE_PRESERVE_AR && (r.x2 < r.x1 || r.y2 < r.y1)) &&
         (reinterpret_cast<uintptr_t>(r.src_chroma) & 1) == 0 && (r.src_pitch & 1) == 0) {  // UV pairs are read as 16-bit words
@@ -196,8 +212,6 @@ void classify(const fkb_chain_desc& ch, PlaneRec& r) {
         r.tile_w = tw;
         r.kclass = KCLASS_RESIZE;
     }
-    r.in_stride = kInRowBytes;
-    r.out_stride = kOutRowBytes;
     r.tiles_x = (r.dst_w + r.tile_w - 1) / r.tile_w;  // tile_h / tiles_y are chosen per launch (rows_per_item)
 }
 
@@ -302,7 +316,7 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         r.src_chroma = static_cast<const uint8_t*>(s.src_chroma);
         r.dst = static_cast<uint8_t*>(s.dst);
         r.dst_cstride = s.dst_channel_stride;
-        r.src_pitch = s.src_pitch;
+        r.src_pitch = s.src_pitch; r.src_w = s.src_w; r.src_h = s.src_h;
         r.crop_x = s.crop_x; r.crop_y = s.crop_y; r.crop_w = s.crop_w; r.crop_h = s.crop_h;
         r.dst_w = s.dst_w; r.dst_h = s.dst_h; r.dst_pitch = s.dst_pitch;
         r.fx = s.fx; r.fy = s.fy; r.x1 = s.x1; r.y1 = s.y1; r.x2 = s.x2; r.y2 = s.y2;
@@ -543,7 +557,7 @@ int lower_fixed(const fkb_chain_desc* chain, const fkb_plane_desc* planes, uint3
         r.src_chroma = static_cast<const uint8_t*>(s.src_chroma);
         r.dst = static_cast<uint8_t*>(s.dst);
         r.dst_cstride = s.dst_channel_stride;
-        r.src_pitch = s.src_pitch;
+        r.src_pitch = s.src_pitch; r.src_w = s.src_w; r.src_h = s.src_h;
         r.crop_x = s.crop_x; r.crop_y = s.crop_y; r.crop_w = s.crop_w; r.crop_h = s.crop_h;
         r.dst_w = s.dst_w; r.dst_h = s.dst_h; r.dst_pitch = s.dst_pitch;
         r.fx = s.fx; r.fy = s.fy; r.x1 = s.x1; r.y1 = s.y1; r.x2 = s.x2; r.y2 = s.y2;

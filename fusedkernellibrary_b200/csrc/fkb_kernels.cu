@@ -30,8 +30,8 @@ __device__ __forceinline__ const PlaneRec* plane_table(const LaunchParams& p) {
     return p.table ? p.table : p.inline_planes;
 }
 
-__device__ __forceinline__ void read_tap_global(const fkb_chain_desc& ch, const PlaneRec& pl, int cx, int cy, float (&o)[3]) {
-    const size_t X = static_cast<size_t>(cx) + pl.crop_x, Y = static_cast<size_t>(cy) + pl.crop_y;
+// Frame pixel (X,Y) as three floats (uchar3 channels, or Y / Cb / Cr).
+__device__ __forceinline__ void read_frame_global(const fkb_chain_desc& ch, const PlaneRec& pl, size_t X, size_t Y, float (&o)[3]) {
     if (ch.src_format == FKB_PIX_NV12 || ch.src_format == FKB_PIX_NV21) {
         const uint8_t* uv = pl.src_chroma + (Y >> 1) * pl.src_pitch + (X >> 1) * 2;
         const uint32_t vu = ch.src_format == FKB_PIX_NV21;  // V first
@@ -49,6 +49,51 @@ __device__ __forceinline__ void read_tap_global(const fkb_chain_desc& ch, const 
         o[1] = static_cast<float>(__ldg(q + 1));
         o[2] = static_cast<float>(__ldg(q + 2));
     }
+}
+// Index maps of the reference's BorderReader modes (border_reader.h:211-330), idx = low(high(i)); n is the frame extent.
+__device__ __forceinline__ int border_index(uint32_t mode, int i, int n) {
+    const int last = n - 1;
+    switch (mode) {
+    case FKB_BORDER_REPLICATE: return max(min(i, last), 0);
+    case FKB_BORDER_REFLECT: {
+        const int hi = last - abs(last - i) + (i > last ? 1 : 0);
+        return (abs(hi) - (hi < 0 ? 1 : 0)) % n;
+    }
+    case FKB_BORDER_WRAP: {
+        const int hi = i < n ? i : i % n;
+        return hi >= 0 ? hi : hi - ((hi - n + 1) / n) * n;
+    }
+    case FKB_BORDER_REFLECT_101: return abs(abs(last - abs(last - i)) % n) % n;
+    default: return i;
+    }
+}
+// Crop-relative pixel (cx,cy) of a plane: the Crop adds its (signed) origin, a BorderReader maps what leaves the frame.
+// Returns true when the tap lies outside the frame of a CONSTANT border: nothing is read and the caller substitutes
+// the chain's border value.
+__device__ __forceinline__ bool read_tap_global(const fkb_chain_desc& ch, const PlaneRec& pl, int cx, int cy, float (&o)[3]) {
+    int X = cx + static_cast<int>(pl.crop_x), Y = cy + static_cast<int>(pl.crop_y);
+    if (ch.border) {
+        const int w = static_cast<int>(pl.src_w), h = static_cast<int>(pl.src_h);
+        if (ch.border == FKB_BORDER_CONSTANT) {
+            if (X < 0 || X >= w || Y < 0 || Y >= h) { o[0] = o[1] = o[2] = 0.f; return true; }
+        } else {
+            X = border_index(ch.border, X, w);
+            Y = border_index(ch.border, Y, h);
+        }
+    }
+    read_frame_global(ch, pl, static_cast<size_t>(X), static_cast<size_t>(Y), o);
+    return false;
+}
+// ops[first..last) on N values of which some (mask bit n) are constant-border taps: those take the border value after
+// the ops that precede the BorderReader.
+template <int N>
+__device__ __forceinline__ void apply_ops_bordered(float (&v)[N][3], const fkb_chain_desc& ch, const PlaneRec& pl, uint32_t last, uint32_t outside) {
+    if (outside == 0u) { apply_ops<N>(v, ch, pl, 0, last); return; }
+    apply_ops<N>(v, ch, pl, 0, ch.border_at);
+#pragma unroll
+    for (int n = 0; n < N; ++n)
+        if ((outside >> n) & 1u) { v[n][0] = ch.border_value[0]; v[n][1] = ch.border_value[1]; v[n][2] = ch.border_value[2]; }
+    apply_ops<N>(v, ch, pl, ch.border_at, last);
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -81,11 +126,12 @@ __global__ void __launch_bounds__(256) gather_kernel(const __grid_constant__ Lau
             apply_ops<PPT>(v, ch, pl, ch.geometry == FKB_GEOM_NONE ? 0 : ch.n_pre_ops, ch.n_ops);
         } else if (ch.geometry == FKB_GEOM_NONE) {
 #pragma unroll
+            uint32_t outside = 0;
             for (int n = 0; n < PPT; ++n) {
-                if (n < nvalid) read_tap_global(ch, pl, x0 + n, y, v[n]);
+                if (n < nvalid) outside |= static_cast<uint32_t>(read_tap_global(ch, pl, static_cast<int>(x0) + n, static_cast<int>(y), v[n])) << n;
                 else { v[n][0] = v[n][1] = v[n][2] = 0.f; }
             }
-            apply_ops<PPT>(v, ch, pl, 0, ch.n_ops);
+            apply_ops_bordered<PPT>(v, ch, pl, ch.n_ops, outside);
         } else {
             const bool par = ch.geometry >= FKB_GEOM_RESIZE_PRESERVE_AR;
             const int ox = par ? pl.x1 : 0, oy = par ? pl.y1 : 0;
@@ -98,11 +144,11 @@ __global__ void __launch_bounds__(256) gather_kernel(const __grid_constant__ Lau
                 if (inside) {
                     const AxisTap ax = axis_tap(x - ox, pl.fx, pl.crop_w);
                     float t[4][3];
-                    read_tap_global(ch, pl, ax.i0, ay.i0, t[0]);
-                    read_tap_global(ch, pl, ax.i1, ay.i0, t[1]);
-                    read_tap_global(ch, pl, ax.i0, ay.i1, t[2]);
-                    read_tap_global(ch, pl, ax.i1, ay.i1, t[3]);
-                    apply_ops<4>(t, ch, pl, 0, ch.n_pre_ops);
+                    uint32_t outside = read_tap_global(ch, pl, ax.i0, ay.i0, t[0]) ? 1u : 0u;
+                    outside |= read_tap_global(ch, pl, ax.i1, ay.i0, t[1]) ? 2u : 0u;
+                    outside |= read_tap_global(ch, pl, ax.i0, ay.i1, t[2]) ? 4u : 0u;
+                    outside |= read_tap_global(ch, pl, ax.i1, ay.i1, t[3]) ? 8u : 0u;
+                    apply_ops_bordered<4>(t, ch, pl, ch.n_pre_ops, outside);
                     const float w00 = __fmul_rn(ax.w0, ay.w0), w10 = __fmul_rn(ax.w1, ay.w0);
                     const float w01 = __fmul_rn(ax.w0, ay.w1), w11 = __fmul_rn(ax.w1, ay.w1);
 #pragma unroll

@@ -30,7 +30,8 @@ def op(code: int, v=(0.0, 0.0, 0.0), slot: int = -1) -> abi.Op:
     return o
 
 
-def chain(src_format, geometry, dst_format, write_kind, ops, n_pre_ops=0, ccm=None, yuv_sub=None) -> abi.ChainDesc:
+def chain(src_format, geometry, dst_format, write_kind, ops, n_pre_ops=0, ccm=None, yuv_sub=None, border=0, border_at=0,
+          border_value=(0.0, 0.0, 0.0)) -> abi.ChainDesc:
     ch = abi.ChainDesc()
     ch.src_format, ch.geometry, ch.dst_format, ch.write_kind = src_format, geometry, dst_format, write_kind
     ch.n_ops, ch.n_pre_ops = len(ops), n_pre_ops
@@ -40,6 +41,8 @@ def chain(src_format, geometry, dst_format, write_kind, ops, n_pre_ops=0, ccm=No
         ch.ccm[:] = ccm
     if yuv_sub is not None:
         ch.yuv_sub[:] = yuv_sub
+    ch.border, ch.border_at = border, border_at
+    ch.border_value[:] = border_value
     return ch
 
 
@@ -124,7 +127,7 @@ class Workload:
             nv12 = ch.src_format in (abi.PIX_NV12, abi.PIX_NV21) or uyvy  # one luma byte per pixel, one chroma pair per 2 (x2) pixels
             elt = 12 if ch.dst_format == abi.PIX_F32C3 else 3
             out_bytes += s.dst_w * s.dst_h * elt
-            if s.default:
+            if s.default or ch.border:
                 continue
             if s.src not in masks:
                 masks[s.src] = (np.zeros((s.src_h, s.src_w), bool),
@@ -215,6 +218,46 @@ def nv12_preprocess(w=3840, h=2160, dst=(640, 640), seed=3, pitch_align=16, ccm=
     name = {abi.PIX_NV12: "nv12_preprocess", abi.PIX_NV21: "nv21_preprocess", abi.PIX_UYVY: "uyvy_preprocess"}[src_format]
     return Workload(name, [ch], [_frame(seed, pitch * h if uyvy else pitch * (h + h // 2), 16, 236)], [dw * dh * 12], planes,
                     f"{name[:4].upper()} {w}x{h} -> planar fp32 3x{dh}x{dw}", extra={"colour": colour})
+
+
+def tsplit_resize(w=300, h=170, dst=(96, 64), seed=13) -> Workload:
+    """Four frames -> Resize IGNORE_AR -> Mul -> TensorTSplit<float3>: a colour-plane-transposed tensor (all first
+    channels of the four images, then all second ones, then all third ones)."""
+    pitch = _pitch(w * 3, 16)
+    dw, dh = dst
+    plane = dw * dh * 4
+    ch = chain(abi.PIX_U8C3, abi.GEOM_RESIZE_IGNORE_AR, abi.PIX_F32C3, abi.WRITE_SPLIT, [op(abi.OP_MUL, (0.25, 1.0, 2.5))])
+    planes = [PlaneSpec(i, 0, i * plane, w, h, pitch, (0, 0, w, h), dw, dh, dw * 4, dst_channel_stride=4 * plane) for i in range(4)]
+    return Workload("tsplit_resize", [ch], [_frame(seed + i, pitch * h) for i in range(4)], [12 * plane], planes,
+                    "4 frames -> transposed planar fp32 tensor")
+
+
+def border_crops(mode=abi.BORDER_REPLICATE, w=200, h=120, dst=(96, 80), value=(9, 77, 250), seed=14) -> Workload:
+    """Four frames -> BorderReader<mode> -> Crop (rectangles that leave the frame on every side; one stays inside) ->
+    Resize PRESERVE_AR -> Mul -> TensorWrite<float3>."""
+    pitch = _pitch(w * 3, 16)
+    dw, dh = dst
+    ch = chain(abi.PIX_U8C3, abi.GEOM_RESIZE_PRESERVE_AR, abi.PIX_F32C3, abi.WRITE_PACKED, [op(abi.OP_MUL, (0.5, 1.0, 2.0))],
+               border=mode, border_at=0, border_value=tuple(float(v) for v in value))
+    rects = [(-30, -20, 100, 90), (w - 40, h - 25, 90, 70), (20, 10, 64, 48), (-w // 2, h - 10, 2 * w, 60)]
+    planes = [PlaneSpec(i, 0, i * dw * dh * 12, w, h, pitch, (x & 0xffffffff, y & 0xffffffff, cw, chh), dw, dh, dw * 12,
+                        bg=(114.0, 114.0, 114.0)) for i, (x, y, cw, chh) in enumerate(rects)]
+    return Workload("border_crops", [ch], [_frame(seed + i, pitch * h) for i in range(4)], [4 * dw * dh * 12], planes,
+                    f"BorderReader mode {mode}", extra={"mode": mode, "value": value, "rects": rects})
+
+
+def nv12_border_constant(w=128, h=72, dst=(80, 60), rect=(-16, -8, 160, 90), value=(12.5, 200.25, 99.0), seed=15) -> Workload:
+    """ReadYUV<NV12> -> ConvertYUVToRGB -> BorderReader<CONSTANT>(float3) -> Crop -> Resize IGNORE_AR -> TensorSplit<float3>:
+    the constant stands for the converted colour."""
+    pitch = _pitch(w, 16)
+    dw, dh = dst
+    ch = chain(abi.PIX_NV12, abi.GEOM_RESIZE_IGNORE_AR, abi.PIX_F32C3, abi.WRITE_SPLIT, [op(abi.OP_YUV2RGB)], n_pre_ops=1,
+               ccm=BT709_FULL_8BIT, yuv_sub=(0.0, 128.0, 128.0), border=abi.BORDER_CONSTANT, border_at=1, border_value=value)
+    x, y, cw, chh = rect
+    planes = [PlaneSpec(0, 0, 0, w, h, pitch, (x & 0xffffffff, y & 0xffffffff, cw, chh), dw, dh, dw * 4, dst_channel_stride=dw * dh * 4,
+                        chroma_offset=pitch * h)]
+    return Workload("nv12_border_constant", [ch], [_frame(seed, pitch * (h + h // 2), 16, 236)], [dw * dh * 12], planes,
+                    "NV12 with a constant border in RGB", extra={"value": value, "rect": rect})
 
 
 def conditional_resize(used=5, w=320, h=180, dst=(96, 64), default=(7, 200, 33), seed=11) -> Workload:

@@ -40,7 +40,7 @@
 extern "C" {
 #endif
 
-#define FKB_ABI_VERSION 1u
+#define FKB_ABI_VERSION 2u
 #define FKB_PLANE_DEFAULT 0x80000000u
 #define FKB_MAX_OPS 12u          /* compute ops per chain */
 #define FKB_MAX_PLANE_PARAMS 4u  /* per-plane float3 operands a chain may refer to */
@@ -72,6 +72,10 @@ enum { FKB_GEOM_NONE = 0, FKB_GEOM_RESIZE_IGNORE_AR = 1, FKB_GEOM_RESIZE_PRESERV
         * number (resize.h:212-222), and the image flush with the left edge (resize.h:176-189).  On the device they are
         * PRESERVE_AR with other x1..y2; only fkb_resize_params tells them apart. */
        FKB_GEOM_RESIZE_PRESERVE_AR_RN_EVEN = 3, FKB_GEOM_RESIZE_PRESERVE_AR_LEFT = 4 };
+
+/* BorderType of the reference (border_reader.h:25-36), shifted by one so that 0 means "no BorderReader". */
+enum { FKB_BORDER_NONE = 0, FKB_BORDER_CONSTANT = 1, FKB_BORDER_REPLICATE = 2, FKB_BORDER_REFLECT = 3, FKB_BORDER_WRAP = 4,
+       FKB_BORDER_REFLECT_101 = 5 };
 
 /* Write kinds.  PACKED: interleaved pixels in pitched rows — PerThreadWrite<_2D,T> and
  * TensorWrite<T> (memory_operations.h:85-107, 160-179).  SPLIT: TensorSplit<float3>
@@ -111,6 +115,14 @@ typedef struct fkb_chain_desc {
     fkb_op ops[FKB_MAX_OPS];
     float ccm[9];         /* FKB_OP_YUV2RGB: row-major 3x3 (algorithms/image_processing/itu_color.h:185-258) */
     float yuv_sub[3];     /* FKB_OP_YUV2RGB: subtracted from (Y,U,V) first; Full range 8 bit = (0,128,128) */
+    uint32_t border;      /* FKB_BORDER_*: a BorderReader between the Read and the Crop
+                             (algorithms/image_processing/border_reader.h:25-334).  With one, the crop rectangle may leave
+                             the frame: a frame coordinate outside [0,src_w) x [0,src_h) is remapped by the mode, or
+                             (CONSTANT) the read yields border_value.  crop_x / crop_y are then taken as signed, as
+                             Crop::exec casts them (crop.h:36-39). */
+    uint32_t border_at;   /* ops[0..border_at) sit before the BorderReader (border_at <= n_pre_ops with a RESIZE
+                             geometry): CONSTANT's value replaces their result, the later ops still run on it */
+    float border_value[3];
 } fkb_chain_desc;
 
 typedef struct fkb_plane_desc {

@@ -84,6 +84,7 @@ protected:
 
     size_t bytes() const {
         if constexpr (D == ND::_2D) return static_cast<size_t>(ptr_a.dims.pitch) * ptr_a.dims.height;
+        else if constexpr (D == ND::T3D) return static_cast<size_t>(ptr_a.dims.color_planes_pitch) * ptr_a.dims.color_planes;
         else return static_cast<size_t>(ptr_a.dims.plane_pitch) * ptr_a.dims.planes * ptr_a.dims.color_planes;
     }
 
@@ -119,6 +120,7 @@ public:
         } else {
             if (dims.pitch == 0) dims.pitch = sizeof(T) * dims.width;
             dims.plane_pitch = dims.pitch * dims.height;
+            if constexpr (D == ND::T3D) dims.color_planes_pitch = dims.plane_pitch * dims.planes;  // ptr_nd.h:119-125
             if (on_device) gpuErrchk(cudaMalloc(&m_alloc->device, static_cast<size_t>(dims.plane_pitch) * dims.planes * dims.color_planes));
         }
         ptr_a.dims = dims;
@@ -143,6 +145,7 @@ public:
         if (!ptr_pinned.data) throw std::runtime_error("This Ptr has no host side to index");
         char* base = reinterpret_cast<char*>(ptr_pinned.data);
         if constexpr (D == ND::_3D) base += static_cast<size_t>(z) * ptr_pinned.dims.plane_pitch * ptr_pinned.dims.color_planes;
+        if constexpr (D == ND::T3D) base += static_cast<size_t>(z) * ptr_pinned.dims.plane_pitch;  // colour plane 0
         return *(reinterpret_cast<T*>(base + static_cast<size_t>(y) * ptr_pinned.dims.pitch) + x);
     }
     T& at(const Point& p) const { return at(p.x, p.y, p.z); }
@@ -180,6 +183,24 @@ public:
     Tensor(T* data, const uint& width_, const uint& height_, const uint& planes_, const uint& color_planes_ = 1,
            const MemType& type_ = defaultMemType, const int& deviceID_ = 0)
         : Ptr<ND::_3D, T>(data, PtrDims<ND::_3D>(width_, height_, planes_, color_planes_, sizeof(T) * width_), type_, deviceID_) {}
+};
+
+// A colour-plane-transposed tensor (core/data/ptr_nd.h:696-714)
+template <typename T>
+class TensorT : public Ptr<ND::T3D, T> {
+    static PtrDims<ND::T3D> wrapped(uint w, uint h, uint planes, uint color_planes) {
+        PtrDims<ND::T3D> d(w, h, planes, color_planes);
+        d.pitch = sizeof(T) * w; d.plane_pitch = d.pitch * h; d.color_planes_pitch = d.plane_pitch * planes;
+        return d;
+    }
+public:
+    TensorT() = default;
+    TensorT(const uint& width_, const uint& height_, const uint& planes_, const uint& color_planes_ = 1,
+            const MemType& type_ = defaultMemType, const int& deviceID_ = 0)
+        : Ptr<ND::T3D, T>(PtrDims<ND::T3D>(width_, height_, planes_, color_planes_), type_, deviceID_) {}
+    TensorT(T* data, const uint& width_, const uint& height_, const uint& planes_, const uint& color_planes_ = 1,
+            const MemType& type_ = defaultMemType, const int& deviceID_ = 0)
+        : Ptr<ND::T3D, T>(data, wrapped(width_, height_, planes_, color_planes_), type_, deviceID_) {}
 };
 
 // The reference's enumerators (itu_color.h:30, 53); the 8-bit formats NV12, NV21 and UYVY are the ones these kernels read.

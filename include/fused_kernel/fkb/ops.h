@@ -25,6 +25,8 @@ namespace fk {
 
 enum class InterpolationType { INTER_LINEAR = 1 };
 enum class AspectRatio { PRESERVE_AR = 0, IGNORE_AR = 1, PRESERVE_AR_RN_EVEN = 2, PRESERVE_AR_LEFT = 3 };  // resize.h:42
+// border_reader.h:25-36
+enum class BorderType : int { CONSTANT = 0, REPLICATE = 1, REFLECT = 2, WRAP = 3, REFLECT_101 = 4, TRANSPARENT_ = 5, DEFAULT = REFLECT_101, ISOLATED = 16 };
 enum class PlanePolicy { PROCESS_ALL = 0, CONDITIONAL_WITH_DEFAULT = 1 };  // batch_operations.h:75
 enum class ColorConversionCodes { COLOR_BGR2RGB, COLOR_RGB2BGR };
 
@@ -50,8 +52,14 @@ struct ReadState {
     // BatchRead<CONDITIONAL_WITH_DEFAULT>: planes >= used_planes yield dflt instead of reading (-1: every plane reads)
     int used_planes{-1};
     float dflt[3]{0.f, 0.f, 0.f};
+    // BorderReader between the first border_at ops and the Crop (0 = none, else FKB_BORDER_*)
+    uint32_t border{0};
+    size_t border_at{0};
+    float border_value[3]{0.f, 0.f, 0.f};
 };
 inline std::array<float, 3> f3(const float3& v) { return {v.x, v.y, v.z}; }
+template <typename T, typename = void> struct has_read_state : std::false_type {};
+template <typename T> struct has_read_state<T, std::void_t<decltype(std::declval<T>().st)>> : std::true_type {};
 }  // namespace detail
 
 // ---- compute IOps -------------------------------------------------------------------------------------------------
@@ -109,6 +117,34 @@ struct ConvertYUVToRGB {
     }
 };
 
+// ---- BorderReader (algorithms/image_processing/border_reader.h) ------------------------------------------------
+struct BorderIOp {
+    uint32_t mode;     // FKB_BORDER_*
+    float value[3];    // CONSTANT only
+};
+template <BorderType BT>
+struct BorderReader {
+    static_assert(BT == BorderType::CONSTANT || BT == BorderType::REPLICATE || BT == BorderType::REFLECT || BT == BorderType::WRAP ||
+                  BT == BorderType::REFLECT_101, "CONSTANT, REPLICATE, REFLECT, WRAP and REFLECT_101 are the border modes the reference implements");
+    static constexpr uint32_t mode = static_cast<uint32_t>(BT) + 1u;
+    static auto build() {
+        static_assert(BT != BorderType::CONSTANT, "BorderReader<CONSTANT> needs its value: build(value)");
+        return BorderIOp{mode, {0.f, 0.f, 0.f}};
+    }
+    // build(value): the incomplete CONSTANT reader; build(readIOp): the complete form of the other modes
+    template <typename A>
+    static auto build(const A& a) {
+        if constexpr (detail::has_read_state<A>::value) {
+            return a.then(build());
+        } else {
+            static_assert(BT == BorderType::CONSTANT, "only BorderReader<CONSTANT> takes a value");
+            return BorderIOp{mode, {static_cast<float>(a.x), static_cast<float>(a.y), static_cast<float>(a.z)}};
+        }
+    }
+    template <typename R, typename V>
+    static auto build(const R& read, const V& value) { return read.then(build(value)); }
+};
+
 // ---- incomplete ReadBack IOps ----------------------------------------------------------------------------------
 template <size_t BATCH>
 struct CropIOp {
@@ -159,6 +195,14 @@ struct ReadIOp {
     }
     ActiveThreads getActiveThreads() const { return params.activeThreads; }
 
+    auto then(const BorderIOp& b) const {
+        if (st.has_resize || !st.crops.empty() || st.border)
+            throw std::runtime_error("a BorderReader directly on the Read (before any Crop or Resize) is the placement the B200 kernels implement");
+        detail::ReadState s = st;
+        s.border = b.mode; s.border_at = s.ops.size();
+        for (int c = 0; c < 3; ++c) s.border_value[c] = b.value[c];
+        return ReadIOp<OutT, BATCH>(std::move(s));
+    }
     template <size_t N>
     auto then(const CropIOp<N>& c) const {
         static_assert(BATCH == 0 || N == 0 || BATCH == N, "Fusing two batch operations of different BATCH size is not allowed.");
@@ -196,6 +240,9 @@ struct ReadIOp {
         return ReadIOp<O, BATCH>(std::move(s));
     }
 };
+// readIOp & nextIOp: the reference's other spelling of .then()
+template <typename O, size_t B, typename Next>
+auto operator&(const ReadIOp<O, B>& read, const Next& next) -> decltype(read.then(next)) { return read.then(next); }
 template <typename T> constexpr bool isReadIOp = false;
 template <typename O, size_t B> constexpr bool isReadIOp<ReadIOp<O, B>> = true;
 
@@ -292,14 +339,27 @@ struct TensorWrite {
 };
 template <typename T>
 struct TensorSplit {
-    static_assert(std::is_same_v<T, float3>, "TensorSplit<float3> is the planar write the B200 kernels implement");
-    static auto build(const RawPtr<ND::_3D, float>& p) {
+    static_assert(std::is_same_v<T, float3> || std::is_same_v<T, uchar3>, "TensorSplit<float3|uchar3> are the planar writes the B200 kernels implement");
+    using Base = std::conditional_t<std::is_same_v<T, float3>, float, uchar>;
+    static auto build(const RawPtr<ND::_3D, Base>& p) {
         // memory_operations.h:189-205: channel c of pixel (x,y) lies width*height elements after channel c-1
         return WriteIOp<T>{FKB_WRITE_SPLIT, p.data, p.dims.width, p.dims.height, p.dims.pitch, p.dims.planes,
                            static_cast<size_t>(p.dims.plane_pitch) * p.dims.color_planes,
-                           static_cast<size_t>(p.dims.width) * p.dims.height * sizeof(float)};
+                           static_cast<size_t>(p.dims.width) * p.dims.height * sizeof(Base)};
     }
-    static auto build(const Ptr<ND::_3D, float>& p) { return build(p.ptr()); }
+    static auto build(const Ptr<ND::_3D, Base>& p) { return build(p.ptr()); }
+};
+// The same planar write into a colour-plane-transposed tensor (memory_operations.h:214-241): channel c of image z lies
+// at c * color_planes_pitch + z * plane_pitch (core/data/rawptr.h:229-239).
+template <typename T>
+struct TensorTSplit {
+    static_assert(std::is_same_v<T, float3> || std::is_same_v<T, uchar3>, "TensorTSplit<float3|uchar3> are the planar writes the B200 kernels implement");
+    using Base = std::conditional_t<std::is_same_v<T, float3>, float, uchar>;
+    static auto build(const RawPtr<ND::T3D, Base>& p) {
+        return WriteIOp<T>{FKB_WRITE_SPLIT, p.data, p.dims.width, p.dims.height, p.dims.pitch, p.dims.planes,
+                           static_cast<size_t>(p.dims.plane_pitch), static_cast<size_t>(p.dims.color_planes_pitch)};
+    }
+    static auto build(const Ptr<ND::T3D, Base>& p) { return build(p.ptr()); }
 };
 
 }  // namespace fk

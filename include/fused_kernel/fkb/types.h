@@ -30,7 +30,7 @@ inline void gpuAssert(cudaError_t code, const char* file, int line) {
 }
 #define gpuErrchk(ans) ::fk::gpuAssert((ans), __FILE__, __LINE__)
 
-enum class ND { _1D = 1, _2D = 2, _3D = 3 };
+enum class ND { _1D = 1, _2D = 2, _3D = 3, T3D = 4 };  // core/data/ptr_nd.h: T3D is the colour-plane-transposed tensor
 enum class MemType { Device, Host, HostPinned, DeviceAndPinned };
 constexpr MemType defaultMemType = MemType::DeviceAndPinned;
 // Only the NVIDIA GPU architecture is executable here; the other enumerators exist so that user code naming them still
@@ -87,6 +87,13 @@ template <> struct PtrDims<ND::_3D> {
     constexpr PtrDims() = default;
     constexpr PtrDims(uint w, uint h, uint planes_, uint color_planes_ = 1, uint p = 0)
         : width(w), height(h), planes(planes_), color_planes(color_planes_), pitch(p), plane_pitch(p * h) {}
+};
+// Colour-plane-transposed batch (core/data/rawptr.h:76-104): all first channels of all images, then all second ones, ...
+template <> struct PtrDims<ND::T3D> {
+    uint width{0}, height{0}, planes{0}, color_planes{0}, pitch{0}, plane_pitch{0}, color_planes_pitch{0};
+    constexpr PtrDims() = default;
+    constexpr PtrDims(uint w, uint h, uint planes_, uint color_planes_ = 1)
+        : width(w), height(h), planes(planes_), color_planes(color_planes_) {}
 };
 template <ND D, typename T>
 struct RawPtr {

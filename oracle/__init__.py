@@ -69,6 +69,12 @@ def load_ref() -> C.CDLL:
         lib.fklref_saturate_u8.argtypes = [C.c_float]
         lib.fklref_resize_params.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, f32p, i32p]
         u8p = C.POINTER(C.c_uint8)
+        lib.fklref_resize_tsplit_f32.restype = C.c_int
+        lib.fklref_resize_tsplit_f32.argtypes = [pp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, f32p, C.c_void_p]
+        lib.fklref_border_crop_resize.restype = C.c_int
+        lib.fklref_border_crop_resize.argtypes = [C.c_int, pp, C.c_int, C.c_int, C.c_int, i32p, f32p, C.c_int, C.c_int, f32p, f32p, C.c_void_p]
+        lib.fklref_nv12_border_constant.restype = C.c_int
+        lib.fklref_nv12_border_constant.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, i32p, f32p, C.c_int, C.c_int, C.c_void_p]
         lib.fklref_ycbcr_matrix.restype = C.c_int
         lib.fklref_ycbcr_matrix.argtypes = [C.c_int, C.c_int, f32p]
         lib.fklref_yuv_resize_split.restype = C.c_int
@@ -188,6 +194,18 @@ def run_ref(wl, threads: int = 1):
         offs = (C.c_float * k)(*[float(x) for x in wl.extra["offs"]])
         rc = lib.fklref_divergent(frame_ptrs(wl.planes), p0.src_w, p0.src_h, p0.src_pitch, p0.dst_w, p0.dst_h, scales, offs,
                                   outs[0].ctypes.data, outs[1].ctypes.data, k)
+    elif wl.name == "border_crops":
+        flat = [v for r in wl.extra["rects"] for v in r]
+        rc = lib.fklref_border_crop_resize(wl.extra["mode"] - 1, frame_ptrs(wl.planes), p0.src_w, p0.src_h, p0.src_pitch,
+                                           (C.c_int32 * 16)(*flat), _f3(wl.extra["value"]), p0.dst_w, p0.dst_h, _f3(p0.bg),
+                                           _f3(ch.ops[0].v), outs[0].ctypes.data)
+    elif wl.name == "nv12_border_constant":
+        rc = lib.fklref_nv12_border_constant(wl.sources[0].ctypes.data, p0.src_w, p0.src_h, p0.src_pitch,
+                                             (C.c_int32 * 4)(*wl.extra["rect"]), _f3(wl.extra["value"]), p0.dst_w, p0.dst_h,
+                                             outs[0].ctypes.data)
+    elif wl.name == "tsplit_resize":
+        rc = lib.fklref_resize_tsplit_f32(frame_ptrs(wl.planes), p0.src_w, p0.src_h, p0.src_pitch, p0.dst_w, p0.dst_h,
+                                          _f3(ch.ops[0].v), outs[0].ctypes.data)
     elif wl.name in ("conditional_resize", "conditional_pointwise"):
         dflt = (C.c_uint8 * 3)(*[int(v) for v in wl.extra["default"]])
         every = list(wl.planes)

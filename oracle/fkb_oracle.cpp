@@ -31,6 +31,7 @@
 //   writes ......................... algorithms/basic_ops/memory_operations.h:92-97, 167-170, 189-205
 #include <cmath>
 #include <cstdint>
+#include <cstdlib>
 #include <cstring>
 #include <thread>
 #include <vector>
@@ -112,9 +113,8 @@ inline V3 apply_ops(V3 v, const fkb_chain_desc& ch, const fkb_plane_desc& pl, ui
     return v;
 }
 
-// Read of crop-relative pixel (cx,cy): Crop adds the rectangle origin (crop.h:36-39), then the Read.
-inline V3 read_tap(const fkb_chain_desc& ch, const fkb_plane_desc& pl, int cx, int cy) {
-    const size_t X = static_cast<size_t>(cx) + pl.crop_x, Y = static_cast<size_t>(cy) + pl.crop_y;
+// Read of frame pixel (X,Y).
+inline V3 read_frame(const fkb_chain_desc& ch, const fkb_plane_desc& pl, size_t X, size_t Y) {
     const uint8_t* base = static_cast<const uint8_t*>(pl.src);
     V3 v;
     if (ch.src_format == FKB_PIX_NV12) {
@@ -139,6 +139,52 @@ inline V3 read_tap(const fkb_chain_desc& ch, const fkb_plane_desc& pl, int cx, i
     return v;
 }
 
+// BorderReader index maps (border_reader.h:211-330): idx = low(high(i)), written out per mode.  `n` is the extent of
+// the back operation along the axis (last = n - 1).
+inline int border_index(uint32_t mode, int i, int n) {
+    const int last = n - 1;
+    switch (mode) {
+    case FKB_BORDER_REPLICATE: {                     // :211-232
+        const int hi = i < last ? i : last;
+        return hi > 0 ? hi : 0;
+    }
+    case FKB_BORDER_REFLECT: {                       // :234-256
+        const int hi = last - std::abs(last - i) + (i > last ? 1 : 0);
+        return (std::abs(hi) - (hi < 0 ? 1 : 0)) % (last + 1);
+    }
+    case FKB_BORDER_WRAP: {                          // :258-287
+        const int hi = i < n ? i : i % n;
+        return hi >= 0 ? hi : hi - ((hi - n + 1) / n) * n;
+    }
+    case FKB_BORDER_REFLECT_101: {                   // :289-311
+        const int hi = std::abs(last - std::abs(last - i)) % (last + 1);
+        return std::abs(hi) % (last + 1);
+    }
+    default: return i;
+    }
+}
+
+// Value of crop-relative pixel (cx,cy) after ops[0..n_tap_ops): Crop adds the rectangle origin as signed integers
+// (crop.h:36-39); a BorderReader, if the chain has one, sits between the first border_at ops and the Crop
+// (border_reader.h:177-209 for CONSTANT, :166-172 for the index-mapping modes).
+inline V3 tap(const fkb_chain_desc& ch, const fkb_plane_desc& pl, int cx, int cy, uint32_t n_tap_ops) {
+    const int X = cx + static_cast<int>(pl.crop_x), Y = cy + static_cast<int>(pl.crop_y);
+    if (ch.border == FKB_BORDER_NONE)
+        return apply_ops(read_frame(ch, pl, static_cast<size_t>(X), static_cast<size_t>(Y)), ch, pl, 0, n_tap_ops);
+    const int w = static_cast<int>(pl.src_w), h = static_cast<int>(pl.src_h);
+    if (ch.border == FKB_BORDER_CONSTANT) {
+        V3 v;
+        if (X >= 0 && X < w && Y >= 0 && Y < h) {
+            v = apply_ops(read_frame(ch, pl, static_cast<size_t>(X), static_cast<size_t>(Y)), ch, pl, 0, ch.border_at);
+        } else {
+            v.c[0] = ch.border_value[0]; v.c[1] = ch.border_value[1]; v.c[2] = ch.border_value[2];
+        }
+        return apply_ops(v, ch, pl, ch.border_at, n_tap_ops);
+    }
+    const int bx = border_index(ch.border, X, w), by = border_index(ch.border, Y, h);
+    return apply_ops(read_frame(ch, pl, static_cast<size_t>(bx), static_cast<size_t>(by)), ch, pl, 0, n_tap_ops);
+}
+
 inline V3 pixel(const fkb_chain_desc& ch, const fkb_plane_desc& pl, int x, int y) {
     if (pl.chain & FKB_PLANE_DEFAULT) {
         // a plane beyond usedPlanes of BatchRead<CONDITIONAL_WITH_DEFAULT> (batch_operations.h:262-266): the read —
@@ -148,7 +194,7 @@ inline V3 pixel(const fkb_chain_desc& ch, const fkb_plane_desc& pl, int x, int y
         return apply_ops(d, ch, pl, ch.geometry == FKB_GEOM_NONE ? 0 : ch.n_pre_ops, ch.n_ops);
     }
     if (ch.geometry == FKB_GEOM_NONE) {
-        return apply_ops(read_tap(ch, pl, x, y), ch, pl, 0, ch.n_ops);
+        return tap(ch, pl, x, y, ch.n_ops);
     }
     V3 v;
     int tx = x, ty = y;
@@ -167,10 +213,10 @@ inline V3 pixel(const fkb_chain_desc& ch, const fkb_plane_desc& pl, int x, int y
         // The reference reads x1,y1 unclamped; they stay inside the crop for every sane scale.  Clamp the
         // address only (weights still use the unclamped values) so a degenerate scale cannot read outside.
         const int x1r = x1 < pl.crop_w - 1 ? x1 : pl.crop_w - 1, y1r = y1 < pl.crop_h - 1 ? y1 : pl.crop_h - 1;
-        const V3 p00 = apply_ops(read_tap(ch, pl, x1r, y1r), ch, pl, 0, ch.n_pre_ops);
-        const V3 p10 = apply_ops(read_tap(ch, pl, x2r, y1r), ch, pl, 0, ch.n_pre_ops);
-        const V3 p01 = apply_ops(read_tap(ch, pl, x1r, y2r), ch, pl, 0, ch.n_pre_ops);
-        const V3 p11 = apply_ops(read_tap(ch, pl, x2r, y2r), ch, pl, 0, ch.n_pre_ops);
+        const V3 p00 = tap(ch, pl, x1r, y1r, ch.n_pre_ops);
+        const V3 p10 = tap(ch, pl, x2r, y1r, ch.n_pre_ops);
+        const V3 p01 = tap(ch, pl, x1r, y2r, ch.n_pre_ops);
+        const V3 p11 = tap(ch, pl, x2r, y2r, ch.n_pre_ops);
         const float w00 = (x2 - sx) * (y2 - sy), w10 = (sx - x1) * (y2 - sy);
         const float w01 = (x2 - sx) * (sy - y1), w11 = (sx - x1) * (sy - y1);
         for (int c = 0; c < 3; ++c)

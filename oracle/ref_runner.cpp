@@ -12,6 +12,7 @@
 #include <fused_kernel/algorithms/basic_ops/cast.h>
 #include <fused_kernel/algorithms/basic_ops/memory_operations.h>
 #include <fused_kernel/algorithms/image_processing/color_conversion.h>
+#include <fused_kernel/algorithms/image_processing/border_reader.h>
 #include <fused_kernel/algorithms/image_processing/crop.h>
 #include <fused_kernel/algorithms/image_processing/image.h>
 #include <fused_kernel/algorithms/image_processing/resize.h>
@@ -220,6 +221,23 @@ int fklref_conditional_pointwise_u8(const uint8_t* const* frames, int w, int h, 
     return 0;
 }
 
+// Four frames -> Resize(IGNORE_AR) -> Mul -> TensorTSplit<float3> into a colour-plane-transposed tensor
+// (memory_operations.h:214-241): all R planes, then all G planes, then all B planes.
+int fklref_resize_tsplit_f32(const uint8_t* const* frames, int w, int h, int pitch, int dw, int dh, const float* mul, float* out) {
+    CpuStream stream;
+    std::array<Ptr2D<uchar3>, 4> ptrs;
+    for (size_t i = 0; i < 4; ++i) ptrs[i] = wrap_frame(frames[i], w, h, pitch);
+    // (the reference's TensorT constructor that wraps caller memory leaves the three pitches at zero; they are set here
+    // the way its allocating constructor sets them, ptr_nd.h:119-125)
+    PtrDims<ND::T3D> dims(dw, dh, 4, 3);
+    dims.pitch = sizeof(float) * dw; dims.plane_pitch = dims.pitch * dh; dims.color_planes_pitch = dims.plane_pitch * 4;
+    const RawPtr<ND::T3D, float> t{out, dims};
+    executeOperations<CpuDPP>(stream, PerThreadRead<ND::_2D, uchar3>::build(ptrs),
+        Resize<InterpolationType::INTER_LINEAR, AspectRatio::IGNORE_AR>::build(Size(dw, dh)),
+        Mul<float3>::build(make_<float3>(mul[0], mul[1], mul[2])), TensorTSplit<float3>::build(t));
+    return 0;
+}
+
 // Read -> Cast -> Mul -> Add -> Div -> ColorConversion<BGR2RGB> -> SaturateCast -> PerThreadWrite
 int fklref_pointwise_u8(const uint8_t* src, int w, int h, int spitch, const float* mul, const float* add,
                         const float* div, uint8_t* dst, int dpitch) {
@@ -287,6 +305,61 @@ extern "C" int fklref_ycbcr_matrix(int range, int primitives, float* m9) {
     case 5: matrix_of<ColorRange::Full, ColorPrimitives::bt2020>(m9); return 0;
     default: return -1;
     }
+}
+
+// Four frames -> BorderReader<BT> -> Crop (rectangles that may leave the frame) -> Resize(PRESERVE_AR, bg) -> Mul ->
+// TensorWrite<float3>.  mode: the reference's BorderType value (0 CONSTANT .. 4 REFLECT_101).
+template <BorderType BT>
+static int border_crop_resize(const uint8_t* const* frames, int w, int h, int pitch, const int32_t* rects, const float* value, int dw, int dh,
+                              const float* bg, const float* mul, float* out) {
+    CpuStream stream;
+    std::array<Ptr2D<uchar3>, 4> ptrs; std::array<Rect, 4> rs;
+    for (size_t i = 0; i < 4; ++i) {
+        ptrs[i] = wrap_frame(frames[i], w, h, pitch);
+        rs[i] = Rect(rects[4 * i], rects[4 * i + 1], rects[4 * i + 2], rects[4 * i + 3]);
+    }
+    Tensor<float3> t(reinterpret_cast<float3*>(out), dw, dh, 4, 1, MemType::Host, 0);
+    const auto resize = Resize<InterpolationType::INTER_LINEAR, AspectRatio::PRESERVE_AR>::build(Size(dw, dh), make_<float3>(bg[0], bg[1], bg[2]));
+    const auto m = Mul<float3>::build(make_<float3>(mul[0], mul[1], mul[2]));
+    if constexpr (BT == BorderType::CONSTANT) {
+        // the incomplete form BorderReader<CONSTANT>::build(value) does not compile as a link of a chain in the reference;
+        // its complete form build(readIOp, value) does (tests/algorithm/test_border_reader.h:26): one plane per call
+        const uchar3 v = make_<uchar3>(static_cast<uchar>(value[0]), static_cast<uchar>(value[1]), static_cast<uchar>(value[2]));
+        for (size_t i = 0; i < 4; ++i) {
+            Tensor<float3> ti(reinterpret_cast<float3*>(out) + i * static_cast<size_t>(dw) * dh, dw, dh, 1, 1, MemType::Host, 0);
+            const auto bordered = BorderReader<BT>::build(PerThreadRead<ND::_2D, uchar3>::build(ptrs[i]), v);
+            executeOperations<CpuDPP>(stream, bordered, Crop<>::build(rs[i]), resize, m, TensorWrite<float3>::build(ti));
+        }
+    } else {
+        executeOperations<CpuDPP>(stream, PerThreadRead<ND::_2D, uchar3>::build(ptrs), BorderReader<BT>::build(), Crop<>::build(rs), resize, m,
+                                  TensorWrite<float3>::build(t));
+    }
+    return 0;
+}
+extern "C" int fklref_border_crop_resize(int mode, const uint8_t* const* frames, int w, int h, int pitch, const int32_t* rects, const float* value,
+                                         int dw, int dh, const float* bg, const float* mul, float* out) {
+    switch (mode) {
+    case 0: return border_crop_resize<BorderType::CONSTANT>(frames, w, h, pitch, rects, value, dw, dh, bg, mul, out);
+    case 1: return border_crop_resize<BorderType::REPLICATE>(frames, w, h, pitch, rects, value, dw, dh, bg, mul, out);
+    case 2: return border_crop_resize<BorderType::REFLECT>(frames, w, h, pitch, rects, value, dw, dh, bg, mul, out);
+    case 3: return border_crop_resize<BorderType::WRAP>(frames, w, h, pitch, rects, value, dw, dh, bg, mul, out);
+    case 4: return border_crop_resize<BorderType::REFLECT_101>(frames, w, h, pitch, rects, value, dw, dh, bg, mul, out);
+    default: return -1;
+    }
+}
+// ReadYUV<NV12> -> ConvertYUVToRGB<p8bit, Full, bt709> -> BorderReader<CONSTANT>(float3) -> Crop -> Resize(IGNORE_AR) -> TensorSplit:
+// the constant replaces the converted colour, not the YCbCr triple.
+extern "C" int fklref_nv12_border_constant(const uint8_t* nv12, int w, int h, int pitch, const int32_t* rect, const float* value, int dw, int dh,
+                                           float* out) {
+    CpuStream stream;
+    const Ptr<ND::_2D, uchar> data(const_cast<uint8_t*>(nv12), PtrDims<ND::_2D>(w, h + h / 2, pitch), MemType::Host, 0);
+    const Image<PixelFormat::NV12> img(data, w, h);
+    Tensor<float> t(out, dw, dh, 1, 3, MemType::Host, 0);
+    const auto rgb = ReadYUV<PixelFormat::NV12>::build(img).then(ConvertYUVToRGB<ColorDepth::p8bit, ColorRange::Full, ColorPrimitives::bt709>::build());
+    const auto bordered = BorderReader<BorderType::CONSTANT>::build(rgb, make_<float3>(value[0], value[1], value[2]));
+    executeOperations<CpuDPP>(stream, bordered, Crop<>::build(Rect(rect[0], rect[1], rect[2], rect[3])),
+        Resize<InterpolationType::INTER_LINEAR, AspectRatio::IGNORE_AR>::build(Size(dw, dh)), TensorSplit<float3>::build(t));
+    return 0;
 }
 
 // ReadYUV<PF> -> ConvertYUVToRGB<p8bit, CR, CP> -> Resize(IGNORE_AR) -> Sub -> Div -> TensorSplit<float3>

@@ -236,6 +236,66 @@ static void test_conditional_batch() {
     report("conditional batch read (activeBatch, defaultValue)", std::memcmp(want.data(), out.ptrPinned().data, want.size() * 4) == 0);
 }
 
+// ---- BorderReader: crops that leave the frame -----------------------------------------------------------------------------
+template <BorderType BT>
+static void test_border(const char* what) {
+    Stream stream;
+    constexpr size_t BATCH = 3;
+    std::array<Ptr2D<uchar3>, BATCH> ptrs;
+    for (size_t i = 0; i < BATCH; ++i) { ptrs[i] = Ptr2D<uchar3>(150, 100); fill_random(ptrs[i], 500 + i); ptrs[i].upload(stream); }
+    const std::array<Rect, BATCH> rects{Rect(-20, -10, 90, 70), Rect(100, 60, 120, 80), Rect(10, 10, 50, 40)};
+    Tensor<float3> out(64, 64, BATCH);
+    const auto read = PerThreadRead<ND::_2D, uchar3>::build(ptrs);
+    const auto resize = Resize<InterpolationType::INTER_LINEAR, AspectRatio::PRESERVE_AR>::build(Size(64, 64), make_<float3>(1.f, 2.f, 3.f));
+    fkb_chain_desc ch{};
+    if constexpr (BT == BorderType::CONSTANT) {
+        executeOperations<TransformDPP<>>(stream, BorderReader<BT>::build(read, make_<uchar3>(200, 100, 50)) & Crop<>::build(rects) & resize,
+                                          TensorWrite<float3>::build(out));
+        ch.border_value[0] = 200.f; ch.border_value[1] = 100.f; ch.border_value[2] = 50.f;
+    } else {
+        executeOperations<TransformDPP<>>(stream, read, BorderReader<BT>::build(), Crop<>::build(rects), resize, TensorWrite<float3>::build(out));
+    }
+    out.download(stream);
+    stream.sync();
+    ch.src_format = FKB_PIX_U8C3; ch.geometry = FKB_GEOM_RESIZE_PRESERVE_AR; ch.dst_format = FKB_PIX_F32C3; ch.write_kind = FKB_WRITE_PACKED;
+    ch.border = static_cast<uint32_t>(BT) + 1u;
+    std::vector<float> want(64 * 64 * 3 * BATCH);
+    std::vector<fkb_plane_desc> planes;
+    for (size_t i = 0; i < BATCH; ++i) {
+        fkb_plane_desc d = host_plane(ptrs[i], rects[i], 64, 64, want.data() + i * 64 * 64 * 3, 64 * 12, ch.geometry);
+        d.bg[0] = 1.f; d.bg[1] = 2.f; d.bg[2] = 3.f;
+        planes.push_back(d);
+    }
+    fkb_oracle_run(&ch, 1, planes.data(), BATCH, 1);
+    report(what, std::memcmp(want.data(), out.ptrPinned().data, want.size() * 4) == 0);
+}
+
+// ---- transposed planar tensor: TensorTSplit<float3> ---------------------------------------------------------------------
+static void test_tensor_t_split() {
+    Stream stream;
+    constexpr size_t BATCH = 3;
+    std::array<Ptr2D<uchar3>, BATCH> ptrs;
+    for (size_t i = 0; i < BATCH; ++i) { ptrs[i] = Ptr2D<uchar3>(160, 90); fill_random(ptrs[i], 400 + i); ptrs[i].upload(stream); }
+    TensorT<float> out(80, 40, BATCH, 3);
+    executeOperations<TransformDPP<>>(stream, PerThreadRead<ND::_2D, uchar3>::build(ptrs), Resize<InterpolationType::INTER_LINEAR>::build(Size(80, 40)),
+                                      Mul<float3>::build(make_<float3>(2.f, 0.5f, 1.f)), TensorTSplit<float3>::build(out));
+    out.download(stream);
+    stream.sync();
+    fkb_chain_desc ch{};
+    ch.src_format = FKB_PIX_U8C3; ch.geometry = FKB_GEOM_RESIZE_IGNORE_AR; ch.dst_format = FKB_PIX_F32C3; ch.write_kind = FKB_WRITE_SPLIT;
+    ch.n_ops = 1; ch.ops[0] = op(FKB_OP_MUL, 2.f, 0.5f, 1.f);
+    const size_t plane = 80 * 40;
+    std::vector<float> want(plane * 3 * BATCH);
+    std::vector<fkb_plane_desc> planes;
+    for (size_t i = 0; i < BATCH; ++i) {
+        fkb_plane_desc d = host_plane(ptrs[i], Rect(0, 0, 160, 90), 80, 40, want.data() + i * plane, 80 * 4, ch.geometry);
+        d.dst_channel_stride = plane * BATCH * 4;  // all first channels, then all second ones, ...
+        planes.push_back(d);
+    }
+    fkb_oracle_run(&ch, 1, planes.data(), BATCH, 1);
+    report("TensorTSplit<float3> (transposed planar tensor)", std::memcmp(want.data(), out.ptrPinned().data, want.size() * 4) == 0);
+}
+
 // ---- divergent horizontal fusion: two sequences in one launch, global plane indices ------------------------------------
 struct Sel { static uint at(const uint& z) { return z < 2 ? 0u : 1u; } };
 static void test_divergent() {
@@ -305,6 +365,11 @@ int main() {
     test_batched<AspectRatio::PRESERVE_AR_RN_EVEN>("batched crop-resize-normalise, PRESERVE_AR_RN_EVEN", FKB_GEOM_RESIZE_PRESERVE_AR_RN_EVEN);
     test_batched<AspectRatio::PRESERVE_AR_LEFT>("batched crop-resize-normalise, PRESERVE_AR_LEFT", FKB_GEOM_RESIZE_PRESERVE_AR_LEFT);
     test_conditional_batch();
+    test_tensor_t_split();
+    test_border<BorderType::CONSTANT>("BorderReader<CONSTANT> (complete form, operator&)");
+    test_border<BorderType::REPLICATE>("BorderReader<REPLICATE>");
+    test_border<BorderType::REFLECT_101>("BorderReader<REFLECT_101>");
+    test_border<BorderType::WRAP>("BorderReader<WRAP>");
     test_divergent();
     test_errors();
     std::printf("%s\n", g_failed ? "FAILED" : "ALL PASSED");

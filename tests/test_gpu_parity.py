@@ -76,6 +76,7 @@ SMALL = {
     "divergent": lambda: W.divergent_planes(n_per_seq=4, w=480, h=270),
     "divergent_odd": lambda: W.divergent_planes(n_per_seq=3, w=330, h=190),
     "crop_reorder": lambda: W.crop_reorder(n=5),
+    "tsplit_resize": lambda: W.tsplit_resize(),
     "conditional_resize": lambda: W.conditional_resize(),
     "conditional_pointwise": lambda: W.conditional_pointwise(),
 }
@@ -145,6 +146,19 @@ def test_yuv_formats_ranges_primitives(fmt, rng, prim):
         wl = W.nv12_preprocess(**shape, src_format=fmt, colour=(rng, prim))
         check(wl)
         check(wl, force_gather=True)
+
+
+@pytest.mark.parametrize("mode", [abi.BORDER_CONSTANT, abi.BORDER_REPLICATE, abi.BORDER_REFLECT, abi.BORDER_WRAP, abi.BORDER_REFLECT_101])
+def test_border_reader_modes(mode):
+    for kw in [dict(), dict(w=37, h=23), dict(w=640, h=360, dst=(224, 224))]:
+        wl = W.border_crops(mode, **kw)
+        check(wl)
+        check(wl, use_plan=True)
+
+
+def test_border_constant_after_colour_conversion():
+    check(W.nv12_border_constant())
+    check(W.nv12_border_constant(w=640, h=360, rect=(500, 300, 400, 200), dst=(320, 320)))
 
 
 def test_many_planes_use_the_descriptor_arena():

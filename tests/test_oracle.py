@@ -136,8 +136,11 @@ def test_oracle_matches_golden_fixture(name):
     W.readme_crops(), W.vertical_fusion(w=1000, h=300), W.nv12_preprocess(w=1280, h=720, dst=(320, 320)),
     W.batched_crop_resize(n_frames=4, crops_per_frame=8, w=960, h=540), W.divergent_planes(n_per_seq=4, w=480, h=270),
     W.divergent_planes(n_per_seq=1, w=200, h=100), W.crop_reorder(n=5),
-    W.conditional_resize(), W.conditional_resize(used=0), W.conditional_resize(used=8), W.conditional_pointwise(),
-], ids=lambda w: w.name)
+    W.border_crops(abi.BORDER_CONSTANT), W.border_crops(abi.BORDER_REPLICATE), W.border_crops(abi.BORDER_REFLECT),
+    W.border_crops(abi.BORDER_WRAP), W.border_crops(abi.BORDER_REFLECT_101), W.border_crops(abi.BORDER_WRAP, w=37, h=23),
+    W.border_crops(abi.BORDER_REFLECT, w=37, h=23), W.border_crops(abi.BORDER_REFLECT_101, w=37, h=23), W.nv12_border_constant(),
+    W.tsplit_resize(), W.conditional_resize(), W.conditional_resize(used=0), W.conditional_resize(used=8), W.conditional_pointwise(),
+], ids=lambda w: w.name + w.description[-7:].replace(" ", "_"))
 def test_oracle_matches_reference_backend(wl):
     got, want = oracle.run_oracle(wl, threads=4), oracle.run_ref(wl, threads=4)
     for g, w in zip(got, want):

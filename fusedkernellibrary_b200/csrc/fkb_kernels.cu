@@ -561,7 +561,7 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
             for (int j = 0; j < 8; ++j)
                 if (j < nj) put(out_s + ooff[j], bgbits[0], bgbits[1], bgbits[2]);
         } else {
-            {   // every lane writes the same three bytes (even lanes the first staged row, odd lanes the second)
+            if (replicate) {  // every lane writes the same three bytes (even lanes the first staged row, odd lanes the second)
                 const uint32_t q = in_s + (lane & 1u) * kInRowBytes + rep_off;
                 const uint8_t c0 = smem_raw[q], c1 = smem_raw[q + 1], c2 = smem_raw[q + 2];
                 smem_raw[q + 3] = c0; smem_raw[q + 4] = c1; smem_raw[q + 5] = c2;

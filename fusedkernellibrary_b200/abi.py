@@ -22,7 +22,7 @@ PRIMITIVES_BT601, PRIMITIVES_BT709, PRIMITIVES_BT2020 = 0, 1, 2
 GEOM_NONE, GEOM_RESIZE_IGNORE_AR, GEOM_RESIZE_PRESERVE_AR = 0, 1, 2
 GEOM_RESIZE_PRESERVE_AR_RN_EVEN, GEOM_RESIZE_PRESERVE_AR_LEFT = 3, 4
 PLANE_DEFAULT = 0x80000000  # fkb_plane_desc.chain bit: the plane's read yields bg (conditional batch read)
-WRITE_PACKED, WRITE_SPLIT = 1, 2
+WRITE_PACKED, WRITE_SPLIT, WRITE_SPLIT_PLANES = 1, 2, 3
 BORDER_NONE, BORDER_CONSTANT, BORDER_REPLICATE, BORDER_REFLECT, BORDER_WRAP, BORDER_REFLECT_101 = 0, 1, 2, 3, 4, 5
 OP_CAST_F32, OP_MUL, OP_ADD, OP_SUB, OP_DIV, OP_REORDER_ZYX, OP_YUV2RGB, OP_SATCAST_U8 = 1, 2, 3, 4, 5, 6, 7, 8
 
@@ -51,10 +51,11 @@ class PlaneDesc(C.Structure):
         ("x1", C.c_int32), ("y1", C.c_int32), ("x2", C.c_int32), ("y2", C.c_int32),
         ("bg", C.c_float * 3), ("chain", C.c_uint32),
         ("params", (C.c_float * 3) * MAX_PLANE_PARAMS),
+        ("dst_y", C.c_void_p), ("dst_z", C.c_void_p),
     ]
 
 
-assert C.sizeof(Op) == 16 and C.sizeof(ChainDesc) == 284 and C.sizeof(PlaneDesc) == 160
+assert C.sizeof(Op) == 16 and C.sizeof(ChainDesc) == 284 and C.sizeof(PlaneDesc) == 176
 
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libfkb.so")
 

@@ -22,7 +22,8 @@ struct __align__(16) PlaneRec {
     const uint8_t* src;
     const uint8_t* src_chroma;
     uint8_t* dst;
-    uint64_t dst_cstride;
+    uint64_t dst_cstride;       // planar writes: byte offset of channel 1 from channel 0 ...
+    uint64_t dst_cstride2;      // ... and of channel 2 (twice the former for a tensor; arbitrary for three separate planes)
     uint32_t src_pitch;
     uint32_t crop_x, crop_y;
     int32_t crop_w, crop_h;
@@ -33,14 +34,17 @@ struct __align__(16) PlaneRec {
     uint32_t chain;
     uint32_t kclass;
     uint32_t tile_w, tile_h;    // output pixels per tile
-    uint32_t tiles_x, tiles_y;  // tiles per plane
+    uint32_t tiles_x;           // column tiles per plane
     uint32_t tile_base;         // index of this plane's first staged tile in the launch (LUT planes: first LUT unit)
     uint32_t src_w, src_h;      // frame size in pixels (what a BorderReader maps coordinates into)
     float params[FKB_MAX_PLANE_PARAMS][3];
     uint32_t lut_base;          // LUT units of all earlier planes (monotone over the table, searched by lut_kernel)
-    uint32_t pad_[1];
 };
 static_assert(sizeof(PlaneRec) == 192, "layout is mirrored by the host lowering");
+// byte offset of channel c of a planar destination
+__host__ __device__ __forceinline__ uint64_t channel_offset(const PlaneRec& pl, int c) {
+    return c == 0 ? 0ull : c == 1 ? pl.dst_cstride : pl.dst_cstride2;
+}
 static_assert(sizeof(PlaneRec) % 16 == 0, "PlaneRec is copied in 16-byte words");
 
 constexpr uint32_t kInlinePlanes = 8;  // launches of up to this many planes carry their records in the kernel parameters

@@ -60,7 +60,7 @@ int check_chain(const fkb_chain_desc& ch) {
         ch.src_format != FKB_PIX_UYVY) return FKB_ERR_UNSUPPORTED;
     if (ch.dst_format != FKB_PIX_U8C3 && ch.dst_format != FKB_PIX_F32C3) return FKB_ERR_UNSUPPORTED;
     if (ch.geometry > FKB_GEOM_RESIZE_PRESERVE_AR_LEFT) return FKB_ERR_UNSUPPORTED;
-    if (ch.write_kind != FKB_WRITE_PACKED && ch.write_kind != FKB_WRITE_SPLIT) return FKB_ERR_UNSUPPORTED;
+    if (ch.write_kind != FKB_WRITE_PACKED && ch.write_kind != FKB_WRITE_SPLIT && ch.write_kind != FKB_WRITE_SPLIT_PLANES) return FKB_ERR_UNSUPPORTED;
     if (ch.n_ops > FKB_MAX_OPS || ch.n_pre_ops > ch.n_ops) return FKB_ERR_INVALID;
     if (ch.border > FKB_BORDER_REFLECT_101) return FKB_ERR_UNSUPPORTED;
     if (ch.border && ch.border_at > (ch.geometry == FKB_GEOM_NONE ? ch.n_ops : ch.n_pre_ops)) return FKB_ERR_INVALID;
@@ -106,11 +106,14 @@ int check_plane(const fkb_chain_desc& ch, const fkb_plane_desc& pl) {
     }
     if (pl.dst_w == 0 || pl.dst_h == 0) return FKB_ERR_INVALID;
     const bool f32 = ch.dst_format == FKB_PIX_F32C3;
-    const bool split = ch.write_kind == FKB_WRITE_SPLIT;
+    const bool planes3 = ch.write_kind == FKB_WRITE_SPLIT_PLANES;
+    if (planes3 && (!pl.dst_y || !pl.dst_z)) return FKB_ERR_NULL;
+    const bool split = ch.write_kind == FKB_WRITE_SPLIT || planes3;
     const uint64_t dst_row = static_cast<uint64_t>(pl.dst_w) * (split ? (f32 ? 4 : 1) : (f32 ? 12 : 3));
     if (pl.dst_pitch < dst_row) return FKB_ERR_INVALID;
     if (f32 && ((reinterpret_cast<uintptr_t>(pl.dst) & 3) || (pl.dst_pitch & 3) || (pl.dst_channel_stride & 3))) return FKB_ERR_INVALID;
-    if (split && pl.dst_channel_stride < static_cast<uint64_t>(pl.dst_pitch) * (pl.dst_h - 1) + dst_row) return FKB_ERR_INVALID;
+    if (f32 && planes3 && ((reinterpret_cast<uintptr_t>(pl.dst_y) & 3) || (reinterpret_cast<uintptr_t>(pl.dst_z) & 3))) return FKB_ERR_INVALID;
+    if (split && !planes3 && pl.dst_channel_stride < static_cast<uint64_t>(pl.dst_pitch) * (pl.dst_h - 1) + dst_row) return FKB_ERR_INVALID;
     if (dflt) return FKB_OK;
     if (ch.geometry == FKB_GEOM_NONE) {
         if (pl.dst_w > static_cast<uint32_t>(pl.crop_w) || pl.dst_h > static_cast<uint32_t>(pl.crop_h)) return FKB_ERR_INVALID;
@@ -166,7 +169,7 @@ uint32_t post_kind_of(const fkb_chain_desc& ch);
 // Chooses the kernel path and tile shape of one plane.
 void classify(const fkb_chain_desc& ch, PlaneRec& r) {
     r.kclass = KCLASS_GATHER;
-    r.tile_w = r.tile_h = r.tiles_x = r.tiles_y = 0;
+    r.tile_w = r.tile_h = r.tiles_x = 0;
     if (force_gather()) return;
     if (ch.border) {
         // a rectangle inside the frame never meets the border: it takes the usual paths; one that leaves it is
@@ -212,7 +215,7 @@ void classify(const fkb_chain_desc& ch, PlaneRec& r) {
         r.tile_w = tw;
         r.kclass = KCLASS_RESIZE;
     }
-    r.tiles_x = (r.dst_w + r.tile_w - 1) / r.tile_w;  // tile_h / tiles_y are chosen per launch (rows_per_item)
+    r.tiles_x = (r.dst_w + r.tile_w - 1) / r.tile_w;  // tile_h is chosen per launch (rows_per_item)
 }
 
 // Output rows a warp processes per item.  Inside an item the next row's footprint is prefetched while the current
@@ -315,7 +318,12 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         r.src = static_cast<const uint8_t*>(s.src);
         r.src_chroma = static_cast<const uint8_t*>(s.src_chroma);
         r.dst = static_cast<uint8_t*>(s.dst);
-        r.dst_cstride = s.dst_channel_stride;
+        if (chains[s.chain & ~FKB_PLANE_DEFAULT].write_kind == FKB_WRITE_SPLIT_PLANES) {  // three separate planes: address differences
+            r.dst_cstride = static_cast<uint64_t>(static_cast<const uint8_t*>(s.dst_y) - static_cast<const uint8_t*>(s.dst));
+            r.dst_cstride2 = static_cast<uint64_t>(static_cast<const uint8_t*>(s.dst_z) - static_cast<const uint8_t*>(s.dst));
+        } else {
+            r.dst_cstride = s.dst_channel_stride; r.dst_cstride2 = 2 * s.dst_channel_stride;
+        }
         r.src_pitch = s.src_pitch; r.src_w = s.src_w; r.src_h = s.src_h;
         r.crop_x = s.crop_x; r.crop_y = s.crop_y; r.crop_w = s.crop_w; r.crop_h = s.crop_h;
         r.dst_w = s.dst_w; r.dst_h = s.dst_h; r.dst_pitch = s.dst_pitch;
@@ -357,14 +365,12 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         r.lut_base = n_lut_units;
         if (r.kclass == KCLASS_LUT) {
             r.tile_h = std::min(r.dst_h, lut_rpu);
-            r.tiles_y = (r.dst_h + r.tile_h - 1) / r.tile_h;
-            n_lut_units += r.tiles_y;
+            n_lut_units += (r.dst_h + r.tile_h - 1) / r.tile_h;
         } else if (r.kclass != KCLASS_GATHER) {
             r.tile_h = std::min(r.dst_h, rpi);
-            r.tiles_y = (r.dst_h + r.tile_h - 1) / r.tile_h;
         }
         r.tile_base = n_tiles;
-        const uint32_t count = (r.kclass == KCLASS_POINT || r.kclass == KCLASS_RESIZE) ? r.tiles_x * r.tiles_y : 0u;
+        const uint32_t count = (r.kclass == KCLASS_POINT || r.kclass == KCLASS_RESIZE) ? r.tiles_x * ((r.dst_h + r.tile_h - 1) / r.tile_h) : 0u;
         if (z == 0) first_count = count; else if (count != first_count) uniform = false;
         if (static_cast<uint64_t>(n_tiles) + count > 0xfffffff0ull) return FKB_ERR_TOO_LARGE;
         n_tiles += count;
@@ -400,7 +406,7 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         const PostImm imm = post_imm_of(ch);
         std::memcpy(k.m, imm.m, sizeof(k.m)); std::memcpy(k.a, imm.a, sizeof(k.a)); std::memcpy(k.d, imm.d, sizeof(k.d));
         k.kind = post_kind_of(ch); k.chain = c; k.slots = imm.slots;
-        k.preserve_ar = ch.geometry >= FKB_GEOM_RESIZE_PRESERVE_AR; k.f32 = ch.dst_format == FKB_PIX_F32C3; k.split = ch.write_kind == FKB_WRITE_SPLIT;
+        k.preserve_ar = ch.geometry >= FKB_GEOM_RESIZE_PRESERVE_AR; k.f32 = ch.dst_format == FKB_PIX_F32C3; k.split = ch.write_kind != FKB_WRITE_PACKED;
         // nv12_pair_kernel's conditions: the colour matrix of the YCbCr standards ([s 0 r; s g1 g2; s b 0]), integer
         // offsets, immediate operands, and plane offsets that fit 32 bits
         k.vu = ch.src_format == FKB_PIX_NV21;
@@ -418,7 +424,7 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
             const uint64_t src_end = static_cast<uint64_t>(r.src_pitch) * (static_cast<uint64_t>(r.crop_y) + r.crop_h) + r.crop_x + r.crop_w;
             const uint64_t dst_end = static_cast<uint64_t>(r.dst_pitch) * r.dst_h;
             pair = src_end < (1ull << 31) && dst_end < (1ull << 31);
-            wide = wide && (reinterpret_cast<uintptr_t>(r.dst) & 7) == 0 && (r.dst_pitch & 7) == 0 && (r.dst_cstride & 7) == 0;
+            wide = wide && (reinterpret_cast<uintptr_t>(r.dst) & 7) == 0 && (r.dst_pitch & 7) == 0 && (r.dst_cstride & 7) == 0 && (r.dst_cstride2 & 7) == 0;
         }
         k.pair = pair; k.wide_store = wide;
         L.nv12_grid = dim3((nw + (pair ? 63 : 31)) / (pair ? 64 : 32), (nh + 7) / 8, std::min<uint32_t>(n_planes, 65535u));
@@ -556,7 +562,12 @@ int lower_fixed(const fkb_chain_desc* chain, const fkb_plane_desc* planes, uint3
         r.src = static_cast<const uint8_t*>(s.src);
         r.src_chroma = static_cast<const uint8_t*>(s.src_chroma);
         r.dst = static_cast<uint8_t*>(s.dst);
-        r.dst_cstride = s.dst_channel_stride;
+        if (chain->write_kind == FKB_WRITE_SPLIT_PLANES) {
+            r.dst_cstride = static_cast<uint64_t>(static_cast<const uint8_t*>(s.dst_y) - static_cast<const uint8_t*>(s.dst));
+            r.dst_cstride2 = static_cast<uint64_t>(static_cast<const uint8_t*>(s.dst_z) - static_cast<const uint8_t*>(s.dst));
+        } else {
+            r.dst_cstride = s.dst_channel_stride; r.dst_cstride2 = 2 * s.dst_channel_stride;
+        }
         r.src_pitch = s.src_pitch; r.src_w = s.src_w; r.src_h = s.src_h;
         r.crop_x = s.crop_x; r.crop_y = s.crop_y; r.crop_w = s.crop_w; r.crop_h = s.crop_h;
         r.dst_w = s.dst_w; r.dst_h = s.dst_h; r.dst_pitch = s.dst_pitch;
@@ -579,14 +590,12 @@ int lower_fixed(const fkb_chain_desc* chain, const fkb_plane_desc* planes, uint3
         r.lut_base = n_lut_units;
         if (r.kclass == KCLASS_LUT) {
             r.tile_h = std::min(r.dst_h, lut_rpu);
-            r.tiles_y = (r.dst_h + r.tile_h - 1) / r.tile_h;
-            n_lut_units += r.tiles_y;
+            n_lut_units += (r.dst_h + r.tile_h - 1) / r.tile_h;
         } else if (r.kclass != KCLASS_GATHER) {
             r.tile_h = std::min(r.dst_h, rpi);
-            r.tiles_y = (r.dst_h + r.tile_h - 1) / r.tile_h;
         }
         r.tile_base = n_tiles;
-        const uint32_t count = (r.kclass == KCLASS_POINT || r.kclass == KCLASS_RESIZE) ? r.tiles_x * r.tiles_y : 0u;
+        const uint32_t count = (r.kclass == KCLASS_POINT || r.kclass == KCLASS_RESIZE) ? r.tiles_x * ((r.dst_h + r.tile_h - 1) / r.tile_h) : 0u;
         if (z == 0) first_count = count; else if (count != first_count) uniform = false;
         if (static_cast<uint64_t>(n_tiles) + count > 0xfffffff0ull) return FKB_ERR_TOO_LARGE;
         n_tiles += count;
@@ -758,6 +767,10 @@ int fkb_plan_create(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_p
 
 int fkb_plan_launch(const fkb_plan* plan, void* cuda_stream) {
     if (!plan) return FKB_ERR_NULL;
+    // a plan belongs to the device it was created on (its plane table and its status word live there)
+    int dev = -1;
+    FKB_CUDA(cudaGetDevice(&dev));
+    if (dev != plan->device) return FKB_ERR_INVALID;
     return run(plan->L, plan->L.lp, static_cast<cudaStream_t>(cuda_stream));
 }
 

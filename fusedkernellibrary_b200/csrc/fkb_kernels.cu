@@ -161,10 +161,10 @@ __global__ void __launch_bounds__(256) gather_kernel(const __grid_constant__ Lau
         }
 
         uint8_t* row = pl.dst + static_cast<size_t>(y) * pl.dst_pitch;
-        if (ch.write_kind == FKB_WRITE_SPLIT) {
+        if (ch.write_kind != FKB_WRITE_PACKED) {
 #pragma unroll
             for (int c = 0; c < 3; ++c) {
-                uint8_t* q = row + static_cast<size_t>(c) * pl.dst_cstride;
+                uint8_t* q = row + channel_offset(pl, c);
                 if (ch.dst_format == FKB_PIX_F32C3) {
                     float* f = reinterpret_cast<float*>(q) + x0;
                     if (PPT == 4 && nvalid == 4 && (reinterpret_cast<uintptr_t>(f) & 15) == 0) {
@@ -725,7 +725,7 @@ __device__ __forceinline__ void nv12_pixel(const LaunchParams& p, const PlaneRec
     if (k.split) {
 #pragma unroll
         for (int c = 0; c < 3; ++c) {
-            uint8_t* q8 = row + static_cast<size_t>(c) * pl.dst_cstride;
+            uint8_t* q8 = row + channel_offset(pl, c);
             if (k.f32) reinterpret_cast<float*>(q8)[x] = v[c]; else q8[x] = static_cast<uint8_t>(u8_of_exact(v[c]));
         }
     } else if (k.f32) {
@@ -837,7 +837,7 @@ __device__ __forceinline__ void nv12_pair(const LaunchParams& p, const PlaneRec&
         if (k.split) {
 #pragma unroll
             for (int c = 0; c < 3; ++c) {
-                float* q = reinterpret_cast<float*>(row + c * pl.dst_cstride) + xa;
+                float* q = reinterpret_cast<float*>(row + channel_offset(pl, c)) + xa;
                 if (has_b && k.wide_store) *reinterpret_cast<float2*>(q) = make_float2(acc[c].x, acc[c].y);
                 else { q[0] = acc[c].x; if (has_b) q[1] = acc[c].y; }
             }
@@ -855,7 +855,7 @@ __device__ __forceinline__ void nv12_pair(const LaunchParams& p, const PlaneRec&
     } else {
 #pragma unroll
         for (int c = 0; c < 3; ++c) {
-            uint8_t* q = k.split ? row + c * pl.dst_cstride + xa : row + xa * 3u + c;
+            uint8_t* q = k.split ? row + channel_offset(pl, c) + xa : row + xa * 3u + c;
             const uint32_t step = k.split ? 1u : 3u;
             q[0] = static_cast<uint8_t>(u8_of_exact(acc[c].x));
             if (has_b) q[step] = static_cast<uint8_t>(u8_of_exact(acc[c].y));

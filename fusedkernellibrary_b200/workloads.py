@@ -63,6 +63,7 @@ class PlaneSpec:
     bg: tuple = (0.0, 0.0, 0.0)
     params: tuple = ()           # up to four float3 operands
     chroma_offset: int = 0       # NV12: byte offset of the UV rows inside the source buffer
+    dst_planes: tuple = ()       # WRITE_SPLIT_PLANES: byte offsets of the second and third channel plane in the output buffer
     default: bool = False        # a plane beyond usedPlanes of a conditional batch read: its read yields `bg`
 
 
@@ -102,6 +103,8 @@ class Workload:
             d.crop_x, d.crop_y, d.crop_w, d.crop_h = s.crop
             d.dst_w, d.dst_h, d.dst_pitch = s.dst_w, s.dst_h, s.dst_pitch
             d.dst_channel_stride = s.dst_channel_stride
+            if s.dst_planes:
+                d.dst_y, d.dst_z = dst_addrs[s.dst] + s.dst_planes[0], dst_addrs[s.dst] + s.dst_planes[1]
             d.bg[:] = s.bg
             d.chain = s.chain | (abi.PLANE_DEFAULT if s.default else 0)
             for k, pv in enumerate(s.params):
@@ -258,6 +261,21 @@ def nv12_border_constant(w=128, h=72, dst=(80, 60), rect=(-16, -8, 160, 90), val
                         chroma_offset=pitch * h)]
     return Workload("nv12_border_constant", [ch], [_frame(seed, pitch * (h + h // 2), 16, 236)], [dw * dh * 12], planes,
                     "NV12 with a constant border in RGB", extra={"value": value, "rect": rect})
+
+
+def split_planes(w=300, h=170, dst=(100, 64), seed=16, f32=True) -> Workload:
+    """One frame -> Resize IGNORE_AR -> Mul [-> SaturateCast] -> SplitWrite: three separate planes, here at unequal
+    distances inside one buffer (second plane last, a gap before the third)."""
+    pitch = _pitch(w * 3, 16)
+    dw, dh = dst
+    elt = 4 if f32 else 1
+    dpitch = _pitch(dw * elt, 16)
+    plane = dpitch * dh
+    ops = [op(abi.OP_MUL, (0.5, 1.0, 1.5))] + ([] if f32 else [op(abi.OP_SATCAST_U8)])
+    ch = chain(abi.PIX_U8C3, abi.GEOM_RESIZE_IGNORE_AR, abi.PIX_F32C3 if f32 else abi.PIX_U8C3, abi.WRITE_SPLIT_PLANES, ops)
+    planes = [PlaneSpec(0, 0, 0, w, h, pitch, (0, 0, w, h), dw, dh, dpitch, dst_planes=(3 * plane + 64, plane + 32))]
+    return Workload("split_planes", [ch], [_frame(seed, pitch * h)], [4 * plane + 64], planes,
+                    "SplitWrite into three separate planes " + ("f32" if f32 else "u8"), extra={"f32": f32, "plane": plane})
 
 
 def conditional_resize(used=5, w=320, h=180, dst=(96, 64), default=(7, 200, 33), seed=11) -> Workload:

@@ -80,7 +80,10 @@ enum { FKB_BORDER_NONE = 0, FKB_BORDER_CONSTANT = 1, FKB_BORDER_REPLICATE = 2, F
 /* Write kinds.  PACKED: interleaved pixels in pitched rows — PerThreadWrite<_2D,T> and
  * TensorWrite<T> (memory_operations.h:85-107, 160-179).  SPLIT: TensorSplit<float3>
  * (memory_operations.h:182-212): channel c of pixel (x,y) at dst + c*dst_channel_stride + y*dst_pitch + x*4. */
-enum { FKB_WRITE_PACKED = 1, FKB_WRITE_SPLIT = 2 };
+enum { FKB_WRITE_PACKED = 1, FKB_WRITE_SPLIT = 2,
+       /* SplitWrite<_2D,T> (memory_operations.h:360-393): three unrelated planes dst (x), dst_y, dst_z, one base element
+        * per pixel each, all with the pitch dst_pitch */
+       FKB_WRITE_SPLIT_PLANES = 3 };
 
 /* Compute ops.  The value type is tracked like the reference's Input/OutputType: it starts as
  * uchar3, ops that need float3 are rejected on uchar3 and vice versa. */
@@ -147,6 +150,8 @@ typedef struct fkb_plane_desc {
                                 the resize parameters are ignored.  Without a Resize the read is uchar3, so bg must
                                 hold integers in [0,255]. */
     float params[FKB_MAX_PLANE_PARAMS][3]; /* operands of ops whose plane_slot >= 0 */
+    void* dst_y;             /* FKB_WRITE_SPLIT_PLANES: first byte of the second ... */
+    void* dst_z;             /* ... and of the third channel plane; else unused */
 } fkb_plane_desc;
 
 /* Fills plane->fx, fy, x1, y1, x2, y2 from plane->crop_w/crop_h (the size of the back operation) and
@@ -204,7 +209,7 @@ int fkb_launch_divergent(const fkb_chain_desc* chains, uint32_t n_chains,
 typedef struct fkb_plan fkb_plan;
 int fkb_plan_create(const fkb_chain_desc* chains, uint32_t n_chains,
                     const fkb_plane_desc* planes, uint32_t n_planes, fkb_plan** out);
-int fkb_plan_launch(const fkb_plan* plan, void* cuda_stream);
+int fkb_plan_launch(const fkb_plan* plan, void* cuda_stream);  /* FKB_ERR_INVALID when the current device is not the plan's */
 void fkb_plan_destroy(fkb_plan* plan);
 /* Kernel launches one fkb_plan_launch issues (for launch accounting). */
 uint32_t fkb_plan_kernel_launches(const fkb_plan* plan);

@@ -123,6 +123,7 @@ struct Lowered {
         d.dst = static_cast<uint8_t*>(wr.data) + static_cast<size_t>(z) * wr.plane_stride;
         d.dst_pitch = wr.pitch;
         d.dst_channel_stride = wr.channel_stride;
+        d.dst_y = wr.data_y; d.dst_z = wr.data_z;
         d.bg[0] = st.bg[0]; d.bg[1] = st.bg[1]; d.bg[2] = st.bg[2];
         d.chain = chain_index;
         if (st.used_planes >= 0 && z >= static_cast<uint32_t>(st.used_planes)) {

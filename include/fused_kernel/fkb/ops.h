@@ -319,6 +319,8 @@ struct WriteIOp {
     uint width{0}, height{0}, pitch{0}, planes{1};
     size_t plane_stride{0};    // bytes between consecutive planes (tensors)
     size_t channel_stride{0};  // TensorSplit: bytes between channel planes
+    void* data_y{nullptr};     // SplitWrite: the second and third channel plane
+    void* data_z{nullptr};
 };
 template <typename T> constexpr bool isWriteIOp = false;
 template <typename T> constexpr bool isWriteIOp<WriteIOp<T>> = true;
@@ -348,6 +350,22 @@ struct TensorSplit {
                            static_cast<size_t>(p.dims.width) * p.dims.height * sizeof(Base)};
     }
     static auto build(const Ptr<ND::_3D, Base>& p) { return build(p.ptr()); }
+};
+// Three separate 2-D planes, one per channel (memory_operations.h:360-393).
+template <ND D, typename T>
+struct SplitWrite {
+    static_assert(D == ND::_2D && (std::is_same_v<T, float3> || std::is_same_v<T, uchar3>),
+                  "SplitWrite<ND::_2D, float3|uchar3> is the split write the B200 kernels implement");
+    using Base = std::conditional_t<std::is_same_v<T, float3>, float, uchar>;
+    static auto build(const std::vector<Ptr2D<Base>>& output) {
+        const auto x = output.at(0).ptr(), y = output.at(1).ptr(), z = output.at(2).ptr();
+        if (y.dims.pitch != x.dims.pitch || z.dims.pitch != x.dims.pitch || y.dims.width != x.dims.width || z.dims.width != x.dims.width ||
+            y.dims.height != x.dims.height || z.dims.height != x.dims.height)
+            throw std::runtime_error("SplitWrite: the three planes must have the same size and pitch");
+        WriteIOp<T> w{FKB_WRITE_SPLIT_PLANES, x.data, x.dims.width, x.dims.height, x.dims.pitch, 1, 0, 0};
+        w.data_y = y.data; w.data_z = z.data;
+        return w;
+    }
 };
 // The same planar write into a colour-plane-transposed tensor (memory_operations.h:214-241): channel c of image z lies
 // at c * color_planes_pitch + z * plane_pitch (core/data/rawptr.h:229-239).

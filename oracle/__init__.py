@@ -69,6 +69,9 @@ def load_ref() -> C.CDLL:
         lib.fklref_saturate_u8.argtypes = [C.c_float]
         lib.fklref_resize_params.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, f32p, i32p]
         u8p = C.POINTER(C.c_uint8)
+        lib.fklref_resize_split_planes.restype = C.c_int
+        lib.fklref_resize_split_planes.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, f32p, C.c_int, C.c_void_p,
+                                                   C.c_void_p, C.c_void_p, C.c_int]
         lib.fklref_resize_tsplit_f32.restype = C.c_int
         lib.fklref_resize_tsplit_f32.argtypes = [pp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, f32p, C.c_void_p]
         lib.fklref_border_crop_resize.restype = C.c_int
@@ -203,6 +206,11 @@ def run_ref(wl, threads: int = 1):
         rc = lib.fklref_nv12_border_constant(wl.sources[0].ctypes.data, p0.src_w, p0.src_h, p0.src_pitch,
                                              (C.c_int32 * 4)(*wl.extra["rect"]), _f3(wl.extra["value"]), p0.dst_w, p0.dst_h,
                                              outs[0].ctypes.data)
+    elif wl.name == "split_planes":
+        base = outs[0].ctypes.data
+        rc = lib.fklref_resize_split_planes(wl.sources[0].ctypes.data, p0.src_w, p0.src_h, p0.src_pitch, p0.dst_w, p0.dst_h,
+                                            _f3(ch.ops[0].v), 1 if wl.extra["f32"] else 0, base, base + p0.dst_planes[0],
+                                            base + p0.dst_planes[1], p0.dst_pitch)
     elif wl.name == "tsplit_resize":
         rc = lib.fklref_resize_tsplit_f32(frame_ptrs(wl.planes), p0.src_w, p0.src_h, p0.src_pitch, p0.dst_w, p0.dst_h,
                                           _f3(ch.ops[0].v), outs[0].ctypes.data)

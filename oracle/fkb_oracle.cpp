@@ -231,7 +231,14 @@ void run_plane(const fkb_chain_desc& ch, const fkb_plane_desc& pl) {
         for (uint32_t x = 0; x < pl.dst_w; ++x) {
             const V3 v = pixel(ch, pl, static_cast<int>(x), static_cast<int>(y));
             uint8_t* row = dst + static_cast<size_t>(y) * pl.dst_pitch;
-            if (ch.write_kind == FKB_WRITE_SPLIT) {
+            if (ch.write_kind == FKB_WRITE_SPLIT_PLANES) {  // SplitWrite (memory_operations.h:360-393): one RawPtr per channel
+                uint8_t* const base[3] = {dst, static_cast<uint8_t*>(pl.dst_y), static_cast<uint8_t*>(pl.dst_z)};
+                for (int c = 0; c < 3; ++c) {
+                    uint8_t* q = base[c] + static_cast<size_t>(y) * pl.dst_pitch;
+                    if (ch.dst_format == FKB_PIX_F32C3) reinterpret_cast<float*>(q)[x] = v.c[c];
+                    else q[x] = static_cast<uint8_t>(v.c[c]);
+                }
+            } else if (ch.write_kind == FKB_WRITE_SPLIT) {
                 for (int c = 0; c < 3; ++c) {
                     uint8_t* q = row + static_cast<size_t>(c) * pl.dst_channel_stride;
                     if (ch.dst_format == FKB_PIX_F32C3) reinterpret_cast<float*>(q)[x] = v.c[c];

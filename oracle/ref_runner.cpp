@@ -221,6 +221,27 @@ int fklref_conditional_pointwise_u8(const uint8_t* const* frames, int w, int h, 
     return 0;
 }
 
+// One frame -> Resize(IGNORE_AR) -> Mul [-> SaturateCast] -> SplitWrite<_2D, float3|uchar3> into three separate planes
+int fklref_resize_split_planes(const uint8_t* frame, int w, int h, int pitch, int dw, int dh, const float* mul, int f32, void* px, void* py,
+                               void* pz, int dpitch) {
+    CpuStream stream;
+    const auto read = PerThreadRead<ND::_2D, uchar3>::build(wrap_frame(frame, w, h, pitch));
+    const auto resize = Resize<InterpolationType::INTER_LINEAR, AspectRatio::IGNORE_AR>::build(Size(dw, dh));
+    const auto m = Mul<float3>::build(make_<float3>(mul[0], mul[1], mul[2]));
+    if (f32) {
+        const std::vector<Ptr2D<float>> out{Ptr2D<float>(static_cast<float*>(px), dw, dh, dpitch, MemType::Host, 0),
+                                            Ptr2D<float>(static_cast<float*>(py), dw, dh, dpitch, MemType::Host, 0),
+                                            Ptr2D<float>(static_cast<float*>(pz), dw, dh, dpitch, MemType::Host, 0)};
+        executeOperations<CpuDPP>(stream, read, resize, m, SplitWrite<ND::_2D, float3>::build(out));
+    } else {
+        const std::vector<Ptr2D<uchar>> out{Ptr2D<uchar>(static_cast<uchar*>(px), dw, dh, dpitch, MemType::Host, 0),
+                                            Ptr2D<uchar>(static_cast<uchar*>(py), dw, dh, dpitch, MemType::Host, 0),
+                                            Ptr2D<uchar>(static_cast<uchar*>(pz), dw, dh, dpitch, MemType::Host, 0)};
+        executeOperations<CpuDPP>(stream, read, resize, m, SaturateCast<float3, uchar3>::build(), SplitWrite<ND::_2D, uchar3>::build(out));
+    }
+    return 0;
+}
+
 // Four frames -> Resize(IGNORE_AR) -> Mul -> TensorTSplit<float3> into a colour-plane-transposed tensor
 // (memory_operations.h:214-241): all R planes, then all G planes, then all B planes.
 int fklref_resize_tsplit_f32(const uint8_t* const* frames, int w, int h, int pitch, int dw, int dh, const float* mul, float* out) {

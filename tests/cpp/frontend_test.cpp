@@ -296,6 +296,33 @@ static void test_tensor_t_split() {
     report("TensorTSplit<float3> (transposed planar tensor)", std::memcmp(want.data(), out.ptrPinned().data, want.size() * 4) == 0);
 }
 
+// ---- SplitWrite: three separate planes ------------------------------------------------------------------------------------
+static void test_split_write() {
+    Stream stream;
+    Ptr2D<uchar3> in(200, 120);
+    fill_random(in, 600);
+    in.upload(stream);
+    std::vector<Ptr2D<float>> out{Ptr2D<float>(90, 50), Ptr2D<float>(90, 50), Ptr2D<float>(90, 50)};
+    executeOperations<TransformDPP<>>(stream, PerThreadRead<ND::_2D, uchar3>::build(in), Resize<InterpolationType::INTER_LINEAR>::build(Size(90, 50)),
+                                      Mul<float3>::build(make_<float3>(1.f, 2.f, 3.f)), SplitWrite<ND::_2D, float3>::build(out));
+    for (auto& p : out) p.download(stream);
+    stream.sync();
+    fkb_chain_desc ch{};
+    ch.src_format = FKB_PIX_U8C3; ch.geometry = FKB_GEOM_RESIZE_IGNORE_AR; ch.dst_format = FKB_PIX_F32C3; ch.write_kind = FKB_WRITE_SPLIT_PLANES;
+    ch.n_ops = 1; ch.ops[0] = op(FKB_OP_MUL, 1.f, 2.f, 3.f);
+    const uint32_t pitch = out[0].dims().pitch;
+    std::vector<uint8_t> wx(pitch * 50), wy(pitch * 50), wz(pitch * 50);
+    fkb_plane_desc d = host_plane(in, Rect(0, 0, 200, 120), 90, 50, wx.data(), pitch, ch.geometry);
+    d.dst_y = wy.data(); d.dst_z = wz.data();
+    fkb_oracle_run(&ch, 1, &d, 1, 1);
+    bool same = true;
+    const std::vector<uint8_t>* want[3] = {&wx, &wy, &wz};
+    for (int c = 0; c < 3; ++c)
+        for (int y = 0; y < 50; ++y)
+            same = same && std::memcmp(want[c]->data() + y * pitch, reinterpret_cast<const uint8_t*>(out[c].ptrPinned().data) + y * pitch, 90 * 4) == 0;
+    report("SplitWrite<ND::_2D, float3> (three planes)", same);
+}
+
 // ---- divergent horizontal fusion: two sequences in one launch, global plane indices ------------------------------------
 struct Sel { static uint at(const uint& z) { return z < 2 ? 0u : 1u; } };
 static void test_divergent() {
@@ -366,6 +393,7 @@ int main() {
     test_batched<AspectRatio::PRESERVE_AR_LEFT>("batched crop-resize-normalise, PRESERVE_AR_LEFT", FKB_GEOM_RESIZE_PRESERVE_AR_LEFT);
     test_conditional_batch();
     test_tensor_t_split();
+    test_split_write();
     test_border<BorderType::CONSTANT>("BorderReader<CONSTANT> (complete form, operator&)");
     test_border<BorderType::REPLICATE>("BorderReader<REPLICATE>");
     test_border<BorderType::REFLECT_101>("BorderReader<REFLECT_101>");

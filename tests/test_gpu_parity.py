@@ -77,6 +77,8 @@ SMALL = {
     "divergent_odd": lambda: W.divergent_planes(n_per_seq=3, w=330, h=190),
     "crop_reorder": lambda: W.crop_reorder(n=5),
     "tsplit_resize": lambda: W.tsplit_resize(),
+    "split_planes_f32": lambda: W.split_planes(),
+    "split_planes_u8": lambda: W.split_planes(f32=False, dst=(333, 77)),
     "conditional_resize": lambda: W.conditional_resize(),
     "conditional_pointwise": lambda: W.conditional_pointwise(),
 }

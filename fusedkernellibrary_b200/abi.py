@@ -22,9 +22,9 @@ PRIMITIVES_BT601, PRIMITIVES_BT709, PRIMITIVES_BT2020 = 0, 1, 2
 GEOM_NONE, GEOM_RESIZE_IGNORE_AR, GEOM_RESIZE_PRESERVE_AR = 0, 1, 2
 GEOM_RESIZE_PRESERVE_AR_RN_EVEN, GEOM_RESIZE_PRESERVE_AR_LEFT = 3, 4
 PLANE_DEFAULT = 0x80000000  # fkb_plane_desc.chain bit: the plane's read yields bg (conditional batch read)
-WRITE_PACKED, WRITE_SPLIT, WRITE_SPLIT_PLANES = 1, 2, 3
+WRITE_PACKED, WRITE_SPLIT, WRITE_SPLIT_PLANES, WRITE_NV12, WRITE_NV21, WRITE_UYVY = 1, 2, 3, 4, 5, 6
 BORDER_NONE, BORDER_CONSTANT, BORDER_REPLICATE, BORDER_REFLECT, BORDER_WRAP, BORDER_REFLECT_101 = 0, 1, 2, 3, 4, 5
-OP_CAST_F32, OP_MUL, OP_ADD, OP_SUB, OP_DIV, OP_REORDER_ZYX, OP_YUV2RGB, OP_SATCAST_U8 = 1, 2, 3, 4, 5, 6, 7, 8
+OP_CAST_F32, OP_MUL, OP_ADD, OP_SUB, OP_DIV, OP_REORDER_ZYX, OP_YUV2RGB, OP_SATCAST_U8, OP_RGB2YUV = 1, 2, 3, 4, 5, 6, 7, 8, 9
 
 
 class Op(C.Structure):
@@ -36,6 +36,7 @@ class ChainDesc(C.Structure):
         ("src_format", C.c_uint32), ("geometry", C.c_uint32), ("dst_format", C.c_uint32),
         ("write_kind", C.c_uint32), ("n_ops", C.c_uint32), ("n_pre_ops", C.c_uint32),
         ("ops", Op * MAX_OPS), ("ccm", C.c_float * 9), ("yuv_sub", C.c_float * 3),
+        ("ccm2", C.c_float * 9), ("yuv_add", C.c_float * 3),
         ("border", C.c_uint32), ("border_at", C.c_uint32), ("border_value", C.c_float * 3),
     ]
 
@@ -55,7 +56,7 @@ class PlaneDesc(C.Structure):
     ]
 
 
-assert C.sizeof(Op) == 16 and C.sizeof(ChainDesc) == 284 and C.sizeof(PlaneDesc) == 176
+assert C.sizeof(Op) == 16 and C.sizeof(ChainDesc) == 332 and C.sizeof(PlaneDesc) == 176
 
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libfkb.so")
 
@@ -63,6 +64,7 @@ LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libf
 SIGNATURES = {
     "fkb_resize_params": (C.c_int, [C.c_uint32, C.POINTER(PlaneDesc)]),
     "fkb_ycbcr_to_rgb": (C.c_int, [C.c_uint32, C.c_uint32, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
+    "fkb_rgb_to_ycbcr": (C.c_int, [C.c_uint32, C.c_uint32, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "fkb_validate": (C.c_int, [C.POINTER(ChainDesc), C.c_uint32, C.POINTER(PlaneDesc), C.c_uint32]),
     "fkb_launch_transform": (C.c_int, [C.POINTER(ChainDesc), C.POINTER(PlaneDesc), C.c_uint32, C.c_void_p]),
     "fkb_launch_transform_noalloc": (C.c_int, [C.POINTER(ChainDesc), C.POINTER(PlaneDesc), C.c_uint32, C.c_void_p]),

@@ -256,6 +256,17 @@ __device__ __forceinline__ void apply_ops(float (&v)[N][3], const fkb_chain_desc
                     v[n][c] = __fadd_rn(__fadd_rn(__fmul_rn(a, ch.ccm[3 * c]), __fmul_rn(b, ch.ccm[3 * c + 1])), __fmul_rn(d, ch.ccm[3 * c + 2]));
             }
             break;
+        case FKB_OP_RGB2YUV:
+#pragma unroll
+            for (int n = 0; n < N; ++n) {
+                const float r = v[n][0], g = v[n][1], b = v[n][2];
+#pragma unroll
+                for (int c = 0; c < 3; ++c) {
+                    const float y = __fadd_rn(__fadd_rn(__fmul_rn(r, ch.ccm2[3 * c]), __fmul_rn(g, ch.ccm2[3 * c + 1])), __fmul_rn(b, ch.ccm2[3 * c + 2]));
+                    v[n][c] = ch.yuv_add[c] != 0.f ? __fadd_rn(y, ch.yuv_add[c]) : y;  // full-range luma gets no offset at all
+                }
+            }
+            break;
         case FKB_OP_SATCAST_U8:
 #pragma unroll
             for (int n = 0; n < N; ++n) { v[n][0] = sat_u8_as_float(v[n][0]); v[n][1] = sat_u8_as_float(v[n][1]); v[n][2] = sat_u8_as_float(v[n][2]); }

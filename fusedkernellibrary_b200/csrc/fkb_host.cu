@@ -47,7 +47,7 @@ int check_ops(const fkb_chain_desc& ch, uint32_t first, uint32_t last, ValueType
         case FKB_OP_CAST_F32: if (t != VT_U8) return FKB_ERR_INVALID; t = VT_F32; break;
         case FKB_OP_MUL: case FKB_OP_ADD: case FKB_OP_SUB: case FKB_OP_DIV: if (t != VT_F32) return FKB_ERR_INVALID; break;
         case FKB_OP_REORDER_ZYX: break;
-        case FKB_OP_YUV2RGB: if (t != VT_U8) return FKB_ERR_INVALID; t = VT_F32; break;
+        case FKB_OP_YUV2RGB: case FKB_OP_RGB2YUV: if (t != VT_U8) return FKB_ERR_INVALID; t = VT_F32; break;
         case FKB_OP_SATCAST_U8: if (t != VT_F32) return FKB_ERR_INVALID; t = VT_U8; break;
         default: return FKB_ERR_UNSUPPORTED;
         }
@@ -60,7 +60,8 @@ int check_chain(const fkb_chain_desc& ch) {
         ch.src_format != FKB_PIX_UYVY) return FKB_ERR_UNSUPPORTED;
     if (ch.dst_format != FKB_PIX_U8C3 && ch.dst_format != FKB_PIX_F32C3) return FKB_ERR_UNSUPPORTED;
     if (ch.geometry > FKB_GEOM_RESIZE_PRESERVE_AR_LEFT) return FKB_ERR_UNSUPPORTED;
-    if (ch.write_kind != FKB_WRITE_PACKED && ch.write_kind != FKB_WRITE_SPLIT && ch.write_kind != FKB_WRITE_SPLIT_PLANES) return FKB_ERR_UNSUPPORTED;
+    if (ch.write_kind < FKB_WRITE_PACKED || ch.write_kind > FKB_WRITE_UYVY) return FKB_ERR_UNSUPPORTED;
+    if (ch.write_kind >= FKB_WRITE_NV12 && ch.dst_format != FKB_PIX_U8C3) return FKB_ERR_INVALID;  // WriteYUV takes byte triples
     if (ch.n_ops > FKB_MAX_OPS || ch.n_pre_ops > ch.n_ops) return FKB_ERR_INVALID;
     if (ch.border > FKB_BORDER_REFLECT_101) return FKB_ERR_UNSUPPORTED;
     if (ch.border && ch.border_at > (ch.geometry == FKB_GEOM_NONE ? ch.n_ops : ch.n_pre_ops)) return FKB_ERR_INVALID;
@@ -109,7 +110,11 @@ int check_plane(const fkb_chain_desc& ch, const fkb_plane_desc& pl) {
     const bool planes3 = ch.write_kind == FKB_WRITE_SPLIT_PLANES;
     if (planes3 && (!pl.dst_y || !pl.dst_z)) return FKB_ERR_NULL;
     const bool split = ch.write_kind == FKB_WRITE_SPLIT || planes3;
-    const uint64_t dst_row = static_cast<uint64_t>(pl.dst_w) * (split ? (f32 ? 4 : 1) : (f32 ? 12 : 3));
+    const bool semi = ch.write_kind == FKB_WRITE_NV12 || ch.write_kind == FKB_WRITE_NV21;
+    if (semi && !pl.dst_y) return FKB_ERR_NULL;
+    const uint64_t dst_row = semi ? ((static_cast<uint64_t>(pl.dst_w) + 1) / 2) * 2
+                             : ch.write_kind == FKB_WRITE_UYVY ? ((static_cast<uint64_t>(pl.dst_w) + 1) / 2) * 4
+                             : static_cast<uint64_t>(pl.dst_w) * (split ? (f32 ? 4 : 1) : (f32 ? 12 : 3));
     if (pl.dst_pitch < dst_row) return FKB_ERR_INVALID;
     if (f32 && ((reinterpret_cast<uintptr_t>(pl.dst) & 3) || (pl.dst_pitch & 3) || (pl.dst_channel_stride & 3))) return FKB_ERR_INVALID;
     if (f32 && planes3 && ((reinterpret_cast<uintptr_t>(pl.dst_y) & 3) || (reinterpret_cast<uintptr_t>(pl.dst_z) & 3))) return FKB_ERR_INVALID;
@@ -178,7 +183,7 @@ void classify(const fkb_chain_desc& ch, PlaneRec& r) {
         if (x < 0 || y < 0 || x + r.crop_w > static_cast<int64_t>(r.src_w) || y + r.crop_h > static_cast<int64_t>(r.src_h)) return;
     }
     if ((ch.src_format == FKB_PIX_NV12 || ch.src_format == FKB_PIX_NV21) && ch.geometry != FKB_GEOM_NONE && ch.n_pre_ops == 1 && ch.ops[0].code == FKB_OP_YUV2RGB &&
-        post_kind_of(ch) != 8u && !(ch.geometry >= FKB_GEOM_RESIZE_PRESERVE_AR && (r.x2 < r.x1 || r.y2 < r.y1)) &&
+        ch.write_kind <= FKB_WRITE_SPLIT_PLANES && post_kind_of(ch) != 8u && !(ch.geometry >= FKB_GEOM_RESIZE_PRESERVE_AR && (r.x2 < r.x1 || r.y2 < r.y1)) &&
         (reinterpret_cast<uintptr_t>(r.src_chroma) & 1) == 0 && (r.src_pitch & 1) == 0) {  // UV pairs are read as 16-bit words
         r.kclass = KCLASS_NV12;  // NV12 -> RGB on the taps -> resize -> [Mul][Add|Sub][Div][SaturateCast]: nv12_kernel
         return;
@@ -318,7 +323,10 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         r.src = static_cast<const uint8_t*>(s.src);
         r.src_chroma = static_cast<const uint8_t*>(s.src_chroma);
         r.dst = static_cast<uint8_t*>(s.dst);
-        if (chains[s.chain & ~FKB_PLANE_DEFAULT].write_kind == FKB_WRITE_SPLIT_PLANES) {  // three separate planes: address differences
+        const uint32_t wk = chains[s.chain & ~FKB_PLANE_DEFAULT].write_kind;
+        if (wk == FKB_WRITE_NV12 || wk == FKB_WRITE_NV21) {  // luma plane + chroma rows: one address difference
+            r.dst_cstride = static_cast<uint64_t>(static_cast<const uint8_t*>(s.dst_y) - static_cast<const uint8_t*>(s.dst));
+        } else if (wk == FKB_WRITE_SPLIT_PLANES) {  // three separate planes: address differences
             r.dst_cstride = static_cast<uint64_t>(static_cast<const uint8_t*>(s.dst_y) - static_cast<const uint8_t*>(s.dst));
             r.dst_cstride2 = static_cast<uint64_t>(static_cast<const uint8_t*>(s.dst_z) - static_cast<const uint8_t*>(s.dst));
         } else {
@@ -562,7 +570,9 @@ int lower_fixed(const fkb_chain_desc* chain, const fkb_plane_desc* planes, uint3
         r.src = static_cast<const uint8_t*>(s.src);
         r.src_chroma = static_cast<const uint8_t*>(s.src_chroma);
         r.dst = static_cast<uint8_t*>(s.dst);
-        if (chain->write_kind == FKB_WRITE_SPLIT_PLANES) {
+        if (chain->write_kind == FKB_WRITE_NV12 || chain->write_kind == FKB_WRITE_NV21) {
+            r.dst_cstride = static_cast<uint64_t>(static_cast<const uint8_t*>(s.dst_y) - static_cast<const uint8_t*>(s.dst));
+        } else if (chain->write_kind == FKB_WRITE_SPLIT_PLANES) {
             r.dst_cstride = static_cast<uint64_t>(static_cast<const uint8_t*>(s.dst_y) - static_cast<const uint8_t*>(s.dst));
             r.dst_cstride2 = static_cast<uint64_t>(static_cast<const uint8_t*>(s.dst_z) - static_cast<const uint8_t*>(s.dst));
         } else {
@@ -711,6 +721,25 @@ int fkb_ycbcr_to_rgb(uint32_t range, uint32_t primitives, float ccm[9], float yu
     for (int i = 0; i < 9; ++i) ccm[i] = m[i / 3][i % 3];
     yuv_sub[0] = range == FKB_RANGE_LIMITED ? 16.f : 0.f;  // full range subtracts nothing from the luma
     yuv_sub[1] = yuv_sub[2] = 128.f;
+    return FKB_OK;
+}
+
+int fkb_rgb_to_ycbcr(uint32_t range, uint32_t primitives, float ccm2[9], float yuv_add[3]) {
+    if (!ccm2 || !yuv_add) return FKB_ERR_NULL;
+    if (range > FKB_RANGE_FULL || primitives > FKB_PRIMITIVES_BT2020) return FKB_ERR_INVALID;
+    static const float kKr[3] = {0.299f, 0.2126f, 0.2627f}, kKb[3] = {0.114f, 0.0722f, 0.0593f};
+    const float Kr = kKr[primitives], Kb = kKb[primitives];
+    const float Kg = 1.0f - Kr - Kb;
+    float m[3][3] = {{Kr, Kg, Kb},
+                     {-Kr / (2.0f * (1.0f - Kb)), -Kg / (2.0f * (1.0f - Kb)), 0.5f},
+                     {0.5f, -Kg / (2.0f * (1.0f - Kr)), -Kb / (2.0f * (1.0f - Kr))}};
+    if (range == FKB_RANGE_LIMITED) {  // 8 bit: 219 luma codes, 224 chroma codes out of 255
+        const float scale_y = 219.f / 255.f, scale_c = 224.f / 255.f;
+        for (int i = 0; i < 3; ++i) { m[0][i] *= scale_y; m[1][i] *= scale_c; m[2][i] *= scale_c; }
+    }
+    for (int i = 0; i < 9; ++i) ccm2[i] = m[i / 3][i % 3];
+    yuv_add[0] = range == FKB_RANGE_LIMITED ? 16.f : 0.f;
+    yuv_add[1] = yuv_add[2] = 128.f;
     return FKB_OK;
 }
 

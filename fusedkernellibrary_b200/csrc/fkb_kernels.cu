@@ -161,7 +161,25 @@ __global__ void __launch_bounds__(256) gather_kernel(const __grid_constant__ Lau
         }
 
         uint8_t* row = pl.dst + static_cast<size_t>(y) * pl.dst_pitch;
-        if (ch.write_kind != FKB_WRITE_PACKED) {
+        if (ch.write_kind >= FKB_WRITE_NV12) {
+            // (Y,Cb,Cr) byte triples into a YCbCr image; the chroma rows of NV12 / NV21 start dst_cstride bytes after dst
+            for (uint32_t n = 0; n < nvalid; ++n) {
+                const uint32_t x = x0 + n;
+                const uint8_t yy = static_cast<uint8_t>(v[n][0]), cb = static_cast<uint8_t>(v[n][1]), cr = static_cast<uint8_t>(v[n][2]);
+                if (ch.write_kind == FKB_WRITE_UYVY) {
+                    uint8_t* g = row + static_cast<size_t>(x >> 1) * 4;
+                    if (x & 1u) g[3] = yy; else { g[0] = cb; g[1] = yy; g[2] = cr; }
+                } else {
+                    row[x] = yy;
+                    uint8_t* uv = pl.dst + pl.dst_cstride + static_cast<size_t>(y >> 1) * pl.dst_pitch + static_cast<size_t>(x >> 1) * 2;
+                    if (ch.write_kind == FKB_WRITE_NV12) {
+                        if (!(x & 1u) && !(y & 1u)) { uv[0] = cb; uv[1] = cr; }
+                    } else if (x == min(x | 1u, pl.dst_w - 1u) && y == min(y | 1u, pl.dst_h - 1u)) {  // last pixel of the 2x2 block
+                        uv[0] = cr; uv[1] = cb;
+                    }
+                }
+            }
+        } else if (ch.write_kind != FKB_WRITE_PACKED) {
 #pragma unroll
             for (int c = 0; c < 3; ++c) {
                 uint8_t* q = row + channel_offset(pl, c);

@@ -31,7 +31,7 @@ def op(code: int, v=(0.0, 0.0, 0.0), slot: int = -1) -> abi.Op:
 
 
 def chain(src_format, geometry, dst_format, write_kind, ops, n_pre_ops=0, ccm=None, yuv_sub=None, border=0, border_at=0,
-          border_value=(0.0, 0.0, 0.0)) -> abi.ChainDesc:
+          border_value=(0.0, 0.0, 0.0), ccm2=None, yuv_add=None) -> abi.ChainDesc:
     ch = abi.ChainDesc()
     ch.src_format, ch.geometry, ch.dst_format, ch.write_kind = src_format, geometry, dst_format, write_kind
     ch.n_ops, ch.n_pre_ops = len(ops), n_pre_ops
@@ -41,6 +41,10 @@ def chain(src_format, geometry, dst_format, write_kind, ops, n_pre_ops=0, ccm=No
         ch.ccm[:] = ccm
     if yuv_sub is not None:
         ch.yuv_sub[:] = yuv_sub
+    if ccm2 is not None:
+        ch.ccm2[:] = ccm2
+    if yuv_add is not None:
+        ch.yuv_add[:] = yuv_add
     ch.border, ch.border_at = border, border_at
     ch.border_value[:] = border_value
     return ch
@@ -276,6 +280,22 @@ def split_planes(w=300, h=170, dst=(100, 64), seed=16, f32=True) -> Workload:
     planes = [PlaneSpec(0, 0, 0, w, h, pitch, (0, 0, w, h), dw, dh, dpitch, dst_planes=(3 * plane + 64, plane + 32))]
     return Workload("split_planes", [ch], [_frame(seed, pitch * h)], [4 * plane + 64], planes,
                     "SplitWrite into three separate planes " + ("f32" if f32 else "u8"), extra={"f32": f32, "plane": plane})
+
+
+def rgb_to_yuv_image(fmt=abi.PIX_NV12, colour=(abi.RANGE_FULL, abi.PRIMITIVES_BT709), w=322, h=180, seed=17) -> Workload:
+    """PerThreadRead<uchar3> (R,G,B) -> ConvertRGBToYUV -> SaturateCast -> WriteYUV<NV12|NV21|UYVY>."""
+    pitch = _pitch(w * 3, 16)
+    m, add = (C.c_float * 9)(), (C.c_float * 3)()
+    if abi.load().fkb_rgb_to_ycbcr(colour[0], colour[1], m, add) != 0:
+        raise ValueError("fkb_rgb_to_ycbcr refused the colour description")
+    kind = {abi.PIX_NV12: abi.WRITE_NV12, abi.PIX_NV21: abi.WRITE_NV21, abi.PIX_UYVY: abi.WRITE_UYVY}[fmt]
+    ch = chain(abi.PIX_U8C3, abi.GEOM_NONE, abi.PIX_U8C3, kind, [op(abi.OP_RGB2YUV), op(abi.OP_SATCAST_U8)], ccm2=tuple(m), yuv_add=tuple(add))
+    uyvy = fmt == abi.PIX_UYVY
+    opitch = _pitch(w * 2 if uyvy else w, 16)
+    size = opitch * h if uyvy else opitch * (h + (h + 1) // 2)  # an odd height still has a chroma row for its last line
+    planes = [PlaneSpec(0, 0, 0, w, h, pitch, (0, 0, w, h), w, h, opitch, dst_planes=() if uyvy else (opitch * h, 0))]
+    return Workload("rgb_to_yuv_image", [ch], [_frame(seed, pitch * h)], [size], planes, f"RGB -> format {fmt} colour {colour}",
+                    extra={"fmt": fmt, "colour": colour})
 
 
 def conditional_resize(used=5, w=320, h=180, dst=(96, 64), default=(7, 200, 33), seed=11) -> Workload:

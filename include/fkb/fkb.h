@@ -83,7 +83,14 @@ enum { FKB_BORDER_NONE = 0, FKB_BORDER_CONSTANT = 1, FKB_BORDER_REPLICATE = 2, F
 enum { FKB_WRITE_PACKED = 1, FKB_WRITE_SPLIT = 2,
        /* SplitWrite<_2D,T> (memory_operations.h:360-393): three unrelated planes dst (x), dst_y, dst_z, one base element
         * per pixel each, all with the pitch dst_pitch */
-       FKB_WRITE_SPLIT_PLANES = 3 };
+       FKB_WRITE_SPLIT_PLANES = 3,
+       /* WriteYUV<NV12|NV21|UYVY> (color_conversion.h:296-406) of (Y,Cb,Cr) byte triples; dst_format is U8C3.
+        * NV12 / NV21: dst is the luma plane, dst_y the interleaved chroma rows (reference: dst + pitch * height), both
+        * with the pitch dst_pitch.  NV12 takes the chroma pair of the pixel with even x and even y.  The reference's
+        * NV21 branch lets every pixel of a 2x2 block store its pair (the last store wins; on its CPU backend that is the
+        * last pixel of the block in raster order) — that pixel is the one written here.  UYVY: dst holds U Y0 V Y1
+        * groups, U and V from the even pixel. */
+       FKB_WRITE_NV12 = 4, FKB_WRITE_NV21 = 5, FKB_WRITE_UYVY = 6 };
 
 /* Compute ops.  The value type is tracked like the reference's Input/OutputType: it starts as
  * uchar3, ops that need float3 are rejected on uchar3 and vice versa. */
@@ -97,7 +104,9 @@ enum {
                                 (color_conversion.h:473-476, basic_ops/vector_ops.h:43-56)         any */
     FKB_OP_YUV2RGB = 7,      /* ConvertYUVToRGB<p8bit,CR,CP> (color_conversion.h:150-174): subtracts
                                 chain.yuv_sub, multiplies by chain.ccm rows, sums (x+y)+z          u8 -> f32 */
-    FKB_OP_SATCAST_U8 = 8    /* SaturateCast<float3,uchar3>    (image_processing/saturate.h:25-36) f32 -> u8 */
+    FKB_OP_SATCAST_U8 = 8,   /* SaturateCast<float3,uchar3>    (image_processing/saturate.h:25-36) f32 -> u8 */
+    FKB_OP_RGB2YUV = 9       /* ConvertRGBToYUV<p8bit,CR,CP> (color_conversion.h:176-199): ccm2 x (R,G,B), then adds
+                                yuv_add to (Y,Cb,Cr)                                                   u8 -> f32 */
 };
 
 typedef struct fkb_op {
@@ -118,6 +127,8 @@ typedef struct fkb_chain_desc {
     fkb_op ops[FKB_MAX_OPS];
     float ccm[9];         /* FKB_OP_YUV2RGB: row-major 3x3 (algorithms/image_processing/itu_color.h:185-258) */
     float yuv_sub[3];     /* FKB_OP_YUV2RGB: subtracted from (Y,U,V) first; Full range 8 bit = (0,128,128) */
+    float ccm2[9];        /* FKB_OP_RGB2YUV: row-major 3x3 (itu_color.h:185-258, direction RGB2YCbCr) */
+    float yuv_add[3];     /* FKB_OP_RGB2YUV: added to (Y,Cb,Cr) afterwards; Full range 8 bit = (0,128,128) */
     uint32_t border;      /* FKB_BORDER_*: a BorderReader between the Read and the Crop
                              (algorithms/image_processing/border_reader.h:25-334).  With one, the crop rectangle may leave
                              the frame: a frame coordinate outside [0,src_w) x [0,src_h) is remapped by the mode, or
@@ -150,7 +161,7 @@ typedef struct fkb_plane_desc {
                                 the resize parameters are ignored.  Without a Resize the read is uchar3, so bg must
                                 hold integers in [0,255]. */
     float params[FKB_MAX_PLANE_PARAMS][3]; /* operands of ops whose plane_slot >= 0 */
-    void* dst_y;             /* FKB_WRITE_SPLIT_PLANES: first byte of the second ... */
+    void* dst_y;             /* FKB_WRITE_SPLIT_PLANES: first byte of the second (FKB_WRITE_NV12/NV21: of the chroma rows) ... */
     void* dst_z;             /* ... and of the third channel plane; else unused */
 } fkb_plane_desc;
 
@@ -165,6 +176,8 @@ int fkb_resize_params(uint32_t geometry, fkb_plane_desc* plane);
 enum { FKB_RANGE_LIMITED = 0, FKB_RANGE_FULL = 1 };
 enum { FKB_PRIMITIVES_BT601 = 0, FKB_PRIMITIVES_BT709 = 1, FKB_PRIMITIVES_BT2020 = 2 };
 int fkb_ycbcr_to_rgb(uint32_t range, uint32_t primitives, float ccm[9], float yuv_sub[3]);
+/* The other direction, for fkb_chain_desc.ccm2 / yuv_add of a chain with FKB_OP_RGB2YUV (ConvertRGBToYUV). */
+int fkb_rgb_to_ycbcr(uint32_t range, uint32_t primitives, float ccm2[9], float yuv_add[3]);
 
 /* Host-only check of a launch: pointer, size, pitch, rectangle, type-flow and chain-index rules.
  * Launches run it first and return its code.  Needs no GPU. */

@@ -84,6 +84,8 @@ struct Lowered {
         chain.n_pre_ops = static_cast<uint32_t>(st.has_resize ? st.n_pre_ops : 0);
         chain.border = st.border; chain.border_at = static_cast<uint32_t>(st.border_at);
         for (int i = 0; i < 3; ++i) chain.border_value[i] = st.border_value[i];
+        for (int i = 0; i < 9; ++i) chain.ccm2[i] = st.ccm2[i];
+        for (int i = 0; i < 3; ++i) chain.yuv_add[i] = st.yuv_add[i];
         for (int i = 0; i < 9; ++i) chain.ccm[i] = st.ccm[i];
         for (int i = 0; i < 3; ++i) chain.yuv_sub[i] = st.yuv_sub[i];
         int next_slot = 0;

@@ -49,6 +49,8 @@ struct ReadState {
     size_t n_pre_ops{0};         // ops that were chained before the Resize run on the taps
     float ccm[9]{};
     float yuv_sub[3]{};
+    float ccm2[9]{};             // ConvertRGBToYUV: matrix and offsets
+    float yuv_add[3]{};
     // BatchRead<CONDITIONAL_WITH_DEFAULT>: planes >= used_planes yield dflt instead of reading (-1: every plane reads)
     int used_planes{-1};
     float dflt[3]{0.f, 0.f, 0.f};
@@ -114,6 +116,19 @@ struct ConvertYUVToRGB {
         if (fkb_ycbcr_to_rgb(CR == ColorRange::Full ? FKB_RANGE_FULL : FKB_RANGE_LIMITED, prim, op.ccm, op.yuv_sub) != FKB_OK)
             throw std::runtime_error("ConvertYUVToRGB: colour description refused");
         return op;
+    }
+};
+
+// RGB -> YCbCr (color_conversion.h:176-199); the matrix and offsets come from fkb_rgb_to_ycbcr.
+template <ColorDepth CD, ColorRange CR, ColorPrimitives CP>
+struct ConvertRGBToYUV {
+    static_assert(CD == ColorDepth::p8bit, "8-bit YCbCr is the depth the B200 kernels convert");
+    static auto build() {
+        ComputeIOp<FKB_OP_RGB2YUV, uchar3, float3> op{};
+        const uint32_t prim = CP == ColorPrimitives::bt601 ? FKB_PRIMITIVES_BT601 : CP == ColorPrimitives::bt709 ? FKB_PRIMITIVES_BT709 : FKB_PRIMITIVES_BT2020;
+        if (fkb_rgb_to_ycbcr(CR == ColorRange::Full ? FKB_RANGE_FULL : FKB_RANGE_LIMITED, prim, op.ccm, op.yuv_sub) != FKB_OK)
+            throw std::runtime_error("ConvertRGBToYUV: colour description refused");
+        return op;  // (ccm / yuv_sub of the IOp carry the matrix and the offsets to add)
     }
 };
 
@@ -237,6 +252,7 @@ struct ReadIOp {
         s.used_planes = -1;
         s.ops.push_back(detail::OpRec{C, {detail::f3(op.params)}});
         if (C == FKB_OP_YUV2RGB) { for (int i = 0; i < 9; ++i) s.ccm[i] = op.ccm[i]; for (int i = 0; i < 3; ++i) s.yuv_sub[i] = op.yuv_sub[i]; }
+        if (C == FKB_OP_RGB2YUV) { for (int i = 0; i < 9; ++i) s.ccm2[i] = op.ccm[i]; for (int i = 0; i < 3; ++i) s.yuv_add[i] = op.yuv_sub[i]; }
         return ReadIOp<O, BATCH>(std::move(s));
     }
 };
@@ -350,6 +366,18 @@ struct TensorSplit {
                            static_cast<size_t>(p.dims.width) * p.dims.height * sizeof(Base)};
     }
     static auto build(const Ptr<ND::_3D, Base>& p) { return build(p.ptr()); }
+};
+// (Y,Cb,Cr) byte triples into a YCbCr image (color_conversion.h:296-406).
+template <PixelFormat PF>
+struct WriteYUV {
+    static_assert(PF == PixelFormat::NV12 || PF == PixelFormat::NV21 || PF == PixelFormat::UYVY, "NV12, NV21 and UYVY are the images the B200 kernels write");
+    static auto build(const Image<PF>& img) { return build(img.ptr()); }
+    static auto build(const RawImage<PF>& raw) {
+        constexpr uint32_t kind = PF == PixelFormat::NV12 ? FKB_WRITE_NV12 : PF == PixelFormat::NV21 ? FKB_WRITE_NV21 : FKB_WRITE_UYVY;
+        WriteIOp<uchar3> w{kind, raw.data.data, raw.width, raw.height, raw.data.dims.pitch, 1, 0, 0};
+        if (PF != PixelFormat::UYVY) w.data_y = reinterpret_cast<uint8_t*>(raw.data.data) + static_cast<size_t>(raw.data.dims.pitch) * raw.height;
+        return w;
+    }
 };
 // Three separate 2-D planes, one per channel (memory_operations.h:360-393).
 template <ND D, typename T>

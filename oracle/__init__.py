@@ -41,6 +41,8 @@ def load_oracle() -> C.CDLL:
         lib.fkb_oracle_run.argtypes = [C.POINTER(abi.ChainDesc), C.c_uint32, C.POINTER(abi.PlaneDesc), C.c_uint32, C.c_uint32]
         lib.fkb_oracle_ycbcr_to_rgb.restype = C.c_int
         lib.fkb_oracle_ycbcr_to_rgb.argtypes = [C.c_uint32, C.c_uint32, C.POINTER(C.c_float), C.POINTER(C.c_float)]
+        lib.fkb_oracle_rgb_to_ycbcr.restype = C.c_int
+        lib.fkb_oracle_rgb_to_ycbcr.argtypes = [C.c_uint32, C.c_uint32, C.POINTER(C.c_float), C.POINTER(C.c_float)]
         lib.fkb_oracle_saturate_u8.restype = C.c_uint8
         lib.fkb_oracle_saturate_u8.argtypes = [C.c_float]
         lib.fkb_oracle_round_half_away.restype = C.c_float
@@ -69,6 +71,10 @@ def load_ref() -> C.CDLL:
         lib.fklref_saturate_u8.argtypes = [C.c_float]
         lib.fklref_resize_params.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, f32p, i32p]
         u8p = C.POINTER(C.c_uint8)
+        lib.fklref_rgb_to_ycbcr_matrix.restype = C.c_int
+        lib.fklref_rgb_to_ycbcr_matrix.argtypes = [C.c_int, C.c_int, f32p]
+        lib.fklref_rgb_to_yuv_image.restype = C.c_int
+        lib.fklref_rgb_to_yuv_image.argtypes = [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int]
         lib.fklref_resize_split_planes.restype = C.c_int
         lib.fklref_resize_split_planes.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, f32p, C.c_int, C.c_void_p,
                                                    C.c_void_p, C.c_void_p, C.c_int]
@@ -206,6 +212,12 @@ def run_ref(wl, threads: int = 1):
         rc = lib.fklref_nv12_border_constant(wl.sources[0].ctypes.data, p0.src_w, p0.src_h, p0.src_pitch,
                                              (C.c_int32 * 4)(*wl.extra["rect"]), _f3(wl.extra["value"]), p0.dst_w, p0.dst_h,
                                              outs[0].ctypes.data)
+    elif wl.name == "rgb_to_yuv_image":
+        rng, prim = wl.extra["colour"]
+        rc = lib.fklref_rgb_to_yuv_image(wl.extra["fmt"], rng, prim, wl.sources[0].ctypes.data, p0.src_w, p0.src_h, p0.src_pitch,
+                                         outs[0].ctypes.data, p0.dst_pitch)
+        if rc == -1:
+            raise ValueError("the reference runner has no instantiation for this format / range / primitives")
     elif wl.name == "split_planes":
         base = outs[0].ctypes.data
         rc = lib.fklref_resize_split_planes(wl.sources[0].ctypes.data, p0.src_w, p0.src_h, p0.src_pitch, p0.dst_w, p0.dst_h,

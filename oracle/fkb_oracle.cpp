@@ -104,6 +104,15 @@ inline V3 apply_ops(V3 v, const fkb_chain_desc& ch, const fkb_plane_desc& pl, ui
             v = r;
             break;
         }
+        case FKB_OP_RGB2YUV: {  // ConvertRGBToYUV::exec (color_conversion.h:188-198): matrix, then the offsets
+            V3 r;
+            for (int c = 0; c < 3; ++c) {
+                const float y = ((v.c[0] * ch.ccm2[3 * c + 0]) + (v.c[1] * ch.ccm2[3 * c + 1])) + (v.c[2] * ch.ccm2[3 * c + 2]);
+                r.c[c] = ch.yuv_add[c] != 0.f ? y + ch.yuv_add[c] : y;  // Full range: the luma is returned as computed
+            }
+            v = r;
+            break;
+        }
         case FKB_OP_SATCAST_U8:
             for (int c = 0; c < 3; ++c) v.c[c] = static_cast<float>(sat_u8(v.c[c]));
             break;
@@ -231,7 +240,23 @@ void run_plane(const fkb_chain_desc& ch, const fkb_plane_desc& pl) {
         for (uint32_t x = 0; x < pl.dst_w; ++x) {
             const V3 v = pixel(ch, pl, static_cast<int>(x), static_cast<int>(y));
             uint8_t* row = dst + static_cast<size_t>(y) * pl.dst_pitch;
-            if (ch.write_kind == FKB_WRITE_SPLIT_PLANES) {  // SplitWrite (memory_operations.h:360-393): one RawPtr per channel
+            if (ch.write_kind >= FKB_WRITE_NV12) {  // WriteYUV::exec (color_conversion.h:309-383)
+                const uint8_t yy = static_cast<uint8_t>(v.c[0]), cb = static_cast<uint8_t>(v.c[1]), cr = static_cast<uint8_t>(v.c[2]);
+                if (ch.write_kind == FKB_WRITE_UYVY) {
+                    uint8_t* g = row + static_cast<size_t>(x >> 1) * 4;
+                    if (x & 1u) g[3] = yy; else { g[0] = cb; g[1] = yy; g[2] = cr; }
+                } else {
+                    row[x] = yy;
+                    uint8_t* uv = static_cast<uint8_t*>(pl.dst_y) + static_cast<size_t>(y >> 1) * pl.dst_pitch + static_cast<size_t>(x >> 1) * 2;
+                    if (ch.write_kind == FKB_WRITE_NV12) {
+                        if (!(x & 1u) && !(y & 1u)) { uv[0] = cb; uv[1] = cr; }
+                    } else {
+                        // NV21: every pixel stores its (Cr,Cb) pair; this loop visits pixels in raster order, as the
+                        // reference's CPU backend does, so the last pixel of each 2x2 block is what stays
+                        uv[0] = cr; uv[1] = cb;
+                    }
+                }
+            } else if (ch.write_kind == FKB_WRITE_SPLIT_PLANES) {  // SplitWrite (memory_operations.h:360-393): one RawPtr per channel
                 uint8_t* const base[3] = {dst, static_cast<uint8_t*>(pl.dst_y), static_cast<uint8_t*>(pl.dst_z)};
                 for (int c = 0; c < 3; ++c) {
                     uint8_t* q = base[c] + static_cast<size_t>(y) * pl.dst_pitch;
@@ -315,6 +340,30 @@ int fkb_oracle_ycbcr_to_rgb(uint32_t range, uint32_t primitives, float* ccm, flo
     }
     yuv_sub[0] = range == FKB_RANGE_LIMITED ? 16.f : 0.f;
     yuv_sub[1] = 128.f; yuv_sub[2] = 128.f;
+    return FKB_OK;
+}
+
+// ccMatrix<CR, CP, RGB2YCbCr, p8bit> (itu_color.h:193-218) and the offsets ConvertRGBToYUV adds (color_conversion.h:191-197).
+int fkb_oracle_rgb_to_ycbcr(uint32_t range, uint32_t primitives, float* ccm2, float* yuv_add) {
+    float kr, kb;
+    switch (primitives) {
+    case FKB_PRIMITIVES_BT601: kr = 0.299f; kb = 0.114f; break;
+    case FKB_PRIMITIVES_BT709: kr = 0.2126f; kb = 0.0722f; break;
+    case FKB_PRIMITIVES_BT2020: kr = 0.2627f; kb = 0.0593f; break;
+    default: return FKB_ERR_INVALID;
+    }
+    const float kg = 1.0f - kr - kb;
+    ccm2[0] = kr; ccm2[1] = kg; ccm2[2] = kb;
+    ccm2[3] = -kr / (2.0f * (1.0f - kb)); ccm2[4] = -kg / (2.0f * (1.0f - kb)); ccm2[5] = 0.5f;
+    ccm2[6] = 0.5f; ccm2[7] = -kg / (2.0f * (1.0f - kr)); ccm2[8] = -kb / (2.0f * (1.0f - kr));
+    if (range == FKB_RANGE_LIMITED) {
+        const float sy = 219.f / 255.f, sc = 224.f / 255.f;
+        for (int i = 0; i < 3; ++i) { ccm2[i] *= sy; ccm2[3 + i] *= sc; ccm2[6 + i] *= sc; }
+    } else if (range != FKB_RANGE_FULL) {
+        return FKB_ERR_INVALID;
+    }
+    yuv_add[0] = range == FKB_RANGE_LIMITED ? 16.f : 0.f;
+    yuv_add[1] = 128.f; yuv_add[2] = 128.f;
     return FKB_OK;
 }
 

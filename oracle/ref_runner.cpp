@@ -383,6 +383,46 @@ extern "C" int fklref_nv12_border_constant(const uint8_t* nv12, int w, int h, in
     return 0;
 }
 
+// PerThreadRead<uchar3> (R,G,B) -> ConvertRGBToYUV<p8bit, CR, CP> -> SaturateCast -> WriteYUV<PF>
+template <PixelFormat PF, ColorRange CR, ColorPrimitives CP>
+static int rgb_to_yuv_image(const uint8_t* rgb, int w, int h, int pitch, uint8_t* out, int opitch) {
+    CpuStream stream;
+    constexpr bool packed = PF == PixelFormat::UYVY;
+    const Ptr<ND::_2D, uchar> buf(out, packed ? PtrDims<ND::_2D>(w * 2, h, opitch) : PtrDims<ND::_2D>(w, h + h / 2, opitch), MemType::Host, 0);
+    const Image<PF> img(buf, w, h);
+    executeOperations<CpuDPP>(stream, PerThreadRead<ND::_2D, uchar3>::build(wrap_frame(rgb, w, h, pitch)),
+        ConvertRGBToYUV<ColorDepth::p8bit, CR, CP>::build(), SaturateCast<float3, uchar3>::build(), WriteYUV<PF>::build(img));
+    return 0;
+}
+extern "C" int fklref_rgb_to_yuv_image(int format, int range, int primitives, const uint8_t* rgb, int w, int h, int pitch, uint8_t* out, int opitch) {
+    switch (format * 100 + range * 10 + primitives) {
+    case 311: return rgb_to_yuv_image<PixelFormat::NV12, ColorRange::Full, ColorPrimitives::bt709>(rgb, w, h, pitch, out, opitch);
+    case 300: return rgb_to_yuv_image<PixelFormat::NV12, ColorRange::Limited, ColorPrimitives::bt601>(rgb, w, h, pitch, out, opitch);
+    case 402: return rgb_to_yuv_image<PixelFormat::NV21, ColorRange::Limited, ColorPrimitives::bt2020>(rgb, w, h, pitch, out, opitch);
+    case 410: return rgb_to_yuv_image<PixelFormat::NV21, ColorRange::Full, ColorPrimitives::bt601>(rgb, w, h, pitch, out, opitch);
+    case 501: return rgb_to_yuv_image<PixelFormat::UYVY, ColorRange::Limited, ColorPrimitives::bt709>(rgb, w, h, pitch, out, opitch);
+    case 512: return rgb_to_yuv_image<PixelFormat::UYVY, ColorRange::Full, ColorPrimitives::bt2020>(rgb, w, h, pitch, out, opitch);
+    default: return -1;
+    }
+}
+template <ColorRange CR, ColorPrimitives CP>
+static void inverse_matrix_of(float* m9) {
+    constexpr M3x3Float m = ccMatrix<CR, CP, ColorConversionDir::RGB2YCbCr, ColorDepth::p8bit>;
+    m9[0] = m.x.x; m9[1] = m.x.y; m9[2] = m.x.z; m9[3] = m.y.x; m9[4] = m.y.y; m9[5] = m.y.z;
+    m9[6] = m.z.x; m9[7] = m.z.y; m9[8] = m.z.z;
+}
+extern "C" int fklref_rgb_to_ycbcr_matrix(int range, int primitives, float* m9) {
+    switch (range * 3 + primitives) {
+    case 0: inverse_matrix_of<ColorRange::Limited, ColorPrimitives::bt601>(m9); return 0;
+    case 1: inverse_matrix_of<ColorRange::Limited, ColorPrimitives::bt709>(m9); return 0;
+    case 2: inverse_matrix_of<ColorRange::Limited, ColorPrimitives::bt2020>(m9); return 0;
+    case 3: inverse_matrix_of<ColorRange::Full, ColorPrimitives::bt601>(m9); return 0;
+    case 4: inverse_matrix_of<ColorRange::Full, ColorPrimitives::bt709>(m9); return 0;
+    case 5: inverse_matrix_of<ColorRange::Full, ColorPrimitives::bt2020>(m9); return 0;
+    default: return -1;
+    }
+}
+
 // ReadYUV<PF> -> ConvertYUVToRGB<p8bit, CR, CP> -> Resize(IGNORE_AR) -> Sub -> Div -> TensorSplit<float3>
 template <PixelFormat PF, ColorRange CR, ColorPrimitives CP>
 static int yuv_resize_split(const uint8_t* data, int w, int h, int pitch, int dw, int dh, const float* sub, const float* div, float* out) {

@@ -172,6 +172,35 @@ static void test_yuv(const char* what, uint32_t fmt, uint32_t range, uint32_t pr
     report(what, std::memcmp(want.data(), out.ptrPinned().data, want.size() * 4) == 0);
 }
 
+// ---- RGB -> YCbCr image: ConvertRGBToYUV, SaturateCast, WriteYUV -----------------------------------------------------
+extern "C" int fkb_oracle_rgb_to_ycbcr(uint32_t range, uint32_t primitives, float* ccm2, float* yuv_add);
+static void test_write_yuv() {
+    Stream stream;
+    const uint W = 322, H = 180;
+    Ptr2D<uchar3> rgb(W, H);
+    fill_random(rgb, 700);
+    rgb.upload(stream);
+    Image<PixelFormat::NV12> img(W, H);
+    executeOperations<TransformDPP<>>(stream, PerThreadRead<ND::_2D, uchar3>::build(rgb),
+        ConvertRGBToYUV<ColorDepth::p8bit, ColorRange::Limited, ColorPrimitives::bt601>::build(), SaturateCast<float3, uchar3>::build(),
+        WriteYUV<PixelFormat::NV12>::build(img));
+    img.download(stream);
+    stream.sync();
+    fkb_chain_desc ch{};
+    ch.src_format = FKB_PIX_U8C3; ch.geometry = FKB_GEOM_NONE; ch.dst_format = FKB_PIX_U8C3; ch.write_kind = FKB_WRITE_NV12;
+    ch.n_ops = 2; ch.ops[0] = op(FKB_OP_RGB2YUV); ch.ops[1] = op(FKB_OP_SATCAST_U8);
+    fkb_oracle_rgb_to_ycbcr(FKB_RANGE_LIMITED, FKB_PRIMITIVES_BT601, ch.ccm2, ch.yuv_add);
+    const auto out = img.getData().ptrPinned();
+    std::vector<uint8_t> want(static_cast<size_t>(out.dims.pitch) * (H + H / 2), 0);
+    fkb_plane_desc d = host_plane(rgb, Rect(0, 0, W, H), W, H, want.data(), out.dims.pitch, ch.geometry);
+    d.dst_y = want.data() + static_cast<size_t>(out.dims.pitch) * H;
+    fkb_oracle_run(&ch, 1, &d, 1, 1);
+    bool same = true;
+    for (uint y = 0; y < H + H / 2; ++y)
+        same = same && std::memcmp(want.data() + y * out.dims.pitch, reinterpret_cast<const uint8_t*>(out.data) + y * out.dims.pitch, W) == 0;
+    report("RGB -> NV12 image (ConvertRGBToYUV, WriteYUV)", same);
+}
+
 // ---- batched crop-resize-normalise over several frames --------------------------------------------------------------
 template <AspectRatio AR>
 static void test_batched(const char* what, uint32_t geometry) {
@@ -393,6 +422,7 @@ int main() {
     test_batched<AspectRatio::PRESERVE_AR_LEFT>("batched crop-resize-normalise, PRESERVE_AR_LEFT", FKB_GEOM_RESIZE_PRESERVE_AR_LEFT);
     test_conditional_batch();
     test_tensor_t_split();
+    test_write_yuv();
     test_split_write();
     test_border<BorderType::CONSTANT>("BorderReader<CONSTANT> (complete form, operator&)");
     test_border<BorderType::REPLICATE>("BorderReader<REPLICATE>");

@@ -81,6 +81,10 @@ def test_ycbcr_matrices_match_oracle():
             assert list(a) == list(b) and list(sa) == list(sb)
     assert lib.fkb_ycbcr_to_rgb(2, 0, a, sa) == abi.ERR_INVALID and lib.fkb_ycbcr_to_rgb(0, 3, a, sa) == abi.ERR_INVALID
     assert lib.fkb_ycbcr_to_rgb(0, 0, None, sa) == abi.ERR_NULL
+    for rng in (abi.RANGE_LIMITED, abi.RANGE_FULL):
+        for prim in (abi.PRIMITIVES_BT601, abi.PRIMITIVES_BT709, abi.PRIMITIVES_BT2020):
+            assert lib.fkb_rgb_to_ycbcr(rng, prim, a, sa) == 0 and orc.fkb_oracle_rgb_to_ycbcr(rng, prim, b, sb) == 0
+            assert list(a) == list(b) and list(sa) == list(sb)
 
 
 def _bound(wl):

@@ -163,6 +163,13 @@ def test_border_constant_after_colour_conversion():
     check(W.nv12_border_constant(w=640, h=360, rect=(500, 300, 400, 200), dst=(320, 320)))
 
 
+@pytest.mark.parametrize("fmt", [abi.PIX_NV12, abi.PIX_NV21, abi.PIX_UYVY])
+def test_write_yuv_images(fmt):
+    for colour in [(abi.RANGE_FULL, abi.PRIMITIVES_BT709), (abi.RANGE_LIMITED, abi.PRIMITIVES_BT601)]:
+        for size in [dict(w=322, h=180), dict(w=64, h=36), dict(w=1280, h=720), dict(w=33, h=21)]:
+            check(W.rgb_to_yuv_image(fmt, colour, **size))
+
+
 def test_many_planes_use_the_descriptor_arena():
     # more planes than fit in the kernel parameters: descriptors travel through the pinned/device ring
     wl = W.batched_crop_resize(n_frames=3, crops_per_frame=100, w=320, h=240, dst=(32, 24), crop_range=(4, 100))

@@ -109,6 +109,32 @@ def test_ycbcr_matrices_against_reference():
             assert list(sub) == [16.0 if rng == abi.RANGE_LIMITED else 0.0, 128.0, 128.0]
 
 
+@pytest.mark.skipif(not oracle.have_ref(), reason="reference-backed checker not built")
+def test_rgb_to_ycbcr_matrices_against_reference():
+    lib, ref = oracle.load_oracle(), oracle.load_ref()
+    for rng in (abi.RANGE_LIMITED, abi.RANGE_FULL):
+        for prim in (abi.PRIMITIVES_BT601, abi.PRIMITIVES_BT709, abi.PRIMITIVES_BT2020):
+            want, got, add = (C.c_float * 9)(), (C.c_float * 9)(), (C.c_float * 3)()
+            assert ref.fklref_rgb_to_ycbcr_matrix(rng, prim, want) == 0
+            assert lib.fkb_oracle_rgb_to_ycbcr(rng, prim, got, add) == 0
+            assert list(got) == list(want), (rng, prim)
+            assert list(add) == [16.0 if rng == abi.RANGE_LIMITED else 0.0, 128.0, 128.0]
+
+
+WRITE_YUV_CASES = [(abi.PIX_NV12, abi.RANGE_FULL, abi.PRIMITIVES_BT709), (abi.PIX_NV12, abi.RANGE_LIMITED, abi.PRIMITIVES_BT601),
+                   (abi.PIX_NV21, abi.RANGE_LIMITED, abi.PRIMITIVES_BT2020), (abi.PIX_NV21, abi.RANGE_FULL, abi.PRIMITIVES_BT601),
+                   (abi.PIX_UYVY, abi.RANGE_LIMITED, abi.PRIMITIVES_BT709), (abi.PIX_UYVY, abi.RANGE_FULL, abi.PRIMITIVES_BT2020)]
+
+
+@pytest.mark.skipif(not oracle.have_ref(), reason="reference-backed checker not built")
+@pytest.mark.parametrize("fmt,rng,prim", WRITE_YUV_CASES)
+def test_oracle_write_yuv_matches_reference_backend(fmt, rng, prim):
+    for size in [dict(w=322, h=180), dict(w=64, h=36)]:
+        wl = W.rgb_to_yuv_image(fmt, (rng, prim), **size)
+        got, want = oracle.run_oracle(wl), oracle.run_ref(wl)
+        assert np.array_equal(got[0], want[0])
+
+
 YUV_CASES = [(abi.PIX_NV12, abi.RANGE_FULL, abi.PRIMITIVES_BT709), (abi.PIX_NV12, abi.RANGE_LIMITED, abi.PRIMITIVES_BT601),
              (abi.PIX_NV12, abi.RANGE_LIMITED, abi.PRIMITIVES_BT2020), (abi.PIX_NV21, abi.RANGE_FULL, abi.PRIMITIVES_BT601),
              (abi.PIX_NV21, abi.RANGE_LIMITED, abi.PRIMITIVES_BT709), (abi.PIX_UYVY, abi.RANGE_FULL, abi.PRIMITIVES_BT2020),

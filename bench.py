@@ -208,14 +208,27 @@ def time_launches(fn, steps: int, torch) -> float:
     return start.elapsed_time(stop) / 1e3
 
 
-def other_configs(torch, steps: int, peak: float) -> dict:
+def other_configs(torch, steps: int, peak: float, widened: bool = False) -> dict:
     """Kernel-only figures of the other four configurations on one GPU.  Their launches last a few microseconds, less
     than the host needs to submit one, so a round over all buffer sets is captured once into a CUDA graph and the graph
     is replayed; rotating the buffer sets (together larger than the L2) makes every launch read from HBM."""
-    from fusedkernellibrary_b200 import runtime, workloads as W
+    from fusedkernellibrary_b200 import abi, runtime, workloads as W
     out = {}
-    for name, factory in (("readme_crops", W.readme_crops), ("vertical_fusion", W.vertical_fusion),
-                          ("nv12_preprocess", W.nv12_preprocess), ("divergent_planes", W.divergent_planes)):
+    cases = [("readme_crops", W.readme_crops), ("vertical_fusion", W.vertical_fusion),
+             ("nv12_preprocess", W.nv12_preprocess), ("divergent_planes", W.divergent_planes)]
+    if widened:
+        # the chains beside the five configurations (border handling, other YCbCr sources, conditional batches, planar and
+        # YCbCr destinations), each on a launch large enough to time
+        cases = [
+            ("border_replicate_crops", lambda: W.border_crops(abi.BORDER_REPLICATE, w=1920, h=1080, dst=(224, 224))),
+            ("nv21_limited_bt601_preprocess", lambda: W.nv12_preprocess(src_format=abi.PIX_NV21, colour=(abi.RANGE_LIMITED, abi.PRIMITIVES_BT601))),
+            ("uyvy_preprocess", lambda: W.nv12_preprocess(src_format=abi.PIX_UYVY, colour=(abi.RANGE_FULL, abi.PRIMITIVES_BT709))),
+            ("conditional_batch_resize", lambda: W.conditional_resize(used=6, w=1920, h=1080, dst=(640, 360))),
+            ("tensor_t_split_resize", lambda: W.tsplit_resize(w=1920, h=1080, dst=(640, 360))),
+            ("split_planes_resize", lambda: W.split_planes(w=1920, h=1080, dst=(960, 540))),
+            ("rgb_to_nv12_image", lambda: W.rgb_to_yuv_image(abi.PIX_NV12, (abi.RANGE_LIMITED, abi.PRIMITIVES_BT709), w=1920, h=1080)),
+        ]
+    for name, factory in cases:
         wl = factory()
         alg = wl.algorithmic_bytes()
         footprint = sum(s.nbytes for s in wl.sources) + sum(wl.out_sizes)
@@ -427,6 +440,7 @@ def our_arm(args) -> None:
             del dw
             torch.cuda.empty_cache()
             line["other_configs"] = other_configs(torch, max(10, min(args.steps, 50)), peak)
+            line["widened_rows"] = other_configs(torch, max(10, min(args.steps, 50)), peak, widened=True)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -188,9 +188,12 @@ void classify(const fkb_chain_desc& ch, PlaneRec& r) {
         r.kclass = KCLASS_NV12;  // NV12 -> RGB on the taps -> resize -> [Mul][Add|Sub][Div][SaturateCast]: nv12_kernel
         return;
     }
-    if (ch.src_format != FKB_PIX_U8C3 || ch.write_kind != FKB_WRITE_PACKED) return;
-    if (!aligned16(r.src) || !aligned16(r.dst) || (r.src_pitch & 15) || (r.dst_pitch & 15)) return;
     const bool f32 = ch.dst_format == FKB_PIX_F32C3;
+    // planar float destinations (tensor, transposed tensor, three planes) have a staged path for resampling chains
+    const bool planar = (ch.write_kind == FKB_WRITE_SPLIT || ch.write_kind == FKB_WRITE_SPLIT_PLANES) && f32 && ch.geometry != FKB_GEOM_NONE;
+    if (ch.src_format != FKB_PIX_U8C3 || (ch.write_kind != FKB_WRITE_PACKED && !planar)) return;
+    if (!aligned16(r.src) || !aligned16(r.dst) || (r.src_pitch & 15) || (r.dst_pitch & 15)) return;
+    if (planar && ((r.dst_cstride & 15) || (r.dst_cstride2 & 15))) return;
     const uint32_t elt = f32 ? 12u : 3u;
 
     (void)elt;

@@ -287,6 +287,26 @@ __device__ __forceinline__ void store_row(uint8_t* gdst, uint32_t srow, uint32_t
     }
 }
 
+// The same for a planar float row: one bulk store per channel segment, one commit for the three.
+__device__ __forceinline__ void store_row_planar(uint8_t* gdst, uint64_t off1, uint64_t off2, uint32_t srow, uint32_t row_bytes, uint32_t lane) {
+    const uint32_t bulk = row_bytes & ~15u;
+    fence_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+        if (bulk) {
+            bulk_store(gdst, smem_raw + srow, bulk);
+            bulk_store(gdst + off1, smem_raw + srow + kPlanarSegBytes, bulk);
+            bulk_store(gdst + off2, smem_raw + srow + 2 * kPlanarSegBytes, bulk);
+        }
+        bulk_commit();
+    }
+    if (row_bytes != bulk && lane < row_bytes - bulk) {  // a row whose byte length is not a multiple of 16
+        gdst[bulk + lane] = smem_raw[srow + bulk + lane];
+        gdst[off1 + bulk + lane] = smem_raw[srow + kPlanarSegBytes + bulk + lane];
+        gdst[off2 + bulk + lane] = smem_raw[srow + 2 * kPlanarSegBytes + bulk + lane];
+    }
+}
+
 // --- post-ops ---------------------------------------------------------------------------------------------
 // The ops that follow the read (POINT) or the interpolation (RESIZE).  Chains of the shape [Mul] [Add|Sub] [SaturateCast]
 // (each part optional, in this order) are specialised at compile time: KIND is a bit mask of the parts present and the
@@ -435,10 +455,12 @@ __device__ __forceinline__ bool point_item(const LaunchParams& p, const WarpSlic
 // the crop is made a copy of the last column after the row lands, which is exactly the reference's clamp of x2.
 // Bytes become fp32 through the half-subnormal trick (byte_times_2m24), and all arithmetic runs on pixel pairs with
 // packed f32x2 instructions.  The background bars are written into the two output-row buffers once per item.
-template <bool F32, int KIND>
+template <bool F32, int KIND, bool PLANAR = false>
 __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSlice& w, uint32_t ox, uint32_t oy0,
                                             uint32_t ow, uint32_t nr, uint32_t& k, uint32_t lane) {
-    constexpr uint32_t ELT = F32 ? 12u : 3u;
+    static_assert(F32 || !PLANAR, "planar rows are float rows");
+    constexpr uint32_t ELT = PLANAR ? 4u : F32 ? 12u : 3u;            // bytes between columns of a staged output row
+    constexpr uint32_t DEAD = PLANAR ? 1024u : kOutRowBytes;          // where columns that do not exist are stored
     const PlaneRec& pl = *w.pl;
     const fkb_chain_desc& ch = p.chains[pl.chain];
     const bool par = ch.geometry >= FKB_GEOM_RESIZE_PRESERVE_AR;
@@ -471,7 +493,7 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
         const AxisTap t = axis_tap(xa + col - X1, fx, crop_w);
         boff[j] = n_in ? static_cast<uint32_t>(t.i0 - c_lo) * 3u + shift : 0u;
         wx0[j] = t.w0; wx1[j] = t.w1;
-        ooff[j] = live ? static_cast<uint32_t>(xa - static_cast<int>(ox) + col) * ELT : kOutRowBytes;
+        ooff[j] = live ? static_cast<uint32_t>(xa - static_cast<int>(ox) + col) * ELT : DEAD;
     }
     // Offset (in a staged row) of the crop's last column when a tap pair reaches one past it; that column is then
     // duplicated into the next three bytes.  Otherwise the copy is aimed at the unused tail of the staged row.
@@ -490,7 +512,12 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
         for (int c = 0; c < 3; ++c) bgbits[c] = F32 ? __float_as_uint(b[0][c]) : u8_of_exact(b[0][c]);
     }
     auto put = [&](uint32_t q, uint32_t b0, uint32_t b1, uint32_t b2) {
-        if (F32) { uint32_t* f = reinterpret_cast<uint32_t*>(smem_raw + q); f[0] = b0; f[1] = b1; f[2] = b2; }
+        if (PLANAR) {
+            *reinterpret_cast<uint32_t*>(smem_raw + q) = b0;
+            *reinterpret_cast<uint32_t*>(smem_raw + q + kPlanarSegBytes) = b1;
+            *reinterpret_cast<uint32_t*>(smem_raw + q + 2 * kPlanarSegBytes) = b2;
+        }
+        else if (F32) { uint32_t* f = reinterpret_cast<uint32_t*>(smem_raw + q); f[0] = b0; f[1] = b1; f[2] = b2; }
         else { smem_raw[q] = static_cast<uint8_t>(b0); smem_raw[q + 1] = static_cast<uint8_t>(b1); smem_raw[q + 2] = static_cast<uint8_t>(b2); }
     };
     // the bars left and right of the image are the same for every row of the item: fill them in both row buffers once
@@ -595,21 +622,22 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
             default: break;
             }
         }
-        store_row(gdst + static_cast<size_t>(r) * dst_pitch, out_s, ow * ELT, lane);
+        if (PLANAR) store_row_planar(gdst + static_cast<size_t>(r) * dst_pitch, pl.dst_cstride, pl.dst_cstride2, out_s, ow * ELT, lane);
+        else store_row(gdst + static_cast<size_t>(r) * dst_pitch, out_s, ow * ELT, lane);
     }
     return true;
 }
 
-template <bool F32>
+template <bool F32, bool PLANAR = false>
 __device__ __forceinline__ bool resize_dispatch(const LaunchParams& p, const WarpSlice& w, uint32_t kind, uint32_t ox,
                                                 uint32_t oy0, uint32_t ow, uint32_t nr, uint32_t& k, uint32_t lane) {
     constexpr int S = F32 ? 0 : kPostSat;  // a uchar3 destination ends in a SaturateCast, a float3 one cannot
     switch (kind) {
-    case S: return resize_item<F32, S>(p, w, ox, oy0, ow, nr, k, lane);
-    case S | kPostMul: return resize_item<F32, S | kPostMul>(p, w, ox, oy0, ow, nr, k, lane);
-    case S | kPostAdd: return resize_item<F32, S | kPostAdd>(p, w, ox, oy0, ow, nr, k, lane);
-    case S | kPostMul | kPostAdd: return resize_item<F32, S | kPostMul | kPostAdd>(p, w, ox, oy0, ow, nr, k, lane);
-    default: return resize_item<F32, kPostGeneric>(p, w, ox, oy0, ow, nr, k, lane);
+    case S: return resize_item<F32, S, PLANAR>(p, w, ox, oy0, ow, nr, k, lane);
+    case S | kPostMul: return resize_item<F32, S | kPostMul, PLANAR>(p, w, ox, oy0, ow, nr, k, lane);
+    case S | kPostAdd: return resize_item<F32, S | kPostAdd, PLANAR>(p, w, ox, oy0, ow, nr, k, lane);
+    case S | kPostMul | kPostAdd: return resize_item<F32, S | kPostMul | kPostAdd, PLANAR>(p, w, ox, oy0, ow, nr, k, lane);
+    default: return resize_item<F32, kPostGeneric, PLANAR>(p, w, ox, oy0, ow, nr, k, lane);
     }
 }
 
@@ -660,6 +688,7 @@ __global__ void __launch_bounds__(kStagedThreads, 2) staged_kernel(const __grid_
                 default: ok = point_item<true, kPostGeneric>(p, w, ox, oy0, ow, nr, k4, lane); break;
             }
         }
+        else if (p.chains[pl.chain].write_kind != FKB_WRITE_PACKED) ok = resize_dispatch<true, true>(p, w, p.post_kind[pl.chain], ox, oy0, ow, nr, k, lane);
         else ok = f32 ? resize_dispatch<true>(p, w, p.post_kind[pl.chain], ox, oy0, ow, nr, k, lane)
                       : resize_dispatch<false>(p, w, p.post_kind[pl.chain], ox, oy0, ow, nr, k, lane);
     }

@@ -14,7 +14,10 @@ constexpr uint32_t kStagedWarps = kStagedThreads / 32;
 constexpr uint32_t kSliceHeader = 256;
 constexpr uint32_t kInRowBytes = 1600;   // one staged source row segment (512 uchar3 pixels + alignment slack)
 constexpr uint32_t kOutRowBytes = 3072;  // one output row segment (256 float3 pixels, or 512 uchar3 with room to spare)
-constexpr uint32_t kOutSlotBytes = kOutRowBytes + 16;  // the 16 spare bytes take the stores of columns that do not exist
+// A planar float row is three segments (one per channel) of 256 values, each followed by 16 spare bytes; a packed row is
+// followed by 16 spare bytes.  The spare bytes take the stores of columns that do not exist.
+constexpr uint32_t kPlanarSegBytes = 1024 + 16;
+constexpr uint32_t kOutSlotBytes = 3 * kPlanarSegBytes;
 constexpr uint32_t kSliceBytes = kSliceHeader + 4 * kInRowBytes + 2 * kOutSlotBytes;
 constexpr uint32_t kStagedSmemBytes = kStagedWarps * kSliceBytes;
 constexpr uint32_t kMaxRowsPerItem = 32;

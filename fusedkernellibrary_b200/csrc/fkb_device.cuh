@@ -76,6 +76,7 @@ struct LaunchParams {
     uint32_t n_tiles;
     uint32_t tiles_per_plane;  // > 0 when every plane has the same number of tiles; else PlaneRec::tile_base is searched
     int* status;
+    uint32_t* work;            // staged_kernel: {next item, warps finished} for dynamic item claiming; null = items dealt round-robin
     uint32_t n_lut_units;     // work units of lut_kernel (a block of rows of one LUT plane)
     uint32_t lut_swap;        // bit c: chain c contains an odd number of channel reorders
     uint32_t post_kind[FKB_MAX_CHAINS];

@@ -227,10 +227,12 @@ void classify(const fkb_chain_desc& ch, PlaneRec& r) {
 }
 
 // Output rows a warp processes per item.  Inside an item the next row's footprint is prefetched while the current
-// row is computed, so longer items pipeline better; more items balance better.  Large launches get about eight items
-// per resident warp; launches too small to occupy every warp get one row per item.
+// row is computed, so longer items pipeline better; more items balance better (warps claim them from a counter).  Large
+// launches get about sixteen items per resident warp — measured on the 2048-plane crop-resize launch, 10 to 16 rows per
+// item are within 1 % of each other, 4 or 24 rows cost 3 to 12 % — launches too small to occupy every warp get one
+// row per item.
 uint32_t rows_per_item(uint64_t row_segments, uint32_t resident_warps) {
-    const uint64_t per = row_segments / (static_cast<uint64_t>(resident_warps) * 8u);
+    const uint64_t per = row_segments / (static_cast<uint64_t>(resident_warps) * 16u);
     uint32_t rpi = static_cast<uint32_t>(std::min<uint64_t>(std::max<uint64_t>(per, 1), kMaxRowsPerItem));
     if (rpi < 4 && row_segments >= static_cast<uint64_t>(resident_warps) * 4u) rpi = 4;
     return rpi;
@@ -450,6 +452,11 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
     return status_word(&L.lp.status);
 }
 
+// Whether the staged kernel of this launch should claim its items from a counter: more items than resident warps.
+bool wants_work_counter(const Lowered& L) {
+    return L.staged_grid != 0 && L.lp.n_tiles > L.staged_grid * kStagedWarps;
+}
+
 int run(const Lowered& L, const LaunchParams& lp, cudaStream_t stream) {
     if (L.staged_grid) FKB_CUDA(launch_staged(lp, L.staged_grid, stream));
     if (L.lut_grid) FKB_CUDA(launch_lut(lp, L.lut_grid, stream));
@@ -469,6 +476,7 @@ struct Arena {
     size_t slot_bytes = 0;
     uint8_t* pinned = nullptr;
     uint8_t* dev = nullptr;
+    uint32_t* work = nullptr;
     cudaEvent_t ev[kSlots] = {};
     bool used[kSlots] = {};
     int next = 0;
@@ -483,6 +491,10 @@ struct Arena {
         while (want < bytes) want <<= 1;
         FKB_CUDA(cudaMallocHost(reinterpret_cast<void**>(&pinned), want * kSlots));
         FKB_CUDA(cudaMalloc(reinterpret_cast<void**>(&dev), want * kSlots));
+        if (!work) {  // one pair of item counters per slot; a kernel leaves its pair at zero
+            FKB_CUDA(cudaMalloc(reinterpret_cast<void**>(&work), sizeof(uint32_t) * 2 * kSlots));
+            FKB_CUDA(cudaMemset(work, 0, sizeof(uint32_t) * 2 * kSlots));
+        }
         if (!ev[0])
             for (int i = 0; i < kSlots; ++i) FKB_CUDA(cudaEventCreateWithFlags(&ev[i], cudaEventDisableTiming));
         slot_bytes = want;
@@ -509,24 +521,29 @@ int launch_once(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane
     Lowered L;
     int rc = lower(chains, n_chains, planes, n_planes, L);
     if (rc != FKB_OK) return rc;
-    if (n_planes <= kInlinePlanes) {
+    const bool inline_planes = n_planes <= kInlinePlanes, counter = wants_work_counter(L);
+    if (inline_planes) {
         std::memcpy(L.lp.inline_planes, L.recs.data(), sizeof(PlaneRec) * n_planes);
         L.lp.table = nullptr;
-        return run(L, L.lp, stream);
+        if (!counter) return run(L, L.lp, stream);
     }
+    // a slot of the arena: its part of the device table (launches of many planes) and its pair of item counters
     Arena& a = arena_for_current_device(rc);
     if (rc != FKB_OK) return rc;
     std::lock_guard<std::mutex> g(a.m);
-    const size_t bytes = sizeof(PlaneRec) * n_planes;
+    const size_t bytes = inline_planes ? 1 : sizeof(PlaneRec) * n_planes;
     if ((rc = a.ensure(bytes)) != FKB_OK) return rc;
     const int slot = a.next;
     a.next = (a.next + 1) % Arena::kSlots;
     if (a.used[slot]) { FKB_CUDA(cudaEventSynchronize(a.ev[slot])); a.used[slot] = false; }
-    uint8_t* h = a.pinned + static_cast<size_t>(slot) * a.slot_bytes;
-    uint8_t* d = a.dev + static_cast<size_t>(slot) * a.slot_bytes;
-    std::memcpy(h, L.recs.data(), bytes);
-    FKB_CUDA(cudaMemcpyAsync(d, h, bytes, cudaMemcpyHostToDevice, stream));
-    L.lp.table = reinterpret_cast<const PlaneRec*>(d);
+    if (!inline_planes) {
+        uint8_t* h = a.pinned + static_cast<size_t>(slot) * a.slot_bytes;
+        uint8_t* d = a.dev + static_cast<size_t>(slot) * a.slot_bytes;
+        std::memcpy(h, L.recs.data(), bytes);
+        FKB_CUDA(cudaMemcpyAsync(d, h, bytes, cudaMemcpyHostToDevice, stream));
+        L.lp.table = reinterpret_cast<const PlaneRec*>(d);
+    }
+    if (counter) L.lp.work = a.work + 2 * slot;
     rc = run(L, L.lp, stream);
     if (rc != FKB_OK) return rc;
     FKB_CUDA(cudaEventRecord(a.ev[slot], stream));
@@ -667,6 +684,7 @@ int launch_noalloc(const fkb_chain_desc* chain, const fkb_plane_desc* planes, ui
 struct fkb_plan {
     fkb::Lowered L;
     fkb::PlaneRec* table = nullptr;
+    uint32_t* work = nullptr;  // item counters of the staged kernel (launches of one plan are expected not to overlap on the GPU)
     int device = 0;
 };
 
@@ -775,9 +793,14 @@ int fkb_plan_create(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_p
     int rc = lower(chains, n_chains, planes, n_planes, plan->L);
     if (rc != FKB_OK) { delete plan; return rc; }
     cudaError_t e = cudaGetDevice(&plan->device);
+    if (e == cudaSuccess && wants_work_counter(plan->L)) {
+        e = cudaMalloc(reinterpret_cast<void**>(&plan->work), 2 * sizeof(uint32_t));
+        if (e == cudaSuccess) e = cudaMemset(plan->work, 0, 2 * sizeof(uint32_t));
+        plan->L.lp.work = plan->work;
+    }
     if (n_planes <= kInlinePlanes) {
         // a few planes travel in the kernel parameters, as in fkb_launch_transform: no table read before the first tap
-        if (e != cudaSuccess) { t_last_cuda_error = static_cast<int>(e); delete plan; return FKB_ERR_CUDA; }
+        if (e != cudaSuccess) { t_last_cuda_error = static_cast<int>(e); (void)cudaGetLastError(); if (plan->work) cudaFree(plan->work); delete plan; return FKB_ERR_CUDA; }
         std::memcpy(plan->L.lp.inline_planes, plan->L.recs.data(), sizeof(PlaneRec) * n_planes);
         plan->L.lp.table = nullptr;
         *out = plan;
@@ -789,6 +812,7 @@ int fkb_plan_create(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_p
         t_last_cuda_error = static_cast<int>(e);
         (void)cudaGetLastError();
         if (plan->table) cudaFree(plan->table);
+        if (plan->work) cudaFree(plan->work);
         delete plan;
         return FKB_ERR_CUDA;
     }
@@ -809,6 +833,7 @@ int fkb_plan_launch(const fkb_plan* plan, void* cuda_stream) {
 void fkb_plan_destroy(fkb_plan* plan) {
     if (!plan) return;
     if (plan->table) cudaFree(plan->table);
+    if (plan->work) cudaFree(plan->work);
     delete plan;
 }
 

@@ -650,29 +650,41 @@ __global__ void __launch_bounds__(kStagedThreads, 2) staged_kernel(const __grid_
     }
     __syncwarp();
     const uint32_t warps_per_cta = blockDim.x >> 5;
-    // item i runs on warp (i / gridDim.x) % warps_per_cta of CTA i % gridDim.x: a small launch spreads over all SMs
+    // Items are dealt in two ways.  Statically, item i runs on warp (i / gridDim.x) % warps_per_cta of CTA i % gridDim.x
+    // (a small launch spreads over all SMs).  With a work counter (launches of more items than warps), a warp starts on
+    // the item of its own number and then claims further ones from the counter, so that warps whose items were cheap
+    // (small crops, letterbox rows) take more of them.  A claim is issued two items ahead: its latency, and that of the
+    // plane-record fetch that follows it, are hidden behind the items being processed.
     const uint32_t first = warp * gridDim.x + blockIdx.x, stride = gridDim.x * warps_per_cta;
+    const bool dynamic = p.work != nullptr;
     const PlaneRec* table = plane_table(p);
     uint32_t k = 0, k4 = 0;  // steps done so far by RESIZE items (two stages) and by POINT items (four stages)
     bool ok = true;
     // The plane record of the next item is fetched (12 lanes x 16 bytes, into registers) while the current item is
     // processed, so its global-memory latency is off the critical path.
     constexpr uint32_t kRecLanes = sizeof(PlaneRec) / 16;
-    uint32_t local = 0;
+    uint32_t local = 0, claim = 0;
     uint4 rec = make_uint4(0, 0, 0, 0);
     if (first < p.n_tiles) {
         const uint32_t z = tile_to_plane(p, first, local);
         if (lane < kRecLanes) rec = reinterpret_cast<const uint4*>(table + z)[lane];
     }
-    for (uint32_t item = first; item < p.n_tiles && ok; item += stride) {
+    if (dynamic && first < p.n_tiles && lane == 0) claim = atomicAdd(p.work, 1u);
+    for (uint32_t item = first; item < p.n_tiles && ok;) {
         __syncwarp();
         if (lane < kRecLanes) reinterpret_cast<uint4*>(smem_raw + w.base + 48)[lane] = rec;
         __syncwarp();
         const uint32_t cur_local = local;
-        if (item + stride < p.n_tiles) {
-            const uint32_t z = tile_to_plane(p, item + stride, local);
+        uint32_t next_item = item + stride;
+        if (dynamic) {
+            next_item = stride + __shfl_sync(0xffffffffu, claim, 0);  // the claim issued one item ago
+            if (lane == 0) claim = atomicAdd(p.work, 1u);
+        }
+        if (next_item < p.n_tiles) {
+            const uint32_t z = tile_to_plane(p, next_item, local);
             if (lane < kRecLanes) rec = reinterpret_cast<const uint4*>(table + z)[lane];
         }
+        item = next_item;
         const PlaneRec& pl = *w.pl;
         const uint32_t tyi = cur_local / pl.tiles_x, txi = cur_local - tyi * pl.tiles_x;
         const uint32_t ox = txi * pl.tile_w, oy0 = tyi * pl.tile_h;
@@ -693,6 +705,12 @@ __global__ void __launch_bounds__(kStagedThreads, 2) staged_kernel(const __grid_
                       : resize_dispatch<false>(p, w, p.post_kind[pl.chain], ox, oy0, ow, nr, k, lane);
     }
     if (lane == 0) bulk_wait_all();  // shared memory must stay valid until the last bulk store has read it
+    if (dynamic && lane == 0) {
+        // the last warp to finish puts the counters back to zero for the next launch (every claim of this launch,
+        // used or not, was issued before its warp's increment of the second counter)
+        __threadfence();
+        if (atomicAdd(p.work + 1, 1u) == stride - 1u) { p.work[0] = 0u; p.work[1] = 0u; __threadfence(); }
+    }
     if (!ok) {
         // copies announced on the other stages may still be in flight: give them a bounded chance to land
         mbar_wait_bounded(w.bar((k + 1) & 1u), ((k + 1) >> 1) & 1u);

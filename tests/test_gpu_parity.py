@@ -170,6 +170,27 @@ def test_write_yuv_images(fmt):
             check(W.rgb_to_yuv_image(fmt, colour, **size))
 
 
+def test_plan_relaunches_leave_the_item_counters_clean():
+    # a launch with more items than resident warps claims its items from a counter pair that the kernel resets itself:
+    # repeated launches of one plan (and of the same descriptors through the arena) must each produce the full output
+    from fusedkernellibrary_b200 import runtime
+    wl = W.batched_crop_resize(n_frames=4, crops_per_frame=32, w=640, h=360, dst=(224, 224), crop_range=(8, 300))
+    want = oracle.run_oracle(wl, threads=8, fill=FILL)
+    dw = runtime.DeviceWorkload(wl, poison=FILL)
+    dw.plan()
+    for _ in range(5):
+        for t in dw.out:
+            t.fill_(FILL)
+        dw.launch_plan()
+        assert_same(wl, dw.results(), want)
+    for _ in range(6):
+        for t in dw.out:
+            t.fill_(FILL)
+        dw.launch()
+        assert_same(wl, dw.results(), want)
+    dw.close()
+
+
 def test_many_planes_use_the_descriptor_arena():
     # more planes than fit in the kernel parameters: descriptors travel through the pinned/device ring
     wl = W.batched_crop_resize(n_frames=3, crops_per_frame=100, w=320, h=240, dst=(32, 24), crop_range=(4, 100))

@@ -651,7 +651,7 @@ __global__ void __launch_bounds__(kStagedThreads, 2) staged_kernel(const __grid_
     __syncwarp();
     const uint32_t warps_per_cta = blockDim.x >> 5;
     // Items are dealt in two ways.  Statically, item i runs on warp (i / gridDim.x) % warps_per_cta of CTA i % gridDim.x
-    // (a small launch spreads over all SMs).  With a work counter (launches of more items than warps), a warp starts on
+    // (a small launch spreads over all SMs).  With a work counter (launches of many more items than warps), a warp starts on
     // the item of its own number and then claims further ones from the counter, so that warps whose items were cheap
     // (small crops, letterbox rows) take more of them.  A claim is issued two items ahead: its latency, and that of the
     // plane-record fetch that follows it, are hidden behind the items being processed.

@@ -25,15 +25,10 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-METRIC = "fused-pipeline output Gpix/s"
-UNIT = "Gpix/s"
-N_FRAMES, CROPS_PER_FRAME = 64, 32
-FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one staged_kernel launch on this workload, from the ncu capture of the
-# 8-frame case (28.46 MB read + 95.10 MB written for 256 planes; profiles/staged_kernel_batched_crop_resize.md) scaled by
-# planes to the 64-frame launch.  A lower bound: in the small case a third of the output is still in the write-back L2
-# when the kernel ends, at full size all 1.233 GB of output reach DRAM.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = int((28.460032e6 + 95.097600e6) * 8)
+# DRAM bytes of one staged_kernel launch of the 64-frame workload: dram__bytes_read.sum + dram__bytes_write.sum of one ncu
+# capture of the full-size launch (259.25 MB read + 1 179.92 MB written; profiles/staged_kernel_batched_crop_resize.md),
+# against 1 436.77 MB of algorithmic bytes.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = int(259.252224e6 + 1179.918e6)
 
 
 def make_workload(rank: int, n_frames: int = N_FRAMES, frame_w: int = 1920, frame_h: int = 1080):

@@ -25,6 +25,10 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+METRIC = "fused-pipeline output Gpix/s"
+UNIT = "Gpix/s"
+N_FRAMES, CROPS_PER_FRAME = 64, 32
+FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes of one staged_kernel launch of the 64-frame workload: dram__bytes_read.sum + dram__bytes_write.sum of one ncu
 # capture of the full-size launch (259.25 MB read + 1 179.92 MB written; profiles/staged_kernel_batched_crop_resize.md),
 # against 1 436.77 MB of algorithmic bytes.

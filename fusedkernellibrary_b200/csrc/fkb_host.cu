@@ -152,7 +152,6 @@ int validate(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_de
 // -------------------------------------------------------------------------------------------------------
 // lowering
 // -------------------------------------------------------------------------------------------------------
-inline uint32_t up16(uint32_t v) { return (v + 15u) & ~15u; }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 // FKB_FORCE_GATHER=1 (read at every launch) routes every plane through gather_kernel: a debugging aid that lets
@@ -270,7 +269,8 @@ PostImm post_imm_of(const fkb_chain_desc& ch) {
 }
 
 struct Lowered {
-    std::vector<PlaneRec> recs;
+    PlaneRec* recs = nullptr;        // one record per plane: the caller's fixed array, or `storage`
+    std::vector<PlaneRec> storage;   // used only when the caller gave no array (never by the no-allocation entry point)
     LaunchParams lp;
     uint32_t staged_grid = 0;
     uint32_t lut_grid = 0;
@@ -307,7 +307,7 @@ int status_word(int** out) {
 int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc* planes, uint32_t n_planes, Lowered& L) {
     const int rc = validate(chains, n_chains, planes, n_planes);
     if (rc != FKB_OK) return rc;
-    L.recs.resize(n_planes);
+    if (!L.recs) { L.storage.resize(n_planes); L.recs = L.storage.data(); }
     std::memset(&L.lp, 0, sizeof(L.lp));
     std::memcpy(L.lp.chains, chains, sizeof(fkb_chain_desc) * n_chains);
     uint32_t n_tiles = 0, gw = 0, gh = 0, n_gather = 0;
@@ -525,7 +525,7 @@ int launch_once(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane
     if (rc != FKB_OK) return rc;
     const bool inline_planes = n_planes <= kInlinePlanes, counter = wants_work_counter(L);
     if (inline_planes) {
-        std::memcpy(L.lp.inline_planes, L.recs.data(), sizeof(PlaneRec) * n_planes);
+        std::memcpy(L.lp.inline_planes, L.recs, sizeof(PlaneRec) * n_planes);
         L.lp.table = nullptr;
         if (!counter) return run(L, L.lp, stream);
     }
@@ -541,7 +541,7 @@ int launch_once(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane
     if (!inline_planes) {
         uint8_t* h = a.pinned + static_cast<size_t>(slot) * a.slot_bytes;
         uint8_t* d = a.dev + static_cast<size_t>(slot) * a.slot_bytes;
-        std::memcpy(h, L.recs.data(), bytes);
+        std::memcpy(h, L.recs, bytes);
         FKB_CUDA(cudaMemcpyAsync(d, h, bytes, cudaMemcpyHostToDevice, stream));
         L.lp.table = reinterpret_cast<const PlaneRec*>(d);
     }
@@ -572,83 +572,6 @@ NoAllocState& noalloc_state() {
 }
 
 // The lowering of lower(), writing into a caller-provided array instead of a growing vector.
-int lower_fixed(const fkb_chain_desc* chain, const fkb_plane_desc* planes, uint32_t n_planes, PlaneRec* recs,
-                LaunchParams& lp, uint32_t& staged_grid, uint32_t& lut_grid, dim3& gather_grid) {
-    const int rc = validate(chain, 1, planes, n_planes);
-    if (rc != FKB_OK) return rc;
-    std::memset(&lp, 0, sizeof(lp));
-    lp.chains[0] = *chain;
-    int sms = 0;
-    {
-        const int e = device_sm_count(sms);
-        if (e != FKB_OK) return e;
-    }
-    uint64_t row_segments = 0, lut_rows = 0;
-    uint32_t lut_min_tiles_x = 0xffffffffu;
-    for (uint32_t z = 0; z < n_planes; ++z) {
-        const fkb_plane_desc& s = planes[z];
-        PlaneRec& r = recs[z];
-        std::memset(&r, 0, sizeof(r));
-        r.src = static_cast<const uint8_t*>(s.src);
-        r.src_chroma = static_cast<const uint8_t*>(s.src_chroma);
-        r.dst = static_cast<uint8_t*>(s.dst);
-        if (chain->write_kind == FKB_WRITE_NV12 || chain->write_kind == FKB_WRITE_NV21) {
-            r.dst_cstride = static_cast<uint64_t>(static_cast<const uint8_t*>(s.dst_y) - static_cast<const uint8_t*>(s.dst));
-        } else if (chain->write_kind == FKB_WRITE_SPLIT_PLANES) {
-            r.dst_cstride = static_cast<uint64_t>(static_cast<const uint8_t*>(s.dst_y) - static_cast<const uint8_t*>(s.dst));
-            r.dst_cstride2 = static_cast<uint64_t>(static_cast<const uint8_t*>(s.dst_z) - static_cast<const uint8_t*>(s.dst));
-        } else {
-            r.dst_cstride = s.dst_channel_stride; r.dst_cstride2 = 2 * s.dst_channel_stride;
-        }
-        r.src_pitch = s.src_pitch; r.src_w = s.src_w; r.src_h = s.src_h;
-        r.crop_x = s.crop_x; r.crop_y = s.crop_y; r.crop_w = s.crop_w; r.crop_h = s.crop_h;
-        r.dst_w = s.dst_w; r.dst_h = s.dst_h; r.dst_pitch = s.dst_pitch;
-        r.fx = s.fx; r.fy = s.fy; r.x1 = s.x1; r.y1 = s.y1; r.x2 = s.x2; r.y2 = s.y2;
-        std::memcpy(r.bg, s.bg, sizeof(r.bg));
-        r.chain = 0;
-        std::memcpy(r.params, s.params, sizeof(r.params));
-        classify(*chain, r);
-        if (r.kclass == KCLASS_NV12) r.kclass = KCLASS_GATHER;  // this entry point keeps to the three general-purpose kernels
-        if (r.kclass == KCLASS_POINT || r.kclass == KCLASS_RESIZE) row_segments += static_cast<uint64_t>(r.tiles_x) * r.dst_h;
-        if (r.kclass == KCLASS_LUT) { lut_rows += r.dst_h; lut_min_tiles_x = std::min(lut_min_tiles_x, r.tiles_x); }
-    }
-    const uint32_t rpi = rows_per_item(row_segments, 2u * kStagedWarps * static_cast<uint32_t>(sms));
-    const uint32_t lut_rpu = lut_rows ? std::max<uint32_t>(static_cast<uint32_t>((lut_rows + 1ull * kLutCtasPerSm * sms - 1) / (1ull * kLutCtasPerSm * sms)),
-                                                           (kLutWarps + lut_min_tiles_x - 1) / lut_min_tiles_x) : 1u;
-    uint32_t n_tiles = 0, n_lut_units = 0, n_gather = 0, gw = 0, gh = 0, first_count = 0;
-    bool uniform = true;
-    for (uint32_t z = 0; z < n_planes; ++z) {
-        PlaneRec& r = recs[z];
-        r.lut_base = n_lut_units;
-        if (r.kclass == KCLASS_LUT) {
-            r.tile_h = std::min(r.dst_h, lut_rpu);
-            n_lut_units += (r.dst_h + r.tile_h - 1) / r.tile_h;
-        } else if (r.kclass != KCLASS_GATHER) {
-            r.tile_h = std::min(r.dst_h, rpi);
-        }
-        r.tile_base = n_tiles;
-        const uint32_t count = (r.kclass == KCLASS_POINT || r.kclass == KCLASS_RESIZE) ? r.tiles_x * ((r.dst_h + r.tile_h - 1) / r.tile_h) : 0u;
-        if (z == 0) first_count = count; else if (count != first_count) uniform = false;
-        if (static_cast<uint64_t>(n_tiles) + count > 0xfffffff0ull) return FKB_ERR_TOO_LARGE;
-        n_tiles += count;
-        if (r.kclass == KCLASS_GATHER) { ++n_gather; gw = std::max(gw, r.dst_w); gh = std::max(gh, r.dst_h); }
-    }
-    lp.n_planes = n_planes;
-    lp.neg_zero = -0.0f;
-    lp.post_kind[0] = post_kind_of(*chain);
-    lp.post_imm[0] = post_imm_of(*chain);
-    uint32_t reorders = 0;
-    for (uint32_t i = 0; i < chain->n_ops; ++i) reorders += chain->ops[i].code == FKB_OP_REORDER_ZYX;
-    lp.lut_swap = reorders & 1u;
-    lp.n_tiles = n_tiles;
-    lp.tiles_per_plane = (uniform && first_count) ? first_count : 0;
-    lp.n_lut_units = n_lut_units;
-    staged_grid = n_tiles ? std::min<uint32_t>(n_tiles, 2u * static_cast<uint32_t>(sms)) : 0u;
-    lut_grid = n_lut_units ? std::min<uint32_t>(n_lut_units, kLutCtasPerSm * static_cast<uint32_t>(sms)) : 0u;
-    gather_grid = n_gather ? dim3((gw + 127) / 128, (gh + 7) / 8, std::min<uint32_t>(n_planes, 65535u)) : dim3(0, 0, 0);
-    return status_word(&lp.status);
-}
-
 int launch_noalloc(const fkb_chain_desc* chain, const fkb_plane_desc* planes, uint32_t n_planes, cudaStream_t stream) {
     if (!chain || !planes) return FKB_ERR_NULL;
     if (n_planes > FKB_NOALLOC_MAX_PLANES) return FKB_ERR_TOO_LARGE;  // the fixed table holds no more
@@ -665,19 +588,16 @@ int launch_noalloc(const fkb_chain_desc* chain, const fkb_plane_desc* planes, ui
         FKB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_table));
         st.device_table[dev] = ptr;
     }
-    LaunchParams lp;
-    uint32_t staged_grid = 0, lut_grid = 0;
-    dim3 gather_grid(0, 0, 0);
-    const int rc = lower_fixed(chain, planes, n_planes, st.host_recs, lp, staged_grid, lut_grid, gather_grid);
+    // the same lowering as every other launch, writing its records into the fixed host array (no container grows)
+    Lowered L;
+    L.recs = st.host_recs;
+    const int rc = lower(chain, 1, planes, n_planes, L);
     if (rc != FKB_OK) return rc;
     // Every record the kernels will read is rewritten by this copy; nothing in the table has to start at zero.  The
     // source is pageable memory, so the call returns only after the records have left st.host_recs.
     FKB_CUDA(cudaMemcpyAsync(st.device_table[dev], st.host_recs, sizeof(PlaneRec) * n_planes, cudaMemcpyHostToDevice, stream));
-    lp.table = st.device_table[dev];
-    if (staged_grid) FKB_CUDA(launch_staged(lp, staged_grid, stream));
-    if (lut_grid) FKB_CUDA(launch_lut(lp, lut_grid, stream));
-    if (gather_grid.x) FKB_CUDA(launch_gather(lp, gather_grid, 4, stream));
-    return FKB_OK;
+    L.lp.table = st.device_table[dev];
+    return run(L, L.lp, stream);  // (no work counter: items are dealt round-robin)
 }
 
 }  // namespace
@@ -803,13 +723,13 @@ int fkb_plan_create(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_p
     if (n_planes <= kInlinePlanes) {
         // a few planes travel in the kernel parameters, as in fkb_launch_transform: no table read before the first tap
         if (e != cudaSuccess) { t_last_cuda_error = static_cast<int>(e); (void)cudaGetLastError(); if (plan->work) cudaFree(plan->work); delete plan; return FKB_ERR_CUDA; }
-        std::memcpy(plan->L.lp.inline_planes, plan->L.recs.data(), sizeof(PlaneRec) * n_planes);
+        std::memcpy(plan->L.lp.inline_planes, plan->L.recs, sizeof(PlaneRec) * n_planes);
         plan->L.lp.table = nullptr;
         *out = plan;
         return FKB_OK;
     }
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&plan->table), sizeof(PlaneRec) * n_planes);
-    if (e == cudaSuccess) e = cudaMemcpy(plan->table, plan->L.recs.data(), sizeof(PlaneRec) * n_planes, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy(plan->table, plan->L.recs, sizeof(PlaneRec) * n_planes, cudaMemcpyHostToDevice);
     if (e != cudaSuccess) {
         t_last_cuda_error = static_cast<int>(e);
         (void)cudaGetLastError();

@@ -57,7 +57,7 @@ int check_ops(const fkb_chain_desc& ch, uint32_t first, uint32_t last, ValueType
 
 int check_chain(const fkb_chain_desc& ch) {
     if (ch.src_format != FKB_PIX_U8C3 && ch.src_format != FKB_PIX_NV12 && ch.src_format != FKB_PIX_NV21 &&
-        ch.src_format != FKB_PIX_UYVY) return FKB_ERR_UNSUPPORTED;
+        ch.src_format != FKB_PIX_UYVY && ch.src_format != FKB_PIX_U8C4) return FKB_ERR_UNSUPPORTED;
     if (ch.dst_format != FKB_PIX_U8C3 && ch.dst_format != FKB_PIX_F32C3) return FKB_ERR_UNSUPPORTED;
     if (ch.geometry > FKB_GEOM_RESIZE_PRESERVE_AR_LEFT) return FKB_ERR_UNSUPPORTED;
     if (ch.write_kind < FKB_WRITE_PACKED || ch.write_kind > FKB_WRITE_UYVY) return FKB_ERR_UNSUPPORTED;
@@ -87,7 +87,8 @@ int check_plane(const fkb_chain_desc& ch, const fkb_plane_desc& pl) {
         if (nv12 && !pl.src_chroma) return FKB_ERR_NULL;
         if (pl.src_w == 0 || pl.src_h == 0) return FKB_ERR_INVALID;
         const uint64_t src_row = nv12 ? ((static_cast<uint64_t>(pl.src_w) + 1) / 2) * 2
-                                 : uyvy ? ((static_cast<uint64_t>(pl.src_w) + 1) / 2) * 4 : static_cast<uint64_t>(pl.src_w) * 3;
+                                 : uyvy ? ((static_cast<uint64_t>(pl.src_w) + 1) / 2) * 4
+                                 : static_cast<uint64_t>(pl.src_w) * (ch.src_format == FKB_PIX_U8C4 ? 4 : 3);
         if (pl.src_pitch < src_row) return FKB_ERR_INVALID;
         if (pl.crop_w <= 0 || pl.crop_h <= 0) return FKB_ERR_INVALID;
         if (ch.border) {

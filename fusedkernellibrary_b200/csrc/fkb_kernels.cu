@@ -43,6 +43,11 @@ __device__ __forceinline__ void read_frame_global(const fkb_chain_desc& ch, cons
         o[0] = static_cast<float>(__ldg(g + 1 + 2 * (X & 1)));
         o[1] = static_cast<float>(__ldg(g));
         o[2] = static_cast<float>(__ldg(g + 2));
+    } else if (ch.src_format == FKB_PIX_U8C4) {
+        const uint8_t* q = pl.src + Y * pl.src_pitch + X * 4;  // the alpha byte is not read
+        o[0] = static_cast<float>(__ldg(q));
+        o[1] = static_cast<float>(__ldg(q + 1));
+        o[2] = static_cast<float>(__ldg(q + 2));
     } else {
         const uint8_t* q = pl.src + Y * pl.src_pitch + X * 3;
         o[0] = static_cast<float>(__ldg(q));

@@ -134,7 +134,7 @@ class Workload:
             nv12 = ch.src_format in (abi.PIX_NV12, abi.PIX_NV21) or uyvy  # one luma byte per pixel, one chroma pair per 2 (x2) pixels
             elt = 12 if ch.dst_format == abi.PIX_F32C3 else 3
             out_bytes += s.dst_w * s.dst_h * elt
-            if s.default or ch.border:
+            if s.default or ch.border or ch.src_format == abi.PIX_U8C4:
                 continue
             if s.src not in masks:
                 masks[s.src] = (np.zeros((s.src_h, s.src_w), bool),
@@ -296,6 +296,19 @@ def rgb_to_yuv_image(fmt=abi.PIX_NV12, colour=(abi.RANGE_FULL, abi.PRIMITIVES_BT
     planes = [PlaneSpec(0, 0, 0, w, h, pitch, (0, 0, w, h), w, h, opitch, dst_planes=() if uyvy else (opitch * h, 0))]
     return Workload("rgb_to_yuv_image", [ch], [_frame(seed, pitch * h)], [size], planes, f"RGB -> format {fmt} colour {colour}",
                     extra={"fmt": fmt, "colour": colour})
+
+
+def bgra_crops(swap=False, w=320, h=200, dst=(96, 80), seed=18) -> Workload:
+    """Four uchar4 frames -> Crop -> Resize IGNORE_AR -> alpha discarded (BGRA2BGR, or BGRA2RGB with ``swap``) -> Mul ->
+    TensorWrite<float3>."""
+    pitch = _pitch(w * 4, 16)
+    dw, dh = dst
+    ops = ([op(abi.OP_REORDER_ZYX)] if swap else []) + [op(abi.OP_MUL, (0.5, 1.0, 2.0))]
+    ch = chain(abi.PIX_U8C4, abi.GEOM_RESIZE_IGNORE_AR, abi.PIX_F32C3, abi.WRITE_PACKED, ops)
+    rects = [(0, 0, w, h), (10, 20, 100, 60), (w - 37, h - 21, 37, 21), (5, 5, 8, 9)]
+    planes = [PlaneSpec(i, 0, i * dw * dh * 12, w, h, pitch, r, dw, dh, dw * 12) for i, r in enumerate(rects)]
+    return Workload("bgra_crops", [ch], [_frame(seed + i, pitch * h) for i in range(4)], [4 * dw * dh * 12], planes,
+                    "uchar4 frames, alpha discarded" + (" swap" if swap else ""), extra={"swap": swap, "rects": rects})
 
 
 def conditional_resize(used=5, w=320, h=180, dst=(96, 64), default=(7, 200, 33), seed=11) -> Workload:

@@ -62,7 +62,12 @@ enum {
 enum { FKB_PIX_U8C3 = 1, FKB_PIX_F32C3 = 2, FKB_PIX_NV12 = 3,
        /* two more 8-bit sources of ReadYUV (color_conversion.h:240-268): NV21 is NV12 with the chroma bytes in the
         * order V,U; UYVY is one plane of 4-byte groups U Y0 V Y1 (two pixels), 2*width bytes per row, no src_chroma */
-       FKB_PIX_NV21 = 4, FKB_PIX_UYVY = 5 };
+       FKB_PIX_NV21 = 4, FKB_PIX_UYVY = 5,
+       /* a uchar4 source (PerThreadRead<_2D,uchar4>) of which the first three channels enter the chain: the alpha
+        * channel is dropped, as ColorConversion<COLOR_BGRA2BGR | COLOR_RGBA2RGB> = Discard does (color_conversion.h:448-452;
+        * with the BGRA2RGB / RGBA2BGR codes, :460-464, the chain also carries FKB_OP_REORDER_ZYX).  Where in the chain the
+        * reference discards the channel does not change the other three: every op here acts per channel. */
+       FKB_PIX_U8C4 = 6 };
 
 /* Geometry of the ReadBack stage.  The crop rectangle is always applied (a chain without Crop
  * passes the whole frame as the rectangle).  NONE: output pixel (x,y) reads crop pixel (x,y).

@@ -195,7 +195,16 @@ template <typename DPPType, typename... Args>
 inline void executeOperations(Stream_<DPPType::PAR_ARCH>& stream, const Args&... args) {
     Executor<DPPType>::executeOperations(stream, args...);
 }
-// the batch conveniences of core/execution_model/executors.h:80-114
+// the conveniences of core/execution_model/executors.h:67-78 (one source, optionally one destination) ...
+template <typename DPPType, ND D, typename I, typename... IOps>
+inline void executeOperations(const Ptr<D, I>& input, Stream_<DPPType::PAR_ARCH>& stream, const IOps&... iOps) {
+    Executor<DPPType>::executeOperations(stream, PerThreadRead<D, I>::build(input), iOps...);
+}
+template <typename DPPType, ND D, typename I, typename O, typename... IOps>
+inline void executeOperations(const Ptr<D, I>& input, const Ptr<D, O>& output, Stream_<DPPType::PAR_ARCH>& stream, const IOps&... iOps) {
+    Executor<DPPType>::executeOperations(stream, PerThreadRead<D, I>::build(input), iOps..., PerThreadWrite<D, O>::build(output));
+}
+// ... and the batch conveniences of :80-114
 template <typename DPPType, typename I, size_t BATCH, typename... IOps>
 inline void executeOperations(const std::array<Ptr2D<I>, BATCH>& input, const int& activeBatch, const I& defaultValue,
                               Stream_<DPPType::PAR_ARCH>& stream, const IOps&... iOps) {

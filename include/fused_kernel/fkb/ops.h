@@ -28,7 +28,8 @@ enum class AspectRatio { PRESERVE_AR = 0, IGNORE_AR = 1, PRESERVE_AR_RN_EVEN = 2
 // border_reader.h:25-36
 enum class BorderType : int { CONSTANT = 0, REPLICATE = 1, REFLECT = 2, WRAP = 3, REFLECT_101 = 4, TRANSPARENT_ = 5, DEFAULT = REFLECT_101, ISOLATED = 16 };
 enum class PlanePolicy { PROCESS_ALL = 0, CONDITIONAL_WITH_DEFAULT = 1 };  // batch_operations.h:75
-enum class ColorConversionCodes { COLOR_BGR2RGB, COLOR_RGB2BGR };
+// (color_conversion.h:408-426; the codes that discard the alpha channel of a four-channel source are the ones beside BGR<->RGB)
+enum class ColorConversionCodes { COLOR_BGR2RGB, COLOR_RGB2BGR, COLOR_BGRA2BGR, COLOR_RGBA2RGB, COLOR_BGRA2RGB, COLOR_RGBA2BGR };
 
 namespace detail {
 struct SrcPlane { const void* data{nullptr}; uint pitch{0}, w{0}, h{0}; };
@@ -79,15 +80,16 @@ template <uint16_t C, typename I, typename O> constexpr bool isComputeIOp<Comput
 
 template <typename I, typename O>
 struct Cast {
-    static_assert(std::is_same_v<I, uchar3> && std::is_same_v<O, float3>, "the B200 kernels implement Cast<uchar3,float3>");
+    static_assert((std::is_same_v<I, uchar3> && std::is_same_v<O, float3>) || (std::is_same_v<I, uchar4> && std::is_same_v<O, float4>),
+                  "the B200 kernels implement Cast<uchar3,float3> (and Cast<uchar4,float4> ahead of a discarded alpha channel)");
     static constexpr auto build() { return ComputeIOp<FKB_OP_CAST_F32, I, O>{}; }
 };
 #define FKB_BINARY_OP(Name, CODE)                                                                                     \
     template <typename I, typename P = I, typename O = I>                                                             \
     struct Name {                                                                                                     \
-        static_assert(std::is_same_v<I, float3> && std::is_same_v<P, float3> && std::is_same_v<O, float3>,            \
-                      "the B200 kernels implement " #Name "<float3>");                                                \
-        static constexpr auto build(const float3& params) { return ComputeIOp<CODE, I, O>{params}; }                  \
+        static_assert((std::is_same_v<I, float3> || std::is_same_v<I, float4>) && std::is_same_v<P, I> && std::is_same_v<O, I>,      \
+                      "the B200 kernels implement " #Name "<float3> (and " #Name "<float4> ahead of a discarded alpha channel)");   \
+        static constexpr auto build(const I& params) { return ComputeIOp<CODE, I, O>{float3{params.x, params.y, params.z}}; }     \
     };
 FKB_BINARY_OP(Mul, FKB_OP_MUL)
 FKB_BINARY_OP(Add, FKB_OP_ADD)
@@ -99,11 +101,25 @@ struct SaturateCast {
     static_assert(std::is_same_v<I, float3> && std::is_same_v<O, uchar3>, "the B200 kernels implement SaturateCast<float3,uchar3>");
     static constexpr auto build() { return ComputeIOp<FKB_OP_SATCAST_U8, I, O>{}; }
 };
+// A step of a chain that changes the pixel type without arithmetic (the alpha channel of a uchar4 / float4 is dropped)
+template <typename I, typename O>
+struct RetypeIOp {
+    using InputType = I;
+    using OutputType = O;
+    bool reorder;  // BGRA2RGB / RGBA2BGR: the remaining channels are also reversed
+};
 template <ColorConversionCodes CODE, typename I, typename O = I>
 struct ColorConversion {
-    static_assert(std::is_same_v<I, O> && (std::is_same_v<I, float3> || std::is_same_v<I, uchar3>),
-                  "BGR<->RGB on uchar3 or float3 is the colour conversion the B200 kernels implement");
-    static constexpr auto build() { return ComputeIOp<FKB_OP_REORDER_ZYX, I, O>{}; }
+    static constexpr bool swap3 = CODE == ColorConversionCodes::COLOR_BGR2RGB || CODE == ColorConversionCodes::COLOR_RGB2BGR;
+    static constexpr bool drop = !swap3;
+    static_assert(!swap3 || (std::is_same_v<I, O> && (std::is_same_v<I, float3> || std::is_same_v<I, uchar3>)),
+                  "BGR<->RGB on uchar3 or float3 is the three-channel colour conversion the B200 kernels implement");
+    static_assert(!drop || (std::is_same_v<I, uchar4> && std::is_same_v<O, uchar3>) || (std::is_same_v<I, float4> && std::is_same_v<O, float3>),
+                  "BGRA2BGR / RGBA2RGB / BGRA2RGB / RGBA2BGR take uchar4 -> uchar3 or float4 -> float3");
+    static constexpr auto build() {
+        if constexpr (swap3) return ComputeIOp<FKB_OP_REORDER_ZYX, I, O>{};
+        else return RetypeIOp<I, O>{CODE == ColorConversionCodes::COLOR_BGRA2RGB || CODE == ColorConversionCodes::COLOR_RGBA2BGR};
+    }
 };
 // YCbCr -> RGB: the matrix and offsets of <range, primitives> as the reference evaluates them in fp32
 // (algorithms/image_processing/itu_color.h:185-258, color_conversion.h:150-174), from fkb_ycbcr_to_rgb.
@@ -241,7 +257,14 @@ struct ReadIOp {
         s.has_resize = true; s.ar = r.ar; s.dst_size = r.dst_size;
         s.bg[0] = r.bg.x; s.bg[1] = r.bg.y; s.bg[2] = r.bg.z;
         s.n_pre_ops = s.ops.size();
-        return ReadIOp<float3, BATCH>(std::move(s));  // the interpolation returns float_<cn>
+        return ReadIOp<std::conditional_t<cn<OutT> == 4, float4, float3>, BATCH>(std::move(s));  // the interpolation returns float_<cn>
+    }
+    template <typename I, typename O>
+    auto then(const RetypeIOp<I, O>& r) const {
+        static_assert(std::is_same_v<I, OutT>, "the operation's InputType is not the OutputType of the operation before it");
+        detail::ReadState s = st;
+        if (r.reorder) s.ops.push_back(detail::OpRec{FKB_OP_REORDER_ZYX, {{0.f, 0.f, 0.f}}});
+        return ReadIOp<O, BATCH>(std::move(s));
     }
     template <uint16_t C, typename I, typename O>
     auto then(const ComputeIOp<C, I, O>& op) const {
@@ -264,9 +287,12 @@ template <typename O, size_t B> constexpr bool isReadIOp<ReadIOp<O, B>> = true;
 
 template <ND D, typename T>
 struct PerThreadRead {
-    static_assert(D == ND::_2D && std::is_same_v<T, uchar3>, "PerThreadRead<ND::_2D, uchar3> is the read the B200 kernels implement");
+    static_assert(D == ND::_2D && (std::is_same_v<T, uchar3> || std::is_same_v<T, uchar4>),
+                  "PerThreadRead<ND::_2D, uchar3> (and uchar4, whose alpha channel the chain must discard) are the reads the B200 kernels implement");
+    static constexpr uint32_t fmt = std::is_same_v<T, uchar4> ? FKB_PIX_U8C4 : FKB_PIX_U8C3;
     static auto build(const RawPtr<ND::_2D, T>& p) {
         detail::ReadState s;
+        s.src_format = fmt;
         s.src.push_back({p.data, p.dims.pitch, p.dims.width, p.dims.height});
         return ReadIOp<T, 0>(std::move(s));
     }
@@ -274,6 +300,7 @@ struct PerThreadRead {
     template <size_t N>
     static auto build(const std::array<Ptr2D<T>, N>& ptrs) {
         detail::ReadState s;
+        s.src_format = fmt;
         for (const auto& p : ptrs) { const auto r = p.ptr(); s.src.push_back({r.data, r.dims.pitch, r.dims.width, r.dims.height}); }
         return ReadIOp<T, N>(std::move(s));
     }

@@ -64,6 +64,8 @@ template <typename T> struct VectorTraits { using base = T; static constexpr int
 template <> struct VectorTraits<uchar3> { using base = uchar; static constexpr int cn = 3; };
 template <> struct VectorTraits<float3> { using base = float; static constexpr int cn = 3; };
 template <> struct VectorTraits<uchar2> { using base = uchar; static constexpr int cn = 2; };
+template <> struct VectorTraits<uchar4> { using base = uchar; static constexpr int cn = 4; };
+template <> struct VectorTraits<float4> { using base = float; static constexpr int cn = 4; };
 template <typename T> using VBase = typename VectorTraits<T>::base;
 template <typename T> constexpr int cn = VectorTraits<T>::cn;
 
@@ -71,7 +73,8 @@ template <typename T, typename... A>
 constexpr T make_(A... a) { return T{static_cast<VBase<T>>(a)...}; }
 template <typename T>
 constexpr T make_set(VBase<T> v) {
-    if constexpr (cn<T> == 3) return T{v, v, v};
+    if constexpr (cn<T> == 4) return T{v, v, v, v};
+    else if constexpr (cn<T> == 3) return T{v, v, v};
     else if constexpr (cn<T> == 2) return T{v, v};
     else return T{v};
 }

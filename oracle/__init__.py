@@ -75,6 +75,8 @@ def load_ref() -> C.CDLL:
         lib.fklref_rgb_to_ycbcr_matrix.argtypes = [C.c_int, C.c_int, f32p]
         lib.fklref_rgb_to_yuv_image.restype = C.c_int
         lib.fklref_rgb_to_yuv_image.argtypes = [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int]
+        lib.fklref_bgra_crop_resize_f32.restype = C.c_int
+        lib.fklref_bgra_crop_resize_f32.argtypes = [pp, C.c_int, C.c_int, C.c_int, i32p, C.c_int, C.c_int, f32p, C.c_int, C.c_void_p]
         lib.fklref_resize_split_planes.restype = C.c_int
         lib.fklref_resize_split_planes.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, f32p, C.c_int, C.c_void_p,
                                                    C.c_void_p, C.c_void_p, C.c_int]
@@ -218,6 +220,10 @@ def run_ref(wl, threads: int = 1):
                                          outs[0].ctypes.data, p0.dst_pitch)
         if rc == -1:
             raise ValueError("the reference runner has no instantiation for this format / range / primitives")
+    elif wl.name == "bgra_crops":
+        flat = [v for r in wl.extra["rects"] for v in r]
+        rc = lib.fklref_bgra_crop_resize_f32(frame_ptrs(wl.planes), p0.src_w, p0.src_h, p0.src_pitch, (C.c_int32 * 16)(*flat),
+                                             p0.dst_w, p0.dst_h, _f3(ch.ops[ch.n_ops - 1].v), 1 if wl.extra["swap"] else 0, outs[0].ctypes.data)
     elif wl.name == "split_planes":
         base = outs[0].ctypes.data
         rc = lib.fklref_resize_split_planes(wl.sources[0].ctypes.data, p0.src_w, p0.src_h, p0.src_pitch, p0.dst_w, p0.dst_h,

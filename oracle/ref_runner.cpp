@@ -167,6 +167,23 @@ static void letterbox_params(const Read& read, int dw, int dh, float* f2, int32_
     r4[0] = r.params.x1; r4[1] = r.params.y1; r4[2] = r.params.x2; r4[3] = r.params.y2;
 }
 
+// Four uchar4 frames -> Crop -> Resize(IGNORE_AR) on float4 -> ColorConversion<BGRA2BGR | BGRA2RGB, float4, float3> ->
+// Mul<float3> -> TensorWrite<float3>: the alpha channel is discarded after the interpolation.
+template <ColorConversionCodes CODE>
+static int bgra_crop_resize(const uint8_t* const* frames, int w, int h, int pitch, const int32_t* rects, int dw, int dh, const float* mul, float* out) {
+    CpuStream stream;
+    std::array<Ptr2D<uchar4>, 4> ptrs; std::array<Rect, 4> rs;
+    for (size_t i = 0; i < 4; ++i) {
+        ptrs[i] = Ptr2D<uchar4>(reinterpret_cast<uchar4*>(const_cast<uint8_t*>(frames[i])), w, h, pitch, MemType::Host, 0);
+        rs[i] = Rect(rects[4 * i], rects[4 * i + 1], rects[4 * i + 2], rects[4 * i + 3]);
+    }
+    Tensor<float3> t(reinterpret_cast<float3*>(out), dw, dh, 4, 1, MemType::Host, 0);
+    executeOperations<CpuDPP>(stream, PerThreadRead<ND::_2D, uchar4>::build(ptrs), Crop<>::build(rs),
+        Resize<InterpolationType::INTER_LINEAR, AspectRatio::IGNORE_AR>::build(Size(dw, dh)), ColorConversion<CODE, float4, float3>::build(),
+        Mul<float3>::build(make_<float3>(mul[0], mul[1], mul[2])), TensorWrite<float3>::build(t));
+    return 0;
+}
+
 extern "C" {
 
 int fklref_crop_resize_u8(const uint8_t* const* frames, int w, int h, int pitch, const int32_t* rects, int n,
@@ -240,6 +257,12 @@ int fklref_resize_split_planes(const uint8_t* frame, int w, int h, int pitch, in
         executeOperations<CpuDPP>(stream, read, resize, m, SaturateCast<float3, uchar3>::build(), SplitWrite<ND::_2D, uchar3>::build(out));
     }
     return 0;
+}
+
+int fklref_bgra_crop_resize_f32(const uint8_t* const* frames, int w, int h, int pitch, const int32_t* rects, int dw, int dh, const float* mul,
+                                int swap, float* out) {
+    return swap ? bgra_crop_resize<ColorConversionCodes::COLOR_BGRA2RGB>(frames, w, h, pitch, rects, dw, dh, mul, out)
+                : bgra_crop_resize<ColorConversionCodes::COLOR_BGRA2BGR>(frames, w, h, pitch, rects, dw, dh, mul, out);
 }
 
 // Four frames -> Resize(IGNORE_AR) -> Mul -> TensorTSplit<float3> into a colour-plane-transposed tensor

@@ -299,6 +299,43 @@ static void test_border(const char* what) {
     report(what, std::memcmp(want.data(), out.ptrPinned().data, want.size() * 4) == 0);
 }
 
+// ---- a uchar4 (BGRA) frame: crops, resize on float4, alpha discarded with BGRA2RGB, normalise ---------------------------------
+static void test_bgra_source() {
+    Stream stream;
+    Ptr2D<uchar4> input(320, 200);
+    {
+        const auto h = input.ptrPinned();
+        std::mt19937 rng(800);
+        for (uint y = 0; y < 200; ++y) for (uint x = 0; x < 320 * 4; ++x) reinterpret_cast<uint8_t*>(h.data)[y * h.dims.pitch + x] = rng() & 255;
+    }
+    input.upload(stream);
+    constexpr size_t BATCH = 3;
+    const std::array<Rect, BATCH> crops{Rect(0, 0, 120, 40), Rect(100, 100, 60, 40), Rect(290, 170, 30, 30)};
+    Tensor<float3> out(64, 64, BATCH);
+    executeOperations<TransformDPP<>>(input, stream, Crop<>::build(crops), Resize<InterpolationType::INTER_LINEAR>::build(Size(64, 64)),
+                                      Mul<float4>::build(make_set<float4>(1.f / 255.f)),
+                                      ColorConversion<ColorConversionCodes::COLOR_BGRA2RGB, float4, float3>::build(),
+                                      Add<float3>::build(make_<float3>(0.5f, 0.25f, 0.125f)), TensorWrite<float3>::build(out));
+    out.download(stream);
+    stream.sync();
+    fkb_chain_desc ch{};
+    ch.src_format = FKB_PIX_U8C4; ch.geometry = FKB_GEOM_RESIZE_IGNORE_AR; ch.dst_format = FKB_PIX_F32C3; ch.write_kind = FKB_WRITE_PACKED;
+    ch.n_ops = 3; ch.ops[0] = op(FKB_OP_MUL, 1.f / 255.f, 1.f / 255.f, 1.f / 255.f); ch.ops[1] = op(FKB_OP_REORDER_ZYX); ch.ops[2] = op(FKB_OP_ADD, 0.5f, 0.25f, 0.125f);
+    std::vector<float> want(64 * 64 * 3 * BATCH);
+    std::vector<fkb_plane_desc> planes;
+    const auto r = input.ptrPinned();
+    for (size_t i = 0; i < BATCH; ++i) {
+        fkb_plane_desc d{};
+        d.src = r.data; d.src_pitch = r.dims.pitch; d.src_w = 320; d.src_h = 200;
+        d.crop_x = crops[i].x; d.crop_y = crops[i].y; d.crop_w = crops[i].width; d.crop_h = crops[i].height;
+        d.dst = want.data() + i * 64 * 64 * 3; d.dst_w = 64; d.dst_h = 64; d.dst_pitch = 64 * 12;
+        fkb_oracle_resize_params(ch.geometry, &d);
+        planes.push_back(d);
+    }
+    fkb_oracle_run(&ch, 1, planes.data(), BATCH, 1);
+    report("uchar4 source, alpha discarded (BGRA2RGB)", std::memcmp(want.data(), out.ptrPinned().data, want.size() * 4) == 0);
+}
+
 // ---- transposed planar tensor: TensorTSplit<float3> ---------------------------------------------------------------------
 static void test_tensor_t_split() {
     Stream stream;
@@ -422,6 +459,7 @@ int main() {
     test_batched<AspectRatio::PRESERVE_AR_LEFT>("batched crop-resize-normalise, PRESERVE_AR_LEFT", FKB_GEOM_RESIZE_PRESERVE_AR_LEFT);
     test_conditional_batch();
     test_tensor_t_split();
+    test_bgra_source();
     test_write_yuv();
     test_split_write();
     test_border<BorderType::CONSTANT>("BorderReader<CONSTANT> (complete form, operator&)");

@@ -76,6 +76,8 @@ SMALL = {
     "divergent": lambda: W.divergent_planes(n_per_seq=4, w=480, h=270),
     "divergent_odd": lambda: W.divergent_planes(n_per_seq=3, w=330, h=190),
     "crop_reorder": lambda: W.crop_reorder(n=5),
+    "bgra_crops": lambda: W.bgra_crops(),
+    "bgra_crops_swap": lambda: W.bgra_crops(swap=True, w=333, h=97, dst=(111, 50)),
     "tsplit_resize": lambda: W.tsplit_resize(),
     "split_planes_f32": lambda: W.split_planes(),
     "split_planes_u8": lambda: W.split_planes(f32=False, dst=(333, 77)),

@@ -191,7 +191,10 @@ void classify(const fkb_chain_desc& ch, PlaneRec& r) {
     const bool f32 = ch.dst_format == FKB_PIX_F32C3;
     // planar float destinations (tensor, transposed tensor, three planes) have a staged path for resampling chains
     const bool planar = (ch.write_kind == FKB_WRITE_SPLIT || ch.write_kind == FKB_WRITE_SPLIT_PLANES) && f32 && ch.geometry != FKB_GEOM_NONE;
-    if (ch.src_format != FKB_PIX_U8C3 || (ch.write_kind != FKB_WRITE_PACKED && !planar)) return;
+    // uchar4 sources (alpha skipped) have a staged path for resampling chains with a float destination
+    const bool src4 = ch.src_format == FKB_PIX_U8C4;
+    if (src4 && (!f32 || ch.geometry == FKB_GEOM_NONE)) return;
+    if ((ch.src_format != FKB_PIX_U8C3 && !src4) || (ch.write_kind != FKB_WRITE_PACKED && !planar)) return;
     if (!aligned16(r.src) || !aligned16(r.dst) || (r.src_pitch & 15) || (r.dst_pitch & 15)) return;
     if (planar && ((r.dst_cstride & 15) || (r.dst_cstride2 & 15))) return;
     const uint32_t elt = f32 ? 12u : 3u;
@@ -216,7 +219,7 @@ void classify(const fkb_chain_desc& ch, PlaneRec& r) {
         uint32_t tw = std::min(r.dst_w, 256u);
         for (;;) {
             const uint32_t cols = std::min<uint32_t>(r.crop_w, static_cast<uint32_t>(std::ceil((tw - 1) * static_cast<double>(r.fx))) + 3u);
-            if (cols * 3u + 63u <= kInRowBytes) break;
+            if (cols * (src4 ? 4u : 3u) + 63u <= kInRowBytes) break;
             if (tw <= 16) return;  // too sparse to stage: general path
             tw = tw > 32 ? ((tw - 1) & ~15u) : 16u;
         }

@@ -460,10 +460,11 @@ __device__ __forceinline__ bool point_item(const LaunchParams& p, const WarpSlic
 // the crop is made a copy of the last column after the row lands, which is exactly the reference's clamp of x2.
 // Bytes become fp32 through the half-subnormal trick (byte_times_2m24), and all arithmetic runs on pixel pairs with
 // packed f32x2 instructions.  The background bars are written into the two output-row buffers once per item.
-template <bool F32, int KIND, bool PLANAR = false>
+template <bool F32, int KIND, bool PLANAR = false, bool SRC4 = false>
 __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSlice& w, uint32_t ox, uint32_t oy0,
                                             uint32_t ow, uint32_t nr, uint32_t& k, uint32_t lane) {
     static_assert(F32 || !PLANAR, "planar rows are float rows");
+    constexpr uint32_t SP = SRC4 ? 4u : 3u;                           // bytes per source pixel (uchar4: the alpha byte is skipped)
     constexpr uint32_t ELT = PLANAR ? 4u : F32 ? 12u : 3u;            // bytes between columns of a staged output row
     constexpr uint32_t DEAD = PLANAR ? 1024u : kOutRowBytes;          // where columns that do not exist are stored
     const PlaneRec& pl = *w.pl;
@@ -479,8 +480,8 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
     const int c_lo = n_in ? axis_tap(xa - X1, fx, crop_w).i0 : 0;
     const int c_hi = n_in ? axis_tap(xb - X1, fx, crop_w).i0 + 1 : 0;  // highest column a tap pair touches
     const bool replicate = c_hi >= crop_w;
-    const uint32_t g0 = (pl.crop_x + static_cast<uint32_t>(c_lo)) * 3u;
-    const uint32_t g1 = (pl.crop_x + static_cast<uint32_t>(min(c_hi, crop_w - 1)) + 1u) * 3u;
+    const uint32_t g0 = (pl.crop_x + static_cast<uint32_t>(c_lo)) * SP;
+    const uint32_t g1 = (pl.crop_x + static_cast<uint32_t>(min(c_hi, crop_w - 1)) + 1u) * SP;
     const uint32_t a0 = g0 & ~15u, shift = g0 - a0;
     const uint32_t row_bytes = ((g1 + 15u) & ~15u) - a0;
     if (row_bytes + 32u > kInRowBytes) return false;  // the host lowering guarantees the footprint fits
@@ -496,13 +497,13 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
         const bool live = j < nj && col < n_in;
         col = min(col, max(n_in - 1, 0));
         const AxisTap t = axis_tap(xa + col - X1, fx, crop_w);
-        boff[j] = n_in ? static_cast<uint32_t>(t.i0 - c_lo) * 3u + shift : 0u;
+        boff[j] = n_in ? static_cast<uint32_t>(t.i0 - c_lo) * SP + shift : 0u;
         wx0[j] = t.w0; wx1[j] = t.w1;
         ooff[j] = live ? static_cast<uint32_t>(xa - static_cast<int>(ox) + col) * ELT : DEAD;
     }
     // Offset (in a staged row) of the crop's last column when a tap pair reaches one past it; that column is then
     // duplicated into the next three bytes.  Otherwise the copy is aimed at the unused tail of the staged row.
-    const uint32_t rep_off = replicate ? static_cast<uint32_t>(crop_w - 1 - c_lo) * 3u + shift : kInRowBytes - 8u;
+    const uint32_t rep_off = replicate ? static_cast<uint32_t>(crop_w - 1 - c_lo) * SP + shift : kInRowBytes - 8u;
     const uint8_t* gsrc = pl.src + static_cast<size_t>(pl.crop_y) * pl.src_pitch + a0;
     const uint32_t src_pitch = pl.src_pitch, dst_pitch = pl.dst_pitch;
     uint8_t* gdst = pl.dst + static_cast<size_t>(oy0) * dst_pitch + static_cast<size_t>(ox) * ELT;
@@ -569,9 +570,9 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
         for (int c = 0; c < 3; ++c) {
             // taps of the two columns: (x1,y1) (x1+1,y1) (x1,y2) (x1+1,y2); bytes come back as b * 2^-24
             const f2 p00 = {byte_times_2m24(smem_raw[a0p + c]), byte_times_2m24(smem_raw[a1p + c])};
-            const f2 p10 = {byte_times_2m24(smem_raw[a0p + 3 + c]), byte_times_2m24(smem_raw[a1p + 3 + c])};
+            const f2 p10 = {byte_times_2m24(smem_raw[a0p + SP + c]), byte_times_2m24(smem_raw[a1p + SP + c])};
             const f2 p01 = {byte_times_2m24(smem_raw[a0p + kInRowBytes + c]), byte_times_2m24(smem_raw[a1p + kInRowBytes + c])};
-            const f2 p11 = {byte_times_2m24(smem_raw[a0p + kInRowBytes + 3 + c]), byte_times_2m24(smem_raw[a1p + kInRowBytes + 3 + c])};
+            const f2 p11 = {byte_times_2m24(smem_raw[a0p + kInRowBytes + SP + c]), byte_times_2m24(smem_raw[a1p + kInRowBytes + SP + c])};
             v[c] = add2(add2(add2(mul2_unfusable(p00, w00, nz), mul2_unfusable(p10, w10, nz)), mul2_unfusable(p01, w01, nz)),
                         mul2_unfusable(p11, w11, nz));
         }
@@ -614,7 +615,7 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
             if (replicate) {  // every lane writes the same three bytes (even lanes the first staged row, odd lanes the second)
                 const uint32_t q = in_s + (lane & 1u) * kInRowBytes + rep_off;
                 const uint8_t c0 = smem_raw[q], c1 = smem_raw[q + 1], c2 = smem_raw[q + 2];
-                smem_raw[q + 3] = c0; smem_raw[q + 4] = c1; smem_raw[q + 5] = c2;
+                smem_raw[q + SP] = c0; smem_raw[q + SP + 1] = c1; smem_raw[q + SP + 2] = c2;
                 __syncwarp();
             }
             const f2 wy0 = {__fmul_rn(ay.w0, kByteScale), __fmul_rn(ay.w0, kByteScale)};  // vertical weights, times 2^24
@@ -633,16 +634,16 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
     return true;
 }
 
-template <bool F32, bool PLANAR = false>
+template <bool F32, bool PLANAR = false, bool SRC4 = false>
 __device__ __forceinline__ bool resize_dispatch(const LaunchParams& p, const WarpSlice& w, uint32_t kind, uint32_t ox,
                                                 uint32_t oy0, uint32_t ow, uint32_t nr, uint32_t& k, uint32_t lane) {
     constexpr int S = F32 ? 0 : kPostSat;  // a uchar3 destination ends in a SaturateCast, a float3 one cannot
     switch (kind) {
-    case S: return resize_item<F32, S, PLANAR>(p, w, ox, oy0, ow, nr, k, lane);
-    case S | kPostMul: return resize_item<F32, S | kPostMul, PLANAR>(p, w, ox, oy0, ow, nr, k, lane);
-    case S | kPostAdd: return resize_item<F32, S | kPostAdd, PLANAR>(p, w, ox, oy0, ow, nr, k, lane);
-    case S | kPostMul | kPostAdd: return resize_item<F32, S | kPostMul | kPostAdd, PLANAR>(p, w, ox, oy0, ow, nr, k, lane);
-    default: return resize_item<F32, kPostGeneric, PLANAR>(p, w, ox, oy0, ow, nr, k, lane);
+    case S: return resize_item<F32, S, PLANAR, SRC4>(p, w, ox, oy0, ow, nr, k, lane);
+    case S | kPostMul: return resize_item<F32, S | kPostMul, PLANAR, SRC4>(p, w, ox, oy0, ow, nr, k, lane);
+    case S | kPostAdd: return resize_item<F32, S | kPostAdd, PLANAR, SRC4>(p, w, ox, oy0, ow, nr, k, lane);
+    case S | kPostMul | kPostAdd: return resize_item<F32, S | kPostMul | kPostAdd, PLANAR, SRC4>(p, w, ox, oy0, ow, nr, k, lane);
+    default: return resize_item<F32, kPostGeneric, PLANAR, SRC4>(p, w, ox, oy0, ow, nr, k, lane);
     }
 }
 
@@ -704,6 +705,10 @@ __global__ void __launch_bounds__(kStagedThreads, 2) staged_kernel(const __grid_
                 case kPostMul | kPostAdd: ok = point_item<true, kPostMul | kPostAdd>(p, w, ox, oy0, ow, nr, k4, lane); break;
                 default: ok = point_item<true, kPostGeneric>(p, w, ox, oy0, ow, nr, k4, lane); break;
             }
+        }
+        else if (p.chains[pl.chain].src_format == FKB_PIX_U8C4) {  // (float destinations only: the host lowering sees to it)
+            ok = p.chains[pl.chain].write_kind != FKB_WRITE_PACKED ? resize_dispatch<true, true, true>(p, w, p.post_kind[pl.chain], ox, oy0, ow, nr, k, lane)
+                                                                   : resize_dispatch<true, false, true>(p, w, p.post_kind[pl.chain], ox, oy0, ow, nr, k, lane);
         }
         else if (p.chains[pl.chain].write_kind != FKB_WRITE_PACKED) ok = resize_dispatch<true, true>(p, w, p.post_kind[pl.chain], ox, oy0, ow, nr, k, lane);
         else ok = f32 ? resize_dispatch<true>(p, w, p.post_kind[pl.chain], ox, oy0, ow, nr, k, lane)

@@ -134,7 +134,7 @@ class Workload:
             nv12 = ch.src_format in (abi.PIX_NV12, abi.PIX_NV21) or uyvy  # one luma byte per pixel, one chroma pair per 2 (x2) pixels
             elt = 12 if ch.dst_format == abi.PIX_F32C3 else 3
             out_bytes += s.dst_w * s.dst_h * elt
-            if s.default or ch.border or ch.src_format == abi.PIX_U8C4:
+            if s.default or ch.border:
                 continue
             if s.src not in masks:
                 masks[s.src] = (np.zeros((s.src_h, s.src_w), bool),
@@ -345,18 +345,19 @@ def random_rects(n, w, h, lo, hi, rs: np.random.RandomState):
 
 
 def batched_crop_resize(n_frames=64, crops_per_frame=32, w=1920, h=1080, dst=(224, 224), crop_range=(16, 512),
-                        seed=4, pitch_align=16, frame_seed_base=1000) -> Workload:
-    """Config 4: per frame, random crops -> Resize PRESERVE_AR (bg 114) -> Mul 1/255 -> TensorWrite<float3>."""
-    pitch = _pitch(w * 3, pitch_align)
+                        seed=4, pitch_align=16, frame_seed_base=1000, src4=False) -> Workload:
+    """Config 4: per frame, random crops -> Resize PRESERVE_AR (bg 114) -> Mul 1/255 -> TensorWrite<float3>.  With
+    ``src4`` the frames are uchar4 and the chain discards their alpha channel."""
+    pitch = _pitch(w * (4 if src4 else 3), pitch_align)
     dw, dh = dst
-    ch = chain(abi.PIX_U8C3, abi.GEOM_RESIZE_PRESERVE_AR, abi.PIX_F32C3, abi.WRITE_PACKED,
+    ch = chain(abi.PIX_U8C4 if src4 else abi.PIX_U8C3, abi.GEOM_RESIZE_PRESERVE_AR, abi.PIX_F32C3, abi.WRITE_PACKED,
                [op(abi.OP_MUL, (1.0 / 255.0,) * 3)])
     rs = np.random.RandomState(seed)
     rects = random_rects(n_frames * crops_per_frame, w, h, crop_range[0], crop_range[1], rs)
     planes = [PlaneSpec(i // crops_per_frame, 0, i * dw * dh * 12, w, h, pitch, r, dw, dh, dw * 12, bg=(114.0, 114.0, 114.0))
               for i, r in enumerate(rects)]
     sources = [_frame(frame_seed_base + f, pitch * h) for f in range(n_frames)]
-    return Workload("batched_crop_resize", [ch], sources, [dw * dh * 12 * len(planes)], planes,
+    return Workload("batched_crop_resize_uchar4" if src4 else "batched_crop_resize", [ch], sources, [dw * dh * 12 * len(planes)], planes,
                     f"{n_frames} frames {w}x{h} uchar3 x {crops_per_frame} crops -> {dw}x{dh} float3 tensor",
                     extra={"n_frames": n_frames, "crops_per_frame": crops_per_frame})
 
@@ -455,7 +456,10 @@ def random_workload(seed: int, max_dim: int = 260) -> Workload:
     if nv12:
         w, h = w + (w & 1), h + (h & 1)
     align = int(rs.choice([1, 4, 16, 64, 512]))
-    pitch = _pitch(w if nv12 else w * 3, max(align, 2 if nv12 else 1))
+    src4 = not nv12 and seed % 5 == 3  # a uchar4 source whose alpha is discarded (decided by the seed alone: other seeds keep their launches)
+    if src4:
+        ch.src_format = abi.PIX_U8C4
+    pitch = _pitch(w if nv12 else w * (4 if src4 else 3), max(align, 2 if nv12 else 1))
     src = _frame(seed + 7, pitch * (h + h // 2 if nv12 else h), 16 if nv12 else 0, 236 if nv12 else 256)
     elt = (4 if split else 12) if dst_format == abi.PIX_F32C3 else (1 if split else 3)
     dalign = int(rs.choice([1, 16, 64])) if dst_format == abi.PIX_U8C3 else int(rs.choice([4, 16, 64]))

@@ -77,6 +77,7 @@ SMALL = {
     "divergent_odd": lambda: W.divergent_planes(n_per_seq=3, w=330, h=190),
     "crop_reorder": lambda: W.crop_reorder(n=5),
     "bgra_crops": lambda: W.bgra_crops(),
+    "batched_uchar4": lambda: W.batched_crop_resize(n_frames=4, crops_per_frame=8, w=960, h=540, src4=True),
     "bgra_crops_swap": lambda: W.bgra_crops(swap=True, w=333, h=97, dst=(111, 50)),
     "tsplit_resize": lambda: W.tsplit_resize(),
     "split_planes_f32": lambda: W.split_planes(),

@@ -16,7 +16,7 @@ NOALLOC_MAX_PLANES = 4096
 
 OK, ERR_NULL, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_TOO_LARGE, ERR_DEVICE_WAIT = 0, -1, -2, -3, -4, -5, -6
 
-PIX_U8C3, PIX_F32C3, PIX_NV12, PIX_NV21, PIX_UYVY, PIX_U8C4 = 1, 2, 3, 4, 5, 6
+PIX_U8C3, PIX_F32C3, PIX_NV12, PIX_NV21, PIX_UYVY, PIX_U8C4, PIX_F32C4 = 1, 2, 3, 4, 5, 6, 7
 RANGE_LIMITED, RANGE_FULL = 0, 1
 PRIMITIVES_BT601, PRIMITIVES_BT709, PRIMITIVES_BT2020 = 0, 1, 2
 GEOM_NONE, GEOM_RESIZE_IGNORE_AR, GEOM_RESIZE_PRESERVE_AR = 0, 1, 2
@@ -38,6 +38,7 @@ class ChainDesc(C.Structure):
         ("ops", Op * MAX_OPS), ("ccm", C.c_float * 9), ("yuv_sub", C.c_float * 3),
         ("ccm2", C.c_float * 9), ("yuv_add", C.c_float * 3),
         ("border", C.c_uint32), ("border_at", C.c_uint32), ("border_value", C.c_float * 3),
+        ("op_w", C.c_float * MAX_OPS), ("border_value_w", C.c_float),
     ]
 
 
@@ -53,10 +54,11 @@ class PlaneDesc(C.Structure):
         ("bg", C.c_float * 3), ("chain", C.c_uint32),
         ("params", (C.c_float * 3) * MAX_PLANE_PARAMS),
         ("dst_y", C.c_void_p), ("dst_z", C.c_void_p),
+        ("bg_w", C.c_float), ("params_w", C.c_float * MAX_PLANE_PARAMS),
     ]
 
 
-assert C.sizeof(Op) == 16 and C.sizeof(ChainDesc) == 332 and C.sizeof(PlaneDesc) == 176
+assert C.sizeof(Op) == 16 and C.sizeof(ChainDesc) == 384 and C.sizeof(PlaneDesc) == 200
 
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libfkb.so")
 

@@ -14,7 +14,7 @@
 
 namespace fkb {
 
-enum : uint32_t { KCLASS_GATHER = 0, KCLASS_POINT = 1, KCLASS_RESIZE = 2, KCLASS_LUT = 3, KCLASS_NV12 = 4 };
+enum : uint32_t { KCLASS_GATHER = 0, KCLASS_POINT = 1, KCLASS_RESIZE = 2, KCLASS_LUT = 3, KCLASS_NV12 = 4, KCLASS_GATHER4 = 5 };
 
 // One output plane as the kernels see it: the caller's fkb_plane_desc plus what the host lowering derived
 // (which kernel path runs it, its tile shape and its first tile index).
@@ -39,8 +39,11 @@ struct __align__(16) PlaneRec {
     uint32_t src_w, src_h;      // frame size in pixels (what a BorderReader maps coordinates into)
     float params[FKB_MAX_PLANE_PARAMS][3];
     uint32_t lut_base;          // LUT units of all earlier planes (monotone over the table, searched by lut_kernel)
+    float bg_w;                 // four-channel chains: the fourth channel of bg and of the per-plane operands
+    float params_w[FKB_MAX_PLANE_PARAMS];
+    uint32_t spare_[3];
 };
-static_assert(sizeof(PlaneRec) == 192, "layout is mirrored by the host lowering");
+static_assert(sizeof(PlaneRec) == 224, "layout is mirrored by the host lowering");
 // byte offset of channel c of a planar destination
 __host__ __device__ __forceinline__ uint64_t channel_offset(const PlaneRec& pl, int c) {
     return c == 0 ? 0ull : c == 1 ? pl.dst_cstride : pl.dst_cstride2;

@@ -58,7 +58,13 @@ int check_ops(const fkb_chain_desc& ch, uint32_t first, uint32_t last, ValueType
 int check_chain(const fkb_chain_desc& ch) {
     if (ch.src_format != FKB_PIX_U8C3 && ch.src_format != FKB_PIX_NV12 && ch.src_format != FKB_PIX_NV21 &&
         ch.src_format != FKB_PIX_UYVY && ch.src_format != FKB_PIX_U8C4) return FKB_ERR_UNSUPPORTED;
-    if (ch.dst_format != FKB_PIX_U8C3 && ch.dst_format != FKB_PIX_F32C3) return FKB_ERR_UNSUPPORTED;
+    const bool four = ch.dst_format == FKB_PIX_U8C4 || ch.dst_format == FKB_PIX_F32C4;  // the chain keeps four channels
+    if (ch.dst_format != FKB_PIX_U8C3 && ch.dst_format != FKB_PIX_F32C3 && !four) return FKB_ERR_UNSUPPORTED;
+    if (four) {
+        if (ch.src_format != FKB_PIX_U8C4 || ch.write_kind != FKB_WRITE_PACKED) return FKB_ERR_UNSUPPORTED;
+        for (uint32_t i = 0; i < ch.n_ops && i < FKB_MAX_OPS; ++i)
+            if (ch.ops[i].code == FKB_OP_YUV2RGB || ch.ops[i].code == FKB_OP_RGB2YUV) return FKB_ERR_UNSUPPORTED;
+    }
     if (ch.geometry > FKB_GEOM_RESIZE_PRESERVE_AR_LEFT) return FKB_ERR_UNSUPPORTED;
     if (ch.write_kind < FKB_WRITE_PACKED || ch.write_kind > FKB_WRITE_UYVY) return FKB_ERR_UNSUPPORTED;
     if (ch.write_kind >= FKB_WRITE_NV12 && ch.dst_format != FKB_PIX_U8C3) return FKB_ERR_INVALID;  // WriteYUV takes byte triples
@@ -74,7 +80,7 @@ int check_chain(const fkb_chain_desc& ch) {
         t = VT_F32;  // the interpolation returns float_<cn> whatever it reads
         if ((rc = check_ops(ch, ch.n_pre_ops, ch.n_ops, t)) != FKB_OK) return rc;
     }
-    const ValueType want = ch.dst_format == FKB_PIX_F32C3 ? VT_F32 : VT_U8;
+    const ValueType want = (ch.dst_format == FKB_PIX_F32C3 || ch.dst_format == FKB_PIX_F32C4) ? VT_F32 : VT_U8;
     return t == want ? FKB_OK : FKB_ERR_INVALID;  // the Write's input type must be the chain's output type
 }
 
@@ -105,9 +111,12 @@ int check_plane(const fkb_chain_desc& ch, const fkb_plane_desc& pl) {
     } else if (ch.geometry == FKB_GEOM_NONE) {
         for (int c = 0; c < 3; ++c)  // a uchar3 default
             if (!(pl.bg[c] >= 0.f && pl.bg[c] <= 255.f) || pl.bg[c] != std::floor(pl.bg[c])) return FKB_ERR_INVALID;
+        if ((ch.dst_format == FKB_PIX_U8C4 || ch.dst_format == FKB_PIX_F32C4) &&
+            (!(pl.bg_w >= 0.f && pl.bg_w <= 255.f) || pl.bg_w != std::floor(pl.bg_w))) return FKB_ERR_INVALID;
     }
     if (pl.dst_w == 0 || pl.dst_h == 0) return FKB_ERR_INVALID;
-    const bool f32 = ch.dst_format == FKB_PIX_F32C3;
+    const bool four = ch.dst_format == FKB_PIX_U8C4 || ch.dst_format == FKB_PIX_F32C4;
+    const bool f32 = ch.dst_format == FKB_PIX_F32C3 || ch.dst_format == FKB_PIX_F32C4;
     const bool planes3 = ch.write_kind == FKB_WRITE_SPLIT_PLANES;
     if (planes3 && (!pl.dst_y || !pl.dst_z)) return FKB_ERR_NULL;
     const bool split = ch.write_kind == FKB_WRITE_SPLIT || planes3;
@@ -115,6 +124,7 @@ int check_plane(const fkb_chain_desc& ch, const fkb_plane_desc& pl) {
     if (semi && !pl.dst_y) return FKB_ERR_NULL;
     const uint64_t dst_row = semi ? ((static_cast<uint64_t>(pl.dst_w) + 1) / 2) * 2
                              : ch.write_kind == FKB_WRITE_UYVY ? ((static_cast<uint64_t>(pl.dst_w) + 1) / 2) * 4
+                             : four ? static_cast<uint64_t>(pl.dst_w) * (f32 ? 16 : 4)
                              : static_cast<uint64_t>(pl.dst_w) * (split ? (f32 ? 4 : 1) : (f32 ? 12 : 3));
     if (pl.dst_pitch < dst_row) return FKB_ERR_INVALID;
     if (f32 && ((reinterpret_cast<uintptr_t>(pl.dst) & 3) || (pl.dst_pitch & 3) || (pl.dst_channel_stride & 3))) return FKB_ERR_INVALID;
@@ -175,6 +185,7 @@ uint32_t post_kind_of(const fkb_chain_desc& ch);
 void classify(const fkb_chain_desc& ch, PlaneRec& r) {
     r.kclass = KCLASS_GATHER;
     r.tile_w = r.tile_h = r.tiles_x = 0;
+    if (ch.dst_format == FKB_PIX_U8C4 || ch.dst_format == FKB_PIX_F32C4) { r.kclass = KCLASS_GATHER4; return; }
     if (force_gather()) return;
     if (ch.border) {
         // a rectangle inside the frame never meets the border: it takes the usual paths; one that leaves it is
@@ -279,6 +290,7 @@ struct Lowered {
     uint32_t staged_grid = 0;
     uint32_t lut_grid = 0;
     dim3 gather_grid{0, 0, 0};
+    dim3 gather4_grid{0, 0, 0};
     dim3 nv12_grid{0, 0, 0};
     int gather_ppt = 4;
     uint32_t kernels = 0;
@@ -314,7 +326,7 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
     if (!L.recs) { L.storage.resize(n_planes); L.recs = L.storage.data(); }
     std::memset(&L.lp, 0, sizeof(L.lp));
     std::memcpy(L.lp.chains, chains, sizeof(fkb_chain_desc) * n_chains);
-    uint32_t n_tiles = 0, gw = 0, gh = 0, n_gather = 0;
+    uint32_t n_tiles = 0, gw = 0, gh = 0, n_gather = 0, g4w = 0, g4h = 0, n_gather4 = 0;
     bool uniform = true;
     uint32_t first_count = 0;
     int sms = 0;
@@ -348,9 +360,12 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         std::memcpy(r.bg, s.bg, sizeof(r.bg));
         r.chain = s.chain & ~FKB_PLANE_DEFAULT;
         std::memcpy(r.params, s.params, sizeof(r.params));
-        if (s.chain & FKB_PLANE_DEFAULT) {  // the kernels know such a plane by its null source; the general kernel fills it
+        r.bg_w = s.bg_w;
+        std::memcpy(r.params_w, s.params_w, sizeof(r.params_w));
+        if (s.chain & FKB_PLANE_DEFAULT) {  // the kernels know such a plane by its null source; the general kernels fill it
             r.src = r.src_chroma = nullptr;
-            r.kclass = KCLASS_GATHER;
+            const uint32_t df = chains[r.chain].dst_format;
+            r.kclass = (df == FKB_PIX_U8C4 || df == FKB_PIX_F32C4) ? KCLASS_GATHER4 : KCLASS_GATHER;
         } else {
             classify(chains[r.chain], r);
         }
@@ -360,7 +375,7 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
     // so it goes through the general kernel, one pixel per thread.
     if (total_pixels < tiny_launch_pixels())
         for (uint32_t z = 0; z < n_planes; ++z)
-            if (L.recs[z].kclass != KCLASS_NV12) { L.recs[z].kclass = KCLASS_GATHER; L.recs[z].tiles_x = 0; }
+            if (L.recs[z].kclass != KCLASS_NV12 && L.recs[z].kclass != KCLASS_GATHER4) { L.recs[z].kclass = KCLASS_GATHER; L.recs[z].tiles_x = 0; }
     for (uint32_t z = 0; z < n_planes; ++z) {
         const PlaneRec& r = L.recs[z];
         if (r.kclass == KCLASS_POINT || r.kclass == KCLASS_RESIZE) row_segments += static_cast<uint64_t>(r.tiles_x) * r.dst_h;
@@ -392,6 +407,7 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         if (static_cast<uint64_t>(n_tiles) + count > 0xfffffff0ull) return FKB_ERR_TOO_LARGE;
         n_tiles += count;
         if (r.kclass == KCLASS_GATHER) { ++n_gather; gw = std::max(gw, r.dst_w); gh = std::max(gh, r.dst_h); }
+        if (r.kclass == KCLASS_GATHER4) { ++n_gather4; g4w = std::max(g4w, r.dst_w); g4h = std::max(g4h, r.dst_h); }
     }
     L.lp.n_planes = n_planes;
     L.lp.neg_zero = -0.0f;
@@ -447,6 +463,10 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         L.nv12_grid = dim3((nw + (pair ? 63 : 31)) / (pair ? 64 : 32), (nh + 7) / 8, std::min<uint32_t>(n_planes, 65535u));
         ++L.kernels;
     }
+    if (n_gather4) {
+        L.gather4_grid = dim3((g4w + 31) / 32, (g4h + 7) / 8, std::min<uint32_t>(n_planes, 65535u));
+        ++L.kernels;
+    }
     if (n_gather) {
         // small launches are latency-bound: one pixel per thread puts four times as many threads on the taps
         L.gather_ppt = gather_pixels < (2u << 20) ? 1 : 4;
@@ -468,6 +488,7 @@ int run(const Lowered& L, const LaunchParams& lp, cudaStream_t stream) {
     if (L.lut_grid) FKB_CUDA(launch_lut(lp, L.lut_grid, stream));
     if (L.nv12_grid.x) FKB_CUDA(launch_nv12(lp, L.nv12_grid, stream));
     if (L.gather_grid.x) FKB_CUDA(launch_gather(lp, L.gather_grid, L.gather_ppt, stream));
+    if (L.gather4_grid.x) FKB_CUDA(launch_gather4(lp, L.gather4_grid, stream));
     return FKB_OK;
 }
 
@@ -561,7 +582,7 @@ int launch_once(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane
 // fkb_launch_transform_noalloc: the plane-record table lives in a fixed array inside the library image
 // -------------------------------------------------------------------------------------------------------
 // Device-side table of the allocation-free entry point.  Every GPU that loads this library carries these
-// FKB_NOALLOC_MAX_PLANES * sizeof(PlaneRec) bytes (768 KB) until the process exits.  In host code this name is only a
+// FKB_NOALLOC_MAX_PLANES * sizeof(PlaneRec) bytes (896 KB) until the process exits.  In host code this name is only a
 // handle for cudaGetSymbolAddress, never an address a kernel may be given.
 static __device__ __align__(256) unsigned char g_noalloc_table[FKB_NOALLOC_MAX_PLANES * sizeof(PlaneRec)];
 

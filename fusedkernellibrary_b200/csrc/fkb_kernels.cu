@@ -230,6 +230,140 @@ __global__ void __launch_bounds__(256) gather_kernel(const __grid_constant__ Lau
 }
 
 // ---------------------------------------------------------------------------------------------------------
+// gather4_kernel: chains that keep four channels (uchar4 -> ... -> uchar4 | float4)
+// ---------------------------------------------------------------------------------------------------------
+// One output pixel per thread; a source pixel is one 32-bit load.  The ops are Cast, Mul / Add / Sub / Div with four
+// operands (the fourth in fkb_chain_desc::op_w or PlaneRec::params_w), the BGRA <-> RGBA reorder and SaturateCast.
+__device__ __forceinline__ bool read_tap4(const fkb_chain_desc& ch, const PlaneRec& pl, int cx, int cy, float (&o)[4]) {
+    int X = cx + static_cast<int>(pl.crop_x), Y = cy + static_cast<int>(pl.crop_y);
+    if (ch.border) {
+        const int w = static_cast<int>(pl.src_w), h = static_cast<int>(pl.src_h);
+        if (ch.border == FKB_BORDER_CONSTANT) {
+            if (X < 0 || X >= w || Y < 0 || Y >= h) { o[0] = o[1] = o[2] = o[3] = 0.f; return true; }
+        } else {
+            X = border_index(ch.border, X, w);
+            Y = border_index(ch.border, Y, h);
+        }
+    }
+    const uint8_t* q = pl.src + static_cast<size_t>(Y) * pl.src_pitch + static_cast<size_t>(X) * 4;
+    uint32_t px;
+    if ((reinterpret_cast<uintptr_t>(q) & 3) == 0) px = __ldg(reinterpret_cast<const uint32_t*>(q));
+    else px = __ldg(q) | (__ldg(q + 1) << 8) | (__ldg(q + 2) << 16) | (__ldg(q + 3) << 24);
+    o[0] = static_cast<float>(px & 0xffu); o[1] = static_cast<float>((px >> 8) & 0xffu);
+    o[2] = static_cast<float>((px >> 16) & 0xffu); o[3] = static_cast<float>(px >> 24);
+    return false;
+}
+template <int N>
+__device__ __forceinline__ void apply_ops4(float (&v)[N][4], const fkb_chain_desc& ch, const PlaneRec& pl, uint32_t first, uint32_t last) {
+    for (uint32_t i = first; i < last; ++i) {
+        const int slot = ch.ops[i].plane_slot;
+        float p[4];
+        if (slot >= 0) { p[0] = pl.params[slot][0]; p[1] = pl.params[slot][1]; p[2] = pl.params[slot][2]; p[3] = pl.params_w[slot]; }
+        else { p[0] = ch.ops[i].v[0]; p[1] = ch.ops[i].v[1]; p[2] = ch.ops[i].v[2]; p[3] = ch.op_w[i]; }
+        switch (ch.ops[i].code) {
+        case FKB_OP_MUL:
+#pragma unroll
+            for (int n = 0; n < N; ++n)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) v[n][c] = __fmul_rn(v[n][c], p[c]);
+            break;
+        case FKB_OP_ADD:
+#pragma unroll
+            for (int n = 0; n < N; ++n)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) v[n][c] = __fadd_rn(v[n][c], p[c]);
+            break;
+        case FKB_OP_SUB:
+#pragma unroll
+            for (int n = 0; n < N; ++n)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) v[n][c] = __fsub_rn(v[n][c], p[c]);
+            break;
+        case FKB_OP_DIV:
+#pragma unroll
+            for (int n = 0; n < N; ++n)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) v[n][c] = __fdiv_rn(v[n][c], p[c]);
+            break;
+        case FKB_OP_REORDER_ZYX:
+#pragma unroll
+            for (int n = 0; n < N; ++n) { const float t = v[n][0]; v[n][0] = v[n][2]; v[n][2] = t; }
+            break;
+        case FKB_OP_SATCAST_U8:
+#pragma unroll
+            for (int n = 0; n < N; ++n)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) v[n][c] = sat_u8_as_float(v[n][c]);
+            break;
+        default: break;  // FKB_OP_CAST_F32: values are already carried as fp32
+        }
+    }
+}
+template <int N>
+__device__ __forceinline__ void apply_ops4_bordered(float (&v)[N][4], const fkb_chain_desc& ch, const PlaneRec& pl, uint32_t last, uint32_t outside) {
+    if (outside == 0u) { apply_ops4<N>(v, ch, pl, 0, last); return; }
+    apply_ops4<N>(v, ch, pl, 0, ch.border_at);
+#pragma unroll
+    for (int n = 0; n < N; ++n)
+        if ((outside >> n) & 1u) { v[n][0] = ch.border_value[0]; v[n][1] = ch.border_value[1]; v[n][2] = ch.border_value[2]; v[n][3] = ch.border_value_w; }
+    apply_ops4<N>(v, ch, pl, ch.border_at, last);
+}
+
+__global__ void __launch_bounds__(256) gather4_kernel(const __grid_constant__ LaunchParams p) {
+    __shared__ PlaneRec s_pl;
+    const PlaneRec* table = plane_table(p);
+    const uint32_t x = blockIdx.x * 32 + (threadIdx.x & 31), y = blockIdx.y * 8 + (threadIdx.x >> 5);
+    for (uint32_t z = blockIdx.z; z < p.n_planes; z += gridDim.z) {
+        __syncthreads();
+        if (threadIdx.x < sizeof(PlaneRec) / 16)
+            reinterpret_cast<uint4*>(&s_pl)[threadIdx.x] = reinterpret_cast<const uint4*>(table + z)[threadIdx.x];
+        __syncthreads();
+        const PlaneRec& pl = s_pl;
+        if (pl.kclass != KCLASS_GATHER4 || x >= pl.dst_w || y >= pl.dst_h) continue;
+        const fkb_chain_desc& ch = p.chains[pl.chain];
+        float v[1][4];
+        if (pl.src == nullptr) {  // a plane whose read yields its default value
+            v[0][0] = pl.bg[0]; v[0][1] = pl.bg[1]; v[0][2] = pl.bg[2]; v[0][3] = pl.bg_w;
+            apply_ops4<1>(v, ch, pl, ch.geometry == FKB_GEOM_NONE ? 0 : ch.n_pre_ops, ch.n_ops);
+        } else if (ch.geometry == FKB_GEOM_NONE) {
+            const uint32_t outside = read_tap4(ch, pl, static_cast<int>(x), static_cast<int>(y), v[0]) ? 1u : 0u;
+            apply_ops4_bordered<1>(v, ch, pl, ch.n_ops, outside);
+        } else {
+            const bool par = ch.geometry >= FKB_GEOM_RESIZE_PRESERVE_AR;
+            const int xi = static_cast<int>(x), yi = static_cast<int>(y);
+            if (!par || (xi >= pl.x1 && xi <= pl.x2 && yi >= pl.y1 && yi <= pl.y2)) {
+                const AxisTap ax = axis_tap(xi - (par ? pl.x1 : 0), pl.fx, pl.crop_w), ay = axis_tap(yi - (par ? pl.y1 : 0), pl.fy, pl.crop_h);
+                float t[4][4];
+                uint32_t outside = read_tap4(ch, pl, ax.i0, ay.i0, t[0]) ? 1u : 0u;
+                outside |= read_tap4(ch, pl, ax.i1, ay.i0, t[1]) ? 2u : 0u;
+                outside |= read_tap4(ch, pl, ax.i0, ay.i1, t[2]) ? 4u : 0u;
+                outside |= read_tap4(ch, pl, ax.i1, ay.i1, t[3]) ? 8u : 0u;
+                apply_ops4_bordered<4>(t, ch, pl, ch.n_pre_ops, outside);
+                const float w00 = __fmul_rn(ax.w0, ay.w0), w10 = __fmul_rn(ax.w1, ay.w0);
+                const float w01 = __fmul_rn(ax.w0, ay.w1), w11 = __fmul_rn(ax.w1, ay.w1);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) v[0][c] = bilerp(t[0][c], t[1][c], t[2][c], t[3][c], w00, w10, w01, w11);
+            } else {
+                v[0][0] = pl.bg[0]; v[0][1] = pl.bg[1]; v[0][2] = pl.bg[2]; v[0][3] = pl.bg_w;
+            }
+            apply_ops4<1>(v, ch, pl, ch.n_pre_ops, ch.n_ops);
+        }
+        uint8_t* row = pl.dst + static_cast<size_t>(y) * pl.dst_pitch;
+        if (ch.dst_format == FKB_PIX_F32C4) {
+            float* f = reinterpret_cast<float*>(row) + static_cast<size_t>(x) * 4;
+            if ((reinterpret_cast<uintptr_t>(f) & 15) == 0) *reinterpret_cast<float4*>(f) = make_float4(v[0][0], v[0][1], v[0][2], v[0][3]);
+            else { f[0] = v[0][0]; f[1] = v[0][1]; f[2] = v[0][2]; f[3] = v[0][3]; }
+        } else {
+            uint8_t* q = row + static_cast<size_t>(x) * 4;
+            const uint32_t px = static_cast<uint32_t>(v[0][0]) | (static_cast<uint32_t>(v[0][1]) << 8) | (static_cast<uint32_t>(v[0][2]) << 16) |
+                                (static_cast<uint32_t>(v[0][3]) << 24);
+            if ((reinterpret_cast<uintptr_t>(q) & 3) == 0) *reinterpret_cast<uint32_t*>(q) = px;
+            else { q[0] = static_cast<uint8_t>(px); q[1] = static_cast<uint8_t>(px >> 8); q[2] = static_cast<uint8_t>(px >> 16); q[3] = static_cast<uint8_t>(px >> 24); }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
 // staged_kernel: every warp runs its own load -> compute -> store pipeline; warps never wait for one another
 // ---------------------------------------------------------------------------------------------------------
 // Shared memory of one warp (kSliceBytes): two mbarriers, the plane record of the item being processed, two
@@ -1139,6 +1273,11 @@ cudaError_t launch_nv12(const LaunchParams& p, dim3 grid, cudaStream_t stream) {
         else nv12_pair_kernel<128, 10, false, false><<<g, 128, 0, stream>>>(p);
     }
     else nv12_kernel<<<grid, 256, 0, stream>>>(p);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_gather4(const LaunchParams& p, dim3 grid, cudaStream_t stream) {
+    gather4_kernel<<<grid, 256, 0, stream>>>(p);
     return cudaGetLastError();
 }
 

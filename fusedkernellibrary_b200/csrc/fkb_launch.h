@@ -9,9 +9,10 @@ struct LaunchParams;
 
 constexpr uint32_t kStagedThreads = 256;
 constexpr uint32_t kStagedWarps = kStagedThreads / 32;
-// Shared memory of one warp of a staged CTA: a 256-byte header (two mbarriers, the plane record), two stages of two
-// source rows, and two output rows.  12.5 KB per warp, 100 KB per CTA, so two CTAs fit in the 228 KB of an SM.
-constexpr uint32_t kSliceHeader = 256;
+// Shared memory of one warp of a staged CTA: a 288-byte header (six mbarriers, the plane record), two stages of two
+// source rows (or four stages of one), and two output rows.  12.6 KB per warp, 101 KB per CTA, so two CTAs fit in the
+// 228 KB of an SM.
+constexpr uint32_t kSliceHeader = 288;
 constexpr uint32_t kInRowBytes = 1600;   // one staged source row segment (512 uchar3 pixels + alignment slack)
 constexpr uint32_t kOutRowBytes = 3072;  // one output row segment (256 float3 pixels, or 512 uchar3 with room to spare)
 // A planar float row is three segments (one per channel) of 256 values, each followed by 16 spare bytes; a packed row is
@@ -40,6 +41,7 @@ cudaError_t launch_staged(const LaunchParams& p, uint32_t grid, cudaStream_t str
 cudaError_t launch_lut(const LaunchParams& p, uint32_t grid, cudaStream_t stream);
 cudaError_t launch_nv12(const LaunchParams& p, dim3 grid, cudaStream_t stream);
 cudaError_t launch_gather(const LaunchParams& p, dim3 grid, int pixels_per_thread, cudaStream_t stream);
+cudaError_t launch_gather4(const LaunchParams& p, dim3 grid, cudaStream_t stream);
 cudaError_t status_word_address(int** out);
 
 }  // namespace fkb

@@ -31,7 +31,7 @@ def op(code: int, v=(0.0, 0.0, 0.0), slot: int = -1) -> abi.Op:
 
 
 def chain(src_format, geometry, dst_format, write_kind, ops, n_pre_ops=0, ccm=None, yuv_sub=None, border=0, border_at=0,
-          border_value=(0.0, 0.0, 0.0), ccm2=None, yuv_add=None) -> abi.ChainDesc:
+          border_value=(0.0, 0.0, 0.0), ccm2=None, yuv_add=None, op_w=None) -> abi.ChainDesc:
     ch = abi.ChainDesc()
     ch.src_format, ch.geometry, ch.dst_format, ch.write_kind = src_format, geometry, dst_format, write_kind
     ch.n_ops, ch.n_pre_ops = len(ops), n_pre_ops
@@ -46,7 +46,12 @@ def chain(src_format, geometry, dst_format, write_kind, ops, n_pre_ops=0, ccm=No
     if yuv_add is not None:
         ch.yuv_add[:] = yuv_add
     ch.border, ch.border_at = border, border_at
-    ch.border_value[:] = border_value
+    ch.border_value[:] = border_value[:3]
+    if len(border_value) > 3:
+        ch.border_value_w = border_value[3]
+    if op_w is not None:  # four-channel chains: the fourth operand of each op
+        for i, wv in enumerate(op_w):
+            ch.op_w[i] = float(np.float32(wv))
     return ch
 
 
@@ -109,7 +114,9 @@ class Workload:
             d.dst_channel_stride = s.dst_channel_stride
             if s.dst_planes:
                 d.dst_y, d.dst_z = dst_addrs[s.dst] + s.dst_planes[0], dst_addrs[s.dst] + s.dst_planes[1]
-            d.bg[:] = s.bg
+            d.bg[:] = s.bg[:3]
+            if len(s.bg) > 3:
+                d.bg_w = s.bg[3]
             d.chain = s.chain | (abi.PLANE_DEFAULT if s.default else 0)
             for k, pv in enumerate(s.params):
                 d.params[k][:] = pv
@@ -132,7 +139,7 @@ class Workload:
             ch = self.chains[s.chain]
             uyvy = ch.src_format == abi.PIX_UYVY
             nv12 = ch.src_format in (abi.PIX_NV12, abi.PIX_NV21) or uyvy  # one luma byte per pixel, one chroma pair per 2 (x2) pixels
-            elt = 12 if ch.dst_format == abi.PIX_F32C3 else 3
+            elt = {abi.PIX_F32C3: 12, abi.PIX_U8C3: 3, abi.PIX_F32C4: 16, abi.PIX_U8C4: 4}[ch.dst_format]
             out_bytes += s.dst_w * s.dst_h * elt
             if s.default or ch.border:
                 continue
@@ -309,6 +316,31 @@ def bgra_crops(swap=False, w=320, h=200, dst=(96, 80), seed=18) -> Workload:
     planes = [PlaneSpec(i, 0, i * dw * dh * 12, w, h, pitch, r, dw, dh, dw * 12) for i, r in enumerate(rects)]
     return Workload("bgra_crops", [ch], [_frame(seed + i, pitch * h) for i in range(4)], [4 * dw * dh * 12], planes,
                     "uchar4 frames, alpha discarded" + (" swap" if swap else ""), extra={"swap": swap, "rects": rects})
+
+
+RGBA_RECTS = ((0, 0, 120, 40), (100, 200, 60, 40), (400, 20, 30, 50), (1000, 800, 30, 30), (40, 40, 40, 40))
+
+
+def rgba_crops(reorder=False, f32=False, w=1920, h=1080, dst=(64, 64), rects=RGBA_RECTS, seed=19, border=0) -> Workload:
+    """The four-channel pipeline of the reference's compiler-explorer example: one uchar4 frame, five crops -> Resize ->
+    Mul -> Add -> [Mul 255 -> [BGRA2RGBA] -> SaturateCast -> TensorWrite<uchar4> | [BGRA2RGBA] -> TensorWrite<float4>]."""
+    pitch = _pitch(w * 4, 16)
+    dw, dh = dst
+    m1, a1 = (0.33 / 255.0, 0.5 / 255.0, 1.0 / 255.0, 0.25 / 255.0), (0.5, 0.25, 0.0, 0.125)
+    ops, op_w = [op(abi.OP_MUL, m1[:3]), op(abi.OP_ADD, a1[:3])], [m1[3], a1[3]]
+    if not f32:
+        ops.append(op(abi.OP_MUL, (255.0,) * 3)); op_w.append(255.0)
+    if reorder:
+        ops.append(op(abi.OP_REORDER_ZYX)); op_w.append(0.0)
+    if not f32:
+        ops.append(op(abi.OP_SATCAST_U8)); op_w.append(0.0)
+    elt = 16 if f32 else 4
+    ch = chain(abi.PIX_U8C4, abi.GEOM_RESIZE_IGNORE_AR, abi.PIX_F32C4 if f32 else abi.PIX_U8C4, abi.WRITE_PACKED, ops, op_w=op_w,
+               border=border, border_value=(9.0, 99.0, 199.0, 250.0))
+    planes = [PlaneSpec(0, 0, i * dw * dh * elt, w, h, pitch, (x & 0xffffffff, y & 0xffffffff, cw, chh), dw, dh, dw * elt)
+              for i, (x, y, cw, chh) in enumerate(rects)]
+    return Workload("rgba_crops", [ch], [_frame(seed, pitch * h)], [len(rects) * dw * dh * elt], planes,
+                    f"four channels reorder={reorder} f32={f32}", extra={"reorder": reorder, "f32": f32, "m1": m1, "a1": a1, "rects": rects})
 
 
 def conditional_resize(used=5, w=320, h=180, dst=(96, 64), default=(7, 200, 33), seed=11) -> Workload:

@@ -67,7 +67,12 @@ enum { FKB_PIX_U8C3 = 1, FKB_PIX_F32C3 = 2, FKB_PIX_NV12 = 3,
         * channel is dropped, as ColorConversion<COLOR_BGRA2BGR | COLOR_RGBA2RGB> = Discard does (color_conversion.h:448-452;
         * with the BGRA2RGB / RGBA2BGR codes, :460-464, the chain also carries FKB_OP_REORDER_ZYX).  Where in the chain the
         * reference discards the channel does not change the other three: every op here acts per channel. */
-       FKB_PIX_U8C4 = 6 };
+       FKB_PIX_U8C4 = 6,
+       /* Four-channel chains: a chain whose dst_format is U8C4 or F32C4 keeps all four channels of its U8C4 source to the
+        * Write (PerThreadRead<_2D,uchar4> ... TensorWrite<uchar4 | float4>, e.g. tests/examples/compiler_explorer_example.h:23-46).
+        * Its ops are Cast, Mul / Add / Sub / Div (fourth operands in op_w / params_w), BGRA<->RGBA (FKB_OP_REORDER_ZYX leaves the
+        * fourth channel in place: VectorReorder<T,2,1,0,3>, color_conversion.h:472-476) and SaturateCast; the write is PACKED. */
+       FKB_PIX_F32C4 = 7 };
 
 /* Geometry of the ReadBack stage.  The crop rectangle is always applied (a chain without Crop
  * passes the whole frame as the rectangle).  NONE: output pixel (x,y) reads crop pixel (x,y).
@@ -142,6 +147,8 @@ typedef struct fkb_chain_desc {
     uint32_t border_at;   /* ops[0..border_at) sit before the BorderReader (border_at <= n_pre_ops with a RESIZE
                              geometry): CONSTANT's value replaces their result, the later ops still run on it */
     float border_value[3];
+    float op_w[FKB_MAX_OPS]; /* four-channel chains: the fourth operand of ops[i] (v holds the first three) */
+    float border_value_w;    /* four-channel chains: the fourth channel of border_value */
 } fkb_chain_desc;
 
 typedef struct fkb_plane_desc {
@@ -168,6 +175,8 @@ typedef struct fkb_plane_desc {
     float params[FKB_MAX_PLANE_PARAMS][3]; /* operands of ops whose plane_slot >= 0 */
     void* dst_y;             /* FKB_WRITE_SPLIT_PLANES: first byte of the second (FKB_WRITE_NV12/NV21: of the chroma rows) ... */
     void* dst_z;             /* ... and of the third channel plane; else unused */
+    float bg_w;              /* four-channel chains: the fourth channel of bg ... */
+    float params_w[FKB_MAX_PLANE_PARAMS]; /* ... and of params[slot] */
 } fkb_plane_desc;
 
 /* Fills plane->fx, fy, x1, y1, x2, y2 from plane->crop_w/crop_h (the size of the back operation) and
@@ -204,7 +213,7 @@ int fkb_launch_transform(const fkb_chain_desc* chain, const fkb_plane_desc* plan
  * entry point instead keeps them in a fixed array that is part of the library image on every GPU, and calls neither
  * cudaMalloc / cudaMallocHost / cudaFree nor any other allocating routine, on the device or on the host.
  *   - Limit: at most FKB_NOALLOC_MAX_PLANES planes per call; more returns FKB_ERR_TOO_LARGE and launches nothing.
- *   - Cost: FKB_NOALLOC_MAX_PLANES * 192 bytes (768 KB) of device memory on each GPU that loads the library, and the
+ *   - Cost: FKB_NOALLOC_MAX_PLANES * 224 bytes (896 KB) of device memory on each GPU that loads the library, and the
  *     same again in host memory, until the process exits, whether or not this entry point is ever called.
  *   - The first call on a device looks up the array's device address (one cudaGetSymbolAddress, with that device
  *     current).  Make that first call before any stream capture begins.

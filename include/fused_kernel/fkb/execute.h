@@ -70,20 +70,23 @@ struct Lowered {
 
     Lowered(const ReadIOp<OutT, BATCH>& r, const WriteIOp<WT>& w) : st(r.st), wr(w) {
         static_assert(std::is_same_v<OutT, WT>, "the Write's InputType is not the OutputType of the last operation");
-        static_assert(std::is_same_v<WT, uchar3> || std::is_same_v<WT, float3>, "uchar3 and float3 are the pixel types the B200 kernels write");
+        static_assert(std::is_same_v<WT, uchar3> || std::is_same_v<WT, float3> || std::is_same_v<WT, uchar4> || std::is_same_v<WT, float4>,
+                      "uchar3, float3, uchar4 and float4 are the pixel types the B200 kernels write");
         n_planes = r.params.activeThreads.z;
         chain.src_format = st.src_format;
         chain.geometry = !st.has_resize ? FKB_GEOM_NONE
                        : st.ar == AspectRatio::IGNORE_AR ? FKB_GEOM_RESIZE_IGNORE_AR
                        : st.ar == AspectRatio::PRESERVE_AR_RN_EVEN ? FKB_GEOM_RESIZE_PRESERVE_AR_RN_EVEN
                        : st.ar == AspectRatio::PRESERVE_AR_LEFT ? FKB_GEOM_RESIZE_PRESERVE_AR_LEFT : FKB_GEOM_RESIZE_PRESERVE_AR;
-        chain.dst_format = std::is_same_v<WT, float3> ? FKB_PIX_F32C3 : FKB_PIX_U8C3;
+        chain.dst_format = std::is_same_v<WT, float3> ? FKB_PIX_F32C3 : std::is_same_v<WT, uchar3> ? FKB_PIX_U8C3
+                         : std::is_same_v<WT, float4> ? FKB_PIX_F32C4 : FKB_PIX_U8C4;
         chain.write_kind = wr.write_kind;
         if (st.ops.size() > FKB_MAX_OPS) check(FKB_ERR_UNSUPPORTED);
         chain.n_ops = static_cast<uint32_t>(st.ops.size());
         chain.n_pre_ops = static_cast<uint32_t>(st.has_resize ? st.n_pre_ops : 0);
         chain.border = st.border; chain.border_at = static_cast<uint32_t>(st.border_at);
         for (int i = 0; i < 3; ++i) chain.border_value[i] = st.border_value[i];
+        chain.border_value_w = st.border_value[3];
         for (int i = 0; i < 9; ++i) chain.ccm2[i] = st.ccm2[i];
         for (int i = 0; i < 3; ++i) chain.yuv_add[i] = st.yuv_add[i];
         for (int i = 0; i < 9; ++i) chain.ccm[i] = st.ccm[i];
@@ -102,6 +105,7 @@ struct Lowered {
             chain.ops[k].code = op.code;
             chain.ops[k].plane_slot = static_cast<int16_t>(slot);
             for (int c = 0; c < 3; ++c) chain.ops[k].v[c] = op.v[0][c];
+            chain.op_w[k] = op.v[0][3];
         }
     }
 
@@ -126,14 +130,14 @@ struct Lowered {
         d.dst_pitch = wr.pitch;
         d.dst_channel_stride = wr.channel_stride;
         d.dst_y = wr.data_y; d.dst_z = wr.data_z;
-        d.bg[0] = st.bg[0]; d.bg[1] = st.bg[1]; d.bg[2] = st.bg[2];
+        d.bg[0] = st.bg[0]; d.bg[1] = st.bg[1]; d.bg[2] = st.bg[2]; d.bg_w = st.bg[3];
         d.chain = chain_index;
         if (st.used_planes >= 0 && z >= static_cast<uint32_t>(st.used_planes)) {
             d.chain |= FKB_PLANE_DEFAULT;
-            d.bg[0] = st.dflt[0]; d.bg[1] = st.dflt[1]; d.bg[2] = st.dflt[2];
+            d.bg[0] = st.dflt[0]; d.bg[1] = st.dflt[1]; d.bg[2] = st.dflt[2]; d.bg_w = st.dflt[3];
         }
         for (size_t k = 0; k < st.ops.size(); ++k)
-            if (op_slot[k] >= 0) { const auto& v = pick(st.ops[k].v); for (int c = 0; c < 3; ++c) d.params[op_slot[k]][c] = v[c]; }
+            if (op_slot[k] >= 0) { const auto& v = pick(st.ops[k].v); for (int c = 0; c < 3; ++c) d.params[op_slot[k]][c] = v[c]; d.params_w[op_slot[k]] = v[3]; }
         if (st.has_resize && !(d.chain & FKB_PLANE_DEFAULT)) check(fkb_resize_params(chain.geometry, &d));
         return d;
     }

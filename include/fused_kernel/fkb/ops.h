@@ -29,13 +29,13 @@ enum class AspectRatio { PRESERVE_AR = 0, IGNORE_AR = 1, PRESERVE_AR_RN_EVEN = 2
 enum class BorderType : int { CONSTANT = 0, REPLICATE = 1, REFLECT = 2, WRAP = 3, REFLECT_101 = 4, TRANSPARENT_ = 5, DEFAULT = REFLECT_101, ISOLATED = 16 };
 enum class PlanePolicy { PROCESS_ALL = 0, CONDITIONAL_WITH_DEFAULT = 1 };  // batch_operations.h:75
 // (color_conversion.h:408-426; the codes that discard the alpha channel of a four-channel source are the ones beside BGR<->RGB)
-enum class ColorConversionCodes { COLOR_BGR2RGB, COLOR_RGB2BGR, COLOR_BGRA2BGR, COLOR_RGBA2RGB, COLOR_BGRA2RGB, COLOR_RGBA2BGR };
+enum class ColorConversionCodes { COLOR_BGR2RGB, COLOR_RGB2BGR, COLOR_BGRA2BGR, COLOR_RGBA2RGB, COLOR_BGRA2RGB, COLOR_RGBA2BGR, COLOR_BGRA2RGBA, COLOR_RGBA2BGRA };
 
 namespace detail {
 struct SrcPlane { const void* data{nullptr}; uint pitch{0}, w{0}, h{0}; };
 struct OpRec {
     uint16_t code{0};
-    std::vector<std::array<float, 3>> v;  // one operand per plane, or a single one shared by all planes
+    std::vector<std::array<float, 4>> v;  // one operand per plane, or a single one shared by all planes (fourth component: four-channel chains)
 };
 // Everything a chain knows before its Write: the run-time image of the reference's fused Read IOp.
 struct ReadState {
@@ -45,7 +45,7 @@ struct ReadState {
     bool has_resize{false};
     AspectRatio ar{AspectRatio::IGNORE_AR};
     Size dst_size;
-    float bg[3]{0.f, 0.f, 0.f};
+    float bg[4]{0.f, 0.f, 0.f, 0.f};
     std::vector<OpRec> ops;
     size_t n_pre_ops{0};         // ops that were chained before the Resize run on the taps
     float ccm[9]{};
@@ -54,13 +54,15 @@ struct ReadState {
     float yuv_add[3]{};
     // BatchRead<CONDITIONAL_WITH_DEFAULT>: planes >= used_planes yield dflt instead of reading (-1: every plane reads)
     int used_planes{-1};
-    float dflt[3]{0.f, 0.f, 0.f};
+    float dflt[4]{0.f, 0.f, 0.f, 0.f};
     // BorderReader between the first border_at ops and the Crop (0 = none, else FKB_BORDER_*)
     uint32_t border{0};
     size_t border_at{0};
-    float border_value[3]{0.f, 0.f, 0.f};
+    float border_value[4]{0.f, 0.f, 0.f, 0.f};
 };
-inline std::array<float, 3> f3(const float3& v) { return {v.x, v.y, v.z}; }
+inline std::array<float, 4> f3(const float3& v, float w = 0.f) { return {v.x, v.y, v.z, w}; }
+// fourth component of a vector value, or 0 for the three-channel types
+template <typename V> float w_of(const V& v) { if constexpr (cn<V> == 4) return static_cast<float>(v.w); else return 0.f; }
 template <typename T, typename = void> struct has_read_state : std::false_type {};
 template <typename T> struct has_read_state<T, std::void_t<decltype(std::declval<T>().st)>> : std::true_type {};
 }  // namespace detail
@@ -74,6 +76,7 @@ struct ComputeIOp {
     float3 params{0.f, 0.f, 0.f};
     float ccm[9]{};
     float yuv_sub[3]{};
+    float w{0.f};  // fourth operand (four-channel chains)
 };
 template <typename T> constexpr bool isComputeIOp = false;
 template <uint16_t C, typename I, typename O> constexpr bool isComputeIOp<ComputeIOp<C, I, O>> = true;
@@ -89,7 +92,11 @@ struct Cast {
     struct Name {                                                                                                     \
         static_assert((std::is_same_v<I, float3> || std::is_same_v<I, float4>) && std::is_same_v<P, I> && std::is_same_v<O, I>,      \
                       "the B200 kernels implement " #Name "<float3> (and " #Name "<float4> ahead of a discarded alpha channel)");   \
-        static constexpr auto build(const I& params) { return ComputeIOp<CODE, I, O>{float3{params.x, params.y, params.z}}; }     \
+        static constexpr auto build(const I& params) {                                                                            \
+            ComputeIOp<CODE, I, O> op{float3{params.x, params.y, params.z}};                                                      \
+            if constexpr (cn<I> == 4) op.w = params.w;                                                                            \
+            return op;                                                                                                            \
+        }                                                                                                                         \
     };
 FKB_BINARY_OP(Mul, FKB_OP_MUL)
 FKB_BINARY_OP(Add, FKB_OP_ADD)
@@ -98,7 +105,8 @@ FKB_BINARY_OP(Div, FKB_OP_DIV)
 #undef FKB_BINARY_OP
 template <typename I, typename O>
 struct SaturateCast {
-    static_assert(std::is_same_v<I, float3> && std::is_same_v<O, uchar3>, "the B200 kernels implement SaturateCast<float3,uchar3>");
+    static_assert((std::is_same_v<I, float3> && std::is_same_v<O, uchar3>) || (std::is_same_v<I, float4> && std::is_same_v<O, uchar4>),
+                  "the B200 kernels implement SaturateCast<float3,uchar3> and SaturateCast<float4,uchar4>");
     static constexpr auto build() { return ComputeIOp<FKB_OP_SATCAST_U8, I, O>{}; }
 };
 // A step of a chain that changes the pixel type without arithmetic (the alpha channel of a uchar4 / float4 is dropped)
@@ -110,10 +118,13 @@ struct RetypeIOp {
 };
 template <ColorConversionCodes CODE, typename I, typename O = I>
 struct ColorConversion {
-    static constexpr bool swap3 = CODE == ColorConversionCodes::COLOR_BGR2RGB || CODE == ColorConversionCodes::COLOR_RGB2BGR;
+    static constexpr bool swap4 = CODE == ColorConversionCodes::COLOR_BGRA2RGBA || CODE == ColorConversionCodes::COLOR_RGBA2BGRA;
+    static constexpr bool swap3 = CODE == ColorConversionCodes::COLOR_BGR2RGB || CODE == ColorConversionCodes::COLOR_RGB2BGR || swap4;
     static constexpr bool drop = !swap3;
-    static_assert(!swap3 || (std::is_same_v<I, O> && (std::is_same_v<I, float3> || std::is_same_v<I, uchar3>)),
+    static_assert(!swap3 || swap4 || (std::is_same_v<I, O> && (std::is_same_v<I, float3> || std::is_same_v<I, uchar3>)),
                   "BGR<->RGB on uchar3 or float3 is the three-channel colour conversion the B200 kernels implement");
+    static_assert(!swap4 || (std::is_same_v<I, O> && (std::is_same_v<I, float4> || std::is_same_v<I, uchar4>)),
+                  "BGRA<->RGBA takes uchar4 or float4 and leaves the fourth channel in place");
     static_assert(!drop || (std::is_same_v<I, uchar4> && std::is_same_v<O, uchar3>) || (std::is_same_v<I, float4> && std::is_same_v<O, float3>),
                   "BGRA2BGR / RGBA2RGB / BGRA2RGB / RGBA2BGR take uchar4 -> uchar3 or float4 -> float3");
     static constexpr auto build() {
@@ -151,7 +162,7 @@ struct ConvertRGBToYUV {
 // ---- BorderReader (algorithms/image_processing/border_reader.h) ------------------------------------------------
 struct BorderIOp {
     uint32_t mode;     // FKB_BORDER_*
-    float value[3];    // CONSTANT only
+    float value[4];    // CONSTANT only
 };
 template <BorderType BT>
 struct BorderReader {
@@ -160,7 +171,7 @@ struct BorderReader {
     static constexpr uint32_t mode = static_cast<uint32_t>(BT) + 1u;
     static auto build() {
         static_assert(BT != BorderType::CONSTANT, "BorderReader<CONSTANT> needs its value: build(value)");
-        return BorderIOp{mode, {0.f, 0.f, 0.f}};
+        return BorderIOp{mode, {0.f, 0.f, 0.f, 0.f}};
     }
     // build(value): the incomplete CONSTANT reader; build(readIOp): the complete form of the other modes
     template <typename A>
@@ -169,7 +180,7 @@ struct BorderReader {
             return a.then(build());
         } else {
             static_assert(BT == BorderType::CONSTANT, "only BorderReader<CONSTANT> takes a value");
-            return BorderIOp{mode, {static_cast<float>(a.x), static_cast<float>(a.y), static_cast<float>(a.z)}};
+            return BorderIOp{mode, {static_cast<float>(a.x), static_cast<float>(a.y), static_cast<float>(a.z), detail::w_of(a)}};
         }
     }
     template <typename R, typename V>
@@ -191,6 +202,7 @@ struct ResizeIOp {
     AspectRatio ar;
     Size dst_size;
     float3 bg;
+    float bg_w{0.f};  // fourth channel of the background (four-channel chains)
 };
 template <InterpolationType IT = InterpolationType::INTER_LINEAR, AspectRatio AR = AspectRatio::IGNORE_AR, typename DefaultType = void>
 struct Resize {
@@ -200,6 +212,9 @@ struct Resize {
         return ResizeIOp{AR, dstSize, float3{0.f, 0.f, 0.f}};
     }
     static auto build(const Size& dstSize, const float3& backgroundValue) { return ResizeIOp{AR, dstSize, backgroundValue}; }
+    static auto build(const Size& dstSize, const float4& backgroundValue) {
+        return ResizeIOp{AR, dstSize, float3{backgroundValue.x, backgroundValue.y, backgroundValue.z}, backgroundValue.w};
+    }
 };
 
 // ---- Read IOps -------------------------------------------------------------------------------------------------
@@ -231,7 +246,7 @@ struct ReadIOp {
             throw std::runtime_error("a BorderReader directly on the Read (before any Crop or Resize) is the placement the B200 kernels implement");
         detail::ReadState s = st;
         s.border = b.mode; s.border_at = s.ops.size();
-        for (int c = 0; c < 3; ++c) s.border_value[c] = b.value[c];
+        for (int c = 0; c < 4; ++c) s.border_value[c] = b.value[c];
         return ReadIOp<OutT, BATCH>(std::move(s));
     }
     template <size_t N>
@@ -255,7 +270,7 @@ struct ReadIOp {
         if (st.has_resize) throw std::runtime_error("two Resize operations in one chain are not implemented by the B200 kernels");
         detail::ReadState s = st;
         s.has_resize = true; s.ar = r.ar; s.dst_size = r.dst_size;
-        s.bg[0] = r.bg.x; s.bg[1] = r.bg.y; s.bg[2] = r.bg.z;
+        s.bg[0] = r.bg.x; s.bg[1] = r.bg.y; s.bg[2] = r.bg.z; s.bg[3] = r.bg_w;
         s.n_pre_ops = s.ops.size();
         return ReadIOp<std::conditional_t<cn<OutT> == 4, float4, float3>, BATCH>(std::move(s));  // the interpolation returns float_<cn>
     }
@@ -263,7 +278,7 @@ struct ReadIOp {
     auto then(const RetypeIOp<I, O>& r) const {
         static_assert(std::is_same_v<I, OutT>, "the operation's InputType is not the OutputType of the operation before it");
         detail::ReadState s = st;
-        if (r.reorder) s.ops.push_back(detail::OpRec{FKB_OP_REORDER_ZYX, {{0.f, 0.f, 0.f}}});
+        if (r.reorder) s.ops.push_back(detail::OpRec{FKB_OP_REORDER_ZYX, {{0.f, 0.f, 0.f, 0.f}}});
         return ReadIOp<O, BATCH>(std::move(s));
     }
     template <uint16_t C, typename I, typename O>
@@ -273,7 +288,7 @@ struct ReadIOp {
         // the reference's fuser rebuilds a batch of fused per-plane reads here with PROCESS_ALL (iop_fuser.h:89-95):
         // a conditional batch read stops being conditional when a compute operation is fused into it
         s.used_planes = -1;
-        s.ops.push_back(detail::OpRec{C, {detail::f3(op.params)}});
+        s.ops.push_back(detail::OpRec{C, {detail::f3(op.params, op.w)}});
         if (C == FKB_OP_YUV2RGB) { for (int i = 0; i < 9; ++i) s.ccm[i] = op.ccm[i]; for (int i = 0; i < 3; ++i) s.yuv_sub[i] = op.yuv_sub[i]; }
         if (C == FKB_OP_RGB2YUV) { for (int i = 0; i < 9; ++i) s.ccm2[i] = op.ccm[i]; for (int i = 0; i < 3; ++i) s.yuv_add[i] = op.yuv_sub[i]; }
         return ReadIOp<O, BATCH>(std::move(s));
@@ -311,6 +326,7 @@ struct PerThreadRead {
         auto r = build(ptrs);
         r.st.used_planes = usedPlanes;
         r.st.dflt[0] = static_cast<float>(defaultValue.x); r.st.dflt[1] = static_cast<float>(defaultValue.y); r.st.dflt[2] = static_cast<float>(defaultValue.z);
+        r.st.dflt[3] = detail::w_of(defaultValue);
         return r;
     }
 };

@@ -75,6 +75,8 @@ def load_ref() -> C.CDLL:
         lib.fklref_rgb_to_ycbcr_matrix.argtypes = [C.c_int, C.c_int, f32p]
         lib.fklref_rgb_to_yuv_image.restype = C.c_int
         lib.fklref_rgb_to_yuv_image.argtypes = [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int]
+        lib.fklref_rgba_crops.restype = C.c_int
+        lib.fklref_rgba_crops.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, i32p, C.c_int, C.c_int, f32p, f32p, C.c_int, C.c_int, C.c_void_p]
         lib.fklref_bgra_crop_resize_f32.restype = C.c_int
         lib.fklref_bgra_crop_resize_f32.argtypes = [pp, C.c_int, C.c_int, C.c_int, i32p, C.c_int, C.c_int, f32p, C.c_int, C.c_void_p]
         lib.fklref_resize_split_planes.restype = C.c_int
@@ -220,6 +222,11 @@ def run_ref(wl, threads: int = 1):
                                          outs[0].ctypes.data, p0.dst_pitch)
         if rc == -1:
             raise ValueError("the reference runner has no instantiation for this format / range / primitives")
+    elif wl.name == "rgba_crops":
+        flat = [v for r in wl.extra["rects"] for v in r]
+        m1, a1 = (C.c_float * 4)(*wl.extra["m1"]), (C.c_float * 4)(*wl.extra["a1"])
+        rc = lib.fklref_rgba_crops(wl.sources[0].ctypes.data, p0.src_w, p0.src_h, p0.src_pitch, (C.c_int32 * 20)(*flat), p0.dst_w, p0.dst_h,
+                                   m1, a1, 1 if wl.extra["reorder"] else 0, 1 if wl.extra["f32"] else 0, outs[0].ctypes.data)
     elif wl.name == "bgra_crops":
         flat = [v for r in wl.extra["rects"] for v in r]
         rc = lib.fklref_bgra_crop_resize_f32(frame_ptrs(wl.planes), p0.src_w, p0.src_h, p0.src_pitch, (C.c_int32 * 16)(*flat),

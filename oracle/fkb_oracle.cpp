@@ -41,8 +41,10 @@
 namespace {
 
 struct V3 {
-    float c[3];
+    float c[4] = {0.f, 0.f, 0.f, 0.f};  // three channels, or four for the chains that keep the alpha channel (the fourth is ignored otherwise)
 };
+// channels a chain carries: four when its destination is uchar4 / float4
+inline int channels(const fkb_chain_desc& ch) { return (ch.dst_format == FKB_PIX_U8C4 || ch.dst_format == FKB_PIX_F32C4) ? 4 : 3; }
 
 // round-half-away-from-zero, as cxp::round (core/constexpr_libs/constexpr_cmath.h:354-385)
 inline float round_half_away(float v) {
@@ -79,22 +81,25 @@ inline uint8_t sat_u8(float s) {
     return static_cast<uint8_t>(rounded);
 }
 
-inline void operand(const fkb_op& op, const fkb_plane_desc& pl, float o[3]) {
+inline void operand(const fkb_chain_desc& ch, uint32_t i, const fkb_plane_desc& pl, float o[4]) {
+    const fkb_op& op = ch.ops[i];
     const float* s = op.plane_slot >= 0 ? pl.params[op.plane_slot] : op.v;
     o[0] = s[0]; o[1] = s[1]; o[2] = s[2];
+    o[3] = op.plane_slot >= 0 ? pl.params_w[op.plane_slot] : ch.op_w[i];
 }
 
 inline V3 apply_ops(V3 v, const fkb_chain_desc& ch, const fkb_plane_desc& pl, uint32_t first, uint32_t last) {
     for (uint32_t i = first; i < last; ++i) {
         const fkb_op& op = ch.ops[i];
-        float p[3];
+        const int nc = channels(ch);
+        float p[4];
         switch (op.code) {
         case FKB_OP_CAST_F32:  // static_cast<float>(uchar): exact
             break;
-        case FKB_OP_MUL: operand(op, pl, p); for (int c = 0; c < 3; ++c) v.c[c] = v.c[c] * p[c]; break;
-        case FKB_OP_ADD: operand(op, pl, p); for (int c = 0; c < 3; ++c) v.c[c] = v.c[c] + p[c]; break;
-        case FKB_OP_SUB: operand(op, pl, p); for (int c = 0; c < 3; ++c) v.c[c] = v.c[c] - p[c]; break;
-        case FKB_OP_DIV: operand(op, pl, p); for (int c = 0; c < 3; ++c) v.c[c] = v.c[c] / p[c]; break;
+        case FKB_OP_MUL: operand(ch, i, pl, p); for (int c = 0; c < nc; ++c) v.c[c] = v.c[c] * p[c]; break;
+        case FKB_OP_ADD: operand(ch, i, pl, p); for (int c = 0; c < nc; ++c) v.c[c] = v.c[c] + p[c]; break;
+        case FKB_OP_SUB: operand(ch, i, pl, p); for (int c = 0; c < nc; ++c) v.c[c] = v.c[c] - p[c]; break;
+        case FKB_OP_DIV: operand(ch, i, pl, p); for (int c = 0; c < nc; ++c) v.c[c] = v.c[c] / p[c]; break;
         case FKB_OP_REORDER_ZYX: { const float t = v.c[0]; v.c[0] = v.c[2]; v.c[2] = t; break; }
         case FKB_OP_YUV2RGB: {
             const float a = v.c[0] - ch.yuv_sub[0], b = v.c[1] - ch.yuv_sub[1], d = v.c[2] - ch.yuv_sub[2];
@@ -114,7 +119,7 @@ inline V3 apply_ops(V3 v, const fkb_chain_desc& ch, const fkb_plane_desc& pl, ui
             break;
         }
         case FKB_OP_SATCAST_U8:
-            for (int c = 0; c < 3; ++c) v.c[c] = static_cast<float>(sat_u8(v.c[c]));
+            for (int c = 0; c < nc; ++c) v.c[c] = static_cast<float>(sat_u8(v.c[c]));
             break;
         default: break;
         }
@@ -143,7 +148,7 @@ inline V3 read_frame(const fkb_chain_desc& ch, const fkb_plane_desc& pl, size_t 
         v.c[2] = g[2];
     } else if (ch.src_format == FKB_PIX_U8C4) {  // uchar4 whose alpha is discarded (Discard<uchar4,uchar3>, color_conversion.h:448-452)
         const uint8_t* p = base + Y * pl.src_pitch + X * 4;
-        v.c[0] = p[0]; v.c[1] = p[1]; v.c[2] = p[2];
+        v.c[0] = p[0]; v.c[1] = p[1]; v.c[2] = p[2]; v.c[3] = p[3];
     } else {
         const uint8_t* p = base + Y * pl.src_pitch + X * 3;
         v.c[0] = p[0]; v.c[1] = p[1]; v.c[2] = p[2];
@@ -189,7 +194,7 @@ inline V3 tap(const fkb_chain_desc& ch, const fkb_plane_desc& pl, int cx, int cy
         if (X >= 0 && X < w && Y >= 0 && Y < h) {
             v = apply_ops(read_frame(ch, pl, static_cast<size_t>(X), static_cast<size_t>(Y)), ch, pl, 0, ch.border_at);
         } else {
-            v.c[0] = ch.border_value[0]; v.c[1] = ch.border_value[1]; v.c[2] = ch.border_value[2];
+            v.c[0] = ch.border_value[0]; v.c[1] = ch.border_value[1]; v.c[2] = ch.border_value[2]; v.c[3] = ch.border_value_w;
         }
         return apply_ops(v, ch, pl, ch.border_at, n_tap_ops);
     }
@@ -202,7 +207,7 @@ inline V3 pixel(const fkb_chain_desc& ch, const fkb_plane_desc& pl, int x, int y
         // a plane beyond usedPlanes of BatchRead<CONDITIONAL_WITH_DEFAULT> (batch_operations.h:262-266): the read —
         // including a Resize fused into it (iop_fuser.h:71-88) — yields the default value; the later ops still run
         V3 d;
-        d.c[0] = pl.bg[0]; d.c[1] = pl.bg[1]; d.c[2] = pl.bg[2];
+        d.c[0] = pl.bg[0]; d.c[1] = pl.bg[1]; d.c[2] = pl.bg[2]; d.c[3] = pl.bg_w;
         return apply_ops(d, ch, pl, ch.geometry == FKB_GEOM_NONE ? 0 : ch.n_pre_ops, ch.n_ops);
     }
     if (ch.geometry == FKB_GEOM_NONE) {
@@ -216,7 +221,7 @@ inline V3 pixel(const fkb_chain_desc& ch, const fkb_plane_desc& pl, int x, int y
         tx = x - pl.x1; ty = y - pl.y1;
     }
     if (!inside) {
-        v.c[0] = pl.bg[0]; v.c[1] = pl.bg[1]; v.c[2] = pl.bg[2];
+        v.c[0] = pl.bg[0]; v.c[1] = pl.bg[1]; v.c[2] = pl.bg[2]; v.c[3] = pl.bg_w;
     } else {
         const float sx = tx * pl.fx, sy = ty * pl.fy;
         int x1 = static_cast<int>(std::floor(sx)), y1 = static_cast<int>(std::floor(sy));
@@ -231,7 +236,7 @@ inline V3 pixel(const fkb_chain_desc& ch, const fkb_plane_desc& pl, int x, int y
         const V3 p11 = tap(ch, pl, x2r, y2r, ch.n_pre_ops);
         const float w00 = (x2 - sx) * (y2 - sy), w10 = (sx - x1) * (y2 - sy);
         const float w01 = (x2 - sx) * (sy - y1), w11 = (sx - x1) * (sy - y1);
-        for (int c = 0; c < 3; ++c)
+        for (int c = 0; c < channels(ch); ++c)
             v.c[c] = (p00.c[c] * w00) + (p10.c[c] * w10) + (p01.c[c] * w01) + (p11.c[c] * w11);
     }
     return apply_ops(v, ch, pl, ch.n_pre_ops, ch.n_ops);
@@ -243,7 +248,15 @@ void run_plane(const fkb_chain_desc& ch, const fkb_plane_desc& pl) {
         for (uint32_t x = 0; x < pl.dst_w; ++x) {
             const V3 v = pixel(ch, pl, static_cast<int>(x), static_cast<int>(y));
             uint8_t* row = dst + static_cast<size_t>(y) * pl.dst_pitch;
-            if (ch.write_kind >= FKB_WRITE_NV12) {  // WriteYUV::exec (color_conversion.h:309-383)
+            if (channels(ch) == 4) {  // PerThreadWrite / TensorWrite of uchar4 or float4
+                if (ch.dst_format == FKB_PIX_F32C4) {
+                    float* q = reinterpret_cast<float*>(row) + static_cast<size_t>(x) * 4;
+                    for (int c = 0; c < 4; ++c) q[c] = v.c[c];
+                } else {
+                    uint8_t* q = row + static_cast<size_t>(x) * 4;
+                    for (int c = 0; c < 4; ++c) q[c] = static_cast<uint8_t>(v.c[c]);
+                }
+            } else if (ch.write_kind >= FKB_WRITE_NV12) {  // WriteYUV::exec (color_conversion.h:309-383)
                 const uint8_t yy = static_cast<uint8_t>(v.c[0]), cb = static_cast<uint8_t>(v.c[1]), cr = static_cast<uint8_t>(v.c[2]);
                 if (ch.write_kind == FKB_WRITE_UYVY) {
                     uint8_t* g = row + static_cast<size_t>(x >> 1) * 4;

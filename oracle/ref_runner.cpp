@@ -265,6 +265,34 @@ int fklref_bgra_crop_resize_f32(const uint8_t* const* frames, int w, int h, int 
                 : bgra_crop_resize<ColorConversionCodes::COLOR_BGRA2BGR>(frames, w, h, pitch, rects, dw, dh, mul, out);
 }
 
+// The four-channel pipeline of tests/examples/compiler_explorer_example.h:23-46 on one uchar4 frame and five crops:
+// Crop -> Resize -> Mul x2 -> Add -> Mul -> [BGRA2RGBA] -> SaturateCast -> TensorWrite<uchar4>, or without the SaturateCast into
+// a float4 tensor.
+int fklref_rgba_crops(const uint8_t* frame, int w, int h, int pitch, const int32_t* rects, int dw, int dh, const float* m1, const float* a1,
+                      int reorder, int f32, void* out) {
+    CpuStream stream;
+    const Ptr2D<uchar4> input(reinterpret_cast<uchar4*>(const_cast<uint8_t*>(frame)), w, h, pitch, MemType::Host, 0);
+    std::array<Rect, 5> rs;
+    for (size_t i = 0; i < 5; ++i) rs[i] = Rect(rects[4 * i], rects[4 * i + 1], rects[4 * i + 2], rects[4 * i + 3]);
+    const auto read = PerThreadRead<ND::_2D, uchar4>::build(input);
+    const auto crop = Crop<>::build(rs);
+    const auto resize = Resize<InterpolationType::INTER_LINEAR>::build(Size(dw, dh));
+    const auto mul = Mul<float4>::build(make_<float4>(m1[0], m1[1], m1[2], m1[3]));
+    const auto add = Add<float4>::build(make_<float4>(a1[0], a1[1], a1[2], a1[3]));
+    const auto mul255 = Mul<float4>::build(make_set<float4>(255.f));
+    if (f32) {
+        Tensor<float4> t(static_cast<float4*>(out), dw, dh, 5, 1, MemType::Host, 0);
+        if (reorder) executeOperations<CpuDPP>(stream, read, crop, resize, mul, add, ColorConversion<ColorConversionCodes::COLOR_BGRA2RGBA, float4, float4>::build(), TensorWrite<float4>::build(t));
+        else executeOperations<CpuDPP>(stream, read, crop, resize, mul, add, TensorWrite<float4>::build(t));
+    } else {
+        Tensor<uchar4> t(static_cast<uchar4*>(out), dw, dh, 5, 1, MemType::Host, 0);
+        if (reorder) executeOperations<CpuDPP>(stream, read, crop, resize, mul, add, mul255, ColorConversion<ColorConversionCodes::COLOR_BGRA2RGBA, float4, float4>::build(),
+                                               SaturateCast<float4, uchar4>::build(), TensorWrite<uchar4>::build(t));
+        else executeOperations<CpuDPP>(stream, read, crop, resize, mul, add, mul255, SaturateCast<float4, uchar4>::build(), TensorWrite<uchar4>::build(t));
+    }
+    return 0;
+}
+
 // Four frames -> Resize(IGNORE_AR) -> Mul -> TensorTSplit<float3> into a colour-plane-transposed tensor
 // (memory_operations.h:214-241): all R planes, then all G planes, then all B planes.
 int fklref_resize_tsplit_f32(const uint8_t* const* frames, int w, int h, int pitch, int dw, int dh, const float* mul, float* out) {

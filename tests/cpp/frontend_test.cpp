@@ -336,6 +336,48 @@ static void test_bgra_source() {
     report("uchar4 source, alpha discarded (BGRA2RGB)", std::memcmp(want.data(), out.ptrPinned().data, want.size() * 4) == 0);
 }
 
+// ---- four channels to the end: the pipeline of the reference's compiler-explorer example ----------------------------------
+static void test_four_channels() {
+    Stream stream;
+    Ptr2D<uchar4> input(1920, 1080);
+    {
+        const auto h = input.ptrPinned();
+        std::mt19937 rng(900);
+        for (uint y = 0; y < 1080; ++y) for (uint x = 0; x < 1920 * 4; ++x) reinterpret_cast<uint8_t*>(h.data)[y * h.dims.pitch + x] = rng() & 255;
+    }
+    input.upload(stream);
+    const std::array<Rect, 5> crops{Rect(0, 0, 120, 40), Rect(100, 200, 60, 40), Rect(400, 20, 30, 50), Rect(1000, 800, 30, 30), Rect(40, 40, 40, 40)};
+    Tensor<uchar4> output(64, 64, 5);
+    executeOperations<TransformDPP<>>(input, stream, Crop<>::build(crops), Resize<InterpolationType::INTER_LINEAR>::build(Size(64, 64)),
+                                      Mul<float4>::build(make_set<float4>(1.f / 255.f)), Mul<float4>::build(make_set<float4>(0.33f)),
+                                      Add<float4>::build(make_<float4>(0.5f, 0.25f, 0.125f, 0.f)), Mul<float4>::build(make_set<float4>(255.f)),
+                                      ColorConversion<ColorConversionCodes::COLOR_BGRA2RGBA, float4, float4>::build(),
+                                      SaturateCast<float4, uchar4>::build(), TensorWrite<uchar4>::build(output));
+    output.download(stream);
+    stream.sync();
+    fkb_chain_desc ch{};
+    ch.src_format = FKB_PIX_U8C4; ch.geometry = FKB_GEOM_RESIZE_IGNORE_AR; ch.dst_format = FKB_PIX_U8C4; ch.write_kind = FKB_WRITE_PACKED;
+    ch.n_ops = 6;
+    ch.ops[0] = op(FKB_OP_MUL, 1.f / 255.f, 1.f / 255.f, 1.f / 255.f); ch.op_w[0] = 1.f / 255.f;
+    ch.ops[1] = op(FKB_OP_MUL, 0.33f, 0.33f, 0.33f); ch.op_w[1] = 0.33f;
+    ch.ops[2] = op(FKB_OP_ADD, 0.5f, 0.25f, 0.125f); ch.op_w[2] = 0.f;
+    ch.ops[3] = op(FKB_OP_MUL, 255.f, 255.f, 255.f); ch.op_w[3] = 255.f;
+    ch.ops[4] = op(FKB_OP_REORDER_ZYX); ch.ops[5] = op(FKB_OP_SATCAST_U8);
+    std::vector<uint8_t> want(64 * 64 * 4 * 5);
+    std::vector<fkb_plane_desc> planes;
+    const auto r = input.ptrPinned();
+    for (size_t i = 0; i < 5; ++i) {
+        fkb_plane_desc d{};
+        d.src = r.data; d.src_pitch = r.dims.pitch; d.src_w = 1920; d.src_h = 1080;
+        d.crop_x = crops[i].x; d.crop_y = crops[i].y; d.crop_w = crops[i].width; d.crop_h = crops[i].height;
+        d.dst = want.data() + i * 64 * 64 * 4; d.dst_w = 64; d.dst_h = 64; d.dst_pitch = 64 * 4;
+        fkb_oracle_resize_params(ch.geometry, &d);
+        planes.push_back(d);
+    }
+    fkb_oracle_run(&ch, 1, planes.data(), 5, 1);
+    report("four channels to the Write (uchar4 -> uchar4 tensor)", std::memcmp(want.data(), output.ptrPinned().data, want.size()) == 0);
+}
+
 // ---- transposed planar tensor: TensorTSplit<float3> ---------------------------------------------------------------------
 static void test_tensor_t_split() {
     Stream stream;
@@ -460,6 +502,7 @@ int main() {
     test_conditional_batch();
     test_tensor_t_split();
     test_bgra_source();
+    test_four_channels();
     test_write_yuv();
     test_split_write();
     test_border<BorderType::CONSTANT>("BorderReader<CONSTANT> (complete form, operator&)");

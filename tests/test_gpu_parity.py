@@ -76,6 +76,10 @@ SMALL = {
     "divergent": lambda: W.divergent_planes(n_per_seq=4, w=480, h=270),
     "divergent_odd": lambda: W.divergent_planes(n_per_seq=3, w=330, h=190),
     "crop_reorder": lambda: W.crop_reorder(n=5),
+    "rgba_crops": lambda: W.rgba_crops(),
+    "rgba_crops_f32_reorder": lambda: W.rgba_crops(reorder=True, f32=True, w=333, h=211, dst=(77, 45), rects=((0, 0, 333, 211), (5, 7, 100, 90), (300, 180, 33, 31))),
+    "rgba_crops_border": lambda: W.rgba_crops(w=200, h=120, dst=(64, 48), rects=((-20, -10, 90, 70), (150, 90, 120, 80), (10, 10, 50, 40)), border=abi.BORDER_CONSTANT),
+    "rgba_crops_border_wrap": lambda: W.rgba_crops(f32=True, w=200, h=120, dst=(64, 48), rects=((-20, -10, 90, 70), (150, 90, 120, 80)), border=abi.BORDER_WRAP),
     "bgra_crops": lambda: W.bgra_crops(),
     "batched_uchar4": lambda: W.batched_crop_resize(n_frames=4, crops_per_frame=8, w=960, h=540, src4=True),
     "bgra_crops_swap": lambda: W.bgra_crops(swap=True, w=333, h=97, dst=(111, 50)),

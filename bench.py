@@ -220,6 +220,7 @@ def other_configs(torch, steps: int, peak: float, widened: bool = False) -> dict
         # YCbCr destinations), each on a launch large enough to time
         cases = [
             ("uchar4_batched_crop_resize", lambda: W.batched_crop_resize(n_frames=8, crops_per_frame=32, src4=True)),
+            ("four_channel_crops", lambda: W.rgba_crops(dst=(224, 224), rects=tuple((30 * i, 15 * i, 200 + 8 * i, 160 + 4 * i) for i in range(32)))),
             ("border_replicate_crops", lambda: W.border_crops(abi.BORDER_REPLICATE, w=1920, h=1080, dst=(224, 224))),
             ("nv21_limited_bt601_preprocess", lambda: W.nv12_preprocess(src_format=abi.PIX_NV21, colour=(abi.RANGE_LIMITED, abi.PRIMITIVES_BT601))),
             ("uyvy_preprocess", lambda: W.nv12_preprocess(src_format=abi.PIX_UYVY, colour=(abi.RANGE_FULL, abi.PRIMITIVES_BT709))),

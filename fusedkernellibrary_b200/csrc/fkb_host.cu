@@ -56,8 +56,9 @@ int check_ops(const fkb_chain_desc& ch, uint32_t first, uint32_t last, ValueType
 }
 
 int check_chain(const fkb_chain_desc& ch) {
+    const bool float_src = ch.src_format == FKB_PIX_F32C3 || ch.src_format == FKB_PIX_F32P3;
     if (ch.src_format != FKB_PIX_U8C3 && ch.src_format != FKB_PIX_NV12 && ch.src_format != FKB_PIX_NV21 &&
-        ch.src_format != FKB_PIX_UYVY && ch.src_format != FKB_PIX_U8C4) return FKB_ERR_UNSUPPORTED;
+        ch.src_format != FKB_PIX_UYVY && ch.src_format != FKB_PIX_U8C4 && !float_src) return FKB_ERR_UNSUPPORTED;
     const bool four = ch.dst_format == FKB_PIX_U8C4 || ch.dst_format == FKB_PIX_F32C4;  // the chain keeps four channels
     if (ch.dst_format != FKB_PIX_U8C3 && ch.dst_format != FKB_PIX_F32C3 && !four) return FKB_ERR_UNSUPPORTED;
     if (four) {
@@ -71,7 +72,7 @@ int check_chain(const fkb_chain_desc& ch) {
     if (ch.n_ops > FKB_MAX_OPS || ch.n_pre_ops > ch.n_ops) return FKB_ERR_INVALID;
     if (ch.border > FKB_BORDER_REFLECT_101) return FKB_ERR_UNSUPPORTED;
     if (ch.border && ch.border_at > (ch.geometry == FKB_GEOM_NONE ? ch.n_ops : ch.n_pre_ops)) return FKB_ERR_INVALID;
-    ValueType t = VT_U8;  // both reads produce uchar3
+    ValueType t = float_src ? VT_F32 : VT_U8;  // the byte reads produce uchar3, the tensor reads float3
     int rc;
     if (ch.geometry == FKB_GEOM_NONE) {
         if ((rc = check_ops(ch, 0, ch.n_ops, t)) != FKB_OK) return rc;
@@ -88,13 +89,15 @@ int check_plane(const fkb_chain_desc& ch, const fkb_plane_desc& pl) {
     const bool dflt = (pl.chain & FKB_PLANE_DEFAULT) != 0;  // the read yields bg: no source is touched
     if ((!dflt && !pl.src) || !pl.dst) return FKB_ERR_NULL;
     const bool nv12 = ch.src_format == FKB_PIX_NV12 || ch.src_format == FKB_PIX_NV21;  // luma plane + interleaved chroma rows
+    const bool float_src = ch.src_format == FKB_PIX_F32C3 || ch.src_format == FKB_PIX_F32P3;
     const bool uyvy = ch.src_format == FKB_PIX_UYVY;
     if (!dflt) {
-        if (nv12 && !pl.src_chroma) return FKB_ERR_NULL;
+        if ((nv12 || ch.src_format == FKB_PIX_F32P3) && !pl.src_chroma) return FKB_ERR_NULL;
+        if (float_src && ((reinterpret_cast<uintptr_t>(pl.src) & 3) || (reinterpret_cast<uintptr_t>(pl.src_chroma) & 3) || (pl.src_pitch & 3))) return FKB_ERR_INVALID;
         if (pl.src_w == 0 || pl.src_h == 0) return FKB_ERR_INVALID;
         const uint64_t src_row = nv12 ? ((static_cast<uint64_t>(pl.src_w) + 1) / 2) * 2
                                  : uyvy ? ((static_cast<uint64_t>(pl.src_w) + 1) / 2) * 4
-                                 : static_cast<uint64_t>(pl.src_w) * (ch.src_format == FKB_PIX_U8C4 ? 4 : 3);
+                                 : static_cast<uint64_t>(pl.src_w) * (ch.src_format == FKB_PIX_F32C3 ? 12 : (ch.src_format == FKB_PIX_U8C4 || ch.src_format == FKB_PIX_F32P3) ? 4 : 3);
         if (pl.src_pitch < src_row) return FKB_ERR_INVALID;
         if (pl.crop_w <= 0 || pl.crop_h <= 0) return FKB_ERR_INVALID;
         if (ch.border) {

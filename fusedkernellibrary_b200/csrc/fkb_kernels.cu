@@ -43,6 +43,14 @@ __device__ __forceinline__ void read_frame_global(const fkb_chain_desc& ch, cons
         o[0] = static_cast<float>(__ldg(g + 1 + 2 * (X & 1)));
         o[1] = static_cast<float>(__ldg(g));
         o[2] = static_cast<float>(__ldg(g + 2));
+    } else if (ch.src_format == FKB_PIX_F32C3) {
+        const float* q = reinterpret_cast<const float*>(pl.src + Y * pl.src_pitch) + X * 3;
+        o[0] = __ldg(q); o[1] = __ldg(q + 1); o[2] = __ldg(q + 2);
+    } else if (ch.src_format == FKB_PIX_F32P3) {
+        const size_t step = static_cast<size_t>(pl.src_chroma - pl.src);  // bytes between channel planes
+        const uint8_t* q = pl.src + Y * pl.src_pitch + X * 4;
+        o[0] = __ldg(reinterpret_cast<const float*>(q)); o[1] = __ldg(reinterpret_cast<const float*>(q + step));
+        o[2] = __ldg(reinterpret_cast<const float*>(q + 2 * step));
     } else if (ch.src_format == FKB_PIX_U8C4) {
         const uint8_t* q = pl.src + Y * pl.src_pitch + X * 4;  // the alpha byte is not read
         o[0] = static_cast<float>(__ldg(q));

@@ -515,3 +515,58 @@ def random_workload(seed: int, max_dim: int = 260) -> Workload:
                                 chroma_offset=pitch * h))
         off += _pitch(total, int(rs.choice([4, 16, 256])))
     return Workload(f"random_{seed}", [ch], [src], [off], planes, "random launch")
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# CircularTensor::update (core/data/circular_tensor.h:111-161) as one divergent launch
+# ---------------------------------------------------------------------------------------------------------------
+def circular_update_launch(kind, oldest_first, first, batch, frame_addr, frame_w, frame_h, frame_pitch, dw, dh, mul, temp_addr, out_addr):
+    """Descriptors of one update of a circular tensor of ``batch`` planes of dw x dh float pixels.
+
+    kind 0: packed float3 planes (TensorWrite<float3>); 1: planar channels per plane (TensorSplit<float3>); 2: the
+    colour-plane-transposed tensor (TensorTSplit<float3>).  The update sequence (frame -> Resize IGNORE_AR -> Mul -> write)
+    runs twice: into plane ``first``-derived of the temporary tensor (the reference's mid-chain CircularTensorWrite) and into
+    its plane of the output; the copy sequence moves the other batch - 1 planes from the temporary tensor to the output in
+    circular order.  Returns (chain array, plane array, next ``first``)."""
+    packed = kind == 0
+    px = dw * dh
+    if packed:
+        plane_step, chan_step, pitch, wk, copy_src = px * 12, 0, dw * 12, abi.WRITE_PACKED, abi.PIX_F32C3
+    elif kind == 1:
+        plane_step, chan_step, pitch, wk, copy_src = px * 12, px * 4, dw * 4, abi.WRITE_SPLIT, abi.PIX_F32P3
+    else:
+        plane_step, chan_step, pitch, wk, copy_src = px * 4, px * 4 * batch, dw * 4, abi.WRITE_SPLIT, abi.PIX_F32P3
+    update = chain(abi.PIX_U8C3, abi.GEOM_RESIZE_IGNORE_AR, abi.PIX_F32C3, wk, [op(abi.OP_MUL, mul)])
+    copy = chain(copy_src, abi.GEOM_NONE, abi.PIX_F32C3, wk, [])
+    chains = (abi.ChainDesc * 2)(update, copy)
+    lib = abi.load()
+    planes = []
+
+    def dst(d, base, z):
+        d.dst = base + z * plane_step
+        d.dst_w, d.dst_h, d.dst_pitch, d.dst_channel_stride = dw, dh, pitch, chan_step
+
+    # where the new image goes: (z + first) mod batch in the temporary tensor, z in the output (z = the update sequence's plane)
+    zu = batch - 1 if oldest_first else 0
+    for base, z in ((temp_addr, (zu + first) % batch), (out_addr, zu)):
+        d = abi.PlaneDesc()
+        d.src, d.src_pitch, d.src_w, d.src_h = frame_addr, frame_pitch, frame_w, frame_h
+        d.crop_x, d.crop_y, d.crop_w, d.crop_h = 0, 0, frame_w, frame_h
+        dst(d, base, z)
+        d.chain = 0
+        lib.fkb_resize_params(abi.GEOM_RESIZE_IGNORE_AR, C.byref(d))
+        planes.append(d)
+    for z in range(batch):
+        if z == zu:
+            continue
+        zs = (z + first) % batch if oldest_first else (first - z) % batch  # Ascendent / Descendent read (memory_operations.h:423-431)
+        d = abi.PlaneDesc()
+        d.src = temp_addr + zs * plane_step
+        d.src_chroma = d.src + chan_step if not packed else None
+        d.src_pitch, d.src_w, d.src_h = pitch, dw, dh
+        d.crop_x, d.crop_y, d.crop_w, d.crop_h = 0, 0, dw, dh
+        dst(d, out_addr, z)
+        d.chain = 1
+        planes.append(d)
+    arr = (abi.PlaneDesc * len(planes))(*planes)
+    return chains, arr, (first + 1) % batch

@@ -72,7 +72,12 @@ enum { FKB_PIX_U8C3 = 1, FKB_PIX_F32C3 = 2, FKB_PIX_NV12 = 3,
         * Write (PerThreadRead<_2D,uchar4> ... TensorWrite<uchar4 | float4>, e.g. tests/examples/compiler_explorer_example.h:23-46).
         * Its ops are Cast, Mul / Add / Sub / Div (fourth operands in op_w / params_w), BGRA<->RGBA (FKB_OP_REORDER_ZYX leaves the
         * fourth channel in place: VectorReorder<T,2,1,0,3>, color_conversion.h:472-476) and SaturateCast; the write is PACKED. */
-       FKB_PIX_F32C4 = 7 };
+       FKB_PIX_F32C4 = 7,
+       /* Float sources: FKB_PIX_F32C3 as src_format is a packed float3 image or tensor plane (TensorRead<float3>,
+        * memory_operations.h:243-262); FKB_PIX_F32P3 is three float planes, channel c at src + c * (src_chroma - src)
+        * (TensorPack / TensorTPack, memory_operations.h:264-330).  They feed chains that start in float: the copy sequence
+        * of CircularTensor::update (core/data/circular_tensor.h:111-161) is such a chain without ops. */
+       FKB_PIX_F32P3 = 8 };
 
 /* Geometry of the ReadBack stage.  The crop rectangle is always applied (a chain without Crop
  * passes the whole frame as the rectangle).  NONE: output pixel (x,y) reads crop pixel (x,y).

@@ -75,6 +75,8 @@ def load_ref() -> C.CDLL:
         lib.fklref_rgb_to_ycbcr_matrix.argtypes = [C.c_int, C.c_int, f32p]
         lib.fklref_rgb_to_yuv_image.restype = C.c_int
         lib.fklref_rgb_to_yuv_image.argtypes = [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int]
+        lib.fklref_circular_updates.restype = C.c_int
+        lib.fklref_circular_updates.argtypes = [pp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, f32p, C.c_int, C.c_int, C.c_void_p]
         lib.fklref_rgba_crops.restype = C.c_int
         lib.fklref_rgba_crops.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, i32p, C.c_int, C.c_int, f32p, f32p, C.c_int, C.c_int, C.c_void_p]
         lib.fklref_bgra_crop_resize_f32.restype = C.c_int

@@ -146,6 +146,14 @@ inline V3 read_frame(const fkb_chain_desc& ch, const fkb_plane_desc& pl, size_t 
         v.c[0] = (X & 1) ? g[3] : g[1];
         v.c[1] = g[0];
         v.c[2] = g[2];
+    } else if (ch.src_format == FKB_PIX_F32C3) {  // TensorRead<float3> / PerThreadRead<float3>
+        const float* p = reinterpret_cast<const float*>(base + Y * pl.src_pitch) + X * 3;
+        v.c[0] = p[0]; v.c[1] = p[1]; v.c[2] = p[2];
+    } else if (ch.src_format == FKB_PIX_F32P3) {  // TensorPack / TensorTPack: one float plane per channel
+        const size_t step = static_cast<size_t>(static_cast<const uint8_t*>(pl.src_chroma) - base);
+        const uint8_t* p = base + Y * pl.src_pitch + X * 4;
+        v.c[0] = *reinterpret_cast<const float*>(p); v.c[1] = *reinterpret_cast<const float*>(p + step);
+        v.c[2] = *reinterpret_cast<const float*>(p + 2 * step);
     } else if (ch.src_format == FKB_PIX_U8C4) {  // uchar4 whose alpha is discarded (Discard<uchar4,uchar3>, color_conversion.h:448-452)
         const uint8_t* p = base + Y * pl.src_pitch + X * 4;
         v.c[0] = p[0]; v.c[1] = p[1]; v.c[2] = p[2]; v.c[3] = p[3];

@@ -18,9 +18,11 @@
 #include <fused_kernel/algorithms/image_processing/resize.h>
 #include <fused_kernel/algorithms/image_processing/saturate.h>
 #include <fused_kernel/fused_kernel.h>
+#include <fused_kernel/core/data/circular_tensor.h>
 
 #include <array>
 #include <cstdint>
+#include <cstring>
 #include <functional>
 #include <thread>
 #include <vector>
@@ -182,6 +184,42 @@ static int bgra_crop_resize(const uint8_t* const* frames, int w, int h, int pitc
         Resize<InterpolationType::INTER_LINEAR, AspectRatio::IGNORE_AR>::build(Size(dw, dh)), ColorConversion<CODE, float4, float3>::build(),
         Mul<float3>::build(make_<float3>(mul[0], mul[1], mul[2])), TensorWrite<float3>::build(t));
     return 0;
+}
+
+// CircularTensor<float, 3, 4, ORDER, MODE>::update (core/data/circular_tensor.h:111-161), n_updates times: frame k ->
+// Resize(IGNORE_AR) -> Mul -> write into the circular tensor.  kind: 0 TensorWrite<float3> (Standard, packed float3 planes),
+// 1 TensorSplit<float3> (Standard, planar), 2 TensorTSplit<float3> (Transposed).  The tensor's bytes after the last update
+// are copied to `out`.
+template <CircularTensorOrder ORDER>
+static int circular_updates(const uint8_t* const* frames, int n_updates, int w, int h, int pitch, int dw, int dh, const float* mul, int kind, void* out) {
+    CpuStream stream;
+    const auto resize = Resize<InterpolationType::INTER_LINEAR, AspectRatio::IGNORE_AR>::build(Size(dw, dh));
+    const auto m = Mul<float3>::build(make_<float3>(mul[0], mul[1], mul[2]));
+    if (kind == 0) {
+        CircularTensor<float3, 1, 4, ORDER, ColorPlanes::Standard> ct(dw, dh, MemType::Host, 0);
+        std::memset(ct.ptr().data, 0, ct.sizeInBytes());
+        for (int k = 0; k < n_updates; ++k)
+            ct.update(stream, PerThreadRead<ND::_2D, uchar3>::build(wrap_frame(frames[k], w, h, pitch)), resize, m, TensorWrite<float3>::build(ct.ptr()));
+        std::memcpy(out, ct.ptr().data, ct.sizeInBytes());
+    } else if (kind == 1) {
+        CircularTensor<float, 3, 4, ORDER, ColorPlanes::Standard> ct(dw, dh, MemType::Host, 0);
+        std::memset(ct.ptr().data, 0, ct.sizeInBytes());
+        for (int k = 0; k < n_updates; ++k)
+            ct.update(stream, PerThreadRead<ND::_2D, uchar3>::build(wrap_frame(frames[k], w, h, pitch)), resize, m, TensorSplit<float3>::build(ct.ptr()));
+        std::memcpy(out, ct.ptr().data, ct.sizeInBytes());
+    } else {
+        CircularTensor<float, 3, 4, ORDER, ColorPlanes::Transposed> ct(dw, dh, MemType::Host, 0);
+        std::memset(ct.ptr().data, 0, ct.sizeInBytes());
+        for (int k = 0; k < n_updates; ++k)
+            ct.update(stream, PerThreadRead<ND::_2D, uchar3>::build(wrap_frame(frames[k], w, h, pitch)), resize, m, TensorTSplit<float3>::build(ct.ptr()));
+        std::memcpy(out, ct.ptr().data, ct.sizeInBytes());
+    }
+    return 0;
+}
+extern "C" int fklref_circular_updates(const uint8_t* const* frames, int n_updates, int w, int h, int pitch, int dw, int dh, const float* mul,
+                                       int kind, int oldest_first, void* out) {
+    return oldest_first ? circular_updates<CircularTensorOrder::OldestFirst>(frames, n_updates, w, h, pitch, dw, dh, mul, kind, out)
+                        : circular_updates<CircularTensorOrder::NewestFirst>(frames, n_updates, w, h, pitch, dw, dh, mul, kind, out);
 }
 
 extern "C" {

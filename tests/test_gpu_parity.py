@@ -198,6 +198,33 @@ def test_plan_relaunches_leave_the_item_counters_clean():
     dw.close()
 
 
+@pytest.mark.parametrize("kind", [0, 1, 2])
+@pytest.mark.parametrize("oldest_first", [0, 1])
+def test_circular_tensor_updates(kind, oldest_first):
+    # nine updates of a four-plane circular tensor, each one divergent launch (update sequence + copy sequence reading float
+    # planes), device against the CPU checker after every update
+    lib, orc = abi.load(), oracle.load_oracle()
+    w, h, dw, dh, batch = 320, 180, 96, 64, 4
+    pitch = w * 3
+    frames = [np.random.RandomState(70 + k).randint(0, 256, pitch * h, dtype=np.uint8) for k in range(9)]
+    mul = (0.5, 1.0, 2.0)
+    size = batch * dw * dh * 12
+    h_temp, h_out = np.zeros(size, np.uint8), np.zeros(size, np.uint8)
+    d_temp, d_out = torch.zeros(size, dtype=torch.uint8, device="cuda"), torch.zeros(size, dtype=torch.uint8, device="cuda")
+    d_frames = [torch.from_numpy(f).cuda() for f in frames]
+    first_h = first_d = 0
+    for k in range(9):
+        ch, pl, first_h = W.circular_update_launch(kind, oldest_first, first_h, batch, frames[k].ctypes.data, w, h, pitch, dw, dh, mul,
+                                                   h_temp.ctypes.data, h_out.ctypes.data)
+        assert orc.fkb_oracle_run(ch, 2, pl, len(pl), 1) == 0
+        ch, pl, first_d = W.circular_update_launch(kind, oldest_first, first_d, batch, d_frames[k].data_ptr(), w, h, pitch, dw, dh, mul,
+                                                   d_temp.data_ptr(), d_out.data_ptr())
+        assert lib.fkb_launch_divergent(ch, 2, pl, len(pl), torch.cuda.current_stream().cuda_stream) == abi.OK
+        torch.cuda.synchronize()
+        assert np.array_equal(d_out.cpu().numpy(), h_out) and np.array_equal(d_temp.cpu().numpy(), h_temp), (kind, oldest_first, k)
+    assert lib.fkb_device_status() == abi.OK
+
+
 def test_many_planes_use_the_descriptor_arena():
     # more planes than fit in the kernel parameters: descriptors travel through the pinned/device ring
     wl = W.batched_crop_resize(n_frames=3, crops_per_frame=100, w=320, h=240, dst=(32, 24), crop_range=(4, 100))

@@ -174,6 +174,29 @@ def test_oracle_matches_reference_backend(wl):
         assert np.array_equal(g, w)
 
 
+@pytest.mark.skipif(not oracle.have_ref(), reason="reference-backed checker not built")
+@pytest.mark.parametrize("kind", [0, 1, 2])          # TensorWrite<float3>, TensorSplit<float3>, TensorTSplit<float3>
+@pytest.mark.parametrize("oldest_first", [0, 1])
+def test_circular_tensor_updates_match_reference(kind, oldest_first):
+    # CircularTensor<.., BATCH = 4>::update of the reference, n times, against the same updates written as divergent launches
+    # (n >= BATCH: before that the reference copies planes of its uninitialised temporary tensor)
+    lib, ref = oracle.load_oracle(), oracle.load_ref()
+    w, h, dw, dh, batch = 160, 90, 48, 32, 4
+    pitch = w * 3
+    frames = [np.random.RandomState(50 + k).randint(0, 256, pitch * h, dtype=np.uint8) for k in range(9)]
+    mul = (0.5, 1.0, 2.0)
+    for n in (4, 6, 9):
+        temp, out, first = np.zeros(batch * dw * dh * 12, np.uint8), np.zeros(batch * dw * dh * 12, np.uint8), 0
+        for k in range(n):
+            chains, planes, first = W.circular_update_launch(kind, oldest_first, first, batch, frames[k].ctypes.data, w, h, pitch, dw, dh, mul,
+                                                             temp.ctypes.data, out.ctypes.data)
+            assert lib.fkb_oracle_run(chains, 2, planes, len(planes), 1) == 0
+        want = np.zeros_like(out)
+        ptrs = (C.c_void_p * n)(*[f.ctypes.data for f in frames[:n]])
+        assert ref.fklref_circular_updates(ptrs, n, w, h, pitch, dw, dh, (C.c_float * 3)(*mul), kind, oldest_first, want.ctypes.data) == 0
+        assert np.array_equal(out, want), (kind, oldest_first, n)
+
+
 def test_oracle_threads_do_not_change_results():
     wl = W.batched_crop_resize(n_frames=2, crops_per_frame=5, w=320, h=240, dst=(64, 64))
     a, b = oracle.run_oracle(wl, threads=1), oracle.run_oracle(wl, threads=4)

@@ -4,3 +4,4 @@
 #include "memory.h"
 #include "ops.h"
 #include "execute.h"
+#include "circular_tensor.h"

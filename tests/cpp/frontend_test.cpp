@@ -378,6 +378,69 @@ static void test_four_channels() {
     report("four channels to the Write (uchar4 -> uchar4 tensor)", std::memcmp(want.data(), output.ptrPinned().data, want.size()) == 0);
 }
 
+// ---- CircularTensor: after n updates plane z holds the chain's result for the z-th newest (or oldest) frame --------------------
+template <CircularTensorOrder ORDER, ColorPlanes MODE>
+static void test_circular(const char* what) {
+    Stream stream;
+    constexpr int BATCH = 4, N = 7;
+    const uint W = 200, H = 120, DW = 80, DH = 48;
+    std::vector<Ptr2D<uchar3>> frames;
+    for (int k = 0; k < N; ++k) { frames.emplace_back(W, H); fill_random(frames[k], 1000 + k); frames[k].upload(stream); }
+    CircularTensor<float, 3, BATCH, ORDER, MODE> ct(DW, DH);
+    const auto resize = Resize<InterpolationType::INTER_LINEAR>::build(Size(DW, DH));
+    const auto mul = Mul<float3>::build(make_<float3>(0.5f, 1.f, 2.f));
+    for (int k = 0; k < N; ++k) {
+        if constexpr (MODE == ColorPlanes::Standard) ct.update(stream, PerThreadRead<ND::_2D, uchar3>::build(frames[k]), resize, mul, TensorSplit<float3>::build(ct.ptr()));
+        else ct.update(stream, PerThreadRead<ND::_2D, uchar3>::build(frames[k]), resize, mul, TensorTSplit<float3>::build(ct.ptr()));
+    }
+    ct.download(stream);
+    stream.sync();
+    // expected: plane z = the chain on frame N-1-z (newest first) or N-BATCH+z (oldest first), computed one plane at a time
+    fkb_chain_desc ch{};
+    ch.src_format = FKB_PIX_U8C3; ch.geometry = FKB_GEOM_RESIZE_IGNORE_AR; ch.dst_format = FKB_PIX_F32C3; ch.write_kind = FKB_WRITE_SPLIT;
+    ch.n_ops = 1; ch.ops[0] = op(FKB_OP_MUL, 0.5f, 1.f, 2.f);
+    const size_t px = static_cast<size_t>(DW) * DH;
+    bool same = true;
+    for (int z = 0; z < BATCH; ++z) {
+        const int k = ORDER == CircularTensorOrder::NewestFirst ? N - 1 - z : N - BATCH + z;
+        std::vector<float> want(px * 3);
+        fkb_plane_desc d = host_plane(frames[k], Rect(0, 0, W, H), DW, DH, want.data(), DW * 4, ch.geometry);
+        d.dst_channel_stride = px * 4;
+        fkb_oracle_run(&ch, 1, &d, 1, 1);
+        const float* got = ct.ptrPinned().data;
+        for (int c = 0; c < 3; ++c) {
+            const float* g = MODE == ColorPlanes::Standard ? got + (static_cast<size_t>(z) * 3 + c) * px : got + (static_cast<size_t>(c) * BATCH + z) * px;
+            same = same && std::memcmp(want.data() + c * px, g, px * 4) == 0;
+        }
+    }
+    report(what, same);
+}
+static void test_circular_packed() {
+    Stream stream;
+    constexpr int BATCH = 3, N = 5;
+    const uint W = 160, H = 90, DW = 64, DH = 40;
+    std::vector<Ptr2D<uchar3>> frames;
+    for (int k = 0; k < N; ++k) { frames.emplace_back(W, H); fill_random(frames[k], 1100 + k); frames[k].upload(stream); }
+    CircularTensor<float3, 1, BATCH, CircularTensorOrder::NewestFirst, ColorPlanes::Standard> ct(DW, DH);
+    for (int k = 0; k < N; ++k)
+        ct.update(stream, PerThreadRead<ND::_2D, uchar3>::build(frames[k]), Resize<InterpolationType::INTER_LINEAR>::build(Size(DW, DH)),
+                  Mul<float3>::build(make_<float3>(2.f, 1.f, 0.5f)), TensorWrite<float3>::build(ct.ptr()));
+    ct.download(stream);
+    stream.sync();
+    fkb_chain_desc ch{};
+    ch.src_format = FKB_PIX_U8C3; ch.geometry = FKB_GEOM_RESIZE_IGNORE_AR; ch.dst_format = FKB_PIX_F32C3; ch.write_kind = FKB_WRITE_PACKED;
+    ch.n_ops = 1; ch.ops[0] = op(FKB_OP_MUL, 2.f, 1.f, 0.5f);
+    const size_t px = static_cast<size_t>(DW) * DH;
+    bool same = true;
+    for (int z = 0; z < BATCH; ++z) {
+        std::vector<float> want(px * 3);
+        fkb_plane_desc d = host_plane(frames[N - 1 - z], Rect(0, 0, W, H), DW, DH, want.data(), DW * 12, ch.geometry);
+        fkb_oracle_run(&ch, 1, &d, 1, 1);
+        same = same && std::memcmp(want.data(), reinterpret_cast<const float*>(ct.ptrPinned().data) + z * px * 3, px * 12) == 0;
+    }
+    report("CircularTensor<float3, 1, 3, NewestFirst> (packed)", same);
+}
+
 // ---- transposed planar tensor: TensorTSplit<float3> ---------------------------------------------------------------------
 static void test_tensor_t_split() {
     Stream stream;
@@ -501,6 +564,11 @@ int main() {
     test_batched<AspectRatio::PRESERVE_AR_LEFT>("batched crop-resize-normalise, PRESERVE_AR_LEFT", FKB_GEOM_RESIZE_PRESERVE_AR_LEFT);
     test_conditional_batch();
     test_tensor_t_split();
+    test_circular<CircularTensorOrder::NewestFirst, ColorPlanes::Standard>("CircularTensor<float, 3, 4, NewestFirst, Standard>");
+    test_circular<CircularTensorOrder::OldestFirst, ColorPlanes::Standard>("CircularTensor<float, 3, 4, OldestFirst, Standard>");
+    test_circular<CircularTensorOrder::NewestFirst, ColorPlanes::Transposed>("CircularTensor<float, 3, 4, NewestFirst, Transposed>");
+    test_circular<CircularTensorOrder::OldestFirst, ColorPlanes::Transposed>("CircularTensor<float, 3, 4, OldestFirst, Transposed>");
+    test_circular_packed();
     test_bgra_source();
     test_four_channels();
     test_write_yuv();

@@ -32,6 +32,27 @@ CASES = {
                                               "crop_range": [8, 300], "seed": 16}),
     "divergent_small": ("divergent_planes", {"n_per_seq": 2, "w": 160, "h": 90, "seed": 17}),
     "crop_reorder_small": ("crop_reorder", {"n": 3, "w": 320, "h": 200, "crop_size": [50, 30], "seed": 18}),
+    # chains beside the five configurations
+    "border_constant": ("border_crops", {"mode": 1, "w": 120, "h": 72, "dst": [48, 40]}),
+    "border_replicate": ("border_crops", {"mode": 2, "w": 120, "h": 72, "dst": [48, 40]}),
+    "border_reflect": ("border_crops", {"mode": 3, "w": 37, "h": 23, "dst": [48, 40]}),
+    "border_wrap": ("border_crops", {"mode": 4, "w": 37, "h": 23, "dst": [48, 40]}),
+    "border_reflect_101": ("border_crops", {"mode": 5, "w": 37, "h": 23, "dst": [48, 40]}),
+    "nv12_border_constant": ("nv12_border_constant", {}),
+    "conditional_resize": ("conditional_resize", {"used": 5, "w": 160, "h": 90, "dst": [48, 32]}),
+    "conditional_pointwise": ("conditional_pointwise", {"used": 3, "w": 100, "h": 20}),
+    "tsplit_resize": ("tsplit_resize", {"w": 150, "h": 85, "dst": [48, 32]}),
+    "split_planes_f32": ("split_planes", {"w": 150, "h": 85, "dst": [52, 32]}),
+    "split_planes_u8": ("split_planes", {"w": 150, "h": 85, "dst": [52, 32], "f32": False}),
+    "nv21_limited_bt709": ("nv12_preprocess", {"w": 320, "h": 180, "dst": [80, 60], "src_format": 4, "colour": [0, 1]}),
+    "uyvy_full_bt2020": ("nv12_preprocess", {"w": 320, "h": 180, "dst": [80, 60], "src_format": 5, "colour": [1, 2]}),
+    "rgb_to_nv12": ("rgb_to_yuv_image", {"fmt": 3, "colour": [0, 0], "w": 162, "h": 90}),
+    "rgb_to_nv21": ("rgb_to_yuv_image", {"fmt": 4, "colour": [0, 2], "w": 162, "h": 90}),
+    "rgb_to_uyvy": ("rgb_to_yuv_image", {"fmt": 5, "colour": [1, 2], "w": 162, "h": 90}),
+    "bgra_crops_swap": ("bgra_crops", {"swap": True, "w": 160, "h": 100, "dst": [48, 40]}),
+    "rgba_crops_u8": ("rgba_crops", {"w": 480, "h": 270, "dst": [32, 32], "rects": [[0, 0, 120, 40], [100, 200, 60, 40], [400, 20, 30, 50], [300, 100, 30, 30], [40, 40, 40, 40]]}),
+    "rgba_crops_f32_reorder": ("rgba_crops", {"reorder": True, "f32": True, "w": 480, "h": 270, "dst": [32, 32],
+                                              "rects": [[0, 0, 120, 40], [100, 200, 60, 40], [400, 20, 30, 50], [300, 100, 30, 30], [40, 40, 40, 40]]}),
 }
 
 
@@ -50,6 +71,8 @@ def input_crc(wl) -> int:
 def main() -> None:
     here = os.path.dirname(os.path.abspath(__file__))
     for name, (factory, kwargs) in CASES.items():
+        if "--missing" in sys.argv and os.path.exists(os.path.join(here, name + ".npz")):
+            continue  # keep the fixtures that exist
         wl = build_case(factory, kwargs)
         outs = oracle.run_ref(wl)
         np.savez_compressed(os.path.join(here, name + ".npz"), factory=factory, kwargs=json.dumps(kwargs),

@@ -113,17 +113,21 @@ __device__ __forceinline__ void apply_ops_bordered(float (&v)[N][3], const fkb_c
 // gather_kernel
 // ---------------------------------------------------------------------------------------------------------
 // PPT pixels per thread: 4 for large launches (vector stores), 1 for small ones (more threads hide the tap latency).
-template <int PPT>
+// INLINE: the plane records are kernel parameters (launches of a few planes): they are read where they lie, through the
+// constant bank, instead of being copied to shared memory first — two block-wide barriers less per plane, which is most
+// of what a launch of a few ten thousand pixels can save.
+template <int PPT, bool INLINE>
 __global__ void __launch_bounds__(256) gather_kernel(const __grid_constant__ LaunchParams p) {
     __shared__ PlaneRec s_pl;
-    const PlaneRec* table = plane_table(p);
     const uint32_t tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     for (uint32_t z = blockIdx.z; z < p.n_planes; z += gridDim.z) {
-        __syncthreads();
-        if (threadIdx.x < sizeof(PlaneRec) / 16)
-            reinterpret_cast<uint4*>(&s_pl)[threadIdx.x] = reinterpret_cast<const uint4*>(table + z)[threadIdx.x];
-        __syncthreads();
-        const PlaneRec& pl = s_pl;
+        if (!INLINE) {
+            __syncthreads();
+            if (threadIdx.x < sizeof(PlaneRec) / 16)
+                reinterpret_cast<uint4*>(&s_pl)[threadIdx.x] = reinterpret_cast<const uint4*>(p.table + z)[threadIdx.x];
+            __syncthreads();
+        }
+        const PlaneRec& pl = INLINE ? p.inline_planes[z] : s_pl;
         if (pl.kclass != KCLASS_GATHER) continue;
         const fkb_chain_desc& ch = p.chains[pl.chain];
         const uint32_t y = blockIdx.y * 8 + ty;
@@ -1290,8 +1294,9 @@ cudaError_t launch_gather4(const LaunchParams& p, dim3 grid, cudaStream_t stream
 }
 
 cudaError_t launch_gather(const LaunchParams& p, dim3 grid, int pixels_per_thread, cudaStream_t stream) {
-    if (pixels_per_thread == 1) gather_kernel<1><<<grid, 256, 0, stream>>>(p);
-    else gather_kernel<4><<<grid, 256, 0, stream>>>(p);
+    const bool inl = p.table == nullptr;
+    if (pixels_per_thread == 1) { if (inl) gather_kernel<1, true><<<grid, 256, 0, stream>>>(p); else gather_kernel<1, false><<<grid, 256, 0, stream>>>(p); }
+    else { if (inl) gather_kernel<4, true><<<grid, 256, 0, stream>>>(p); else gather_kernel<4, false><<<grid, 256, 0, stream>>>(p); }
     return cudaGetLastError();
 }
 

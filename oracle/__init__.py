@@ -123,6 +123,10 @@ def load_ref_cuda() -> C.CDLL:
         lib.fklrefcuda_pointwise_u8.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, f32p, f32p, f32p, C.c_void_p, C.c_int, C.c_void_p]
         lib.fklrefcuda_nv12_resize_split.restype = C.c_int
         lib.fklrefcuda_nv12_resize_split.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, f32p, f32p, C.c_void_p, C.c_void_p]
+        lib.fklrefcuda_readme_crops.restype = C.c_int
+        lib.fklrefcuda_readme_crops.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, i32p, C.c_int, C.c_int, f32p, f32p, f32p, C.c_void_p, C.c_void_p]
+        lib.fklrefcuda_divergent4.restype = C.c_int
+        lib.fklrefcuda_divergent4.argtypes = [pp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, f32p, f32p, C.c_void_p, C.c_void_p, C.c_void_p]
         _ref_cuda = lib
     return _ref_cuda
 
@@ -139,6 +143,18 @@ def ref_cuda_launcher(wl, src_addrs, dst_addrs, stream_ptr):
         bg, mul = _f3(p0.bg), _f3(ch.ops[0].v)
         return lambda: lib.fklrefcuda_crop_resize_f32(frames, p0.src_w, p0.src_h, p0.src_pitch, rects, n, p0.dst_w, p0.dst_h, bg, mul,
                                                       dst_addrs[0], stream_ptr)
+    if wl.name == "readme_crops" and n == 5:
+        flat = [v for s in wl.planes for v in s.crop]
+        rects = (C.c_int32 * len(flat))(*flat)
+        bg, mul, sub = _f3(p0.bg), _f3(ch.ops[0].v), _f3(ch.ops[1].v)
+        return lambda: lib.fklrefcuda_readme_crops(src_addrs[0], p0.src_w, p0.src_h, p0.src_pitch, rects, p0.dst_w, p0.dst_h, bg, mul, sub,
+                                                   dst_addrs[0], stream_ptr)
+    if wl.name == "divergent_planes" and n == 8:
+        frames = (C.c_void_p * n)(*[src_addrs[s.src] for s in wl.planes])
+        scales = (C.c_float * 4)(*[float(x) for x in wl.extra["scales"]])
+        offs = (C.c_float * 4)(*[float(x) for x in wl.extra["offs"]])
+        return lambda: lib.fklrefcuda_divergent4(frames, p0.src_w, p0.src_h, p0.src_pitch, p0.dst_w, p0.dst_h, scales, offs,
+                                                 dst_addrs[0], dst_addrs[1], stream_ptr)
     if wl.name == "vertical_fusion":
         a, b, c = _f3(ch.ops[1].v), _f3(ch.ops[2].v), _f3(ch.ops[3].v)
         return lambda: lib.fklrefcuda_pointwise_u8(src_addrs[0], p0.src_w, p0.src_h, p0.src_pitch, a, b, c, dst_addrs[0], p0.dst_pitch, stream_ptr)

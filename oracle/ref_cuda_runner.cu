@@ -45,9 +45,64 @@ void crop_resize_f32(GpuStream& stream, const uint8_t* const* frames, int w, int
         Resize<InterpolationType::INTER_LINEAR, AspectRatio::PRESERVE_AR>::build(Size(dw, dh), bg), Mul<float3>::build(mul),
         TensorWrite<float3>::build(t));
 }
+// README pipeline: five crops of one frame -> Resize(PRESERVE_AR, bg) -> Mul -> Sub -> SaturateCast -> TensorWrite<uchar3>
+void readme_crops(GpuStream& stream, const uint8_t* frame, int w, int h, int pitch, const int32_t* rects, int dw, int dh, float3 bg, float3 mul,
+                  float3 sub, uint8_t* out) {
+    std::array<Ptr2D<uchar3>, 5> ptrs;
+    std::array<Rect, 5> rs;
+    for (size_t i = 0; i < 5; ++i) { ptrs[i] = wrap(frame, w, h, pitch); rs[i] = Rect(rects[4 * i], rects[4 * i + 1], rects[4 * i + 2], rects[4 * i + 3]); }
+    Tensor<uchar3> t(reinterpret_cast<uchar3*>(out), dw, dh, 5, 1, MemType::Device, 0);
+    executeOperations<GpuDPP>(stream, PerThreadRead<ND::_2D, uchar3>::build(ptrs), Crop<>::build(rs),
+        Resize<InterpolationType::INTER_LINEAR, AspectRatio::PRESERVE_AR>::build(Size(dw, dh), bg), Mul<float3>::build(mul), Sub<float3>::build(sub),
+        SaturateCast<float3, uchar3>::build(), TensorWrite<uchar3>::build(t));
+}
+
+// Divergent batch of 2N planes: planes [0,N) Resize -> SaturateCast -> TensorWrite<uchar3>; planes [N,2N) Cast -> Mul -> Sub fused
+// into each plane's Read -> TensorWrite<float3> by global plane index (executors.h:360-411).
+template <uint N>
+struct SelN { FK_HOST_DEVICE_FUSE uint at(const uint& z) { return z < N ? 0u : 1u; } };
+template <uint N>
+void divergent(GpuStream& stream, const uint8_t* const* frames, int w, int h, int pitch, int dw, int dh, const float* scales, const float* offs,
+               uint8_t* outA, float* outB) {
+    std::array<Ptr2D<uchar3>, N> firstN;
+    for (uint i = 0; i < N; ++i) firstN[i] = wrap(frames[i], w, h, pitch);
+    Tensor<uchar3> tA(reinterpret_cast<uchar3*>(outA), dw, dh, N, 1, MemType::Device, 0);
+    const auto seq0 = buildOperationSequence(PerThreadRead<ND::_2D, uchar3>::build(firstN), Resize<InterpolationType::INTER_LINEAR>::build(Size(dw, dh)),
+                                             SaturateCast<float3, uchar3>::build(), TensorWrite<uchar3>::build(tA));
+    const Ptr2D<uchar3> f0 = wrap(frames[N], w, h, pitch);
+    using FusedRead = decltype(PerThreadRead<ND::_2D, uchar3>::build(f0).then(Cast<uchar3, float3>::build())
+        .then(Mul<float3>::build(make_set<float3>(1.f))).then(Sub<float3>::build(make_set<float3>(0.f))));
+    std::array<FusedRead, 2 * N> reads;
+    for (uint i = 0; i < 2 * N; ++i) {
+        const uint k = i < N ? 0 : i - N;
+        reads[i] = PerThreadRead<ND::_2D, uchar3>::build(wrap(frames[N + k], w, h, pitch)).then(Cast<uchar3, float3>::build())
+            .then(Mul<float3>::build(make_set<float3>(scales[k]))).then(Sub<float3>::build(make_set<float3>(offs[k])));
+    }
+    auto batchRead = BatchRead<PlanePolicy::PROCESS_ALL>::build(reads);
+    batchRead.params.activeThreads.z = N;
+    Tensor<float3> tB(reinterpret_cast<float3*>(outB), w, h, 2 * N, 1, MemType::Device, 0);
+    const auto seq1 = buildOperationSequence(batchRead, TensorWrite<float3>::build(tB));
+    Executor<DivergentBatchTransformDPP<ParArch::GPU_NVIDIA, SelN<N>>>::executeOperations(stream, seq0, seq1);
+}
 }  // namespace
 
 extern "C" {
+
+int fklrefcuda_readme_crops(const uint8_t* frame, int w, int h, int pitch, const int32_t* rects, int dw, int dh, const float* bg, const float* mul,
+                            const float* sub, uint8_t* out, void* cuda_stream) {
+    GpuStream stream(static_cast<cudaStream_t>(cuda_stream));
+    readme_crops(stream, frame, w, h, pitch, rects, dw, dh, make_<float3>(bg[0], bg[1], bg[2]), make_<float3>(mul[0], mul[1], mul[2]),
+                 make_<float3>(sub[0], sub[1], sub[2]), out);
+    return 1;
+}
+
+// frames: 2*4 host-array of device pointers; outA: 4 planes of dw x dh uchar3; outB: 8 planes of w x h float3
+int fklrefcuda_divergent4(const uint8_t* const* frames, int w, int h, int pitch, int dw, int dh, const float* scales, const float* offs,
+                          uint8_t* outA, float* outB, void* cuda_stream) {
+    GpuStream stream(static_cast<cudaStream_t>(cuda_stream));
+    divergent<4>(stream, frames, w, h, pitch, dw, dh, scales, offs, outA, outB);
+    return 1;
+}
 
 // frames/rects are HOST arrays (of device pointers / of ints); out is a device pointer.  n must be a multiple of 32.
 // Returns the number of kernel launches, or -1.

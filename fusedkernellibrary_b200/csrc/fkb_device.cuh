@@ -66,6 +66,7 @@ struct Nv12Consts {
     uint32_t kind;           // post-op shape bits
     uint32_t chain;          // the one chain whose planes take nv12_kernel
     uint32_t preserve_ar, f32, split, slots;
+    uint32_t src_px;      // 0: NV12 / NV21 source (nv12 kernels); 3 or 4: bytes per pixel of a packed byte source (rgb_kernel)
     uint32_t vu;          // NV21: the chroma pairs are stored V,U
     uint32_t pair;        // nv12_pair_kernel's conditions hold (two pixels per thread, reduced colour matrix)
     uint32_t wide_store;  // with `pair`: destinations, pitches and channel strides are multiples of 8 bytes

@@ -243,6 +243,19 @@ void classify(const fkb_chain_desc& ch, PlaneRec& r) {
     r.tiles_x = (r.dst_w + r.tile_w - 1) / r.tile_w;  // tile_h is chosen per launch (rows_per_item)
 }
 
+// Whether a plane can run on rgb_kernel (one pixel per thread, post-ops specialised): a packed byte source, a resampling
+// geometry with nothing but casts ahead of it, a specialisable op shape behind it, and a rectangle inside the frame.
+bool rgb_kernel_takes(const fkb_chain_desc& ch, const PlaneRec& r) {
+    if (ch.src_format != FKB_PIX_U8C3 && ch.src_format != FKB_PIX_U8C4) return false;
+    if (ch.dst_format != FKB_PIX_U8C3 && ch.dst_format != FKB_PIX_F32C3) return false;
+    if (ch.geometry == FKB_GEOM_NONE || ch.write_kind > FKB_WRITE_SPLIT_PLANES || post_kind_of(ch) == 8u || r.src == nullptr) return false;
+    for (uint32_t i = 0; i < ch.n_pre_ops; ++i)
+        if (ch.ops[i].code != FKB_OP_CAST_F32) return false;
+    if (ch.geometry >= FKB_GEOM_RESIZE_PRESERVE_AR && (r.x2 < r.x1 || r.y2 < r.y1)) return false;
+    const int64_t x = static_cast<int32_t>(r.crop_x), y = static_cast<int32_t>(r.crop_y);
+    return x >= 0 && y >= 0 && x + r.crop_w <= static_cast<int64_t>(r.src_w) && y + r.crop_h <= static_cast<int64_t>(r.src_h);
+}
+
 // Output rows a warp processes per item.  Inside an item the next row's footprint is prefetched while the current
 // row is computed, so longer items pipeline better; more items balance better (warps claim them from a counter).  Large
 // launches get about sixteen items per resident warp — measured on the 2048-plane crop-resize launch, 10 to 16 rows per
@@ -378,7 +391,11 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
     // so it goes through the general kernel, one pixel per thread.
     if (total_pixels < tiny_launch_pixels())
         for (uint32_t z = 0; z < n_planes; ++z)
-            if (L.recs[z].kclass != KCLASS_NV12 && L.recs[z].kclass != KCLASS_GATHER4) { L.recs[z].kclass = KCLASS_GATHER; L.recs[z].tiles_x = 0; }
+            if (L.recs[z].kclass != KCLASS_NV12 && L.recs[z].kclass != KCLASS_GATHER4) {
+                // (the one-pixel-per-thread kernel where its conditions hold, else the general kernel)
+                L.recs[z].kclass = (!force_gather() && rgb_kernel_takes(chains[L.recs[z].chain], L.recs[z])) ? KCLASS_NV12 : KCLASS_GATHER;
+                L.recs[z].tiles_x = 0;
+            }
     for (uint32_t z = 0; z < n_planes; ++z) {
         const PlaneRec& r = L.recs[z];
         if (r.kclass == KCLASS_POINT || r.kclass == KCLASS_RESIZE) row_segments += static_cast<uint64_t>(r.tiles_x) * r.dst_h;
@@ -446,7 +463,8 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         // nv12_pair_kernel's conditions: the colour matrix of the YCbCr standards ([s 0 r; s g1 g2; s b 0]), integer
         // offsets, immediate operands, and plane offsets that fit 32 bits
         k.vu = ch.src_format == FKB_PIX_NV21;
-        bool pair = !imm.slots && k.ccm[0] > 0.f && std::isfinite(k.ccm[0]) && k.ccm[3] == k.ccm[0] && k.ccm[6] == k.ccm[0] &&
+        k.src_px = ch.src_format == FKB_PIX_U8C3 ? 3u : ch.src_format == FKB_PIX_U8C4 ? 4u : 0u;
+        bool pair = k.src_px == 0 && !imm.slots && k.ccm[0] > 0.f && std::isfinite(k.ccm[0]) && k.ccm[3] == k.ccm[0] && k.ccm[6] == k.ccm[0] &&
                     k.ccm[1] == 0.f && k.ccm[8] == 0.f;
         for (int i = 0; i < 3; ++i) {
             pair = pair && k.sub[i] >= 0.f && k.sub[i] <= 255.f && k.sub[i] == std::floor(k.sub[i]);

@@ -883,6 +883,42 @@ __global__ void __launch_bounds__(kStagedThreads, 2) staged_kernel(const __grid_
 // the colour matrix and the chain's operands held in registers, no interpretation.  The conversion runs on each tap
 // before the interpolation, which is what the reference computes when ConvertYUVToRGB is fused into the Read under the
 // Resize (algorithms/image_processing/color_conversion.h:150-174, interpolation.h:70-104).
+// The ops after the interpolation and the write of one pixel, shared by the one-pixel-per-thread kernels: operands from
+// Nv12Consts (immediates) or from the plane record (per-plane operands).
+__device__ __forceinline__ void pixel_tail(const LaunchParams& p, const PlaneRec& pl, uint32_t x, uint32_t y, float (&v)[3]) {
+    const Nv12Consts& k = p.nv12;
+    float m[3], a[3], d[3];
+    if (k.slots) {
+        const PostParams q = load_post(p.chains[k.chain], pl, p.chains[k.chain].n_pre_ops);
+#pragma unroll
+        for (int c = 0; c < 3; ++c) { m[c] = q.m[c]; a[c] = q.a[c]; d[c] = q.d[c]; }
+    } else {
+#pragma unroll
+        for (int c = 0; c < 3; ++c) { m[c] = k.m[c]; a[c] = k.a[c]; d[c] = k.d[c]; }
+    }
+#pragma unroll
+    for (int c = 0; c < 3; ++c) {
+        if (k.kind & kPostMul) v[c] = __fmul_rn(v[c], m[c]);
+        if (k.kind & kPostAdd) v[c] = __fadd_rn(v[c], a[c]);
+        if (k.kind & kPostDiv) v[c] = __fdiv_rn(v[c], d[c]);
+        if (k.kind & kPostSat) v[c] = sat_u8_as_float(v[c]);
+    }
+    uint8_t* row = pl.dst + static_cast<size_t>(y * pl.dst_pitch);
+    if (k.split) {
+#pragma unroll
+        for (int c = 0; c < 3; ++c) {
+            uint8_t* q8 = row + channel_offset(pl, c);
+            if (k.f32) reinterpret_cast<float*>(q8)[x] = v[c]; else q8[x] = static_cast<uint8_t>(u8_of_exact(v[c]));
+        }
+    } else if (k.f32) {
+        float* f = reinterpret_cast<float*>(row) + static_cast<size_t>(x) * 3;
+        f[0] = v[0]; f[1] = v[1]; f[2] = v[2];
+    } else {
+        uint8_t* q8 = row + static_cast<size_t>(x) * 3;
+        q8[0] = static_cast<uint8_t>(u8_of_exact(v[0])); q8[1] = static_cast<uint8_t>(u8_of_exact(v[1])); q8[2] = static_cast<uint8_t>(u8_of_exact(v[2]));
+    }
+}
+
 __device__ __forceinline__ void nv12_pixel(const LaunchParams& p, const PlaneRec& pl, uint32_t x, uint32_t y) {
     if (pl.kclass != KCLASS_NV12) return;
     if (x >= pl.dst_w || y >= pl.dst_h) return;
@@ -926,35 +962,46 @@ __device__ __forceinline__ void nv12_pixel(const LaunchParams& p, const PlaneRec
 #pragma unroll
         for (int c = 0; c < 3; ++c) v[c] = acc[c];
     }
-    float m[3], a[3], d[3];
-    if (k.slots) {
-        const PostParams q = load_post(p.chains[k.chain], pl, p.chains[k.chain].n_pre_ops);
+    pixel_tail(p, pl, x, y, v);
+}
+
+// rgb_kernel: the same latency-oriented shape for packed byte sources (uchar3, or uchar4 whose alpha is skipped): one output
+// pixel per thread, the twelve tap bytes requested before any is used, the post-ops' operands in registers.  It serves the
+// launches of a few ten thousand pixels, where the general kernel's per-tap format dispatch and op interpreter are most of
+// the time.
+__device__ __forceinline__ void rgb_pixel(const LaunchParams& p, const PlaneRec& pl, uint32_t x, uint32_t y) {
+    if (pl.kclass != KCLASS_NV12) return;
+    if (x >= pl.dst_w || y >= pl.dst_h) return;
+    const Nv12Consts& k = p.nv12;
+    const bool par = k.preserve_ar != 0;
+    const bool inside = !par || (static_cast<int>(x) >= pl.x1 && static_cast<int>(x) <= pl.x2 &&
+                                 static_cast<int>(y) >= pl.y1 && static_cast<int>(y) <= pl.y2);
+    float v[3] = {pl.bg[0], pl.bg[1], pl.bg[2]};
+    if (inside) {
+        const AxisTap ax = axis_tap(static_cast<int>(x) - (par ? pl.x1 : 0), pl.fx, pl.crop_w);
+        const AxisTap ay = axis_tap(static_cast<int>(y) - (par ? pl.y1 : 0), pl.fy, pl.crop_h);
+        const uint32_t sp = k.src_px, pitch = pl.src_pitch;
+        const uint8_t* r0 = pl.src + static_cast<size_t>(ay.i0 + pl.crop_y) * pitch;
+        const uint8_t* r1 = pl.src + static_cast<size_t>(ay.i1 + pl.crop_y) * pitch;
+        const uint32_t o0 = (ax.i0 + pl.crop_x) * sp, o1 = (ax.i1 + pl.crop_x) * sp;
+        uint32_t t[4][3];
 #pragma unroll
-        for (int c = 0; c < 3; ++c) { m[c] = q.m[c]; a[c] = q.a[c]; d[c] = q.d[c]; }
-    } else {
+        for (int c = 0; c < 3; ++c) { t[0][c] = __ldg(r0 + o0 + c); t[1][c] = __ldg(r0 + o1 + c); t[2][c] = __ldg(r1 + o0 + c); t[3][c] = __ldg(r1 + o1 + c); }
+        const float w00 = __fmul_rn(ax.w0, ay.w0), w10 = __fmul_rn(ax.w1, ay.w0);
+        const float w01 = __fmul_rn(ax.w0, ay.w1), w11 = __fmul_rn(ax.w1, ay.w1);
 #pragma unroll
-        for (int c = 0; c < 3; ++c) { m[c] = k.m[c]; a[c] = k.a[c]; d[c] = k.d[c]; }
+        for (int c = 0; c < 3; ++c)
+            v[c] = bilerp(static_cast<float>(t[0][c]), static_cast<float>(t[1][c]), static_cast<float>(t[2][c]), static_cast<float>(t[3][c]), w00, w10, w01, w11);
     }
-#pragma unroll
-    for (int c = 0; c < 3; ++c) {
-        if (k.kind & kPostMul) v[c] = __fmul_rn(v[c], m[c]);
-        if (k.kind & kPostAdd) v[c] = __fadd_rn(v[c], a[c]);
-        if (k.kind & kPostDiv) v[c] = __fdiv_rn(v[c], d[c]);
-        if (k.kind & kPostSat) v[c] = sat_u8_as_float(v[c]);
-    }
-    uint8_t* row = pl.dst + static_cast<size_t>(y * pl.dst_pitch);
-    if (k.split) {
-#pragma unroll
-        for (int c = 0; c < 3; ++c) {
-            uint8_t* q8 = row + channel_offset(pl, c);
-            if (k.f32) reinterpret_cast<float*>(q8)[x] = v[c]; else q8[x] = static_cast<uint8_t>(u8_of_exact(v[c]));
-        }
-    } else if (k.f32) {
-        float* f = reinterpret_cast<float*>(row) + static_cast<size_t>(x) * 3;
-        f[0] = v[0]; f[1] = v[1]; f[2] = v[2];
+    pixel_tail(p, pl, x, y, v);
+}
+
+__global__ void __launch_bounds__(256, 4) rgb_kernel(const __grid_constant__ LaunchParams p) {
+    const uint32_t x = blockIdx.x * 32 + (threadIdx.x & 31), y = blockIdx.y * 8 + (threadIdx.x >> 5);
+    if (p.table == nullptr) {
+        for (uint32_t z = blockIdx.z; z < p.n_planes; z += gridDim.z) rgb_pixel(p, p.inline_planes[z], x, y);
     } else {
-        uint8_t* q8 = row + static_cast<size_t>(x) * 3;
-        q8[0] = static_cast<uint8_t>(u8_of_exact(v[0])); q8[1] = static_cast<uint8_t>(u8_of_exact(v[1])); q8[2] = static_cast<uint8_t>(u8_of_exact(v[2]));
+        for (uint32_t z = blockIdx.z; z < p.n_planes; z += gridDim.z) rgb_pixel(p, p.table[z], x, y);
     }
 }
 
@@ -1284,6 +1331,7 @@ cudaError_t launch_nv12(const LaunchParams& p, dim3 grid, cudaStream_t stream) {
         else if (p.nv12.vu) nv12_pair_kernel<128, 10, false, true><<<g, 128, 0, stream>>>(p);
         else nv12_pair_kernel<128, 10, false, false><<<g, 128, 0, stream>>>(p);
     }
+    else if (p.nv12.src_px) rgb_kernel<<<grid, 256, 0, stream>>>(p);
     else nv12_kernel<<<grid, 256, 0, stream>>>(p);
     return cudaGetLastError();
 }

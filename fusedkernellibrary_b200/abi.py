@@ -17,6 +17,7 @@ NOALLOC_MAX_PLANES = 4096
 OK, ERR_NULL, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_TOO_LARGE, ERR_DEVICE_WAIT = 0, -1, -2, -3, -4, -5, -6
 
 PIX_U8C3, PIX_F32C3, PIX_NV12, PIX_NV21, PIX_UYVY, PIX_U8C4, PIX_F32C4, PIX_F32P3 = 1, 2, 3, 4, 5, 6, 7, 8
+PIX_P010, PIX_P210, PIX_Y210 = 9, 10, 11
 RANGE_LIMITED, RANGE_FULL = 0, 1
 PRIMITIVES_BT601, PRIMITIVES_BT709, PRIMITIVES_BT2020 = 0, 1, 2
 GEOM_NONE, GEOM_RESIZE_IGNORE_AR, GEOM_RESIZE_PRESERVE_AR = 0, 1, 2
@@ -66,6 +67,7 @@ LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libf
 SIGNATURES = {
     "fkb_resize_params": (C.c_int, [C.c_uint32, C.POINTER(PlaneDesc)]),
     "fkb_ycbcr_to_rgb": (C.c_int, [C.c_uint32, C.c_uint32, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
+    "fkb_ycbcr_to_rgb_bits": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "fkb_rgb_to_ycbcr": (C.c_int, [C.c_uint32, C.c_uint32, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "fkb_validate": (C.c_int, [C.POINTER(ChainDesc), C.c_uint32, C.POINTER(PlaneDesc), C.c_uint32]),
     "fkb_launch_transform": (C.c_int, [C.POINTER(ChainDesc), C.POINTER(PlaneDesc), C.c_uint32, C.c_void_p]),

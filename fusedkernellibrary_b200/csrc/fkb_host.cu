@@ -57,8 +57,9 @@ int check_ops(const fkb_chain_desc& ch, uint32_t first, uint32_t last, ValueType
 
 int check_chain(const fkb_chain_desc& ch) {
     const bool float_src = ch.src_format == FKB_PIX_F32C3 || ch.src_format == FKB_PIX_F32P3;
+    const bool wide_yuv = ch.src_format == FKB_PIX_P010 || ch.src_format == FKB_PIX_P210 || ch.src_format == FKB_PIX_Y210;
     if (ch.src_format != FKB_PIX_U8C3 && ch.src_format != FKB_PIX_NV12 && ch.src_format != FKB_PIX_NV21 &&
-        ch.src_format != FKB_PIX_UYVY && ch.src_format != FKB_PIX_U8C4 && !float_src) return FKB_ERR_UNSUPPORTED;
+        ch.src_format != FKB_PIX_UYVY && ch.src_format != FKB_PIX_U8C4 && !float_src && !wide_yuv) return FKB_ERR_UNSUPPORTED;
     const bool four = ch.dst_format == FKB_PIX_U8C4 || ch.dst_format == FKB_PIX_F32C4;  // the chain keeps four channels
     if (ch.dst_format != FKB_PIX_U8C3 && ch.dst_format != FKB_PIX_F32C3 && !four) return FKB_ERR_UNSUPPORTED;
     if (four) {
@@ -90,12 +91,17 @@ int check_plane(const fkb_chain_desc& ch, const fkb_plane_desc& pl) {
     if ((!dflt && !pl.src) || !pl.dst) return FKB_ERR_NULL;
     const bool nv12 = ch.src_format == FKB_PIX_NV12 || ch.src_format == FKB_PIX_NV21;  // luma plane + interleaved chroma rows
     const bool float_src = ch.src_format == FKB_PIX_F32C3 || ch.src_format == FKB_PIX_F32P3;
+    const bool semi16 = ch.src_format == FKB_PIX_P010 || ch.src_format == FKB_PIX_P210;
     const bool uyvy = ch.src_format == FKB_PIX_UYVY;
     if (!dflt) {
-        if ((nv12 || ch.src_format == FKB_PIX_F32P3) && !pl.src_chroma) return FKB_ERR_NULL;
+        if ((nv12 || semi16 || ch.src_format == FKB_PIX_F32P3) && !pl.src_chroma) return FKB_ERR_NULL;
+        if ((semi16 || ch.src_format == FKB_PIX_Y210) &&
+            ((reinterpret_cast<uintptr_t>(pl.src) & 1) || (reinterpret_cast<uintptr_t>(pl.src_chroma) & 1) || (pl.src_pitch & 1))) return FKB_ERR_INVALID;
         if (float_src && ((reinterpret_cast<uintptr_t>(pl.src) & 3) || (reinterpret_cast<uintptr_t>(pl.src_chroma) & 3) || (pl.src_pitch & 3))) return FKB_ERR_INVALID;
         if (pl.src_w == 0 || pl.src_h == 0) return FKB_ERR_INVALID;
-        const uint64_t src_row = nv12 ? ((static_cast<uint64_t>(pl.src_w) + 1) / 2) * 2
+        const uint64_t src_row = semi16 ? ((static_cast<uint64_t>(pl.src_w) + 1) / 2) * 4
+                                 : ch.src_format == FKB_PIX_Y210 ? ((static_cast<uint64_t>(pl.src_w) + 1) / 2) * 8
+                                 : nv12 ? ((static_cast<uint64_t>(pl.src_w) + 1) / 2) * 2
                                  : uyvy ? ((static_cast<uint64_t>(pl.src_w) + 1) / 2) * 4
                                  : static_cast<uint64_t>(pl.src_w) * (ch.src_format == FKB_PIX_F32C3 ? 12 : (ch.src_format == FKB_PIX_U8C4 || ch.src_format == FKB_PIX_F32P3) ? 4 : 3);
         if (pl.src_pitch < src_row) return FKB_ERR_INVALID;
@@ -694,8 +700,16 @@ int fkb_resize_params(uint32_t geometry, fkb_plane_desc* pl) {
 }
 
 int fkb_ycbcr_to_rgb(uint32_t range, uint32_t primitives, float ccm[9], float yuv_sub[3]) {
+    return fkb_ycbcr_to_rgb_bits(8, range, primitives, ccm, yuv_sub);
+}
+
+int fkb_ycbcr_to_rgb_bits(uint32_t bits, uint32_t range, uint32_t primitives, float ccm[9], float yuv_sub[3]) {
     if (!ccm || !yuv_sub) return FKB_ERR_NULL;
-    if (range > FKB_RANGE_FULL || primitives > FKB_PRIMITIVES_BT2020) return FKB_ERR_INVALID;
+    if (range > FKB_RANGE_FULL || primitives > FKB_PRIMITIVES_BT2020 || (bits != 8 && bits != 10 && bits != 12)) return FKB_ERR_INVALID;
+    // per depth: the largest code, the luma and chroma offsets, the luma and chroma spans of limited range
+    const float max_v = bits == 8 ? 255.f : bits == 10 ? 1023.f : 4095.f;
+    const float sub_y = bits == 8 ? 16.f : bits == 10 ? 64.f : 256.f, sub_c = bits == 8 ? 128.f : bits == 10 ? 512.f : 2048.f;
+    const float lim_y = bits == 8 ? 219.f : bits == 10 ? 876.f : 3504.f, lim_c = bits == 8 ? 224.f : bits == 10 ? 896.f : 3584.f;
     // luma weights of Rec. BT.601 / BT.709 / BT.2020; every step below is an fp32 operation, in this order
     static const float kKr[3] = {0.299f, 0.2126f, 0.2627f}, kKb[3] = {0.114f, 0.0722f, 0.0593f};
     const float Kr = kKr[primitives], Kb = kKb[primitives];
@@ -703,13 +717,13 @@ int fkb_ycbcr_to_rgb(uint32_t range, uint32_t primitives, float ccm[9], float yu
     float m[3][3] = {{1.0f, 0.0f, 2.0f * (1.0f - Kr)},
                      {1.0f, -2.0f * Kb * (1.0f - Kb) / Kg, -2.0f * Kr * (1.0f - Kr) / Kg},
                      {1.0f, 2.0f * (1.0f - Kb), 0.0f}};
-    if (range == FKB_RANGE_LIMITED) {  // 8 bit: luma spans 219 codes from 16, chroma 224 around 128
-        const float scale_y = 255.f / 219.f, scale_c = 255.f / 224.f;
+    if (range == FKB_RANGE_LIMITED) {  // (8 bit: luma spans 219 codes from 16, chroma 224 around 128)
+        const float scale_y = max_v / lim_y, scale_c = max_v / lim_c;
         for (int i = 0; i < 3; ++i) { m[i][0] *= scale_y; m[i][1] *= scale_c; m[i][2] *= scale_c; }
     }
     for (int i = 0; i < 9; ++i) ccm[i] = m[i / 3][i % 3];
-    yuv_sub[0] = range == FKB_RANGE_LIMITED ? 16.f : 0.f;  // full range subtracts nothing from the luma
-    yuv_sub[1] = yuv_sub[2] = 128.f;
+    yuv_sub[0] = range == FKB_RANGE_LIMITED ? sub_y : 0.f;  // full range subtracts nothing from the luma
+    yuv_sub[1] = yuv_sub[2] = sub_c;
     return FKB_OK;
 }
 

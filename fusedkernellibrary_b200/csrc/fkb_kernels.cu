@@ -32,35 +32,56 @@ __device__ __forceinline__ const PlaneRec* plane_table(const LaunchParams& p) {
 
 // Frame pixel (X,Y) as three floats (uchar3 channels, or Y / Cb / Cr).
 __device__ __forceinline__ void read_frame_global(const fkb_chain_desc& ch, const PlaneRec& pl, size_t X, size_t Y, float (&o)[3]) {
-    if (ch.src_format == FKB_PIX_NV12 || ch.src_format == FKB_PIX_NV21) {
+    switch (ch.src_format) {
+    case FKB_PIX_NV12: case FKB_PIX_NV21: {
         const uint8_t* uv = pl.src_chroma + (Y >> 1) * pl.src_pitch + (X >> 1) * 2;
         const uint32_t vu = ch.src_format == FKB_PIX_NV21;  // V first
         o[0] = static_cast<float>(__ldg(pl.src + Y * pl.src_pitch + X));
         o[1] = static_cast<float>(__ldg(uv + vu));
         o[2] = static_cast<float>(__ldg(uv + (vu ^ 1u)));
-    } else if (ch.src_format == FKB_PIX_UYVY) {
+        break;
+    }
+    case FKB_PIX_UYVY: {
         const uint8_t* g = pl.src + Y * pl.src_pitch + (X >> 1) * 4;  // U Y0 V Y1
         o[0] = static_cast<float>(__ldg(g + 1 + 2 * (X & 1)));
         o[1] = static_cast<float>(__ldg(g));
         o[2] = static_cast<float>(__ldg(g + 2));
-    } else if (ch.src_format == FKB_PIX_F32C3) {
+        break;
+    }
+    case FKB_PIX_P010: case FKB_PIX_P210: {  // ushort luma plane, ushort2 chroma rows (every second row for 4:2:0)
+        const size_t cy = ch.src_format == FKB_PIX_P010 ? (Y >> 1) : Y;
+        const unsigned short* uv = reinterpret_cast<const unsigned short*>(pl.src_chroma + cy * pl.src_pitch) + (X >> 1) * 2;
+        o[0] = static_cast<float>(__ldg(reinterpret_cast<const unsigned short*>(pl.src + Y * pl.src_pitch) + X));
+        o[1] = static_cast<float>(__ldg(uv));
+        o[2] = static_cast<float>(__ldg(uv + 1));
+        break;
+    }
+    case FKB_PIX_Y210: {  // ushort4 groups Y0 U Y1 V
+        const unsigned short* g = reinterpret_cast<const unsigned short*>(pl.src + Y * pl.src_pitch) + (X >> 1) * 4;
+        o[0] = static_cast<float>(__ldg(g + 2 * (X & 1)));
+        o[1] = static_cast<float>(__ldg(g + 1));
+        o[2] = static_cast<float>(__ldg(g + 3));
+        break;
+    }
+    case FKB_PIX_F32C3: {
         const float* q = reinterpret_cast<const float*>(pl.src + Y * pl.src_pitch) + X * 3;
         o[0] = __ldg(q); o[1] = __ldg(q + 1); o[2] = __ldg(q + 2);
-    } else if (ch.src_format == FKB_PIX_F32P3) {
+        break;
+    }
+    case FKB_PIX_F32P3: {
         const size_t step = static_cast<size_t>(pl.src_chroma - pl.src);  // bytes between channel planes
         const uint8_t* q = pl.src + Y * pl.src_pitch + X * 4;
         o[0] = __ldg(reinterpret_cast<const float*>(q)); o[1] = __ldg(reinterpret_cast<const float*>(q + step));
         o[2] = __ldg(reinterpret_cast<const float*>(q + 2 * step));
-    } else if (ch.src_format == FKB_PIX_U8C4) {
-        const uint8_t* q = pl.src + Y * pl.src_pitch + X * 4;  // the alpha byte is not read
+        break;
+    }
+    default: {  // uchar3, or uchar4 whose alpha byte is not read
+        const uint8_t* q = pl.src + Y * pl.src_pitch + X * (ch.src_format == FKB_PIX_U8C4 ? 4u : 3u);
         o[0] = static_cast<float>(__ldg(q));
         o[1] = static_cast<float>(__ldg(q + 1));
         o[2] = static_cast<float>(__ldg(q + 2));
-    } else {
-        const uint8_t* q = pl.src + Y * pl.src_pitch + X * 3;
-        o[0] = static_cast<float>(__ldg(q));
-        o[1] = static_cast<float>(__ldg(q + 1));
-        o[2] = static_cast<float>(__ldg(q + 2));
+        break;
+    }
     }
 }
 // Index maps of the reference's BorderReader modes (border_reader.h:211-330), idx = low(high(i)); n is the frame extent.

@@ -106,7 +106,7 @@ class Workload:
             d = arr[i]
             ch = self.chains[s.chain]
             d.src = src_addrs[s.src]
-            d.src_chroma = src_addrs[s.src] + s.chroma_offset if ch.src_format in (abi.PIX_NV12, abi.PIX_NV21) else None
+            d.src_chroma = src_addrs[s.src] + s.chroma_offset if ch.src_format in (abi.PIX_NV12, abi.PIX_NV21, abi.PIX_P010, abi.PIX_P210) else None
             d.dst = dst_addrs[s.dst] + s.dst_offset
             d.src_pitch, d.src_w, d.src_h = s.src_pitch, s.src_w, s.src_h
             d.crop_x, d.crop_y, d.crop_w, d.crop_h = s.crop
@@ -214,23 +214,34 @@ def vertical_fusion(w=3840, h=2160, seed=2, pitch_align=16, dst_pitch_align=16) 
 def nv12_preprocess(w=3840, h=2160, dst=(640, 640), seed=3, pitch_align=16, ccm=None, yuv_sub=(0.0, 128.0, 128.0),
                     src_format=abi.PIX_NV12, colour=None) -> Workload:
     """Config 3: ReadYUV<NV12> -> ConvertYUVToRGB<p8bit,Full,bt709> -> Resize IGNORE_AR -> Sub mean -> Div std ->
-    TensorSplit<float3> (planar CHW fp32).  ``src_format`` selects NV21 or UYVY instead; ``colour=(range, primitives)``
-    takes the matrix and offsets from fkb_ycbcr_to_rgb."""
-    uyvy = src_format == abi.PIX_UYVY
-    pitch = _pitch(w * 2 if uyvy else w, pitch_align)
+    TensorSplit<float3> (planar CHW fp32).  ``src_format`` selects NV21, UYVY or one of the 10-bit formats (P010, P210,
+    Y210: ushort samples in 0..1023) instead; ``colour=(range, primitives)`` takes the matrix and offsets from
+    fkb_ycbcr_to_rgb_bits for the format's depth (required for the 10-bit formats)."""
+    wide = src_format in (abi.PIX_P010, abi.PIX_P210, abi.PIX_Y210)
+    packed = src_format in (abi.PIX_UYVY, abi.PIX_Y210)
+    pitch = _pitch(w * (2 if packed else 1) * (2 if wide else 1), pitch_align)
     dw, dh = dst
     if colour is not None:
         m, sub = (C.c_float * 9)(), (C.c_float * 3)()
-        if abi.load().fkb_ycbcr_to_rgb(colour[0], colour[1], m, sub) != 0:
-            raise ValueError("fkb_ycbcr_to_rgb refused the colour description")
+        if abi.load().fkb_ycbcr_to_rgb_bits(10 if wide else 8, colour[0], colour[1], m, sub) != 0:
+            raise ValueError("fkb_ycbcr_to_rgb_bits refused the colour description")
         ccm, yuv_sub = tuple(m), tuple(sub)
+    elif wide:
+        raise ValueError("a 10-bit source needs colour=(range, primitives)")
+    mean, std = ((496.7, 466.9, 415.6), (234.2, 229.1, 230.2)) if wide else ((123.675, 116.28, 103.53), (58.395, 57.12, 57.375))
     ch = chain(src_format, abi.GEOM_RESIZE_IGNORE_AR, abi.PIX_F32C3, abi.WRITE_SPLIT,
-               [op(abi.OP_YUV2RGB), op(abi.OP_SUB, (123.675, 116.28, 103.53)), op(abi.OP_DIV, (58.395, 57.12, 57.375))],
+               [op(abi.OP_YUV2RGB), op(abi.OP_SUB, mean), op(abi.OP_DIV, std)],
                n_pre_ops=1, ccm=BT709_FULL_8BIT if ccm is None else ccm, yuv_sub=yuv_sub)
     planes = [PlaneSpec(0, 0, 0, w, h, pitch, (0, 0, w, h), dw, dh, dw * 4, dst_channel_stride=dw * dh * 4,
                         chroma_offset=pitch * h)]
-    name = {abi.PIX_NV12: "nv12_preprocess", abi.PIX_NV21: "nv21_preprocess", abi.PIX_UYVY: "uyvy_preprocess"}[src_format]
-    return Workload(name, [ch], [_frame(seed, pitch * h if uyvy else pitch * (h + h // 2), 16, 236)], [dw * dh * 12], planes,
+    name = {abi.PIX_NV12: "nv12_preprocess", abi.PIX_NV21: "nv21_preprocess", abi.PIX_UYVY: "uyvy_preprocess",
+            abi.PIX_P010: "p010_preprocess", abi.PIX_P210: "p210_preprocess", abi.PIX_Y210: "y210_preprocess"}[src_format]
+    rows = h if packed else 2 * h if src_format == abi.PIX_P210 else h + h // 2
+    if wide:  # samples over the whole 10-bit scale, stored as they are in 16-bit words
+        frame = np.random.RandomState(seed).randint(40, 1000, size=pitch * rows // 2).astype(np.uint16).view(np.uint8)
+    else:
+        frame = _frame(seed, pitch * rows, 16, 236)
+    return Workload(name, [ch], [frame], [dw * dh * 12], planes,
                     f"{name[:4].upper()} {w}x{h} -> planar fp32 3x{dh}x{dw}", extra={"colour": colour})
 
 

@@ -77,7 +77,12 @@ enum { FKB_PIX_U8C3 = 1, FKB_PIX_F32C3 = 2, FKB_PIX_NV12 = 3,
         * memory_operations.h:243-262); FKB_PIX_F32P3 is three float planes, channel c at src + c * (src_chroma - src)
         * (TensorPack / TensorTPack, memory_operations.h:264-330).  They feed chains that start in float: the copy sequence
         * of CircularTensor::update (core/data/circular_tensor.h:111-161) is such a chain without ops. */
-       FKB_PIX_F32P3 = 8 };
+       FKB_PIX_F32P3 = 8,
+       /* 10-bit YCbCr sources of ReadYUV, 16-bit containers read as they are stored (color_conversion.h:219-238, 255-265):
+        * P010 = NV12's layout with ushort samples (4:2:0), P210 the same with full-height chroma (4:2:2), Y210 one plane of
+        * ushort4 groups Y0 U Y1 V.  src_pitch in bytes; P010 / P210 take src_chroma.  The matrix and offsets of their
+        * FKB_OP_YUV2RGB come from fkb_ycbcr_to_rgb_bits(10, ...). */
+       FKB_PIX_P010 = 9, FKB_PIX_P210 = 10, FKB_PIX_Y210 = 11 };
 
 /* Geometry of the ReadBack stage.  The crop rectangle is always applied (a chain without Crop
  * passes the whole frame as the rectangle).  NONE: output pixel (x,y) reads crop pixel (x,y).
@@ -195,6 +200,8 @@ int fkb_resize_params(uint32_t geometry, fkb_plane_desc* plane);
 enum { FKB_RANGE_LIMITED = 0, FKB_RANGE_FULL = 1 };
 enum { FKB_PRIMITIVES_BT601 = 0, FKB_PRIMITIVES_BT709 = 1, FKB_PRIMITIVES_BT2020 = 2 };
 int fkb_ycbcr_to_rgb(uint32_t range, uint32_t primitives, float ccm[9], float yuv_sub[3]);
+/* The same for a colour depth of 8, 10 or 12 bits (maxDepthValue, subCoefficients and rangeLimits of itu_color.h:104-171). */
+int fkb_ycbcr_to_rgb_bits(uint32_t bits, uint32_t range, uint32_t primitives, float ccm[9], float yuv_sub[3]);
 /* The other direction, for fkb_chain_desc.ccm2 / yuv_add of a chain with FKB_OP_RGB2YUV (ConvertRGBToYUV). */
 int fkb_rgb_to_ycbcr(uint32_t range, uint32_t primitives, float ccm2[9], float yuv_add[3]);
 

@@ -119,7 +119,8 @@ struct Lowered {
         };
         const SrcPlane& s = pick(st.src);
         d.src = s.data; d.src_pitch = s.pitch; d.src_w = s.w; d.src_h = s.h;
-        if (st.src_format == FKB_PIX_NV12 || st.src_format == FKB_PIX_NV21) d.src_chroma = static_cast<const uint8_t*>(s.data) + static_cast<size_t>(s.pitch) * s.h;
+        if (st.src_format == FKB_PIX_NV12 || st.src_format == FKB_PIX_NV21 || st.src_format == FKB_PIX_P010 || st.src_format == FKB_PIX_P210)
+            d.src_chroma = static_cast<const uint8_t*>(s.data) + static_cast<size_t>(s.pitch) * s.h;
         if (st.crops.empty()) { d.crop_x = 0; d.crop_y = 0; d.crop_w = static_cast<int>(s.w); d.crop_h = static_cast<int>(s.h); }
         else { const Rect& r = pick(st.crops); d.crop_x = r.x; d.crop_y = r.y; d.crop_w = r.width; d.crop_h = r.height; }
         if (st.has_resize) { d.dst_w = st.dst_size.width; d.dst_h = st.dst_size.height; }

@@ -14,6 +14,7 @@
 #include <memory>
 
 #include "types.h"
+#include "fkb/fkb.h"
 
 namespace fk {
 
@@ -203,39 +204,58 @@ public:
         : Ptr<ND::T3D, T>(data, wrapped(width_, height_, planes_, color_planes_), type_, deviceID_) {}
 };
 
-// The reference's enumerators (itu_color.h:30, 53); the 8-bit formats NV12, NV21 and UYVY are the ones these kernels read.
+// The reference's enumerators (itu_color.h:30, 53).  These kernels read the 8-bit formats NV12, NV21 and UYVY and the
+// 10-bit formats P010, P210 and Y210 (ushort samples holding 0..1023).
 enum class PixelFormat { NV12, NV21, YV12, P010, P016, P216, P210, Y216, Y210, Y416, UYVY };
 enum class ColorDepth { p8bit, p10bit, p12bit, fn8bit, fn10bit, fn12bit };
 enum class ColorRange { Limited, Full };
 enum class ColorPrimitives { bt601, bt709, bt2020 };
 
+// Depth, sample type and buffer shape of a format (PixelFormatTraits, itu_color.h:57-102): `wf` samples per pixel along
+// a row; the one buffer holds `h`, `h + h/2` (4:2:0 semi-planar) or `2h` (4:2:2 semi-planar) rows.
+template <PixelFormat PF>
+struct PixelFormatTraits {
+    static constexpr bool supported = PF == PixelFormat::NV12 || PF == PixelFormat::NV21 || PF == PixelFormat::UYVY ||
+                                      PF == PixelFormat::P010 || PF == PixelFormat::P210 || PF == PixelFormat::Y210;
+    static constexpr bool wide = PF == PixelFormat::P010 || PF == PixelFormat::P210 || PF == PixelFormat::Y210;
+    static constexpr ColorDepth depth = wide ? ColorDepth::p10bit : ColorDepth::p8bit;
+    static constexpr uint wf = (PF == PixelFormat::UYVY || PF == PixelFormat::Y210) ? 2u : 1u;
+    static constexpr uint rows(uint h) { return wf == 2u ? h : PF == PixelFormat::P210 ? 2u * h : h + h / 2u; }
+    static constexpr uint32_t code = PF == PixelFormat::NV12 ? FKB_PIX_NV12 : PF == PixelFormat::NV21 ? FKB_PIX_NV21
+                                   : PF == PixelFormat::UYVY ? FKB_PIX_UYVY : PF == PixelFormat::P010 ? FKB_PIX_P010
+                                   : PF == PixelFormat::P210 ? FKB_PIX_P210 : FKB_PIX_Y210;
+};
+template <ColorDepth CD> using ColorDepthPixelBaseType = std::conditional_t<CD == ColorDepth::p8bit, uchar, ushort>;
+template <ColorDepth CD> using ColorDepthPixelType = std::conditional_t<CD == ColorDepth::p8bit, uchar3, ushort3>;
+
 template <PixelFormat PF>
 struct RawImage {
-    RawPtr<ND::_2D, uchar> data;
+    RawPtr<ND::_2D, ColorDepthPixelBaseType<PixelFormatTraits<PF>::depth>> data;
     uint width, height;
 };
 
 template <PixelFormat PF>
 class Image {
-    static_assert(PF == PixelFormat::NV12 || PF == PixelFormat::NV21 || PF == PixelFormat::UYVY,
-                  "NV12, NV21 and UYVY are the image formats the B200 kernels read");
-    // bytes per row and rows of the one buffer that holds the image (PixelFormatTraits<PF>::rf, itu_color.h:57-102)
-    static constexpr bool packed422 = PF == PixelFormat::UYVY;
-    Ptr<ND::_2D, uchar> data;
+    static_assert(PixelFormatTraits<PF>::supported, "NV12, NV21, UYVY, P010, P210 and Y210 are the image formats the B200 kernels read");
+public:
+    using BaseType = ColorDepthPixelBaseType<PixelFormatTraits<PF>::depth>;
+    static constexpr PixelFormat pixelFormat = PF;
+private:
+    Ptr<ND::_2D, BaseType> data;
     uint width{0}, height{0};
 
 public:
-    Image(const Ptr<ND::_2D, uchar>& data_, const uint& width_, const uint& height_) : data(data_), width(width_), height(height_) {}
+    Image(const Ptr<ND::_2D, BaseType>& data_, const uint& width_, const uint& height_) : data(data_), width(width_), height(height_) {}
     Image(const uint width_, const uint height_, const MemType memType = defaultMemType, const uint deviceID = 0)
         : width(width_), height(height_) {
-        data = Ptr<ND::_2D, uchar>(packed422 ? PtrDims<ND::_2D>(width_ * 2, height_, 0) : PtrDims<ND::_2D>(width_, height_ + height_ / 2, 0),
-                                   memType, static_cast<int>(deviceID));
+        data = Ptr<ND::_2D, BaseType>(PtrDims<ND::_2D>(width_ * PixelFormatTraits<PF>::wf, PixelFormatTraits<PF>::rows(height_), 0),
+                                      memType, static_cast<int>(deviceID));
     }
     uint imageWidth() const { return width; }
     uint imageHeight() const { return height; }
     RawImage<PF> ptr() const { return RawImage<PF>{data.ptr(), width, height}; }
     RawImage<PF> operator()() const { return ptr(); }
-    Ptr<ND::_2D, uchar> getData() const { return data; }
+    Ptr<ND::_2D, BaseType> getData() const { return data; }
     void upload(Stream_<ParArch::GPU_NVIDIA>& stream) { data.upload(stream); }
     void download(Stream_<ParArch::GPU_NVIDIA>& stream) { data.download(stream); }
 };

@@ -136,11 +136,12 @@ struct ColorConversion {
 // (algorithms/image_processing/itu_color.h:185-258, color_conversion.h:150-174), from fkb_ycbcr_to_rgb.
 template <ColorDepth CD, ColorRange CR, ColorPrimitives CP>
 struct ConvertYUVToRGB {
-    static_assert(CD == ColorDepth::p8bit, "8-bit YCbCr is the depth the B200 kernels convert");
+    static_assert(CD == ColorDepth::p8bit || CD == ColorDepth::p10bit, "8-bit and 10-bit YCbCr are the depths the B200 kernels convert");
     static auto build() {
-        ComputeIOp<FKB_OP_YUV2RGB, uchar3, float3> op{};
+        ComputeIOp<FKB_OP_YUV2RGB, ColorDepthPixelType<CD>, float3> op{};
         const uint32_t prim = CP == ColorPrimitives::bt601 ? FKB_PRIMITIVES_BT601 : CP == ColorPrimitives::bt709 ? FKB_PRIMITIVES_BT709 : FKB_PRIMITIVES_BT2020;
-        if (fkb_ycbcr_to_rgb(CR == ColorRange::Full ? FKB_RANGE_FULL : FKB_RANGE_LIMITED, prim, op.ccm, op.yuv_sub) != FKB_OK)
+        if (fkb_ycbcr_to_rgb_bits(CD == ColorDepth::p8bit ? 8u : 10u, CR == ColorRange::Full ? FKB_RANGE_FULL : FKB_RANGE_LIMITED, prim,
+                                  op.ccm, op.yuv_sub) != FKB_OK)
             throw std::runtime_error("ConvertYUVToRGB: colour description refused");
         return op;
     }
@@ -334,12 +335,11 @@ template <PixelFormat PF>
 struct ReadYUV {
     static auto build(const Image<PF>& img) { return build(img.ptr()); }
     static auto build(const RawImage<PF>& raw) {
+        static_assert(PixelFormatTraits<PF>::supported, "NV12, NV21, UYVY, P010, P210 and Y210 are the formats the B200 kernels read");
         detail::ReadState s;
-        static_assert(PF == PixelFormat::NV12 || PF == PixelFormat::NV21 || PF == PixelFormat::UYVY,
-                      "NV12, NV21 and UYVY are the formats the B200 kernels read");
-        s.src_format = PF == PixelFormat::NV12 ? FKB_PIX_NV12 : PF == PixelFormat::NV21 ? FKB_PIX_NV21 : FKB_PIX_UYVY;
+        s.src_format = PixelFormatTraits<PF>::code;
         s.src.push_back({raw.data.data, raw.data.dims.pitch, raw.width, raw.height});
-        return ReadIOp<uchar3, 0>(std::move(s));
+        return ReadIOp<ColorDepthPixelType<PixelFormatTraits<PF>::depth>, 0>(std::move(s));
     }
 };
 // A batch whose planes are complete read chains of the same shape but different parameters (their own source,

@@ -22,6 +22,7 @@
 namespace fk {
 
 using uchar = unsigned char;
+using ushort = unsigned short;
 using uint = unsigned int;
 
 inline void gpuAssert(cudaError_t code, const char* file, int line) {
@@ -62,6 +63,7 @@ struct ActiveThreads {
 // channel count and base type of the CUDA vector types this front end handles
 template <typename T> struct VectorTraits { using base = T; static constexpr int cn = 1; };
 template <> struct VectorTraits<uchar3> { using base = uchar; static constexpr int cn = 3; };
+template <> struct VectorTraits<ushort3> { using base = ushort; static constexpr int cn = 3; };
 template <> struct VectorTraits<float3> { using base = float; static constexpr int cn = 3; };
 template <> struct VectorTraits<uchar2> { using base = uchar; static constexpr int cn = 2; };
 template <> struct VectorTraits<uchar4> { using base = uchar; static constexpr int cn = 4; };

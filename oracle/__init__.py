@@ -41,6 +41,8 @@ def load_oracle() -> C.CDLL:
         lib.fkb_oracle_run.argtypes = [C.POINTER(abi.ChainDesc), C.c_uint32, C.POINTER(abi.PlaneDesc), C.c_uint32, C.c_uint32]
         lib.fkb_oracle_ycbcr_to_rgb.restype = C.c_int
         lib.fkb_oracle_ycbcr_to_rgb.argtypes = [C.c_uint32, C.c_uint32, C.POINTER(C.c_float), C.POINTER(C.c_float)]
+        lib.fkb_oracle_ycbcr_to_rgb_bits.restype = C.c_int
+        lib.fkb_oracle_ycbcr_to_rgb_bits.argtypes = [C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(C.c_float), C.POINTER(C.c_float)]
         lib.fkb_oracle_rgb_to_ycbcr.restype = C.c_int
         lib.fkb_oracle_rgb_to_ycbcr.argtypes = [C.c_uint32, C.c_uint32, C.POINTER(C.c_float), C.POINTER(C.c_float)]
         lib.fkb_oracle_saturate_u8.restype = C.c_uint8
@@ -92,6 +94,10 @@ def load_ref() -> C.CDLL:
         lib.fklref_nv12_border_constant.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, i32p, f32p, C.c_int, C.c_int, C.c_void_p]
         lib.fklref_ycbcr_matrix.restype = C.c_int
         lib.fklref_ycbcr_matrix.argtypes = [C.c_int, C.c_int, f32p]
+        lib.fklref_ycbcr_matrix10.restype = C.c_int
+        lib.fklref_ycbcr_matrix10.argtypes = [C.c_int, C.c_int, f32p, f32p]
+        lib.fklref_yuv10_resize_split.restype = C.c_int
+        lib.fklref_yuv10_resize_split.argtypes = [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, f32p, f32p, C.c_void_p]
         lib.fklref_yuv_resize_split.restype = C.c_int
         lib.fklref_yuv_resize_split.argtypes = [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, f32p, f32p, C.c_void_p]
         lib.fklref_conditional_resize_f32.argtypes = [pp, C.c_int, C.c_int, C.c_int, C.c_int, u8p, C.c_int, C.c_int, f32p, C.c_void_p]
@@ -212,7 +218,8 @@ def run_ref(wl, threads: int = 1):
                                      _f3(ch.ops[2].v), _f3(ch.ops[3].v), outs[0].ctypes.data, p0.dst_pitch)
     elif wl.name.endswith("_preprocess") and wl.extra.get("colour") is not None:
         rng, prim = wl.extra["colour"]
-        rc = lib.fklref_yuv_resize_split(ch.src_format, rng, prim, wl.sources[0].ctypes.data, p0.src_w, p0.src_h, p0.src_pitch,
+        fn = lib.fklref_yuv10_resize_split if ch.src_format >= 9 else lib.fklref_yuv_resize_split  # ushort sample formats
+        rc = fn(ch.src_format, rng, prim, wl.sources[0].ctypes.data, p0.src_w, p0.src_h, p0.src_pitch,
                                          p0.dst_w, p0.dst_h, _f3(ch.ops[1].v), _f3(ch.ops[2].v), outs[0].ctypes.data)
         if rc == -1:
             raise ValueError("the reference runner has no instantiation for this format / range / primitives")

@@ -146,6 +146,17 @@ inline V3 read_frame(const fkb_chain_desc& ch, const fkb_plane_desc& pl, size_t 
         v.c[0] = (X & 1) ? g[3] : g[1];
         v.c[1] = g[0];
         v.c[2] = g[2];
+    } else if (ch.src_format == FKB_PIX_P010 || ch.src_format == FKB_PIX_P210) {  // color_conversion.h:219-238, ushort samples
+        const size_t cy = ch.src_format == FKB_PIX_P010 ? (Y >> 1) : Y;             // 4:2:0 halves the chroma rows, 4:2:2 does not
+        const uint16_t* uv = reinterpret_cast<const uint16_t*>(static_cast<const uint8_t*>(pl.src_chroma) + cy * pl.src_pitch) + (X >> 1) * 2;
+        v.c[0] = reinterpret_cast<const uint16_t*>(base + Y * pl.src_pitch)[X];
+        v.c[1] = uv[0];
+        v.c[2] = uv[1];
+    } else if (ch.src_format == FKB_PIX_Y210) {  // color_conversion.h:255-265: ushort4 (Y0, U, Y1, V) per two pixels
+        const uint16_t* g = reinterpret_cast<const uint16_t*>(base + Y * pl.src_pitch) + (X >> 1) * 4;
+        v.c[0] = (X & 1) ? g[2] : g[0];
+        v.c[1] = g[1];
+        v.c[2] = g[3];
     } else if (ch.src_format == FKB_PIX_F32C3) {  // TensorRead<float3> / PerThreadRead<float3>
         const float* p = reinterpret_cast<const float*>(base + Y * pl.src_pitch) + X * 3;
         v.c[0] = p[0]; v.c[1] = p[1]; v.c[2] = p[2];
@@ -344,7 +355,19 @@ int fkb_oracle_resize_params(uint32_t geometry, fkb_plane_desc* pl) {
 
 // ccMatrix<CR, CP, YCbCr2RGB, p8bit> and subCoefficients<p8bit> (itu_color.h:112-124, 142-153, 185-258), with the
 // luma offset dropped for Full range as ConvertYUVToRGB::exec does (color_conversion.h:163-171).
+int fkb_oracle_ycbcr_to_rgb_bits(uint32_t bits, uint32_t range, uint32_t primitives, float* ccm, float* yuv_sub);
 int fkb_oracle_ycbcr_to_rgb(uint32_t range, uint32_t primitives, float* ccm, float* yuv_sub) {
+    return fkb_oracle_ycbcr_to_rgb_bits(8, range, primitives, ccm, yuv_sub);
+}
+int fkb_oracle_ycbcr_to_rgb_bits(uint32_t bits, uint32_t range, uint32_t primitives, float* ccm, float* yuv_sub) {
+    // maxDepthValue (itu_color.h:104-110), subCoefficients (:119-124), rangeLimits (:160-165) of the integer depths
+    float max_v, sub_y, sub_c, lim_y, lim_c;
+    switch (bits) {
+    case 8: max_v = 255.f; sub_y = 16.f; sub_c = 128.f; lim_y = 219.f; lim_c = 224.f; break;
+    case 10: max_v = 1023.f; sub_y = 64.f; sub_c = 512.f; lim_y = 876.f; lim_c = 896.f; break;
+    case 12: max_v = 4095.f; sub_y = 256.f; sub_c = 2048.f; lim_y = 3504.f; lim_c = 3584.f; break;
+    default: return FKB_ERR_INVALID;
+    }
     float kr, kb;
     switch (primitives) {
     case FKB_PRIMITIVES_BT601: kr = 0.299f; kb = 0.114f; break;
@@ -357,13 +380,13 @@ int fkb_oracle_ycbcr_to_rgb(uint32_t range, uint32_t primitives, float* ccm, flo
     ccm[3] = 1.0f; ccm[4] = -2.0f * kb * (1.0f - kb) / kg; ccm[5] = -2.0f * kr * (1.0f - kr) / kg;
     ccm[6] = 1.0f; ccm[7] = 2.0f * (1.0f - kb); ccm[8] = 0.0f;
     if (range == FKB_RANGE_LIMITED) {
-        const float sy = 255.f / 219.f, sc = 255.f / 224.f;
+        const float sy = max_v / lim_y, sc = max_v / lim_c;
         for (int r = 0; r < 3; ++r) { ccm[3 * r] *= sy; ccm[3 * r + 1] *= sc; ccm[3 * r + 2] *= sc; }
     } else if (range != FKB_RANGE_FULL) {
         return FKB_ERR_INVALID;
     }
-    yuv_sub[0] = range == FKB_RANGE_LIMITED ? 16.f : 0.f;
-    yuv_sub[1] = 128.f; yuv_sub[2] = 128.f;
+    yuv_sub[0] = range == FKB_RANGE_LIMITED ? sub_y : 0.f;
+    yuv_sub[1] = sub_c; yuv_sub[2] = sub_c;
     return FKB_OK;
 }
 

@@ -543,6 +543,56 @@ extern "C" int fklref_yuv_resize_split(int format, int range, int primitives, co
     }
 }
 
+// ccMatrix<range, primitives, YCbCr2RGB, p10bit> and subCoefficients<p10bit> (luma, chroma)
+template <ColorRange CR, ColorPrimitives CP>
+static void matrix10_of(float* m9, float* sub2) {
+    constexpr M3x3Float m = ccMatrix<CR, CP, ColorConversionDir::YCbCr2RGB, ColorDepth::p10bit>;
+    m9[0] = m.x.x; m9[1] = m.x.y; m9[2] = m.x.z; m9[3] = m.y.x; m9[4] = m.y.y; m9[5] = m.y.z;
+    m9[6] = m.z.x; m9[7] = m.z.y; m9[8] = m.z.z;
+    sub2[0] = subCoefficients<ColorDepth::p10bit>.luma; sub2[1] = subCoefficients<ColorDepth::p10bit>.chroma;
+}
+extern "C" int fklref_ycbcr_matrix10(int range, int primitives, float* m9, float* sub2) {
+    switch (range * 3 + primitives) {
+    case 0: matrix10_of<ColorRange::Limited, ColorPrimitives::bt601>(m9, sub2); return 0;
+    case 1: matrix10_of<ColorRange::Limited, ColorPrimitives::bt709>(m9, sub2); return 0;
+    case 2: matrix10_of<ColorRange::Limited, ColorPrimitives::bt2020>(m9, sub2); return 0;
+    case 3: matrix10_of<ColorRange::Full, ColorPrimitives::bt601>(m9, sub2); return 0;
+    case 4: matrix10_of<ColorRange::Full, ColorPrimitives::bt709>(m9, sub2); return 0;
+    case 5: matrix10_of<ColorRange::Full, ColorPrimitives::bt2020>(m9, sub2); return 0;
+    default: return -1;
+    }
+}
+
+// ReadYUV<PF> (ushort samples) -> ConvertYUVToRGB<p10bit, CR, CP> -> Resize(IGNORE_AR) -> Sub -> Div -> TensorSplit<float3>.
+// The buffer is PixelFormatTraits<PF>::rf times the picture, in ushort elements; pitch is in bytes.
+template <PixelFormat PF, ColorRange CR, ColorPrimitives CP>
+static int yuv10_resize_split(const uint16_t* data, int w, int h, int pitch, int dw, int dh, const float* sub, const float* div, float* out) {
+    CpuStream stream;
+    const uint bw = static_cast<uint>(w * PixelFormatTraits<PF>::rf.width_f), bh = static_cast<uint>(h * PixelFormatTraits<PF>::rf.height_f);
+    const Ptr<ND::_2D, ushort> buf(const_cast<uint16_t*>(data), PtrDims<ND::_2D>(bw, bh, pitch), MemType::Host, 0);
+    const Image<PF> img(buf, w, h);
+    Tensor<float> t(out, dw, dh, 1, 3, MemType::Host, 0);
+    executeOperations<CpuDPP>(stream, ReadYUV<PF>::build(img), ConvertYUVToRGB<ColorDepth::p10bit, CR, CP>::build(),
+        Resize<InterpolationType::INTER_LINEAR, AspectRatio::IGNORE_AR>::build(Size(dw, dh)),
+        Sub<float3>::build(make_<float3>(sub[0], sub[1], sub[2])), Div<float3>::build(make_<float3>(div[0], div[1], div[2])),
+        TensorSplit<float3>::build(t));
+    return 0;
+}
+// format: 9 P010, 10 P210, 11 Y210 (this library's source-format codes)
+extern "C" int fklref_yuv10_resize_split(int format, int range, int primitives, const uint16_t* data, int w, int h, int pitch, int dw,
+                                         int dh, const float* sub, const float* div, float* out) {
+    const int key = format * 100 + range * 10 + primitives;
+    switch (key) {
+    case 902: return yuv10_resize_split<PixelFormat::P010, ColorRange::Limited, ColorPrimitives::bt2020>(data, w, h, pitch, dw, dh, sub, div, out);
+    case 911: return yuv10_resize_split<PixelFormat::P010, ColorRange::Full, ColorPrimitives::bt709>(data, w, h, pitch, dw, dh, sub, div, out);
+    case 1001: return yuv10_resize_split<PixelFormat::P210, ColorRange::Limited, ColorPrimitives::bt709>(data, w, h, pitch, dw, dh, sub, div, out);
+    case 1012: return yuv10_resize_split<PixelFormat::P210, ColorRange::Full, ColorPrimitives::bt2020>(data, w, h, pitch, dw, dh, sub, div, out);
+    case 1102: return yuv10_resize_split<PixelFormat::Y210, ColorRange::Limited, ColorPrimitives::bt2020>(data, w, h, pitch, dw, dh, sub, div, out);
+    case 1110: return yuv10_resize_split<PixelFormat::Y210, ColorRange::Full, ColorPrimitives::bt601>(data, w, h, pitch, dw, dh, sub, div, out);
+    default: return -1;
+    }
+}
+
 extern "C" {
 uint8_t fklref_saturate_u8(float v) { return cxp::saturate_cast<uchar>::f(v); }
 

@@ -142,17 +142,24 @@ static void test_nv12() {
 }
 
 // ---- the other 8-bit sources and colour descriptions: NV21 / UYVY, limited range, bt601 / bt2020 -------------------
-extern "C" int fkb_oracle_ycbcr_to_rgb(uint32_t range, uint32_t primitives, float* ccm, float* yuv_sub);
+extern "C" int fkb_oracle_ycbcr_to_rgb_bits(uint32_t bits, uint32_t range, uint32_t primitives, float* ccm, float* yuv_sub);
 template <PixelFormat PF, ColorRange CR, ColorPrimitives CP>
 static void test_yuv(const char* what, uint32_t fmt, uint32_t range, uint32_t prim) {
     Stream stream;
     const uint W = 320, H = 180, DW = 111, DH = 70;
     Image<PF> img(W, H);
     auto data = img.getData();
-    fill_random(data, 5, 16, 235);
+    constexpr bool wide = PixelFormatTraits<PF>::wide;  // ushort samples holding ten bits
+    if constexpr (wide) {
+        std::mt19937 rng(5);
+        uint16_t* b = reinterpret_cast<uint16_t*>(data.ptrPinned().data);
+        for (size_t i = 0; i < data.sizeInBytes() / 2; ++i) b[i] = static_cast<uint16_t>(40 + rng() % 960);
+    } else {
+        fill_random(data, 5, 16, 235);
+    }
     img.upload(stream);
     Tensor<float> out(DW, DH, 1, 3);
-    executeOperations<TransformDPP<>>(stream, ReadYUV<PF>::build(img), ConvertYUVToRGB<ColorDepth::p8bit, CR, CP>::build(),
+    executeOperations<TransformDPP<>>(stream, ReadYUV<PF>::build(img), ConvertYUVToRGB<PixelFormatTraits<PF>::depth, CR, CP>::build(),
         Resize<InterpolationType::INTER_LINEAR, AspectRatio::IGNORE_AR>::build(Size(DW, DH)),
         Sub<float3>::build(make_<float3>(123.675f, 116.28f, 103.53f)), TensorSplit<float3>::build(out));
     out.download(stream);
@@ -160,12 +167,12 @@ static void test_yuv(const char* what, uint32_t fmt, uint32_t range, uint32_t pr
     fkb_chain_desc ch{};
     ch.src_format = fmt; ch.geometry = FKB_GEOM_RESIZE_IGNORE_AR; ch.dst_format = FKB_PIX_F32C3; ch.write_kind = FKB_WRITE_SPLIT;
     ch.n_ops = 2; ch.n_pre_ops = 1; ch.ops[0] = op(FKB_OP_YUV2RGB); ch.ops[1] = op(FKB_OP_SUB, 123.675f, 116.28f, 103.53f);
-    fkb_oracle_ycbcr_to_rgb(range, prim, ch.ccm, ch.yuv_sub);
+    fkb_oracle_ycbcr_to_rgb_bits(wide ? 10 : 8, range, prim, ch.ccm, ch.yuv_sub);
     std::vector<float> want(DW * DH * 3);
     fkb_plane_desc d{};
     const auto r = data.ptrPinned();
     d.src = r.data; d.src_pitch = r.dims.pitch; d.src_w = W; d.src_h = H;
-    if (fmt != FKB_PIX_UYVY) d.src_chroma = reinterpret_cast<uint8_t*>(r.data) + static_cast<size_t>(r.dims.pitch) * H;
+    if (fmt != FKB_PIX_UYVY && fmt != FKB_PIX_Y210) d.src_chroma = reinterpret_cast<uint8_t*>(r.data) + static_cast<size_t>(r.dims.pitch) * H;
     d.crop_w = W; d.crop_h = H; d.dst = want.data(); d.dst_w = DW; d.dst_h = DH; d.dst_pitch = DW * 4; d.dst_channel_stride = DW * DH * 4;
     fkb_oracle_resize_params(ch.geometry, &d);
     fkb_oracle_run(&ch, 1, &d, 1, 1);
@@ -559,6 +566,9 @@ int main() {
     test_yuv<PixelFormat::NV21, ColorRange::Limited, ColorPrimitives::bt601>("NV21, limited range bt601", FKB_PIX_NV21, FKB_RANGE_LIMITED, FKB_PRIMITIVES_BT601);
     test_yuv<PixelFormat::UYVY, ColorRange::Full, ColorPrimitives::bt2020>("UYVY, full range bt2020", FKB_PIX_UYVY, FKB_RANGE_FULL, FKB_PRIMITIVES_BT2020);
     test_yuv<PixelFormat::NV12, ColorRange::Limited, ColorPrimitives::bt709>("NV12, limited range bt709", FKB_PIX_NV12, FKB_RANGE_LIMITED, FKB_PRIMITIVES_BT709);
+    test_yuv<PixelFormat::P010, ColorRange::Limited, ColorPrimitives::bt2020>("P010, limited range bt2020", FKB_PIX_P010, FKB_RANGE_LIMITED, FKB_PRIMITIVES_BT2020);
+    test_yuv<PixelFormat::P210, ColorRange::Full, ColorPrimitives::bt709>("P210, full range bt709", FKB_PIX_P210, FKB_RANGE_FULL, FKB_PRIMITIVES_BT709);
+    test_yuv<PixelFormat::Y210, ColorRange::Limited, ColorPrimitives::bt601>("Y210, limited range bt601", FKB_PIX_Y210, FKB_RANGE_LIMITED, FKB_PRIMITIVES_BT601);
     test_batched<AspectRatio::PRESERVE_AR>("batched crop-resize-normalise", FKB_GEOM_RESIZE_PRESERVE_AR);
     test_batched<AspectRatio::PRESERVE_AR_RN_EVEN>("batched crop-resize-normalise, PRESERVE_AR_RN_EVEN", FKB_GEOM_RESIZE_PRESERVE_AR_RN_EVEN);
     test_batched<AspectRatio::PRESERVE_AR_LEFT>("batched crop-resize-normalise, PRESERVE_AR_LEFT", FKB_GEOM_RESIZE_PRESERVE_AR_LEFT);

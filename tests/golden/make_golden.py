@@ -46,6 +46,9 @@ CASES = {
     "split_planes_u8": ("split_planes", {"w": 150, "h": 85, "dst": [52, 32], "f32": False}),
     "nv21_limited_bt709": ("nv12_preprocess", {"w": 320, "h": 180, "dst": [80, 60], "src_format": 4, "colour": [0, 1]}),
     "uyvy_full_bt2020": ("nv12_preprocess", {"w": 320, "h": 180, "dst": [80, 60], "src_format": 5, "colour": [1, 2]}),
+    "p010_limited_bt2020": ("nv12_preprocess", {"w": 320, "h": 180, "dst": [80, 60], "src_format": 9, "colour": [0, 2]}),
+    "p210_full_bt2020": ("nv12_preprocess", {"w": 322, "h": 90, "dst": [100, 70], "src_format": 10, "colour": [1, 2]}),
+    "y210_full_bt601": ("nv12_preprocess", {"w": 320, "h": 180, "dst": [80, 60], "src_format": 11, "colour": [1, 0]}),
     "rgb_to_nv12": ("rgb_to_yuv_image", {"fmt": 3, "colour": [0, 0], "w": 162, "h": 90}),
     "rgb_to_nv21": ("rgb_to_yuv_image", {"fmt": 4, "colour": [0, 2], "w": 162, "h": 90}),
     "rgb_to_uyvy": ("rgb_to_yuv_image", {"fmt": 5, "colour": [1, 2], "w": 162, "h": 90}),

@@ -131,7 +131,7 @@ def test_validate_rejects_bad_descriptors():
     assert status(lambda p, c: setattr(p[4], "chain", 1)) == abi.ERR_INVALID                  # chain index out of range
     assert status(lambda p, c: setattr(c[0], "dst_format", abi.PIX_F32C3)) == abi.ERR_INVALID  # chain ends in uchar3
     assert status(lambda p, c: setattr(c[0], "n_ops", abi.MAX_OPS + 1)) == abi.ERR_INVALID
-    assert status(lambda p, c: setattr(c[0], "src_format", 9)) == abi.ERR_UNSUPPORTED
+    assert status(lambda p, c: setattr(c[0], "src_format", 12)) == abi.ERR_UNSUPPORTED
     assert status(lambda p, c: setattr(c[0].ops[0], "code", 77)) == abi.ERR_UNSUPPORTED
     assert status(lambda p, c: setattr(c[0].ops[0], "plane_slot", 4)) == abi.ERR_INVALID
 

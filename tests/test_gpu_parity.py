@@ -157,6 +157,17 @@ def test_yuv_formats_ranges_primitives(fmt, rng, prim):
         check(wl, force_gather=True)
 
 
+@pytest.mark.parametrize("fmt", [abi.PIX_P010, abi.PIX_P210, abi.PIX_Y210])
+@pytest.mark.parametrize("rng", [abi.RANGE_LIMITED, abi.RANGE_FULL])
+@pytest.mark.parametrize("prim", [abi.PRIMITIVES_BT601, abi.PRIMITIVES_BT709, abi.PRIMITIVES_BT2020])
+def test_ten_bit_yuv_formats(fmt, rng, prim):
+    # ushort samples; odd sizes make the last chroma pair and the last chroma row serve one pixel only
+    for shape in [dict(w=1280, h=720, dst=(321, 203)), dict(w=66, h=50, dst=(300, 301)), dict(w=130, h=46, dst=(33, 17), pitch_align=64)]:
+        wl = W.nv12_preprocess(**shape, src_format=fmt, colour=(rng, prim))
+        check(wl)
+        check(wl, use_plan=True)
+
+
 @pytest.mark.parametrize("mode", [abi.BORDER_CONSTANT, abi.BORDER_REPLICATE, abi.BORDER_REFLECT, abi.BORDER_WRAP, abi.BORDER_REFLECT_101])
 def test_border_reader_modes(mode):
     for kw in [dict(), dict(w=37, h=23), dict(w=640, h=360, dst=(224, 224))]:

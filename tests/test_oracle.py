@@ -107,6 +107,12 @@ def test_ycbcr_matrices_against_reference():
             assert lib.fkb_oracle_ycbcr_to_rgb(rng, prim, got, sub) == 0
             assert list(got) == list(want), (rng, prim)  # bit for bit
             assert list(sub) == [16.0 if rng == abi.RANGE_LIMITED else 0.0, 128.0, 128.0]
+            want10, got10, sub10, refsub = (C.c_float * 9)(), (C.c_float * 9)(), (C.c_float * 3)(), (C.c_float * 2)()
+            assert ref.fklref_ycbcr_matrix10(rng, prim, want10, refsub) == 0       # ten-bit samples
+            assert lib.fkb_oracle_ycbcr_to_rgb_bits(10, rng, prim, got10, sub10) == 0
+            assert list(got10) == list(want10), (rng, prim)
+            assert list(sub10) == [refsub[0] if rng == abi.RANGE_LIMITED else 0.0, refsub[1], refsub[1]]
+    assert lib.fkb_oracle_ycbcr_to_rgb_bits(9, 0, 0, got, sub) != 0
 
 
 @pytest.mark.skipif(not oracle.have_ref(), reason="reference-backed checker not built")
@@ -138,7 +144,10 @@ def test_oracle_write_yuv_matches_reference_backend(fmt, rng, prim):
 YUV_CASES = [(abi.PIX_NV12, abi.RANGE_FULL, abi.PRIMITIVES_BT709), (abi.PIX_NV12, abi.RANGE_LIMITED, abi.PRIMITIVES_BT601),
              (abi.PIX_NV12, abi.RANGE_LIMITED, abi.PRIMITIVES_BT2020), (abi.PIX_NV21, abi.RANGE_FULL, abi.PRIMITIVES_BT601),
              (abi.PIX_NV21, abi.RANGE_LIMITED, abi.PRIMITIVES_BT709), (abi.PIX_UYVY, abi.RANGE_FULL, abi.PRIMITIVES_BT2020),
-             (abi.PIX_UYVY, abi.RANGE_LIMITED, abi.PRIMITIVES_BT601)]
+             (abi.PIX_UYVY, abi.RANGE_LIMITED, abi.PRIMITIVES_BT601),
+             (abi.PIX_P010, abi.RANGE_LIMITED, abi.PRIMITIVES_BT2020), (abi.PIX_P010, abi.RANGE_FULL, abi.PRIMITIVES_BT709),
+             (abi.PIX_P210, abi.RANGE_LIMITED, abi.PRIMITIVES_BT709), (abi.PIX_P210, abi.RANGE_FULL, abi.PRIMITIVES_BT2020),
+             (abi.PIX_Y210, abi.RANGE_LIMITED, abi.PRIMITIVES_BT2020), (abi.PIX_Y210, abi.RANGE_FULL, abi.PRIMITIVES_BT601)]
 
 
 @pytest.mark.skipif(not oracle.have_ref(), reason="reference-backed checker not built")

@@ -25,7 +25,7 @@ GEOM_RESIZE_PRESERVE_AR_RN_EVEN, GEOM_RESIZE_PRESERVE_AR_LEFT = 3, 4
 PLANE_DEFAULT = 0x80000000  # fkb_plane_desc.chain bit: the plane's read yields bg (conditional batch read)
 WRITE_PACKED, WRITE_SPLIT, WRITE_SPLIT_PLANES, WRITE_NV12, WRITE_NV21, WRITE_UYVY = 1, 2, 3, 4, 5, 6
 BORDER_NONE, BORDER_CONSTANT, BORDER_REPLICATE, BORDER_REFLECT, BORDER_WRAP, BORDER_REFLECT_101 = 0, 1, 2, 3, 4, 5
-OP_CAST_F32, OP_MUL, OP_ADD, OP_SUB, OP_DIV, OP_REORDER_ZYX, OP_YUV2RGB, OP_SATCAST_U8, OP_RGB2YUV = 1, 2, 3, 4, 5, 6, 7, 8, 9
+OP_CAST_F32, OP_MUL, OP_ADD, OP_SUB, OP_DIV, OP_REORDER_ZYX, OP_YUV2RGB, OP_SATCAST_U8, OP_RGB2YUV, OP_ADD_ALPHA = 1, 2, 3, 4, 5, 6, 7, 8, 9, 10
 
 
 class Op(C.Structure):

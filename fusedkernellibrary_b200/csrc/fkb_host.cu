@@ -49,6 +49,7 @@ int check_ops(const fkb_chain_desc& ch, uint32_t first, uint32_t last, ValueType
         case FKB_OP_REORDER_ZYX: break;
         case FKB_OP_YUV2RGB: case FKB_OP_RGB2YUV: if (t != VT_U8) return FKB_ERR_INVALID; t = VT_F32; break;
         case FKB_OP_SATCAST_U8: if (t != VT_F32) return FKB_ERR_INVALID; t = VT_U8; break;
+        case FKB_OP_ADD_ALPHA: break;  // uchar3 -> uchar4 or float3 -> float4; check_chain counts it
         default: return FKB_ERR_UNSUPPORTED;
         }
     }
@@ -62,10 +63,15 @@ int check_chain(const fkb_chain_desc& ch) {
         ch.src_format != FKB_PIX_UYVY && ch.src_format != FKB_PIX_U8C4 && !float_src && !wide_yuv) return FKB_ERR_UNSUPPORTED;
     const bool four = ch.dst_format == FKB_PIX_U8C4 || ch.dst_format == FKB_PIX_F32C4;  // the chain keeps four channels
     if (ch.dst_format != FKB_PIX_U8C3 && ch.dst_format != FKB_PIX_F32C3 && !four) return FKB_ERR_UNSUPPORTED;
+    uint32_t n_alpha = 0;  // AddOpaqueAlpha: the step from three channels to four
+    for (uint32_t i = 0; i < ch.n_ops && i < FKB_MAX_OPS; ++i) n_alpha += ch.ops[i].code == FKB_OP_ADD_ALPHA;
     if (four) {
-        if (ch.src_format != FKB_PIX_U8C4 || ch.write_kind != FKB_WRITE_PACKED) return FKB_ERR_UNSUPPORTED;
+        if ((ch.src_format != FKB_PIX_U8C4 && ch.src_format != FKB_PIX_U8C3) || ch.write_kind != FKB_WRITE_PACKED) return FKB_ERR_UNSUPPORTED;
+        if (n_alpha != (ch.src_format == FKB_PIX_U8C3 ? 1u : 0u)) return FKB_ERR_INVALID;
         for (uint32_t i = 0; i < ch.n_ops && i < FKB_MAX_OPS; ++i)
             if (ch.ops[i].code == FKB_OP_YUV2RGB || ch.ops[i].code == FKB_OP_RGB2YUV) return FKB_ERR_UNSUPPORTED;
+    } else if (n_alpha) {
+        return FKB_ERR_INVALID;
     }
     if (ch.geometry > FKB_GEOM_RESIZE_PRESERVE_AR_LEFT) return FKB_ERR_UNSUPPORTED;
     if (ch.write_kind < FKB_WRITE_PACKED || ch.write_kind > FKB_WRITE_UYVY) return FKB_ERR_UNSUPPORTED;

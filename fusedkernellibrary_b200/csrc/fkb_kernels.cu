@@ -263,7 +263,7 @@ __global__ void __launch_bounds__(256) gather_kernel(const __grid_constant__ Lau
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// gather4_kernel: chains that keep four channels (uchar4 -> ... -> uchar4 | float4)
+// gather4_kernel: chains that write four channels (uchar4 | uchar3 + opaque alpha -> ... -> uchar4 | float4)
 // ---------------------------------------------------------------------------------------------------------
 // One output pixel per thread; a source pixel is one 32-bit load.  The ops are Cast, Mul / Add / Sub / Div with four
 // operands (the fourth in fkb_chain_desc::op_w or PlaneRec::params_w), the BGRA <-> RGBA reorder and SaturateCast.
@@ -277,6 +277,12 @@ __device__ __forceinline__ bool read_tap4(const fkb_chain_desc& ch, const PlaneR
             X = border_index(ch.border, X, w);
             Y = border_index(ch.border, Y, h);
         }
+    }
+    if (ch.src_format == FKB_PIX_U8C3) {  // three channels until FKB_OP_ADD_ALPHA appends the fourth
+        const uint8_t* q3 = pl.src + static_cast<size_t>(Y) * pl.src_pitch + static_cast<size_t>(X) * 3;
+        o[0] = static_cast<float>(__ldg(q3)); o[1] = static_cast<float>(__ldg(q3 + 1)); o[2] = static_cast<float>(__ldg(q3 + 2));
+        o[3] = 0.f;
+        return false;
     }
     const uint8_t* q = pl.src + static_cast<size_t>(Y) * pl.src_pitch + static_cast<size_t>(X) * 4;
     uint32_t px;
@@ -327,6 +333,10 @@ __device__ __forceinline__ void apply_ops4(float (&v)[N][4], const fkb_chain_des
             for (int n = 0; n < N; ++n)
 #pragma unroll
                 for (int c = 0; c < 4; ++c) v[n][c] = sat_u8_as_float(v[n][c]);
+            break;
+        case FKB_OP_ADD_ALPHA:
+#pragma unroll
+            for (int n = 0; n < N; ++n) v[n][3] = ch.ops[i].v[0];
             break;
         default: break;  // FKB_OP_CAST_F32: values are already carried as fp32
         }

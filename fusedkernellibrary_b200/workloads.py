@@ -354,6 +354,38 @@ def rgba_crops(reorder=False, f32=False, w=1920, h=1080, dst=(64, 64), rects=RGB
                     f"four channels reorder={reorder} f32={f32}", extra={"reorder": reorder, "f32": f32, "m1": m1, "a1": a1, "rects": rects})
 
 
+def add_alpha_crops(swap=False, f32=False, w=640, h=360, dst=(64, 48), seed=21) -> Workload:
+    """One uchar3 frame, five crops -> Resize -> Mul<float3> -> ColorConversion<COLOR_BGR2BGRA | COLOR_BGR2RGBA, float3, float4>
+    (an opaque alpha channel of 255 is appended, after a channel swap with ``swap``) -> Mul<float4> ->
+    [SaturateCast -> TensorWrite<uchar4> | TensorWrite<float4>]."""
+    pitch = _pitch(w * 3, 16)
+    dw, dh = dst
+    m3, m4 = (0.5, 1.25, 2.0), (1.0, 0.5, 0.75, 0.5)
+    rects = [(10, 20, 100, 60), (w // 2, h // 3, 64, 48), (0, 0, w, h), (w - 33, h - 21, 33, 21), (w // 3, h // 3, w // 5, h // 2)]
+    ops, op_w = [op(abi.OP_MUL, m3)], [0.0]
+    if swap:
+        ops.append(op(abi.OP_REORDER_ZYX)); op_w.append(0.0)
+    ops += [op(abi.OP_ADD_ALPHA, (255.0, 0.0, 0.0)), op(abi.OP_MUL, m4[:3])]
+    op_w += [0.0, m4[3]]
+    if not f32:
+        ops.append(op(abi.OP_SATCAST_U8)); op_w.append(0.0)
+    elt = 16 if f32 else 4
+    ch = chain(abi.PIX_U8C3, abi.GEOM_RESIZE_IGNORE_AR, abi.PIX_F32C4 if f32 else abi.PIX_U8C4, abi.WRITE_PACKED, ops, op_w=op_w)
+    planes = [PlaneSpec(0, 0, i * dw * dh * elt, w, h, pitch, r, dw, dh, dw * elt) for i, r in enumerate(rects)]
+    return Workload("add_alpha_crops", [ch], [_frame(seed, pitch * h)], [5 * dw * dh * elt], planes,
+                    f"opaque alpha appended swap={swap} f32={f32}", extra={"swap": swap, "f32": f32, "m3": m3, "m4": m4, "rects": rects})
+
+
+def add_alpha_image(swap=False, w=322, h=180, seed=22) -> Workload:
+    """PerThreadRead<uchar3> -> ColorConversion<COLOR_BGR2BGRA | COLOR_BGR2RGBA, uchar3, uchar4> -> PerThreadWrite<uchar4>."""
+    pitch, opitch = _pitch(w * 3, 16), _pitch(w * 4, 64)
+    ops = ([op(abi.OP_REORDER_ZYX)] if swap else []) + [op(abi.OP_ADD_ALPHA, (255.0, 0.0, 0.0))]
+    ch = chain(abi.PIX_U8C3, abi.GEOM_NONE, abi.PIX_U8C4, abi.WRITE_PACKED, ops)
+    planes = [PlaneSpec(0, 0, 0, w, h, pitch, (0, 0, w, h), w, h, opitch)]
+    return Workload("add_alpha_image", [ch], [_frame(seed, pitch * h)], [opitch * h], planes, f"uchar3 -> uchar4 swap={swap}",
+                    extra={"swap": swap})
+
+
 def conditional_resize(used=5, w=320, h=180, dst=(96, 64), default=(7, 200, 33), seed=11) -> Workload:
     """BatchRead<CONDITIONAL_WITH_DEFAULT> over eight frames of which `used` are read -> Resize IGNORE_AR -> Mul ->
     TensorWrite<float3>; the other planes come out as Mul(float3(default))."""

@@ -125,8 +125,14 @@ enum {
     FKB_OP_YUV2RGB = 7,      /* ConvertYUVToRGB<p8bit,CR,CP> (color_conversion.h:150-174): subtracts
                                 chain.yuv_sub, multiplies by chain.ccm rows, sums (x+y)+z          u8 -> f32 */
     FKB_OP_SATCAST_U8 = 8,   /* SaturateCast<float3,uchar3>    (image_processing/saturate.h:25-36) f32 -> u8 */
-    FKB_OP_RGB2YUV = 9       /* ConvertRGBToYUV<p8bit,CR,CP> (color_conversion.h:176-199): ccm2 x (R,G,B), then adds
+    FKB_OP_RGB2YUV = 9,      /* ConvertRGBToYUV<p8bit,CR,CP> (color_conversion.h:176-199): ccm2 x (R,G,B), then adds
                                 yuv_add to (Y,Cb,Cr)                                                   u8 -> f32 */
+    FKB_OP_ADD_ALPHA = 10    /* AddOpaqueAlpha<I,CD> (color_conversion.h:81-94), the second half of
+                                ColorConversion<COLOR_BGR2BGRA|COLOR_RGB2RGBA> (and, after FKB_OP_REORDER_ZYX, of
+                                COLOR_BGR2RGBA|COLOR_RGB2BGRA): appends a fourth channel v[0] = maxDepthValue<CD> (255
+                                for p8bit, 1 for fn8bit).  Exactly once in a chain from a three-channel source
+                                (FKB_PIX_U8C3) to a four-channel write; ops before it work on three channels,
+                                ops after it on four                                                any */
 };
 
 typedef struct fkb_op {

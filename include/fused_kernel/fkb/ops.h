@@ -29,7 +29,8 @@ enum class AspectRatio { PRESERVE_AR = 0, IGNORE_AR = 1, PRESERVE_AR_RN_EVEN = 2
 enum class BorderType : int { CONSTANT = 0, REPLICATE = 1, REFLECT = 2, WRAP = 3, REFLECT_101 = 4, TRANSPARENT_ = 5, DEFAULT = REFLECT_101, ISOLATED = 16 };
 enum class PlanePolicy { PROCESS_ALL = 0, CONDITIONAL_WITH_DEFAULT = 1 };  // batch_operations.h:75
 // (color_conversion.h:408-426; the codes that discard the alpha channel of a four-channel source are the ones beside BGR<->RGB)
-enum class ColorConversionCodes { COLOR_BGR2RGB, COLOR_RGB2BGR, COLOR_BGRA2BGR, COLOR_RGBA2RGB, COLOR_BGRA2RGB, COLOR_RGBA2BGR, COLOR_BGRA2RGBA, COLOR_RGBA2BGRA };
+enum class ColorConversionCodes { COLOR_BGR2RGB, COLOR_RGB2BGR, COLOR_BGRA2BGR, COLOR_RGBA2RGB, COLOR_BGRA2RGB, COLOR_RGBA2BGR, COLOR_BGRA2RGBA, COLOR_RGBA2BGRA,
+                                  COLOR_BGR2BGRA, COLOR_RGB2RGBA = COLOR_BGR2BGRA, COLOR_BGR2RGBA, COLOR_RGB2BGRA = COLOR_BGR2RGBA };
 
 namespace detail {
 struct SrcPlane { const void* data{nullptr}; uint pitch{0}, w{0}, h{0}; };
@@ -109,18 +110,25 @@ struct SaturateCast {
                   "the B200 kernels implement SaturateCast<float3,uchar3> and SaturateCast<float4,uchar4>");
     static constexpr auto build() { return ComputeIOp<FKB_OP_SATCAST_U8, I, O>{}; }
 };
-// A step of a chain that changes the pixel type without arithmetic (the alpha channel of a uchar4 / float4 is dropped)
+// A step of a chain that changes the number of channels without arithmetic: the alpha channel of a uchar4 / float4 is
+// dropped, or an opaque one is appended to a uchar3 / float3 (AddOpaqueAlpha, color_conversion.h:81-94)
 template <typename I, typename O>
 struct RetypeIOp {
     using InputType = I;
     using OutputType = O;
-    bool reorder;  // BGRA2RGB / RGBA2BGR: the remaining channels are also reversed
+    bool reorder;          // BGRA2RGB / RGBA2BGR / BGR2RGBA / RGB2BGRA: the three colour channels are also reversed
+    bool add_alpha{false};
+    float alpha{0.f};      // maxDepthValue<CD>
 };
-template <ColorConversionCodes CODE, typename I, typename O = I>
+template <ColorConversionCodes CODE, typename I, typename O = I, ColorDepth CD = ColorDepth::p8bit>
 struct ColorConversion {
     static constexpr bool swap4 = CODE == ColorConversionCodes::COLOR_BGRA2RGBA || CODE == ColorConversionCodes::COLOR_RGBA2BGRA;
     static constexpr bool swap3 = CODE == ColorConversionCodes::COLOR_BGR2RGB || CODE == ColorConversionCodes::COLOR_RGB2BGR || swap4;
-    static constexpr bool drop = !swap3;
+    static constexpr bool add = CODE == ColorConversionCodes::COLOR_BGR2BGRA || CODE == ColorConversionCodes::COLOR_BGR2RGBA;
+    static constexpr bool drop = !swap3 && !add;
+    static_assert(!add || (std::is_same_v<I, uchar3> && std::is_same_v<O, uchar4>) || (std::is_same_v<I, float3> && std::is_same_v<O, float4>),
+                  "BGR2BGRA / RGB2RGBA / BGR2RGBA / RGB2BGRA take uchar3 -> uchar4 or float3 -> float4");
+    static_assert(!add || CD == ColorDepth::p8bit || CD == ColorDepth::fn8bit, "the appended alpha is that of an 8-bit depth (255) or of a normalised one (1)");
     static_assert(!swap3 || swap4 || (std::is_same_v<I, O> && (std::is_same_v<I, float3> || std::is_same_v<I, uchar3>)),
                   "BGR<->RGB on uchar3 or float3 is the three-channel colour conversion the B200 kernels implement");
     static_assert(!swap4 || (std::is_same_v<I, O> && (std::is_same_v<I, float4> || std::is_same_v<I, uchar4>)),
@@ -129,6 +137,7 @@ struct ColorConversion {
                   "BGRA2BGR / RGBA2RGB / BGRA2RGB / RGBA2BGR take uchar4 -> uchar3 or float4 -> float3");
     static constexpr auto build() {
         if constexpr (swap3) return ComputeIOp<FKB_OP_REORDER_ZYX, I, O>{};
+        else if constexpr (add) return RetypeIOp<I, O>{CODE == ColorConversionCodes::COLOR_BGR2RGBA, true, CD == ColorDepth::p8bit ? 255.f : 1.f};
         else return RetypeIOp<I, O>{CODE == ColorConversionCodes::COLOR_BGRA2RGB || CODE == ColorConversionCodes::COLOR_RGBA2BGR};
     }
 };
@@ -280,6 +289,7 @@ struct ReadIOp {
         static_assert(std::is_same_v<I, OutT>, "the operation's InputType is not the OutputType of the operation before it");
         detail::ReadState s = st;
         if (r.reorder) s.ops.push_back(detail::OpRec{FKB_OP_REORDER_ZYX, {{0.f, 0.f, 0.f, 0.f}}});
+        if (r.add_alpha) s.ops.push_back(detail::OpRec{FKB_OP_ADD_ALPHA, {{r.alpha, 0.f, 0.f, 0.f}}});
         return ReadIOp<O, BATCH>(std::move(s));
     }
     template <uint16_t C, typename I, typename O>

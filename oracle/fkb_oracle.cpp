@@ -121,6 +121,9 @@ inline V3 apply_ops(V3 v, const fkb_chain_desc& ch, const fkb_plane_desc& pl, ui
         case FKB_OP_SATCAST_U8:
             for (int c = 0; c < nc; ++c) v.c[c] = static_cast<float>(sat_u8(v.c[c]));
             break;
+        case FKB_OP_ADD_ALPHA:  // AddOpaqueAlpha::exec (color_conversion.h:89-92): the input's channels, then maxDepthValue<CD>
+            v.c[3] = op.v[0];
+            break;
         default: break;
         }
     }

@@ -331,6 +331,42 @@ int fklref_rgba_crops(const uint8_t* frame, int w, int h, int pitch, const int32
     return 0;
 }
 
+// Conversions that append an opaque alpha channel.  One uchar3 frame, five crops -> Crop -> Resize -> Mul<float3> ->
+// ColorConversion<COLOR_BGR2BGRA | COLOR_BGR2RGBA, float3, float4> (alpha = 255) -> Mul<float4> ->
+// [SaturateCast<float4,uchar4> -> TensorWrite<uchar4> | TensorWrite<float4>].
+int fklref_add_alpha_crops(const uint8_t* frame, int w, int h, int pitch, const int32_t* rects, int dw, int dh, const float* m3, const float* m4,
+                           int swap, int f32, void* out) {
+    CpuStream stream;
+    std::array<Rect, 5> rs;
+    for (size_t i = 0; i < 5; ++i) rs[i] = Rect(rects[4 * i], rects[4 * i + 1], rects[4 * i + 2], rects[4 * i + 3]);
+    const auto read = PerThreadRead<ND::_2D, uchar3>::build(wrap_frame(frame, w, h, pitch));
+    const auto crop = Crop<>::build(rs);
+    const auto resize = Resize<InterpolationType::INTER_LINEAR>::build(Size(dw, dh));
+    const auto mul3 = Mul<float3>::build(make_<float3>(m3[0], m3[1], m3[2]));
+    const auto mul4 = Mul<float4>::build(make_<float4>(m4[0], m4[1], m4[2], m4[3]));
+    const auto keep = ColorConversion<ColorConversionCodes::COLOR_BGR2BGRA, float3, float4>::build();
+    const auto flip = ColorConversion<ColorConversionCodes::COLOR_BGR2RGBA, float3, float4>::build();
+    if (f32) {
+        Tensor<float4> t(static_cast<float4*>(out), dw, dh, 5, 1, MemType::Host, 0);
+        if (swap) executeOperations<CpuDPP>(stream, read, crop, resize, mul3, flip, mul4, TensorWrite<float4>::build(t));
+        else executeOperations<CpuDPP>(stream, read, crop, resize, mul3, keep, mul4, TensorWrite<float4>::build(t));
+    } else {
+        Tensor<uchar4> t(static_cast<uchar4*>(out), dw, dh, 5, 1, MemType::Host, 0);
+        if (swap) executeOperations<CpuDPP>(stream, read, crop, resize, mul3, flip, mul4, SaturateCast<float4, uchar4>::build(), TensorWrite<uchar4>::build(t));
+        else executeOperations<CpuDPP>(stream, read, crop, resize, mul3, keep, mul4, SaturateCast<float4, uchar4>::build(), TensorWrite<uchar4>::build(t));
+    }
+    return 0;
+}
+// PerThreadRead<uchar3> -> ColorConversion<COLOR_BGR2BGRA | COLOR_BGR2RGBA, uchar3, uchar4> -> PerThreadWrite<uchar4>
+int fklref_add_alpha_image(const uint8_t* frame, int w, int h, int pitch, int swap, uint8_t* out, int opitch) {
+    CpuStream stream;
+    const auto read = PerThreadRead<ND::_2D, uchar3>::build(wrap_frame(frame, w, h, pitch));
+    const Ptr2D<uchar4> o(reinterpret_cast<uchar4*>(out), w, h, opitch, MemType::Host, 0);
+    if (swap) executeOperations<CpuDPP>(stream, read, ColorConversion<ColorConversionCodes::COLOR_BGR2RGBA, uchar3, uchar4>::build(), PerThreadWrite<ND::_2D, uchar4>::build(o));
+    else executeOperations<CpuDPP>(stream, read, ColorConversion<ColorConversionCodes::COLOR_BGR2BGRA, uchar3, uchar4>::build(), PerThreadWrite<ND::_2D, uchar4>::build(o));
+    return 0;
+}
+
 // Four frames -> Resize(IGNORE_AR) -> Mul -> TensorTSplit<float3> into a colour-plane-transposed tensor
 // (memory_operations.h:214-241): all R planes, then all G planes, then all B planes.
 int fklref_resize_tsplit_f32(const uint8_t* const* frames, int w, int h, int pitch, int dw, int dh, const float* mul, float* out) {

@@ -41,4 +41,5 @@ GOLDEN_CASES = ["readme_crops_full", "readme_crops_pitched", "vertical_fusion_sm
                 "border_constant", "border_replicate", "border_reflect", "border_wrap", "border_reflect_101", "nv12_border_constant",
                 "conditional_resize", "conditional_pointwise", "tsplit_resize", "split_planes_f32", "split_planes_u8",
                 "nv21_limited_bt709", "uyvy_full_bt2020", "rgb_to_nv12", "rgb_to_nv21", "rgb_to_uyvy", "bgra_crops_swap",
-                "rgba_crops_u8", "rgba_crops_f32_reorder", "p010_limited_bt2020", "p210_full_bt2020", "y210_full_bt601"]
+                "rgba_crops_u8", "rgba_crops_f32_reorder", "p010_limited_bt2020", "p210_full_bt2020", "y210_full_bt601",
+                "add_alpha_crops_u8_swap", "add_alpha_image"]

@@ -385,6 +385,49 @@ static void test_four_channels() {
     report("four channels to the Write (uchar4 -> uchar4 tensor)", std::memcmp(want.data(), output.ptrPinned().data, want.size()) == 0);
 }
 
+// ---- conversions that append an opaque alpha channel: uchar3 source, uchar4 tensor ---------------------------------------------------
+static void test_add_alpha() {
+    Stream stream;
+    Ptr2D<uchar3> input(640, 360);
+    fill_random(input, 901);
+    input.upload(stream);
+    const std::array<Rect, 3> crops{Rect(0, 0, 120, 40), Rect(100, 200, 60, 40), Rect(400, 20, 30, 50)};
+    Tensor<uchar4> output(48, 40, 3);
+    executeOperations<TransformDPP<>>(input, stream, Crop<>::build(crops), Resize<InterpolationType::INTER_LINEAR>::build(Size(48, 40)),
+                                      Mul<float3>::build(make_<float3>(0.5f, 1.f, 1.5f)),
+                                      ColorConversion<ColorConversionCodes::COLOR_BGR2RGBA, float3, float4>::build(),
+                                      Mul<float4>::build(make_<float4>(1.f, 0.5f, 0.75f, 0.5f)), SaturateCast<float4, uchar4>::build(),
+                                      TensorWrite<uchar4>::build(output));
+    output.download(stream);
+    Ptr2D<uchar4> image(640, 360);  // and the conversion alone, on byte pixels
+    executeOperations<TransformDPP<>>(stream, PerThreadRead<ND::_2D, uchar3>::build(input),
+                                      ColorConversion<ColorConversionCodes::COLOR_RGB2RGBA, uchar3, uchar4>::build(),
+                                      PerThreadWrite<ND::_2D, uchar4>::build(image));
+    image.download(stream);
+    stream.sync();
+    fkb_chain_desc ch{};
+    ch.src_format = FKB_PIX_U8C3; ch.geometry = FKB_GEOM_RESIZE_IGNORE_AR; ch.dst_format = FKB_PIX_U8C4; ch.write_kind = FKB_WRITE_PACKED;
+    ch.n_ops = 5;
+    ch.ops[0] = op(FKB_OP_MUL, 0.5f, 1.f, 1.5f); ch.ops[1] = op(FKB_OP_REORDER_ZYX); ch.ops[2] = op(FKB_OP_ADD_ALPHA, 255.f);
+    ch.ops[3] = op(FKB_OP_MUL, 1.f, 0.5f, 0.75f); ch.op_w[3] = 0.5f; ch.ops[4] = op(FKB_OP_SATCAST_U8);
+    std::vector<uint8_t> want(48 * 40 * 4 * 3);
+    std::vector<fkb_plane_desc> planes;
+    for (size_t i = 0; i < 3; ++i) planes.push_back(host_plane(input, crops[i], 48, 40, want.data() + i * 48 * 40 * 4, 48 * 4, ch.geometry));
+    fkb_oracle_run(&ch, 1, planes.data(), 3, 1);
+    report("BGR2RGBA in a resize chain (uchar3 -> uchar4 tensor)", std::memcmp(want.data(), output.ptrPinned().data, want.size()) == 0);
+    fkb_chain_desc pc{};
+    pc.src_format = FKB_PIX_U8C3; pc.geometry = FKB_GEOM_NONE; pc.dst_format = FKB_PIX_U8C4; pc.write_kind = FKB_WRITE_PACKED;
+    pc.n_ops = 1; pc.ops[0] = op(FKB_OP_ADD_ALPHA, 255.f);
+    const auto o = image.ptrPinned();
+    std::vector<uint8_t> want2(static_cast<size_t>(o.dims.pitch) * 360, 0);
+    fkb_plane_desc d = host_plane(input, Rect(0, 0, 640, 360), 640, 360, want2.data(), o.dims.pitch, pc.geometry);
+    fkb_oracle_run(&pc, 1, &d, 1, 1);
+    bool same = true;
+    for (uint y = 0; y < 360; ++y)
+        same = same && std::memcmp(want2.data() + y * o.dims.pitch, reinterpret_cast<const uint8_t*>(o.data) + y * o.dims.pitch, 640 * 4) == 0;
+    report("RGB2RGBA on byte pixels (uchar3 -> uchar4 image)", same);
+}
+
 // ---- CircularTensor: after n updates plane z holds the chain's result for the z-th newest (or oldest) frame --------------------
 template <CircularTensorOrder ORDER, ColorPlanes MODE>
 static void test_circular(const char* what) {
@@ -581,6 +624,7 @@ int main() {
     test_circular_packed();
     test_bgra_source();
     test_four_channels();
+    test_add_alpha();
     test_write_yuv();
     test_split_write();
     test_border<BorderType::CONSTANT>("BorderReader<CONSTANT> (complete form, operator&)");

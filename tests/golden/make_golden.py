@@ -53,6 +53,8 @@ CASES = {
     "rgb_to_nv21": ("rgb_to_yuv_image", {"fmt": 4, "colour": [0, 2], "w": 162, "h": 90}),
     "rgb_to_uyvy": ("rgb_to_yuv_image", {"fmt": 5, "colour": [1, 2], "w": 162, "h": 90}),
     "bgra_crops_swap": ("bgra_crops", {"swap": True, "w": 160, "h": 100, "dst": [48, 40]}),
+    "add_alpha_crops_u8_swap": ("add_alpha_crops", {"swap": True, "w": 480, "h": 270, "dst": [32, 24]}),
+    "add_alpha_image": ("add_alpha_image", {"w": 162, "h": 90}),
     "rgba_crops_u8": ("rgba_crops", {"w": 480, "h": 270, "dst": [32, 32], "rects": [[0, 0, 120, 40], [100, 200, 60, 40], [400, 20, 30, 50], [300, 100, 30, 30], [40, 40, 40, 40]]}),
     "rgba_crops_f32_reorder": ("rgba_crops", {"reorder": True, "f32": True, "w": 480, "h": 270, "dst": [32, 32],
                                               "rects": [[0, 0, 120, 40], [100, 200, 60, 40], [400, 20, 30, 50], [300, 100, 30, 30], [40, 40, 40, 40]]}),

@@ -140,6 +140,15 @@ def test_validate_rejects_bad_descriptors():
     wl2 = W.vertical_fusion(w=32, h=4)
     arr = (abi.ChainDesc * 1)(bad)
     assert lib.fkb_validate(arr, 1, _bound(wl2), 1) == abi.ERR_INVALID
+    # AddOpaqueAlpha: once, and only on the way from a three-channel source to a four-channel write
+    wl4 = W.add_alpha_image(w=32, h=4)
+    assert lib.fkb_validate(wl4.chain_array(), 1, _bound(wl4), 1) == abi.OK
+    two = W.chain(abi.PIX_U8C3, abi.GEOM_NONE, abi.PIX_U8C4, abi.WRITE_PACKED, [W.op(abi.OP_ADD_ALPHA, (255, 0, 0))] * 2)
+    assert lib.fkb_validate((abi.ChainDesc * 1)(two), 1, _bound(wl4), 1) == abi.ERR_INVALID
+    none = W.chain(abi.PIX_U8C3, abi.GEOM_NONE, abi.PIX_U8C4, abi.WRITE_PACKED, [])
+    assert lib.fkb_validate((abi.ChainDesc * 1)(none), 1, _bound(wl4), 1) == abi.ERR_INVALID
+    three = W.chain(abi.PIX_U8C3, abi.GEOM_NONE, abi.PIX_U8C3, abi.WRITE_PACKED, [W.op(abi.OP_ADD_ALPHA, (255, 0, 0))])
+    assert lib.fkb_validate((abi.ChainDesc * 1)(three), 1, _bound(wl2), 1) == abi.ERR_INVALID
     # geometry NONE cannot write more pixels than the crop holds
     wl3 = W.crop_reorder(n=1)
     p3 = _bound(wl3)

@@ -80,6 +80,10 @@ SMALL = {
     "rgba_crops_f32_reorder": lambda: W.rgba_crops(reorder=True, f32=True, w=333, h=211, dst=(77, 45), rects=((0, 0, 333, 211), (5, 7, 100, 90), (300, 180, 33, 31))),
     "rgba_crops_border": lambda: W.rgba_crops(w=200, h=120, dst=(64, 48), rects=((-20, -10, 90, 70), (150, 90, 120, 80), (10, 10, 50, 40)), border=abi.BORDER_CONSTANT),
     "rgba_crops_border_wrap": lambda: W.rgba_crops(f32=True, w=200, h=120, dst=(64, 48), rects=((-20, -10, 90, 70), (150, 90, 120, 80)), border=abi.BORDER_WRAP),
+    "add_alpha_crops": lambda: W.add_alpha_crops(),
+    "add_alpha_crops_f32_swap": lambda: W.add_alpha_crops(swap=True, f32=True, w=333, h=211, dst=(77, 45)),
+    "add_alpha_image": lambda: W.add_alpha_image(),
+    "add_alpha_image_swap": lambda: W.add_alpha_image(swap=True, w=1001, h=37),
     "bgra_crops": lambda: W.bgra_crops(),
     "batched_uchar4": lambda: W.batched_crop_resize(n_frames=4, crops_per_frame=8, w=960, h=540, src4=True),
     "bgra_crops_swap": lambda: W.bgra_crops(swap=True, w=333, h=97, dst=(111, 50)),

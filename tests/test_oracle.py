@@ -175,6 +175,8 @@ def test_oracle_matches_golden_fixture(name):
     W.border_crops(abi.BORDER_WRAP), W.border_crops(abi.BORDER_REFLECT_101), W.border_crops(abi.BORDER_WRAP, w=37, h=23),
     W.border_crops(abi.BORDER_REFLECT, w=37, h=23), W.border_crops(abi.BORDER_REFLECT_101, w=37, h=23), W.nv12_border_constant(),
     W.rgba_crops(), W.rgba_crops(reorder=True), W.rgba_crops(f32=True), W.rgba_crops(reorder=True, f32=True),
+    W.add_alpha_crops(), W.add_alpha_crops(swap=True), W.add_alpha_crops(f32=True), W.add_alpha_crops(swap=True, f32=True),
+    W.add_alpha_image(), W.add_alpha_image(swap=True),
     W.bgra_crops(), W.bgra_crops(swap=True), W.split_planes(), W.split_planes(f32=False), W.tsplit_resize(), W.conditional_resize(), W.conditional_resize(used=0), W.conditional_resize(used=8), W.conditional_pointwise(),
 ], ids=lambda w: w.name + w.description[-7:].replace(" ", "_"))
 def test_oracle_matches_reference_backend(wl):

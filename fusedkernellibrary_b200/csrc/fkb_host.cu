@@ -271,12 +271,14 @@ bool rgb_kernel_takes(const fkb_chain_desc& ch, const PlaneRec& r) {
 // Output rows a warp processes per item.  Inside an item the next row's footprint is prefetched while the current
 // row is computed, so longer items pipeline better; more items balance better (warps claim them from a counter).  Large
 // launches get about sixteen items per resident warp — measured on the 2048-plane crop-resize launch, 10 to 16 rows per
-// item are within 1 % of each other, 4 or 24 rows cost 3 to 12 % — launches too small to occupy every warp get one
-// row per item.
+// item are within 1 % of each other, 4 or 24 rows cost 3 to 12 %.  Launches with 16 to 128 rows per warp (256 to 1024
+// planes of that shape) get eight rows per item (4 to 7 % faster than four), smaller ones four, and launches too small
+// to occupy every warp one row per item.
 uint32_t rows_per_item(uint64_t row_segments, uint32_t resident_warps) {
-    const uint64_t per = row_segments / (static_cast<uint64_t>(resident_warps) * 16u);
-    uint32_t rpi = static_cast<uint32_t>(std::min<uint64_t>(std::max<uint64_t>(per, 1), kMaxRowsPerItem));
-    if (rpi < 4 && row_segments >= static_cast<uint64_t>(resident_warps) * 4u) rpi = 4;
+    const uint64_t per_warp = row_segments / resident_warps;
+    uint32_t rpi = static_cast<uint32_t>(std::min<uint64_t>(std::max<uint64_t>(per_warp / 16u, 1), kMaxRowsPerItem));
+    if (rpi < 8 && per_warp >= 16) rpi = 8;
+    else if (rpi < 4 && per_warp >= 4) rpi = 4;
     return rpi;
 }
 
@@ -501,8 +503,12 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         ++L.kernels;
     }
     if (n_gather) {
-        // small launches are latency-bound: one pixel per thread puts four times as many threads on the taps
-        L.gather_ppt = gather_pixels < (2u << 20) ? 1 : 4;
+        // small launches are latency-bound: one pixel per thread puts four times as many threads on the taps.  Writes of a
+        // YCbCr image go four pixels per thread much earlier: that turns their byte stores into word stores.
+        bool yuv_write = false;
+        for (uint32_t z = 0; z < n_planes; ++z)
+            yuv_write = yuv_write || (L.recs[z].kclass == KCLASS_GATHER && chains[L.recs[z].chain].write_kind >= FKB_WRITE_NV12);
+        L.gather_ppt = gather_pixels < (yuv_write ? (1u << 17) : (2u << 20)) ? 1 : 4;
         L.gather_grid = dim3((gw + 32 * L.gather_ppt - 1) / (32 * L.gather_ppt), (gh + 7) / 8, std::min<uint32_t>(n_planes, 65535u));
         ++L.kernels;
     }

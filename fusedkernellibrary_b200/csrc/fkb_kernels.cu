@@ -163,11 +163,20 @@ __global__ void __launch_bounds__(256) gather_kernel(const __grid_constant__ Lau
             for (int n = 0; n < PPT; ++n) { v[n][0] = pl.bg[0]; v[n][1] = pl.bg[1]; v[n][2] = pl.bg[2]; }
             apply_ops<PPT>(v, ch, pl, ch.geometry == FKB_GEOM_NONE ? 0 : ch.n_pre_ops, ch.n_ops);
         } else if (ch.geometry == FKB_GEOM_NONE) {
-#pragma unroll
             uint32_t outside = 0;
-            for (int n = 0; n < PPT; ++n) {
-                if (n < nvalid) outside |= static_cast<uint32_t>(read_tap_global(ch, pl, static_cast<int>(x0) + n, static_cast<int>(y), v[n])) << n;
-                else { v[n][0] = v[n][1] = v[n][2] = 0.f; }
+            const uint8_t* q12 = pl.src + static_cast<size_t>(pl.crop_y + y) * pl.src_pitch + static_cast<size_t>(pl.crop_x + x0) * 3;
+            if (PPT == 4 && nvalid == 4 && ch.src_format == FKB_PIX_U8C3 && !ch.border && (reinterpret_cast<uintptr_t>(q12) & 3) == 0) {
+                // four packed byte pixels = three aligned words
+                const uint32_t* q4 = reinterpret_cast<const uint32_t*>(q12);
+                const uint32_t w3[3] = {__ldg(q4), __ldg(q4 + 1), __ldg(q4 + 2)};
+#pragma unroll
+                for (int b = 0; b < 12; ++b) v[(b / 3) % PPT][b % 3] = static_cast<float>((w3[b >> 2] >> (8 * (b & 3))) & 0xffu);
+            } else {
+#pragma unroll
+                for (int n = 0; n < PPT; ++n) {
+                    if (n < nvalid) outside |= static_cast<uint32_t>(read_tap_global(ch, pl, static_cast<int>(x0) + n, static_cast<int>(y), v[n])) << n;
+                    else { v[n][0] = v[n][1] = v[n][2] = 0.f; }
+                }
             }
             apply_ops_bordered<PPT>(v, ch, pl, ch.n_ops, outside);
         } else {
@@ -199,7 +208,27 @@ __global__ void __launch_bounds__(256) gather_kernel(const __grid_constant__ Lau
         }
 
         uint8_t* row = pl.dst + static_cast<size_t>(y) * pl.dst_pitch;
-        if (ch.write_kind >= FKB_WRITE_NV12) {
+        if (ch.write_kind >= FKB_WRITE_NV12 && PPT == 4 && nvalid == 4 && (pl.dst_pitch & 7u) == 0 &&
+            (reinterpret_cast<uintptr_t>(pl.dst) & 7u) == 0 && (pl.dst_cstride & 3u) == 0) {
+            // four pixels of a YCbCr image with word stores (x0 is a multiple of four: two whole chroma pairs)
+            uint32_t b[4][3];
+#pragma unroll
+            for (int n = 0; n < 4; ++n)
+#pragma unroll
+                for (int c = 0; c < 3; ++c) b[n][c] = static_cast<uint32_t>(v[n % PPT][c]);
+            if (ch.write_kind == FKB_WRITE_UYVY) {
+                *reinterpret_cast<uint2*>(row + static_cast<size_t>(x0) * 2) =
+                    make_uint2(b[0][1] | (b[0][0] << 8) | (b[0][2] << 16) | (b[1][0] << 24), b[2][1] | (b[2][0] << 8) | (b[2][2] << 16) | (b[3][0] << 24));
+            } else {
+                *reinterpret_cast<uint32_t*>(row + x0) = b[0][0] | (b[1][0] << 8) | (b[2][0] << 16) | (b[3][0] << 24);
+                uint32_t* uv = reinterpret_cast<uint32_t*>(pl.dst + pl.dst_cstride + static_cast<size_t>(y >> 1) * pl.dst_pitch + x0);
+                if (ch.write_kind == FKB_WRITE_NV12) {
+                    if (!(y & 1u)) *uv = b[0][1] | (b[0][2] << 8) | (b[2][1] << 16) | (b[2][2] << 24);   // the block's first pixel
+                } else if (y == min(y | 1u, pl.dst_h - 1u)) {
+                    *uv = b[1][2] | (b[1][1] << 8) | (b[3][2] << 16) | (b[3][1] << 24);                  // the block's last pixel, V first
+                }
+            }
+        } else if (ch.write_kind >= FKB_WRITE_NV12) {
             // (Y,Cb,Cr) byte triples into a YCbCr image; the chroma rows of NV12 / NV21 start dst_cstride bytes after dst
             for (uint32_t n = 0; n < nvalid; ++n) {
                 const uint32_t x = x0 + n;

@@ -224,6 +224,8 @@ def other_configs(torch, steps: int, peak: float, widened: bool = False) -> dict
             ("border_replicate_crops", lambda: W.border_crops(abi.BORDER_REPLICATE, w=1920, h=1080, dst=(224, 224))),
             ("nv21_limited_bt601_preprocess", lambda: W.nv12_preprocess(src_format=abi.PIX_NV21, colour=(abi.RANGE_LIMITED, abi.PRIMITIVES_BT601))),
             ("uyvy_preprocess", lambda: W.nv12_preprocess(src_format=abi.PIX_UYVY, colour=(abi.RANGE_FULL, abi.PRIMITIVES_BT709))),
+            ("p010_limited_bt2020_preprocess", lambda: W.nv12_preprocess(src_format=abi.PIX_P010, colour=(abi.RANGE_LIMITED, abi.PRIMITIVES_BT2020))),
+            ("bgr_to_rgba_crops", lambda: W.add_alpha_crops(swap=True, w=1920, h=1080, dst=(224, 224))),
             ("conditional_batch_resize", lambda: W.conditional_resize(used=6, w=1920, h=1080, dst=(640, 360))),
             ("tensor_t_split_resize", lambda: W.tsplit_resize(w=1920, h=1080, dst=(640, 360))),
             ("split_planes_resize", lambda: W.split_planes(w=1920, h=1080, dst=(960, 540))),

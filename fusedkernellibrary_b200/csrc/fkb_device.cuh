@@ -68,6 +68,7 @@ struct Nv12Consts {
     uint32_t preserve_ar, f32, split, slots;
     uint32_t src_px;      // 0: NV12 / NV21 source (nv12 kernels); 3 or 4: bytes per pixel of a packed byte source (rgb_kernel)
     uint32_t vu;          // NV21: the chroma pairs are stored V,U
+    uint32_t yuv_fmt;     // with src_px == 0: the FKB_PIX_* code of the YCbCr source (nv12_kernel reads all six; the pair kernel NV12 / NV21)
     uint32_t pair;        // nv12_pair_kernel's conditions hold (two pixels per thread, reduced colour matrix)
     uint32_t wide_store;  // with `pair`: destinations, pitches and channel strides are multiples of 8 bytes
     float kmag[3];        // with `pair`: 2^23 + sub[c], exact

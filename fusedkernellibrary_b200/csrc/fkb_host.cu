@@ -208,9 +208,19 @@ void classify(const fkb_chain_desc& ch, PlaneRec& r) {
         const int64_t x = static_cast<int32_t>(r.crop_x), y = static_cast<int32_t>(r.crop_y);
         if (x < 0 || y < 0 || x + r.crop_w > static_cast<int64_t>(r.src_w) || y + r.crop_h > static_cast<int64_t>(r.src_h)) return;
     }
-    if ((ch.src_format == FKB_PIX_NV12 || ch.src_format == FKB_PIX_NV21) && ch.geometry != FKB_GEOM_NONE && ch.n_pre_ops == 1 && ch.ops[0].code == FKB_OP_YUV2RGB &&
-        ch.write_kind <= FKB_WRITE_SPLIT_PLANES && post_kind_of(ch) != 8u && !(ch.geometry >= FKB_GEOM_RESIZE_PRESERVE_AR && (r.x2 < r.x1 || r.y2 < r.y1)) &&
-        (reinterpret_cast<uintptr_t>(r.src_chroma) & 1) == 0 && (r.src_pitch & 1) == 0) {  // UV pairs are read as 16-bit words
+    // what nv12_kernel's aligned tap loads need: 16-bit UV pairs (NV12 / NV21), one word per pixel pair (UYVY, and the
+    // chroma of P010 / P210), one 64-bit group per pixel pair (Y210)
+    const uintptr_t sa = reinterpret_cast<uintptr_t>(r.src), ca = reinterpret_cast<uintptr_t>(r.src_chroma);
+    bool yuv_aligned = false;
+    switch (ch.src_format) {
+    case FKB_PIX_NV12: case FKB_PIX_NV21: yuv_aligned = (ca & 1) == 0 && (r.src_pitch & 1) == 0; break;
+    case FKB_PIX_UYVY: yuv_aligned = (sa & 3) == 0 && (r.src_pitch & 3) == 0; break;
+    case FKB_PIX_P010: case FKB_PIX_P210: yuv_aligned = (ca & 3) == 0 && (r.src_pitch & 3) == 0; break;
+    case FKB_PIX_Y210: yuv_aligned = (sa & 7) == 0 && (r.src_pitch & 7) == 0; break;
+    default: break;
+    }
+    if (yuv_aligned && ch.geometry != FKB_GEOM_NONE && ch.n_pre_ops == 1 && ch.ops[0].code == FKB_OP_YUV2RGB &&
+        ch.write_kind <= FKB_WRITE_SPLIT_PLANES && post_kind_of(ch) != 8u && !(ch.geometry >= FKB_GEOM_RESIZE_PRESERVE_AR && (r.x2 < r.x1 || r.y2 < r.y1))) {
         r.kclass = KCLASS_NV12;  // NV12 -> RGB on the taps -> resize -> [Mul][Add|Sub][Div][SaturateCast]: nv12_kernel
         return;
     }
@@ -477,8 +487,9 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         // nv12_pair_kernel's conditions: the colour matrix of the YCbCr standards ([s 0 r; s g1 g2; s b 0]), integer
         // offsets, immediate operands, and plane offsets that fit 32 bits
         k.vu = ch.src_format == FKB_PIX_NV21;
+        k.yuv_fmt = ch.src_format;
         k.src_px = ch.src_format == FKB_PIX_U8C3 ? 3u : ch.src_format == FKB_PIX_U8C4 ? 4u : 0u;
-        bool pair = k.src_px == 0 && !imm.slots && k.ccm[0] > 0.f && std::isfinite(k.ccm[0]) && k.ccm[3] == k.ccm[0] && k.ccm[6] == k.ccm[0] &&
+        bool pair = (ch.src_format == FKB_PIX_NV12 || ch.src_format == FKB_PIX_NV21) && !imm.slots && k.ccm[0] > 0.f && std::isfinite(k.ccm[0]) && k.ccm[3] == k.ccm[0] && k.ccm[6] == k.ccm[0] &&
                     k.ccm[1] == 0.f && k.ccm[8] == 0.f;
         for (int i = 0; i < 3; ++i) {
             pair = pair && k.sub[i] >= 0.f && k.sub[i] <= 255.f && k.sub[i] == std::floor(k.sub[i]);

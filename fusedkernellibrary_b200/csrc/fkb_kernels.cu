@@ -990,28 +990,56 @@ __device__ __forceinline__ void nv12_pixel(const LaunchParams& p, const PlaneRec
     if (inside) {
         const AxisTap ax = axis_tap(static_cast<int>(x) - (par ? pl.x1 : 0), pl.fx, pl.crop_w);
         const AxisTap ay = axis_tap(static_cast<int>(y) - (par ? pl.y1 : 0), pl.fy, pl.crop_h);
-        const uint32_t X0 = ax.i0 + pl.crop_x, X1 = ax.i1 + pl.crop_x, Y0 = ay.i0 + pl.crop_y, Y1 = ay.i1 + pl.crop_y;
-        const uint32_t pitch = pl.src_pitch;
-        const uint8_t* yr0 = pl.src + static_cast<size_t>(Y0 * pitch);
-        const uint8_t* yr1 = pl.src + static_cast<size_t>(Y1 * pitch);
-        const uint8_t* cr0 = pl.src_chroma + static_cast<size_t>((Y0 >> 1) * pitch);
-        const uint8_t* cr1 = pl.src_chroma + static_cast<size_t>((Y1 >> 1) * pitch);
-        const uint32_t u0 = X0 & ~1u, u1 = X1 & ~1u;
-        // all eight loads first (a UV pair is one aligned 16-bit word)
-        const uint32_t l00 = __ldg(yr0 + X0), l10 = __ldg(yr0 + X1), l01 = __ldg(yr1 + X0), l11 = __ldg(yr1 + X1);
-        const uint32_t c00 = __ldg(reinterpret_cast<const unsigned short*>(cr0 + u0)), c10 = __ldg(reinterpret_cast<const unsigned short*>(cr0 + u1));
-        const uint32_t c01 = __ldg(reinterpret_cast<const unsigned short*>(cr1 + u0)), c11 = __ldg(reinterpret_cast<const unsigned short*>(cr1 + u1));
+        const uint32_t Xs[2] = {ax.i0 + pl.crop_x, ax.i1 + pl.crop_x}, Ys[2] = {ay.i0 + pl.crop_y, ay.i1 + pl.crop_y};
+        const size_t pitch = pl.src_pitch;
+        // the loads of all four taps first; tap t = (Xs[t & 1], Ys[t >> 1])
+        uint32_t lum[4], cbs[4], crs[4];
+        switch (k.yuv_fmt) {
+        case FKB_PIX_UYVY:  // one aligned word U Y0 V Y1 per pixel pair
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const uint32_t X = Xs[t & 1];
+                const uint32_t g = __ldg(reinterpret_cast<const uint32_t*>(pl.src + Ys[t >> 1] * pitch) + (X >> 1));
+                lum[t] = (g >> (8u + 16u * (X & 1u))) & 0xffu; cbs[t] = g & 0xffu; crs[t] = (g >> 16) & 0xffu;
+            }
+            break;
+        case FKB_PIX_P010: case FKB_PIX_P210:  // ushort luma; one aligned word (U,V) per pixel pair, every second row for 4:2:0
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const uint32_t X = Xs[t & 1], Y = Ys[t >> 1], cy = k.yuv_fmt == FKB_PIX_P010 ? Y >> 1 : Y;
+                lum[t] = __ldg(reinterpret_cast<const unsigned short*>(pl.src + Y * pitch) + X);
+                const uint32_t g = __ldg(reinterpret_cast<const uint32_t*>(pl.src_chroma + cy * pitch) + (X >> 1));
+                cbs[t] = g & 0xffffu; crs[t] = g >> 16;
+            }
+            break;
+        case FKB_PIX_Y210:  // one aligned ushort4 Y0 U Y1 V per pixel pair
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const uint32_t X = Xs[t & 1];
+                const uint2 g = __ldg(reinterpret_cast<const uint2*>(pl.src + Ys[t >> 1] * pitch) + (X >> 1));
+                lum[t] = (X & 1u) ? g.y & 0xffffu : g.x & 0xffffu; cbs[t] = g.x >> 16; crs[t] = g.y >> 16;
+            }
+            break;
+        default:  // NV12 / NV21: byte luma, one aligned 16-bit word per chroma pair
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const uint32_t X = Xs[t & 1], Y = Ys[t >> 1];
+                lum[t] = __ldg(pl.src + Y * pitch + X);
+                const uint32_t g = __ldg(reinterpret_cast<const unsigned short*>(pl.src_chroma + (Y >> 1) * pitch) + (X >> 1));
+                cbs[t] = k.vu ? g >> 8 : g & 0xffu; crs[t] = k.vu ? g & 0xffu : g >> 8;
+            }
+            break;
+        }
         const float w00 = __fmul_rn(ax.w0, ay.w0), w10 = __fmul_rn(ax.w1, ay.w0);
         const float w01 = __fmul_rn(ax.w0, ay.w1), w11 = __fmul_rn(ax.w1, ay.w1);
-        const uint32_t lum[4] = {l00, l10, l01, l11}, chr[4] = {c00, c10, c01, c11};
         const float w[4] = {w00, w10, w01, w11};
         float acc[3];
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
             const float yy = static_cast<float>(lum[t]);
             const float a = k.sub[0] != 0.f ? __fsub_rn(yy, k.sub[0]) : yy;  // x - 0 is x
-            const float b = __fsub_rn(static_cast<float>(k.vu ? chr[t] >> 8 : chr[t] & 0xffu), k.sub[1]);
-            const float d = __fsub_rn(static_cast<float>(k.vu ? chr[t] & 0xffu : chr[t] >> 8), k.sub[2]);
+            const float b = __fsub_rn(static_cast<float>(cbs[t]), k.sub[1]);
+            const float d = __fsub_rn(static_cast<float>(crs[t]), k.sub[2]);
 #pragma unroll
             for (int c = 0; c < 3; ++c) {
                 const float rgb = __fadd_rn(__fadd_rn(__fmul_rn(a, k.ccm[3 * c]), __fmul_rn(b, k.ccm[3 * c + 1])), __fmul_rn(d, k.ccm[3 * c + 2]));

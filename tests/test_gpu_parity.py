@@ -170,6 +170,7 @@ def test_ten_bit_yuv_formats(fmt, rng, prim):
         wl = W.nv12_preprocess(**shape, src_format=fmt, colour=(rng, prim))
         check(wl)
         check(wl, use_plan=True)
+        check(wl, force_gather=True)
 
 
 @pytest.mark.parametrize("mode", [abi.BORDER_CONSTANT, abi.BORDER_REPLICATE, abi.BORDER_REFLECT, abi.BORDER_WRAP, abi.BORDER_REFLECT_101])

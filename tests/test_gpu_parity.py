@@ -11,7 +11,7 @@ import numpy as np
 import pytest
 
 import oracle
-from conftest import GOLDEN_CASES, load_golden
+from conftest import GOLDEN_CASES, conversion_kat_workload, ycbcr_round_trip, load_golden, read_uyvy_kat_workload, reference_kats
 from fusedkernellibrary_b200 import abi, workloads as W
 
 torch = pytest.importorskip("torch")
@@ -93,6 +93,31 @@ SMALL = {
     "conditional_resize": lambda: W.conditional_resize(),
     "conditional_pointwise": lambda: W.conditional_pointwise(),
 }
+
+
+@pytest.mark.parametrize("case", reference_kats()["conversions"], ids=lambda c: c["code"])
+def test_colour_conversion_known_answers_of_the_reference_tests(case):
+    # utests/algorithm/image_processing/utest_color_conversion.h:76-101, 144-168, through the C ABI
+    wl, want = conversion_kat_workload(case)
+    for kw in [dict(), dict(tiny_route=True)]:
+        assert np.array_equal(gpu_run(wl, **kw)[0][:want.size], want)
+
+
+@pytest.mark.parametrize("case", reference_kats()["read_uyvy"], ids=lambda c: f"{c['w']}x{c['h']}")
+def test_read_uyvy_known_answers_of_the_reference_tests(case):
+    # utests/algorithm/image_processing/utest_color_conversion.h:299-348, through the C ABI
+    wl, want = read_uyvy_kat_workload(case)
+    assert np.array_equal(gpu_run(wl)[0][:want.size], want)
+
+
+@pytest.mark.parametrize("rng", [abi.RANGE_LIMITED, abi.RANGE_FULL])
+@pytest.mark.parametrize("prim", [abi.PRIMITIVES_BT601, abi.PRIMITIVES_BT709, abi.PRIMITIVES_BT2020])
+def test_rgb_ycbcr_round_trip_property(rng, prim):
+    # utests/algorithm/image_processing/utest_color_conversion.h:683-735, through the C ABI: back within 1 % of full scale,
+    # and the same bytes as the oracle's round trip
+    err = ycbcr_round_trip(gpu_run, rng, prim)
+    assert err <= 255 * 0.01
+    assert err == ycbcr_round_trip(oracle.run_oracle, rng, prim)
 
 
 @pytest.mark.parametrize("name", sorted(SMALL))

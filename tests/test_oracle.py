@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 
 import oracle
-from conftest import GOLDEN_CASES, load_golden
+from conftest import GOLDEN_CASES, conversion_kat_workload, ycbcr_round_trip, load_golden, read_uyvy_kat_workload, reference_kats
 from fusedkernellibrary_b200 import abi, workloads as W
 
 
@@ -51,6 +51,50 @@ def test_bt709_matrix_golden():
         m = (C.c_float * 9)()
         oracle.load_ref().fklref_bt709_full_matrix(m)
         assert np.array_equal(np.array(list(m), np.float32), want)
+
+
+RANGES = {"limited": abi.RANGE_LIMITED, "full": abi.RANGE_FULL}
+PRIMS = {"bt601": abi.PRIMITIVES_BT601, "bt709": abi.PRIMITIVES_BT709, "bt2020": abi.PRIMITIVES_BT2020}
+
+
+def test_colour_matrices_equal_the_reference_tests_constants():
+    # the twelve 8-bit matrices the reference's unit test compares with == against ccMatrix
+    # (utests/algorithm/image_processing/utest_color_conversion.h:407-509, 576-597): the oracle's and the library's
+    # host functions must produce the same floats
+    lib, prod = oracle.load_oracle(), abi.load()
+    for key, vals in reference_kats()["matrices"].items():
+        rng, prim, direction = key.split("/")
+        want = np.array(vals, np.float32)
+        got_o, got_p, off = (C.c_float * 9)(), (C.c_float * 9)(), (C.c_float * 3)()
+        if direction == "ycbcr2rgb":
+            assert lib.fkb_oracle_ycbcr_to_rgb(RANGES[rng], PRIMS[prim], got_o, off) == 0
+            assert prod.fkb_ycbcr_to_rgb(RANGES[rng], PRIMS[prim], got_p, off) == 0
+        else:
+            assert lib.fkb_oracle_rgb_to_ycbcr(RANGES[rng], PRIMS[prim], got_o, off) == 0
+            assert prod.fkb_rgb_to_ycbcr(RANGES[rng], PRIMS[prim], got_p, off) == 0
+        assert np.array_equal(np.array(list(got_o), np.float32), want), key
+        assert np.array_equal(np.array(list(got_p), np.float32), want), key
+
+
+@pytest.mark.parametrize("case", reference_kats()["conversions"], ids=lambda c: c["code"])
+def test_colour_conversion_known_answers(case):
+    # utests/algorithm/image_processing/utest_color_conversion.h:76-101, 144-168
+    wl, want = conversion_kat_workload(case)
+    assert np.array_equal(oracle.run_oracle(wl)[0], want)
+
+
+@pytest.mark.parametrize("case", reference_kats()["read_uyvy"], ids=lambda c: f"{c['w']}x{c['h']}")
+def test_read_uyvy_known_answers(case):
+    # utests/algorithm/image_processing/utest_color_conversion.h:299-348: every pixel of three small UYVY images
+    wl, want = read_uyvy_kat_workload(case)
+    assert np.array_equal(oracle.run_oracle(wl)[0], want)
+
+
+@pytest.mark.parametrize("rng", sorted(RANGES))
+@pytest.mark.parametrize("prim", sorted(PRIMS))
+def test_rgb_ycbcr_round_trip_property(rng, prim):
+    # utests/algorithm/image_processing/utest_color_conversion.h:683-735: back within 1 % of full scale
+    assert ycbcr_round_trip(oracle.run_oracle, RANGES[rng], PRIMS[prim]) <= 255 * 0.01
 
 
 # letterbox placement and scale factors the reference computes for the README crops (Resize<>::build run in the

@@ -69,6 +69,8 @@ def workload_config(n_gpus: int, scaling: str, frames_per_gpu: int) -> dict:
         "frames_per_gpu": frames_per_gpu, "crops_per_frame": CROPS_PER_FRAME, "planes_per_gpu": frames_per_gpu * CROPS_PER_FRAME,
         "sharding": f"by frame over {n_gpus} GPU(s), each GPU owns its frames and its slice of the output, no collective",
         "l2": "inputs + outputs per launch (1.6 GB per GPU at 64 frames) exceed the 126 MB L2; no flush needed",
+        "timing": "the K launches are captured into one CUDA graph and replayed between two CUDA events (device time, "
+                  "max over ranks); --stream-launches submits them one by one instead",
     }
 
 
@@ -81,7 +83,7 @@ class ClockSampler:
     REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
                0x2: "applications_clocks_setting", 0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting", 0x10: "sync_boost"}
 
-    def __init__(self, cuda_index: int, period_s: float = 0.02):
+    def __init__(self, cuda_index: int, period_s: float = 0.05):
         self.samples, self.reasons, self.max_mhz = [], set(), None
         self._stop = threading.Event()
         self._thread = None
@@ -103,10 +105,9 @@ class ClockSampler:
         nv = self.nv
         while not self._stop.is_set():
             try:
-                util = nv.nvmlDeviceGetUtilizationRates(self.h).gpu
                 mhz = int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
                 mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
-                self.samples.append((mhz, util))
+                self.samples.append((mhz, 0))
                 for bit, name in self.REASONS.items():
                     if mask & bit:
                         self.reasons.add(name)
@@ -175,7 +176,8 @@ def reference_arm(args) -> None:
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
-        "dtype": "f32", "data": "synthetic", "config": workload_config(args.gpus, args.scaling, N_FRAMES),
+        "dtype": "f32", "data": "synthetic",
+        "config": {**workload_config(args.gpus, args.scaling, N_FRAMES), "timing": "host wall clock around each step of the CPU backend"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -342,9 +344,24 @@ def our_arm(args) -> None:
         for _ in range(50):
             dw.launch_plan()
         torch.cuda.synchronize()
+    # The K timed launches are captured once into a CUDA graph and replayed inside the CUDA-event bracket: the device
+    # time of K back-to-back launches must not depend on how promptly the host thread gets to submit each one (with
+    # one process per GPU and a clock sampler in each, eight ranks can outnumber the cores a box gives them).
+    # --stream-launches submits them one by one instead.
+    if args.stream_launches:
+        timed = lambda: [dw.launch_plan() for _ in range(args.steps)]
+    else:
+        graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(args.steps):
+                    dw.launch_plan()
+        graph.replay()
+        torch.cuda.synchronize()
+        timed = graph.replay
     if world > 1:
         dist.barrier()
-    dt = time_launches(dw.launch_plan, args.steps, torch)
+    dt = time_launches(timed, 1, torch)
     t_end = time.perf_counter() + 0.4
     while time.perf_counter() < t_end:
         for _ in range(50):
@@ -352,8 +369,12 @@ def our_arm(args) -> None:
         torch.cuda.synchronize()
     clocks = sampler.stop()
     abi.check(abi.load().fkb_device_status())
+    per_rank_ms = [dt / args.steps * 1e3]
     if world > 1:
         t = torch.tensor([dt], device="cuda", dtype=torch.float64)
+        every = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(every, t)
+        per_rank_ms = [float(e.item()) / args.steps * 1e3 for e in every]
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dt = float(t.item())
     ms_per_step = dt / args.steps * 1e3
@@ -418,7 +439,7 @@ def our_arm(args) -> None:
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic", "config": workload_config(world, args.scaling, frames),
+        "data": "synthetic", "config": workload_config(world, args.scaling, frames), "ms_per_step_by_rank": per_rank_ms,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_source": peak_src, "kernel": "fkb::staged_kernel",
                      "algorithmic_bytes_per_launch": alg["total"], "frac_of_nominal_8TBs": achieved / 8000.0},
@@ -458,6 +479,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
+    ap.add_argument("--stream-launches", action="store_true", help="submit the timed launches one by one instead of replaying a CUDA graph of them")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-other-configs", action="store_true")
     args = ap.parse_args()

@@ -337,13 +337,6 @@ def our_arm(args) -> None:
     for _ in range(max(3, args.warmup)):
         dw.launch_plan()
     torch.cuda.synchronize()
-    sampler.start()
-    # a sustained stretch of the same launch so that the clock samples are taken under this load
-    t_end = time.perf_counter() + 0.6
-    while time.perf_counter() < t_end:
-        for _ in range(50):
-            dw.launch_plan()
-        torch.cuda.synchronize()
     # The K timed launches are captured once into a CUDA graph and replayed inside the CUDA-event bracket: the device
     # time of K back-to-back launches must not depend on how promptly the host thread gets to submit each one (with
     # one process per GPU and a clock sampler in each, eight ranks can outnumber the cores a box gives them).
@@ -361,6 +354,16 @@ def our_arm(args) -> None:
         timed = graph.replay
     if world > 1:
         dist.barrier()
+    # Ranks reach the barrier seconds apart (set-up times differ), and a GPU that idled there has dropped its clocks:
+    # a few milliseconds of timed work right after the barrier would mostly measure the ramp back up.  So every rank
+    # first runs a sustained stretch of the same launch (during which the clock samples start), and the timed launches
+    # follow it without a pause.
+    sampler.start()
+    t_end = time.perf_counter() + 0.6
+    while time.perf_counter() < t_end:
+        for _ in range(50):
+            dw.launch_plan()
+        torch.cuda.synchronize()
     dt = time_launches(timed, 1, torch)
     t_end = time.perf_counter() + 0.4
     while time.perf_counter() < t_end:
@@ -368,6 +371,8 @@ def our_arm(args) -> None:
             dw.launch_plan()
         torch.cuda.synchronize()
     clocks = sampler.stop()
+    if world > 1:
+        dist.barrier()
     abi.check(abi.load().fkb_device_status())
     per_rank_ms = [dt / args.steps * 1e3]
     if world > 1:

@@ -382,6 +382,15 @@ def our_arm(args) -> None:
         per_rank_ms = [float(e.item()) / args.steps * 1e3 for e in every]
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dt = float(t.item())
+        # every rank's clock record: the line reports the slowest GPU's clock and the union of the reasons, and keeps
+        # the list, so that a GPU left with locked clocks shows next to its step time
+        by_rank = [None] * world
+        dist.all_gather_object(by_rank, clocks)
+        known = [c["sm_mhz"] for c in by_rank if c.get("sm_mhz") is not None]
+        clocks = {"sm_mhz": min(known) if known else None, "sm_max_mhz": clocks.get("sm_max_mhz"),
+                  "reasons": sorted({r for c in by_rank for r in c.get("reasons", [])}),
+                  "samples": sum(c.get("samples", 0) for c in by_rank),
+                  "sm_mhz_by_rank": [c.get("sm_mhz") for c in by_rank]}
     ms_per_step = dt / args.steps * 1e3
     total_pixels = wl.out_pixels * world
     value = total_pixels / (dt / args.steps) / 1e9

@@ -84,6 +84,8 @@ struct LaunchParams {
     uint32_t* work;            // staged_kernel: {next item, warps finished} for dynamic item claiming; null = items dealt round-robin
     uint32_t n_lut_units;     // work units of lut_kernel (a block of rows of one LUT plane)
     uint32_t lut_swap;        // bit c: chain c contains an odd number of channel reorders
+    uint32_t gather_z0, gather_z1;    // planes [z0, z1) hold every plane of the general kernel (grid.z covers this range only)
+    uint32_t gather4_z0, gather4_z1;  // the same for the four-channel kernel
     uint32_t post_kind[FKB_MAX_CHAINS];
     PostImm post_imm[FKB_MAX_CHAINS];
     Nv12Consts nv12;  // per chain: bit mask of {Mul, Add|Sub, SaturateCast} when its post-ops have that shape, else 8

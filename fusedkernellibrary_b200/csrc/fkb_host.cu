@@ -249,7 +249,15 @@ void classify(const fkb_chain_desc& ch, PlaneRec& r) {
     } else {
         for (uint32_t i = 0; i < ch.n_pre_ops; ++i)
             if (ch.ops[i].code != FKB_OP_CAST_F32) return;  // taps are transformed before interpolation: general path
-        if (ch.geometry >= FKB_GEOM_RESIZE_PRESERVE_AR && (r.x2 < r.x1 || r.y2 < r.y1)) return;  // all background
+        if (ch.geometry >= FKB_GEOM_RESIZE_PRESERVE_AR && (r.x2 < r.x1 || r.y2 < r.y1)) {
+            // a crop so thin that its resized image has no pixel: every row of the plane is background, which the staged
+            // kernel writes without touching the source (its scale factors may be infinite and are not used)
+            r.x1 = 0; r.x2 = -1;  // (an empty row range is recorded as an empty column range: no column has a footprint)
+            r.tile_w = std::min(r.dst_w, 256u);
+            r.kclass = KCLASS_RESIZE;
+            r.tiles_x = (r.dst_w + r.tile_w - 1) / r.tile_w;
+            return;
+        }
         if (!(r.fx <= 32.f) || !(r.fy <= 4096.f)) return;
         // widest segment (at most 8 columns per lane) whose source columns fit one staged row
         uint32_t tw = std::min(r.dst_w, 256u);
@@ -450,8 +458,16 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         if (z == 0) first_count = count; else if (count != first_count) uniform = false;
         if (static_cast<uint64_t>(n_tiles) + count > 0xfffffff0ull) return FKB_ERR_TOO_LARGE;
         n_tiles += count;
-        if (r.kclass == KCLASS_GATHER) { ++n_gather; gw = std::max(gw, r.dst_w); gh = std::max(gh, r.dst_h); }
-        if (r.kclass == KCLASS_GATHER4) { ++n_gather4; g4w = std::max(g4w, r.dst_w); g4h = std::max(g4h, r.dst_h); }
+        if (r.kclass == KCLASS_GATHER) {
+            if (!n_gather++) L.lp.gather_z0 = z;
+            L.lp.gather_z1 = z + 1;
+            gw = std::max(gw, r.dst_w); gh = std::max(gh, r.dst_h);
+        }
+        if (r.kclass == KCLASS_GATHER4) {
+            if (!n_gather4++) L.lp.gather4_z0 = z;
+            L.lp.gather4_z1 = z + 1;
+            g4w = std::max(g4w, r.dst_w); g4h = std::max(g4h, r.dst_h);
+        }
     }
     L.lp.n_planes = n_planes;
     L.lp.neg_zero = -0.0f;
@@ -510,7 +526,8 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         ++L.kernels;
     }
     if (n_gather4) {
-        L.gather4_grid = dim3((g4w + 31) / 32, (g4h + 7) / 8, std::min<uint32_t>(n_planes, 65535u));
+        // (grid.z spans only the planes from the first to the last of this class: a stray plane costs one layer of CTAs)
+        L.gather4_grid = dim3((g4w + 31) / 32, (g4h + 7) / 8, std::min<uint32_t>(L.lp.gather4_z1 - L.lp.gather4_z0, 65535u));
         ++L.kernels;
     }
     if (n_gather) {
@@ -520,7 +537,7 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         for (uint32_t z = 0; z < n_planes; ++z)
             yuv_write = yuv_write || (L.recs[z].kclass == KCLASS_GATHER && chains[L.recs[z].chain].write_kind >= FKB_WRITE_NV12);
         L.gather_ppt = gather_pixels < (yuv_write ? (1u << 17) : (2u << 20)) ? 1 : 4;
-        L.gather_grid = dim3((gw + 32 * L.gather_ppt - 1) / (32 * L.gather_ppt), (gh + 7) / 8, std::min<uint32_t>(n_planes, 65535u));
+        L.gather_grid = dim3((gw + 32 * L.gather_ppt - 1) / (32 * L.gather_ppt), (gh + 7) / 8, std::min<uint32_t>(L.lp.gather_z1 - L.lp.gather_z0, 65535u));
         ++L.kernels;
     }
     return status_word(&L.lp.status);

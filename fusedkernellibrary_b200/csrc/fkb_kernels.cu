@@ -141,7 +141,7 @@ template <int PPT, bool INLINE>
 __global__ void __launch_bounds__(256) gather_kernel(const __grid_constant__ LaunchParams p) {
     __shared__ PlaneRec s_pl;
     const uint32_t tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-    for (uint32_t z = blockIdx.z; z < p.n_planes; z += gridDim.z) {
+    for (uint32_t z = p.gather_z0 + blockIdx.z; z < p.gather_z1; z += gridDim.z) {
         if (!INLINE) {
             __syncthreads();
             if (threadIdx.x < sizeof(PlaneRec) / 16)
@@ -385,7 +385,7 @@ __global__ void __launch_bounds__(256) gather4_kernel(const __grid_constant__ La
     __shared__ PlaneRec s_pl;
     const PlaneRec* table = plane_table(p);
     const uint32_t x = blockIdx.x * 32 + (threadIdx.x & 31), y = blockIdx.y * 8 + (threadIdx.x >> 5);
-    for (uint32_t z = blockIdx.z; z < p.n_planes; z += gridDim.z) {
+    for (uint32_t z = p.gather4_z0 + blockIdx.z; z < p.gather4_z1; z += gridDim.z) {
         __syncthreads();
         if (threadIdx.x < sizeof(PlaneRec) / 16)
             reinterpret_cast<uint4*>(&s_pl)[threadIdx.x] = reinterpret_cast<const uint4*>(table + z)[threadIdx.x];

@@ -76,6 +76,8 @@ SMALL = {
     "divergent": lambda: W.divergent_planes(n_per_seq=4, w=480, h=270),
     "divergent_odd": lambda: W.divergent_planes(n_per_seq=3, w=330, h=190),
     "crop_reorder": lambda: W.crop_reorder(n=5),
+    # crops so thin that the letterboxed image has no column or no row (the whole plane is background), among usual ones
+    "thin_crops": lambda: W.readme_crops(crops=((300, 125, 1, 500), (400, 125, 500, 1), (10, 10, 2, 700), (530, 270, 130, 140), (0, 0, 1, 1)), dst=(224, 224)),
     "rgba_crops": lambda: W.rgba_crops(),
     "rgba_crops_f32_reorder": lambda: W.rgba_crops(reorder=True, f32=True, w=333, h=211, dst=(77, 45), rects=((0, 0, 333, 211), (5, 7, 100, 90), (300, 180, 33, 31))),
     "rgba_crops_border": lambda: W.rgba_crops(w=200, h=120, dst=(64, 48), rects=((-20, -10, 90, 70), (150, 90, 120, 80), (10, 10, 50, 40)), border=abi.BORDER_CONSTANT),

@@ -210,6 +210,10 @@ def test_oracle_matches_golden_fixture(name):
         assert np.array_equal(g, w)  # bit-exact, integer and float outputs alike
 
 
+# crops so thin that the letterboxed image has no column (or no row): the whole plane is background
+THIN_CROPS = ((300, 125, 1, 500), (400, 125, 500, 1), (10, 10, 2, 700), (530, 270, 130, 140), (0, 0, 1, 1))
+
+
 @pytest.mark.skipif(not oracle.have_ref(), reason="reference-backed checker not built")
 @pytest.mark.parametrize("wl", [
     W.readme_crops(), W.vertical_fusion(w=1000, h=300), W.nv12_preprocess(w=1280, h=720, dst=(320, 320)),
@@ -219,6 +223,7 @@ def test_oracle_matches_golden_fixture(name):
     W.border_crops(abi.BORDER_WRAP), W.border_crops(abi.BORDER_REFLECT_101), W.border_crops(abi.BORDER_WRAP, w=37, h=23),
     W.border_crops(abi.BORDER_REFLECT, w=37, h=23), W.border_crops(abi.BORDER_REFLECT_101, w=37, h=23), W.nv12_border_constant(),
     W.rgba_crops(), W.rgba_crops(reorder=True), W.rgba_crops(f32=True), W.rgba_crops(reorder=True, f32=True),
+    W.readme_crops(crops=THIN_CROPS, dst=(224, 224)),
     W.add_alpha_crops(), W.add_alpha_crops(swap=True), W.add_alpha_crops(f32=True), W.add_alpha_crops(swap=True, f32=True),
     W.add_alpha_image(), W.add_alpha_image(swap=True),
     W.bgra_crops(), W.bgra_crops(swap=True), W.split_planes(), W.split_planes(f32=False), W.tsplit_resize(), W.conditional_resize(), W.conditional_resize(used=0), W.conditional_resize(used=8), W.conditional_pointwise(),

@@ -443,6 +443,23 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
     const uint32_t lut_rpu = lut_rows ? std::max<uint32_t>(static_cast<uint32_t>((lut_rows + 1ull * kLutCtasPerSm * sms - 1) / (1ull * kLutCtasPerSm * sms)),
                                                            (kLutWarps + lut_min_tiles_x - 1) / lut_min_tiles_x) : 1u;
     uint32_t n_lut_units = 0;
+    // The records of the general kernels' planes move to the end of the table (a record is self-contained, so the order
+    // of the table is free): each of those kernels then gets a grid that covers exactly its own planes, however they were
+    // scattered among the others.  In place, no allocation: [other classes | four-channel | general].
+    {
+        auto to_back = [&](uint32_t cls, uint32_t end) {
+            uint32_t lo = 0, hi = end;
+            while (lo < hi) {
+                if (L.recs[lo].kclass != cls) { ++lo; continue; }
+                if (L.recs[hi - 1].kclass == cls) { --hi; continue; }
+                std::swap(L.recs[lo], L.recs[hi - 1]);
+                ++lo; --hi;
+            }
+            return hi;  // first record of class `cls`
+        };
+        const uint32_t first_general = to_back(KCLASS_GATHER, n_planes);
+        to_back(KCLASS_GATHER4, first_general);
+    }
     const uint32_t rpi = rows_per_item(row_segments, 2u * kStagedWarps * static_cast<uint32_t>(sms));
     for (uint32_t z = 0; z < n_planes; ++z) {
         PlaneRec& r = L.recs[z];

@@ -150,6 +150,26 @@ def test_tiny_launch_routing():
         check(wl, tiny_route=True, use_plan=True)
 
 
+def test_one_thin_crop_does_not_add_a_kernel_to_a_batch():
+    # A crop whose letterboxed image has no column is all background.  It must stay in the batch's one fused launch: sent
+    # to the general kernel, a single such plane once cost a 2048-plane launch more than its other 2047 planes together.
+    from fusedkernellibrary_b200 import runtime
+    rs = np.random.RandomState(5)
+    rects = W.random_rects(63, 640, 480, 16, 300, rs) + [(100, 0, 1, 470)]  # round(224 / 470 * 1) = 0 columns
+    wl = W.readme_crops(w=640, h=480, crops=tuple(rects), dst=(224, 224))
+    os.environ["FKB_TINY_PIXELS"] = "0"
+    try:
+        dw = runtime.DeviceWorkload(wl)
+        try:
+            assert dw.kernel_launches() == 1
+        finally:
+            dw.close()
+    finally:
+        os.environ.pop("FKB_TINY_PIXELS", None)
+    check(wl)
+    check(wl, use_plan=True)
+
+
 def test_edge_shapes():
     # 1x1 image, single-row / single-column images, crops touching every frame edge, extreme up- and down-scaling
     for wl in [

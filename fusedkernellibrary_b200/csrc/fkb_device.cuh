@@ -86,6 +86,7 @@ struct LaunchParams {
     uint32_t lut_swap;        // bit c: chain c contains an odd number of channel reorders
     uint32_t gather_z0, gather_z1;    // planes [z0, z1) hold every plane of the general kernel (grid.z covers this range only)
     uint32_t gather4_z0, gather4_z1;  // the same for the four-channel kernel
+    uint32_t pixel_z0, pixel_z1;      // the same for the one-pixel-per-thread kernels (nv12_kernel, nv12_pair_kernel, rgb_kernel)
     uint32_t post_kind[FKB_MAX_CHAINS];
     PostImm post_imm[FKB_MAX_CHAINS];
     Nv12Consts nv12;  // per chain: bit mask of {Mul, Add|Sub, SaturateCast} when its post-ops have that shape, else 8

@@ -445,7 +445,7 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
     uint32_t n_lut_units = 0;
     // The records of the general kernels' planes move to the end of the table (a record is self-contained, so the order
     // of the table is free): each of those kernels then gets a grid that covers exactly its own planes, however they were
-    // scattered among the others.  In place, no allocation: [other classes | four-channel | general].
+    // scattered among the others.  In place, no allocation: [other classes | one pixel per thread | four-channel | general].
     {
         auto to_back = [&](uint32_t cls, uint32_t end) {
             uint32_t lo = 0, hi = end;
@@ -458,7 +458,9 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
             return hi;  // first record of class `cls`
         };
         const uint32_t first_general = to_back(KCLASS_GATHER, n_planes);
-        to_back(KCLASS_GATHER4, first_general);
+        const uint32_t first_four = to_back(KCLASS_GATHER4, first_general);
+        const uint32_t first_pixel = to_back(KCLASS_NV12, first_four);
+        L.lp.pixel_z0 = first_pixel; L.lp.pixel_z1 = first_four;
     }
     const uint32_t rpi = rows_per_item(row_segments, 2u * kStagedWarps * static_cast<uint32_t>(sms));
     for (uint32_t z = 0; z < n_planes; ++z) {
@@ -539,7 +541,7 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
             wide = wide && (reinterpret_cast<uintptr_t>(r.dst) & 7) == 0 && (r.dst_pitch & 7) == 0 && (r.dst_cstride & 7) == 0 && (r.dst_cstride2 & 7) == 0;
         }
         k.pair = pair; k.wide_store = wide;
-        L.nv12_grid = dim3((nw + (pair ? 63 : 31)) / (pair ? 64 : 32), (nh + 7) / 8, std::min<uint32_t>(n_planes, 65535u));
+        L.nv12_grid = dim3((nw + (pair ? 63 : 31)) / (pair ? 64 : 32), (nh + 7) / 8, std::min<uint32_t>(L.lp.pixel_z1 - L.lp.pixel_z0, 65535u));
         ++L.kernels;
     }
     if (n_gather4) {

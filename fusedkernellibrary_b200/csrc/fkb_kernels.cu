@@ -1087,9 +1087,9 @@ __device__ __forceinline__ void rgb_pixel(const LaunchParams& p, const PlaneRec&
 __global__ void __launch_bounds__(256, 4) rgb_kernel(const __grid_constant__ LaunchParams p) {
     const uint32_t x = blockIdx.x * 32 + (threadIdx.x & 31), y = blockIdx.y * 8 + (threadIdx.x >> 5);
     if (p.table == nullptr) {
-        for (uint32_t z = blockIdx.z; z < p.n_planes; z += gridDim.z) rgb_pixel(p, p.inline_planes[z], x, y);
+        for (uint32_t z = p.pixel_z0 + blockIdx.z; z < p.pixel_z1; z += gridDim.z) rgb_pixel(p, p.inline_planes[z], x, y);
     } else {
-        for (uint32_t z = blockIdx.z; z < p.n_planes; z += gridDim.z) rgb_pixel(p, p.table[z], x, y);
+        for (uint32_t z = p.pixel_z0 + blockIdx.z; z < p.pixel_z1; z += gridDim.z) rgb_pixel(p, p.table[z], x, y);
     }
 }
 
@@ -1098,9 +1098,9 @@ __global__ void __launch_bounds__(256, 8) nv12_kernel(const __grid_constant__ La
     // Two copies of the body so that each knows where its plane records live: in the kernel parameters (constant-bank
     // reads, shared by all threads) for launches of a few planes, in the global table otherwise.
     if (p.table == nullptr) {
-        for (uint32_t z = blockIdx.z; z < p.n_planes; z += gridDim.z) nv12_pixel(p, p.inline_planes[z], x, y);
+        for (uint32_t z = p.pixel_z0 + blockIdx.z; z < p.pixel_z1; z += gridDim.z) nv12_pixel(p, p.inline_planes[z], x, y);
     } else {
-        for (uint32_t z = blockIdx.z; z < p.n_planes; z += gridDim.z) nv12_pixel(p, p.table[z], x, y);
+        for (uint32_t z = p.pixel_z0 + blockIdx.z; z < p.pixel_z1; z += gridDim.z) nv12_pixel(p, p.table[z], x, y);
     }
 }
 
@@ -1226,9 +1226,9 @@ __global__ void __launch_bounds__(THREADS, MINB) nv12_pair_kernel(const __grid_c
     // (every field a constant-bank operand, the pointers uniform), one of a few kernel-parameter records, or a table entry
     if (p.table == nullptr) {
         if (p.n_planes == 1) nv12_pair<SCALED_LUMA, VU>(p, p.inline_planes[0], x, y);
-        else for (uint32_t z = blockIdx.z; z < p.n_planes; z += gridDim.z) nv12_pair<SCALED_LUMA, VU>(p, p.inline_planes[z], x, y);
+        else for (uint32_t z = p.pixel_z0 + blockIdx.z; z < p.pixel_z1; z += gridDim.z) nv12_pair<SCALED_LUMA, VU>(p, p.inline_planes[z], x, y);
     } else {
-        for (uint32_t z = blockIdx.z; z < p.n_planes; z += gridDim.z) nv12_pair<SCALED_LUMA, VU>(p, p.table[z], x, y);
+        for (uint32_t z = p.pixel_z0 + blockIdx.z; z < p.pixel_z1; z += gridDim.z) nv12_pair<SCALED_LUMA, VU>(p, p.table[z], x, y);
     }
 }
 

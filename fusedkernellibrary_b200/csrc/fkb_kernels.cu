@@ -382,15 +382,10 @@ __device__ __forceinline__ void apply_ops4_bordered(float (&v)[N][4], const fkb_
 }
 
 __global__ void __launch_bounds__(256) gather4_kernel(const __grid_constant__ LaunchParams p) {
-    __shared__ PlaneRec s_pl;
     const PlaneRec* table = plane_table(p);
     const uint32_t x = blockIdx.x * 32 + (threadIdx.x & 31), y = blockIdx.y * 8 + (threadIdx.x >> 5);
     for (uint32_t z = p.gather4_z0 + blockIdx.z; z < p.gather4_z1; z += gridDim.z) {
-        __syncthreads();
-        if (threadIdx.x < sizeof(PlaneRec) / 16)
-            reinterpret_cast<uint4*>(&s_pl)[threadIdx.x] = reinterpret_cast<const uint4*>(table + z)[threadIdx.x];
-        __syncthreads();
-        const PlaneRec& pl = s_pl;
+        const PlaneRec& pl = table[z];  // read in place: every thread of the CTA reads the same words (broadcast, cached)
         if (pl.kclass != KCLASS_GATHER4 || x >= pl.dst_w || y >= pl.dst_h) continue;
         const fkb_chain_desc& ch = p.chains[pl.chain];
         float v[1][4];

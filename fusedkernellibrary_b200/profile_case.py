@@ -15,15 +15,24 @@ import torch
 from . import runtime, workloads as W
 
 
+# workloads beside the five configurations that have a profile of their own
+EXTRA = {
+    # 32 crops of one 1920x1080 uchar4 frame -> 224x224 uchar4 (the four-channel chain of the benchmark's widened rows)
+    "four_channel_crops": lambda: W.rgba_crops(dst=(224, 224), rects=tuple((30 * i, 15 * i, 200 + 8 * i, 160 + 4 * i) for i in range(32))),
+}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("workload", choices=sorted(W.CONFIGS))
+    ap.add_argument("workload", choices=sorted(W.CONFIGS) + sorted(EXTRA))
     ap.add_argument("--frames", type=int, default=8, help="batched_crop_resize: frames (32 crops each)")
     ap.add_argument("--sets", type=int, default=1, help="rotate this many independent buffer sets (defeats the L2)")
     ap.add_argument("--launches", type=int, default=4)
     args = ap.parse_args()
     if args.workload == "batched_crop_resize":
         wl = W.batched_crop_resize(n_frames=args.frames)
+    elif args.workload in EXTRA:
+        wl = EXTRA[args.workload]()
     else:
         wl = W.CONFIGS[args.workload]()
     sets = [runtime.DeviceWorkload(wl, poison=None) for _ in range(args.sets)]

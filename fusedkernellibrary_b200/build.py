@@ -35,7 +35,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         return OUT
     os.makedirs(OUT_DIR, exist_ok=True)
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-    cmd = [nvcc, *NVCC_FLAGS, "-I", os.path.join(ROOT, "include"), "-I", CSRC, "-o", OUT,
+    cmd = [nvcc, *NVCC_FLAGS, *os.environ.get("FKB_NVCC_EXTRA", "").split(), "-I", os.path.join(ROOT, "include"), "-I", CSRC, "-o", os.environ.get("FKB_BUILD_OUT", OUT),
            *[os.path.join(CSRC, s) for s in SOURCES]]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if verbose or res.returncode != 0:

@@ -79,7 +79,7 @@ struct LaunchParams {
     const PlaneRec* table;    // device table, or null when `inline_planes` is used
     uint32_t n_planes;
     uint32_t n_tiles;
-    uint32_t tiles_per_plane;  // > 0 when every plane has the same number of tiles; else PlaneRec::tile_base is searched
+    uint32_t tiles_per_plane;  // > 0 when every plane has the same shape; else PlaneRec::tile_base is searched
     int* status;
     uint32_t* work;            // staged_kernel: {next item, warps finished} for dynamic item claiming; null = items dealt round-robin
     uint32_t n_lut_units;     // work units of lut_kernel (a block of rows of one LUT plane)

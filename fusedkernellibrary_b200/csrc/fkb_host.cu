@@ -9,6 +9,7 @@
 //     each plane.
 //   * Resize<>::build computes its parameters on the host in double and stores floats
 //     (algorithms/image_processing/resize.h:164-233, 266-278): fkb_resize_params.
+#include <atomic>
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
@@ -180,28 +181,33 @@ int validate(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_de
 // -------------------------------------------------------------------------------------------------------
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-// FKB_FORCE_GATHER=1 (read at every launch) routes every plane through gather_kernel: a debugging aid that lets
-// the two kernel paths be checked against each other.
-bool force_gather() {
+// Debugging and tuning switches, read from the environment once per lowering (not once per plane):
+//   FKB_FORCE_GATHER=1       routes every plane through gather_kernel, which lets the kernel paths check each other;
+//   FKB_TINY_PIXELS=n        launches below n output pixels take the one-pixel-per-thread kernels (0 switches that off,
+//                            which the tests use to drive small cases through the pipelined kernels);
+//   FKB_ROWS_PER_ITEM=n      output rows per item of the staged kernel (default: chosen from the launch size).
+struct Tuning {
+    bool force_gather = false;
+    uint64_t tiny_pixels = kTinyLaunchPixels;
+    uint32_t rows_per_item = 0;
+};
+Tuning read_tuning() {
+    Tuning t;
     const char* e = std::getenv("FKB_FORCE_GATHER");
-    return e && e[0] == '1';
-}
-
-// Launches below this many output pixels take the general kernel.  FKB_TINY_PIXELS (read at every launch) overrides the
-// default; 0 switches the routing off, which the tests use to drive small cases through the pipelined kernels.
-uint64_t tiny_launch_pixels() {
-    const char* e = std::getenv("FKB_TINY_PIXELS");
-    return e && e[0] ? std::strtoull(e, nullptr, 10) : kTinyLaunchPixels;
+    t.force_gather = e && e[0] == '1';
+    if ((e = std::getenv("FKB_TINY_PIXELS")) && e[0]) t.tiny_pixels = std::strtoull(e, nullptr, 10);
+    if ((e = std::getenv("FKB_ROWS_PER_ITEM")) && e[0]) t.rows_per_item = static_cast<uint32_t>(std::strtoul(e, nullptr, 10));
+    return t;
 }
 
 uint32_t post_kind_of(const fkb_chain_desc& ch);
 
 // Chooses the kernel path and tile shape of one plane.
-void classify(const fkb_chain_desc& ch, PlaneRec& r) {
+void classify(const fkb_chain_desc& ch, PlaneRec& r, const Tuning& tune) {
     r.kclass = KCLASS_GATHER;
     r.tile_w = r.tile_h = r.tiles_x = 0;
     if (ch.dst_format == FKB_PIX_U8C4 || ch.dst_format == FKB_PIX_F32C4) { r.kclass = KCLASS_GATHER4; return; }
-    if (force_gather()) return;
+    if (tune.force_gather) return;
     if (ch.border) {
         // a rectangle inside the frame never meets the border: it takes the usual paths; one that leaves it is
         // remapped tap by tap in the general kernel
@@ -259,6 +265,13 @@ void classify(const fkb_chain_desc& ch, PlaneRec& r) {
             return;
         }
         if (!(r.fx <= 32.f) || !(r.fy <= 4096.f)) return;
+        for (uint32_t i = ch.n_pre_ops; i < ch.n_ops; ++i)  // (a per-plane Mul operand takes a factor of 2^22 there, too)
+            if (ch.ops[i].code == FKB_OP_MUL && ch.ops[i].plane_slot >= 0)
+                for (int c = 0; c < 3; ++c)
+                    if (!(std::fabs(r.params[ch.ops[i].plane_slot][c]) < 0x1p100f)) return;
+        // the staged kernel reads tap bytes as subnormal floats and scales them by powers of two; with scale factors
+        // this small (an enlargement by 2^24) a weight could underflow there
+        if (!(r.fx >= 5.9604645e-8f) || !(r.fy >= 5.9604645e-8f)) return;
         // widest segment (at most 8 columns per lane) whose source columns fit one staged row
         uint32_t tw = std::min(r.dst_w, 256u);
         for (;;) {
@@ -286,18 +299,16 @@ bool rgb_kernel_takes(const fkb_chain_desc& ch, const PlaneRec& r) {
     return x >= 0 && y >= 0 && x + r.crop_w <= static_cast<int64_t>(r.src_w) && y + r.crop_h <= static_cast<int64_t>(r.src_h);
 }
 
-// Output rows a warp processes per item.  Inside an item the next row's footprint is prefetched while the current
-// row is computed, so longer items pipeline better; more items balance better (warps claim them from a counter).  Large
-// launches get about sixteen items per resident warp — measured on the 2048-plane crop-resize launch, 10 to 16 rows per
-// item are within 1 % of each other, 4 or 24 rows cost 3 to 12 %.  Launches with 16 to 128 rows per warp (256 to 1024
-// planes of that shape) get eight rows per item (4 to 7 % faster than four), smaller ones four, and launches too small
-// to occupy every warp one row per item.
+// Output rows a warp processes per item.  An item costs a set-up (about as much as one row) and, inside an item, the
+// source rows of the row after next are already in flight, so longer items run better; shorter ones balance better
+// (warps claim them from a counter) and leave a shorter tail when the launch ends.  Measured on crop-resize launches of
+// 64 to 2048 planes of 224 x 224: eight rows per item are the best or within 1 % of it at every size (2048 planes:
+// 6 rows +3 %, 12 rows +2 %, 16 rows +8 %, 32 rows +25 %).  A launch too small to give every resident warp eight rows
+// gets items of just the length that spreads its rows over all warps in one round.
 uint32_t rows_per_item(uint64_t row_segments, uint32_t resident_warps) {
-    const uint64_t per_warp = row_segments / resident_warps;
-    uint32_t rpi = static_cast<uint32_t>(std::min<uint64_t>(std::max<uint64_t>(per_warp / 16u, 1), kMaxRowsPerItem));
-    if (rpi < 8 && per_warp >= 16) rpi = 8;
-    else if (rpi < 4 && per_warp >= 4) rpi = 4;
-    return rpi;
+    constexpr uint32_t kRows = 8;
+    if (row_segments >= static_cast<uint64_t>(kRows) * resident_warps) return kRows;
+    return static_cast<uint32_t>(std::max<uint64_t>((row_segments + resident_warps - 1) / resident_warps, 1));
 }
 
 // Shape of the ops that follow the read / the interpolation: bit 0 Mul, bit 1 Add or Sub, bit 2 SaturateCast when the
@@ -306,7 +317,13 @@ uint32_t rows_per_item(uint64_t row_segments, uint32_t resident_warps) {
 uint32_t post_kind_of(const fkb_chain_desc& ch) {
     uint32_t i = ch.geometry == FKB_GEOM_NONE ? 0 : ch.n_pre_ops, kind = 0;
     while (i < ch.n_ops && ch.ops[i].code == FKB_OP_CAST_F32) ++i;
-    if (i < ch.n_ops && ch.ops[i].code == FKB_OP_MUL) { kind |= 1; ++i; }
+    if (i < ch.n_ops && ch.ops[i].code == FKB_OP_MUL) {
+        // (the staged kernel folds a factor of 2^22 into this operand: a huge one goes through the interpreter instead)
+        if (ch.ops[i].plane_slot < 0)
+            for (int c = 0; c < 3; ++c)
+                if (!(std::fabs(ch.ops[i].v[c]) < 0x1p100f)) return 8u;
+        kind |= 1; ++i;
+    }
     if (i < ch.n_ops && (ch.ops[i].code == FKB_OP_ADD || ch.ops[i].code == FKB_OP_SUB)) { kind |= 2; ++i; }
     if (i < ch.n_ops && ch.ops[i].code == FKB_OP_DIV) { kind |= 16; ++i; }  // only nv12_kernel specialises this part
     if (i < ch.n_ops && ch.ops[i].code == FKB_OP_SATCAST_U8) { kind |= 4; ++i; }
@@ -372,10 +389,10 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
     const int rc = validate(chains, n_chains, planes, n_planes);
     if (rc != FKB_OK) return rc;
     if (!L.recs) { L.storage.resize(n_planes); L.recs = L.storage.data(); }
+    const Tuning tune = read_tuning();
     std::memset(&L.lp, 0, sizeof(L.lp));
     std::memcpy(L.lp.chains, chains, sizeof(fkb_chain_desc) * n_chains);
     uint32_t n_tiles = 0, gw = 0, gh = 0, n_gather = 0, g4w = 0, g4h = 0, n_gather4 = 0;
-    bool uniform = true;
     uint32_t first_count = 0;
     int sms = 0;
     {
@@ -415,17 +432,17 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
             const uint32_t df = chains[r.chain].dst_format;
             r.kclass = (df == FKB_PIX_U8C4 || df == FKB_PIX_F32C4) ? KCLASS_GATHER4 : KCLASS_GATHER;
         } else {
-            classify(chains[r.chain], r);
+            classify(chains[r.chain], r, tune);
         }
         total_pixels += static_cast<uint64_t>(r.dst_w) * r.dst_h;
     }
     // A launch of a few ten thousand pixels is pure latency: the pipelined paths would spend it filling their stages,
     // so it goes through the general kernel, one pixel per thread.
-    if (total_pixels < tiny_launch_pixels())
+    if (total_pixels < tune.tiny_pixels)
         for (uint32_t z = 0; z < n_planes; ++z)
             if (L.recs[z].kclass != KCLASS_NV12 && L.recs[z].kclass != KCLASS_GATHER4) {
                 // (the one-pixel-per-thread kernel where its conditions hold, else the general kernel)
-                L.recs[z].kclass = (!force_gather() && rgb_kernel_takes(chains[L.recs[z].chain], L.recs[z])) ? KCLASS_NV12 : KCLASS_GATHER;
+                L.recs[z].kclass = (!tune.force_gather && rgb_kernel_takes(chains[L.recs[z].chain], L.recs[z])) ? KCLASS_NV12 : KCLASS_GATHER;
                 L.recs[z].tiles_x = 0;
             }
     for (uint32_t z = 0; z < n_planes; ++z) {
@@ -462,7 +479,15 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         const uint32_t first_pixel = to_back(KCLASS_NV12, first_four);
         L.lp.pixel_z0 = first_pixel; L.lp.pixel_z1 = first_four;
     }
-    const uint32_t rpi = rows_per_item(row_segments, 2u * kStagedWarps * static_cast<uint32_t>(sms));
+    // Items of the staged kernel; when every plane of the launch has the same shape (the batched crop-resize case) the
+    // kernel finds an item's plane by division instead of a search.
+    const uint32_t resident_warps = 2u * kStagedWarps * static_cast<uint32_t>(sms);
+    const uint32_t rpi = tune.rows_per_item ? std::min(tune.rows_per_item, kMaxRowsPerItem) : rows_per_item(row_segments, resident_warps);
+    bool same_shape = n_planes > 0;
+    for (uint32_t z = 0; z < n_planes && same_shape; ++z) {
+        const PlaneRec& r = L.recs[z];
+        same_shape = (r.kclass == KCLASS_POINT || r.kclass == KCLASS_RESIZE) && r.tiles_x == L.recs[0].tiles_x && r.dst_h == L.recs[0].dst_h;
+    }
     for (uint32_t z = 0; z < n_planes; ++z) {
         PlaneRec& r = L.recs[z];
         r.lut_base = n_lut_units;
@@ -474,7 +499,7 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         }
         r.tile_base = n_tiles;
         const uint32_t count = (r.kclass == KCLASS_POINT || r.kclass == KCLASS_RESIZE) ? r.tiles_x * ((r.dst_h + r.tile_h - 1) / r.tile_h) : 0u;
-        if (z == 0) first_count = count; else if (count != first_count) uniform = false;
+        if (z == 0) first_count = count;
         if (static_cast<uint64_t>(n_tiles) + count > 0xfffffff0ull) return FKB_ERR_TOO_LARGE;
         n_tiles += count;
         if (r.kclass == KCLASS_GATHER) {
@@ -498,7 +523,7 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         L.lp.lut_swap |= (reorders & 1u) << c;
     }
     L.lp.n_tiles = n_tiles;
-    L.lp.tiles_per_plane = (uniform && first_count) ? first_count : 0;
+    L.lp.tiles_per_plane = (same_shape && first_count) ? first_count : 0;
     if (n_tiles) {
         L.staged_grid = std::min<uint32_t>(n_tiles, 2u * static_cast<uint32_t>(sms));
         ++L.kernels;
@@ -562,11 +587,10 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
     return status_word(&L.lp.status);
 }
 
-// Whether the staged kernel of this launch should claim its items from a counter: at least four items per resident warp.
-// Below that the claims themselves (every warp hits one address when the kernel starts) cost more than the balance
-// gains: a 4 320-item launch took 17 us with the counter and 12 us without.
+// Whether the staged kernel of this launch needs a work counter: every warp takes its first two items by position and
+// claims the rest, so a counter is needed as soon as some warp has a third item.
 bool wants_work_counter(const Lowered& L) {
-    return L.staged_grid != 0 && L.lp.n_tiles >= 4u * L.staged_grid * kStagedWarps;
+    return L.staged_grid != 0 && L.lp.n_tiles > 2u * L.staged_grid * kStagedWarps;
 }
 
 int run(const Lowered& L, const LaunchParams& lp, cudaStream_t stream) {
@@ -598,12 +622,26 @@ struct Arena {
         if (bytes <= slot_bytes) return FKB_OK;
         for (int i = 0; i < kSlots; ++i)
             if (used[i]) { FKB_CUDA(cudaEventSynchronize(ev[i])); used[i] = false; }
-        if (pinned) { FKB_CUDA(cudaFreeHost(pinned)); pinned = nullptr; }
-        if (dev) { FKB_CUDA(cudaFree(dev)); dev = nullptr; }
+        // the old buffers go first and the arena counts as empty until both new ones exist: a failed allocation must not
+        // leave a slot size behind that no buffer backs
+        slot_bytes = 0;
+        if (pinned) { uint8_t* q = pinned; pinned = nullptr; FKB_CUDA(cudaFreeHost(q)); }
+        if (dev) { uint8_t* q = dev; dev = nullptr; FKB_CUDA(cudaFree(q)); }
         size_t want = 1u << 20;
         while (want < bytes) want <<= 1;
-        FKB_CUDA(cudaMallocHost(reinterpret_cast<void**>(&pinned), want * kSlots));
-        FKB_CUDA(cudaMalloc(reinterpret_cast<void**>(&dev), want * kSlots));
+        uint8_t* new_pinned = nullptr;
+        uint8_t* new_dev = nullptr;
+        FKB_CUDA(cudaMallocHost(reinterpret_cast<void**>(&new_pinned), want * kSlots));
+        {
+            const cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&new_dev), want * kSlots);
+            if (e != cudaSuccess) {
+                (void)cudaFreeHost(new_pinned);
+                t_last_cuda_error = static_cast<int>(e);
+                (void)cudaGetLastError();
+                return FKB_ERR_CUDA;
+            }
+        }
+        pinned = new_pinned; dev = new_dev;
         if (!work) {  // one pair of item counters per slot; a kernel leaves its pair at zero
             FKB_CUDA(cudaMalloc(reinterpret_cast<void**>(&work), sizeof(uint32_t) * 2 * kSlots));
             FKB_CUDA(cudaMemset(work, 0, sizeof(uint32_t) * 2 * kSlots));
@@ -629,6 +667,17 @@ Arena& arena_for_current_device(int& rc) {
     return a;
 }
 
+// A launch that stages its plane records through host memory owned by the library (an arena slot, the fixed array of
+// the no-allocation entry point) cannot be recorded into a CUDA graph: the recorded copy would read that memory again at
+// every replay, long after another launch has overwritten it, and the arena's event waits are illegal on a capturing
+// stream.  Such launches are refused while the stream is capturing; launches whose records travel in the kernel
+// parameters, and plans, record fine.
+int refuse_if_capturing(cudaStream_t stream) {
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    FKB_CUDA(cudaStreamIsCapturing(stream, &st));
+    return st == cudaStreamCaptureStatusNone ? FKB_OK : FKB_ERR_UNSUPPORTED;
+}
+
 int launch_once(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc* planes, uint32_t n_planes,
                 cudaStream_t stream) {
     Lowered L;
@@ -640,6 +689,7 @@ int launch_once(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane
         L.lp.table = nullptr;
         if (!counter) return run(L, L.lp, stream);
     }
+    if ((rc = refuse_if_capturing(stream)) != FKB_OK) return rc;
     // a slot of the arena: its part of the device table (launches of many planes) and its pair of item counters
     Arena& a = arena_for_current_device(rc);
     if (rc != FKB_OK) return rc;
@@ -687,7 +737,11 @@ int launch_noalloc(const fkb_chain_desc* chain, const fkb_plane_desc* planes, ui
     if (!chain || !planes) return FKB_ERR_NULL;
     if (n_planes > FKB_NOALLOC_MAX_PLANES) return FKB_ERR_TOO_LARGE;  // the fixed table holds no more
     for (uint32_t z = 0; z < n_planes; ++z)
-        if (planes[z].chain != 0) return FKB_ERR_INVALID;
+        if ((planes[z].chain & ~FKB_PLANE_DEFAULT) != 0) return FKB_ERR_INVALID;
+    {
+        const int rc = refuse_if_capturing(stream);
+        if (rc != FKB_OK) return rc;
+    }
     NoAllocState& st = noalloc_state();
     std::lock_guard<std::mutex> g(st.m);
     int dev = 0;
@@ -705,7 +759,8 @@ int launch_noalloc(const fkb_chain_desc* chain, const fkb_plane_desc* planes, ui
     const int rc = lower(chain, 1, planes, n_planes, L);
     if (rc != FKB_OK) return rc;
     // Every record the kernels will read is rewritten by this copy; nothing in the table has to start at zero.  The
-    // source is pageable memory, so the call returns only after the records have left st.host_recs.
+    // source is pageable memory: outside a stream capture (refused above) the runtime has taken the records out of
+    // st.host_recs by the time the call returns, so the next call may overwrite them.
     FKB_CUDA(cudaMemcpyAsync(st.device_table[dev], st.host_recs, sizeof(PlaneRec) * n_planes, cudaMemcpyHostToDevice, stream));
     L.lp.table = st.device_table[dev];
     return run(L, L.lp, stream);  // (no work counter: items are dealt round-robin)
@@ -714,10 +769,15 @@ int launch_noalloc(const fkb_chain_desc* chain, const fkb_plane_desc* planes, ui
 }  // namespace
 }  // namespace fkb
 
+// Item counters of a plan's staged kernel: a ring of pairs, one pair per launch in turn.  A kernel leaves its pair at
+// zero, so a pair is ready again when the launch that used it has finished; launches of one plan may therefore overlap
+// on the GPU (different streams) as long as fewer than kPlanCounterPairs of them are in flight at once.
+constexpr uint32_t kPlanCounterPairs = 64;
 struct fkb_plan {
     fkb::Lowered L;
     fkb::PlaneRec* table = nullptr;
-    uint32_t* work = nullptr;  // item counters of the staged kernel (launches of one plan are expected not to overlap on the GPU)
+    uint32_t* work = nullptr;
+    mutable std::atomic<uint32_t> launches{0};
     int device = 0;
 };
 
@@ -835,8 +895,8 @@ int fkb_plan_create(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_p
     if (rc != FKB_OK) { delete plan; return rc; }
     cudaError_t e = cudaGetDevice(&plan->device);
     if (e == cudaSuccess && wants_work_counter(plan->L)) {
-        e = cudaMalloc(reinterpret_cast<void**>(&plan->work), 2 * sizeof(uint32_t));
-        if (e == cudaSuccess) e = cudaMemset(plan->work, 0, 2 * sizeof(uint32_t));
+        e = cudaMalloc(reinterpret_cast<void**>(&plan->work), 2 * sizeof(uint32_t) * kPlanCounterPairs);
+        if (e == cudaSuccess) e = cudaMemset(plan->work, 0, 2 * sizeof(uint32_t) * kPlanCounterPairs);
         plan->L.lp.work = plan->work;
     }
     if (n_planes <= kInlinePlanes) {
@@ -868,7 +928,10 @@ int fkb_plan_launch(const fkb_plan* plan, void* cuda_stream) {
     int dev = -1;
     FKB_CUDA(cudaGetDevice(&dev));
     if (dev != plan->device) return FKB_ERR_INVALID;
-    return run(plan->L, plan->L.lp, static_cast<cudaStream_t>(cuda_stream));
+    if (!plan->work) return run(plan->L, plan->L.lp, static_cast<cudaStream_t>(cuda_stream));
+    LaunchParams lp = plan->L.lp;  // this launch's own pair of item counters
+    lp.work = plan->work + 2u * (plan->launches.fetch_add(1u, std::memory_order_relaxed) % kPlanCounterPairs);
+    return run(plan->L, lp, static_cast<cudaStream_t>(cuda_stream));
 }
 
 void fkb_plan_destroy(fkb_plan* plan) {

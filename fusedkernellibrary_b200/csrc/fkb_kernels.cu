@@ -657,14 +657,40 @@ __device__ __forceinline__ bool point_item(const LaunchParams& p, const WarpSlic
 // are dealt to the lanes in groups of 32: lane l owns columns xa+l, xa+32+l, ...; the last group is shifted left so
 // that it is full too (a few columns are then computed twice, with identical results).  Everything that depends only
 // on the column — the byte offset of its tap pair in a staged row and the two horizontal weights — is computed once
-// per item and kept in registers for all rows.  A tap pair (x1, x1+1) is six consecutive bytes; the column one past
-// the crop is made a copy of the last column after the row lands, which is exactly the reference's clamp of x2.
-// Bytes become fp32 through the half-subnormal trick (byte_times_2m24), and all arithmetic runs on pixel pairs with
-// packed f32x2 instructions.  The background bars are written into the two output-row buffers once per item.
+// per item and kept in registers for all rows; what depends only on the row — the two source rows and the vertical
+// weights — is computed once per item too, row r by lane r, and handed round with shuffles.  A tap pair (x1, x1+1) is
+// six consecutive bytes; the column one past the crop is made a copy of the last column after the row lands, which is
+// exactly the reference's clamp of x2.
+//
+// A tap byte needs no conversion instruction at all: the zero-extended byte b, read as an fp32 bit pattern, is the
+// subnormal number b * 2^-149, and the FMA pipe takes subnormal operands at full rate.  The vertical weights are
+// pre-multiplied by 2^127 (exact), so every product is fl(b * w) * 2^-22 — the correctly rounded product, scaled by a
+// power of two — and so is every partial sum (all terms are non-negative, nothing cancels, nothing underflows: the
+// host sends planes whose scale factors are below 2^-24 elsewhere).  The 2^22 that is still missing is folded into the
+// Mul operand when the chain has one (fl((v * 2^-22) * (m * 2^22)) = fl(v * m)), else it is one exact multiplication.
+// Groups are computed two at a time with packed f32x2 instructions; an odd last group runs as scalars.
+// The background bars are written into the two output-row buffers once per item.
+constexpr float kTapScale = 1.7014118346046923e38f;  // 2^127
+constexpr float kTapUnscale = 4194304.0f;            // 2^22 = 2^149 / 2^127
+static_assert(kMaxRowsPerItem <= 32, "one lane per row of an item");
+
+__device__ __forceinline__ float tap_subnormal(uint32_t smem_off) {
+    return __uint_as_float(static_cast<uint32_t>(smem_raw[smem_off]));
+}
+// [Mul][Add][Sat] on one scalar; with a SaturateCast the result is 2^23 + n (the integer in the low byte)
+template <int KIND>
+__device__ __forceinline__ float post_scalar(float r, float m, float a) {
+    if (KIND & kPostMul) r = __fmul_rn(r, m);
+    if (KIND & kPostAdd) r = __fadd_rn(r, a);
+    if (KIND & kPostSat) r = __fadd_rn(fminf(fmaxf(r, 0.f), 255.f), kMagic);
+    return r;
+}
+
 template <bool F32, int KIND, bool PLANAR = false, bool SRC4 = false>
 __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSlice& w, uint32_t ox, uint32_t oy0,
                                             uint32_t ow, uint32_t nr, uint32_t& k, uint32_t lane) {
     static_assert(F32 || !PLANAR, "planar rows are float rows");
+    constexpr uint32_t FULL = 0xffffffffu;
     constexpr uint32_t SP = SRC4 ? 4u : 3u;                           // bytes per source pixel (uchar4: the alpha byte is skipped)
     constexpr uint32_t ELT = PLANAR ? 4u : F32 ? 12u : 3u;            // bytes between columns of a staged output row
     constexpr uint32_t DEAD = PLANAR ? 1024u : kOutRowBytes;          // where columns that do not exist are stored
@@ -687,37 +713,98 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
     const uint32_t row_bytes = ((g1 + 15u) & ~15u) - a0;
     if (row_bytes + 32u > kInRowBytes) return false;  // the host lowering guarantees the footprint fits
 
-    // per-column state of this lane: staged-row byte offset of the tap pair, horizontal weights, output offset
-    // (columns that do not exist write to the spare bytes behind the output row)
-    uint32_t boff[8], ooff[8];
+    // per-row state, row r of the item in lane r: the two source rows (as an offset from the crop's first row, in
+    // units of 16 bytes: staged sources have pitches that are multiples of 16) and the vertical weights times 2^127
+    const uint32_t pitch16 = pl.src_pitch >> 4;
+    const int y_l = static_cast<int>(oy0 + min(lane, nr - 1u));
+    const bool in_l = n_in > 0 && y_l >= Y1 && y_l <= Y2;
+    const AxisTap ay_l = axis_tap(in_l ? y_l - Y1 : 0, fy, crop_h);
+    const uint32_t in_mask = __ballot_sync(FULL, in_l);
+    const uint32_t row0_l = static_cast<uint32_t>(ay_l.i0) * pitch16;
+    const uint32_t row1_l = static_cast<uint32_t>(ay_l.i1) * pitch16;
+    const float wy0_l = __fmul_rn(ay_l.w0, kTapScale), wy1_l = __fmul_rn(ay_l.w1, kTapScale);
+
+    const uint8_t* gsrc = pl.src + static_cast<size_t>(pl.crop_y) * pl.src_pitch + a0;
+    // Lane 0 requests row r's two source rows (r0, r1: offsets in units of 16 bytes) into stage s.  Always two staged rows
+    // (the second repeats the first where the reference clamps y2), so that the second row sits at a fixed distance
+    // from the first.
+    auto load_rows = [&](uint32_t r, uint32_t s, uint32_t r0, uint32_t r1) {
+        const bool in = (in_mask >> r) & 1u;
+        mbar_arrive_expect_tx(w.bar(s), in ? 2u * row_bytes : 0u);
+        if (in) {
+            bulk_load(smem_raw + w.in(s), gsrc + static_cast<size_t>(r0) * 16u, row_bytes, w.bar(s));
+            bulk_load(smem_raw + w.in(s) + kInRowBytes, gsrc + static_cast<size_t>(r1) * 16u, row_bytes, w.bar(s));
+        }
+    };
+    // The source rows of the first two output rows are requested before the rest of the set-up, which then overlaps
+    // their latency (both stages were last read by rows this warp has finished).
+    {
+        const uint32_t r0a = __shfl_sync(FULL, row0_l, 0), r1a = __shfl_sync(FULL, row1_l, 0);
+        const uint32_t r0b = __shfl_sync(FULL, row0_l, 1), r1b = __shfl_sync(FULL, row1_l, 1);
+        if (lane == 0) {
+            load_rows(0u, k & 1u, r0a, r1a);
+            if (nr > 1) load_rows(1u, (k + 1u) & 1u, r0b, r1b);
+        }
+    }
+
+    // per-column state of this lane: staged-row byte offset of the tap pair and the horizontal weights.  Where a column
+    // goes in the output row follows from its group: group j starts 32 j columns after the lane's first column, except
+    // the last group, which is shifted (or, when the item has fewer than 32 columns, partly missing: those lanes write
+    // to the spare bytes behind the output row).
+    uint32_t boff[8];
     float wx0[8], wx1[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-        int col = 32 * j + static_cast<int>(lane);                 // index among the inside columns
-        if (j == nj - 1 && n_in >= 32) col = n_in - 32 + static_cast<int>(lane);  // last group, shifted to be full
-        const bool live = j < nj && col < n_in;
-        col = min(col, max(n_in - 1, 0));
-        const AxisTap t = axis_tap(xa + col - X1, fx, crop_w);
-        boff[j] = n_in ? static_cast<uint32_t>(t.i0 - c_lo) * SP + shift : 0u;
-        wx0[j] = t.w0; wx1[j] = t.w1;
-        ooff[j] = live ? static_cast<uint32_t>(xa - static_cast<int>(ox) + col) * ELT : DEAD;
+        if (j < nj) {
+            int col = 32 * j + static_cast<int>(lane);                 // index among the inside columns
+            if (j == nj - 1 && n_in >= 32) col = n_in - 32 + static_cast<int>(lane);  // last group, shifted to be full
+            col = min(col, n_in - 1);
+            const AxisTap t = axis_tap(xa + col - X1, fx, crop_w);
+            boff[j] = static_cast<uint32_t>(t.i0 - c_lo) * SP + shift;
+            wx0[j] = t.w0; wx1[j] = t.w1;
+        } else {
+            boff[j] = 0u; wx0[j] = wx1[j] = 0.f;
+        }
     }
+    const uint32_t obase = static_cast<uint32_t>(xa - static_cast<int>(ox) + static_cast<int>(lane)) * ELT;
+    const uint32_t olast = n_in >= 32 ? static_cast<uint32_t>(xa - static_cast<int>(ox) + n_in - 32 + static_cast<int>(lane)) * ELT
+                                      : (static_cast<int>(lane) < n_in ? obase : DEAD);
+    // output-row offset of this lane's column of group j
+    auto ocol = [&](int j) { return j + 1 == nj ? olast : obase + static_cast<uint32_t>(j) * (32u * ELT); };
     // Offset (in a staged row) of the crop's last column when a tap pair reaches one past it; that column is then
     // duplicated into the next three bytes.  Otherwise the copy is aimed at the unused tail of the staged row.
     const uint32_t rep_off = replicate ? static_cast<uint32_t>(crop_w - 1 - c_lo) * SP + shift : kInRowBytes - 8u;
-    const uint8_t* gsrc = pl.src + static_cast<size_t>(pl.crop_y) * pl.src_pitch + a0;
-    const uint32_t src_pitch = pl.src_pitch, dst_pitch = pl.dst_pitch;
+    const uint32_t dst_pitch = pl.dst_pitch;
     uint8_t* gdst = pl.dst + static_cast<size_t>(oy0) * dst_pitch + static_cast<size_t>(ox) * ELT;
 
+    // operands of the specialised post-ops; the Mul operand also takes the 2^22 the taps' scale leaves behind
+    PostParams post;
+    if (KIND != kPostGeneric) {
+        const PostImm& imm = p.post_imm[pl.chain];
+        if (imm.slots) post = load_post(ch, pl, ch.n_pre_ops);
+        else {
+#pragma unroll
+            for (int c = 0; c < 3; ++c) { post.m[c] = imm.m[c]; post.a[c] = imm.a[c]; post.d[c] = 1.f; }
+        }
+    }
     // what a background pixel becomes, as the bit patterns that are stored
-    const PostParams post = load_post(ch, pl, ch.n_pre_ops);
     uint32_t bgbits[3];
-    {
+    if (KIND != kPostGeneric) {
+#pragma unroll
+        for (int c = 0; c < 3; ++c) {
+            const float b = post_scalar<KIND>(pl.bg[c], post.m[c], post.a[c]);
+            bgbits[c] = (KIND & kPostSat) ? (__float_as_uint(b) & 0xffu) : __float_as_uint(b);
+        }
+    } else {
         float b[1][3] = {{pl.bg[0], pl.bg[1], pl.bg[2]}};
         apply_ops<1>(b, ch, pl, ch.n_pre_ops, ch.n_ops);
 #pragma unroll
         for (int c = 0; c < 3; ++c) bgbits[c] = F32 ? __float_as_uint(b[0][c]) : u8_of_exact(b[0][c]);
     }
+    float mq[3];  // Mul operand times 2^22 (or 2^22 alone)
+#pragma unroll
+    for (int c = 0; c < 3; ++c) mq[c] = (KIND != kPostGeneric && (KIND & kPostMul)) ? __fmul_rn(post.m[c], kTapUnscale) : kTapUnscale;
+
     auto put = [&](uint32_t q, uint32_t b0, uint32_t b1, uint32_t b2) {
         if (PLANAR) {
             *reinterpret_cast<uint32_t*>(smem_raw + q) = b0;
@@ -732,54 +819,21 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
     if (lane == 0) bulk_wait_read_all();
     __syncwarp();
     if (static_cast<uint32_t>(n_in) < ow) {
-        for (int c = static_cast<int>(lane); c < static_cast<int>(ow); c += 32) {
-            if (n_in == 0 || c < xa - static_cast<int>(ox) || c > xb - static_cast<int>(ox)) {
-                put(w.out(0) + static_cast<uint32_t>(c) * ELT, bgbits[0], bgbits[1], bgbits[2]);
-                put(w.out(1) + static_cast<uint32_t>(c) * ELT, bgbits[0], bgbits[1], bgbits[2]);
-            }
+        const int left = n_in ? xa - static_cast<int>(ox) : static_cast<int>(ow);  // columns of the left bar (all of them when nothing is inside)
+        const int n_bar = static_cast<int>(ow) - n_in;
+        for (int c = static_cast<int>(lane); c < n_bar; c += 32) {
+            const uint32_t q = static_cast<uint32_t>(c < left ? c : c + n_in) * ELT;
+            put(w.out(0) + q, bgbits[0], bgbits[1], bgbits[2]);
+            put(w.out(1) + q, bgbits[0], bgbits[1], bgbits[2]);
         }
     }
 
-    AxisTap ay_next;
-    bool in_next;
-    // Row r's vertical taps, and (lane 0) its bulk loads into stage s.  Always two staged rows (the second repeats the
-    // first where the reference clamps y2), so that the second row sits at a fixed distance from the first.  With
-    // `wait_out`, lane 0 first waits until the bulk store issued two rows ago has finished reading its row buffer.
-    auto issue = [&](uint32_t r, uint32_t s, bool load, bool wait_out) {
-        const int y = static_cast<int>(oy0 + r);
-        in_next = n_in > 0 && y >= Y1 && y <= Y2;
-        ay_next = axis_tap(in_next ? y - Y1 : 0, fy, crop_h);
-        if (lane == 0) {
-            if (wait_out) bulk_wait_read_1();
-            if (load) {
-                mbar_arrive_expect_tx(w.bar(s), in_next ? 2u * row_bytes : 0u);
-                if (in_next) {
-                    bulk_load(smem_raw + w.in(s), gsrc + static_cast<size_t>(ay_next.i0) * src_pitch, row_bytes, w.bar(s));
-                    bulk_load(smem_raw + w.in(s) + kInRowBytes, gsrc + static_cast<size_t>(ay_next.i1) * src_pitch, row_bytes, w.bar(s));
-                }
-            }
-        }
-    };
-
-    // one pair of columns (j, j+1) of the current row
-    auto pair = [&](int j, uint32_t in_s, uint32_t out_s, f2 wy0, f2 wy1) {
-        const uint32_t a0p = in_s + boff[j], a1p = in_s + boff[j + 1];
-        const f2 wx0p = {wx0[j], wx0[j + 1]}, wx1p = {wx1[j], wx1[j + 1]};
-        const f2 w00 = mul2(wx0p, wy0), w10 = mul2(wx1p, wy0), w01 = mul2(wx0p, wy1), w11 = mul2(wx1p, wy1);
-        f2 v[3];
-#pragma unroll
-        for (int c = 0; c < 3; ++c) {
-            // taps of the two columns: (x1,y1) (x1+1,y1) (x1,y2) (x1+1,y2); bytes come back as b * 2^-24
-            const f2 p00 = {byte_times_2m24(smem_raw[a0p + c]), byte_times_2m24(smem_raw[a1p + c])};
-            const f2 p10 = {byte_times_2m24(smem_raw[a0p + SP + c]), byte_times_2m24(smem_raw[a1p + SP + c])};
-            const f2 p01 = {byte_times_2m24(smem_raw[a0p + kInRowBytes + c]), byte_times_2m24(smem_raw[a1p + kInRowBytes + c])};
-            const f2 p11 = {byte_times_2m24(smem_raw[a0p + kInRowBytes + SP + c]), byte_times_2m24(smem_raw[a1p + kInRowBytes + SP + c])};
-            v[c] = add2(add2(add2(mul2_unfusable(p00, w00, nz), mul2_unfusable(p10, w10, nz)), mul2_unfusable(p01, w01, nz)),
-                        mul2_unfusable(p11, w11, nz));
-        }
-        uint32_t bx[3], by[3];
+    // the post-ops of one channel of a pixel pair and the bits to store
+    auto finish = [&](const f2 (&v)[3], uint32_t (&bx)[3], uint32_t (&by)[3]) {
         if (KIND == kPostGeneric) {
-            float t[2][3] = {{v[0].x, v[1].x, v[2].x}, {v[0].y, v[1].y, v[2].y}};
+            float t[2][3];
+#pragma unroll
+            for (int c = 0; c < 3; ++c) { const f2 u = mul2(v[c], f2{kTapUnscale, kTapUnscale}); t[0][c] = u.x; t[1][c] = u.y; }
             apply_ops<2>(t, ch, pl, ch.n_pre_ops, ch.n_ops);
 #pragma unroll
             for (int c = 0; c < 3; ++c) {
@@ -789,39 +843,96 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
         } else {
 #pragma unroll
             for (int c = 0; c < 3; ++c) {
-                const f2 t = post_channel<KIND>(v[c], post, c, nz);
+                // (a product by 2^22 alone is exact, so it may fuse with the addition that follows; a Mul operand's may not)
+                f2 t = ((KIND & kPostMul) && (KIND & kPostAdd)) ? mul2_unfusable(v[c], f2{mq[c], mq[c]}, nz) : mul2(v[c], f2{mq[c], mq[c]});
+                if (KIND & kPostAdd) t = add2(t, f2{post.a[c], post.a[c]});
+                if (KIND & kPostSat) {
+                    t.x = fminf(fmaxf(t.x, 0.f), 255.f);
+                    t.y = fminf(fmaxf(t.y, 0.f), 255.f);
+                    t = add2(t, f2{kMagic, kMagic});
+                }
                 bx[c] = __float_as_uint(t.x); by[c] = __float_as_uint(t.y);  // with SaturateCast: low byte = value
             }
         }
-        put(out_s + ooff[j], bx[0], bx[1], bx[2]);
-        put(out_s + ooff[j + 1], by[0], by[1], by[2]);
     };
 
-    const int npairs = (nj + 1) >> 1;
-    issue(0u, k & 1u, true, false);
-    for (uint32_t r = 0; r < nr; ++r, ++k) {
+    // two groups of columns (j, j+1) of the current row
+    auto pair = [&](int j, uint32_t in_s, uint32_t out_s, f2 wy0, f2 wy1) {
+        const uint32_t a0p = in_s + boff[j], a1p = in_s + boff[j + 1];
+        const f2 wx0p = {wx0[j], wx0[j + 1]}, wx1p = {wx1[j], wx1[j + 1]};
+        const f2 w00 = mul2(wx0p, wy0), w10 = mul2(wx1p, wy0), w01 = mul2(wx0p, wy1), w11 = mul2(wx1p, wy1);
+        f2 v[3];
+#pragma unroll
+        for (int c = 0; c < 3; ++c) {
+            // taps of the two columns: (x1,y1) (x1+1,y1) (x1,y2) (x1+1,y2), each b * 2^-149
+            const f2 p00 = {tap_subnormal(a0p + c), tap_subnormal(a1p + c)};
+            const f2 p10 = {tap_subnormal(a0p + SP + c), tap_subnormal(a1p + SP + c)};
+            const f2 p01 = {tap_subnormal(a0p + kInRowBytes + c), tap_subnormal(a1p + kInRowBytes + c)};
+            const f2 p11 = {tap_subnormal(a0p + kInRowBytes + SP + c), tap_subnormal(a1p + kInRowBytes + SP + c)};
+            v[c] = add2(add2(add2(mul2_unfusable(p00, w00, nz), mul2_unfusable(p10, w10, nz)), mul2_unfusable(p01, w01, nz)),
+                        mul2_unfusable(p11, w11, nz));
+        }
+        uint32_t bx[3], by[3];
+        finish(v, bx, by);
+        put(out_s + obase + static_cast<uint32_t>(j) * (32u * ELT), bx[0], bx[1], bx[2]);  // (the first group of a pair is never the last)
+        put(out_s + ocol(j + 1), by[0], by[1], by[2]);
+    };
+    // one group of columns: channels 0 and 1 as a packed pair, channel 2 with itself
+    auto single = [&](int j, uint32_t in_s, uint32_t out_s, f2 wy0, f2 wy1) {
+        const uint32_t ap = in_s + boff[j];
+        const f2 wx0p = {wx0[j], wx0[j]}, wx1p = {wx1[j], wx1[j]};
+        const f2 w00 = mul2(wx0p, wy0), w10 = mul2(wx1p, wy0), w01 = mul2(wx0p, wy1), w11 = mul2(wx1p, wy1);
+        const f2 p00 = {tap_subnormal(ap), tap_subnormal(ap + 1)}, p10 = {tap_subnormal(ap + SP), tap_subnormal(ap + SP + 1)};
+        const f2 p01 = {tap_subnormal(ap + kInRowBytes), tap_subnormal(ap + kInRowBytes + 1)};
+        const f2 p11 = {tap_subnormal(ap + kInRowBytes + SP), tap_subnormal(ap + kInRowBytes + SP + 1)};
+        const f2 q00 = {tap_subnormal(ap + 2), 0.f}, q10 = {tap_subnormal(ap + SP + 2), 0.f};
+        const f2 q01 = {tap_subnormal(ap + kInRowBytes + 2), 0.f}, q11 = {tap_subnormal(ap + kInRowBytes + SP + 2), 0.f};
+        const f2 v01 = add2(add2(add2(mul2_unfusable(p00, w00, nz), mul2_unfusable(p10, w10, nz)), mul2_unfusable(p01, w01, nz)),
+                            mul2_unfusable(p11, w11, nz));
+        const f2 v2 = add2(add2(add2(mul2_unfusable(q00, w00, nz), mul2_unfusable(q10, w10, nz)), mul2_unfusable(q01, w01, nz)),
+                           mul2_unfusable(q11, w11, nz));
+        const f2 v[3] = {f2{v01.x, v2.y}, f2{v01.y, v2.y}, f2{v2.x, v2.y}};
+        uint32_t bx[3], by[3];
+        finish(v, bx, by);
+        put(out_s + olast, bx[0], bx[1], bx[2]);  // (an odd group is the last one)
+    };
+
+    // Row loop.  Per row: wait for its source rows, compute it into an output-row buffer, and then — in lane 0's one
+    // divergent stretch per row — send the row off with a bulk store, request the source rows of the row after next into
+    // the stage just read, and wait until the store of the previous row has finished reading the other buffer.
+    const uint32_t out_bytes = ow * ELT, out_bulk = out_bytes & ~15u;
+    uint8_t* gout = gdst;
+    for (uint32_t r = 0; r < nr; ++r, ++k, gout += dst_pitch) {
         const uint32_t s = k & 1u;
-        const AxisTap ay = ay_next;
-        const bool row_in = in_next;
-        issue(r + 1, s ^ 1u, r + 1 < nr, true);  // also: the store that read w.out(s) two rows ago is done with it
-        const bool ok = mbar_wait_bounded(w.bar(s), (k >> 1) & 1u);
-        if (__any_sync(0xffffffffu, !ok)) return false;  // (a convergence point for the whole warp, too)
+        const float wy0s = __shfl_sync(FULL, wy0_l, r), wy1s = __shfl_sync(FULL, wy1_l, r);
+        const uint32_t r0n = __shfl_sync(FULL, row0_l, (r + 2u) & 31u), r1n = __shfl_sync(FULL, row1_l, (r + 2u) & 31u);
+        const bool row_in = (in_mask >> r) & 1u;
+        bool ok = mbar_try_wait(w.bar(s), (k >> 1) & 1u);
+        if (!ok) ok = mbar_wait_bounded(w.bar(s), (k >> 1) & 1u);
+        if (__any_sync(FULL, !ok)) return false;  // (a convergence point for the whole warp, too)
         const uint32_t in_s = w.in(s), out_s = w.out(s);
         if (!row_in) {
             // a row above or below the image: background over the inside columns too
 #pragma unroll
             for (int j = 0; j < 8; ++j)
-                if (j < nj) put(out_s + ooff[j], bgbits[0], bgbits[1], bgbits[2]);
+                if (j < nj) put(out_s + ocol(j), bgbits[0], bgbits[1], bgbits[2]);
         } else {
-            if (replicate) {  // every lane writes the same three bytes (even lanes the first staged row, odd lanes the second)
+            if (replicate)
+            {  // every lane writes the same three bytes (even lanes the first staged row, odd lanes the second)
                 const uint32_t q = in_s + (lane & 1u) * kInRowBytes + rep_off;
                 const uint8_t c0 = smem_raw[q], c1 = smem_raw[q + 1], c2 = smem_raw[q + 2];
                 smem_raw[q + SP] = c0; smem_raw[q + SP + 1] = c1; smem_raw[q + SP + 2] = c2;
                 __syncwarp();
             }
-            const f2 wy0 = {__fmul_rn(ay.w0, kByteScale), __fmul_rn(ay.w0, kByteScale)};  // vertical weights, times 2^24
-            const f2 wy1 = {__fmul_rn(ay.w1, kByteScale), __fmul_rn(ay.w1, kByteScale)};
-            switch (npairs) {  // one uniform jump instead of a test per pair
+            const f2 wy0 = {wy0s, wy0s}, wy1 = {wy1s, wy1s};
+            switch (nj) {  // the odd group, if there is one ...
+            case 7: single(6, in_s, out_s, wy0, wy1); break;
+            case 5: single(4, in_s, out_s, wy0, wy1); break;
+            case 3: single(2, in_s, out_s, wy0, wy1); break;
+            case 1: single(0, in_s, out_s, wy0, wy1); break;
+            default: break;
+            }
+            switch (nj >> 1) {  // ... and the pairs: one uniform jump instead of a test per pair
             case 4: pair(6, in_s, out_s, wy0, wy1);
             case 3: pair(4, in_s, out_s, wy0, wy1);
             case 2: pair(2, in_s, out_s, wy0, wy1);
@@ -829,8 +940,27 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
             default: break;
             }
         }
-        if (PLANAR) store_row_planar(gdst + static_cast<size_t>(r) * dst_pitch, pl.dst_cstride, pl.dst_cstride2, out_s, ow * ELT, lane);
-        else store_row(gdst + static_cast<size_t>(r) * dst_pitch, out_s, ow * ELT, lane);
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+            if (out_bulk) {
+                bulk_store(gout, smem_raw + out_s, out_bulk);
+                if (PLANAR) {
+                    bulk_store(gout + pl.dst_cstride, smem_raw + out_s + kPlanarSegBytes, out_bulk);
+                    bulk_store(gout + pl.dst_cstride2, smem_raw + out_s + 2 * kPlanarSegBytes, out_bulk);
+                }
+            }
+            bulk_commit();
+            if (r + 2u < nr) load_rows(r + 2u, s, r0n, r1n);
+            bulk_wait_read_1();  // the store of the row before has read its buffer: the next row may be written there
+        }
+        if (out_bytes != out_bulk && lane < out_bytes - out_bulk) {  // rare: a row whose byte length is not a multiple of 16
+            gout[out_bulk + lane] = smem_raw[out_s + out_bulk + lane];
+            if (PLANAR) {
+                gout[pl.dst_cstride + out_bulk + lane] = smem_raw[out_s + kPlanarSegBytes + out_bulk + lane];
+                gout[pl.dst_cstride2 + out_bulk + lane] = smem_raw[out_s + 2 * kPlanarSegBytes + out_bulk + lane];
+            }
+        }
     }
     return true;
 }
@@ -858,33 +988,33 @@ __global__ void __launch_bounds__(kStagedThreads, 2) staged_kernel(const __grid_
     __syncwarp();
     const uint32_t warps_per_cta = blockDim.x >> 5;
     // Items are dealt in two ways.  Statically, item i runs on warp (i / gridDim.x) % warps_per_cta of CTA i % gridDim.x
-    // (a small launch spreads over all SMs).  With a work counter (launches of many more items than warps), a warp starts on
-    // the item of its own number and then claims further ones from the counter, so that warps whose items were cheap
-    // (small crops, letterbox rows) take more of them.  A claim is issued two items ahead: its latency, and that of the
-    // plane-record fetch that follows it, are hidden behind the items being processed.
+    // (a small launch spreads over all SMs).  With a work counter (launches of more than two items per warp), a warp takes
+    // its first two items that way and claims every further one from the counter, so that warps whose items were cheap
+    // (small crops, letterbox rows) take more of them.  A claim is issued one item before it is needed — the first one
+    // while the first item is processed — so neither its latency nor the crowd of warps that hit the counter when the
+    // kernel starts is on anybody's critical path.
     const uint32_t first = warp * gridDim.x + blockIdx.x, stride = gridDim.x * warps_per_cta;
     const bool dynamic = p.work != nullptr;
     const PlaneRec* table = plane_table(p);
     uint32_t k = 0, k4 = 0;  // steps done so far by RESIZE items (two stages) and by POINT items (four stages)
     bool ok = true;
-    // The plane record of the next item is fetched (12 lanes x 16 bytes, into registers) while the current item is
+    // The plane record of the next item is fetched (14 lanes x 16 bytes, into registers) while the current item is
     // processed, so its global-memory latency is off the critical path.
     constexpr uint32_t kRecLanes = sizeof(PlaneRec) / 16;
-    uint32_t local = 0, claim = 0;
+    uint32_t local = 0, claim = 0, round = 0;
     uint4 rec = make_uint4(0, 0, 0, 0);
     if (first < p.n_tiles) {
         const uint32_t z = tile_to_plane(p, first, local);
         if (lane < kRecLanes) rec = reinterpret_cast<const uint4*>(table + z)[lane];
     }
-    if (dynamic && first < p.n_tiles && lane == 0) claim = atomicAdd(p.work, 1u);
-    for (uint32_t item = first; item < p.n_tiles && ok;) {
+    for (uint32_t item = first; item < p.n_tiles && ok; ++round) {
         __syncwarp();
         if (lane < kRecLanes) reinterpret_cast<uint4*>(smem_raw + w.base + 48)[lane] = rec;
         __syncwarp();
         const uint32_t cur_local = local;
         uint32_t next_item = item + stride;
         if (dynamic) {
-            next_item = stride + __shfl_sync(0xffffffffu, claim, 0);  // the claim issued one item ago
+            if (round) next_item = 2u * stride + __shfl_sync(0xffffffffu, claim, 0);  // the claim issued one item ago
             if (lane == 0) claim = atomicAdd(p.work, 1u);
         }
         if (next_item < p.n_tiles) {
@@ -893,7 +1023,8 @@ __global__ void __launch_bounds__(kStagedThreads, 2) staged_kernel(const __grid_
         }
         item = next_item;
         const PlaneRec& pl = *w.pl;
-        const uint32_t tyi = cur_local / pl.tiles_x, txi = cur_local - tyi * pl.tiles_x;
+        uint32_t tyi = cur_local, txi = 0;  // (most planes are one segment wide: no division then)
+        if (pl.tiles_x != 1u) { tyi = cur_local / pl.tiles_x; txi = cur_local - tyi * pl.tiles_x; }
         const uint32_t ox = txi * pl.tile_w, oy0 = tyi * pl.tile_h;
         const uint32_t ow = min(pl.tile_w, pl.dst_w - ox), nr = min(pl.tile_h, pl.dst_h - oy0);
         const bool f32 = p.chains[pl.chain].dst_format == FKB_PIX_F32C3;
@@ -958,7 +1089,7 @@ __device__ __forceinline__ void pixel_tail(const LaunchParams& p, const PlaneRec
         if (k.kind & kPostDiv) v[c] = __fdiv_rn(v[c], d[c]);
         if (k.kind & kPostSat) v[c] = sat_u8_as_float(v[c]);
     }
-    uint8_t* row = pl.dst + static_cast<size_t>(y * pl.dst_pitch);
+    uint8_t* row = pl.dst + static_cast<size_t>(y) * pl.dst_pitch;
     if (k.split) {
 #pragma unroll
         for (int c = 0; c < 3; ++c) {

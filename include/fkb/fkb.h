@@ -74,8 +74,8 @@ enum { FKB_PIX_U8C3 = 1, FKB_PIX_F32C3 = 2, FKB_PIX_NV12 = 3,
         * fourth channel in place: VectorReorder<T,2,1,0,3>, color_conversion.h:472-476) and SaturateCast; the write is PACKED. */
        FKB_PIX_F32C4 = 7,
        /* Float sources: FKB_PIX_F32C3 as src_format is a packed float3 image or tensor plane (TensorRead<float3>,
-        * memory_operations.h:243-262); FKB_PIX_F32P3 is three float planes, channel c at src + c * (src_chroma - src)
-        * (TensorPack / TensorTPack, memory_operations.h:264-330).  They feed chains that start in float: the copy sequence
+        * memory_operations.h:124-157); FKB_PIX_F32P3 is three float planes, channel c at src + c * (src_chroma - src)
+        * (TensorPack, memory_operations.h:243-290; TensorTPack, :292-335).  They feed chains that start in float: the copy sequence
         * of CircularTensor::update (core/data/circular_tensor.h:111-161) is such a chain without ops. */
        FKB_PIX_F32P3 = 8,
        /* 10-bit YCbCr sources of ReadYUV, 16-bit containers read as they are stored (color_conversion.h:219-238, 255-265):
@@ -219,7 +219,11 @@ int fkb_validate(const fkb_chain_desc* chains, uint32_t n_chains,
 /* One fused launch of `chain` over n_planes planes (plane z uses planes[z]); replaces
  * executeOperations<TransformDPP<>> (executors.h:316-351).  `planes` is a host array, copied before the
  * call returns.  Asynchronous on `cuda_stream` (a cudaStream_t; null = legacy default stream), on the
- * current device; the caller keeps src/dst alive until the stream has run the work. */
+ * current device; the caller keeps src/dst alive until the stream has run the work.
+ * Stream capture: a launch of at most 8 planes carries its plane records in the kernel parameters and can be recorded
+ * into a CUDA graph like any kernel launch.  A larger launch stages its records through buffers the library reuses from
+ * call to call, which a recorded graph would read again at every replay; on a capturing stream such a launch returns
+ * FKB_ERR_UNSUPPORTED and records nothing.  To put a large launch into a graph, create a plan and record fkb_plan_launch. */
 int fkb_launch_transform(const fkb_chain_desc* chain, const fkb_plane_desc* planes,
                          uint32_t n_planes, void* cuda_stream);
 
@@ -234,7 +238,12 @@ int fkb_launch_transform(const fkb_chain_desc* chain, const fkb_plane_desc* plan
  *   - Cost: FKB_NOALLOC_MAX_PLANES * 224 bytes (896 KB) of device memory on each GPU that loads the library, and the
  *     same again in host memory, until the process exits, whether or not this entry point is ever called.
  *   - The first call on a device looks up the array's device address (one cudaGetSymbolAddress, with that device
- *     current).  Make that first call before any stream capture begins.
+ *     current), and the first launch of each kernel lets the CUDA runtime load that kernel, which may allocate inside
+ *     the driver.  Make one warm-up call per chain shape you will use before the window in which nothing may allocate,
+ *     and before any stream capture begins.
+ *   - On a capturing stream the call returns FKB_ERR_UNSUPPORTED (its copy of the records out of the shared host array
+ *     cannot be replayed).
+ *   - Planes of a conditional batch read (FKB_PLANE_DEFAULT) are accepted, as by fkb_launch_transform.
  *   - All calls share the one array.  A call overwrites every record it uses, so nothing has to be cleared, but two
  *     calls whose GPU work can overlap (different streams, no dependency between them) race on it: keep calls to this
  *     entry point ordered on the GPU, or use fkb_launch_transform / a plan for concurrent launches.
@@ -249,8 +258,10 @@ int fkb_launch_divergent(const fkb_chain_desc* chains, uint32_t n_chains,
                          const fkb_plane_desc* planes, uint32_t n_planes, void* cuda_stream);
 
 /* A plan keeps the lowered launch (descriptor table, tile schedule) resident on the device so that a
- * pipeline that repeats the same launch pays the lowering once.  fkb_plan_launch is asynchronous.
- * The reference rebuilds its IOps on every call (executors.h:53-58); a plan is the same launch, cached. */
+ * pipeline that repeats the same launch pays the lowering once.  fkb_plan_launch is asynchronous and may be recorded
+ * into a CUDA graph.  The reference rebuilds its IOps on every call (executors.h:53-58); a plan is the same launch, cached.
+ * Launches of one plan may overlap on the GPU (different streams): each takes its own pair of work counters from a ring
+ * of 64, so up to 64 launches of one plan can be in flight at a time.  They all write the same destination buffers. */
 typedef struct fkb_plan fkb_plan;
 int fkb_plan_create(const fkb_chain_desc* chains, uint32_t n_chains,
                     const fkb_plane_desc* planes, uint32_t n_planes, fkb_plan** out);

@@ -1,7 +1,7 @@
 """Runs a few launches of one workload so that a profiler can capture them:
 
-    python -m fusedkernellibrary_b200.profile_case batched_crop_resize --frames 8 --launches 4
-    python -m fusedkernellibrary_b200.profile_case vertical_fusion --sets 4 --launches 8
+    python profile_case.py batched_crop_resize --frames 8 --launches 4
+    python profile_case.py vertical_fusion --sets 4 --launches 8
 
 The case is kept small (a few hundred MB on the device, but more than the 126 MB L2) so that a multi-pass capture
 ends by itself quickly.  Prints the CUDA-event time per launch of the un-profiled run.
@@ -12,7 +12,11 @@ import argparse
 
 import torch
 
-from . import runtime, workloads as W
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from fusedkernellibrary_b200 import runtime, workloads as W  # noqa: E402
 
 
 # workloads beside the five configurations that have a profile of their own

@@ -1,6 +1,7 @@
 """Compiles tests/cpp/frontend_test.cpp — a program written against the fk:: front end (include/fused_kernel/) — with
-g++ (C++20) and links it to lib/libfkb.so, the CUDA runtime and the CPU checker.  It doubles as the build check of the
-header-only front end.  Run as ``python -m fusedkernellibrary_b200.frontend_build``; no GPU is needed to build.
+g++ (C++20) and links it to lib/libfkb.so, the CUDA runtime and the CPU checker (test infrastructure: the checker is
+linked into this test program only).  It doubles as the build check of the header-only front end.  Run as
+``python tests/frontend_build.py``; no GPU is needed to build.
 """
 from __future__ import annotations
 
@@ -8,8 +9,7 @@ import os
 import subprocess
 import sys
 
-HERE = os.path.dirname(os.path.abspath(__file__))
-ROOT = os.path.dirname(HERE)
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 SRC = os.path.join(ROOT, "tests", "cpp", "frontend_test.cpp")
 OUT = os.path.join(ROOT, "tests", "cpp", "frontend_test")
 CUDA = os.environ.get("CUDA_HOME", "/usr/local/cuda")
@@ -28,7 +28,7 @@ def needs_build() -> bool:
 def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not needs_build():
         return OUT
-    lib_dir, oracle_dir = os.path.join(HERE, "lib"), os.path.join(ROOT, "oracle")
+    lib_dir, oracle_dir = os.path.join(ROOT, "fusedkernellibrary_b200", "lib"), os.path.join(ROOT, "oracle")
     cmd = ["g++", "-std=c++20", "-O1", "-Wall", "-Wno-unused-function", "-I", os.path.join(ROOT, "include"),
            "-I", os.path.join(CUDA, "include"), SRC, "-o", OUT,
            "-L", lib_dir, "-lfkb", "-L", oracle_dir, "-loracle", "-L", os.path.join(CUDA, "lib64"), "-lcudart",

@@ -31,7 +31,7 @@ def syntax_check(body: str):
 
 
 def test_frontend_program_builds():
-    from fusedkernellibrary_b200 import frontend_build
+    import frontend_build
     assert os.path.exists(frontend_build.build())
 
 
@@ -61,7 +61,7 @@ def test_ill_typed_chains_are_compile_errors(body, needle):
 
 @pytest.mark.gpu
 def test_frontend_pipelines_match_oracle_on_gpu():
-    from fusedkernellibrary_b200 import frontend_build
+    import frontend_build
     exe = frontend_build.build()
     r = subprocess.run([exe], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and "ALL PASSED" in r.stdout, r.stdout + r.stderr

@@ -5,9 +5,12 @@
 
 A step is one fused launch of the batched crop -> resize -> normalise workload (64 frames of 1920x1080 uchar3,
 32 random crops per frame, each resized with preserved aspect ratio to 224x224 on a (114,114,114) background, times
-1/255, written as a 224x224x2048 float3 tensor).  With N > 1 (one process per GPU under torch.distributed.run) every
-rank runs that workload on its own frames — no exchange between GPUs — and the value is the pixels of all ranks
-divided by the slowest rank's device time.  Rank 0 prints one JSON line.
+1/255, written as a 224x224x2048 float3 tensor).  With N > 1 (one process per GPU under torch.distributed.run) the
+headline is weak scaling: every rank runs a whole 64-frame job of its own — N independent jobs, no exchange between
+GPUs — and the value is the pixels of all ranks divided by the slowest rank's device time.  The same line also carries,
+inside ``roofline``, the split the workload description names — ONE 64-frame batch divided by frame over the N GPUs
+(``strong_split``) — and the divergent 8-plane launch with its planes dealt over the GPUs (``config5_sharded``), each
+with its efficiency against one GPU of the same run.  Rank 0 prints one JSON line.
 
 ``--impl reference`` times the reference library's own CPU backend (compiled from its headers into
 oracle/_ref/libfkl_ref.so; when that file is absent, the CPU restatement in oracle/) on the host cores, on a bounded
@@ -29,10 +32,21 @@ METRIC = "fused-pipeline output Gpix/s"
 UNIT = "Gpix/s"
 N_FRAMES, CROPS_PER_FRAME = 64, 32
 FALLBACK_HBM_GBS = 6650.0
-# DRAM bytes of one staged_kernel launch of the 64-frame workload: dram__bytes_read.sum + dram__bytes_write.sum of one ncu
-# capture of the full-size launch (259.25 MB read + 1 179.92 MB written; profiles/staged_kernel_batched_crop_resize.md),
-# against 1 436.77 MB of algorithmic bytes.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = int(259.252224e6 + 1179.918e6)
+PROFILE_SUMMARY = os.path.join(ROOT, "profiles", "staged_kernel_batched_crop_resize.md")
+
+
+def profiled_traffic(planes: int):
+    """DRAM bytes of one staged_kernel launch, from the committed ncu summary (its line `dram_bytes_per_plane: N`, measured
+    once under ncu, not in this run), scaled to `planes` planes.  Returns (bytes or None, where the figure comes from)."""
+    try:
+        with open(PROFILE_SUMMARY) as f:
+            for line in f:
+                if line.strip().startswith("dram_bytes_per_plane:"):
+                    per_plane = float(line.split(":", 1)[1].split()[0])
+                    return int(per_plane * planes), "profiles/staged_kernel_batched_crop_resize.md (one ncu capture, scaled by planes)"
+    except OSError:
+        pass
+    return None, "no committed ncu summary found"
 
 
 def make_workload(rank: int, n_frames: int = N_FRAMES, frame_w: int = 1920, frame_h: int = 1080):
@@ -49,25 +63,22 @@ def shard_workload(rank: int, world: int, scaling: str, n_frames: int = N_FRAMES
     from fusedkernellibrary_b200 import workloads as W
     if scaling == "weak":
         return make_workload(rank, n_frames, frame_w, frame_h), n_frames
-    frames = max(1, n_frames // world)
-    wl = make_workload(0, n_frames, frame_w, frame_h)
-    lo = rank * frames * CROPS_PER_FRAME
-    keep = wl.planes[lo: lo + frames * CROPS_PER_FRAME]
-    base_src = keep[0].src
-    plane_bytes = keep[0].dst_w * keep[0].dst_h * 12
-    planes = [W.PlaneSpec(**{**p.__dict__, "src": p.src - base_src, "dst_offset": i * plane_bytes}) for i, p in enumerate(keep)]
-    shard = W.Workload(wl.name, wl.chains, wl.sources[base_src: base_src + frames], [len(planes) * plane_bytes], planes,
-                       extra={"n_frames": frames, "crops_per_frame": CROPS_PER_FRAME})
-    return shard, frames
+    shard = W.shard_by_frame(make_workload(0, n_frames, frame_w, frame_h), rank, world)
+    return shard, len(shard.sources)
 
 
 def workload_config(n_gpus: int, scaling: str, frames_per_gpu: int) -> dict:
+    if scaling == "weak":
+        sharding = (f"weak scaling: {n_gpus} independent {frames_per_gpu}-frame job(s), one per GPU, each on its own seeded frames; "
+                    "no collective; the split of ONE 64-frame batch by frame is reported in roofline.strong_split")
+    else:
+        sharding = f"strong scaling: one {N_FRAMES}-frame batch split by frame over {n_gpus} GPU(s), {frames_per_gpu} frames each; no collective"
     return {
         "workload": "batched_crop_resize = BASELINE configs[3]: 1920x1080 uchar3 frames, 32 random crops each "
                     "(w,h in 16..512, clipped), Resize INTER_LINEAR PRESERVE_AR to 224x224 bg (114,114,114), Mul 1/255, "
                     "float3 tensor 224x224xplanes",
         "frames_per_gpu": frames_per_gpu, "crops_per_frame": CROPS_PER_FRAME, "planes_per_gpu": frames_per_gpu * CROPS_PER_FRAME,
-        "sharding": f"by frame over {n_gpus} GPU(s), each GPU owns its frames and its slice of the output, no collective",
+        "sharding": sharding,
         "l2": "inputs + outputs per launch (1.6 GB per GPU at 64 frames) exceed the 126 MB L2; no flush needed",
         "timing": "the K launches are captured into one CUDA graph and replayed between two CUDA events (device time, "
                   "max over ranks); --stream-launches submits them one by one instead",
@@ -311,6 +322,131 @@ def reference_cuda_main(torch, wl, dw, steps: int, our_ms: float) -> dict:
             "note": "reference templated kernel, nvcc 12.9 sm_100a, 256 planes per launch (kernel-parameter limit)"}
 
 
+def timed_plan_launches(sets, rounds: int, torch, barrier=None, stretch_s: float = 0.15) -> float:
+    """Seconds per launch of the plans of `sets` (DeviceWorkloads rotated so that every launch reads HBM): `rounds` rounds
+    over the sets are captured into one CUDA graph; after `barrier` every rank first replays it for `stretch_s` (clocks up),
+    then one replay is timed with CUDA events."""
+    for s in sets:
+        s.plan()
+    for _ in range(3):
+        for s in sets:
+            s.launch_plan()
+    torch.cuda.synchronize()
+    graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(rounds):
+                for s in sets:
+                    s.launch_plan()
+    graph.replay()
+    torch.cuda.synchronize()
+    if barrier is not None:
+        barrier()
+    t_end = time.perf_counter() + stretch_s
+    while time.perf_counter() < t_end:
+        graph.replay()
+        torch.cuda.synchronize()
+    dt = sorted(time_launches(graph.replay, 1, torch) for _ in range(3))[1]
+    del graph
+    return dt / (rounds * len(sets))
+
+
+def rotating_sets(wl, runtime, target_bytes: float = 300e6, max_sets: int = 8):
+    """Enough independent copies of a workload's buffers that one round over them moves more bytes than the L2 holds."""
+    touched = max(1, wl.algorithmic_bytes()["total"])
+    n = max(1, min(max_sets, int(target_bytes // touched) + 1))
+    return [runtime.DeviceWorkload(wl, poison=None) for _ in range(n)]
+
+
+def gather_max(value: float, torch, dist, world: int):
+    """(max over ranks, list by rank) of a per-rank float."""
+    if world == 1:
+        return value, [value]
+    t = torch.tensor([value], device="cuda", dtype=torch.float64)
+    every = [torch.zeros_like(t) for _ in range(world)]
+    dist.all_gather(every, t)
+    vals = [float(e.item()) for e in every]
+    return max(vals), vals
+
+
+def strong_split(rank: int, world: int, steps: int, t1_ms: float, torch, dist) -> dict:
+    """ONE 64-frame batch divided by frame over the ranks (what the workload description asks of 2, 4 and 8 GPUs): every
+    rank runs its 64 / world frames; time = the slowest rank's; efficiency against one GPU doing all 64 frames in this
+    same run (t1_ms, the mean of the ranks' full-job times)."""
+    from fusedkernellibrary_b200 import runtime, workloads as W
+    shard = W.shard_by_frame(make_workload(0), rank, world)
+    sets = rotating_sets(shard, runtime)
+    sec = timed_plan_launches(sets, max(5, steps), torch, barrier=dist.barrier)
+    for s in sets:
+        s.close()
+    t_max, by_rank = gather_max(sec * 1e3, torch, dist, world)
+    total_px = N_FRAMES * CROPS_PER_FRAME * 224 * 224
+    return {"what": f"one {N_FRAMES}-frame batch split by frame, {N_FRAMES // world} frames ({N_FRAMES // world * CROPS_PER_FRAME} planes) per GPU",
+            "ms_per_step": t_max, "ms_per_step_by_rank": by_rank, "gpix_s": total_px / (t_max / 1e3) / 1e9,
+            "one_gpu_ms_same_run": t1_ms, "speedup_vs_one_gpu": t1_ms / t_max, "efficiency": t1_ms / (world * t_max),
+            "buffer_sets_rotated": len(sets)}
+
+
+def config5_sharded(rank: int, world: int, steps: int, peak: float, torch, dist) -> dict:
+    """The divergent 8-plane launch (BASELINE configs[4]) with its planes dealt over the ranks, plane z to rank z % world, so
+    that resize planes and arithmetic planes are spread evenly.  Rank 0 also times the whole launch on its one GPU."""
+    from fusedkernellibrary_b200 import runtime, workloads as W
+    wl = W.divergent_planes()
+    shard = W.shard_by_plane(wl, rank, world)
+    sets = rotating_sets(shard, runtime)
+    sec = timed_plan_launches(sets, max(5, steps), torch, barrier=dist.barrier)
+    for s in sets:
+        s.close()
+    del sets
+    torch.cuda.empty_cache()
+    t_max, by_rank = gather_max(sec * 1e3, torch, dist, world)
+    t1 = 0.0
+    if rank == 0:
+        whole = rotating_sets(wl, runtime)
+        t1 = timed_plan_launches(whole, max(5, steps), torch) * 1e3
+        for s in whole:
+            s.close()
+    t1, _ = gather_max(t1, torch, dist, world)
+    per_plane = [W.shard_by_plane(wl, z, len(wl.planes)).algorithmic_bytes()["total"] for z in range(len(wl.planes))]
+    heaviest = max(sum(per_plane[z] for z in part) for part in W.plane_partition(len(wl.planes), world))
+    total = wl.algorithmic_bytes()["total"]
+    return {"what": f"8 planes dealt over {world} GPUs (plane z on rank z % {world})", "ms_per_step": t_max, "ms_per_step_by_rank": by_rank,
+            "gpix_s": wl.out_pixels / (t_max / 1e3) / 1e9, "one_gpu_ms_same_run": t1, "speedup_vs_one_gpu": t1 / t_max,
+            "ideal_speedup_cap": total / heaviest, "fraction_of_cap": (t1 / t_max) / (total / heaviest),
+            "heaviest_rank_hbm_gbs": heaviest / (t_max / 1e3) / 1e9, "heaviest_rank_frac_of_peak": heaviest / (t_max / 1e3) / 1e9 / peak}
+
+
+def host_cost(dw, lib, abi, torch) -> dict:
+    """Synchronous host time of one launch of the 2048-plane workload with host descriptors, the GPU idle before every
+    call: fkb_launch_transform through ctypes, and fk::executeOperations through the C++ front end (bench_frontend.cpp)."""
+    import subprocess
+    out = {}
+    stream = torch.cuda.current_stream().cuda_stream
+    ts = []
+    for i in range(25):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        rc = lib.fkb_launch_transform(dw.chains, dw.planes, dw.n_planes, stream)
+        t1 = time.perf_counter()
+        abi.check(rc)
+        if i >= 5:
+            ts.append((t1 - t0) * 1e6)
+    torch.cuda.synchronize()
+    ts.sort()
+    out["fkb_launch_transform_us"] = {"median": ts[len(ts) // 2], "min": ts[0], "planes": dw.n_planes, "via": "ctypes"}
+    exe = os.path.join(ROOT, "fusedkernellibrary_b200", "lib", "bench_frontend")
+    if os.path.exists(exe):
+        try:
+            r = subprocess.run([exe, "30"], capture_output=True, text=True, timeout=120)
+            out["fk_executeOperations_us"] = json.loads(r.stdout.strip().splitlines()[-1])
+        except Exception as exc:
+            out["fk_executeOperations_us"] = {"error": str(exc)}
+    else:
+        out["fk_executeOperations_us"] = {"error": "bench_frontend was not built"}
+    out["reference_quotes_us_per_call"] = "19-70 (.github/skills/fkl-language-bindings/SKILL.md:90)"
+    return out
+
+
 def our_arm(args) -> None:
     import torch
     import torch.distributed as dist
@@ -436,54 +572,101 @@ def our_arm(args) -> None:
         for st in (s_up, s_run, s_down):
             cur.wait_stream(st)
 
+    # the same copies without any kernel: what the host <-> device link of this box gives the step at best
+    def copy_only_step():
+        cur = torch.cuda.current_stream()
+        for st in (s_up, s_down):
+            st.wait_stream(cur)
+        for g, (lo, hi, arr) in enumerate(sub_planes):
+            with torch.cuda.stream(s_up):
+                for f in range(g * group, min((g + 1) * group, len(h_src))):
+                    dw.src[f].copy_(h_src[f], non_blocking=True)
+            with torch.cuda.stream(s_down):
+                h_out[lo * plane_bytes: hi * plane_bytes].copy_(dw.out[0][lo * plane_bytes: hi * plane_bytes], non_blocking=True)
+        for st in (s_up, s_down):
+            cur.wait_stream(st)
+
     e2e_steps = max(2, min(args.steps, 10))
     for _ in range(2):
         e2e_step()
     if world > 1:
         dist.barrier()
     e2e_dt = time_launches(e2e_step, e2e_steps, torch)
+    e2e_dt, _ = gather_max(e2e_dt, torch, dist, world)
+    for _ in range(2):
+        copy_only_step()
     if world > 1:
-        t = torch.tensor([e2e_dt], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_dt = float(t.item())
+        dist.barrier()
+    copy_dt = time_launches(copy_only_step, e2e_steps, torch)
+    copy_dt, _ = gather_max(copy_dt, torch, dist, world)
     e2e_value = total_pixels / (e2e_dt / e2e_steps) / 1e9
-    h2d = sum(s.nbytes for s in wl.sources) + dw.n_planes * 192
+    h2d = sum(s.nbytes for s in wl.sources) + dw.n_planes * 224  # frames + one 224-byte plane record per plane
     d2h = wl.out_sizes[0]
 
+    traffic, traffic_src = profiled_traffic(dw.n_planes)
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": traffic, "traffic_source": traffic_src, "peak_source": peak_src, "kernel": "fkb::staged_kernel",
+                "algorithmic_bytes_per_launch": alg["total"], "frac_of_nominal_8TBs": achieved / 8000.0}
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "f32",
         "data": "synthetic", "config": workload_config(world, args.scaling, frames), "ms_per_step_by_rank": per_rank_ms,
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_source": peak_src, "kernel": "fkb::staged_kernel",
-                     "algorithmic_bytes_per_launch": alg["total"], "frac_of_nominal_8TBs": achieved / 8000.0},
+        "roofline": roofline,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_dt / e2e_steps * 1e3, "steps": e2e_steps,
+                "copy_bound_ms": copy_dt / e2e_steps * 1e3, "frac_of_copy_bound": copy_dt / e2e_dt,
+                "copy_bound_gbs_per_gpu": (h2d + d2h) / (copy_dt / e2e_steps) / 1e9,
+                "copy_bound": "the same pinned host <-> device copies on the same streams without any kernel, slowest rank: "
+                              "the step cannot be faster than this on this box",
                 "path": "per group of 4 frames on three streams: pinned host frames -> device, fkb_launch_transform (host "
                         "descriptors) over the group's planes, its planes of the float3 tensor -> pinned host"},
         "gpu_launches": args.steps * kernels_per_step,
         "clocks": clocks,
     }
+    if world > 1 and args.scaling == "weak" and not args.no_other_configs:
+        # the splits of ONE job the workload descriptions name, beside the weak-scaling headline
+        dw.close()
+        del dw, h_src, h_out
+        torch.cuda.empty_cache()
+        t1_ms = sum(per_rank_ms) / len(per_rank_ms)
+        roofline["strong_split"] = strong_split(rank, world, min(args.steps, 20), t1_ms, torch, dist)
+        roofline["config5_sharded"] = config5_sharded(rank, world, min(args.steps, 20), peak, torch, dist)
     if rank == 0 and world == 1:
+        roofline["host_cost"] = host_cost(dw, lib, abi, torch)
         if not args.no_cpu_baseline:
             threads = host_threads()
             sample_frames = 16
             best, px, kind = cpu_time_sample(sample_frames, threads, repeats=3)
+            one, px1, _ = cpu_time_sample(2, 1, repeats=2)
             line["cpu_baseline"] = {"value": px / best / 1e9, "unit": UNIT, "cores": threads, "kind": kind,
                                     "sample": f"{sample_frames} of the 64 frames ({sample_frames * CROPS_PER_FRAME} planes), best of 3, "
-                                              f"planes spread over {threads} host threads as independent single-threaded reference calls"}
-        line["reference_cuda_backend"] = reference_cuda_main(torch, wl, dw, max(5, min(args.steps, 20)), ms_per_step)
+                                              f"planes spread over {threads} host threads as independent single-threaded reference calls",
+                                    "one_thread": {"value": px1 / one / 1e9, "unit": UNIT, "cores": 1,
+                                                   "sample": "2 of the 64 frames (64 planes), best of 2: the backend as shipped (single-threaded)"}}
+        ref_cuda = reference_cuda_main(torch, wl, dw, max(5, min(args.steps, 20)), ms_per_step)
+        roofline["reference_cuda_backend"] = ref_cuda
         if not args.no_other_configs:
             dw.close()
             del dw
             torch.cuda.empty_cache()
-            line["other_configs"] = other_configs(torch, max(10, min(args.steps, 50)), peak)
-            line["widened_rows"] = other_configs(torch, max(10, min(args.steps, 50)), peak, widened=True)
+            steps_small = max(10, min(args.steps, 50))
+            roofline["by_config"] = compact(other_configs(torch, steps_small, peak))
+            roofline["by_config"]["batched_crop_resize"] = {"us": ms_per_step * 1e3, "ref_cuda_us": ref_cuda.get("ms_per_step", 0) * 1e3 or None,
+                                                            "frac": achieved / peak, "gbs": achieved, "kernels": kernels_per_step}
+            roofline["widened_rows"] = compact(other_configs(torch, steps_small, peak, widened=True))
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def compact(configs: dict) -> dict:
+    """The per-configuration figures in the few keys that matter (they travel inside `roofline`)."""
+    return {name: {"us": round(v["us_per_launch"], 3), "ref_cuda_us": (round(v["reference_cuda_us_per_launch"], 3)
+                                                                         if isinstance(v["reference_cuda_us_per_launch"], float) else v["reference_cuda_us_per_launch"]),
+                   "frac": round(v["frac_of_measured_peak"], 4), "gbs": round(v["hbm_gbs"], 1), "gpix_s": round(v["gpix_s"], 2),
+                   "kernels": v["kernels_per_launch"]} for name, v in configs.items()}
 
 
 def main() -> None:

@@ -45,6 +45,24 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return OUT
 
 
+def build_frontend_bench(force: bool = False) -> str:
+    """Compiles bench_frontend.cpp (the host-cost measurement bench.py runs: a program written against the fk:: front
+    end, linked to libfkb.so and the CUDA runtime only) into lib/bench_frontend."""
+    src = os.path.join(ROOT, "bench_frontend.cpp")
+    out = os.path.join(OUT_DIR, "bench_frontend")
+    if not force and os.path.exists(out) and os.path.getmtime(out) > max(os.path.getmtime(src), os.path.getmtime(OUT)):
+        return out
+    cuda = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    cmd = ["g++", "-std=c++20", "-O2", "-I", os.path.join(ROOT, "include"), "-I", os.path.join(cuda, "include"), src, "-o", out,
+           "-L", OUT_DIR, "-lfkb", "-L", os.path.join(cuda, "lib64"), "-lcudart", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + os.path.join(cuda, "lib64")]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        sys.stderr.write(res.stdout + res.stderr)
+        raise RuntimeError("g++ failed building bench_frontend")
+    return out
+
+
 if __name__ == "__main__":
     build(force=True, verbose=True)
     print(OUT)
+    print(build_frontend_bench(force=True))

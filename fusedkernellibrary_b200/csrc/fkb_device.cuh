@@ -91,6 +91,9 @@ struct LaunchParams {
     PostImm post_imm[FKB_MAX_CHAINS];
     Nv12Consts nv12;  // per chain: bit mask of {Mul, Add|Sub, SaturateCast} when its post-ops have that shape, else 8
     float neg_zero;           // -0.0f, deliberately opaque to the compiler (see mul2_unfusable)
+    uint32_t test_extra_tx;   // 0 in every real launch; a test sets it so that staged_kernel's loads announce bytes that never
+                              // arrive and its bounded waits run out (the FKB_ERR_DEVICE_WAIT path)
+    uint32_t wait_limit_ns;   // how long a device-side wait for a bulk copy may last before the kernel gives up (one second)
     PlaneRec inline_planes[kInlinePlanes];
 };
 
@@ -117,11 +120,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-// Waits for a phase with an iteration cap.  Returns false when the cap ran out (a lowering bug: the expected
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// Waits for a phase, but not for ever: gives up after `limit_ns` nanoseconds (LaunchParams::wait_limit_ns, one second in
+// every real launch) or 2^26 polls, whichever comes first.  Returns false when it gave up (a lowering bug: the expected
 // byte count never arrived); the caller records it in the status word and leaves without touching the data.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
-    for (uint32_t i = 0; i < (1u << 22); ++i)
-        if (mbar_try_wait(bar, parity)) return true;
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t limit_ns) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    for (uint32_t round = 0; round < (1u << 20); ++round) {
+        for (uint32_t i = 0; i < 64; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (global_timer_ns() - t0 > limit_ns) return false;
+    }
     return false;
 }
 // global -> shared bulk copy (the TMA engine, no tensor map, no multicast); completion is signalled on `bar`.

@@ -185,11 +185,14 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 //   FKB_FORCE_GATHER=1       routes every plane through gather_kernel, which lets the kernel paths check each other;
 //   FKB_TINY_PIXELS=n        launches below n output pixels take the one-pixel-per-thread kernels (0 switches that off,
 //                            which the tests use to drive small cases through the pipelined kernels);
-//   FKB_ROWS_PER_ITEM=n      output rows per item of the staged kernel (default: chosen from the launch size).
+//   FKB_ROWS_PER_ITEM=n      output rows per item of the staged kernel (default: chosen from the launch size);
+//   FKB_TEST_EXTRA_TX=n      test hook: the staged kernel's resize loads announce n bytes more than they deliver, so its
+//                            bounded waits run out and the launch ends with FKB_ERR_DEVICE_WAIT in the status word;
+//   FKB_WAIT_LIMIT_US=n      how long such a wait lasts before it gives up (default one second).
 struct Tuning {
     bool force_gather = false;
     uint64_t tiny_pixels = kTinyLaunchPixels;
-    uint32_t rows_per_item = 0;
+    uint32_t rows_per_item = 0, test_extra_tx = 0, wait_limit_ns = 1000000000u;
 };
 Tuning read_tuning() {
     Tuning t;
@@ -197,6 +200,8 @@ Tuning read_tuning() {
     t.force_gather = e && e[0] == '1';
     if ((e = std::getenv("FKB_TINY_PIXELS")) && e[0]) t.tiny_pixels = std::strtoull(e, nullptr, 10);
     if ((e = std::getenv("FKB_ROWS_PER_ITEM")) && e[0]) t.rows_per_item = static_cast<uint32_t>(std::strtoul(e, nullptr, 10));
+    if ((e = std::getenv("FKB_TEST_EXTRA_TX")) && e[0]) t.test_extra_tx = static_cast<uint32_t>(std::strtoul(e, nullptr, 10));
+    if ((e = std::getenv("FKB_WAIT_LIMIT_US")) && e[0]) t.wait_limit_ns = static_cast<uint32_t>(std::min<unsigned long>(std::strtoul(e, nullptr, 10), 4000000ul) * 1000ul);
     return t;
 }
 
@@ -515,6 +520,8 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
     }
     L.lp.n_planes = n_planes;
     L.lp.neg_zero = -0.0f;
+    L.lp.test_extra_tx = tune.test_extra_tx;
+    L.lp.wait_limit_ns = tune.wait_limit_ns;
     for (uint32_t c = 0; c < n_chains; ++c) {
         L.lp.post_kind[c] = post_kind_of(chains[c]);
         L.lp.post_imm[c] = post_imm_of(chains[c]);
@@ -681,37 +688,55 @@ int refuse_if_capturing(cudaStream_t stream) {
 int launch_once(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc* planes, uint32_t n_planes,
                 cudaStream_t stream) {
     Lowered L;
-    int rc = lower(chains, n_chains, planes, n_planes, L);
-    if (rc != FKB_OK) return rc;
-    const bool inline_planes = n_planes <= kInlinePlanes, counter = wants_work_counter(L);
-    if (inline_planes) {
-        std::memcpy(L.lp.inline_planes, L.recs, sizeof(PlaneRec) * n_planes);
+    int rc;
+    if (n_planes <= kInlinePlanes) {
+        // a few planes: the records are lowered on the stack and travel in the kernel parameters
+        PlaneRec local[kInlinePlanes];
+        L.recs = local;
+        if ((rc = lower(chains, n_chains, planes, n_planes, L)) != FKB_OK) return rc;
+        std::memcpy(L.lp.inline_planes, local, sizeof(PlaneRec) * n_planes);
+        L.recs = nullptr;
         L.lp.table = nullptr;
-        if (!counter) return run(L, L.lp, stream);
+        if (!wants_work_counter(L)) return run(L, L.lp, stream);
+        // (a few planes large enough for the kernel to claim its items: a slot of the arena lends its pair of counters)
+        if ((rc = refuse_if_capturing(stream)) != FKB_OK) return rc;
+        Arena& a = arena_for_current_device(rc);
+        if (rc != FKB_OK) return rc;
+        std::lock_guard<std::mutex> g(a.m);
+        if ((rc = a.ensure(1)) != FKB_OK) return rc;
+        const int slot = a.next;
+        a.next = (a.next + 1) % Arena::kSlots;
+        if (a.used[slot]) { FKB_CUDA(cudaEventSynchronize(a.ev[slot])); a.used[slot] = false; }
+        L.lp.work = a.work + 2 * slot;
+        if ((rc = run(L, L.lp, stream)) != FKB_OK) return rc;
+        FKB_CUDA(cudaEventRecord(a.ev[slot], stream));
+        a.used[slot] = true;
+        return FKB_OK;
     }
+    // Many planes: the records are lowered straight into a pinned slot of the arena (no intermediate array, no second
+    // copy) and uploaded from there; the slot also lends the launch its pair of item counters.
+    if (planes == nullptr || chains == nullptr) return FKB_ERR_NULL;
     if ((rc = refuse_if_capturing(stream)) != FKB_OK) return rc;
-    // a slot of the arena: its part of the device table (launches of many planes) and its pair of item counters
     Arena& a = arena_for_current_device(rc);
     if (rc != FKB_OK) return rc;
     std::lock_guard<std::mutex> g(a.m);
-    const size_t bytes = inline_planes ? 1 : sizeof(PlaneRec) * n_planes;
+    const size_t bytes = sizeof(PlaneRec) * n_planes;
     if ((rc = a.ensure(bytes)) != FKB_OK) return rc;
     const int slot = a.next;
-    a.next = (a.next + 1) % Arena::kSlots;
     if (a.used[slot]) { FKB_CUDA(cudaEventSynchronize(a.ev[slot])); a.used[slot] = false; }
-    if (!inline_planes) {
-        uint8_t* h = a.pinned + static_cast<size_t>(slot) * a.slot_bytes;
-        uint8_t* d = a.dev + static_cast<size_t>(slot) * a.slot_bytes;
-        std::memcpy(h, L.recs, bytes);
-        FKB_CUDA(cudaMemcpyAsync(d, h, bytes, cudaMemcpyHostToDevice, stream));
-        L.lp.table = reinterpret_cast<const PlaneRec*>(d);
-    }
-    if (counter) L.lp.work = a.work + 2 * slot;
+    uint8_t* h = a.pinned + static_cast<size_t>(slot) * a.slot_bytes;
+    uint8_t* d = a.dev + static_cast<size_t>(slot) * a.slot_bytes;
+    L.recs = reinterpret_cast<PlaneRec*>(h);
+    if ((rc = lower(chains, n_chains, planes, n_planes, L)) != FKB_OK) return rc;  // (the slot stays free)
+    a.next = (a.next + 1) % Arena::kSlots;
+    FKB_CUDA(cudaMemcpyAsync(d, h, bytes, cudaMemcpyHostToDevice, stream));
+    L.lp.table = reinterpret_cast<const PlaneRec*>(d);
+    if (wants_work_counter(L)) L.lp.work = a.work + 2 * slot;
     rc = run(L, L.lp, stream);
-    if (rc != FKB_OK) return rc;
+    // (even if a kernel launch failed, the copy above may be in flight: the slot counts as used either way)
     FKB_CUDA(cudaEventRecord(a.ev[slot], stream));
     a.used[slot] = true;
-    return FKB_OK;
+    return rc;
 }
 
 // -------------------------------------------------------------------------------------------------------

@@ -644,7 +644,7 @@ __device__ __forceinline__ bool point_item(const LaunchParams& p, const WarpSlic
         const uint32_t s = k & 3u, o = k & 1u;
         if (lane == 0) bulk_wait_read_1();  // the store that read w.out(o) two rows ago is done with it
         if (r + AHEAD < nr) issue(r + AHEAD, (k + AHEAD) & 3u);  // into the stage of the row computed just before
-        const bool landed = mbar_wait_bounded(w.bar(2 + s), (k >> 2) & 1u);
+        const bool landed = mbar_wait_bounded(w.bar(2 + s), (k >> 2) & 1u, p.wait_limit_ns);
         if (__any_sync(0xffffffffu, !landed)) return false;
         compute(w.in4(s), w.out(o));
         store_row(gdst + static_cast<size_t>(r) * dst_pitch, w.out(o), row_bytes, lane);
@@ -730,7 +730,7 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
     // from the first.
     auto load_rows = [&](uint32_t r, uint32_t s, uint32_t r0, uint32_t r1) {
         const bool in = (in_mask >> r) & 1u;
-        mbar_arrive_expect_tx(w.bar(s), in ? 2u * row_bytes : 0u);
+        mbar_arrive_expect_tx(w.bar(s), (in ? 2u * row_bytes : 0u) + p.test_extra_tx);
         if (in) {
             bulk_load(smem_raw + w.in(s), gsrc + static_cast<size_t>(r0) * 16u, row_bytes, w.bar(s));
             bulk_load(smem_raw + w.in(s) + kInRowBytes, gsrc + static_cast<size_t>(r1) * 16u, row_bytes, w.bar(s));
@@ -907,8 +907,7 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
         const float wy0s = __shfl_sync(FULL, wy0_l, r), wy1s = __shfl_sync(FULL, wy1_l, r);
         const uint32_t r0n = __shfl_sync(FULL, row0_l, (r + 2u) & 31u), r1n = __shfl_sync(FULL, row1_l, (r + 2u) & 31u);
         const bool row_in = (in_mask >> r) & 1u;
-        bool ok = mbar_try_wait(w.bar(s), (k >> 1) & 1u);
-        if (!ok) ok = mbar_wait_bounded(w.bar(s), (k >> 1) & 1u);
+        const bool ok = mbar_wait_bounded(w.bar(s), (k >> 1) & 1u, p.wait_limit_ns);
         if (__any_sync(FULL, !ok)) return false;  // (a convergence point for the whole warp, too)
         const uint32_t in_s = w.in(s), out_s = w.out(s);
         if (!row_in) {
@@ -1055,8 +1054,10 @@ __global__ void __launch_bounds__(kStagedThreads, 2) staged_kernel(const __grid_
     }
     if (!ok) {
         // copies announced on the other stages may still be in flight: give them a bounded chance to land
-        mbar_wait_bounded(w.bar((k + 1) & 1u), ((k + 1) >> 1) & 1u);
-        for (uint32_t i = 1; i <= 3; ++i) mbar_wait_bounded(w.bar(2 + ((k4 + i) & 3u)), ((k4 + i) >> 2) & 1u);
+        // (stages without a copy in flight never complete: the limit, shortened, ends those waits)
+        const uint32_t grace = min(p.wait_limit_ns, 1000000u);
+        mbar_wait_bounded(w.bar((k + 1) & 1u), ((k + 1) >> 1) & 1u, grace);
+        for (uint32_t i = 1; i <= 3; ++i) mbar_wait_bounded(w.bar(2 + ((k4 + i) & 3u)), ((k4 + i) >> 2) & 1u, grace);
         if (lane == 0) atomicExch(p.status, FKB_ERR_DEVICE_WAIT);
     }
 }
@@ -1487,7 +1488,7 @@ __global__ void __launch_bounds__(kLutThreads, 1) lut_kernel(const __grid_consta
                 if (pf.g < nseg) issue(pf, (k + AHEAD) % kLutStages);
             }
             advance(pf);
-            const bool landed = mbar_wait_bounded(&bar[s], (k / kLutStages) & 1u);
+            const bool landed = mbar_wait_bounded(&bar[s], (k / kLutStages) & 1u, p.wait_limit_ns);
             if (__any_sync(0xffffffffu, !landed)) { ok = false; break; }
             const uint32_t ow = min(tile_w, dst_w - cu.tx * tile_w);
             const uint32_t seg = buf0 + s * kLutSegBytes;
@@ -1499,7 +1500,7 @@ __global__ void __launch_bounds__(kLutThreads, 1) lut_kernel(const __grid_consta
     }
     if (lane == 0) bulk_wait_all();
     if (!ok) {
-        for (uint32_t i = 1; i < kLutStages; ++i) mbar_wait_bounded(&bar[(k + i) % kLutStages], ((k + i) / kLutStages) & 1u);
+        for (uint32_t i = 1; i < kLutStages; ++i) mbar_wait_bounded(&bar[(k + i) % kLutStages], ((k + i) / kLutStages) & 1u, min(p.wait_limit_ns, 1000000u));
         if (threadIdx.x == 0) atomicExch(p.status, FKB_ERR_DEVICE_WAIT);
     }
 }

@@ -474,6 +474,42 @@ def crop_reorder(n=3, w=640, h=360, crop_size=(100, 60), seed=6, pitch_align=16)
                     f"{n} crops {cw}x{chh} of a {w}x{h} uchar3 frame, channel reorder only")
 
 
+# ---------------------------------------------------------------------------------------------------------------
+# sharding over GPUs: the path has no exchange step, a shard is a subset of the planes with the frames they read
+# ---------------------------------------------------------------------------------------------------------------
+def shard_by_frame(wl: Workload, rank: int, world: int) -> Workload:
+    """The batched workload split by frame, as one 64-frame batch is divided over the GPUs of a box: rank r keeps frames
+    [r * n / world, (r + 1) * n / world), the planes cropped from them, and a dense output tensor of just those planes
+    (in the whole job they are a contiguous range of the result tensor's planes)."""
+    n = len(wl.sources)
+    lo, hi = rank * n // world, (rank + 1) * n // world
+    keep = [p for p in wl.planes if lo <= p.src < hi]
+    plane_bytes = keep[0].dst_pitch * keep[0].dst_h
+    planes = [PlaneSpec(**{**p.__dict__, "src": p.src - lo, "dst_offset": i * plane_bytes}) for i, p in enumerate(keep)]
+    return Workload(wl.name, wl.chains, wl.sources[lo:hi], [len(planes) * plane_bytes], planes, wl.description,
+                    extra={**wl.extra, "n_frames": hi - lo, "first_frame": lo})
+
+
+def plane_partition(n_planes: int, world: int) -> list:
+    """Which planes of the divergent launch each rank runs: plane z goes to rank z % world.  The launch lists the planes
+    of its first chain first and those of its second chain after them, in equal numbers, so for world sizes up to that
+    number every rank gets as many planes of one kind as of the other; beyond it a rank holds a single plane and the
+    slowest kind of plane bounds the speed-up."""
+    return [[z for z in range(n_planes) if z % world == r] for r in range(world)]
+
+
+def shard_by_plane(wl: Workload, rank: int, world: int) -> Workload:
+    """The divergent launch split by plane.  A plane keeps its chain and its place in the output tensors (every sequence
+    of the reference's DivergentBatchTransformDPP sees the global plane index, core/execution_model/
+    data_parallel_patterns.h:322-331), so each rank holds output tensors of the global shape and writes its planes of
+    them; it holds only the frames its planes read."""
+    mine = plane_partition(len(wl.planes), world)[rank]
+    frames = sorted({wl.planes[z].src for z in mine})
+    planes = [PlaneSpec(**{**wl.planes[z].__dict__, "src": frames.index(wl.planes[z].src)}) for z in mine]
+    return Workload(wl.name, wl.chains, [wl.sources[f] for f in frames], list(wl.out_sizes), planes, wl.description,
+                    extra={**wl.extra, "global_planes": mine})
+
+
 CONFIGS = {
     "readme_crops": readme_crops,
     "vertical_fusion": vertical_fusion,

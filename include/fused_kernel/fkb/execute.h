@@ -148,8 +148,8 @@ template <typename... IOps>
 auto lower_sequence(const std::tuple<IOps...>& t) {
     constexpr size_t N = sizeof...(IOps);
     static_assert(N >= 2, "a chain needs at least a Read and a Write");
-    using First = std::tuple_element_t<0, std::tuple<IOps...>>;
-    using Last = std::tuple_element_t<N - 1, std::tuple<IOps...>>;
+    using First = std::decay_t<std::tuple_element_t<0, std::tuple<IOps...>>>;  // (the tuple may hold references)
+    using Last = std::decay_t<std::tuple_element_t<N - 1, std::tuple<IOps...>>>;
     static_assert(isReadIOp<First>, "The first IOp must be a complete Read operation");
     static_assert(isWriteIOp<Last>, "The last IOp must be a Write operation");
     const auto read = fold_all_but_last(t, std::make_index_sequence<N - 1>{});
@@ -167,8 +167,10 @@ struct Executor<TransformDPP<PA, TFEN>> {
     static_assert(PA == ParArch::GPU_NVIDIA, "this library executes on ParArch::GPU_NVIDIA only (there is no CPU path)");
     template <typename... IOps>
     static void executeOperations(Stream_<ParArch::GPU_NVIDIA>& stream, const IOps&... iops) {
-        const auto low = detail::lower_sequence(std::make_tuple(iops...));
-        std::vector<fkb_plane_desc> planes(low.n_planes);
+        const auto low = detail::lower_sequence(std::tie(iops...));
+        // (the descriptor array is kept per thread: a fresh allocation of its size is page-faulted in on every call)
+        static thread_local std::vector<fkb_plane_desc> planes;
+        planes.resize(low.n_planes);
         for (uint32_t z = 0; z < low.n_planes; ++z) planes[z] = low.plane(z, 0);
         detail::check(fkb_launch_transform(&low.chain, planes.data(), low.n_planes, stream.getCUDAStream()));
     }

@@ -84,6 +84,48 @@ static void test_readme() {
     report("activeThreads of the fused read", sender.getActiveThreads().x == 128 && sender.getActiveThreads().y == 64 && sender.getActiveThreads().z == 5);
 }
 
+// ---- thread fusion: TransformDPP<PA, TF::ENABLED> is the same launch ----------------------------------------------
+// The reference's TF::ENABLED makes a thread process several elements of narrow types (core/execution_model/
+// thread_fusion.h:82-160, data_parallel_patterns.h:143-171); its three- and four-channel types get one element per thread
+// either way (thread_fusion.h:54), and a ReadBack switches it off.  Here every path is vectorised by construction, so the
+// flag must compile and change no byte.
+static void test_thread_fusion() {
+    Stream stream;
+    const uint W = 1000, H = 75;
+    Ptr2D<uchar3> in(W, H), out0(W, H), out1(W, H);
+    fill_random(in, 7);
+    in.upload(stream);
+    auto run = [&](auto dpp, Ptr2D<uchar3>& out) {
+        using DPP = decltype(dpp);
+        executeOperations<DPP>(stream, PerThreadRead<ND::_2D, uchar3>::build(in), Cast<uchar3, float3>::build(),
+            Mul<float3>::build(make_<float3>(0.5f, 1.5f, 2.0f)), Add<float3>::build(make_<float3>(10.f, -20.f, 5.f)),
+            SaturateCast<float3, uchar3>::build(), PerThreadWrite<ND::_2D, uchar3>::build(out));
+        out.download(stream);
+    };
+    run(TransformDPP<ParArch::GPU_NVIDIA, TF::DISABLED>{}, out0);
+    run(TransformDPP<ParArch::GPU_NVIDIA, TF::ENABLED>{}, out1);
+    // and a chain with a ReadBack (crop + resize) under both flags
+    constexpr std::array<Rect, 2> crops{Rect(30, 5, 60, 40), Rect(400, 12, 130, 60)};
+    Tensor<float3> t0(64, 48, 2), t1(64, 48, 2);
+    auto run_resize = [&](auto dpp, Tensor<float3>& out) {
+        using DPP = decltype(dpp);
+        executeOperations<DPP>(stream, PerThreadRead<ND::_2D, uchar3>::build(in), Crop<>::build(crops),
+            Resize<InterpolationType::INTER_LINEAR, AspectRatio::PRESERVE_AR>::build(Size(64, 48), make_<float3>(1.f, 2.f, 3.f)),
+            Mul<float3>::build(make_set<float3>(1.f / 255.f)), TensorWrite<float3>::build(out));
+        out.download(stream);
+    };
+    run_resize(TransformDPP<ParArch::GPU_NVIDIA, TF::DISABLED>{}, t0);
+    run_resize(TransformDPP<ParArch::GPU_NVIDIA, TF::ENABLED>{}, t1);
+    stream.sync();
+    bool ok = true;
+    const uint pitch = out0.dims().pitch;
+    for (uint y = 0; y < H && ok; ++y)
+        ok = std::memcmp(reinterpret_cast<uint8_t*>(out0.ptrPinned().data) + static_cast<size_t>(y) * pitch,
+                         reinterpret_cast<uint8_t*>(out1.ptrPinned().data) + static_cast<size_t>(y) * pitch, W * 3) == 0;
+    report("TF::ENABLED == TF::DISABLED (pointwise chain)", ok);
+    report("TF::ENABLED == TF::DISABLED (crop + resize chain)", std::memcmp(t0.ptrPinned().data, t1.ptrPinned().data, 64 * 48 * 2 * 12) == 0);
+}
+
 // ---- vertical fusion: Cast, Mul, Add, Div, BGR2RGB, SaturateCast on every pixel ----------------------------------
 static void test_vertical_fusion() {
     Stream stream;
@@ -605,6 +647,7 @@ static void test_errors() {
 int main() {
     test_readme();
     test_vertical_fusion();
+    test_thread_fusion();
     test_nv12();
     test_yuv<PixelFormat::NV21, ColorRange::Limited, ColorPrimitives::bt601>("NV21, limited range bt601", FKB_PIX_NV21, FKB_RANGE_LIMITED, FKB_PRIMITIVES_BT601);
     test_yuv<PixelFormat::UYVY, ColorRange::Full, ColorPrimitives::bt2020>("UYVY, full range bt2020", FKB_PIX_UYVY, FKB_RANGE_FULL, FKB_PRIMITIVES_BT2020);

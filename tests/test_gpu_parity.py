@@ -396,3 +396,83 @@ def test_full_batched_crop_resize_properties():
         os.environ["FKB_FORCE_GATHER"] = "0"
     assert torch.equal(first.view(torch.int32), out.view(torch.int32))
     dw.close()
+
+
+def test_bounded_wait_runs_out_is_reported_and_leaves_the_context_usable():
+    """Every device-side wait for a bulk copy has a time limit.  Here the staged kernel's loads are made to announce 16
+    bytes that nothing delivers (a host-side test switch: no fault is involved, the copies themselves are complete), so
+    the wait runs out: the kernel must end by itself, fkb_device_status() must report FKB_ERR_DEVICE_WAIT once and then
+    be clear again, and the next launch on the same context must be correct."""
+    from fusedkernellibrary_b200 import runtime
+    wl = SMALL["batched"]()
+    lib = abi.load()
+    torch.cuda.synchronize()
+    assert lib.fkb_device_status() == abi.OK
+    os.environ.update(FKB_TEST_EXTRA_TX="16", FKB_WAIT_LIMIT_US="2000", FKB_TINY_PIXELS="0")
+    try:
+        dw = runtime.DeviceWorkload(wl, poison=FILL)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        dw.launch()
+        stop.record()
+        torch.cuda.synchronize()  # returns: the kernel gave up on its own
+        assert start.elapsed_time(stop) < 2000.0  # a few waits of 2 ms each, not an endless one
+    finally:
+        for k in ("FKB_TEST_EXTRA_TX", "FKB_WAIT_LIMIT_US", "FKB_TINY_PIXELS"):
+            os.environ.pop(k, None)
+    assert lib.fkb_device_status() == abi.ERR_DEVICE_WAIT
+    assert b"wait" in lib.fkb_status_string(abi.ERR_DEVICE_WAIT)
+    assert lib.fkb_device_status() == abi.OK  # reading the status cleared it
+    dw.close()
+    check(wl)  # the same launch without the switch: correct, on the same context
+
+
+def test_launches_of_one_plan_may_overlap_on_two_streams():
+    """fkb_plan_launch gives every launch its own pair of work counters, so launches of one plan on different streams may
+    run at the same time: the result is that of a single launch, and later launches of the plan still are."""
+    from fusedkernellibrary_b200 import runtime
+    wl = W.batched_crop_resize(n_frames=8)  # 256 planes: enough items for the kernel to claim them from a counter
+    dw = runtime.DeviceWorkload(wl, poison=FILL)
+    dw.launch()  # reference result through the one-shot entry point
+    want = dw.results()[0].copy()
+    dw.out[0].fill_(FILL)
+    torch.cuda.synchronize()
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    for _ in range(6):
+        with torch.cuda.stream(s1):
+            dw.launch_plan()
+        with torch.cuda.stream(s2):
+            dw.launch_plan()
+    torch.cuda.synchronize()
+    assert np.array_equal(dw.results()[0], want)
+    dw.out[0].fill_(FILL)
+    dw.launch_plan()
+    assert np.array_equal(dw.results()[0], want)
+    dw.close()
+
+
+def test_stream_capture_small_launches_record_large_one_shot_launches_refuse():
+    """A launch of at most eight planes carries its records in the kernel parameters and records into a CUDA graph; a
+    larger one-shot launch (and the no-allocation entry point) stages records through host memory the library reuses, so
+    on a capturing stream it returns FKB_ERR_UNSUPPORTED and records nothing — the capture itself stays valid."""
+    from fusedkernellibrary_b200 import runtime
+    lib = abi.load()
+    big = runtime.DeviceWorkload(W.batched_crop_resize(n_frames=3, crops_per_frame=100, w=320, h=240, dst=(32, 24), crop_range=(4, 100)), poison=FILL)
+    small = runtime.DeviceWorkload(W.readme_crops(), poison=FILL)
+    big.launch()
+    small.launch()  # warm: kernels are loaded and per-device look-ups are cached before the capture begins
+    abi.check(lib.fkb_launch_transform_noalloc(big.chains, big.planes, big.n_planes, runtime.current_stream_ptr()))
+    want = small.results()[0].copy()
+    small.out[0].fill_(FILL)
+    torch.cuda.synchronize()
+    graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            rc_big = lib.fkb_launch_transform(big.chains, big.planes, big.n_planes, side.cuda_stream)
+            rc_noalloc = lib.fkb_launch_transform_noalloc(big.chains, big.planes, big.n_planes, side.cuda_stream)
+            rc_small = lib.fkb_launch_transform(small.chains, small.planes, small.n_planes, side.cuda_stream)
+    assert rc_big == abi.ERR_UNSUPPORTED and rc_noalloc == abi.ERR_UNSUPPORTED and rc_small == abi.OK
+    graph.replay()
+    assert np.array_equal(small.results()[0], want)
+    big.close()
+    small.close()

@@ -1,5 +1,6 @@
-"""Host-side logic of the multi-GPU benchmark, on CPU: two gloo ranks build their shards of the batched workload, and the
-shards are disjoint, cover the job, and reduce to the timing the benchmark reports (max over ranks)."""
+"""Host-side logic of the multi-GPU benchmark, on CPU: two gloo ranks build their shards of the batched workload (by frame)
+and of the divergent launch (by plane); the shards are disjoint, cover the job, and reduce to the timing the benchmark
+reports (max over ranks)."""
 import os
 import socket
 import subprocess
@@ -24,6 +25,16 @@ WORKER = textwrap.dedent('''
         dist.all_gather_object(gathered, {"frames": frames, "n_src": len(wl.sources), "n_planes": len(wl.planes),
                                           "px": wl.out_pixels, "seeds": seeds, "rects": rects})
         out[scaling] = gathered
+    from fusedkernellibrary_b200 import workloads as W
+    whole = W.divergent_planes(n_per_seq=4, w=64, h=32)
+    mine = W.shard_by_plane(whole, rank, world)
+    gathered = [None] * world
+    dist.all_gather_object(gathered, {"global_planes": mine.extra["global_planes"], "chains": [p.chain for p in mine.planes],
+                                      "dst": [(p.dst, p.dst_offset) for p in mine.planes], "n_src": len(mine.sources),
+                                      "out_sizes": mine.out_sizes,
+                                      "frames": [int(s[:16].sum()) * 31 + int(s[-16:].sum()) for s in mine.sources]})
+    out["config5"] = gathered
+    out["config5_whole"] = {"dst": [(p.dst, p.dst_offset) for p in whole.planes], "out_sizes": whole.out_sizes, "n_planes": len(whole.planes)}
     t = torch.tensor([1.0 + rank], dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     out["max_time"] = float(t.item())
@@ -57,3 +68,15 @@ def test_two_rank_sharding_with_gloo(tmp_path):
     assert set(strong[0]["seeds"]).isdisjoint(strong[1]["seeds"])
     assert strong[0]["rects"] != strong[1]["rects"]
     assert sum(g["px"] for g in strong) == weak[0]["px"]
+    # the divergent launch split by plane: the ranks' planes are disjoint and cover the launch, every rank gets as many
+    # planes of the first chain as of the second, a plane keeps its place in output tensors of the global shape (the
+    # reference hands every sequence the global plane index), and a rank holds only the frames its planes read
+    c5, whole5 = res["config5"], res["config5_whole"]
+    planes = sorted(z for g in c5 for z in g["global_planes"])
+    assert planes == list(range(whole5["n_planes"]))
+    for g in c5:
+        assert g["chains"].count(0) == g["chains"].count(1) == 2
+        assert g["out_sizes"] == whole5["out_sizes"]
+        assert [tuple(d) for d in g["dst"]] == [tuple(whole5["dst"][z]) for z in g["global_planes"]]
+        assert g["n_src"] == len(g["global_planes"])
+    assert set(c5[0]["frames"]).isdisjoint(c5[1]["frames"])

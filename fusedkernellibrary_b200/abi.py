@@ -18,6 +18,7 @@ OK, ERR_NULL, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_TOO_LARGE, ERR_DEVICE_
 
 PIX_U8C3, PIX_F32C3, PIX_NV12, PIX_NV21, PIX_UYVY, PIX_U8C4, PIX_F32C4, PIX_F32P3 = 1, 2, 3, 4, 5, 6, 7, 8
 PIX_P010, PIX_P210, PIX_Y210 = 9, 10, 11
+PIX_U8C1, PIX_F32C1 = 12, 13  # one-channel destinations (after OP_RGB2GRAY)
 RANGE_LIMITED, RANGE_FULL = 0, 1
 PRIMITIVES_BT601, PRIMITIVES_BT709, PRIMITIVES_BT2020 = 0, 1, 2
 GEOM_NONE, GEOM_RESIZE_IGNORE_AR, GEOM_RESIZE_PRESERVE_AR = 0, 1, 2
@@ -26,6 +27,7 @@ PLANE_DEFAULT = 0x80000000  # fkb_plane_desc.chain bit: the plane's read yields 
 WRITE_PACKED, WRITE_SPLIT, WRITE_SPLIT_PLANES, WRITE_NV12, WRITE_NV21, WRITE_UYVY = 1, 2, 3, 4, 5, 6
 BORDER_NONE, BORDER_CONSTANT, BORDER_REPLICATE, BORDER_REFLECT, BORDER_WRAP, BORDER_REFLECT_101 = 0, 1, 2, 3, 4, 5
 OP_CAST_F32, OP_MUL, OP_ADD, OP_SUB, OP_DIV, OP_REORDER_ZYX, OP_YUV2RGB, OP_SATCAST_U8, OP_RGB2YUV, OP_ADD_ALPHA = 1, 2, 3, 4, 5, 6, 7, 8, 9, 10
+OP_RGB2GRAY = 11
 
 
 class Op(C.Structure):

@@ -294,6 +294,13 @@ __device__ __forceinline__ void apply_ops(float (&v)[N][3], const fkb_chain_desc
 #pragma unroll
             for (int n = 0; n < N; ++n) { v[n][0] = sat_u8_as_float(v[n][0]); v[n][1] = sat_u8_as_float(v[n][1]); v[n][2] = sat_u8_as_float(v[n][2]); }
             break;
+        case FKB_OP_RGB2GRAY:  // (the later ops and the write use channel 0 only; the others keep running along unused)
+#pragma unroll
+            for (int n = 0; n < N; ++n) {
+                const float l = __fadd_rn(__fadd_rn(__fmul_rn(v[n][0], 0.299f), __fmul_rn(v[n][1], 0.587f)), __fmul_rn(v[n][2], 0.114f));
+                v[n][0] = rintf(l);  // nearest integer, ties to even, whatever the output type (see FKB_OP_RGB2GRAY in fkb.h)
+            }
+            break;
         default: break;  // FKB_OP_CAST_F32: values are already carried as fp32
         }
     }

@@ -51,6 +51,10 @@ int check_ops(const fkb_chain_desc& ch, uint32_t first, uint32_t last, ValueType
         case FKB_OP_YUV2RGB: case FKB_OP_RGB2YUV: if (t != VT_U8) return FKB_ERR_INVALID; t = VT_F32; break;
         case FKB_OP_SATCAST_U8: if (t != VT_F32) return FKB_ERR_INVALID; t = VT_U8; break;
         case FKB_OP_ADD_ALPHA: break;  // uchar3 -> uchar4 or float3 -> float4; check_chain counts it
+        case FKB_OP_RGB2GRAY:          // uchar3 -> uchar (rounded) or float3 -> float; check_chain counts it and checks what follows
+            if (op.v[0] != 0.f) { if (t != VT_U8) return FKB_ERR_INVALID; }
+            else t = VT_F32;
+            break;
         default: return FKB_ERR_UNSUPPORTED;
         }
     }
@@ -63,9 +67,24 @@ int check_chain(const fkb_chain_desc& ch) {
     if (ch.src_format != FKB_PIX_U8C3 && ch.src_format != FKB_PIX_NV12 && ch.src_format != FKB_PIX_NV21 &&
         ch.src_format != FKB_PIX_UYVY && ch.src_format != FKB_PIX_U8C4 && !float_src && !wide_yuv) return FKB_ERR_UNSUPPORTED;
     const bool four = ch.dst_format == FKB_PIX_U8C4 || ch.dst_format == FKB_PIX_F32C4;  // the chain keeps four channels
-    if (ch.dst_format != FKB_PIX_U8C3 && ch.dst_format != FKB_PIX_F32C3 && !four) return FKB_ERR_UNSUPPORTED;
+    if (ch.dst_format != FKB_PIX_U8C3 && ch.dst_format != FKB_PIX_F32C3 && ch.dst_format != FKB_PIX_U8C1 && ch.dst_format != FKB_PIX_F32C1 && !four)
+        return FKB_ERR_UNSUPPORTED;
     uint32_t n_alpha = 0;  // AddOpaqueAlpha: the step from three channels to four
     for (uint32_t i = 0; i < ch.n_ops && i < FKB_MAX_OPS; ++i) n_alpha += ch.ops[i].code == FKB_OP_ADD_ALPHA;
+    // RGB2Gray: at most once, after the interpolation, nothing behind it that needs three channels, and a one-channel write
+    const bool one = ch.dst_format == FKB_PIX_U8C1 || ch.dst_format == FKB_PIX_F32C1;
+    uint32_t n_gray = 0, gray_at = 0;
+    for (uint32_t i = 0; i < ch.n_ops && i < FKB_MAX_OPS; ++i)
+        if (ch.ops[i].code == FKB_OP_RGB2GRAY) { ++n_gray; gray_at = i; }
+    if (one != (n_gray == 1) || n_gray > 1) return FKB_ERR_INVALID;
+    if (one) {
+        if (ch.write_kind != FKB_WRITE_PACKED || float_src || ch.n_ops > FKB_MAX_OPS) return FKB_ERR_UNSUPPORTED;
+        if (ch.geometry != FKB_GEOM_NONE && gray_at < ch.n_pre_ops) return FKB_ERR_UNSUPPORTED;
+        for (uint32_t i = gray_at + 1; i < ch.n_ops; ++i) {
+            const uint32_t c = ch.ops[i].code;
+            if (c != FKB_OP_CAST_F32 && c != FKB_OP_MUL && c != FKB_OP_ADD && c != FKB_OP_SUB && c != FKB_OP_DIV && c != FKB_OP_SATCAST_U8) return FKB_ERR_INVALID;
+        }
+    }
     if (four) {
         if ((ch.src_format != FKB_PIX_U8C4 && ch.src_format != FKB_PIX_U8C3) || ch.write_kind != FKB_WRITE_PACKED) return FKB_ERR_UNSUPPORTED;
         if (n_alpha != (ch.src_format == FKB_PIX_U8C3 ? 1u : 0u)) return FKB_ERR_INVALID;
@@ -89,7 +108,7 @@ int check_chain(const fkb_chain_desc& ch) {
         t = VT_F32;  // the interpolation returns float_<cn> whatever it reads
         if ((rc = check_ops(ch, ch.n_pre_ops, ch.n_ops, t)) != FKB_OK) return rc;
     }
-    const ValueType want = (ch.dst_format == FKB_PIX_F32C3 || ch.dst_format == FKB_PIX_F32C4) ? VT_F32 : VT_U8;
+    const ValueType want = (ch.dst_format == FKB_PIX_F32C3 || ch.dst_format == FKB_PIX_F32C4 || ch.dst_format == FKB_PIX_F32C1) ? VT_F32 : VT_U8;
     return t == want ? FKB_OK : FKB_ERR_INVALID;  // the Write's input type must be the chain's output type
 }
 
@@ -132,7 +151,8 @@ int check_plane(const fkb_chain_desc& ch, const fkb_plane_desc& pl) {
     }
     if (pl.dst_w == 0 || pl.dst_h == 0) return FKB_ERR_INVALID;
     const bool four = ch.dst_format == FKB_PIX_U8C4 || ch.dst_format == FKB_PIX_F32C4;
-    const bool f32 = ch.dst_format == FKB_PIX_F32C3 || ch.dst_format == FKB_PIX_F32C4;
+    const bool one = ch.dst_format == FKB_PIX_U8C1 || ch.dst_format == FKB_PIX_F32C1;
+    const bool f32 = ch.dst_format == FKB_PIX_F32C3 || ch.dst_format == FKB_PIX_F32C4 || ch.dst_format == FKB_PIX_F32C1;
     const bool planes3 = ch.write_kind == FKB_WRITE_SPLIT_PLANES;
     if (planes3 && (!pl.dst_y || !pl.dst_z)) return FKB_ERR_NULL;
     const bool split = ch.write_kind == FKB_WRITE_SPLIT || planes3;
@@ -141,6 +161,7 @@ int check_plane(const fkb_chain_desc& ch, const fkb_plane_desc& pl) {
     const uint64_t dst_row = semi ? ((static_cast<uint64_t>(pl.dst_w) + 1) / 2) * 2
                              : ch.write_kind == FKB_WRITE_UYVY ? ((static_cast<uint64_t>(pl.dst_w) + 1) / 2) * 4
                              : four ? static_cast<uint64_t>(pl.dst_w) * (f32 ? 16 : 4)
+                             : one ? static_cast<uint64_t>(pl.dst_w) * (f32 ? 4 : 1)
                              : static_cast<uint64_t>(pl.dst_w) * (split ? (f32 ? 4 : 1) : (f32 ? 12 : 3));
     if (pl.dst_pitch < dst_row) return FKB_ERR_INVALID;
     if (f32 && ((reinterpret_cast<uintptr_t>(pl.dst) & 3) || (pl.dst_pitch & 3) || (pl.dst_channel_stride & 3))) return FKB_ERR_INVALID;
@@ -183,8 +204,9 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 // Debugging and tuning switches, read from the environment once per lowering (not once per plane):
 //   FKB_FORCE_GATHER=1       routes every plane through gather_kernel, which lets the kernel paths check each other;
-//   FKB_TINY_PIXELS=n        launches below n output pixels take the one-pixel-per-thread kernels (0 switches that off,
-//                            which the tests use to drive small cases through the pipelined kernels);
+//   FKB_TINY_PIXELS=n        launches below n output pixels take the one-pixel-per-thread kernels (0 switches that off, and
+//                            the joining of small pipelined planes to a general kernel with it, which the tests use to
+//                            drive small cases through the pipelined kernels);
 //   FKB_ROWS_PER_ITEM=n      output rows per item of the staged kernel (default: chosen from the launch size);
 //   FKB_TEST_EXTRA_TX=n      test hook: the staged kernel's resize loads announce n bytes more than they deliver, so its
 //                            bounded waits run out and the launch ends with FKB_ERR_DEVICE_WAIT in the status word;
@@ -212,6 +234,7 @@ void classify(const fkb_chain_desc& ch, PlaneRec& r, const Tuning& tune) {
     r.kclass = KCLASS_GATHER;
     r.tile_w = r.tile_h = r.tiles_x = 0;
     if (ch.dst_format == FKB_PIX_U8C4 || ch.dst_format == FKB_PIX_F32C4) { r.kclass = KCLASS_GATHER4; return; }
+    if (ch.dst_format == FKB_PIX_U8C1 || ch.dst_format == FKB_PIX_F32C1) return;  // one-channel chains: the general kernel
     if (tune.force_gather) return;
     if (ch.border) {
         // a rectangle inside the frame never meets the border: it takes the usual paths; one that leaves it is
@@ -450,6 +473,22 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
                 L.recs[z].kclass = (!tune.force_gather && rgb_kernel_takes(chains[L.recs[z].chain], L.recs[z])) ? KCLASS_NV12 : KCLASS_GATHER;
                 L.recs[z].tiles_x = 0;
             }
+    // A launch that needs the general kernel anyway (say, for crops that leave the frame under a BorderReader) and whose
+    // other planes are small runs them there too: a second kernel costs more than the pipelined path saves on so few pixels.
+    {
+        uint64_t general = 0, pipelined = 0;
+        for (uint32_t z = 0; z < n_planes; ++z) {
+            const uint64_t px = static_cast<uint64_t>(L.recs[z].dst_w) * L.recs[z].dst_h;
+            if (L.recs[z].kclass == KCLASS_GATHER) general += px;
+            else if (L.recs[z].kclass == KCLASS_POINT || L.recs[z].kclass == KCLASS_RESIZE || L.recs[z].kclass == KCLASS_LUT) pipelined += px;
+        }
+        if (tune.tiny_pixels != 0 && general && pipelined && pipelined < kJoinGeneralPixels)  // (FKB_TINY_PIXELS=0 switches this routing off, too)
+            for (uint32_t z = 0; z < n_planes; ++z)
+                if (L.recs[z].kclass == KCLASS_POINT || L.recs[z].kclass == KCLASS_RESIZE || L.recs[z].kclass == KCLASS_LUT) {
+                    L.recs[z].kclass = KCLASS_GATHER;
+                    L.recs[z].tiles_x = 0;
+                }
+    }
     for (uint32_t z = 0; z < n_planes; ++z) {
         const PlaneRec& r = L.recs[z];
         if (r.kclass == KCLASS_POINT || r.kclass == KCLASS_RESIZE) row_segments += static_cast<uint64_t>(r.tiles_x) * r.dst_h;

@@ -208,7 +208,20 @@ __global__ void __launch_bounds__(256) gather_kernel(const __grid_constant__ Lau
         }
 
         uint8_t* row = pl.dst + static_cast<size_t>(y) * pl.dst_pitch;
-        if (ch.write_kind >= FKB_WRITE_NV12 && PPT == 4 && nvalid == 4 && (pl.dst_pitch & 7u) == 0 &&
+        if (ch.dst_format == FKB_PIX_U8C1 || ch.dst_format == FKB_PIX_F32C1) {
+            // one channel (after FKB_OP_RGB2GRAY): channel 0 of each pixel
+            if (ch.dst_format == FKB_PIX_F32C1) {
+                float* f = reinterpret_cast<float*>(row) + x0;
+                if (PPT == 4 && nvalid == 4 && (reinterpret_cast<uintptr_t>(f) & 15) == 0) *reinterpret_cast<float4*>(f) = make_float4(v[0][0], v[1 % PPT][0], v[2 % PPT][0], v[3 % PPT][0]);
+                else for (uint32_t n = 0; n < nvalid; ++n) f[n] = v[n][0];
+            } else {
+                uint8_t* q = row + x0;
+                if (PPT == 4 && nvalid == 4 && (reinterpret_cast<uintptr_t>(q) & 3) == 0)
+                    *reinterpret_cast<uint32_t*>(q) = static_cast<uint32_t>(v[0][0]) | (static_cast<uint32_t>(v[1 % PPT][0]) << 8) |
+                                                      (static_cast<uint32_t>(v[2 % PPT][0]) << 16) | (static_cast<uint32_t>(v[3 % PPT][0]) << 24);
+                else for (uint32_t n = 0; n < nvalid; ++n) q[n] = static_cast<uint8_t>(v[n][0]);
+            }
+        } else if (ch.write_kind >= FKB_WRITE_NV12 && PPT == 4 && nvalid == 4 && (pl.dst_pitch & 7u) == 0 &&
             (reinterpret_cast<uintptr_t>(pl.dst) & 7u) == 0 && (pl.dst_cstride & 3u) == 0) {
             // four pixels of a YCbCr image with word stores (x0 is a multiple of four: two whole chroma pairs)
             uint32_t b[4][3];
@@ -1391,7 +1404,7 @@ __device__ __forceinline__ void lut_segment(uint32_t seg, uint32_t ow, uint32_t 
     uint32_t q[12];
 #pragma unroll
     for (int i = 0; i < 3; ++i) { const uint4 t = buf[i]; q[4 * i] = t.x; q[4 * i + 1] = t.y; q[4 * i + 2] = t.z; q[4 * i + 3] = t.w; }
-    const uint32_t lane_word = lane * 4u;  // byte 0 of every table address
+    const uint32_t lane_word = lane * 4u | kLutTableAddr;  // bytes 0, 2 and 3 of every table address
     uint32_t o[12];
 #pragma unroll
     for (int i = 0; i < 12; ++i) {
@@ -1400,8 +1413,9 @@ __device__ __forceinline__ void lut_segment(uint32_t seg, uint32_t ow, uint32_t 
         for (int t = 0; t < 4; ++t) {
             const int b = 4 * i + t, c = b % 3;          // output byte b is channel c of pixel b / 3
             const int sb = SWAP ? b - c + (2 - c) : b;   // the source byte it is a function of
-            const uint32_t at = __byte_perm(q[sb >> 2], lane_word, 0x5504u | ((sb & 3) << 4));  // value * 256 + lane * 4
-            e[t] = *reinterpret_cast<const uint32_t*>(smem_raw + at);
+            // absolute shared address of lane's copy of the entry: 0x10000 | value << 8 | lane << 2, one byte permute
+            const uint32_t at = __byte_perm(q[sb >> 2], lane_word, 0x7604u | ((sb & 3) << 4));
+            asm("ld.shared.u32 %0, [%1];" : "=r"(e[t]) : "r"(at));
         }
         // byte (4i+t) % 3 of entry t is the channel this output byte wants
         const uint32_t c0 = (4 * i) % 3, c1 = (4 * i + 1) % 3, c2 = (4 * i + 2) % 3, c3 = (4 * i + 3) % 3;  // constants once unrolled
@@ -1416,7 +1430,17 @@ __global__ void __launch_bounds__(kLutThreads, 1) lut_kernel(const __grid_consta
     __shared__ uint32_t s_entry[256];
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);  // tells the compiler the value is warp-uniform
-    const uint32_t slice = kLutBytes + warp * kLutSliceBytes;
+    // Where things are: the table at the absolute shared address kLutTableAddr, warp slices below it as far as they fit
+    // (from the first 128-byte boundary of the dynamic region) and above it for the rest.  Offsets are relative to smem_raw.
+    const uint32_t sbase = smem_addr(smem_raw);
+    const uint32_t low0 = ((sbase + 127u) & ~127u) - sbase;                       // first slice below the table
+    const uint32_t n_low = sbase + low0 < kLutTableAddr ? (kLutTableAddr - sbase - low0) / kLutSliceBytes : 0u;
+    const uint32_t table = kLutTableAddr - sbase;                                 // (offset of the table in smem_raw)
+    if (sbase > kLutTableAddr || table + kLutBytes + (kLutWarps - min(n_low, kLutWarps)) * kLutSliceBytes > kLutSmemBytes) {
+        if (threadIdx.x == 0) atomicExch(p.status, FKB_ERR_DEVICE_WAIT);          // the layout does not fit: nothing is touched
+        return;
+    }
+    const uint32_t slice = warp < n_low ? low0 + warp * kLutSliceBytes : table + kLutBytes + (warp - n_low) * kLutSliceBytes;
     uint64_t* bar = reinterpret_cast<uint64_t*>(smem_raw + slice);
     const uint32_t buf0 = slice + 64;
     if (lane == 0) {
@@ -1424,7 +1448,7 @@ __global__ void __launch_bounds__(kLutThreads, 1) lut_kernel(const __grid_consta
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncwarp();
-    const PlaneRec* table = plane_table(p);
+    const PlaneRec* tbl = plane_table(p);
     uint32_t cur_plane = 0xffffffffu, k = 0;
     bool ok = true;
     for (uint32_t unit = blockIdx.x; unit < p.n_lut_units; unit += gridDim.x) {
@@ -1434,7 +1458,7 @@ __global__ void __launch_bounds__(kLutThreads, 1) lut_kernel(const __grid_consta
         if (rebuild) {
             __syncthreads();  // nobody reads the old table or plane record any more
             if (threadIdx.x < sizeof(PlaneRec) / 16)
-                reinterpret_cast<uint4*>(&s_pl)[threadIdx.x] = reinterpret_cast<const uint4*>(table + z)[threadIdx.x];
+                reinterpret_cast<uint4*>(&s_pl)[threadIdx.x] = reinterpret_cast<const uint4*>(tbl + z)[threadIdx.x];
             __syncthreads();
         }
         const PlaneRec& pl = s_pl;
@@ -1445,7 +1469,7 @@ __global__ void __launch_bounds__(kLutThreads, 1) lut_kernel(const __grid_consta
         uint8_t* gdst = pl.dst + static_cast<size_t>(row0) * pl.dst_pitch;
         const uint32_t src_pitch = pl.src_pitch, dst_pitch = pl.dst_pitch, tiles_x = pl.tiles_x, tile_w = pl.tile_w, dst_w = pl.dst_w;
         // Segment g of the unit is (row g / tiles_x, column tile g % tiles_x); this warp takes g = warp, warp + 24, ...
-        // Two cursors walk that list without dividing: `pf` for the prefetches, `cu` for the segment being computed.
+        // Two cursors walk that list without dividing: `pf` for the loads, three segments ahead of `cu`, the one computed.
         struct Cursor { uint32_t g, r, tx; };
         const uint32_t step_r = kLutWarps / tiles_x, step_tx = kLutWarps % tiles_x;
         auto advance = [&](Cursor& c) {
@@ -1459,7 +1483,7 @@ __global__ void __launch_bounds__(kLutThreads, 1) lut_kernel(const __grid_consta
             bulk_load(smem_raw + buf0 + s * kLutSegBytes, gsrc + static_cast<size_t>(c.r) * src_pitch + static_cast<size_t>(c.tx) * tile_w * 3u, bytes, &bar[s]);
         };
         Cursor cu{warp, warp / tiles_x, warp % tiles_x}, pf = cu;
-        constexpr uint32_t AHEAD = kLutStages - 2;
+        constexpr uint32_t AHEAD = kLutStages - 1;
         if (lane == 0) bulk_wait_read_all();  // the ring's earlier stores have been read out of their buffers
         for (uint32_t i = 0; i < AHEAD; ++i) {  // the first loads fly while the table is built
             if (lane == 0 && pf.g < nseg) issue(pf, (k + i) % kLutStages);
@@ -1476,25 +1500,31 @@ __global__ void __launch_bounds__(kLutThreads, 1) lut_kernel(const __grid_consta
             __syncthreads();
             // copy l of value v sits at v * 256 + l * 4: consecutive threads write consecutive words of a row
             for (uint32_t w = threadIdx.x; w < 256u * 32u; w += kLutThreads)
-                *reinterpret_cast<uint32_t*>(smem_raw + (w >> 5) * 256u + (w & 31u) * 4u) = s_entry[w >> 5];
+                *reinterpret_cast<uint32_t*>(smem_raw + table + (w >> 5) * 256u + (w & 31u) * 4u) = s_entry[w >> 5];
             __syncthreads();
             cur_plane = z;
         }
-        for (; cu.g < nseg && ok; advance(cu), ++k) {
+        // Per segment: wait for it, transform it in place, and then — lane 0's one divergent stretch — send it off, wait
+        // until the store of the segment before has read its buffer, and request the segment three ahead into that buffer.
+        for (; cu.g < nseg && ok; advance(cu), advance(pf), ++k) {
             const uint32_t s = k % kLutStages;
-            // the buffer two segments back is free once its store has read it; the load two ahead goes there
-            if (lane == 0) {
-                bulk_wait_read_1();
-                if (pf.g < nseg) issue(pf, (k + AHEAD) % kLutStages);
-            }
-            advance(pf);
             const bool landed = mbar_wait_bounded(&bar[s], (k / kLutStages) & 1u, p.wait_limit_ns);
             if (__any_sync(0xffffffffu, !landed)) { ok = false; break; }
             const uint32_t ow = min(tile_w, dst_w - cu.tx * tile_w);
             const uint32_t seg = buf0 + s * kLutSegBytes;
             if (swap) lut_segment<true>(seg, ow, lane);
             else lut_segment<false>(seg, ow, lane);
-            store_row(gdst + static_cast<size_t>(cu.r) * dst_pitch + static_cast<size_t>(cu.tx) * tile_w * 3u, seg, ow * 3u, lane);
+            uint8_t* out = gdst + static_cast<size_t>(cu.r) * dst_pitch + static_cast<size_t>(cu.tx) * tile_w * 3u;
+            const uint32_t out_bytes = ow * 3u, out_bulk = out_bytes & ~15u;
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                if (out_bulk) bulk_store(out, smem_raw + seg, out_bulk);
+                bulk_commit();
+                bulk_wait_read_1();
+                if (pf.g < nseg) issue(pf, (k + AHEAD) % kLutStages);
+            }
+            if (out_bytes != out_bulk && lane < out_bytes - out_bulk) out[out_bulk + lane] = smem_raw[seg + out_bulk + lane];  // rare
         }
         if (__syncthreads_or(ok ? 0 : 1)) { ok = false; break; }
     }

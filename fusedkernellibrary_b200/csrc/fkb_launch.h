@@ -23,19 +23,25 @@ constexpr uint32_t kSliceBytes = kSliceHeader + 4 * kInRowBytes + 2 * kOutSlotBy
 constexpr uint32_t kStagedSmemBytes = kStagedWarps * kSliceBytes;
 constexpr uint32_t kMaxRowsPerItem = 32;
 // lut_kernel: a CTA-wide table of 256 rows, 256 bytes apart, each holding 32 copies of one 32-bit word
-// {T0[i], T1[i], T2[i], 0} (copy l belongs to lane l and sits in bank l, so a table read never has a bank conflict),
-// followed by one slice per warp: four mbarriers and a ring of four row segments of 512 uchar3 pixels that are transformed
-// in place.  24 warps, 210 KB: one CTA per SM.
+// {T0[i], T1[i], T2[i], 0} (copy l belongs to lane l and sits in bank l, so a table read never has a bank conflict).  The
+// table sits at the absolute shared-memory address 65536, so that the address of a read — 0x10000 | value << 8 | lane << 2
+// — is a single byte permute with no addition behind it.  Around it one slice per warp: four mbarriers and a ring of four
+// row segments of 512 uchar3 pixels that are transformed in place; as many slices as fit lie below the table, the rest
+// above it.  24 warps, one CTA per SM.
 constexpr uint32_t kLutThreads = 768;
 constexpr uint32_t kLutWarps = kLutThreads / 32;
 constexpr uint32_t kLutCtasPerSm = 1;
+constexpr uint32_t kLutTableAddr = 65536;  // absolute shared-memory address of the table
 constexpr uint32_t kLutBytes = 256 * 256;  // 256 values, rows 256 bytes apart (32 lane copies of a 4-byte entry, then unused)
 constexpr uint32_t kLutSegBytes = 1536;
 constexpr uint32_t kLutStages = 4;
 constexpr uint32_t kLutSliceBytes = 64 + kLutStages * kLutSegBytes;
-constexpr uint32_t kLutSmemBytes = kLutBytes + kLutWarps * kLutSliceBytes;
+// dynamic shared memory: enough for the slices above the table when only nine fit below it (the dynamic region starts
+// after the kernel's static variables and whatever the system reserves; the kernel checks the layout it finds)
+constexpr uint32_t kLutSmemBytes = kLutTableAddr + kLutBytes + (kLutWarps - 9) * kLutSliceBytes;
 
 constexpr uint64_t kTinyLaunchPixels = 100000;  // launches below this many output pixels take the general kernel
+constexpr uint64_t kJoinGeneralPixels = 400000; // pipelined planes below this many pixels join a general kernel that runs anyway
 
 cudaError_t launch_staged(const LaunchParams& p, uint32_t grid, cudaStream_t stream);
 cudaError_t launch_lut(const LaunchParams& p, uint32_t grid, cudaStream_t stream);

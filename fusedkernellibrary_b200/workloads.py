@@ -139,7 +139,7 @@ class Workload:
             ch = self.chains[s.chain]
             uyvy = ch.src_format == abi.PIX_UYVY
             nv12 = ch.src_format in (abi.PIX_NV12, abi.PIX_NV21) or uyvy  # one luma byte per pixel, one chroma pair per 2 (x2) pixels
-            elt = {abi.PIX_F32C3: 12, abi.PIX_U8C3: 3, abi.PIX_F32C4: 16, abi.PIX_U8C4: 4}[ch.dst_format]
+            elt = {abi.PIX_F32C3: 12, abi.PIX_U8C3: 3, abi.PIX_F32C4: 16, abi.PIX_U8C4: 4, abi.PIX_U8C1: 1, abi.PIX_F32C1: 4}[ch.dst_format]
             out_bytes += s.dst_w * s.dst_h * elt
             if s.default or ch.border:
                 continue
@@ -384,6 +384,37 @@ def add_alpha_image(swap=False, w=322, h=180, seed=22) -> Workload:
     planes = [PlaneSpec(0, 0, 0, w, h, pitch, (0, 0, w, h), w, h, opitch)]
     return Workload("add_alpha_image", [ch], [_frame(seed, pitch * h)], [opitch * h], planes, f"uchar3 -> uchar4 swap={swap}",
                     extra={"swap": swap})
+
+
+GRAY_RECTS = ((30, 20, 200, 120), (300, 60, 64, 200), (0, 0, 640, 360), (500, 300, 140, 60), (123, 45, 33, 77))
+
+
+def gray_image(bgr=False, src4=False, w=322, h=180, seed=23) -> Workload:
+    """ColorConversion<COLOR_RGB2GRAY | COLOR_BGR2GRAY | COLOR_RGBA2GRAY | COLOR_BGRA2GRAY, uchar3 | uchar4, uchar> on a whole
+    image: PerThreadRead -> conversion -> PerThreadWrite<_2D, uchar>."""
+    sp = 4 if src4 else 3
+    pitch = _pitch(w * sp, 16)
+    ops = ([op(abi.OP_REORDER_ZYX)] if bgr else []) + [op(abi.OP_RGB2GRAY, (1.0, 0.0, 0.0))]
+    ch = chain(abi.PIX_U8C4 if src4 else abi.PIX_U8C3, abi.GEOM_NONE, abi.PIX_U8C1, abi.WRITE_PACKED, ops)
+    opitch = _pitch(w, 16)
+    plane = PlaneSpec(0, 0, 0, w, h, pitch, (0, 0, w, h), w, h, opitch)
+    return Workload("gray_image", [ch], [_frame(seed, pitch * h)], [opitch * h], [plane], f"gray image bgr={bgr} src4={src4}",
+                    extra={"bgr": bgr, "src4": src4})
+
+
+def gray_crops(bgr=False, f32=False, w=640, h=360, dst=(96, 64), rects=GRAY_RECTS, mul=1.25, seed=24) -> Workload:
+    """One uchar3 frame, five crops -> Resize -> ColorConversion<COLOR_RGB2GRAY | COLOR_BGR2GRAY, float3, float> -> Mul<float> ->
+    [SaturateCast<float, uchar> -> TensorWrite<uchar> | TensorWrite<float>]."""
+    pitch = _pitch(w * 3, 16)
+    dw, dh = dst
+    ops = ([op(abi.OP_REORDER_ZYX)] if bgr else []) + [op(abi.OP_RGB2GRAY), op(abi.OP_MUL, (mul, 0.0, 0.0))]
+    if not f32:
+        ops.append(op(abi.OP_SATCAST_U8))
+    elt = 4 if f32 else 1
+    ch = chain(abi.PIX_U8C3, abi.GEOM_RESIZE_IGNORE_AR, abi.PIX_F32C1 if f32 else abi.PIX_U8C1, abi.WRITE_PACKED, ops)
+    planes = [PlaneSpec(0, 0, i * dw * dh * elt, w, h, pitch, r, dw, dh, dw * elt) for i, r in enumerate(rects)]
+    return Workload("gray_crops", [ch], [_frame(seed, pitch * h)], [len(rects) * dw * dh * elt], planes, f"gray crops bgr={bgr} f32={f32}",
+                    extra={"bgr": bgr, "f32": f32, "rects": rects, "mul": mul})
 
 
 def conditional_resize(used=5, w=320, h=180, dst=(96, 64), default=(7, 200, 33), seed=11) -> Workload:

@@ -40,7 +40,7 @@
 extern "C" {
 #endif
 
-#define FKB_ABI_VERSION 2u
+#define FKB_ABI_VERSION 3u
 #define FKB_PLANE_DEFAULT 0x80000000u
 #define FKB_MAX_OPS 12u          /* compute ops per chain */
 #define FKB_MAX_PLANE_PARAMS 4u  /* per-plane float3 operands a chain may refer to */
@@ -82,7 +82,10 @@ enum { FKB_PIX_U8C3 = 1, FKB_PIX_F32C3 = 2, FKB_PIX_NV12 = 3,
         * P010 = NV12's layout with ushort samples (4:2:0), P210 the same with full-height chroma (4:2:2), Y210 one plane of
         * ushort4 groups Y0 U Y1 V.  src_pitch in bytes; P010 / P210 take src_chroma.  The matrix and offsets of their
         * FKB_OP_YUV2RGB come from fkb_ycbcr_to_rgb_bits(10, ...). */
-       FKB_PIX_P010 = 9, FKB_PIX_P210 = 10, FKB_PIX_Y210 = 11 };
+       FKB_PIX_P010 = 9, FKB_PIX_P210 = 10, FKB_PIX_Y210 = 11,
+       /* One-channel destinations (PerThreadWrite<_2D, uchar | float>, TensorWrite<uchar | float>): what a chain writes
+        * after FKB_OP_RGB2GRAY has reduced it to one channel.  As dst_format only; the write is PACKED. */
+       FKB_PIX_U8C1 = 12, FKB_PIX_F32C1 = 13 };
 
 /* Geometry of the ReadBack stage.  The crop rectangle is always applied (a chain without Crop
  * passes the whole frame as the rectangle).  NONE: output pixel (x,y) reads crop pixel (x,y).
@@ -127,6 +130,17 @@ enum {
     FKB_OP_SATCAST_U8 = 8,   /* SaturateCast<float3,uchar3>    (image_processing/saturate.h:25-36) f32 -> u8 */
     FKB_OP_RGB2YUV = 9,      /* ConvertRGBToYUV<p8bit,CR,CP> (color_conversion.h:176-199): ccm2 x (R,G,B), then adds
                                 yuv_add to (Y,Cb,Cr)                                                   u8 -> f32 */
+    FKB_OP_RGB2GRAY = 11,    /* RGB2Gray<I,O,CCIR_601> (color_conversion.h:46-79), also the second half of
+                                ColorConversion<COLOR_BGR2GRAY | COLOR_BGRA2GRAY> (after FKB_OP_REORDER_ZYX; :484-502):
+                                (x * 0.299f + y * 0.587f) + z * 0.114f in fp32, then rounded to the nearest integer, ties
+                                to even — for every output type: the reference rounds whenever std::is_signed_v<O> or
+                                std::is_unsigned_v<O> holds, and std::is_signed_v<float> does, so its float result is the
+                                rounded luminance too (std::nearbyint on the host, __float2int_rn on the device).
+                                v[0] != 0: the result is a uchar (O = uchar, from a uchar3 / uchar4 input only);
+                                v[0] == 0: it is a float (O = float).
+                                From here on the chain carries ONE channel: Mul / Add / Sub / Div use v[0] only,
+                                SaturateCast acts on that channel, and the destination is FKB_PIX_U8C1 / F32C1.
+                                At most once per chain, after the interpolation when the geometry is a RESIZE.     any */
     FKB_OP_ADD_ALPHA = 10    /* AddOpaqueAlpha<I,CD> (color_conversion.h:81-94), the second half of
                                 ColorConversion<COLOR_BGR2BGRA|COLOR_RGB2RGBA> (and, after FKB_OP_REORDER_ZYX, of
                                 COLOR_BGR2RGBA|COLOR_RGB2BGRA): appends a fourth channel v[0] = maxDepthValue<CD> (255

@@ -70,8 +70,9 @@ struct Lowered {
 
     Lowered(const ReadIOp<OutT, BATCH>& r, const WriteIOp<WT>& w) : st(r.st), wr(w) {
         static_assert(std::is_same_v<OutT, WT>, "the Write's InputType is not the OutputType of the last operation");
-        static_assert(std::is_same_v<WT, uchar3> || std::is_same_v<WT, float3> || std::is_same_v<WT, uchar4> || std::is_same_v<WT, float4>,
-                      "uchar3, float3, uchar4 and float4 are the pixel types the B200 kernels write");
+        static_assert(std::is_same_v<WT, uchar3> || std::is_same_v<WT, float3> || std::is_same_v<WT, uchar4> || std::is_same_v<WT, float4> ||
+                      std::is_same_v<WT, uchar> || std::is_same_v<WT, float>,
+                      "uchar3, float3, uchar4, float4 and (after a gray conversion) uchar and float are the pixel types the B200 kernels write");
         n_planes = r.params.activeThreads.z;
         chain.src_format = st.src_format;
         chain.geometry = !st.has_resize ? FKB_GEOM_NONE
@@ -79,7 +80,8 @@ struct Lowered {
                        : st.ar == AspectRatio::PRESERVE_AR_RN_EVEN ? FKB_GEOM_RESIZE_PRESERVE_AR_RN_EVEN
                        : st.ar == AspectRatio::PRESERVE_AR_LEFT ? FKB_GEOM_RESIZE_PRESERVE_AR_LEFT : FKB_GEOM_RESIZE_PRESERVE_AR;
         chain.dst_format = std::is_same_v<WT, float3> ? FKB_PIX_F32C3 : std::is_same_v<WT, uchar3> ? FKB_PIX_U8C3
-                         : std::is_same_v<WT, float4> ? FKB_PIX_F32C4 : FKB_PIX_U8C4;
+                         : std::is_same_v<WT, float4> ? FKB_PIX_F32C4 : std::is_same_v<WT, uchar4> ? FKB_PIX_U8C4
+                         : std::is_same_v<WT, float> ? FKB_PIX_F32C1 : FKB_PIX_U8C1;
         chain.write_kind = wr.write_kind;
         if (st.ops.size() > FKB_MAX_OPS) check(FKB_ERR_UNSUPPORTED);
         chain.n_ops = static_cast<uint32_t>(st.ops.size());

@@ -30,7 +30,8 @@ enum class BorderType : int { CONSTANT = 0, REPLICATE = 1, REFLECT = 2, WRAP = 3
 enum class PlanePolicy { PROCESS_ALL = 0, CONDITIONAL_WITH_DEFAULT = 1 };  // batch_operations.h:75
 // (color_conversion.h:408-426; the codes that discard the alpha channel of a four-channel source are the ones beside BGR<->RGB)
 enum class ColorConversionCodes { COLOR_BGR2RGB, COLOR_RGB2BGR, COLOR_BGRA2BGR, COLOR_RGBA2RGB, COLOR_BGRA2RGB, COLOR_RGBA2BGR, COLOR_BGRA2RGBA, COLOR_RGBA2BGRA,
-                                  COLOR_BGR2BGRA, COLOR_RGB2RGBA = COLOR_BGR2BGRA, COLOR_BGR2RGBA, COLOR_RGB2BGRA = COLOR_BGR2RGBA };
+                                  COLOR_BGR2BGRA, COLOR_RGB2RGBA = COLOR_BGR2BGRA, COLOR_BGR2RGBA, COLOR_RGB2BGRA = COLOR_BGR2RGBA,
+                                  COLOR_BGR2GRAY, COLOR_RGB2GRAY, COLOR_BGRA2GRAY, COLOR_RGBA2GRAY };
 
 namespace detail {
 struct SrcPlane { const void* data{nullptr}; uint pitch{0}, w{0}, h{0}; };
@@ -84,19 +85,24 @@ template <uint16_t C, typename I, typename O> constexpr bool isComputeIOp<Comput
 
 template <typename I, typename O>
 struct Cast {
-    static_assert((std::is_same_v<I, uchar3> && std::is_same_v<O, float3>) || (std::is_same_v<I, uchar4> && std::is_same_v<O, float4>),
-                  "the B200 kernels implement Cast<uchar3,float3> (and Cast<uchar4,float4> ahead of a discarded alpha channel)");
+    static_assert((std::is_same_v<I, uchar3> && std::is_same_v<O, float3>) || (std::is_same_v<I, uchar4> && std::is_same_v<O, float4>) ||
+                  (std::is_same_v<I, uchar> && std::is_same_v<O, float>),
+                  "the B200 kernels implement Cast<uchar3,float3>, Cast<uchar4,float4> and (after a gray conversion) Cast<uchar,float>");
     static constexpr auto build() { return ComputeIOp<FKB_OP_CAST_F32, I, O>{}; }
 };
 #define FKB_BINARY_OP(Name, CODE)                                                                                     \
     template <typename I, typename P = I, typename O = I>                                                             \
     struct Name {                                                                                                     \
-        static_assert((std::is_same_v<I, float3> || std::is_same_v<I, float4>) && std::is_same_v<P, I> && std::is_same_v<O, I>,      \
-                      "the B200 kernels implement " #Name "<float3> (and " #Name "<float4> ahead of a discarded alpha channel)");   \
+        static_assert((std::is_same_v<I, float3> || std::is_same_v<I, float4> || std::is_same_v<I, float>) && std::is_same_v<P, I> && std::is_same_v<O, I>, \
+                      "the B200 kernels implement " #Name "<float3>, " #Name "<float4> and (after a gray conversion) " #Name "<float>");   \
         static constexpr auto build(const I& params) {                                                                            \
-            ComputeIOp<CODE, I, O> op{float3{params.x, params.y, params.z}};                                                      \
-            if constexpr (cn<I> == 4) op.w = params.w;                                                                            \
-            return op;                                                                                                            \
+            if constexpr (cn<I> == 1) {                                                                                           \
+                return ComputeIOp<CODE, I, O>{float3{params, params, params}};                                                    \
+            } else {                                                                                                              \
+                ComputeIOp<CODE, I, O> op{float3{params.x, params.y, params.z}};                                                  \
+                if constexpr (cn<I> == 4) op.w = params.w;                                                                        \
+                return op;                                                                                                        \
+            }                                                                                                                     \
         }                                                                                                                         \
     };
 FKB_BINARY_OP(Mul, FKB_OP_MUL)
@@ -106,8 +112,9 @@ FKB_BINARY_OP(Div, FKB_OP_DIV)
 #undef FKB_BINARY_OP
 template <typename I, typename O>
 struct SaturateCast {
-    static_assert((std::is_same_v<I, float3> && std::is_same_v<O, uchar3>) || (std::is_same_v<I, float4> && std::is_same_v<O, uchar4>),
-                  "the B200 kernels implement SaturateCast<float3,uchar3> and SaturateCast<float4,uchar4>");
+    static_assert((std::is_same_v<I, float3> && std::is_same_v<O, uchar3>) || (std::is_same_v<I, float4> && std::is_same_v<O, uchar4>) ||
+                  (std::is_same_v<I, float> && std::is_same_v<O, uchar>),
+                  "the B200 kernels implement SaturateCast<float3,uchar3>, SaturateCast<float4,uchar4> and SaturateCast<float,uchar>");
     static constexpr auto build() { return ComputeIOp<FKB_OP_SATCAST_U8, I, O>{}; }
 };
 // A step of a chain that changes the number of channels without arithmetic: the alpha channel of a uchar4 / float4 is
@@ -119,13 +126,27 @@ struct RetypeIOp {
     bool reorder;          // BGRA2RGB / RGBA2BGR / BGR2RGBA / RGB2BGRA: the three colour channels are also reversed
     bool add_alpha{false};
     float alpha{0.f};      // maxDepthValue<CD>
+    bool gray{false};      // RGB2Gray: the three colour channels become one (a fourth channel of the input is ignored)
+};
+// RGB2Gray<I, O, GrayFormula::CCIR_601> (color_conversion.h:44-79): 0.299 x + 0.587 y + 0.114 z, rounded to the nearest integer.
+enum class GrayFormula { CCIR_601 };
+template <typename I, typename O = VBase<I>, GrayFormula GF = GrayFormula::CCIR_601>
+struct RGB2Gray {
+    static_assert((std::is_same_v<O, uchar> && (std::is_same_v<I, uchar3> || std::is_same_v<I, uchar4>)) ||
+                  (std::is_same_v<O, float> && (std::is_same_v<I, uchar3> || std::is_same_v<I, uchar4> || std::is_same_v<I, float3> || std::is_same_v<I, float4>)),
+                  "RGB2Gray takes uchar3 / uchar4 to uchar, or uchar3 / uchar4 / float3 / float4 to float");
+    static constexpr auto build() { return RetypeIOp<I, O>{false, false, 0.f, true}; }
 };
 template <ColorConversionCodes CODE, typename I, typename O = I, ColorDepth CD = ColorDepth::p8bit>
 struct ColorConversion {
     static constexpr bool swap4 = CODE == ColorConversionCodes::COLOR_BGRA2RGBA || CODE == ColorConversionCodes::COLOR_RGBA2BGRA;
     static constexpr bool swap3 = CODE == ColorConversionCodes::COLOR_BGR2RGB || CODE == ColorConversionCodes::COLOR_RGB2BGR || swap4;
     static constexpr bool add = CODE == ColorConversionCodes::COLOR_BGR2BGRA || CODE == ColorConversionCodes::COLOR_BGR2RGBA;
-    static constexpr bool drop = !swap3 && !add;
+    static constexpr bool gray = CODE == ColorConversionCodes::COLOR_BGR2GRAY || CODE == ColorConversionCodes::COLOR_RGB2GRAY ||
+                                 CODE == ColorConversionCodes::COLOR_BGRA2GRAY || CODE == ColorConversionCodes::COLOR_RGBA2GRAY;
+    static constexpr bool drop = !swap3 && !add && !gray;
+    static_assert(!gray || ((CODE == ColorConversionCodes::COLOR_BGR2GRAY || CODE == ColorConversionCodes::COLOR_RGB2GRAY) == (cn<I> == 3)),
+                  "BGR2GRAY / RGB2GRAY take three channels, BGRA2GRAY / RGBA2GRAY four");
     static_assert(!add || (std::is_same_v<I, uchar3> && std::is_same_v<O, uchar4>) || (std::is_same_v<I, float3> && std::is_same_v<O, float4>),
                   "BGR2BGRA / RGB2RGBA / BGR2RGBA / RGB2BGRA take uchar3 -> uchar4 or float3 -> float4");
     static_assert(!add || CD == ColorDepth::p8bit || CD == ColorDepth::fn8bit, "the appended alpha is that of an 8-bit depth (255) or of a normalised one (1)");
@@ -136,7 +157,12 @@ struct ColorConversion {
     static_assert(!drop || (std::is_same_v<I, uchar4> && std::is_same_v<O, uchar3>) || (std::is_same_v<I, float4> && std::is_same_v<O, float3>),
                   "BGRA2BGR / RGBA2RGB / BGRA2RGB / RGBA2BGR take uchar4 -> uchar3 or float4 -> float3");
     static constexpr auto build() {
-        if constexpr (swap3) return ComputeIOp<FKB_OP_REORDER_ZYX, I, O>{};
+        if constexpr (gray) {  // (color_conversion.h:484-502: a channel reversal first for the BGR orders)
+            auto op = RGB2Gray<I, O>::build();
+            op.reorder = CODE == ColorConversionCodes::COLOR_BGR2GRAY || CODE == ColorConversionCodes::COLOR_BGRA2GRAY;
+            return op;
+        }
+        else if constexpr (swap3) return ComputeIOp<FKB_OP_REORDER_ZYX, I, O>{};
         else if constexpr (add) return RetypeIOp<I, O>{CODE == ColorConversionCodes::COLOR_BGR2RGBA, true, CD == ColorDepth::p8bit ? 255.f : 1.f};
         else return RetypeIOp<I, O>{CODE == ColorConversionCodes::COLOR_BGRA2RGB || CODE == ColorConversionCodes::COLOR_RGBA2BGR};
     }
@@ -290,6 +316,7 @@ struct ReadIOp {
         detail::ReadState s = st;
         if (r.reorder) s.ops.push_back(detail::OpRec{FKB_OP_REORDER_ZYX, {{0.f, 0.f, 0.f, 0.f}}});
         if (r.add_alpha) s.ops.push_back(detail::OpRec{FKB_OP_ADD_ALPHA, {{r.alpha, 0.f, 0.f, 0.f}}});
+        if (r.gray) s.ops.push_back(detail::OpRec{FKB_OP_RGB2GRAY, {{std::is_same_v<O, uchar> ? 1.f : 0.f, 0.f, 0.f, 0.f}}});
         return ReadIOp<O, BATCH>(std::move(s));
     }
     template <uint16_t C, typename I, typename O>

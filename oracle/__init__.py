@@ -81,6 +81,10 @@ def load_ref() -> C.CDLL:
         lib.fklref_circular_updates.argtypes = [pp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, f32p, C.c_int, C.c_int, C.c_void_p]
         lib.fklref_add_alpha_crops.restype = C.c_int
         lib.fklref_add_alpha_crops.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, i32p, C.c_int, C.c_int, f32p, f32p, C.c_int, C.c_int, C.c_void_p]
+        lib.fklref_gray_image.restype = C.c_int
+        lib.fklref_gray_image.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int]
+        lib.fklref_gray_crops.restype = C.c_int
+        lib.fklref_gray_crops.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_int, C.c_int, C.c_void_p]
         lib.fklref_add_alpha_image.restype = C.c_int
         lib.fklref_add_alpha_image.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int]
         lib.fklref_rgba_crops.restype = C.c_int
@@ -256,6 +260,13 @@ def run_ref(wl, threads: int = 1):
         rc = lib.fklref_add_alpha_crops(wl.sources[0].ctypes.data, p0.src_w, p0.src_h, p0.src_pitch, (C.c_int32 * 20)(*flat), p0.dst_w, p0.dst_h,
                                         _f3(wl.extra["m3"]), (C.c_float * 4)(*wl.extra["m4"]), int(wl.extra["swap"]), int(wl.extra["f32"]),
                                         outs[0].ctypes.data)
+    elif wl.name == "gray_image":
+        rc = lib.fklref_gray_image(wl.sources[0].ctypes.data, p0.src_w, p0.src_h, p0.src_pitch, int(wl.extra["bgr"]), int(wl.extra["src4"]),
+                                   outs[0].ctypes.data, p0.dst_pitch)
+    elif wl.name == "gray_crops":
+        flat = [v for r in wl.extra["rects"] for v in r]
+        rc = lib.fklref_gray_crops(wl.sources[0].ctypes.data, p0.src_w, p0.src_h, p0.src_pitch, (C.c_int32 * 20)(*flat), p0.dst_w, p0.dst_h,
+                                   C.c_float(wl.extra["mul"]), int(wl.extra["bgr"]), int(wl.extra["f32"]), outs[0].ctypes.data)
     elif wl.name == "add_alpha_image":
         rc = lib.fklref_add_alpha_image(wl.sources[0].ctypes.data, p0.src_w, p0.src_h, p0.src_pitch, int(wl.extra["swap"]),
                                         outs[0].ctypes.data, p0.dst_pitch)

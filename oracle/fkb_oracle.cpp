@@ -121,6 +121,12 @@ inline V3 apply_ops(V3 v, const fkb_chain_desc& ch, const fkb_plane_desc& pl, ui
         case FKB_OP_SATCAST_U8:
             for (int c = 0; c < nc; ++c) v.c[c] = static_cast<float>(sat_u8(v.c[c]));
             break;
+        case FKB_OP_RGB2GRAY: {  // RGB2Gray<I,O,CCIR_601>::exec (color_conversion.h:57-78): luminance, then std::nearbyint — also
+                                 // for O = float, because std::is_signed_v<float> is true and that branch comes first (:65-70)
+            const float l = (v.c[0] * 0.299f) + (v.c[1] * 0.587f) + (v.c[2] * 0.114f);
+            v.c[0] = std::nearbyint(l);
+            break;
+        }
         case FKB_OP_ADD_ALPHA:  // AddOpaqueAlpha::exec (color_conversion.h:89-92): the input's channels, then maxDepthValue<CD>
             v.c[3] = op.v[0];
             break;
@@ -270,7 +276,11 @@ void run_plane(const fkb_chain_desc& ch, const fkb_plane_desc& pl) {
         for (uint32_t x = 0; x < pl.dst_w; ++x) {
             const V3 v = pixel(ch, pl, static_cast<int>(x), static_cast<int>(y));
             uint8_t* row = dst + static_cast<size_t>(y) * pl.dst_pitch;
-            if (channels(ch) == 4) {  // PerThreadWrite / TensorWrite of uchar4 or float4
+            if (ch.dst_format == FKB_PIX_U8C1) {  // PerThreadWrite / TensorWrite of uchar: the one channel a gray conversion leaves
+                row[x] = static_cast<uint8_t>(v.c[0]);
+            } else if (ch.dst_format == FKB_PIX_F32C1) {
+                reinterpret_cast<float*>(row)[x] = v.c[0];
+            } else if (channels(ch) == 4) {  // PerThreadWrite / TensorWrite of uchar4 or float4
                 if (ch.dst_format == FKB_PIX_F32C4) {
                     float* q = reinterpret_cast<float*>(row) + static_cast<size_t>(x) * 4;
                     for (int c = 0; c < 4; ++c) q[c] = v.c[c];

@@ -367,6 +367,50 @@ int fklref_add_alpha_image(const uint8_t* frame, int w, int h, int pitch, int sw
     return 0;
 }
 
+}  // extern "C"
+// PerThreadRead<uchar3 | uchar4> -> ColorConversion<COLOR_{RGB,BGR,RGBA,BGRA}2GRAY, I, uchar> -> PerThreadWrite<uchar>
+template <ColorConversionCodes CODE, typename I>
+static int gray_image(const uint8_t* frame, int w, int h, int pitch, uint8_t* out, int opitch) {
+    CpuStream stream;
+    const Ptr2D<I> in(reinterpret_cast<I*>(const_cast<uint8_t*>(frame)), w, h, pitch, MemType::Host, 0);
+    const Ptr2D<uchar> o(reinterpret_cast<uchar*>(out), w, h, opitch, MemType::Host, 0);
+    executeOperations<CpuDPP>(stream, PerThreadRead<ND::_2D, I>::build(in), ColorConversion<CODE, I, uchar>::build(), PerThreadWrite<ND::_2D, uchar>::build(o));
+    return 0;
+}
+extern "C" int fklref_gray_image(const uint8_t* frame, int w, int h, int pitch, int bgr, int src4, uint8_t* out, int opitch) {
+    if (src4) return bgr ? gray_image<ColorConversionCodes::COLOR_BGRA2GRAY, uchar4>(frame, w, h, pitch, out, opitch)
+                         : gray_image<ColorConversionCodes::COLOR_RGBA2GRAY, uchar4>(frame, w, h, pitch, out, opitch);
+    return bgr ? gray_image<ColorConversionCodes::COLOR_BGR2GRAY, uchar3>(frame, w, h, pitch, out, opitch)
+               : gray_image<ColorConversionCodes::COLOR_RGB2GRAY, uchar3>(frame, w, h, pitch, out, opitch);
+}
+// Five crops of one frame -> Resize(IGNORE_AR) -> ColorConversion<COLOR_RGB2GRAY | COLOR_BGR2GRAY, float3, float> -> Mul<float>
+// -> [SaturateCast<float, uchar> -> TensorWrite<uchar> | TensorWrite<float>]
+template <ColorConversionCodes CODE>
+static int gray_crops(const uint8_t* frame, int w, int h, int pitch, const int32_t* rects, int dw, int dh, float mul, int f32, void* out) {
+    CpuStream stream;
+    constexpr size_t B = 5;
+    std::array<Rect, B> crops;
+    for (size_t i = 0; i < B; ++i) crops[i] = Rect(rects[4 * i], rects[4 * i + 1], rects[4 * i + 2], rects[4 * i + 3]);
+    const auto read = PerThreadRead<ND::_2D, uchar3>::build(wrap_frame(frame, w, h, pitch));
+    const auto crop = Crop<>::build(crops);
+    const auto resize = Resize<InterpolationType::INTER_LINEAR>::build(Size(dw, dh));
+    const auto gray = ColorConversion<CODE, float3, float>::build();
+    const auto scale = Mul<float>::build(mul);
+    if (f32) {
+        const Tensor<float> t(static_cast<float*>(out), dw, dh, B, 1, MemType::Host, 0);
+        executeOperations<CpuDPP>(stream, read, crop, resize, gray, scale, TensorWrite<float>::build(t));
+    } else {
+        const Tensor<uchar> t(static_cast<uchar*>(out), dw, dh, B, 1, MemType::Host, 0);
+        executeOperations<CpuDPP>(stream, read, crop, resize, gray, scale, SaturateCast<float, uchar>::build(), TensorWrite<uchar>::build(t));
+    }
+    return 0;
+}
+extern "C" int fklref_gray_crops(const uint8_t* frame, int w, int h, int pitch, const int32_t* rects, int dw, int dh, float mul, int bgr, int f32, void* out) {
+    return bgr ? gray_crops<ColorConversionCodes::COLOR_BGR2GRAY>(frame, w, h, pitch, rects, dw, dh, mul, f32, out)
+               : gray_crops<ColorConversionCodes::COLOR_RGB2GRAY>(frame, w, h, pitch, rects, dw, dh, mul, f32, out);
+}
+extern "C" {
+
 // Four frames -> Resize(IGNORE_AR) -> Mul -> TensorTSplit<float3> into a colour-plane-transposed tensor
 // (memory_operations.h:214-241): all R planes, then all G planes, then all B planes.
 int fklref_resize_tsplit_f32(const uint8_t* const* frames, int w, int h, int pitch, int dw, int dh, const float* mul, float* out) {

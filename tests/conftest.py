@@ -42,7 +42,7 @@ GOLDEN_CASES = ["readme_crops_full", "readme_crops_pitched", "vertical_fusion_sm
                 "conditional_resize", "conditional_pointwise", "tsplit_resize", "split_planes_f32", "split_planes_u8",
                 "nv21_limited_bt709", "uyvy_full_bt2020", "rgb_to_nv12", "rgb_to_nv21", "rgb_to_uyvy", "bgra_crops_swap",
                 "rgba_crops_u8", "rgba_crops_f32_reorder", "p010_limited_bt2020", "p210_full_bt2020", "y210_full_bt601",
-                "add_alpha_crops_u8_swap", "add_alpha_image"]
+                "add_alpha_crops_u8_swap", "add_alpha_image", "gray_image_bgra", "gray_crops_u8", "gray_crops_f32_bgr"]
 
 
 def reference_kats():
@@ -59,10 +59,13 @@ def conversion_kat_workload(case):
     cin, cout, n = len(case["in"][0]), len(case["out"][0]), len(case["in"])
     ops = {"COLOR_BGR2BGRA": [W.op(abi.OP_ADD_ALPHA, (255.0, 0.0, 0.0))], "COLOR_BGR2RGB": [W.op(abi.OP_REORDER_ZYX)],
            "COLOR_BGR2RGBA": [W.op(abi.OP_REORDER_ZYX), W.op(abi.OP_ADD_ALPHA, (255.0, 0.0, 0.0))],
-           "COLOR_BGRA2RGB": [W.op(abi.OP_REORDER_ZYX)]}[case["code"]]
+           "COLOR_BGRA2RGB": [W.op(abi.OP_REORDER_ZYX)],
+           "COLOR_RGB2GRAY": [W.op(abi.OP_RGB2GRAY, (1.0, 0.0, 0.0))],
+           "COLOR_BGR2GRAY": [W.op(abi.OP_REORDER_ZYX), W.op(abi.OP_RGB2GRAY, (1.0, 0.0, 0.0))],
+           "COLOR_BGRA2GRAY": [W.op(abi.OP_REORDER_ZYX), W.op(abi.OP_RGB2GRAY, (1.0, 0.0, 0.0))]}[case["code"]]
     src = np.zeros(16, np.uint8)
     src[:cin * n] = np.array(case["in"], np.uint8).ravel()
-    ch = W.chain(abi.PIX_U8C4 if cin == 4 else abi.PIX_U8C3, abi.GEOM_NONE, abi.PIX_U8C4 if cout == 4 else abi.PIX_U8C3, abi.WRITE_PACKED, ops)
+    ch = W.chain(abi.PIX_U8C4 if cin == 4 else abi.PIX_U8C3, abi.GEOM_NONE, {4: abi.PIX_U8C4, 3: abi.PIX_U8C3, 1: abi.PIX_U8C1}[cout], abi.WRITE_PACKED, ops)
     wl = W.Workload(case["code"], [ch], [src], [cout * n], [W.PlaneSpec(0, 0, 0, n, 1, 16, (0, 0, n, 1), n, 1, cout * n)])
     return wl, np.array(case["out"], np.uint8).ravel()
 

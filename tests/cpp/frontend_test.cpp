@@ -126,6 +126,54 @@ static void test_thread_fusion() {
     report("TF::ENABLED == TF::DISABLED (crop + resize chain)", std::memcmp(t0.ptrPinned().data, t1.ptrPinned().data, 64 * 48 * 2 * 12) == 0);
 }
 
+// ---- gray conversions: one-channel outputs -------------------------------------------------------------------------
+static void test_gray() {
+    Stream stream;
+    // (1) a whole uchar4 image: ColorConversion<COLOR_BGRA2GRAY, uchar4, uchar> -> PerThreadWrite<_2D, uchar>
+    const uint W = 322, H = 45;
+    Ptr2D<uchar4> in4(W, H);
+    Ptr2D<uchar> g(W, H);
+    fill_random(in4, 31);
+    in4.upload(stream);
+    executeOperations<TransformDPP<>>(stream, PerThreadRead<ND::_2D, uchar4>::build(in4),
+        ColorConversion<ColorConversionCodes::COLOR_BGRA2GRAY, uchar4, uchar>::build(), PerThreadWrite<ND::_2D, uchar>::build(g));
+    g.download(stream);
+    // (2) crops of a uchar3 image: Resize -> RGB2GRAY on float3 -> Mul<float> -> SaturateCast<float, uchar> -> TensorWrite<uchar>
+    Ptr2D<uchar3> in3(640, 360);
+    fill_random(in3, 32);
+    in3.upload(stream);
+    constexpr std::array<Rect, 3> crops{Rect(30, 20, 200, 120), Rect(300, 60, 64, 200), Rect(0, 0, 640, 360)};
+    Tensor<uchar> t(96, 64, 3);
+    executeOperations<TransformDPP<>>(stream, PerThreadRead<ND::_2D, uchar3>::build(in3), Crop<>::build(crops),
+        Resize<InterpolationType::INTER_LINEAR>::build(Size(96, 64)), ColorConversion<ColorConversionCodes::COLOR_RGB2GRAY, float3, float>::build(),
+        Mul<float>::build(1.25f), SaturateCast<float, uchar>::build(), TensorWrite<uchar>::build(t));
+    t.download(stream);
+    stream.sync();
+
+    fkb_chain_desc c1{};
+    c1.src_format = FKB_PIX_U8C4; c1.geometry = FKB_GEOM_NONE; c1.dst_format = FKB_PIX_U8C1; c1.write_kind = FKB_WRITE_PACKED;
+    c1.n_ops = 2; c1.ops[0] = op(FKB_OP_REORDER_ZYX); c1.ops[1] = op(FKB_OP_RGB2GRAY, 1.f);
+    const uint gp = g.dims().pitch;
+    std::vector<uint8_t> want1(static_cast<size_t>(gp) * H, 0);
+    fkb_plane_desc d1{};
+    const auto r4 = in4.ptrPinned();
+    d1.src = r4.data; d1.src_pitch = r4.dims.pitch; d1.src_w = W; d1.src_h = H; d1.crop_w = W; d1.crop_h = H;
+    d1.dst = want1.data(); d1.dst_w = W; d1.dst_h = H; d1.dst_pitch = gp;
+    fkb_oracle_run(&c1, 1, &d1, 1, 1);
+    bool ok = true;
+    for (uint y = 0; y < H && ok; ++y) ok = std::memcmp(want1.data() + static_cast<size_t>(y) * gp, reinterpret_cast<uint8_t*>(g.ptrPinned().data) + static_cast<size_t>(y) * gp, W) == 0;
+    report("COLOR_BGRA2GRAY uchar4 -> uchar image", ok);
+
+    fkb_chain_desc c2{};
+    c2.src_format = FKB_PIX_U8C3; c2.geometry = FKB_GEOM_RESIZE_IGNORE_AR; c2.dst_format = FKB_PIX_U8C1; c2.write_kind = FKB_WRITE_PACKED;
+    c2.n_ops = 3; c2.ops[0] = op(FKB_OP_RGB2GRAY); c2.ops[1] = op(FKB_OP_MUL, 1.25f, 1.25f, 1.25f); c2.ops[2] = op(FKB_OP_SATCAST_U8);
+    std::vector<uint8_t> want2(96 * 64 * 3);
+    std::vector<fkb_plane_desc> planes;
+    for (int i = 0; i < 3; ++i) planes.push_back(host_plane(in3, crops[i], 96, 64, want2.data() + i * 96 * 64, 96, c2.geometry));
+    fkb_oracle_run(&c2, 1, planes.data(), 3, 1);
+    report("crops -> Resize -> COLOR_RGB2GRAY -> Mul<float> -> uchar tensor", std::memcmp(want2.data(), t.ptrPinned().data, want2.size()) == 0);
+}
+
 // ---- vertical fusion: Cast, Mul, Add, Div, BGR2RGB, SaturateCast on every pixel ----------------------------------
 static void test_vertical_fusion() {
     Stream stream;
@@ -648,6 +696,7 @@ int main() {
     test_readme();
     test_vertical_fusion();
     test_thread_fusion();
+    test_gray();
     test_nv12();
     test_yuv<PixelFormat::NV21, ColorRange::Limited, ColorPrimitives::bt601>("NV21, limited range bt601", FKB_PIX_NV21, FKB_RANGE_LIMITED, FKB_PRIMITIVES_BT601);
     test_yuv<PixelFormat::UYVY, ColorRange::Full, ColorPrimitives::bt2020>("UYVY, full range bt2020", FKB_PIX_UYVY, FKB_RANGE_FULL, FKB_PRIMITIVES_BT2020);

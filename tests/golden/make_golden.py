@@ -55,6 +55,10 @@ CASES = {
     "bgra_crops_swap": ("bgra_crops", {"swap": True, "w": 160, "h": 100, "dst": [48, 40]}),
     "add_alpha_crops_u8_swap": ("add_alpha_crops", {"swap": True, "w": 480, "h": 270, "dst": [32, 24]}),
     "add_alpha_image": ("add_alpha_image", {"w": 162, "h": 90}),
+    "gray_image_bgra": ("gray_image", {"bgr": True, "src4": True, "w": 162, "h": 90}),
+    "gray_crops_u8": ("gray_crops", {"w": 480, "h": 270, "dst": [32, 24], "rects": [[0, 0, 120, 40], [100, 200, 60, 40], [400, 20, 30, 50], [300, 100, 30, 30], [40, 40, 40, 40]]}),
+    "gray_crops_f32_bgr": ("gray_crops", {"bgr": True, "f32": True, "w": 480, "h": 270, "dst": [32, 24],
+                                          "rects": [[0, 0, 120, 40], [100, 200, 60, 40], [400, 20, 30, 50], [300, 100, 30, 30], [40, 40, 40, 40]]}),
     "rgba_crops_u8": ("rgba_crops", {"w": 480, "h": 270, "dst": [32, 32], "rects": [[0, 0, 120, 40], [100, 200, 60, 40], [400, 20, 30, 50], [300, 100, 30, 30], [40, 40, 40, 40]]}),
     "rgba_crops_f32_reorder": ("rgba_crops", {"reorder": True, "f32": True, "w": 480, "h": 270, "dst": [32, 32],
                                               "rects": [[0, 0, 120, 40], [100, 200, 60, 40], [400, 20, 30, 50], [300, 100, 30, 30], [40, 40, 40, 40]]}),

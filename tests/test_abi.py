@@ -30,7 +30,7 @@ def test_library_exports_every_declared_symbol():
     for n in names:
         assert hasattr(lib, n), f"{n} is declared in fkb.h but not exported"
         assert n in abi.SIGNATURES, f"{n} has no ctypes signature"
-    assert lib.fkb_abi_version() == 2
+    assert lib.fkb_abi_version() == 3
 
 
 def test_struct_layout_matches_header():

@@ -86,6 +86,12 @@ SMALL = {
     "add_alpha_crops_f32_swap": lambda: W.add_alpha_crops(swap=True, f32=True, w=333, h=211, dst=(77, 45)),
     "add_alpha_image": lambda: W.add_alpha_image(),
     "add_alpha_image_swap": lambda: W.add_alpha_image(swap=True, w=1001, h=37),
+    # gray conversions: one-channel outputs (uchar image; float / uchar tensors after a resize)
+    "gray_image": lambda: W.gray_image(),
+    "gray_image_bgra_odd": lambda: W.gray_image(bgr=True, src4=True, w=1001, h=37),
+    "gray_image_4k": lambda: W.gray_image(bgr=True, w=3840, h=2160),
+    "gray_crops_u8": lambda: W.gray_crops(),
+    "gray_crops_f32_bgr": lambda: W.gray_crops(bgr=True, f32=True, w=333, h=211, dst=(77, 45), rects=((0, 0, 333, 211), (5, 7, 100, 60), (200, 100, 50, 111), (300, 200, 33, 11), (100, 50, 20, 20))),
     "bgra_crops": lambda: W.bgra_crops(),
     "batched_uchar4": lambda: W.batched_crop_resize(n_frames=4, crops_per_frame=8, w=960, h=540, src4=True),
     "bgra_crops_swap": lambda: W.bgra_crops(swap=True, w=333, h=97, dst=(111, 50)),

@@ -226,6 +226,8 @@ THIN_CROPS = ((300, 125, 1, 500), (400, 125, 500, 1), (10, 10, 2, 700), (530, 27
     W.readme_crops(crops=THIN_CROPS, dst=(224, 224)),
     W.add_alpha_crops(), W.add_alpha_crops(swap=True), W.add_alpha_crops(f32=True), W.add_alpha_crops(swap=True, f32=True),
     W.add_alpha_image(), W.add_alpha_image(swap=True),
+    W.gray_image(), W.gray_image(bgr=True), W.gray_image(src4=True), W.gray_image(bgr=True, src4=True, w=1001, h=37),
+    W.gray_crops(), W.gray_crops(bgr=True), W.gray_crops(f32=True), W.gray_crops(bgr=True, f32=True, w=333, h=211, dst=(77, 45), rects=((0, 0, 333, 211), (5, 7, 100, 60), (200, 100, 50, 111), (300, 200, 33, 11), (100, 50, 20, 20))),
     W.bgra_crops(), W.bgra_crops(swap=True), W.split_planes(), W.split_planes(f32=False), W.tsplit_resize(), W.conditional_resize(), W.conditional_resize(used=0), W.conditional_resize(used=8), W.conditional_pointwise(),
 ], ids=lambda w: w.name + w.description[-7:].replace(" ", "_"))
 def test_oracle_matches_reference_backend(wl):

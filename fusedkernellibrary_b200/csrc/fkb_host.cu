@@ -273,7 +273,7 @@ void classify(const fkb_chain_desc& ch, PlaneRec& r, const Tuning& tune) {
     if (ch.geometry == FKB_GEOM_NONE) {
         if ((r.crop_x * 3u) & 15u) return;  // the staged row must start on a 16-byte boundary
         // one row segment per step: 16 pixels per lane (uchar3 out) or 4 pixels per lane in two passes (float3 out)
-        r.tile_w = std::min(r.dst_w, f32 ? 256u : 512u);
+        r.tile_w = std::min(r.dst_w, f32 ? kMaxTileW : kPointTileU8);
         r.kclass = KCLASS_POINT;
         if (!f32) {  // uchar3 -> uchar3 through per-channel ops only: table lookups (lut_kernel)
             bool per_channel = true;
@@ -287,7 +287,7 @@ void classify(const fkb_chain_desc& ch, PlaneRec& r, const Tuning& tune) {
             // a crop so thin that its resized image has no pixel: every row of the plane is background, which the staged
             // kernel writes without touching the source (its scale factors may be infinite and are not used)
             r.x1 = 0; r.x2 = -1;  // (an empty row range is recorded as an empty column range: no column has a footprint)
-            r.tile_w = std::min(r.dst_w, 256u);
+            r.tile_w = std::min(r.dst_w, kMaxTileW);
             r.kclass = KCLASS_RESIZE;
             r.tiles_x = (r.dst_w + r.tile_w - 1) / r.tile_w;
             return;
@@ -301,7 +301,7 @@ void classify(const fkb_chain_desc& ch, PlaneRec& r, const Tuning& tune) {
         // this small (an enlargement by 2^24) a weight could underflow there
         if (!(r.fx >= 5.9604645e-8f) || !(r.fy >= 5.9604645e-8f)) return;
         // widest segment (at most 8 columns per lane) whose source columns fit one staged row
-        uint32_t tw = std::min(r.dst_w, 256u);
+        uint32_t tw = std::min(r.dst_w, kMaxTileW);
         for (;;) {
             const uint32_t cols = std::min<uint32_t>(r.crop_w, static_cast<uint32_t>(std::ceil((tw - 1) * static_cast<double>(r.fx))) + 3u);
             if (cols * (src4 ? 4u : 3u) + 63u <= kInRowBytes) break;
@@ -525,7 +525,7 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
     }
     // Items of the staged kernel; when every plane of the launch has the same shape (the batched crop-resize case) the
     // kernel finds an item's plane by division instead of a search.
-    const uint32_t resident_warps = 2u * kStagedWarps * static_cast<uint32_t>(sms);
+    const uint32_t resident_warps = kStagedCtasPerSm * kStagedWarps * static_cast<uint32_t>(sms);
     const uint32_t rpi = tune.rows_per_item ? std::min(tune.rows_per_item, kMaxRowsPerItem) : rows_per_item(row_segments, resident_warps);
     bool same_shape = n_planes > 0;
     for (uint32_t z = 0; z < n_planes && same_shape; ++z) {
@@ -571,7 +571,7 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
     L.lp.n_tiles = n_tiles;
     L.lp.tiles_per_plane = (same_shape && first_count) ? first_count : 0;
     if (n_tiles) {
-        L.staged_grid = std::min<uint32_t>(n_tiles, 2u * static_cast<uint32_t>(sms));
+        L.staged_grid = std::min<uint32_t>(n_tiles, kStagedCtasPerSm * static_cast<uint32_t>(sms));
         ++L.kernels;
     }
     L.lp.n_lut_units = n_lut_units;

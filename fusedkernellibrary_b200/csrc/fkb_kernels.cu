@@ -455,20 +455,19 @@ extern __shared__ __align__(128) uint8_t smem_raw[];
 struct WarpSlice {
     uint32_t base;  // offset of this warp's slice in smem_raw
     const PlaneRec* pl;
-    // mbarriers 0,1: the two stages of RESIZE items; 2..5: the four stages of POINT items (separate phase counters)
+    // mbarriers 0..3: the (up to four) stages of RESIZE items; 4..7: the four stages of POINT items
     __device__ __forceinline__ uint64_t* bar(uint32_t s) const { return reinterpret_cast<uint64_t*>(smem_raw + base) + s; }
-    __device__ __forceinline__ uint32_t in(uint32_t s) const { return base + kSliceHeader + s * (2 * kInRowBytes); }
+    __device__ __forceinline__ uint32_t in0() const { return base + kSliceHeader; }
     __device__ __forceinline__ uint32_t in4(uint32_t s) const { return base + kSliceHeader + s * kInRowBytes; }
-    __device__ __forceinline__ uint32_t out(uint32_t s) const { return base + kSliceHeader + 4 * kInRowBytes + s * kOutSlotBytes; }
+    __device__ __forceinline__ uint32_t out(uint32_t s) const { return base + kSliceHeader + kInRegionBytes + s * kOutSlotBytes; }
 };
 __device__ __forceinline__ WarpSlice warp_slice(uint32_t base) {
     WarpSlice w;
     w.base = base;
-    w.pl = reinterpret_cast<const PlaneRec*>(smem_raw + base + 48);
+    w.pl = reinterpret_cast<const PlaneRec*>(smem_raw + base + 64);
     return w;
 }
-static_assert(48 + sizeof(PlaneRec) <= kSliceHeader, "slice header");
-static_assert(kSliceHeader + 4 * kInRowBytes + 2 * kOutSlotBytes == kSliceBytes, "slice layout");
+static_assert(64 + sizeof(PlaneRec) <= kSliceHeader, "slice header");
 
 // Plane of staged tile t (warp-uniform t; called by all lanes of a warp).
 __device__ __forceinline__ uint32_t tile_to_plane(const LaunchParams& p, uint32_t t, uint32_t& local) {
@@ -589,8 +588,8 @@ __device__ __forceinline__ bool point_item(const LaunchParams& p, const WarpSlic
     uint8_t* gdst = pl.dst + static_cast<size_t>(oy0) * pl.dst_pitch + static_cast<size_t>(ox) * (F32 ? 12u : 3u);
     auto issue = [&](uint32_t r, uint32_t s) {
         if (lane == 0) {
-            mbar_arrive_expect_tx(w.bar(2 + s), in_bytes);
-            bulk_load(smem_raw + w.in4(s), gsrc + static_cast<size_t>(r) * src_pitch, in_bytes, w.bar(2 + s));
+            mbar_arrive_expect_tx(w.bar(4 + s), in_bytes);
+            bulk_load(smem_raw + w.in4(s), gsrc + static_cast<size_t>(r) * src_pitch, in_bytes, w.bar(4 + s));
         }
     };
     auto compute = [&](uint32_t in_s, uint32_t out_s) {
@@ -657,7 +656,7 @@ __device__ __forceinline__ bool point_item(const LaunchParams& p, const WarpSlic
         const uint32_t s = k & 3u, o = k & 1u;
         if (lane == 0) bulk_wait_read_1();  // the store that read w.out(o) two rows ago is done with it
         if (r + AHEAD < nr) issue(r + AHEAD, (k + AHEAD) & 3u);  // into the stage of the row computed just before
-        const bool landed = mbar_wait_bounded(w.bar(2 + s), (k >> 2) & 1u, p.wait_limit_ns);
+        const bool landed = mbar_wait_bounded(w.bar(4 + s), (k >> 2) & 1u, p.wait_limit_ns);
         if (__any_sync(0xffffffffu, !landed)) return false;
         compute(w.in4(s), w.out(o));
         store_row(gdst + static_cast<size_t>(r) * dst_pitch, w.out(o), row_bytes, lane);
@@ -701,12 +700,12 @@ __device__ __forceinline__ float post_scalar(float r, float m, float a) {
 
 template <bool F32, int KIND, bool PLANAR = false, bool SRC4 = false>
 __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSlice& w, uint32_t ox, uint32_t oy0,
-                                            uint32_t ow, uint32_t nr, uint32_t& k, uint32_t lane) {
+                                            uint32_t ow, uint32_t nr, uint32_t& ph, uint32_t lane) {
     static_assert(F32 || !PLANAR, "planar rows are float rows");
     constexpr uint32_t FULL = 0xffffffffu;
     constexpr uint32_t SP = SRC4 ? 4u : 3u;                           // bytes per source pixel (uchar4: the alpha byte is skipped)
     constexpr uint32_t ELT = PLANAR ? 4u : F32 ? 12u : 3u;            // bytes between columns of a staged output row
-    constexpr uint32_t DEAD = PLANAR ? 1024u : kOutRowBytes;          // where columns that do not exist are stored
+    constexpr uint32_t DEAD = PLANAR ? kMaxTileW * 4u : kOutRowBytes;          // where columns that do not exist are stored
     const PlaneRec& pl = *w.pl;
     const fkb_chain_desc& ch = p.chains[pl.chain];
     const bool par = ch.geometry >= FKB_GEOM_RESIZE_PRESERVE_AR;
@@ -725,6 +724,12 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
     const uint32_t a0 = g0 & ~15u, shift = g0 - a0;
     const uint32_t row_bytes = ((g1 + 15u) & ~15u) - a0;
     if (row_bytes + 32u > kInRowBytes) return false;  // the host lowering guarantees the footprint fits
+    // The staged-row region is cut into as many stages as this item's footprint lets fit, two to four, each of two rows
+    // `rs` bytes apart: row r lands in stage r mod ns, and the source rows of row r + ns are requested as soon as row r
+    // has been computed, so a load is in flight for ns - 1 row times before it is waited for.
+    const uint32_t rs = row_bytes + 16u;
+    const uint32_t ns = min(4u, kInRegionBytes / (2u * rs));
+    const uint32_t in0 = w.in0();
 
     // per-row state, row r of the item in lane r: the two source rows (as an offset from the crop's first row, in
     // units of 16 bytes: staged sources have pitches that are multiples of 16) and the vertical weights times 2^127
@@ -738,27 +743,21 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
     const float wy0_l = __fmul_rn(ay_l.w0, kTapScale), wy1_l = __fmul_rn(ay_l.w1, kTapScale);
 
     const uint8_t* gsrc = pl.src + static_cast<size_t>(pl.crop_y) * pl.src_pitch + a0;
-    // Lane 0 requests row r's two source rows (r0, r1: offsets in units of 16 bytes) into stage s.  Always two staged rows
-    // (the second repeats the first where the reference clamps y2), so that the second row sits at a fixed distance
-    // from the first.
+    // One lane requests row r's two source rows (r0, r1: offsets in units of 16 bytes) into stage s.  Always two staged
+    // rows (the second repeats the first where the reference clamps y2), so that the second row sits at a fixed
+    // distance from the first.
     auto load_rows = [&](uint32_t r, uint32_t s, uint32_t r0, uint32_t r1) {
         const bool in = (in_mask >> r) & 1u;
+        const uint32_t at = in0 + s * (2u * rs);
         mbar_arrive_expect_tx(w.bar(s), (in ? 2u * row_bytes : 0u) + p.test_extra_tx);
         if (in) {
-            bulk_load(smem_raw + w.in(s), gsrc + static_cast<size_t>(r0) * 16u, row_bytes, w.bar(s));
-            bulk_load(smem_raw + w.in(s) + kInRowBytes, gsrc + static_cast<size_t>(r1) * 16u, row_bytes, w.bar(s));
+            bulk_load(smem_raw + at, gsrc + static_cast<size_t>(r0) * 16u, row_bytes, w.bar(s));
+            bulk_load(smem_raw + at + rs, gsrc + static_cast<size_t>(r1) * 16u, row_bytes, w.bar(s));
         }
     };
-    // The source rows of the first two output rows are requested before the rest of the set-up, which then overlaps
-    // their latency (both stages were last read by rows this warp has finished).
-    {
-        const uint32_t r0a = __shfl_sync(FULL, row0_l, 0), r1a = __shfl_sync(FULL, row1_l, 0);
-        const uint32_t r0b = __shfl_sync(FULL, row0_l, 1), r1b = __shfl_sync(FULL, row1_l, 1);
-        if (lane == 0) {
-            load_rows(0u, k & 1u, r0a, r1a);
-            if (nr > 1) load_rows(1u, (k + 1u) & 1u, r0b, r1b);
-        }
-    }
+    // The source rows of the first ns output rows are requested before the rest of the set-up, which then overlaps their
+    // latency (every stage was last read by a row this warp has finished): lane i requests row i, whose state it holds.
+    if (lane < ns && lane < nr) load_rows(lane, lane, row0_l, row1_l);
 
     // per-column state of this lane: staged-row byte offset of the tap pair and the horizontal weights.  Where a column
     // goes in the output row follows from its group: group j starts 32 j columns after the lane's first column, except
@@ -785,8 +784,8 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
     // output-row offset of this lane's column of group j
     auto ocol = [&](int j) { return j + 1 == nj ? olast : obase + static_cast<uint32_t>(j) * (32u * ELT); };
     // Offset (in a staged row) of the crop's last column when a tap pair reaches one past it; that column is then
-    // duplicated into the next three bytes.  Otherwise the copy is aimed at the unused tail of the staged row.
-    const uint32_t rep_off = replicate ? static_cast<uint32_t>(crop_w - 1 - c_lo) * SP + shift : kInRowBytes - 8u;
+    // duplicated into the next three bytes (inside the 16 spare bytes every staged row has).
+    const uint32_t rep_off = replicate ? static_cast<uint32_t>(crop_w - 1 - c_lo) * SP + shift : 0u;
     const uint32_t dst_pitch = pl.dst_pitch;
     uint8_t* gdst = pl.dst + static_cast<size_t>(oy0) * dst_pitch + static_cast<size_t>(ox) * ELT;
 
@@ -872,6 +871,7 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
     // two groups of columns (j, j+1) of the current row
     auto pair = [&](int j, uint32_t in_s, uint32_t out_s, f2 wy0, f2 wy1) {
         const uint32_t a0p = in_s + boff[j], a1p = in_s + boff[j + 1];
+        const uint32_t a0q = a0p + rs, a1q = a1p + rs;  // the same columns in the second staged row
         const f2 wx0p = {wx0[j], wx0[j + 1]}, wx1p = {wx1[j], wx1[j + 1]};
         const f2 w00 = mul2(wx0p, wy0), w10 = mul2(wx1p, wy0), w01 = mul2(wx0p, wy1), w11 = mul2(wx1p, wy1);
         f2 v[3];
@@ -880,8 +880,8 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
             // taps of the two columns: (x1,y1) (x1+1,y1) (x1,y2) (x1+1,y2), each b * 2^-149
             const f2 p00 = {tap_subnormal(a0p + c), tap_subnormal(a1p + c)};
             const f2 p10 = {tap_subnormal(a0p + SP + c), tap_subnormal(a1p + SP + c)};
-            const f2 p01 = {tap_subnormal(a0p + kInRowBytes + c), tap_subnormal(a1p + kInRowBytes + c)};
-            const f2 p11 = {tap_subnormal(a0p + kInRowBytes + SP + c), tap_subnormal(a1p + kInRowBytes + SP + c)};
+            const f2 p01 = {tap_subnormal(a0q + c), tap_subnormal(a1q + c)};
+            const f2 p11 = {tap_subnormal(a0q + SP + c), tap_subnormal(a1q + SP + c)};
             v[c] = add2(add2(add2(mul2_unfusable(p00, w00, nz), mul2_unfusable(p10, w10, nz)), mul2_unfusable(p01, w01, nz)),
                         mul2_unfusable(p11, w11, nz));
         }
@@ -892,14 +892,14 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
     };
     // one group of columns: channels 0 and 1 as a packed pair, channel 2 with itself
     auto single = [&](int j, uint32_t in_s, uint32_t out_s, f2 wy0, f2 wy1) {
-        const uint32_t ap = in_s + boff[j];
+        const uint32_t ap = in_s + boff[j], aq = ap + rs;
         const f2 wx0p = {wx0[j], wx0[j]}, wx1p = {wx1[j], wx1[j]};
         const f2 w00 = mul2(wx0p, wy0), w10 = mul2(wx1p, wy0), w01 = mul2(wx0p, wy1), w11 = mul2(wx1p, wy1);
         const f2 p00 = {tap_subnormal(ap), tap_subnormal(ap + 1)}, p10 = {tap_subnormal(ap + SP), tap_subnormal(ap + SP + 1)};
-        const f2 p01 = {tap_subnormal(ap + kInRowBytes), tap_subnormal(ap + kInRowBytes + 1)};
-        const f2 p11 = {tap_subnormal(ap + kInRowBytes + SP), tap_subnormal(ap + kInRowBytes + SP + 1)};
+        const f2 p01 = {tap_subnormal(aq), tap_subnormal(aq + 1)};
+        const f2 p11 = {tap_subnormal(aq + SP), tap_subnormal(aq + SP + 1)};
         const f2 q00 = {tap_subnormal(ap + 2), 0.f}, q10 = {tap_subnormal(ap + SP + 2), 0.f};
-        const f2 q01 = {tap_subnormal(ap + kInRowBytes + 2), 0.f}, q11 = {tap_subnormal(ap + kInRowBytes + SP + 2), 0.f};
+        const f2 q01 = {tap_subnormal(aq + 2), 0.f}, q11 = {tap_subnormal(aq + SP + 2), 0.f};
         const f2 v01 = add2(add2(add2(mul2_unfusable(p00, w00, nz), mul2_unfusable(p10, w10, nz)), mul2_unfusable(p01, w01, nz)),
                             mul2_unfusable(p11, w11, nz));
         const f2 v2 = add2(add2(add2(mul2_unfusable(q00, w00, nz), mul2_unfusable(q10, w10, nz)), mul2_unfusable(q01, w01, nz)),
@@ -911,18 +911,19 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
     };
 
     // Row loop.  Per row: wait for its source rows, compute it into an output-row buffer, and then — in lane 0's one
-    // divergent stretch per row — send the row off with a bulk store, request the source rows of the row after next into
-    // the stage just read, and wait until the store of the previous row has finished reading the other buffer.
+    // divergent stretch per row — send the row off with a bulk store, request the source rows of row r + ns into the
+    // stage just read, and wait until the store of the previous row has finished reading the other buffer.
     const uint32_t out_bytes = ow * ELT, out_bulk = out_bytes & ~15u;
     uint8_t* gout = gdst;
-    for (uint32_t r = 0; r < nr; ++r, ++k, gout += dst_pitch) {
-        const uint32_t s = k & 1u;
+    uint32_t s = 0;  // stage of the row being computed: r mod ns
+    for (uint32_t r = 0; r < nr; ++r, gout += dst_pitch) {
         const float wy0s = __shfl_sync(FULL, wy0_l, r), wy1s = __shfl_sync(FULL, wy1_l, r);
-        const uint32_t r0n = __shfl_sync(FULL, row0_l, (r + 2u) & 31u), r1n = __shfl_sync(FULL, row1_l, (r + 2u) & 31u);
+        const uint32_t r0n = __shfl_sync(FULL, row0_l, (r + ns) & 31u), r1n = __shfl_sync(FULL, row1_l, (r + ns) & 31u);
         const bool row_in = (in_mask >> r) & 1u;
-        const bool ok = mbar_wait_bounded(w.bar(s), (k >> 1) & 1u, p.wait_limit_ns);
+        const bool ok = mbar_wait_bounded(w.bar(s), (ph >> s) & 1u, p.wait_limit_ns);
         if (__any_sync(FULL, !ok)) return false;  // (a convergence point for the whole warp, too)
-        const uint32_t in_s = w.in(s), out_s = w.out(s);
+        ph ^= 1u << s;
+        const uint32_t in_s = in0 + s * (2u * rs), out_s = w.out(r & 1u);
         if (!row_in) {
             // a row above or below the image: background over the inside columns too
 #pragma unroll
@@ -931,7 +932,7 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
         } else {
             if (replicate)
             {  // every lane writes the same three bytes (even lanes the first staged row, odd lanes the second)
-                const uint32_t q = in_s + (lane & 1u) * kInRowBytes + rep_off;
+                const uint32_t q = in_s + (lane & 1u) * rs + rep_off;
                 const uint8_t c0 = smem_raw[q], c1 = smem_raw[q + 1], c2 = smem_raw[q + 2];
                 smem_raw[q + SP] = c0; smem_raw[q + SP + 1] = c1; smem_raw[q + SP + 2] = c2;
                 __syncwarp();
@@ -963,9 +964,10 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
                 }
             }
             bulk_commit();
-            if (r + 2u < nr) load_rows(r + 2u, s, r0n, r1n);
+            if (r + ns < nr) load_rows(r + ns, s, r0n, r1n);
             bulk_wait_read_1();  // the store of the row before has read its buffer: the next row may be written there
         }
+        s = s + 1u == ns ? 0u : s + 1u;
         if (out_bytes != out_bulk && lane < out_bytes - out_bulk) {  // rare: a row whose byte length is not a multiple of 16
             gout[out_bulk + lane] = smem_raw[out_s + out_bulk + lane];
             if (PLANAR) {
@@ -979,22 +981,22 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
 
 template <bool F32, bool PLANAR = false, bool SRC4 = false>
 __device__ __forceinline__ bool resize_dispatch(const LaunchParams& p, const WarpSlice& w, uint32_t kind, uint32_t ox,
-                                                uint32_t oy0, uint32_t ow, uint32_t nr, uint32_t& k, uint32_t lane) {
+                                                uint32_t oy0, uint32_t ow, uint32_t nr, uint32_t& ph, uint32_t lane) {
     constexpr int S = F32 ? 0 : kPostSat;  // a uchar3 destination ends in a SaturateCast, a float3 one cannot
     switch (kind) {
-    case S: return resize_item<F32, S, PLANAR, SRC4>(p, w, ox, oy0, ow, nr, k, lane);
-    case S | kPostMul: return resize_item<F32, S | kPostMul, PLANAR, SRC4>(p, w, ox, oy0, ow, nr, k, lane);
-    case S | kPostAdd: return resize_item<F32, S | kPostAdd, PLANAR, SRC4>(p, w, ox, oy0, ow, nr, k, lane);
-    case S | kPostMul | kPostAdd: return resize_item<F32, S | kPostMul | kPostAdd, PLANAR, SRC4>(p, w, ox, oy0, ow, nr, k, lane);
-    default: return resize_item<F32, kPostGeneric, PLANAR, SRC4>(p, w, ox, oy0, ow, nr, k, lane);
+    case S: return resize_item<F32, S, PLANAR, SRC4>(p, w, ox, oy0, ow, nr, ph, lane);
+    case S | kPostMul: return resize_item<F32, S | kPostMul, PLANAR, SRC4>(p, w, ox, oy0, ow, nr, ph, lane);
+    case S | kPostAdd: return resize_item<F32, S | kPostAdd, PLANAR, SRC4>(p, w, ox, oy0, ow, nr, ph, lane);
+    case S | kPostMul | kPostAdd: return resize_item<F32, S | kPostMul | kPostAdd, PLANAR, SRC4>(p, w, ox, oy0, ow, nr, ph, lane);
+    default: return resize_item<F32, kPostGeneric, PLANAR, SRC4>(p, w, ox, oy0, ow, nr, ph, lane);
     }
 }
 
-__global__ void __launch_bounds__(kStagedThreads, 2) staged_kernel(const __grid_constant__ LaunchParams p) {
+__global__ void __launch_bounds__(kStagedThreads, kStagedCtasPerSm) staged_kernel(const __grid_constant__ LaunchParams p) {
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const WarpSlice w = warp_slice(warp * kSliceBytes);
     if (lane == 0) {
-        for (uint32_t i = 0; i < 6; ++i) mbar_init(w.bar(i), 1);
+        for (uint32_t i = 0; i < 8; ++i) mbar_init(w.bar(i), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncwarp();
@@ -1008,7 +1010,7 @@ __global__ void __launch_bounds__(kStagedThreads, 2) staged_kernel(const __grid_
     const uint32_t first = warp * gridDim.x + blockIdx.x, stride = gridDim.x * warps_per_cta;
     const bool dynamic = p.work != nullptr;
     const PlaneRec* table = plane_table(p);
-    uint32_t k = 0, k4 = 0;  // steps done so far by RESIZE items (two stages) and by POINT items (four stages)
+    uint32_t ph = 0, k4 = 0;  // phase bits of the RESIZE items' barriers; steps done so far by POINT items (four stages)
     bool ok = true;
     // The plane record of the next item is fetched (14 lanes x 16 bytes, into registers) while the current item is
     // processed, so its global-memory latency is off the critical path.
@@ -1021,7 +1023,7 @@ __global__ void __launch_bounds__(kStagedThreads, 2) staged_kernel(const __grid_
     }
     for (uint32_t item = first; item < p.n_tiles && ok; ++round) {
         __syncwarp();
-        if (lane < kRecLanes) reinterpret_cast<uint4*>(smem_raw + w.base + 48)[lane] = rec;
+        if (lane < kRecLanes) reinterpret_cast<uint4*>(smem_raw + w.base + 64)[lane] = rec;
         __syncwarp();
         const uint32_t cur_local = local;
         uint32_t next_item = item + stride;
@@ -1051,12 +1053,12 @@ __global__ void __launch_bounds__(kStagedThreads, 2) staged_kernel(const __grid_
             }
         }
         else if (p.chains[pl.chain].src_format == FKB_PIX_U8C4) {  // (float destinations only: the host lowering sees to it)
-            ok = p.chains[pl.chain].write_kind != FKB_WRITE_PACKED ? resize_dispatch<true, true, true>(p, w, p.post_kind[pl.chain], ox, oy0, ow, nr, k, lane)
-                                                                   : resize_dispatch<true, false, true>(p, w, p.post_kind[pl.chain], ox, oy0, ow, nr, k, lane);
+            ok = p.chains[pl.chain].write_kind != FKB_WRITE_PACKED ? resize_dispatch<true, true, true>(p, w, p.post_kind[pl.chain], ox, oy0, ow, nr, ph, lane)
+                                                                   : resize_dispatch<true, false, true>(p, w, p.post_kind[pl.chain], ox, oy0, ow, nr, ph, lane);
         }
-        else if (p.chains[pl.chain].write_kind != FKB_WRITE_PACKED) ok = resize_dispatch<true, true>(p, w, p.post_kind[pl.chain], ox, oy0, ow, nr, k, lane);
-        else ok = f32 ? resize_dispatch<true>(p, w, p.post_kind[pl.chain], ox, oy0, ow, nr, k, lane)
-                      : resize_dispatch<false>(p, w, p.post_kind[pl.chain], ox, oy0, ow, nr, k, lane);
+        else if (p.chains[pl.chain].write_kind != FKB_WRITE_PACKED) ok = resize_dispatch<true, true>(p, w, p.post_kind[pl.chain], ox, oy0, ow, nr, ph, lane);
+        else ok = f32 ? resize_dispatch<true>(p, w, p.post_kind[pl.chain], ox, oy0, ow, nr, ph, lane)
+                      : resize_dispatch<false>(p, w, p.post_kind[pl.chain], ox, oy0, ow, nr, ph, lane);
     }
     if (lane == 0) bulk_wait_all();  // shared memory must stay valid until the last bulk store has read it
     if (dynamic && lane == 0) {
@@ -1069,8 +1071,8 @@ __global__ void __launch_bounds__(kStagedThreads, 2) staged_kernel(const __grid_
         // copies announced on the other stages may still be in flight: give them a bounded chance to land
         // (stages without a copy in flight never complete: the limit, shortened, ends those waits)
         const uint32_t grace = min(p.wait_limit_ns, 1000000u);
-        mbar_wait_bounded(w.bar((k + 1) & 1u), ((k + 1) >> 1) & 1u, grace);
-        for (uint32_t i = 1; i <= 3; ++i) mbar_wait_bounded(w.bar(2 + ((k4 + i) & 3u)), ((k4 + i) >> 2) & 1u, grace);
+        for (uint32_t i = 0; i < 4; ++i) mbar_wait_bounded(w.bar(i), (ph >> i) & 1u, grace);
+        for (uint32_t i = 1; i <= 3; ++i) mbar_wait_bounded(w.bar(4 + ((k4 + i) & 3u)), ((k4 + i) >> 2) & 1u, grace);
         if (lane == 0) atomicExch(p.status, FKB_ERR_DEVICE_WAIT);
     }
 }

@@ -9,18 +9,25 @@ struct LaunchParams;
 
 constexpr uint32_t kStagedThreads = 256;
 constexpr uint32_t kStagedWarps = kStagedThreads / 32;
-// Shared memory of one warp of a staged CTA: a 288-byte header (six mbarriers, the plane record), two stages of two
-// source rows (or four stages of one), and two output rows.  12.6 KB per warp, 101 KB per CTA, so two CTAs fit in the
-// 228 KB of an SM.
+constexpr uint32_t kStagedCtasPerSm = 2;
+// Shared memory of one warp of a staged CTA: a 288-byte header (eight mbarriers, the plane record), a region for the
+// staged source rows — two to four stages of two rows each for RESIZE items, as many as the item's footprint lets fit;
+// four stages of one row for POINT items — and two output rows.  14.1 KB per warp, 113 KB per CTA: two CTAs (and the
+// kilobyte the system keeps per CTA) fill the 228 KB of an SM.
 constexpr uint32_t kSliceHeader = 288;
-constexpr uint32_t kInRowBytes = 1600;   // one staged source row segment (512 uchar3 pixels + alignment slack)
-constexpr uint32_t kOutRowBytes = 3072;  // one output row segment (256 float3 pixels, or 512 uchar3 with room to spare)
-// A planar float row is three segments (one per channel) of 256 values, each followed by 16 spare bytes; a packed row is
+constexpr uint32_t kMaxTileW = 256;      // widest column segment of an item, in output pixels
+constexpr uint32_t kInRowBytes = 1600;   // longest staged source row segment (512 uchar3 pixels + alignment slack)
+constexpr uint32_t kInRegionBytes = 7936;
+constexpr uint32_t kPointTileU8 = 512;   // pixels per segment of a uchar3 -> uchar3 item
+constexpr uint32_t kOutRowBytes = kMaxTileW * 12;  // one output row segment (float3 pixels, or uchar3 with room to spare)
+// A planar float row is three segments (one per channel), each followed by 16 spare bytes; a packed row is
 // followed by 16 spare bytes.  The spare bytes take the stores of columns that do not exist.
-constexpr uint32_t kPlanarSegBytes = 1024 + 16;
+constexpr uint32_t kPlanarSegBytes = kMaxTileW * 4 + 16;
 constexpr uint32_t kOutSlotBytes = 3 * kPlanarSegBytes;
-constexpr uint32_t kSliceBytes = kSliceHeader + 4 * kInRowBytes + 2 * kOutSlotBytes;
+constexpr uint32_t kSliceBytes = kSliceHeader + kInRegionBytes + 2 * kOutSlotBytes;
 constexpr uint32_t kStagedSmemBytes = kStagedWarps * kSliceBytes;
+static_assert(4 * kInRowBytes <= kInRegionBytes, "POINT items stage four rows");
+static_assert(kStagedCtasPerSm * (kStagedSmemBytes + 1024) <= 233472, "two CTAs per SM");
 constexpr uint32_t kMaxRowsPerItem = 32;
 // lut_kernel: a CTA-wide table of 256 rows, 256 bytes apart, each holding 32 copies of one 32-bit word
 // {T0[i], T1[i], T2[i], 0} (copy l belongs to lane l and sits in bank l, so a table read never has a bank conflict).  The

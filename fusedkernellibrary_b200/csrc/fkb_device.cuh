@@ -74,6 +74,23 @@ struct Nv12Consts {
     float kmag[3];        // with `pair`: 2^23 + sub[c], exact
 };
 
+// A four-channel chain flattened for rgba_kernel.  Mul, Add and Sub are each one fused multiply-add on every channel —
+// x * m is fma(x, m, -0), x + a is fma(x, 1, a), x - a is fma(x, 1, -a): the same single rounding and the same signed
+// zeros as the plain operation — so a chain of them needs no per-op decoding; Div and SaturateCast are the two other step
+// kinds.  Channel reorders are folded into the operands' order and one final permutation, an appended alpha channel is
+// fma(x, 0, alpha) on a channel that holds a finite value.
+constexpr uint32_t kFourMaxSteps = 6;
+struct FourConsts {
+    uint32_t enabled;     // every four-channel plane of the launch runs this chain and meets rgba_kernel's conditions
+    uint32_t n_steps;
+    uint32_t kinds;       // two bits per step: 0 fused multiply-add, 1 division by m, 2 SaturateCast
+    uint32_t perm;        // two bits per output channel: which stored channel it takes
+    uint32_t src3;        // the source is uchar3 (the fourth channel starts as 0 and gets its value from an appended alpha)
+    uint32_t f32;         // float4 destination (else uchar4)
+    uint32_t resize, preserve_ar;
+    float m[kFourMaxSteps][4], a[kFourMaxSteps][4];
+};
+
 struct LaunchParams {
     fkb_chain_desc chains[FKB_MAX_CHAINS];
     const PlaneRec* table;    // device table, or null when `inline_planes` is used
@@ -90,6 +107,7 @@ struct LaunchParams {
     uint32_t post_kind[FKB_MAX_CHAINS];
     PostImm post_imm[FKB_MAX_CHAINS];
     Nv12Consts nv12;  // per chain: bit mask of {Mul, Add|Sub, SaturateCast} when its post-ops have that shape, else 8
+    FourConsts four;
     float neg_zero;           // -0.0f, deliberately opaque to the compiler (see mul2_unfusable)
     uint32_t test_extra_tx;   // 0 in every real launch; a test sets it so that staged_kernel's loads announce bytes that never
                               // arrive and its bounded waits run out (the FKB_ERR_DEVICE_WAIT path)
@@ -213,6 +231,10 @@ constexpr float kByteScale = 16777216.0f;  // 2^24
 __device__ __forceinline__ float byte_times_2m24(uint32_t b) {
     return __half2float(__ushort_as_half(static_cast<unsigned short>(b)));
 }
+
+// Tap bytes read as fp32 subnormals (b * 2^-149) meet weights that carry 2^127; 2^22 is what is left to multiply by.
+constexpr float kTapScale = 1.7014118346046923e38f;  // 2^127
+constexpr float kTapUnscale = 4194304.0f;            // 2^22 = 2^149 / 2^127
 
 // Runs ops[first..last) of `ch` on N pixels held in registers.  The op loop is outside the pixel loop so
 // the (uniform) decode cost is paid once per N pixels.

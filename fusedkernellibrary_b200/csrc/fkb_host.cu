@@ -413,6 +413,70 @@ int status_word(int** out) {
     return FKB_OK;
 }
 
+// Fills L.lp.four when every four-channel plane of the launch runs one chain that rgba_kernel can take: no per-plane
+// operands, nothing but casts ahead of the interpolation, at most kFourMaxSteps steps behind it, no plane that yields its
+// default value or whose rectangle leaves the frame, word-aligned sources and destinations.  Mul / Add / Sub become one
+// fused multiply-add per channel, reorders a permutation of the operands and of the final store (see FourConsts).
+void flatten_four_channel_chain(const fkb_chain_desc* chains, Lowered& L) {
+    FourConsts& k = L.lp.four;
+    k.enabled = 0;
+    uint32_t chain = 0xffffffffu;
+    for (uint32_t z = L.lp.gather4_z0; z < L.lp.gather4_z1; ++z) {
+        const PlaneRec& r = L.recs[z];
+        if (r.kclass != KCLASS_GATHER4) continue;
+        if (chain == 0xffffffffu) chain = r.chain;
+        const fkb_chain_desc& ch = chains[r.chain];
+        if (r.chain != chain || r.src == nullptr) return;
+        const int64_t x = static_cast<int32_t>(r.crop_x), y = static_cast<int32_t>(r.crop_y);
+        if (x < 0 || y < 0 || x + r.crop_w > static_cast<int64_t>(r.src_w) || y + r.crop_h > static_cast<int64_t>(r.src_h)) return;
+        const bool f32 = ch.dst_format == FKB_PIX_F32C4;
+        const uintptr_t align = f32 ? 15u : 3u;
+        if ((reinterpret_cast<uintptr_t>(r.dst) & align) || (r.dst_pitch & align)) return;
+        if (ch.src_format == FKB_PIX_U8C4 && ((reinterpret_cast<uintptr_t>(r.src) & 3u) || (r.src_pitch & 3u))) return;
+        if (ch.geometry != FKB_GEOM_NONE) {
+            if (ch.geometry >= FKB_GEOM_RESIZE_PRESERVE_AR && (r.x2 < r.x1 || r.y2 < r.y1)) return;
+            if (!(r.fx >= 5.9604645e-8f) || !(r.fy >= 5.9604645e-8f) || !(r.fx <= 16777216.f) || !(r.fy <= 16777216.f)) return;
+        }
+    }
+    if (chain == 0xffffffffu) return;
+    const fkb_chain_desc& ch = chains[chain];
+    uint32_t first = 0;
+    if (ch.geometry != FKB_GEOM_NONE) {
+        for (uint32_t i = 0; i < ch.n_pre_ops; ++i)
+            if (ch.ops[i].code != FKB_OP_CAST_F32) return;
+        first = ch.n_pre_ops;
+    }
+    uint32_t pi[4] = {0, 1, 2, 3};  // actual channel c is held in stored channel pi[c]
+    bool have4 = ch.src_format == FKB_PIX_U8C4;
+    uint32_t n = 0, kinds = 0;
+    for (uint32_t i = first; i < ch.n_ops; ++i) {
+        const fkb_op& op = ch.ops[i];
+        if (op.code == FKB_OP_CAST_F32) continue;
+        if (op.code == FKB_OP_REORDER_ZYX) { std::swap(pi[0], pi[2]); continue; }
+        if (op.plane_slot >= 0 || n == kFourMaxSteps) return;
+        const float operand[4] = {op.v[0], op.v[1], op.v[2], ch.op_w[i]};
+        for (int c = 0; c < 4; ++c) { k.m[n][c] = 1.f; k.a[n][c] = -0.0f; }  // the identity: fma(x, 1, -0) = x
+        const int nc = have4 ? 4 : 3;
+        switch (op.code) {
+        case FKB_OP_MUL: for (int c = 0; c < nc; ++c) k.m[n][pi[c]] = operand[c]; break;
+        case FKB_OP_ADD: for (int c = 0; c < nc; ++c) k.a[n][pi[c]] = operand[c]; break;
+        case FKB_OP_SUB: for (int c = 0; c < nc; ++c) k.a[n][pi[c]] = -operand[c]; break;
+        case FKB_OP_DIV: for (int c = 0; c < nc; ++c) k.m[n][pi[c]] = operand[c]; kinds |= 1u << (2 * n); break;
+        case FKB_OP_SATCAST_U8: kinds |= 2u << (2 * n); break;
+        case FKB_OP_ADD_ALPHA: k.m[n][pi[3]] = 0.f; k.a[n][pi[3]] = op.v[0]; have4 = true; break;  // (the channel holds a finite value)
+        default: return;
+        }
+        ++n;
+    }
+    k.n_steps = n; k.kinds = kinds;
+    k.perm = pi[0] | (pi[1] << 2) | (pi[2] << 4) | (pi[3] << 6);
+    k.src3 = ch.src_format == FKB_PIX_U8C3;
+    k.f32 = ch.dst_format == FKB_PIX_F32C4;
+    k.resize = ch.geometry != FKB_GEOM_NONE;
+    k.preserve_ar = ch.geometry >= FKB_GEOM_RESIZE_PRESERVE_AR;
+    k.enabled = 1;
+}
+
 int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc* planes, uint32_t n_planes, Lowered& L) {
     const int rc = validate(chains, n_chains, planes, n_planes);
     if (rc != FKB_OK) return rc;
@@ -616,6 +680,7 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         ++L.kernels;
     }
     if (n_gather4) {
+        if (!tune.force_gather) flatten_four_channel_chain(chains, L);  // (FKB_FORCE_GATHER keeps the interpreting kernel)
         // (grid.z spans only the planes from the first to the last of this class: a stray plane costs one layer of CTAs)
         L.gather4_grid = dim3((g4w + 31) / 32, (g4h + 7) / 8, std::min<uint32_t>(L.lp.gather4_z1 - L.lp.gather4_z0, 65535u));
         ++L.kernels;

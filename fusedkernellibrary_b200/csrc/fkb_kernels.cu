@@ -443,6 +443,78 @@ __global__ void __launch_bounds__(256) gather4_kernel(const __grid_constant__ La
     }
 }
 
+// rgba_kernel: the same four-channel chains without an interpreter.  One output pixel per thread; the chain's ops after
+// the interpolation arrive flattened as at most six steps (FourConsts), N of them, unrolled.  A tap byte becomes a float
+// without a conversion: the byte, moved to the low end of a word, is the bit pattern of the subnormal b * 2^-149; the
+// vertical weights carry a factor of 2^127, and one exact multiplication by 2^22 puts the scale right (see resize_item).
+template <int N>
+__global__ void __launch_bounds__(256) rgba_kernel(const __grid_constant__ LaunchParams p) {
+    const PlaneRec* table = plane_table(p);
+    const FourConsts& k = p.four;
+    const uint32_t x = blockIdx.x * 32 + (threadIdx.x & 31), y = blockIdx.y * 8 + (threadIdx.x >> 5);
+    for (uint32_t z = p.gather4_z0 + blockIdx.z; z < p.gather4_z1; z += gridDim.z) {
+        const PlaneRec& pl = table[z];
+        if (pl.kclass != KCLASS_GATHER4 || x >= pl.dst_w || y >= pl.dst_h) continue;
+        float v[4];
+        const uint32_t sp = k.src3 ? 3u : 4u, pitch = pl.src_pitch;
+        auto tap = [&](const uint8_t* row, uint32_t X) -> uint32_t {  // the pixel's bytes in one word (byte 3 = 0 for a uchar3 source)
+            const uint8_t* q = row + static_cast<size_t>(X) * sp;
+            if (!k.src3) return __ldg(reinterpret_cast<const uint32_t*>(q));  // (the host checked the alignment)
+            return __ldg(q) | (__ldg(q + 1) << 8) | (__ldg(q + 2) << 16);
+        };
+        if (!k.resize) {
+            const uint32_t px = tap(pl.src + static_cast<size_t>(pl.crop_y + y) * pitch, pl.crop_x + x);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) v[c] = FKB_BYTE_F32(px, c);
+        } else {
+            const bool par = k.preserve_ar != 0;
+            const int xi = static_cast<int>(x), yi = static_cast<int>(y);
+            if (!par || (xi >= pl.x1 && xi <= pl.x2 && yi >= pl.y1 && yi <= pl.y2)) {
+                const AxisTap ax = axis_tap(xi - (par ? pl.x1 : 0), pl.fx, pl.crop_w), ay = axis_tap(yi - (par ? pl.y1 : 0), pl.fy, pl.crop_h);
+                const uint8_t* r0 = pl.src + static_cast<size_t>(ay.i0 + pl.crop_y) * pitch;
+                const uint8_t* r1 = pl.src + static_cast<size_t>(ay.i1 + pl.crop_y) * pitch;
+                const uint32_t t00 = tap(r0, ax.i0 + pl.crop_x), t10 = tap(r0, ax.i1 + pl.crop_x);
+                const uint32_t t01 = tap(r1, ax.i0 + pl.crop_x), t11 = tap(r1, ax.i1 + pl.crop_x);
+                const float wy0 = __fmul_rn(ay.w0, kTapScale), wy1 = __fmul_rn(ay.w1, kTapScale);
+                const float w00 = __fmul_rn(ax.w0, wy0), w10 = __fmul_rn(ax.w1, wy0), w01 = __fmul_rn(ax.w0, wy1), w11 = __fmul_rn(ax.w1, wy1);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const uint32_t sel = 0x4440u | c;  // byte c to the low end, zeros above it
+                    const float b = bilerp(__uint_as_float(__byte_perm(t00, 0u, sel)), __uint_as_float(__byte_perm(t10, 0u, sel)),
+                                           __uint_as_float(__byte_perm(t01, 0u, sel)), __uint_as_float(__byte_perm(t11, 0u, sel)), w00, w10, w01, w11);
+                    v[c] = __fmul_rn(b, kTapUnscale);
+                }
+            } else {
+                v[0] = pl.bg[0]; v[1] = pl.bg[1]; v[2] = pl.bg[2]; v[3] = pl.bg_w;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < N; ++i) {
+            const uint32_t kind = (k.kinds >> (2 * i)) & 3u;
+            if (kind == 0u) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) v[c] = __fmaf_rn(v[c], k.m[i][c], k.a[i][c]);
+            } else if (kind == 1u) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) v[c] = __fdiv_rn(v[c], k.m[i][c]);
+            } else {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) v[c] = sat_u8_as_float(v[c]);
+            }
+        }
+        float o[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const uint32_t from = (k.perm >> (2 * c)) & 3u;
+            o[c] = from == 0u ? v[0] : from == 1u ? v[1] : from == 2u ? v[2] : v[3];
+        }
+        uint8_t* row = pl.dst + static_cast<size_t>(y) * pl.dst_pitch;
+        if (k.f32) *reinterpret_cast<float4*>(row + static_cast<size_t>(x) * 16) = make_float4(o[0], o[1], o[2], o[3]);
+        else *reinterpret_cast<uint32_t*>(row + static_cast<size_t>(x) * 4) =
+                 static_cast<uint32_t>(o[0]) | (static_cast<uint32_t>(o[1]) << 8) | (static_cast<uint32_t>(o[2]) << 16) | (static_cast<uint32_t>(o[3]) << 24);
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------------
 // staged_kernel: every warp runs its own load -> compute -> store pipeline; warps never wait for one another
 // ---------------------------------------------------------------------------------------------------------
@@ -682,8 +754,6 @@ __device__ __forceinline__ bool point_item(const LaunchParams& p, const WarpSlic
 // Mul operand when the chain has one (fl((v * 2^-22) * (m * 2^22)) = fl(v * m)), else it is one exact multiplication.
 // Groups are computed two at a time with packed f32x2 instructions; an odd last group runs as scalars.
 // The background bars are written into the two output-row buffers once per item.
-constexpr float kTapScale = 1.7014118346046923e38f;  // 2^127
-constexpr float kTapUnscale = 4194304.0f;            // 2^22 = 2^149 / 2^127
 static_assert(kMaxRowsPerItem <= 32, "one lane per row of an item");
 
 __device__ __forceinline__ float tap_subnormal(uint32_t smem_off) {
@@ -1584,6 +1654,18 @@ cudaError_t launch_nv12(const LaunchParams& p, dim3 grid, cudaStream_t stream) {
 }
 
 cudaError_t launch_gather4(const LaunchParams& p, dim3 grid, cudaStream_t stream) {
+    if (p.four.enabled) {
+        switch (p.four.n_steps) {
+        case 0: rgba_kernel<0><<<grid, 256, 0, stream>>>(p); break;
+        case 1: rgba_kernel<1><<<grid, 256, 0, stream>>>(p); break;
+        case 2: rgba_kernel<2><<<grid, 256, 0, stream>>>(p); break;
+        case 3: rgba_kernel<3><<<grid, 256, 0, stream>>>(p); break;
+        case 4: rgba_kernel<4><<<grid, 256, 0, stream>>>(p); break;
+        case 5: rgba_kernel<5><<<grid, 256, 0, stream>>>(p); break;
+        default: rgba_kernel<6><<<grid, 256, 0, stream>>>(p); break;
+        }
+        return cudaGetLastError();
+    }
     gather4_kernel<<<grid, 256, 0, stream>>>(p);
     return cudaGetLastError();
 }

@@ -15,6 +15,7 @@
 // compile.  Here the static types carry just enough (value type flowing through the chain, batch size) to keep those
 // compile-time rejections, and the parameters live in a small run-time record that is lowered to include/fkb/fkb.h.
 #pragma once
+#include <memory>
 #include <array>
 #include <vector>
 
@@ -39,11 +40,31 @@ struct OpRec {
     uint16_t code{0};
     std::vector<std::array<float, 4>> v;  // one operand per plane, or a single one shared by all planes (fourth component: four-channel chains)
 };
+// A vector that is shared between the copies of a ReadState until one of them changes it: every .then() of a chain
+// copies the state, and the per-plane vectors of a batch of thousands of planes need not be copied with it.
+template <typename T>
+class SharedVec {
+    std::shared_ptr<std::vector<T>> p_;
+    static const std::vector<T>& none() { static const std::vector<T> e; return e; }
+public:
+    const std::vector<T>& get() const { return p_ ? *p_ : none(); }
+    std::vector<T>& mut() {  // a private copy from here on
+        if (!p_) p_ = std::make_shared<std::vector<T>>();
+        else if (p_.use_count() > 1) p_ = std::make_shared<std::vector<T>>(*p_);
+        return *p_;
+    }
+    void assign(std::vector<T> v) { p_ = std::make_shared<std::vector<T>>(std::move(v)); }
+    size_t size() const { return get().size(); }
+    bool empty() const { return get().empty(); }
+    const T& operator[](size_t i) const { return get()[i]; }
+    auto begin() const { return get().begin(); }
+    auto end() const { return get().end(); }
+};
 // Everything a chain knows before its Write: the run-time image of the reference's fused Read IOp.
 struct ReadState {
     uint32_t src_format{FKB_PIX_U8C3};
-    std::vector<SrcPlane> src;   // 1 entry (shared) or one per plane
-    std::vector<Rect> crops;     // empty (whole frame), 1 entry, or one per plane
+    SharedVec<SrcPlane> src;     // 1 entry (shared) or one per plane
+    SharedVec<Rect> crops;       // empty (whole frame), 1 entry, or one per plane
     bool has_resize{false};
     AspectRatio ar{AspectRatio::IGNORE_AR};
     Size dst_size;
@@ -290,7 +311,7 @@ struct ReadIOp {
         static_assert(BATCH == 0 || N == 0 || BATCH == N, "Fusing two batch operations of different BATCH size is not allowed.");
         if (st.has_resize) throw std::runtime_error("Crop after Resize is not a chain the B200 kernels implement");
         detail::ReadState s = st;
-        if (s.crops.empty()) s.crops = c.rects;
+        if (s.crops.empty()) s.crops.assign(c.rects);
         else {  // a crop of a crop: offsets add up
             std::vector<Rect> out(std::max(s.crops.size(), c.rects.size()));
             for (size_t i = 0; i < out.size(); ++i) {
@@ -298,7 +319,7 @@ struct ReadIOp {
                 const Rect& b = c.rects[c.rects.size() == 1 ? 0 : i];
                 out[i] = Rect(a.x + b.x, a.y + b.y, b.width, b.height);
             }
-            s.crops = out;
+            s.crops.assign(std::move(out));
         }
         return ReadIOp<OutT, (BATCH ? BATCH : N)>(std::move(s));
     }
@@ -346,7 +367,7 @@ struct PerThreadRead {
     static auto build(const RawPtr<ND::_2D, T>& p) {
         detail::ReadState s;
         s.src_format = fmt;
-        s.src.push_back({p.data, p.dims.pitch, p.dims.width, p.dims.height});
+        s.src.mut().push_back({p.data, p.dims.pitch, p.dims.width, p.dims.height});
         return ReadIOp<T, 0>(std::move(s));
     }
     static auto build(const Ptr<ND::_2D, T>& p) { return build(p.ptr()); }
@@ -354,7 +375,9 @@ struct PerThreadRead {
     static auto build(const std::array<Ptr2D<T>, N>& ptrs) {
         detail::ReadState s;
         s.src_format = fmt;
-        for (const auto& p : ptrs) { const auto r = p.ptr(); s.src.push_back({r.data, r.dims.pitch, r.dims.width, r.dims.height}); }
+        auto& src = s.src.mut();
+        src.reserve(N);
+        for (const auto& p : ptrs) { const auto r = p.ptr(); src.push_back({r.data, r.dims.pitch, r.dims.width, r.dims.height}); }
         return ReadIOp<T, N>(std::move(s));
     }
     // BatchRead<CONDITIONAL_WITH_DEFAULT> (batch_operations.h:221-281, builder :530-534): planes >= usedPlanes yield
@@ -375,7 +398,7 @@ struct ReadYUV {
         static_assert(PixelFormatTraits<PF>::supported, "NV12, NV21, UYVY, P010, P210 and Y210 are the formats the B200 kernels read");
         detail::ReadState s;
         s.src_format = PixelFormatTraits<PF>::code;
-        s.src.push_back({raw.data.data, raw.data.dims.pitch, raw.width, raw.height});
+        s.src.mut().push_back({raw.data.data, raw.data.dims.pitch, raw.width, raw.height});
         return ReadIOp<ColorDepthPixelType<PixelFormatTraits<PF>::depth>, 0>(std::move(s));
     }
 };
@@ -387,16 +410,16 @@ struct BatchRead {
     static auto build(const std::array<ReadIOp<O, 0>, N>& iops) {
         detail::ReadState s = iops[0].st;
         for (auto& op : s.ops) op.v.resize(N);
-        if (!s.crops.empty()) s.crops.resize(N);
-        s.src.resize(N);
+        if (!s.crops.empty()) s.crops.mut().resize(N);
+        s.src.mut().resize(N);
         for (size_t i = 0; i < N; ++i) {
             const detail::ReadState& e = iops[i].st;
             if (e.ops.size() != s.ops.size() || e.src_format != s.src_format || e.has_resize != s.has_resize ||
                 e.n_pre_ops != s.n_pre_ops || e.crops.empty() != iops[0].st.crops.empty() ||
                 (e.has_resize && (e.dst_size.width != s.dst_size.width || e.dst_size.height != s.dst_size.height || e.ar != s.ar)))
                 throw std::runtime_error("BatchRead: the planes are not chains of the same operations");
-            s.src[i] = e.src[0];
-            if (!e.crops.empty()) s.crops[i] = e.crops[0];
+            s.src.mut()[i] = e.src[0];
+            if (!e.crops.empty()) s.crops.mut()[i] = e.crops[0];
             for (size_t k = 0; k < s.ops.size(); ++k) {
                 if (e.ops[k].code != s.ops[k].code) throw std::runtime_error("BatchRead: the planes are not chains of the same operations");
                 s.ops[k].v[i] = e.ops[k].v[0];

@@ -24,9 +24,14 @@ _oracle = None
 _ref = None
 
 
+REF_DIR_DEFAULT = "/root/reference"
+
+
 def build() -> None:
-    """Compiles both checkers (the reference one only if its headers are present)."""
-    subprocess.run(["make", "-s", "-C", HERE], check=True)
+    """Compiles both checkers; the reference-backed ones only where the reference tree is installed (environment
+    variable FKB_REF_DIR, else the default location above)."""
+    ref_dir = os.environ.get("FKB_REF_DIR", REF_DIR_DEFAULT)
+    subprocess.run(["make", "-s", "-C", HERE, f"FKB_REF_DIR={ref_dir}"], check=True)
 
 
 def load_oracle() -> C.CDLL:

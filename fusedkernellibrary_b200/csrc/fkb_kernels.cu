@@ -447,7 +447,7 @@ __global__ void __launch_bounds__(256) gather4_kernel(const __grid_constant__ La
 // the interpolation arrive flattened as at most six steps (FourConsts), N of them, unrolled.  A tap byte becomes a float
 // without a conversion: the byte, moved to the low end of a word, is the bit pattern of the subnormal b * 2^-149; the
 // vertical weights carry a factor of 2^127, and one exact multiplication by 2^22 puts the scale right (see resize_item).
-template <int N>
+template <int N, bool SRC3>
 __global__ void __launch_bounds__(256) rgba_kernel(const __grid_constant__ LaunchParams p) {
     const PlaneRec* table = plane_table(p);
     const FourConsts& k = p.four;
@@ -456,10 +456,11 @@ __global__ void __launch_bounds__(256) rgba_kernel(const __grid_constant__ Launc
         const PlaneRec& pl = table[z];
         if (pl.kclass != KCLASS_GATHER4 || x >= pl.dst_w || y >= pl.dst_h) continue;
         float v[4];
-        const uint32_t sp = k.src3 ? 3u : 4u, pitch = pl.src_pitch;
+        constexpr uint32_t sp = SRC3 ? 3u : 4u;
+        const uint32_t pitch = pl.src_pitch;
         auto tap = [&](const uint8_t* row, uint32_t X) -> uint32_t {  // the pixel's bytes in one word (byte 3 = 0 for a uchar3 source)
             const uint8_t* q = row + static_cast<size_t>(X) * sp;
-            if (!k.src3) return __ldg(reinterpret_cast<const uint32_t*>(q));  // (the host checked the alignment)
+            if (!SRC3) return __ldg(reinterpret_cast<const uint32_t*>(q));  // (the host checked the alignment)
             return __ldg(q) | (__ldg(q + 1) << 8) | (__ldg(q + 2) << 16);
         };
         if (!k.resize) {
@@ -1655,15 +1656,17 @@ cudaError_t launch_nv12(const LaunchParams& p, dim3 grid, cudaStream_t stream) {
 
 cudaError_t launch_gather4(const LaunchParams& p, dim3 grid, cudaStream_t stream) {
     if (p.four.enabled) {
+#define FKB_RGBA(N) (p.four.src3 ? rgba_kernel<N, true><<<grid, 256, 0, stream>>>(p) : rgba_kernel<N, false><<<grid, 256, 0, stream>>>(p))
         switch (p.four.n_steps) {
-        case 0: rgba_kernel<0><<<grid, 256, 0, stream>>>(p); break;
-        case 1: rgba_kernel<1><<<grid, 256, 0, stream>>>(p); break;
-        case 2: rgba_kernel<2><<<grid, 256, 0, stream>>>(p); break;
-        case 3: rgba_kernel<3><<<grid, 256, 0, stream>>>(p); break;
-        case 4: rgba_kernel<4><<<grid, 256, 0, stream>>>(p); break;
-        case 5: rgba_kernel<5><<<grid, 256, 0, stream>>>(p); break;
-        default: rgba_kernel<6><<<grid, 256, 0, stream>>>(p); break;
+        case 0: FKB_RGBA(0); break;
+        case 1: FKB_RGBA(1); break;
+        case 2: FKB_RGBA(2); break;
+        case 3: FKB_RGBA(3); break;
+        case 4: FKB_RGBA(4); break;
+        case 5: FKB_RGBA(5); break;
+        default: FKB_RGBA(6); break;
         }
+#undef FKB_RGBA
         return cudaGetLastError();
     }
     gather4_kernel<<<grid, 256, 0, stream>>>(p);

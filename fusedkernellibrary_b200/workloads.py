@@ -591,6 +591,19 @@ def random_workload(seed: int, max_dim: int = 260) -> Workload:
             ops.append(op(abi.OP_SATCAST_U8)); is_f32 = False
     dst_format = abi.PIX_F32C3 if is_f32 else abi.PIX_U8C3
     split = rs.rand() < 0.25
+    gray = seed % 7 == 5  # a grey conversion ends the chain (decided by the seed alone: other seeds keep their launches)
+    if gray:
+        g = np.random.RandomState(1000 + seed)
+        split = False
+        if is_f32:
+            ops.append(op(abi.OP_RGB2GRAY))
+            if g.rand() < 0.6:
+                ops.append(op(abi.OP_MUL, (float(g.uniform(0.3, 1.5)),) * 3))
+            if g.rand() < 0.5:
+                ops.append(op(abi.OP_SATCAST_U8)); is_f32 = False
+        else:
+            ops.append(op(abi.OP_RGB2GRAY, (1.0, 0.0, 0.0)))
+        dst_format = abi.PIX_F32C1 if is_f32 else abi.PIX_U8C1
     ch = chain(abi.PIX_NV12 if nv12 else abi.PIX_U8C3, geometry, dst_format, abi.WRITE_SPLIT if split else abi.WRITE_PACKED,
                ops, n_pre_ops=n_pre, ccm=BT709_FULL_8BIT, yuv_sub=(0.0, 128.0, 128.0))
 
@@ -603,8 +616,8 @@ def random_workload(seed: int, max_dim: int = 260) -> Workload:
         ch.src_format = abi.PIX_U8C4
     pitch = _pitch(w if nv12 else w * (4 if src4 else 3), max(align, 2 if nv12 else 1))
     src = _frame(seed + 7, pitch * (h + h // 2 if nv12 else h), 16 if nv12 else 0, 236 if nv12 else 256)
-    elt = (4 if split else 12) if dst_format == abi.PIX_F32C3 else (1 if split else 3)
-    dalign = int(rs.choice([1, 16, 64])) if dst_format == abi.PIX_U8C3 else int(rs.choice([4, 16, 64]))
+    elt = {abi.PIX_F32C3: 4 if split else 12, abi.PIX_U8C3: 1 if split else 3, abi.PIX_F32C1: 4, abi.PIX_U8C1: 1}[dst_format]
+    dalign = int(rs.choice([1, 16, 64])) if dst_format in (abi.PIX_U8C3, abi.PIX_U8C1) else int(rs.choice([4, 16, 64]))
     planes, off = [], 0
     for _ in range(n_planes):
         cw, chh = int(rs.randint(1, w + 1)), int(rs.randint(1, h + 1))

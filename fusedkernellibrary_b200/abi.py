@@ -14,7 +14,7 @@ MAX_PLANE_PARAMS = 4
 MAX_CHAINS = 8
 NOALLOC_MAX_PLANES = 4096
 
-OK, ERR_NULL, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_TOO_LARGE, ERR_DEVICE_WAIT = 0, -1, -2, -3, -4, -5, -6
+OK, ERR_NULL, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_TOO_LARGE, ERR_DEVICE_WAIT, ERR_DEVICE_CHECK = 0, -1, -2, -3, -4, -5, -6, -7
 
 PIX_U8C3, PIX_F32C3, PIX_NV12, PIX_NV21, PIX_UYVY, PIX_U8C4, PIX_F32C4, PIX_F32P3 = 1, 2, 3, 4, 5, 6, 7, 8
 PIX_P010, PIX_P210, PIX_Y210 = 9, 10, 11
@@ -64,6 +64,8 @@ class PlaneDesc(C.Structure):
 assert C.sizeof(Op) == 16 and C.sizeof(ChainDesc) == 384 and C.sizeof(PlaneDesc) == 200
 
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libfkb.so")
+# the self-checking build (every bulk copy and gathered tap tested against its buffer first; see FKB_ERR_DEVICE_CHECK)
+DEBUG_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libfkb_debug.so")
 
 # name -> (restype, argtypes); every symbol include/fkb/fkb.h declares
 SIGNATURES = {
@@ -89,13 +91,15 @@ _lib = None
 
 
 def load() -> C.CDLL:
-    """Loads lib/libfkb.so and declares the signatures.  Raises if the library was not built."""
+    """Loads lib/libfkb.so (or the build FKB_LIBRARY names) and declares the signatures.  Raises if it was not built."""
     global _lib
     if _lib is None:
-        if not os.path.exists(LIB_PATH):
-            raise RuntimeError(f"{LIB_PATH} is missing: run `python -m fusedkernellibrary_b200.build` "
+        # FKB_LIBRARY names another build of the same library, e.g. the self-checking one
+        path = os.environ.get("FKB_LIBRARY") or LIB_PATH
+        if not os.path.exists(path):
+            raise RuntimeError(f"{path} is missing: run `python -m fusedkernellibrary_b200.build` "
                                "(there is no CPU fallback)")
-        lib = C.CDLL(LIB_PATH)
+        lib = C.CDLL(path)
         for name, (res, args) in SIGNATURES.items():
             fn = getattr(lib, name)
             fn.restype, fn.argtypes = res, args

@@ -18,7 +18,7 @@ OUT = os.path.join(OUT_DIR, "libfkb.so")
 SOURCES = ["fkb_kernels.cu", "fkb_host.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--fmad=false",
-    "-Xcompiler", "-fPIC", "-shared", "-Xptxas", "-v",
+    "-Xcompiler", "-fPIC", "-shared", "-Xptxas", "-v", "-ldl",
 ]
 
 
@@ -45,6 +45,24 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return OUT
 
 
+def build_debug(force: bool = False) -> str:
+    """The self-checking build, lib/libfkb_debug.so: the same sources with -DFKB_DEBUG, which makes every bulk copy and
+    every gathered tap test its addresses against the buffer its plane record describes, record FKB_ERR_DEVICE_CHECK and
+    skip the access on a miss (it stands in for a memory checker; nothing traps).  The tests run the parity cases on it."""
+    out = os.path.join(OUT_DIR, "libfkb_debug.so")
+    if not force and os.path.exists(out) and not needs_build() and os.path.getmtime(out) >= os.path.getmtime(OUT):
+        return out
+    os.makedirs(OUT_DIR, exist_ok=True)
+    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    cmd = [nvcc, *NVCC_FLAGS, "-DFKB_DEBUG", "-I", os.path.join(ROOT, "include"), "-I", CSRC, "-o", out,
+           *[os.path.join(CSRC, s) for s in SOURCES]]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        sys.stderr.write(res.stdout + res.stderr)
+        raise RuntimeError("nvcc failed building libfkb_debug.so")
+    return out
+
+
 def build_frontend_bench(force: bool = False) -> str:
     """Compiles bench_frontend.cpp (the host-cost measurement bench.py runs: a program written against the fk:: front
     end, linked to libfkb.so and the CUDA runtime only) into lib/bench_frontend."""
@@ -65,4 +83,5 @@ def build_frontend_bench(force: bool = False) -> str:
 if __name__ == "__main__":
     build(force=True, verbose=True)
     print(OUT)
+    print(build_debug(force=True))
     print(build_frontend_bench(force=True))

@@ -175,6 +175,27 @@ __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wa
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // ---------------------------------------------------------------------------------------------------------
+// the self-checking build (-DFKB_DEBUG)
+// ---------------------------------------------------------------------------------------------------------
+// Stands in for a memory checker where none can be run: every bulk copy's addresses, sizes and alignment and every
+// gathered tap's coordinates are tested against the buffer the plane record describes before the access is made.  A
+// failed test records FKB_ERR_DEVICE_CHECK in the status word and the access is skipped — nothing traps, nothing faults.
+#ifdef FKB_DEBUG
+constexpr bool kSelfChecking = true;
+#else
+constexpr bool kSelfChecking = false;
+#endif
+__device__ __forceinline__ bool self_check(int* status, bool good) {
+    if (!good) atomicCAS(status, 0, FKB_ERR_DEVICE_CHECK);
+    return good;
+}
+// [a, a + bytes) lies in [lo, lo + size), a and bytes are multiples of 16
+__device__ __forceinline__ bool bulk_range_ok(const void* a, uint32_t bytes, const void* lo, size_t size) {
+    const uintptr_t p = reinterpret_cast<uintptr_t>(a), l = reinterpret_cast<uintptr_t>(lo);
+    return (p & 15u) == 0 && (bytes & 15u) == 0 && p >= l && p + bytes <= l + size;
+}
+
+// ---------------------------------------------------------------------------------------------------------
 // arithmetic
 // ---------------------------------------------------------------------------------------------------------
 // Integer <-> float without conversion instructions (those run at a quarter of the FP32 rate).

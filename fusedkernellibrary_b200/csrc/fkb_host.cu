@@ -17,6 +17,8 @@
 #include <new>
 #include <vector>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "fkb_device.cuh"
 #include "fkb_launch.h"
 
@@ -24,6 +26,15 @@ namespace fkb {
 namespace {
 
 thread_local int t_last_cuda_error = 0;
+
+// An NVTX range around the host side of an entry point (the reference wraps its tests in NVTX ranges behind ENABLE_NVTX,
+// tests/nvtx.h:18-104): visible in a timeline profiler, a few nanoseconds when no tool is attached.
+struct NvtxRange {
+    explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+    ~NvtxRange() { nvtxRangePop(); }
+    NvtxRange(const NvtxRange&) = delete;
+    NvtxRange& operator=(const NvtxRange&) = delete;
+};
 
 #define FKB_CUDA(expr)                                              \
     do {                                                            \
@@ -210,11 +221,15 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 //   FKB_ROWS_PER_ITEM=n      output rows per item of the staged kernel (default: chosen from the launch size);
 //   FKB_TEST_EXTRA_TX=n      test hook: the staged kernel's resize loads announce n bytes more than they deliver, so its
 //                            bounded waits run out and the launch ends with FKB_ERR_DEVICE_WAIT in the status word;
-//   FKB_WAIT_LIMIT_US=n      how long such a wait lasts before it gives up (default one second).
+//   FKB_WAIT_LIMIT_US=n      how long such a wait lasts before it gives up (default one second);
+//   FKB_TEST_SHRINK_FRAME=1  test hook for the self-checking build: the plane records claim source frames of one row, so that
+//                            build's range checks fail, record FKB_ERR_DEVICE_CHECK and skip the copies (the release build
+//                            does not read that field on its pipelined paths).
 struct Tuning {
     bool force_gather = false;
     uint64_t tiny_pixels = kTinyLaunchPixels;
     uint32_t rows_per_item = 0, test_extra_tx = 0, wait_limit_ns = 1000000000u;
+    bool test_shrink_frame = false;
 };
 Tuning read_tuning() {
     Tuning t;
@@ -223,6 +238,7 @@ Tuning read_tuning() {
     if ((e = std::getenv("FKB_TINY_PIXELS")) && e[0]) t.tiny_pixels = std::strtoull(e, nullptr, 10);
     if ((e = std::getenv("FKB_ROWS_PER_ITEM")) && e[0]) t.rows_per_item = static_cast<uint32_t>(std::strtoul(e, nullptr, 10));
     if ((e = std::getenv("FKB_TEST_EXTRA_TX")) && e[0]) t.test_extra_tx = static_cast<uint32_t>(std::strtoul(e, nullptr, 10));
+    if ((e = std::getenv("FKB_TEST_SHRINK_FRAME")) && e[0] == '1') t.test_shrink_frame = true;
     if ((e = std::getenv("FKB_WAIT_LIMIT_US")) && e[0]) t.wait_limit_ns = static_cast<uint32_t>(std::min<unsigned long>(std::strtoul(e, nullptr, 10), 4000000ul) * 1000ul);
     return t;
 }
@@ -526,6 +542,7 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         } else {
             classify(chains[r.chain], r, tune);
         }
+        if (tune.test_shrink_frame) r.src_h = 1;
         total_pixels += static_cast<uint64_t>(r.dst_w) * r.dst_h;
     }
     // A launch of a few ten thousand pixels is pure latency: the pipelined paths would spend it filling their stages,
@@ -999,6 +1016,7 @@ int fkb_validate(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plan
 }
 
 int fkb_launch_transform(const fkb_chain_desc* chain, const fkb_plane_desc* planes, uint32_t n_planes, void* cuda_stream) {
+    const NvtxRange range("fkb_launch_transform");
     if (!chain || !planes) return FKB_ERR_NULL;
     for (uint32_t z = 0; z < n_planes; ++z)
         if ((planes[z].chain & ~FKB_PLANE_DEFAULT) != 0) return FKB_ERR_INVALID;
@@ -1006,11 +1024,13 @@ int fkb_launch_transform(const fkb_chain_desc* chain, const fkb_plane_desc* plan
 }
 
 int fkb_launch_transform_noalloc(const fkb_chain_desc* chain, const fkb_plane_desc* planes, uint32_t n_planes, void* cuda_stream) {
+    const NvtxRange range("fkb_launch_transform_noalloc");
     return launch_noalloc(chain, planes, n_planes, static_cast<cudaStream_t>(cuda_stream));
 }
 
 int fkb_launch_divergent(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc* planes,
                          uint32_t n_planes, void* cuda_stream) {
+    const NvtxRange range("fkb_launch_divergent");
     return launch_once(chains, n_chains, planes, n_planes, static_cast<cudaStream_t>(cuda_stream));
 }
 
@@ -1052,6 +1072,7 @@ int fkb_plan_create(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_p
 }
 
 int fkb_plan_launch(const fkb_plan* plan, void* cuda_stream) {
+    const NvtxRange range("fkb_plan_launch");
     if (!plan) return FKB_ERR_NULL;
     // a plan belongs to the device it was created on (its plane table and its status word live there)
     int dev = -1;
@@ -1097,6 +1118,7 @@ const char* fkb_status_string(int status) {
     case FKB_ERR_CUDA: return "CUDA runtime error";
     case FKB_ERR_TOO_LARGE: return "launch too large";
     case FKB_ERR_DEVICE_WAIT: return "a bounded device-side wait ran out";
+    case FKB_ERR_DEVICE_CHECK: return "the self-checking build found an access outside its buffer and skipped it";
     default: return "unknown status";
     }
 }

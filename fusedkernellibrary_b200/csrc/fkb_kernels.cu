@@ -23,6 +23,8 @@
 
 namespace fkb {
 
+__device__ int g_status_word;  // what fkb_device_status() reads; LaunchParams::status points here
+
 // ---------------------------------------------------------------------------------------------------------
 // shared helpers
 // ---------------------------------------------------------------------------------------------------------
@@ -32,6 +34,7 @@ __device__ __forceinline__ const PlaneRec* plane_table(const LaunchParams& p) {
 
 // Frame pixel (X,Y) as three floats (uchar3 channels, or Y / Cb / Cr).
 __device__ __forceinline__ void read_frame_global(const fkb_chain_desc& ch, const PlaneRec& pl, size_t X, size_t Y, float (&o)[3]) {
+    if (kSelfChecking && !self_check(&g_status_word, X < pl.src_w && Y < pl.src_h)) { o[0] = o[1] = o[2] = 0.f; return; }
     switch (ch.src_format) {
     case FKB_PIX_NV12: case FKB_PIX_NV21: {
         const uint8_t* uv = pl.src_chroma + (Y >> 1) * pl.src_pitch + (X >> 1) * 2;
@@ -320,6 +323,10 @@ __device__ __forceinline__ bool read_tap4(const fkb_chain_desc& ch, const PlaneR
             Y = border_index(ch.border, Y, h);
         }
     }
+    if (kSelfChecking && !self_check(&g_status_word, X >= 0 && Y >= 0 && static_cast<uint32_t>(X) < pl.src_w && static_cast<uint32_t>(Y) < pl.src_h)) {
+        o[0] = o[1] = o[2] = o[3] = 0.f;
+        return false;
+    }
     if (ch.src_format == FKB_PIX_U8C3) {  // three channels until FKB_OP_ADD_ALPHA appends the fourth
         const uint8_t* q3 = pl.src + static_cast<size_t>(Y) * pl.src_pitch + static_cast<size_t>(X) * 3;
         o[0] = static_cast<float>(__ldg(q3)); o[1] = static_cast<float>(__ldg(q3 + 1)); o[2] = static_cast<float>(__ldg(q3 + 2));
@@ -565,36 +572,19 @@ __device__ __forceinline__ uint32_t tile_to_plane(const LaunchParams& p, uint32_
 
 // One output row segment leaves through the TMA engine: lane 0 issues a bulk store of the 16-byte multiple,
 // the (row_bytes mod 16) tail bytes go out with plain byte stores.
-__device__ __forceinline__ void store_row(uint8_t* gdst, uint32_t srow, uint32_t row_bytes, uint32_t lane) {
+__device__ __forceinline__ void store_row(uint8_t* gdst, uint32_t srow, uint32_t row_bytes, uint32_t lane, const PlaneRec& pl) {
     const uint32_t bulk = row_bytes & ~15u;
     fence_async_smem();
     __syncwarp();
     if (lane == 0) {
-        if (bulk) bulk_store(gdst, smem_raw + srow, bulk);
+        bool store = bulk != 0;
+        if (kSelfChecking && store)
+            store = self_check(&g_status_word, bulk_range_ok(gdst, bulk, pl.dst, static_cast<size_t>(pl.dst_pitch) * pl.dst_h) && (srow & 15u) == 0);
+        if (store) bulk_store(gdst, smem_raw + srow, bulk);
         bulk_commit();
     }
     if (row_bytes != bulk) {  // rare: a row whose byte length is not a multiple of 16
         if (lane < row_bytes - bulk) gdst[bulk + lane] = smem_raw[srow + bulk + lane];
-    }
-}
-
-// The same for a planar float row: one bulk store per channel segment, one commit for the three.
-__device__ __forceinline__ void store_row_planar(uint8_t* gdst, uint64_t off1, uint64_t off2, uint32_t srow, uint32_t row_bytes, uint32_t lane) {
-    const uint32_t bulk = row_bytes & ~15u;
-    fence_async_smem();
-    __syncwarp();
-    if (lane == 0) {
-        if (bulk) {
-            bulk_store(gdst, smem_raw + srow, bulk);
-            bulk_store(gdst + off1, smem_raw + srow + kPlanarSegBytes, bulk);
-            bulk_store(gdst + off2, smem_raw + srow + 2 * kPlanarSegBytes, bulk);
-        }
-        bulk_commit();
-    }
-    if (row_bytes != bulk && lane < row_bytes - bulk) {  // a row whose byte length is not a multiple of 16
-        gdst[bulk + lane] = smem_raw[srow + bulk + lane];
-        gdst[off1 + bulk + lane] = smem_raw[srow + kPlanarSegBytes + bulk + lane];
-        gdst[off2 + bulk + lane] = smem_raw[srow + 2 * kPlanarSegBytes + bulk + lane];
     }
 }
 
@@ -661,8 +651,12 @@ __device__ __forceinline__ bool point_item(const LaunchParams& p, const WarpSlic
     uint8_t* gdst = pl.dst + static_cast<size_t>(oy0) * pl.dst_pitch + static_cast<size_t>(ox) * (F32 ? 12u : 3u);
     auto issue = [&](uint32_t r, uint32_t s) {
         if (lane == 0) {
-            mbar_arrive_expect_tx(w.bar(4 + s), in_bytes);
-            bulk_load(smem_raw + w.in4(s), gsrc + static_cast<size_t>(r) * src_pitch, in_bytes, w.bar(4 + s));
+            bool good = true;
+            if (kSelfChecking)
+                good = self_check(p.status, bulk_range_ok(gsrc + static_cast<size_t>(r) * src_pitch, in_bytes, pl.src, static_cast<size_t>(pl.src_pitch) * pl.src_h) &&
+                                                in_bytes <= kInRowBytes);
+            mbar_arrive_expect_tx(w.bar(4 + s), good ? in_bytes : 0u);
+            if (good) bulk_load(smem_raw + w.in4(s), gsrc + static_cast<size_t>(r) * src_pitch, in_bytes, w.bar(4 + s));
         }
     };
     auto compute = [&](uint32_t in_s, uint32_t out_s) {
@@ -732,7 +726,7 @@ __device__ __forceinline__ bool point_item(const LaunchParams& p, const WarpSlic
         const bool landed = mbar_wait_bounded(w.bar(4 + s), (k >> 2) & 1u, p.wait_limit_ns);
         if (__any_sync(0xffffffffu, !landed)) return false;
         compute(w.in4(s), w.out(o));
-        store_row(gdst + static_cast<size_t>(r) * dst_pitch, w.out(o), row_bytes, lane);
+        store_row(gdst + static_cast<size_t>(r) * dst_pitch, w.out(o), row_bytes, lane, pl);
     }
     return true;
 }
@@ -818,8 +812,14 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
     // rows (the second repeats the first where the reference clamps y2), so that the second row sits at a fixed
     // distance from the first.
     auto load_rows = [&](uint32_t r, uint32_t s, uint32_t r0, uint32_t r1) {
-        const bool in = (in_mask >> r) & 1u;
+        bool in = (in_mask >> r) & 1u;
         const uint32_t at = in0 + s * (2u * rs);
+        if (kSelfChecking && in) {
+            const size_t frame = static_cast<size_t>(pl.src_pitch) * pl.src_h;
+            in = self_check(p.status, bulk_range_ok(gsrc + static_cast<size_t>(r0) * 16u, row_bytes, pl.src, frame) &&
+                                          bulk_range_ok(gsrc + static_cast<size_t>(r1) * 16u, row_bytes, pl.src, frame) &&
+                                          at + 2u * rs <= in0 + kInRegionBytes && (at & 15u) == 0 && (rs & 15u) == 0);
+        }
         mbar_arrive_expect_tx(w.bar(s), (in ? 2u * row_bytes : 0u) + p.test_extra_tx);
         if (in) {
             bulk_load(smem_raw + at, gsrc + static_cast<size_t>(r0) * 16u, row_bytes, w.bar(s));
@@ -1027,7 +1027,10 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
         fence_async_smem();
         __syncwarp();
         if (lane == 0) {
-            if (out_bulk) {
+            bool store = out_bulk != 0;
+            if (kSelfChecking && store)  // (a planar destination: the first channel's plane is the one the record describes)
+                store = self_check(p.status, bulk_range_ok(gout, out_bulk, pl.dst, static_cast<size_t>(pl.dst_pitch) * pl.dst_h) && (out_s & 15u) == 0);
+            if (store) {
                 bulk_store(gout, smem_raw + out_s, out_bulk);
                 if (PLANAR) {
                     bulk_store(gout + pl.dst_cstride, smem_raw + out_s + kPlanarSegBytes, out_bulk);
@@ -1552,8 +1555,12 @@ __global__ void __launch_bounds__(kLutThreads, 1) lut_kernel(const __grid_consta
         auto issue = [&](const Cursor& c, uint32_t s) {
             const uint32_t ow = min(tile_w, dst_w - c.tx * tile_w);
             const uint32_t bytes = (ow * 3u + 15u) & ~15u;
-            mbar_arrive_expect_tx(&bar[s], bytes);
-            bulk_load(smem_raw + buf0 + s * kLutSegBytes, gsrc + static_cast<size_t>(c.r) * src_pitch + static_cast<size_t>(c.tx) * tile_w * 3u, bytes, &bar[s]);
+            const uint8_t* from = gsrc + static_cast<size_t>(c.r) * src_pitch + static_cast<size_t>(c.tx) * tile_w * 3u;
+            bool good = true;
+            if (kSelfChecking)
+                good = self_check(&g_status_word, bulk_range_ok(from, bytes, pl.src, static_cast<size_t>(pl.src_pitch) * pl.src_h) && bytes <= kLutSegBytes);
+            mbar_arrive_expect_tx(&bar[s], good ? bytes : 0u);
+            if (good) bulk_load(smem_raw + buf0 + s * kLutSegBytes, from, bytes, &bar[s]);
         };
         Cursor cu{warp, warp / tiles_x, warp % tiles_x}, pf = cu;
         constexpr uint32_t AHEAD = kLutStages - 1;
@@ -1592,7 +1599,10 @@ __global__ void __launch_bounds__(kLutThreads, 1) lut_kernel(const __grid_consta
             fence_async_smem();
             __syncwarp();
             if (lane == 0) {
-                if (out_bulk) bulk_store(out, smem_raw + seg, out_bulk);
+                bool store = out_bulk != 0;
+                if (kSelfChecking && store)
+                    store = self_check(&g_status_word, bulk_range_ok(out, out_bulk, pl.dst, static_cast<size_t>(pl.dst_pitch) * pl.dst_h));
+                if (store) bulk_store(out, smem_raw + seg, out_bulk);
                 bulk_commit();
                 bulk_wait_read_1();
                 if (pf.g < nseg) issue(pf, (k + AHEAD) % kLutStages);
@@ -1679,8 +1689,6 @@ cudaError_t launch_gather(const LaunchParams& p, dim3 grid, int pixels_per_threa
     else { if (inl) gather_kernel<4, true><<<grid, 256, 0, stream>>>(p); else gather_kernel<4, false><<<grid, 256, 0, stream>>>(p); }
     return cudaGetLastError();
 }
-
-__device__ int g_status_word;
 
 cudaError_t status_word_address(int** out) { return cudaGetSymbolAddress(reinterpret_cast<void**>(out), g_status_word); }
 

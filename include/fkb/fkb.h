@@ -54,7 +54,10 @@ enum {
     FKB_ERR_UNSUPPORTED = -3,   /* well-formed, but not a chain these kernels implement */
     FKB_ERR_CUDA = -4,          /* a CUDA runtime call failed; fkb_last_cuda_error() has the code */
     FKB_ERR_TOO_LARGE = -5,     /* more planes / bytes than the entry point accepts */
-    FKB_ERR_DEVICE_WAIT = -6    /* a bounded device-side wait gave up (reported by fkb_device_status) */
+    FKB_ERR_DEVICE_WAIT = -6,   /* a bounded device-side wait gave up (reported by fkb_device_status) */
+    FKB_ERR_DEVICE_CHECK = -7   /* the self-checking build of the library (compiled with -DFKB_DEBUG) found an address or a
+                                   size outside its buffer, or misaligned, and skipped that access (reported by
+                                   fkb_device_status); the release build has no such checks */
 };
 
 /* Pixel formats.  A source is U8C3 (PerThreadRead<_2D,uchar3>, memory_operations.h:27-38) or NV12

@@ -482,3 +482,58 @@ def test_stream_capture_small_launches_record_large_one_shot_launches_refuse():
     assert np.array_equal(small.results()[0], want)
     big.close()
     small.close()
+
+
+def test_self_checking_build_finds_nothing_on_the_parity_cases():
+    """libfkb_debug.so is the same library compiled with -DFKB_DEBUG: every bulk copy and every gathered tap is tested
+    against the buffer its plane record describes before the access, a miss is recorded as FKB_ERR_DEVICE_CHECK and the
+    access skipped (no trap).  It stands in for a memory checker.  The small configurations on all three paths, the golden
+    fixtures and the random launches are run on it in a fresh process: results equal the oracle's and the status word
+    stays clear (every one of those tests reads it)."""
+    import subprocess
+    import sys
+    from fusedkernellibrary_b200 import build as fkb_build
+    from conftest import ROOT
+    lib = fkb_build.build_debug()
+    env = dict(os.environ, FKB_LIBRARY=lib)
+    r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(ROOT, "tests", "test_gpu_parity.py"), "-m", "gpu", "-x", "-q",
+                        "-k", "configurations_small or golden_fixtures or random_launches or edge_shapes or border_reader_modes"],
+                       capture_output=True, text=True, timeout=1200, env=env, cwd=ROOT)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
+
+
+SHRUNK_FRAME = '''
+import os, sys
+sys.path.insert(0, sys.argv[1])
+import torch
+from fusedkernellibrary_b200 import abi, runtime, workloads as W
+wl = W.batched_crop_resize(n_frames=4, crops_per_frame=8, w=960, h=540)
+lib = abi.load()
+os.environ["FKB_TEST_SHRINK_FRAME"] = "1"
+dw = runtime.DeviceWorkload(wl, poison=0xCD)
+dw.launch()
+torch.cuda.synchronize()
+first = lib.fkb_device_status()
+os.environ.pop("FKB_TEST_SHRINK_FRAME")
+dw.launch()
+torch.cuda.synchronize()
+print("STATUS", first, lib.fkb_device_status())
+'''
+
+
+def test_self_checking_build_reports_a_copy_outside_its_frame(tmp_path):
+    """The checker of the self-checking build has to fire when something is wrong: with plane records that claim source
+    frames of a single row (a host-side test switch), its range tests fail for every source row below the first, the
+    copies are skipped — nothing is read out of range, nothing traps — and fkb_device_status() reports
+    FKB_ERR_DEVICE_CHECK once; the same launch without the switch is clean again."""
+    import subprocess
+    import sys
+    from fusedkernellibrary_b200 import build as fkb_build
+    from conftest import ROOT
+    script = tmp_path / "shrunk_frame.py"
+    script.write_text(SHRUNK_FRAME)
+    env = dict(os.environ, FKB_LIBRARY=fkb_build.build_debug(), FKB_TINY_PIXELS="0")
+    r = subprocess.run([sys.executable, str(script), ROOT], capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    fields = [l for l in r.stdout.splitlines() if l.startswith("STATUS ")][0].split()
+    assert int(fields[1]) == abi.ERR_DEVICE_CHECK and int(fields[2]) == abi.OK

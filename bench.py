@@ -534,71 +534,75 @@ def our_arm(args) -> None:
 
     # ---- end to end through the public entry point with host buffers: pinned sources up, launch, tensor down ----
     h_src = [torch.from_numpy(s).pin_memory() for s in wl.sources]
-    h_out = torch.empty(wl.out_sizes[0], dtype=torch.uint8).pin_memory()
     lib = abi.load()
 
-    # The step is pipelined by groups of frames on three streams, as a user feeding a camera batch would: upload the
+    # A step is pipelined by groups of frames on three streams, as a user feeding a camera batch would: upload the
     # frames of group g, launch the fused kernel over that group's planes (fkb_launch_transform with host descriptors),
-    # download its planes of the tensor.  PCIe runs in both directions at once; every byte still crosses it every step.
+    # download its planes of the tensor.  Consecutive steps alternate between two sets of device and pinned buffers, so
+    # the uploads of step i + 1 run under the downloads of step i (a stream of batches, not one batch at a time): the host
+    # link is busy in both directions all the time; every byte of every step still crosses it inside the timed region.
     group = 4  # frames per group
     n_groups = (len(h_src) + group - 1) // group
     planes_per_frame = dw.n_planes // len(h_src)
     plane_bytes = wl.out_sizes[0] // dw.n_planes
     s_up, s_run, s_down = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+    sets = [dw, runtime.DeviceWorkload(wl, poison=None)]
+    h_out = [torch.empty(wl.out_sizes[0], dtype=torch.uint8).pin_memory() for _ in sets]
     sub_planes = []
-    for g in range(n_groups):
-        lo, hi = g * group * planes_per_frame, min((g + 1) * group, len(h_src)) * planes_per_frame
-        arr = (abi.PlaneDesc * (hi - lo))()
-        for i in range(hi - lo):
-            arr[i] = dw.planes[lo + i]
-        sub_planes.append((lo, hi, arr))
+    for d in sets:
+        per_set = []
+        for g in range(n_groups):
+            lo, hi = g * group * planes_per_frame, min((g + 1) * group, len(h_src)) * planes_per_frame
+            arr = (abi.PlaneDesc * (hi - lo))()
+            for i in range(hi - lo):
+                arr[i] = d.planes[lo + i]
+            per_set.append((lo, hi, arr))
+        sub_planes.append(per_set)
 
-    def e2e_step():
+    def run_steps(n_steps: int, with_kernels: bool):
+        """n_steps steps back to back; with_kernels=False leaves the launches out (the copy bound)."""
         cur = torch.cuda.current_stream()
         for st in (s_up, s_run, s_down):
             st.wait_stream(cur)
-        for g, (lo, hi, arr) in enumerate(sub_planes):
-            with torch.cuda.stream(s_up):
-                for f in range(g * group, min((g + 1) * group, len(h_src))):
-                    dw.src[f].copy_(h_src[f], non_blocking=True)
-                up = s_up.record_event()
-            with torch.cuda.stream(s_run):
-                s_run.wait_event(up)
-                abi.check(lib.fkb_launch_transform(dw.chains, arr, hi - lo, s_run.cuda_stream))
-                ran = s_run.record_event()
-            with torch.cuda.stream(s_down):
-                s_down.wait_event(ran)
-                h_out[lo * plane_bytes: hi * plane_bytes].copy_(dw.out[0][lo * plane_bytes: hi * plane_bytes], non_blocking=True)
+        ran_all = [None, None]    # per buffer set: the last kernel that read its frames / the last download of its tensor
+        down_all = [None, None]
+        for step in range(n_steps):
+            k = step % 2
+            d = sets[k]
+            if ran_all[k] is not None:
+                s_up.wait_event(ran_all[k])     # the frames of this set are free again
+                s_run.wait_event(down_all[k])   # and so is its output tensor
+            for g, (lo, hi, arr) in enumerate(sub_planes[k]):
+                with torch.cuda.stream(s_up):
+                    for f in range(g * group, min((g + 1) * group, len(h_src))):
+                        d.src[f].copy_(h_src[f], non_blocking=True)
+                    up = s_up.record_event()
+                with torch.cuda.stream(s_run):
+                    s_run.wait_event(up)
+                    if with_kernels:
+                        abi.check(lib.fkb_launch_transform(d.chains, arr, hi - lo, s_run.cuda_stream))
+                    ran = s_run.record_event()
+                with torch.cuda.stream(s_down):
+                    s_down.wait_event(ran)
+                    h_out[k][lo * plane_bytes: hi * plane_bytes].copy_(d.out[0][lo * plane_bytes: hi * plane_bytes], non_blocking=True)
+            ran_all[k] = ran
+            down_all[k] = s_down.record_event()
         for st in (s_up, s_run, s_down):
-            cur.wait_stream(st)
-
-    # the same copies without any kernel: what the host <-> device link of this box gives the step at best
-    def copy_only_step():
-        cur = torch.cuda.current_stream()
-        for st in (s_up, s_down):
-            st.wait_stream(cur)
-        for g, (lo, hi, arr) in enumerate(sub_planes):
-            with torch.cuda.stream(s_up):
-                for f in range(g * group, min((g + 1) * group, len(h_src))):
-                    dw.src[f].copy_(h_src[f], non_blocking=True)
-            with torch.cuda.stream(s_down):
-                h_out[lo * plane_bytes: hi * plane_bytes].copy_(dw.out[0][lo * plane_bytes: hi * plane_bytes], non_blocking=True)
-        for st in (s_up, s_down):
             cur.wait_stream(st)
 
     e2e_steps = max(2, min(args.steps, 10))
-    for _ in range(2):
-        e2e_step()
+    run_steps(2, True)
     if world > 1:
         dist.barrier()
-    e2e_dt = time_launches(e2e_step, e2e_steps, torch)
+    e2e_dt = time_launches(lambda: run_steps(e2e_steps, True), 1, torch)
     e2e_dt, _ = gather_max(e2e_dt, torch, dist, world)
-    for _ in range(2):
-        copy_only_step()
+    # the same copies without any kernel: what the host <-> device link of this box gives the steps at best
+    run_steps(2, False)
     if world > 1:
         dist.barrier()
-    copy_dt = time_launches(copy_only_step, e2e_steps, torch)
+    copy_dt = time_launches(lambda: run_steps(e2e_steps, False), 1, torch)
     copy_dt, _ = gather_max(copy_dt, torch, dist, world)
+    sets[1].close()
     e2e_value = total_pixels / (e2e_dt / e2e_steps) / 1e9
     h2d = sum(s.nbytes for s in wl.sources) + dw.n_planes * 224  # frames + one 224-byte plane record per plane
     d2h = wl.out_sizes[0]
@@ -619,14 +623,15 @@ def our_arm(args) -> None:
                 "copy_bound": "the same pinned host <-> device copies on the same streams without any kernel, slowest rank: "
                               "the step cannot be faster than this on this box",
                 "path": "per group of 4 frames on three streams: pinned host frames -> device, fkb_launch_transform (host "
-                        "descriptors) over the group's planes, its planes of the float3 tensor -> pinned host"},
+                        "descriptors) over the group's planes, its planes of the float3 tensor -> pinned host; consecutive "
+                        "steps alternate between two buffer sets, so one step's uploads run under the previous step's downloads"},
         "gpu_launches": args.steps * kernels_per_step,
         "clocks": clocks,
     }
     if world > 1 and args.scaling == "weak" and not args.no_other_configs:
         # the splits of ONE job the workload descriptions name, beside the weak-scaling headline
         dw.close()
-        del dw, h_src, h_out
+        del dw, h_src, h_out, sets
         torch.cuda.empty_cache()
         t1_ms = sum(per_rank_ms) / len(per_rank_ms)
         roofline["strong_split"] = strong_split(rank, world, min(args.steps, 20), t1_ms, torch, dist)
@@ -647,7 +652,7 @@ def our_arm(args) -> None:
         roofline["reference_cuda_backend"] = ref_cuda
         if not args.no_other_configs:
             dw.close()
-            del dw
+            del dw, sets, h_src, h_out
             torch.cuda.empty_cache()
             steps_small = max(10, min(args.steps, 50))
             roofline["by_config"] = compact(other_configs(torch, steps_small, peak))

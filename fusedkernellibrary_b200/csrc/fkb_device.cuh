@@ -356,12 +356,19 @@ struct AxisTap {
     int i0, i1;    // clamped read indices
     float w0, w1;  // (x2 - s), (s - x1)
 };
+// No conversion instructions (they run at a quarter of the FP32 rate and sit on the critical path of every tap address):
+// float(t) is 2^23 + t minus 2^23, floor(s) is the mantissa of s + 2^23 rounded toward minus infinity, and float(floor(s))
+// is that sum minus 2^23 — all exact for 0 <= t and 0 <= s < 2^22, which the host's validation guarantees
+// (fx * dst_w and fy * dst_h below 2^22).
 __device__ __forceinline__ AxisTap axis_tap(int t, float f, int extent) {
-    const float s = __fmul_rn(static_cast<float>(t), f);
-    const int a = __float2int_rd(s);
+    const float tf = __fsub_rn(__uint_as_float(0x4B000000u | static_cast<uint32_t>(t)), kMagic);
+    const float s = __fmul_rn(tf, f);
+    const float m = __fadd_rd(s, kMagic);                       // 2^23 + floor(s)
+    const int a = static_cast<int>(__float_as_uint(m) & 0x7fffffu);
+    const float af = __fsub_rn(m, kMagic);                      // float(a)
     AxisTap r;
-    r.w0 = __fsub_rn(static_cast<float>(a + 1), s);
-    r.w1 = __fsub_rn(s, static_cast<float>(a));
+    r.w0 = __fsub_rn(__fadd_rn(af, 1.0f), s);
+    r.w1 = __fsub_rn(s, af);
     r.i0 = min(a, extent - 1);
     r.i1 = min(a + 1, extent - 1);
     return r;

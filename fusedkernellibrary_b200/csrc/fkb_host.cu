@@ -186,6 +186,8 @@ int check_plane(const fkb_chain_desc& ch, const fkb_plane_desc& pl) {
         // no pixel is inside, the whole plane is background, and the scale factors (then infinite) are never used.
         const bool empty = ch.geometry >= FKB_GEOM_RESIZE_PRESERVE_AR && (pl.x2 < pl.x1 || pl.y2 < pl.y1);
         if (!empty && (!(pl.fx > 0.f) || !(pl.fy > 0.f) || !std::isfinite(pl.fx) || !std::isfinite(pl.fy))) return FKB_ERR_INVALID;
+        // source coordinates stay below 2^22 (the kernels take their floor without a conversion instruction)
+        if (!empty && (!(pl.fx * static_cast<float>(pl.dst_w) < 4194304.f) || !(pl.fy * static_cast<float>(pl.dst_h) < 4194304.f))) return FKB_ERR_UNSUPPORTED;
         if (ch.geometry >= FKB_GEOM_RESIZE_PRESERVE_AR && !empty) {
             if (pl.x1 < 0 || pl.y1 < 0 || pl.x2 >= static_cast<int>(pl.dst_w) || pl.y2 >= static_cast<int>(pl.dst_h)) return FKB_ERR_INVALID;
         }

@@ -1337,11 +1337,9 @@ __device__ __forceinline__ f2 magic_pair(uint32_t wa, uint32_t wb, uint32_t sel)
     return f2{__uint_as_float(__byte_perm(wa, 0x4B000000u, sel)), __uint_as_float(__byte_perm(wb, 0x4B000000u, sel))};
 }
 template <bool SCALED_LUMA, bool VU>
-__device__ __forceinline__ void nv12_pair(const LaunchParams& p, const PlaneRec& pl, uint32_t xa, uint32_t y) {
+__device__ __forceinline__ void nv12_pair(const Nv12Consts& k, const float nz, const PlaneRec& pl, uint32_t xa, uint32_t y) {
     if (pl.kclass != KCLASS_NV12) return;
     if (xa >= pl.dst_w || y >= pl.dst_h) return;
-    const Nv12Consts& k = p.nv12;
-    const float nz = p.neg_zero;
     const bool par = k.preserve_ar != 0;
     const uint32_t xb = xa + 1;
     const bool has_b = xb < pl.dst_w;
@@ -1438,14 +1436,25 @@ __device__ __forceinline__ void nv12_pair(const LaunchParams& p, const PlaneRec&
 template <int THREADS, int MINB, bool SCALED_LUMA, bool VU>
 __global__ void __launch_bounds__(THREADS, MINB) nv12_pair_kernel(const __grid_constant__ LaunchParams p) {
     const uint32_t x = (blockIdx.x * 32 + (threadIdx.x & 31)) * 2, y = blockIdx.y * (THREADS / 32) + (threadIdx.x >> 5);
-    // three copies of the body, so that each knows where its plane record lives: the single plane of a one-plane launch
-    // (every field a constant-bank operand, the pointers uniform), one of a few kernel-parameter records, or a table entry
+    // two copies of the body, so that each knows where its plane records live: a few kernel-parameter records, or a table
     if (p.table == nullptr) {
-        if (p.n_planes == 1) nv12_pair<SCALED_LUMA, VU>(p, p.inline_planes[0], x, y);
-        else for (uint32_t z = p.pixel_z0 + blockIdx.z; z < p.pixel_z1; z += gridDim.z) nv12_pair<SCALED_LUMA, VU>(p, p.inline_planes[z], x, y);
+        for (uint32_t z = p.pixel_z0 + blockIdx.z; z < p.pixel_z1; z += gridDim.z) nv12_pair<SCALED_LUMA, VU>(p.nv12, p.neg_zero, p.inline_planes[z], x, y);
     } else {
-        for (uint32_t z = p.pixel_z0 + blockIdx.z; z < p.pixel_z1; z += gridDim.z) nv12_pair<SCALED_LUMA, VU>(p, p.table[z], x, y);
+        for (uint32_t z = p.pixel_z0 + blockIdx.z; z < p.pixel_z1; z += gridDim.z) nv12_pair<SCALED_LUMA, VU>(p.nv12, p.neg_zero, p.table[z], x, y);
     }
+}
+// The one-plane launch (a frame into a network's input tensor) carries only what it reads — the chain's constants and the
+// plane's record, 0.4 KB instead of the 5.6 KB of LaunchParams: every field is a constant-bank operand at a fixed offset,
+// and a launch this short feels the size of its parameter block.
+struct PairParams1 {
+    Nv12Consts nv12;
+    float neg_zero;
+    PlaneRec plane;
+};
+template <int THREADS, int MINB, bool SCALED_LUMA, bool VU>
+__global__ void __launch_bounds__(THREADS, MINB) nv12_pair1_kernel(const __grid_constant__ PairParams1 q) {
+    const uint32_t x = (blockIdx.x * 32 + (threadIdx.x & 31)) * 2, y = blockIdx.y * (THREADS / 32) + (threadIdx.x >> 5);
+    nv12_pair<SCALED_LUMA, VU>(q.nv12, q.neg_zero, q.plane, x, y);
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -1654,7 +1663,15 @@ cudaError_t launch_nv12(const LaunchParams& p, dim3 grid, cudaStream_t stream) {
     if (p.nv12.pair) {
         const dim3 g(grid.x, grid.y * 2, grid.z);
         const bool scaled = p.nv12.ccm[0] != 1.f;
-        if (scaled && p.nv12.vu) nv12_pair_kernel<128, 10, true, true><<<g, 128, 0, stream>>>(p);
+        if (p.table == nullptr && p.n_planes == 1) {
+            PairParams1 q;
+            q.nv12 = p.nv12; q.neg_zero = p.neg_zero; q.plane = p.inline_planes[0];
+            if (scaled && p.nv12.vu) nv12_pair1_kernel<128, 10, true, true><<<g, 128, 0, stream>>>(q);
+            else if (scaled) nv12_pair1_kernel<128, 10, true, false><<<g, 128, 0, stream>>>(q);
+            else if (p.nv12.vu) nv12_pair1_kernel<128, 10, false, true><<<g, 128, 0, stream>>>(q);
+            else nv12_pair1_kernel<128, 10, false, false><<<g, 128, 0, stream>>>(q);
+        }
+        else if (scaled && p.nv12.vu) nv12_pair_kernel<128, 10, true, true><<<g, 128, 0, stream>>>(p);
         else if (scaled) nv12_pair_kernel<128, 10, true, false><<<g, 128, 0, stream>>>(p);
         else if (p.nv12.vu) nv12_pair_kernel<128, 10, false, true><<<g, 128, 0, stream>>>(p);
         else nv12_pair_kernel<128, 10, false, false><<<g, 128, 0, stream>>>(p);

@@ -195,7 +195,8 @@ typedef struct fkb_plane_desc {
     uint32_t dst_w, dst_h;   /* pixels this plane writes */
     uint32_t dst_pitch;      /* bytes between destination rows */
     uint64_t dst_channel_stride; /* FKB_WRITE_SPLIT: bytes between channel planes; else 0 */
-    float fx, fy;            /* ResizeParams::src_conv_factors (resize.h:44-58) */
+    float fx, fy;            /* ResizeParams::src_conv_factors (resize.h:44-58); fx * dst_w and fy * dst_h must stay below
+                                2^22 (source coordinates of four million and more are FKB_ERR_UNSUPPORTED) */
     int32_t x1, y1, x2, y2;  /* PRESERVE_AR: inclusive rectangle of the resized image inside dst */
     float bg[3];             /* PRESERVE_AR: ResizeParams::defaultValue outside that rectangle */
     uint32_t chain;          /* bits 0..30: divergent launch: which chain runs on this plane (0-based); else 0.

@@ -222,8 +222,9 @@ def time_launches(fn, steps: int, torch) -> float:
 
 def other_configs(torch, steps: int, peak: float, widened: bool = False) -> dict:
     """Kernel-only figures of the other four configurations on one GPU.  Their launches last a few microseconds, less
-    than the host needs to submit one, so a round over all buffer sets is captured once into a CUDA graph and the graph
-    is replayed; rotating the buffer sets (together larger than the L2) makes every launch read from HBM."""
+    than the host needs to submit one, so rounds over all buffer sets are captured into one CUDA graph (about two
+    milliseconds of work: a replay far outlasts the host's cost of submitting it) and the graph is replayed; rotating the
+    buffer sets (together larger than the L2) makes every launch read from HBM."""
     from fusedkernellibrary_b200 import abi, runtime, workloads as W
     out = {}
     cases = [("readme_crops", W.readme_crops), ("vertical_fusion", W.vertical_fusion),
@@ -256,17 +257,28 @@ def other_configs(torch, steps: int, peak: float, widened: bool = False) -> dict
             for s in sets:
                 s.launch_plan()
         torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
+        # A replay must last much longer than the host needs to submit it (tens of microseconds), or the figure is the
+        # host's replay rate: as many rounds over the sets go into one graph as fill about two milliseconds.
+        def one_round():
+            for s in sets:
+                s.launch_plan()
+        est = time_launches(one_round, 3, torch) / 3
+        inner = max(1, min(64, int(2e-3 / max(est, 1e-6)) + 1))
         side = torch.cuda.Stream()
-        with torch.cuda.stream(side):
-            with torch.cuda.graph(graph, stream=side):
-                for s in sets:
-                    s.launch_plan()
-        rounds = max(30, steps)  # these launches last microseconds: many replays, and the median of five measurements
-        graph.replay()
+
+        def capture(body):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(g, stream=side):
+                    for _ in range(inner):
+                        body()
+            g.replay()
+            return g
+        graph = capture(one_round)
+        rounds = max(10, steps // 2)  # replays per measurement; the median of five measurements is reported
 
         def median_time(replay):
-            return sorted(time_launches(replay, rounds, torch) / (rounds * n_sets) for _ in range(5))[2]
+            return sorted(time_launches(replay, rounds, torch) / (rounds * inner * n_sets) for _ in range(5))[2]
         dt = median_time(graph.replay)
         ref_us = None
         try:
@@ -277,12 +289,10 @@ def other_configs(torch, steps: int, peak: float, widened: bool = False) -> dict
                     for fn in launchers:
                         fn()
                     torch.cuda.synchronize()
-                    ref_graph = torch.cuda.CUDAGraph()
-                    with torch.cuda.stream(side):
-                        with torch.cuda.graph(ref_graph, stream=side):
-                            for fn in launchers:
-                                fn()
-                    ref_graph.replay()
+                    def ref_round():
+                        for fn in launchers:
+                            fn()
+                    ref_graph = capture(ref_round)
                     ref_us = median_time(ref_graph.replay) * 1e6
                     del ref_graph
         except Exception as exc:  # the comparison is optional; the product's figures never depend on it
@@ -290,7 +300,8 @@ def other_configs(torch, steps: int, peak: float, widened: bool = False) -> dict
         out[name] = {"us_per_launch": dt * 1e6, "reference_cuda_us_per_launch": ref_us, "gpix_s": wl.out_pixels / dt / 1e9, "alg_bytes": alg["total"],
                      "hbm_gbs": alg["total"] / dt / 1e9, "frac_of_measured_peak": alg["total"] / dt / 1e9 / peak,
                      "buffer_sets_rotated": n_sets, "kernels_per_launch": sets[0].kernel_launches(),
-                     "timing": "CUDA graph of one round over the buffer sets, replayed; median of five measurements"}
+                     "rounds_per_graph": inner,
+                     "timing": "CUDA graph of rounds_per_graph rounds over the buffer sets (about 2 ms of work), replayed; median of five measurements"}
         del graph
         for s in sets:
             s.close()

@@ -812,9 +812,10 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
     // rows (the second repeats the first where the reference clamps y2), so that the second row sits at a fixed
     // distance from the first.
     auto load_rows = [&](uint32_t r, uint32_t s, uint32_t r0, uint32_t r1) {
-        bool in = (in_mask >> r) & 1u;
+        if (!((in_mask >> r) & 1u)) return;  // a row above or below the image reads nothing and waits for nothing
+        bool in = true;
         const uint32_t at = in0 + s * (2u * rs);
-        if (kSelfChecking && in) {
+        if (kSelfChecking) {
             const size_t frame = static_cast<size_t>(pl.src_pitch) * pl.src_h;
             in = self_check(p.status, bulk_range_ok(gsrc + static_cast<size_t>(r0) * 16u, row_bytes, pl.src, frame) &&
                                           bulk_range_ok(gsrc + static_cast<size_t>(r1) * 16u, row_bytes, pl.src, frame) &&
@@ -984,23 +985,39 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
     // Row loop.  Per row: wait for its source rows, compute it into an output-row buffer, and then — in lane 0's one
     // divergent stretch per row — send the row off with a bulk store, request the source rows of row r + ns into the
     // stage just read, and wait until the store of the previous row has finished reading the other buffer.
+    // A row above or below the image is background from end to end: the first of a run of them is written into a buffer,
+    // the others are stored from that same buffer again with nothing written and nothing waited for.  The two buffers
+    // alternate by rows written, so a buffer is written only after wait_group.read has covered every store that read it.
     const uint32_t out_bytes = ow * ELT, out_bulk = out_bytes & ~15u;
     uint8_t* gout = gdst;
-    uint32_t s = 0;  // stage of the row being computed: r mod ns
+    uint32_t s = 0;         // stage of the row being computed: r mod ns
+    uint32_t o = 0;         // the output-row buffer the next written row goes to
+    bool bg_ready = false;  // the other buffer holds a background row (the previous row was one)
     for (uint32_t r = 0; r < nr; ++r, gout += dst_pitch) {
-        const float wy0s = __shfl_sync(FULL, wy0_l, r), wy1s = __shfl_sync(FULL, wy1_l, r);
         const uint32_t r0n = __shfl_sync(FULL, row0_l, (r + ns) & 31u), r1n = __shfl_sync(FULL, row1_l, (r + ns) & 31u);
         const bool row_in = (in_mask >> r) & 1u;
-        const bool ok = mbar_wait_bounded(w.bar(s), (ph >> s) & 1u, p.wait_limit_ns);
-        if (__any_sync(FULL, !ok)) return false;  // (a convergence point for the whole warp, too)
-        ph ^= 1u << s;
-        const uint32_t in_s = in0 + s * (2u * rs), out_s = w.out(r & 1u);
+        const uint32_t in_s = in0 + s * (2u * rs);
+        uint32_t out_s;
         if (!row_in) {
-            // a row above or below the image: background over the inside columns too
+            if (bg_ready) out_s = w.out(o ^ 1u);
+            else {
+                out_s = w.out(o);
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-                if (j < nj) put(out_s + ocol(j), bgbits[0], bgbits[1], bgbits[2]);
+                for (int j = 0; j < 8; ++j)
+                    if (j < nj) put(out_s + ocol(j), bgbits[0], bgbits[1], bgbits[2]);
+                o ^= 1u;
+                bg_ready = true;
+                fence_async_smem();
+                __syncwarp();
+            }
         } else {
+            const float wy0s = __shfl_sync(FULL, wy0_l, r), wy1s = __shfl_sync(FULL, wy1_l, r);
+            const bool ok = mbar_wait_bounded(w.bar(s), (ph >> s) & 1u, p.wait_limit_ns);
+            if (__any_sync(FULL, !ok)) return false;  // (a convergence point for the whole warp, too)
+            ph ^= 1u << s;
+            out_s = w.out(o);
+            o ^= 1u;
+            bg_ready = false;
             if (replicate)
             {  // every lane writes the same three bytes (even lanes the first staged row, odd lanes the second)
                 const uint32_t q = in_s + (lane & 1u) * rs + rep_off;
@@ -1023,9 +1040,9 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
             case 1: pair(0, in_s, out_s, wy0, wy1);
             default: break;
             }
+            fence_async_smem();
+            __syncwarp();
         }
-        fence_async_smem();
-        __syncwarp();
         if (lane == 0) {
             bool store = out_bulk != 0;
             if (kSelfChecking && store)  // (a planar destination: the first channel's plane is the one the record describes)

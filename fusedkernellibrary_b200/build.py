@@ -63,6 +63,22 @@ def build_debug(force: bool = False) -> str:
     return out
 
 
+def build_phase_clocks() -> str:
+    """The phase-clock build, lib/libfkb_phase.so: the same sources with -DFKB_PHASE_CLOCKS, in which the warps of
+    staged_kernel add up the cycles they spend in each phase of a resize row (``profile_case.py --phase-clocks`` prints
+    them).  A measuring aid, built on request only; it runs slower than the product."""
+    out = os.path.join(OUT_DIR, "libfkb_phase.so")
+    os.makedirs(OUT_DIR, exist_ok=True)
+    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    cmd = [nvcc, *NVCC_FLAGS, "-DFKB_PHASE_CLOCKS", "-I", os.path.join(ROOT, "include"), "-I", CSRC, "-o", out,
+           *[os.path.join(CSRC, s) for s in SOURCES]]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        sys.stderr.write(res.stdout + res.stderr)
+        raise RuntimeError("nvcc failed building libfkb_phase.so")
+    return out
+
+
 def build_frontend_bench(force: bool = False) -> str:
     """Compiles bench_frontend.cpp (the host-cost measurement bench.py runs: a program written against the fk:: front
     end, linked to libfkb.so and the CUDA runtime only) into lib/bench_frontend."""

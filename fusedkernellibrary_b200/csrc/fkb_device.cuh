@@ -196,6 +196,46 @@ __device__ __forceinline__ bool bulk_range_ok(const void* a, uint32_t bytes, con
 }
 
 // ---------------------------------------------------------------------------------------------------------
+// the phase-clock build (-DFKB_PHASE_CLOCKS)
+// ---------------------------------------------------------------------------------------------------------
+// Shows where a warp of staged_kernel spends the cycles of a resize row: lane 0 reads the SM's cycle counter between
+// the phases of the row loop and adds the differences up; at the end of an item it adds them to its warp's own slot of
+// a device array (no atomics: a slot belongs to one warp), which fkb_debug_phase_clocks() sums and returns.  The reads
+// keep the compiler from moving instructions across them, so this build runs slower than the product; what it gives is
+// the split.  In the product build all of this compiles to nothing.
+enum : int {
+    kPhaseWait = 0,      // shuffles + waiting for the row's source rows to land
+    kPhaseCompute = 1,   // taps, arithmetic, stores into the row buffer, proxy fence, warp sync
+    kPhaseStore = 2,     // issuing the bulk store(s) of the row
+    kPhaseCommit = 3,    // closing the bulk group
+    kPhaseLoads = 4,     // arrive.expect_tx + issuing the two bulk loads of a later row
+    kPhaseWaitRead = 5,  // waiting until the previous row's store has read its buffer
+    kPhaseRows = 6,      // rows processed (a count, not cycles)
+    kPhaseTotal = 7,     // cycles of the whole row loop
+    kPhaseCount = 8
+};
+#ifdef FKB_PHASE_CLOCKS
+constexpr bool kPhaseClocks = true;
+#else
+constexpr bool kPhaseClocks = false;
+#endif
+struct PhaseClock {
+    long long t, acc[kPhaseCount];
+    __device__ __forceinline__ PhaseClock() {
+        if (kPhaseClocks) {
+#pragma unroll
+            for (int i = 0; i < kPhaseCount; ++i) acc[i] = 0;
+            t = clock64();
+        }
+    }
+    // the cycles since the previous call go to phase i
+    __device__ __forceinline__ void lap(int i) {
+        if (kPhaseClocks) { const long long n = clock64(); acc[i] += n - t; acc[kPhaseTotal] += n - t; t = n; }
+    }
+    __device__ __forceinline__ void count(int i) { if (kPhaseClocks) acc[i] += 1; }
+};
+
+// ---------------------------------------------------------------------------------------------------------
 // arithmetic
 // ---------------------------------------------------------------------------------------------------------
 // Integer <-> float without conversion instructions (those run at a quarter of the FP32 rate).

@@ -531,6 +531,20 @@ __global__ void __launch_bounds__(256) rgba_kernel(const __grid_constant__ Launc
 // All shared-memory accesses go through 32-bit offsets into this array, so that the address arithmetic is 32-bit
 // integer adds and the accesses are plain LDS/STS with immediate offsets.
 extern __shared__ __align__(128) uint8_t smem_raw[];
+#ifdef FKB_PHASE_CLOCKS
+constexpr uint32_t kPhaseSlots = 8192;  // one per warp of the grid (2 CTAs x 8 warps on each of at most 512 SMs)
+__device__ unsigned long long g_phase_clocks[kPhaseSlots][kPhaseCount];
+#endif
+__device__ __forceinline__ void phase_clock_flush(const PhaseClock& pc, uint32_t lane) {
+#ifdef FKB_PHASE_CLOCKS
+    const uint32_t slot = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (lane == 0 && slot < kPhaseSlots) {
+#pragma unroll
+        for (int i = 0; i < kPhaseCount; ++i) g_phase_clocks[slot][i] += static_cast<unsigned long long>(pc.acc[i]);
+    }
+#endif
+}
+
 
 struct WarpSlice {
     uint32_t base;  // offset of this warp's slice in smem_raw
@@ -993,6 +1007,7 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
     uint32_t s = 0;         // stage of the row being computed: r mod ns
     uint32_t o = 0;         // the output-row buffer the next written row goes to
     bool bg_ready = false;  // the other buffer holds a background row (the previous row was one)
+    PhaseClock pc;
     for (uint32_t r = 0; r < nr; ++r, gout += dst_pitch) {
         const uint32_t r0n = __shfl_sync(FULL, row0_l, (r + ns) & 31u), r1n = __shfl_sync(FULL, row1_l, (r + ns) & 31u);
         const bool row_in = (in_mask >> r) & 1u;
@@ -1014,6 +1029,7 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
             const float wy0s = __shfl_sync(FULL, wy0_l, r), wy1s = __shfl_sync(FULL, wy1_l, r);
             const bool ok = mbar_wait_bounded(w.bar(s), (ph >> s) & 1u, p.wait_limit_ns);
             if (__any_sync(FULL, !ok)) return false;  // (a convergence point for the whole warp, too)
+            pc.lap(kPhaseWait);
             ph ^= 1u << s;
             out_s = w.out(o);
             o ^= 1u;
@@ -1043,6 +1059,8 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
             fence_async_smem();
             __syncwarp();
         }
+        pc.lap(kPhaseCompute);
+        pc.count(kPhaseRows);
         if (lane == 0) {
             bool store = out_bulk != 0;
             if (kSelfChecking && store)  // (a planar destination: the first channel's plane is the one the record describes)
@@ -1054,9 +1072,13 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
                     bulk_store(gout + pl.dst_cstride2, smem_raw + out_s + 2 * kPlanarSegBytes, out_bulk);
                 }
             }
+            pc.lap(kPhaseStore);
             bulk_commit();
+            pc.lap(kPhaseCommit);
             if (r + ns < nr) load_rows(r + ns, s, r0n, r1n);
+            pc.lap(kPhaseLoads);
             bulk_wait_read_1();  // the store of the row before has read its buffer: the next row may be written there
+            pc.lap(kPhaseWaitRead);
         }
         s = s + 1u == ns ? 0u : s + 1u;
         if (out_bytes != out_bulk && lane < out_bytes - out_bulk) {  // rare: a row whose byte length is not a multiple of 16
@@ -1067,6 +1089,7 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
             }
         }
     }
+    phase_clock_flush(pc, lane);
     return true;
 }
 
@@ -1660,6 +1683,28 @@ cudaError_t launch_staged(const LaunchParams& p, uint32_t grid, cudaStream_t str
     staged_kernel<<<grid, kStagedThreads, kStagedSmemBytes, stream>>>(p);
     return cudaGetLastError();
 }
+
+#ifdef FKB_PHASE_CLOCKS
+}  // namespace fkb
+// Only in the phase-clock build: the sums over all warps since the last reset (see PhaseClock), out[kPhaseCount].
+extern "C" int fkb_debug_phase_clocks(unsigned long long* out, int reset) {
+    static unsigned long long host[fkb::kPhaseSlots][fkb::kPhaseCount];
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    if (out) {
+        if (cudaMemcpyFromSymbol(host, fkb::g_phase_clocks, sizeof(host)) != cudaSuccess) return -1;
+        for (int i = 0; i < fkb::kPhaseCount; ++i) {
+            out[i] = 0;
+            for (uint32_t s = 0; s < fkb::kPhaseSlots; ++s) out[i] += host[s][i];
+        }
+    }
+    if (reset) {
+        void* sym = nullptr;
+        if (cudaGetSymbolAddress(&sym, fkb::g_phase_clocks) != cudaSuccess || cudaMemset(sym, 0, sizeof(host)) != cudaSuccess) return -1;
+    }
+    return 0;
+}
+namespace fkb {
+#endif
 
 cudaError_t launch_lut(const LaunchParams& p, uint32_t grid, cudaStream_t stream) {
     static thread_local int configured_device = -1;

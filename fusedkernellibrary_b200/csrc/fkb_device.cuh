@@ -285,6 +285,14 @@ __device__ __forceinline__ f2 mul2_unfusable(f2 a, f2 b, float neg_zero) {
     return r;
 }
 
+__device__ __forceinline__ f2 fma2(f2 a, f2 b, f2 c) {
+    f2 r;
+    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(r.x), "=f"(r.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+    return r;
+}
+
 // Exact fp32 value b * 2^-24 of a byte b: the byte is read as the bit pattern of a subnormal half and widened, which
 // runs on the FP pipe instead of the slow integer->float conversion unit.  Multiplying by a weight that was pre-scaled
 // by 2^24 (exact) gives exactly the correctly rounded product b * w.

@@ -450,19 +450,23 @@ __global__ void __launch_bounds__(256) gather4_kernel(const __grid_constant__ La
     }
 }
 
-// rgba_kernel: the same four-channel chains without an interpreter.  One output pixel per thread; the chain's ops after
-// the interpolation arrive flattened as at most six steps (FourConsts), N of them, unrolled.  A tap byte becomes a float
-// without a conversion: the byte, moved to the low end of a word, is the bit pattern of the subnormal b * 2^-149; the
-// vertical weights carry a factor of 2^127, and one exact multiplication by 2^22 puts the scale right (see resize_item).
+// rgba_kernel: the same four-channel chains without an interpreter.  Two horizontally adjacent output pixels per thread,
+// so that every arithmetic step is one packed f32x2 instruction per channel; the chain's ops after the interpolation
+// arrive flattened as at most six steps (FourConsts), N of them, unrolled.  A tap byte becomes a float without a
+// conversion: the byte, moved to the low end of a word, is the bit pattern of the subnormal b * 2^-149; the vertical
+// weights carry a factor of 2^127, and one exact multiplication by 2^22 puts the scale right (see resize_item).
+// Taps are computed for clamped coordinates, so that every address is valid; letterbox pixels are replaced afterwards.
 template <int N, bool SRC3>
 __global__ void __launch_bounds__(256) rgba_kernel(const __grid_constant__ LaunchParams p) {
     const PlaneRec* table = plane_table(p);
     const FourConsts& k = p.four;
-    const uint32_t x = blockIdx.x * 32 + (threadIdx.x & 31), y = blockIdx.y * 8 + (threadIdx.x >> 5);
+    const float nz = p.neg_zero;
+    const uint32_t xa = (blockIdx.x * 32 + (threadIdx.x & 31)) * 2, xb = xa + 1, y = blockIdx.y * 8 + (threadIdx.x >> 5);
     for (uint32_t z = p.gather4_z0 + blockIdx.z; z < p.gather4_z1; z += gridDim.z) {
         const PlaneRec& pl = table[z];
-        if (pl.kclass != KCLASS_GATHER4 || x >= pl.dst_w || y >= pl.dst_h) continue;
-        float v[4];
+        if (pl.kclass != KCLASS_GATHER4 || xa >= pl.dst_w || y >= pl.dst_h) continue;
+        const bool has_b = xb < pl.dst_w;
+        f2 v[4];  // channel c of the two pixels
         constexpr uint32_t sp = SRC3 ? 3u : 4u;
         const uint32_t pitch = pl.src_pitch;
         auto tap = [&](const uint8_t* row, uint32_t X) -> uint32_t {  // the pixel's bytes in one word (byte 3 = 0 for a uchar3 source)
@@ -471,29 +475,46 @@ __global__ void __launch_bounds__(256) rgba_kernel(const __grid_constant__ Launc
             return __ldg(q) | (__ldg(q + 1) << 8) | (__ldg(q + 2) << 16);
         };
         if (!k.resize) {
-            const uint32_t px = tap(pl.src + static_cast<size_t>(pl.crop_y + y) * pitch, pl.crop_x + x);
+            const uint8_t* row = pl.src + static_cast<size_t>(pl.crop_y + y) * pitch;
+            const uint32_t pa = tap(row, pl.crop_x + xa), pb = tap(row, pl.crop_x + (has_b ? xb : xa));
 #pragma unroll
-            for (int c = 0; c < 4; ++c) v[c] = FKB_BYTE_F32(px, c);
+            for (int c = 0; c < 4; ++c) v[c] = f2{FKB_BYTE_F32(pa, c), FKB_BYTE_F32(pb, c)};
         } else {
             const bool par = k.preserve_ar != 0;
-            const int xi = static_cast<int>(x), yi = static_cast<int>(y);
-            if (!par || (xi >= pl.x1 && xi <= pl.x2 && yi >= pl.y1 && yi <= pl.y2)) {
-                const AxisTap ax = axis_tap(xi - (par ? pl.x1 : 0), pl.fx, pl.crop_w), ay = axis_tap(yi - (par ? pl.y1 : 0), pl.fy, pl.crop_h);
-                const uint8_t* r0 = pl.src + static_cast<size_t>(ay.i0 + pl.crop_y) * pitch;
-                const uint8_t* r1 = pl.src + static_cast<size_t>(ay.i1 + pl.crop_y) * pitch;
-                const uint32_t t00 = tap(r0, ax.i0 + pl.crop_x), t10 = tap(r0, ax.i1 + pl.crop_x);
-                const uint32_t t01 = tap(r1, ax.i0 + pl.crop_x), t11 = tap(r1, ax.i1 + pl.crop_x);
-                const float wy0 = __fmul_rn(ay.w0, kTapScale), wy1 = __fmul_rn(ay.w1, kTapScale);
-                const float w00 = __fmul_rn(ax.w0, wy0), w10 = __fmul_rn(ax.w1, wy0), w01 = __fmul_rn(ax.w0, wy1), w11 = __fmul_rn(ax.w1, wy1);
+            const int ox = par ? pl.x1 : 0, oy = par ? pl.y1 : 0;
+            const AxisTap ta = axis_tap(max(static_cast<int>(xa) - ox, 0), pl.fx, pl.crop_w);
+            const AxisTap tb = axis_tap(max(static_cast<int>(xb) - ox, 0), pl.fx, pl.crop_w);
+            const AxisTap ty = axis_tap(max(static_cast<int>(y) - oy, 0), pl.fy, pl.crop_h);
+            const uint8_t* r0 = pl.src + static_cast<size_t>(ty.i0 + pl.crop_y) * pitch;
+            const uint8_t* r1 = pl.src + static_cast<size_t>(ty.i1 + pl.crop_y) * pitch;
+            // tap order: (x0,y0) (x1,y0) (x0,y1) (x1,y1); all eight pixel loads are requested before any is used
+            const uint32_t a00 = tap(r0, ta.i0 + pl.crop_x), a10 = tap(r0, ta.i1 + pl.crop_x), a01 = tap(r1, ta.i0 + pl.crop_x), a11 = tap(r1, ta.i1 + pl.crop_x);
+            const uint32_t b00 = tap(r0, tb.i0 + pl.crop_x), b10 = tap(r0, tb.i1 + pl.crop_x), b01 = tap(r1, tb.i0 + pl.crop_x), b11 = tap(r1, tb.i1 + pl.crop_x);
+            const float wy0s = __fmul_rn(ty.w0, kTapScale), wy1s = __fmul_rn(ty.w1, kTapScale);
+            const f2 wy0{wy0s, wy0s}, wy1{wy1s, wy1s}, wx0{ta.w0, tb.w0}, wx1{ta.w1, tb.w1};
+            const f2 w00 = mul2(wx0, wy0), w10 = mul2(wx1, wy0), w01 = mul2(wx0, wy1), w11 = mul2(wx1, wy1);
+            const f2 unscale{kTapUnscale, kTapUnscale};
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const uint32_t sel = 0x4440u | c;  // byte c to the low end, zeros above it
+                const f2 p00{__uint_as_float(__byte_perm(a00, 0u, sel)), __uint_as_float(__byte_perm(b00, 0u, sel))};
+                const f2 p10{__uint_as_float(__byte_perm(a10, 0u, sel)), __uint_as_float(__byte_perm(b10, 0u, sel))};
+                const f2 p01{__uint_as_float(__byte_perm(a01, 0u, sel)), __uint_as_float(__byte_perm(b01, 0u, sel))};
+                const f2 p11{__uint_as_float(__byte_perm(a11, 0u, sel)), __uint_as_float(__byte_perm(b11, 0u, sel))};
+                const f2 s = add2(add2(add2(mul2_unfusable(p00, w00, nz), mul2_unfusable(p10, w10, nz)), mul2_unfusable(p01, w01, nz)),
+                                  mul2_unfusable(p11, w11, nz));
+                v[c] = mul2(s, unscale);  // (exact, and followed by no addition it could fuse with: the steps are FMAs already)
+            }
+            if (par) {
+                const int xi = static_cast<int>(xa), yi = static_cast<int>(y);
+                const bool row_in = yi >= pl.y1 && yi <= pl.y2;
+                const bool in_a = row_in && xi >= pl.x1 && xi <= pl.x2, in_b = row_in && xi + 1 >= pl.x1 && xi + 1 <= pl.x2;
+                const float bg[4] = {pl.bg[0], pl.bg[1], pl.bg[2], pl.bg_w};
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
-                    const uint32_t sel = 0x4440u | c;  // byte c to the low end, zeros above it
-                    const float b = bilerp(__uint_as_float(__byte_perm(t00, 0u, sel)), __uint_as_float(__byte_perm(t10, 0u, sel)),
-                                           __uint_as_float(__byte_perm(t01, 0u, sel)), __uint_as_float(__byte_perm(t11, 0u, sel)), w00, w10, w01, w11);
-                    v[c] = __fmul_rn(b, kTapUnscale);
+                    if (!in_a) v[c].x = bg[c];
+                    if (!in_b) v[c].y = bg[c];
                 }
-            } else {
-                v[0] = pl.bg[0]; v[1] = pl.bg[1]; v[2] = pl.bg[2]; v[3] = pl.bg_w;
             }
         }
 #pragma unroll
@@ -501,25 +522,34 @@ __global__ void __launch_bounds__(256) rgba_kernel(const __grid_constant__ Launc
             const uint32_t kind = (k.kinds >> (2 * i)) & 3u;
             if (kind == 0u) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) v[c] = __fmaf_rn(v[c], k.m[i][c], k.a[i][c]);
+                for (int c = 0; c < 4; ++c) v[c] = fma2(v[c], f2{k.m[i][c], k.m[i][c]}, f2{k.a[i][c], k.a[i][c]});
             } else if (kind == 1u) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) v[c] = __fdiv_rn(v[c], k.m[i][c]);
+                for (int c = 0; c < 4; ++c) v[c] = f2{__fdiv_rn(v[c].x, k.m[i][c]), __fdiv_rn(v[c].y, k.m[i][c])};
             } else {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) v[c] = sat_u8_as_float(v[c]);
+                for (int c = 0; c < 4; ++c) v[c] = f2{sat_u8_as_float(v[c].x), sat_u8_as_float(v[c].y)};
             }
         }
-        float o[4];
+        f2 o[4];
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
             const uint32_t from = (k.perm >> (2 * c)) & 3u;
             o[c] = from == 0u ? v[0] : from == 1u ? v[1] : from == 2u ? v[2] : v[3];
         }
         uint8_t* row = pl.dst + static_cast<size_t>(y) * pl.dst_pitch;
-        if (k.f32) *reinterpret_cast<float4*>(row + static_cast<size_t>(x) * 16) = make_float4(o[0], o[1], o[2], o[3]);
-        else *reinterpret_cast<uint32_t*>(row + static_cast<size_t>(x) * 4) =
-                 static_cast<uint32_t>(o[0]) | (static_cast<uint32_t>(o[1]) << 8) | (static_cast<uint32_t>(o[2]) << 16) | (static_cast<uint32_t>(o[3]) << 24);
+        if (k.f32) {
+            float4* q = reinterpret_cast<float4*>(row + static_cast<size_t>(xa) * 16);
+            q[0] = make_float4(o[0].x, o[1].x, o[2].x, o[3].x);
+            if (has_b) q[1] = make_float4(o[0].y, o[1].y, o[2].y, o[3].y);
+        } else {
+            // (the values are integers in [0, 255] held exactly: the chain ended in a SaturateCast)
+            const uint32_t wa = u8_of_exact(o[0].x) | (u8_of_exact(o[1].x) << 8) | (u8_of_exact(o[2].x) << 16) | (u8_of_exact(o[3].x) << 24);
+            const uint32_t wb = u8_of_exact(o[0].y) | (u8_of_exact(o[1].y) << 8) | (u8_of_exact(o[2].y) << 16) | (u8_of_exact(o[3].y) << 24);
+            uint32_t* q = reinterpret_cast<uint32_t*>(row + static_cast<size_t>(xa) * 4);
+            if (has_b && (reinterpret_cast<uintptr_t>(q) & 7u) == 0) *reinterpret_cast<uint2*>(q) = make_uint2(wa, wb);
+            else { q[0] = wa; if (has_b) q[1] = wb; }
+        }
     }
 }
 
@@ -1745,7 +1775,8 @@ cudaError_t launch_nv12(const LaunchParams& p, dim3 grid, cudaStream_t stream) {
 
 cudaError_t launch_gather4(const LaunchParams& p, dim3 grid, cudaStream_t stream) {
     if (p.four.enabled) {
-#define FKB_RGBA(N) (p.four.src3 ? rgba_kernel<N, true><<<grid, 256, 0, stream>>>(p) : rgba_kernel<N, false><<<grid, 256, 0, stream>>>(p))
+        const dim3 g2((grid.x + 1) / 2, grid.y, grid.z);  // two pixels per thread
+#define FKB_RGBA(N) (p.four.src3 ? rgba_kernel<N, true><<<g2, 256, 0, stream>>>(p) : rgba_kernel<N, false><<<g2, 256, 0, stream>>>(p))
         switch (p.four.n_steps) {
         case 0: FKB_RGBA(0); break;
         case 1: FKB_RGBA(1); break;

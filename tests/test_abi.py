@@ -127,6 +127,9 @@ def test_validate_rejects_bad_descriptors():
     assert status(lambda p, c: setattr(p[3], "dst_pitch", 128 * 3 - 1)) == abi.ERR_INVALID
     assert status(lambda p, c: setattr(p[3], "fx", 0.0)) == abi.ERR_INVALID
     assert status(lambda p, c: setattr(p[3], "fy", float("nan"))) == abi.ERR_INVALID
+    # source coordinates of 2^22 and more (fx * dst_w) are refused: the kernels take floors without a conversion
+    assert status(lambda p, c: setattr(p[3], "fx", float(2 ** 22) / p[3].dst_w)) == abi.ERR_UNSUPPORTED
+    assert status(lambda p, c: setattr(p[3], "fy", float(2 ** 21) / p[3].dst_h)) == abi.OK
     assert status(lambda p, c: setattr(p[4], "x2", 128)) == abi.ERR_INVALID                   # letterbox outside dst
     assert status(lambda p, c: setattr(p[4], "chain", 1)) == abi.ERR_INVALID                  # chain index out of range
     assert status(lambda p, c: setattr(c[0], "dst_format", abi.PIX_F32C3)) == abi.ERR_INVALID  # chain ends in uchar3

@@ -186,6 +186,10 @@ def test_edge_shapes():
         W.readme_crops(w=640, h=480, crops=((100, 100, 58, 3),), dst=(1, 105)),                     # target rounds to zero height
         W.nv12_preprocess(w=2, h=2, dst=(5, 3)), W.nv12_preprocess(w=64, h=48, dst=(1, 1)),
         W.batched_crop_resize(n_frames=1, crops_per_frame=1, w=32, h=32, crop_range=(32, 32), dst=(224, 224)),
+        # large source coordinates and scale factors in the thousands (tap positions are computed without conversions)
+        W.readme_crops(w=16000, h=8, crops=((0, 0, 16000, 8), (1, 0, 15999, 7)), dst=(7, 3)),
+        W.rgba_crops(w=4096, h=8, dst=(5, 3), rects=((0, 0, 4096, 8), (3, 1, 4001, 5))),
+        W.nv12_preprocess(w=4096, h=16, dst=(3, 2)),
     ]:
         check(wl)
         check(wl, force_gather=True)

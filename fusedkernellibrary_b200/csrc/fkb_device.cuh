@@ -211,8 +211,11 @@ enum : int {
     kPhaseLoads = 4,     // arrive.expect_tx + issuing the two bulk loads of a later row
     kPhaseWaitRead = 5,  // waiting until the previous row's store has read its buffer
     kPhaseRows = 6,      // rows processed (a count, not cycles)
-    kPhaseTotal = 7,     // cycles of the whole row loop
-    kPhaseCount = 8
+    kPhaseTotal = 7,     // cycles of the whole item (set-up and row loop)
+    kPhaseSetup = 8,     // an item's set-up: from its start (first loads requested) to the first row
+    kPhaseFirstWait = 9, // waiting for the source rows of the item's first row inside the image (part of no other phase)
+    kPhaseItems = 10,    // items processed (a count)
+    kPhaseCount = 12
 };
 #ifdef FKB_PHASE_CLOCKS
 constexpr bool kPhaseClocks = true;

@@ -811,6 +811,7 @@ template <bool F32, int KIND, bool PLANAR = false, bool SRC4 = false>
 __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSlice& w, uint32_t ox, uint32_t oy0,
                                             uint32_t ow, uint32_t nr, uint32_t& ph, uint32_t lane) {
     static_assert(F32 || !PLANAR, "planar rows are float rows");
+    PhaseClock pc;
     constexpr uint32_t FULL = 0xffffffffu;
     constexpr uint32_t SP = SRC4 ? 4u : 3u;                           // bytes per source pixel (uchar4: the alpha byte is skipped)
     constexpr uint32_t ELT = PLANAR ? 4u : F32 ? 12u : 3u;            // bytes between columns of a staged output row
@@ -882,17 +883,13 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
     uint32_t boff[8];
     float wx0[8], wx1[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        if (j < nj) {
-            int col = 32 * j + static_cast<int>(lane);                 // index among the inside columns
-            if (j == nj - 1 && n_in >= 32) col = n_in - 32 + static_cast<int>(lane);  // last group, shifted to be full
-            col = min(col, n_in - 1);
-            const AxisTap t = axis_tap(xa + col - X1, fx, crop_w);
-            boff[j] = static_cast<uint32_t>(t.i0 - c_lo) * SP + shift;
-            wx0[j] = t.w0; wx1[j] = t.w1;
-        } else {
-            boff[j] = 0u; wx0[j] = wx1[j] = 0.f;
-        }
+    for (int j = 0; j < 8; ++j) {  // (all eight without a branch, so that their chains overlap; groups past nj are never used)
+        int col = 32 * j + static_cast<int>(lane);                 // index among the inside columns
+        if (j == nj - 1 && n_in >= 32) col = n_in - 32 + static_cast<int>(lane);  // last group, shifted to be full
+        col = max(min(col, n_in - 1), 0);
+        const AxisTap t = axis_tap(xa + col - X1, fx, crop_w);
+        boff[j] = static_cast<uint32_t>(t.i0 - c_lo) * SP + shift;
+        wx0[j] = t.w0; wx1[j] = t.w1;
     }
     const uint32_t obase = static_cast<uint32_t>(xa - static_cast<int>(ox) + static_cast<int>(lane)) * ELT;
     const uint32_t olast = n_in >= 32 ? static_cast<uint32_t>(xa - static_cast<int>(ox) + n_in - 32 + static_cast<int>(lane)) * ELT
@@ -1037,7 +1034,9 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
     uint32_t s = 0;         // stage of the row being computed: r mod ns
     uint32_t o = 0;         // the output-row buffer the next written row goes to
     bool bg_ready = false;  // the other buffer holds a background row (the previous row was one)
-    PhaseClock pc;
+    pc.lap(kPhaseSetup);
+    pc.count(kPhaseItems);
+    bool first_wait = true;
     for (uint32_t r = 0; r < nr; ++r, gout += dst_pitch) {
         const uint32_t r0n = __shfl_sync(FULL, row0_l, (r + ns) & 31u), r1n = __shfl_sync(FULL, row1_l, (r + ns) & 31u);
         const bool row_in = (in_mask >> r) & 1u;
@@ -1059,7 +1058,8 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
             const float wy0s = __shfl_sync(FULL, wy0_l, r), wy1s = __shfl_sync(FULL, wy1_l, r);
             const bool ok = mbar_wait_bounded(w.bar(s), (ph >> s) & 1u, p.wait_limit_ns);
             if (__any_sync(FULL, !ok)) return false;  // (a convergence point for the whole warp, too)
-            pc.lap(kPhaseWait);
+            pc.lap(first_wait ? kPhaseFirstWait : kPhaseWait);
+            first_wait = false;
             ph ^= 1u << s;
             out_s = w.out(o);
             o ^= 1u;
@@ -1716,13 +1716,14 @@ cudaError_t launch_staged(const LaunchParams& p, uint32_t grid, cudaStream_t str
 
 #ifdef FKB_PHASE_CLOCKS
 }  // namespace fkb
-// Only in the phase-clock build: the sums over all warps since the last reset (see PhaseClock), out[kPhaseCount].
-extern "C" int fkb_debug_phase_clocks(unsigned long long* out, int reset) {
+// Only in the phase-clock build: the sums over all warps since the last reset (see PhaseClock) go to out[0 .. n), at most
+// kPhaseCount of them.
+extern "C" int fkb_debug_phase_clocks(unsigned long long* out, int n, int reset) {
     static unsigned long long host[fkb::kPhaseSlots][fkb::kPhaseCount];
     if (cudaDeviceSynchronize() != cudaSuccess) return -1;
     if (out) {
         if (cudaMemcpyFromSymbol(host, fkb::g_phase_clocks, sizeof(host)) != cudaSuccess) return -1;
-        for (int i = 0; i < fkb::kPhaseCount; ++i) {
+        for (int i = 0; i < n && i < fkb::kPhaseCount; ++i) {
             out[i] = 0;
             for (uint32_t s = 0; s < fkb::kPhaseSlots; ++s) out[i] += host[s][i];
         }

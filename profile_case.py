@@ -40,18 +40,19 @@ def phase_clocks(sets, launches: int) -> None:
     lib = abi.load()
     if not hasattr(lib, "fkb_debug_phase_clocks"):
         raise SystemExit("FKB_LIBRARY must name the phase-clock build (fusedkernellibrary_b200.build.build_phase_clocks())")
-    lib.fkb_debug_phase_clocks.argtypes = [C.POINTER(C.c_ulonglong), C.c_int]
+    lib.fkb_debug_phase_clocks.argtypes = [C.POINTER(C.c_ulonglong), C.c_int, C.c_int]
     sets[0].launch_plan()  # warm-up
-    assert lib.fkb_debug_phase_clocks(None, 1) == 0
+    assert lib.fkb_debug_phase_clocks(None, 0, 1) == 0
     for i in range(launches):
         sets[i % len(sets)].launch_plan()
-    out = (C.c_ulonglong * 8)()
-    assert lib.fkb_debug_phase_clocks(out, 0) == 0
-    rows = max(1, out[6])
-    print(f"{launches} launches, {rows} resize rows in all; cycles per row of one warp (lane 0's clock):")
+    out = (C.c_ulonglong * 12)()
+    assert lib.fkb_debug_phase_clocks(out, len(out), 0) == 0
+    rows, items = max(1, out[6]), max(1, out[10])
+    print(f"{launches} launches, {rows} resize rows in {items} items; cycles per row of one warp (lane 0's clock):")
     for i, name in enumerate(PHASES):
         print(f"  {name:40s} {out[i] / rows:8.1f}")
-    print(f"  {'row loop total':40s} {out[7] / rows:8.1f}")
+    print(f"cycles per item: set-up {out[8] / items:.1f}, waiting for the first row's source rows {out[9] / items:.1f}, "
+          f"whole item {out[7] / items:.1f} ({rows / items:.2f} rows per item)")
     for s in sets:
         s.close()
 

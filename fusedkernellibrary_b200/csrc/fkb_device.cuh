@@ -112,6 +112,7 @@ struct LaunchParams {
     uint32_t test_extra_tx;   // 0 in every real launch; a test sets it so that staged_kernel's loads announce bytes that never
                               // arrive and its bounded waits run out (the FKB_ERR_DEVICE_WAIT path)
     uint32_t wait_limit_ns;   // how long a device-side wait for a bulk copy may last before the kernel gives up (one second)
+    uint32_t pdl;             // host side only: launch the kernels with programmatic stream serialisation allowed
     PlaneRec inline_planes[kInlinePlanes];
 };
 
@@ -171,6 +172,12 @@ __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.comm
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// Programmatic dependent launch.  pdl_signal() lets the next kernel of the stream (if it was launched with programmatic
+// stream serialisation allowed) be set up while this grid still runs; pdl_wait() returns once the grid before this one
+// has completed and its writes are visible (at once when this launch has no such dependency).  Every kernel calls
+// pdl_signal() first and pdl_wait() before its first access to global memory.
+__device__ __forceinline__ void pdl_signal() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 // make this thread's shared-memory writes visible to the async (bulk-copy) proxy
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 

@@ -644,6 +644,7 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
     L.lp.neg_zero = -0.0f;
     L.lp.test_extra_tx = tune.test_extra_tx;
     L.lp.wait_limit_ns = tune.wait_limit_ns;
+    L.lp.pdl = total_pixels >= kPdlMinPixels;
     for (uint32_t c = 0; c < n_chains; ++c) {
         L.lp.post_kind[c] = post_kind_of(chains[c]);
         L.lp.post_imm[c] = post_imm_of(chains[c]);

@@ -48,6 +48,7 @@ constexpr uint32_t kLutSliceBytes = 64 + kLutStages * kLutSegBytes;
 constexpr uint32_t kLutSmemBytes = kLutTableAddr + kLutBytes + (kLutWarps - 9) * kLutSliceBytes;
 
 constexpr uint64_t kTinyLaunchPixels = 100000;  // launches below this many output pixels take the general kernel
+constexpr uint64_t kPdlMinPixels = 200000;      // launches of at least this many output pixels allow programmatic stream serialisation
 constexpr uint64_t kJoinGeneralPixels = 400000; // pipelined planes below this many pixels join a general kernel that runs anyway
 
 cudaError_t launch_staged(const LaunchParams& p, uint32_t grid, cudaStream_t stream);

@@ -417,7 +417,7 @@ def strong_split(rank: int, world: int, steps: int, t1_ms: float, t1_two_ms: flo
 
 
 def config5_sharded(rank: int, world: int, steps: int, peak: float, torch, dist) -> dict:
-    """The divergent 8-plane launch (BASELINE configs[4]) with its planes dealt over the ranks, plane z to rank z % world, so
+    """The divergent 8-plane launch (benchmark configuration 5) with its planes dealt over the ranks, plane z to rank z % world, so
     that resize planes and arithmetic planes are spread evenly.  Rank 0 also times the whole launch on its one GPU."""
     from fusedkernellibrary_b200 import runtime, workloads as W
     wl = W.divergent_planes()

@@ -241,7 +241,12 @@ int fkb_validate(const fkb_chain_desc* chains, uint32_t n_chains,
  * Stream capture: a launch of at most 8 planes carries its plane records in the kernel parameters and can be recorded
  * into a CUDA graph like any kernel launch.  A larger launch stages its records through buffers the library reuses from
  * call to call, which a recorded graph would read again at every replay; on a capturing stream such a launch returns
- * FKB_ERR_UNSUPPORTED and records nothing.  To put a large launch into a graph, create a plan and record fkb_plan_launch. */
+ * FKB_ERR_UNSUPPORTED and records nothing.  To put a large launch into a graph, create a plan and record fkb_plan_launch.
+ * Ordering: the usual stream order.  The kernels of launches of 200 000 output pixels and more are submitted with
+ * programmatic stream serialisation allowed, so that the GPU may set such a kernel up while an earlier kernel of this
+ * library is still running; every kernel waits for the completion (and the visibility of the writes) of the kernel
+ * before it in the stream before it touches global memory, so a launch may consume what the previous launch or any
+ * other earlier work in the stream produced.  FKB_PDL=0 in the environment switches the attribute off. */
 int fkb_launch_transform(const fkb_chain_desc* chain, const fkb_plane_desc* planes,
                          uint32_t n_planes, void* cuda_stream);
 

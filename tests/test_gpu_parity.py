@@ -461,6 +461,55 @@ def test_launches_of_one_plan_may_overlap_on_two_streams():
     dw.close()
 
 
+def test_a_launch_consumes_the_output_of_the_launch_before_it():
+    """Launches of this size are submitted with programmatic stream serialisation allowed, so a kernel may be set up while
+    the kernel before it in the stream still runs; it must not read anything before that kernel has completed.  A chain of
+    three launches in one stream, each reading what the one before wrote (table-lookup kernel -> table-lookup kernel ->
+    crop-resize kernel), run back to back and from a CUDA graph while the first launch's source alternates between two
+    images, must give what the oracle gives for the image of the last round."""
+    import dataclasses
+    from fusedkernellibrary_b200 import runtime
+    w, h = 1280, 720
+    first = W.vertical_fusion(w=w, h=h, seed=31)
+    other = W.vertical_fusion(w=w, h=h, seed=32)
+    second = W.vertical_fusion(w=w, h=h, seed=33)   # its source buffer is replaced by the first launch's output
+    third = W.readme_crops(w=w, h=h, crops=tuple((40 * i, 20 * i, 300 + 50 * i, 200 + 30 * i) for i in range(8)), dst=(224, 224))
+    assert first.out_sizes[0] == second.sources[0].nbytes == third.sources[0].nbytes
+    want = {}
+    for name, wl in (("a", first), ("b", other)):
+        out1 = oracle.run_oracle(wl, threads=8, fill=FILL)[0]
+        out2 = oracle.run_oracle(dataclasses.replace(second, sources=[out1]), threads=8, fill=FILL)[0]
+        want[name] = oracle.run_oracle(dataclasses.replace(third, sources=[out2]), threads=8, fill=FILL)[0]
+    d1, d2, d3 = (runtime.DeviceWorkload(x, poison=FILL) for x in (first, second, third))
+    d2.planes = second.bind([d1.out[0].data_ptr()], [t.data_ptr() for t in d2.out])
+    d3.planes = third.bind([d2.out[0].data_ptr()], [t.data_ptr() for t in d3.out])
+    images = {"a": d1.src[0].clone(), "b": torch.from_numpy(other.sources[0]).cuda()}
+
+    def round_of(name):
+        d1.src[0].copy_(images[name], non_blocking=True)
+        for d in (d1, d2, d3):
+            d.launch_plan()
+
+    for name in "abababab":
+        round_of(name)
+    assert np.array_equal(d3.results()[0], want["b"])
+    graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for name in "babababa":
+                round_of(name)
+    for _ in range(3):
+        graph.replay()
+    assert np.array_equal(d3.results()[0], want["a"])
+    # and without a copy between the rounds: kernel follows kernel all the way (one-shot launches of at most 8 planes too)
+    for _ in range(4):
+        for d in (d1, d2, d3):
+            d.launch()
+    assert np.array_equal(d3.results()[0], want["a"])
+    for d in (d1, d2, d3):
+        d.close()
+
+
 def test_stream_capture_small_launches_record_large_one_shot_launches_refuse():
     """A launch of at most eight planes carries its records in the kernel parameters and records into a CUDA graph; a
     larger one-shot launch (and the no-allocation entry point) stages records through host memory the library reuses, so

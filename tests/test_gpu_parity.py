@@ -307,6 +307,15 @@ def test_many_planes_use_the_descriptor_arena():
         check(wl)
 
 
+def test_more_planes_than_a_grid_dimension_holds():
+    # 70 000 planes in one launch (gridDim.z ends at 65 535): the pipelined kernel finds a plane by searching the table,
+    # the general kernel walks the planes in strides of its grid
+    wl = W.batched_crop_resize(n_frames=7, crops_per_frame=10000, w=320, h=240, dst=(4, 3), crop_range=(2, 40))
+    assert len(wl.planes) == 70000
+    check(wl)
+    check(wl, force_gather=True)
+
+
 def test_back_to_back_launches_on_side_streams():
     from fusedkernellibrary_b200 import runtime
     wls = [W.batched_crop_resize(n_frames=2, crops_per_frame=20, w=320, h=240, dst=(64, 64), seed=s) for s in range(3)]

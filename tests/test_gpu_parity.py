@@ -564,6 +564,19 @@ def test_self_checking_build_finds_nothing_on_the_parity_cases():
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
 
 
+def test_without_programmatic_stream_serialisation():
+    """FKB_PDL=0 (read once per process) launches every kernel without the attribute: the small configurations, the
+    chain of dependent launches and the launches on two streams give the same results in a fresh process."""
+    import subprocess
+    import sys
+    from conftest import ROOT
+    env = dict(os.environ, FKB_PDL="0")
+    r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(ROOT, "tests", "test_gpu_parity.py"), "-m", "gpu", "-x", "-q",
+                        "-k", "configurations_small or consumes_the_output or overlap_on_two_streams"],
+                       capture_output=True, text=True, timeout=1200, env=env, cwd=ROOT)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
+
+
 SHRUNK_FRAME = '''
 import os, sys
 sys.path.insert(0, sys.argv[1])

@@ -718,8 +718,10 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
     return status_word(&L.lp.status);
 }
 
-// Whether the staged kernel of this launch needs a work counter: every warp takes its first two items by position and
-// claims the rest, so a counter is needed as soon as some warp has a third item.
+// Whether the staged kernel of this launch gets a work counter.  With one, every warp takes its first item by position
+// and claims the rest; without, it takes every n-th item.  Up to two items per warp the positions do as well as claims
+// would (measured: 128 planes of 224 x 224, 1.5 items per warp, 25.1 us by position against 27.7 us with claims, which
+// all arrive at the counter at once when the kernel starts).
 bool wants_work_counter(const Lowered& L) {
     return L.staged_grid != 0 && L.lp.n_tiles > 2u * L.staged_grid * kStagedWarps;
 }

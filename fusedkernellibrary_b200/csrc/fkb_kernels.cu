@@ -620,6 +620,40 @@ __device__ __forceinline__ uint32_t tile_to_plane(const LaunchParams& p, uint32_
     return lo;
 }
 
+// The item a warp processes after the current one.  Its number is either known by position or claimed from the launch's
+// counter.  The item functions call claim_now() four rows before the end of the current item and fetch() two rows
+// before its end: by then the claim has returned, and the plane record requested there (14 lanes x 16 bytes, into
+// registers) arrives while the last rows are computed.  Claiming this late matters at the end of a launch: an item
+// claimed earlier than necessary waits for its warp while other warps have run out of work.
+constexpr uint32_t kRecLanes = sizeof(PlaneRec) / 16;
+struct NextItem {
+    const PlaneRec* table;
+    uint32_t* work;    // the launch's counter, or null: every item is dealt by position
+    uint32_t base;     // what is added to a claimed value: the number of items dealt by position
+    uint32_t item;     // the next item's number
+    uint32_t local;    // ... and its index among the items of its plane
+    uint32_t claim;    // (lane 0) what the counter returned
+    bool pending;      // `item` is to be replaced by the claim
+    uint4 rec;         // the next item's plane record, 16 bytes per lane
+    __device__ __forceinline__ void claim_now(uint32_t lane) {
+        if (work) {
+            if (lane == 0) claim = atomicAdd(work, 1u);
+            pending = true;
+        }
+    }
+    __device__ __forceinline__ void fetch(const LaunchParams& p, uint32_t lane) {
+        if (pending) item = base + __shfl_sync(0xffffffffu, claim, 0);
+        pending = false;
+        if (item < p.n_tiles) {
+            const uint32_t z = tile_to_plane(p, item, local);
+            if (lane < kRecLanes) rec = reinterpret_cast<const uint4*>(table + z)[lane];
+        }
+    }
+};
+// the rows of an item before which the next item is looked up and, two rows earlier, claimed
+__device__ __forceinline__ uint32_t fetch_row(uint32_t nr) { return nr > 2u ? nr - 2u : nr - 1u; }
+__device__ __forceinline__ uint32_t claim_row(uint32_t nr) { const uint32_t fr = fetch_row(nr); return fr > 2u ? fr - 2u : 0u; }
+
 // One output row segment leaves through the TMA engine: lane 0 issues a bulk store of the 16-byte multiple,
 // the (row_bytes mod 16) tail bytes go out with plain byte stores.
 __device__ __forceinline__ void store_row(uint8_t* gdst, uint32_t srow, uint32_t row_bytes, uint32_t lane, const PlaneRec& pl) {
@@ -683,7 +717,7 @@ __device__ __forceinline__ f2 post_channel(f2 r, const PostParams& q, int c, flo
 // Their rows are short (at most 1.5 KB in), so three rows are kept in flight ahead of the one being computed.
 template <bool F32, int KIND>
 __device__ __forceinline__ bool point_item(const LaunchParams& p, const WarpSlice& w, uint32_t ox, uint32_t oy0,
-                                           uint32_t ow, uint32_t nr, uint32_t& k, uint32_t lane) {
+                                           uint32_t ow, uint32_t nr, uint32_t& k, uint32_t lane, NextItem& next) {
     const PlaneRec& pl = *w.pl;
     const fkb_chain_desc& ch = p.chains[pl.chain];
     const float nz = p.neg_zero;
@@ -769,7 +803,10 @@ __device__ __forceinline__ bool point_item(const LaunchParams& p, const WarpSlic
     if (lane == 0) bulk_wait_read_all();
     __syncwarp();
     for (uint32_t i = 0; i < AHEAD && i < nr; ++i) issue(i, (k + i) & 3u);
+    const uint32_t fr = fetch_row(nr), cr = claim_row(nr);
     for (uint32_t r = 0; r < nr; ++r, ++k) {
+        if (r == cr) next.claim_now(lane);
+        if (r == fr) next.fetch(p, lane);
         const uint32_t s = k & 3u, o = k & 1u;
         if (lane == 0) bulk_wait_read_1();  // the store that read w.out(o) two rows ago is done with it
         if (r + AHEAD < nr) issue(r + AHEAD, (k + AHEAD) & 3u);  // into the stage of the row computed just before
@@ -815,7 +852,7 @@ __device__ __forceinline__ float post_scalar(float r, float m, float a) {
 
 template <bool F32, int KIND, bool PLANAR = false, bool SRC4 = false>
 __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSlice& w, uint32_t ox, uint32_t oy0,
-                                            uint32_t ow, uint32_t nr, uint32_t& ph, uint32_t lane) {
+                                            uint32_t ow, uint32_t nr, uint32_t& ph, uint32_t lane, NextItem& next) {
     static_assert(F32 || !PLANAR, "planar rows are float rows");
     PhaseClock pc;
     constexpr uint32_t FULL = 0xffffffffu;
@@ -1043,7 +1080,10 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
     pc.lap(kPhaseSetup);
     pc.count(kPhaseItems);
     bool first_wait = true;
+    const uint32_t fr = fetch_row(nr), cr = claim_row(nr);
     for (uint32_t r = 0; r < nr; ++r, gout += dst_pitch) {
+        if (r == cr) next.claim_now(lane);
+        if (r == fr) next.fetch(p, lane);
         const uint32_t r0n = __shfl_sync(FULL, row0_l, (r + ns) & 31u), r1n = __shfl_sync(FULL, row1_l, (r + ns) & 31u);
         const bool row_in = (in_mask >> r) & 1u;
         const uint32_t in_s = in0 + s * (2u * rs);
@@ -1131,14 +1171,14 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
 
 template <bool F32, bool PLANAR = false, bool SRC4 = false>
 __device__ __forceinline__ bool resize_dispatch(const LaunchParams& p, const WarpSlice& w, uint32_t kind, uint32_t ox,
-                                                uint32_t oy0, uint32_t ow, uint32_t nr, uint32_t& ph, uint32_t lane) {
+                                                uint32_t oy0, uint32_t ow, uint32_t nr, uint32_t& ph, uint32_t lane, NextItem& next) {
     constexpr int S = F32 ? 0 : kPostSat;  // a uchar3 destination ends in a SaturateCast, a float3 one cannot
     switch (kind) {
-    case S: return resize_item<F32, S, PLANAR, SRC4>(p, w, ox, oy0, ow, nr, ph, lane);
-    case S | kPostMul: return resize_item<F32, S | kPostMul, PLANAR, SRC4>(p, w, ox, oy0, ow, nr, ph, lane);
-    case S | kPostAdd: return resize_item<F32, S | kPostAdd, PLANAR, SRC4>(p, w, ox, oy0, ow, nr, ph, lane);
-    case S | kPostMul | kPostAdd: return resize_item<F32, S | kPostMul | kPostAdd, PLANAR, SRC4>(p, w, ox, oy0, ow, nr, ph, lane);
-    default: return resize_item<F32, kPostGeneric, PLANAR, SRC4>(p, w, ox, oy0, ow, nr, ph, lane);
+    case S: return resize_item<F32, S, PLANAR, SRC4>(p, w, ox, oy0, ow, nr, ph, lane, next);
+    case S | kPostMul: return resize_item<F32, S | kPostMul, PLANAR, SRC4>(p, w, ox, oy0, ow, nr, ph, lane, next);
+    case S | kPostAdd: return resize_item<F32, S | kPostAdd, PLANAR, SRC4>(p, w, ox, oy0, ow, nr, ph, lane, next);
+    case S | kPostMul | kPostAdd: return resize_item<F32, S | kPostMul | kPostAdd, PLANAR, SRC4>(p, w, ox, oy0, ow, nr, ph, lane, next);
+    default: return resize_item<F32, kPostGeneric, PLANAR, SRC4>(p, w, ox, oy0, ow, nr, ph, lane, next);
     }
 }
 
@@ -1153,41 +1193,29 @@ __global__ void __launch_bounds__(kStagedThreads, kStagedCtasPerSm) staged_kerne
     __syncwarp();
     pdl_wait();  // nothing above touches global memory
     const uint32_t warps_per_cta = blockDim.x >> 5;
-    // Items are dealt in two ways.  Statically, item i runs on warp (i / gridDim.x) % warps_per_cta of CTA i % gridDim.x
+    // Items are dealt in two ways.  By position, item i runs on warp (i / gridDim.x) % warps_per_cta of CTA i % gridDim.x
     // (a small launch spreads over all SMs).  With a work counter (launches of more than two items per warp), a warp takes
-    // its first two items that way and claims every further one from the counter, so that warps whose items were cheap
-    // (small crops, letterbox rows) take more of them.  A claim is issued one item before it is needed — the first one
-    // while the first item is processed — so neither its latency nor the crowd of warps that hit the counter when the
-    // kernel starts is on anybody's critical path.
+    // only its first item that way and claims every further one from the counter, so that warps whose items were cheap
+    // (small crops, letterbox rows) take more of them.  The claim for the next item is issued four rows before the
+    // current item ends and looked at two rows later (NextItem), so its latency is on nobody's critical path and no item
+    // is held back by more than half an item's time.
     const uint32_t first = warp * gridDim.x + blockIdx.x, stride = gridDim.x * warps_per_cta;
     const bool dynamic = p.work != nullptr;
-    const PlaneRec* table = plane_table(p);
     uint32_t ph = 0, k4 = 0;  // phase bits of the RESIZE items' barriers; steps done so far by POINT items (four stages)
     bool ok = true;
-    // The plane record of the next item is fetched (14 lanes x 16 bytes, into registers) while the current item is
-    // processed, so its global-memory latency is off the critical path.
-    constexpr uint32_t kRecLanes = sizeof(PlaneRec) / 16;
-    uint32_t local = 0, claim = 0, round = 0;
-    uint4 rec = make_uint4(0, 0, 0, 0);
-    if (first < p.n_tiles) {
-        const uint32_t z = tile_to_plane(p, first, local);
-        if (lane < kRecLanes) rec = reinterpret_cast<const uint4*>(table + z)[lane];
-    }
-    for (uint32_t item = first; item < p.n_tiles && ok; ++round) {
+    NextItem next;
+    next.table = plane_table(p);
+    next.work = p.work;
+    next.base = stride;
+    next.item = first; next.local = 0; next.claim = 0; next.pending = false;
+    next.rec = make_uint4(0, 0, 0, 0);
+    next.fetch(p, lane);  // the first item: its record's latency is paid once, at the start
+    for (uint32_t item = first; item < p.n_tiles && ok;) {
         __syncwarp();
-        if (lane < kRecLanes) reinterpret_cast<uint4*>(smem_raw + w.base + 64)[lane] = rec;
+        if (lane < kRecLanes) reinterpret_cast<uint4*>(smem_raw + w.base + 64)[lane] = next.rec;
         __syncwarp();
-        const uint32_t cur_local = local;
-        uint32_t next_item = item + stride;
-        if (dynamic) {
-            if (round) next_item = 2u * stride + __shfl_sync(0xffffffffu, claim, 0);  // the claim issued one item ago
-            if (lane == 0) claim = atomicAdd(p.work, 1u);
-        }
-        if (next_item < p.n_tiles) {
-            const uint32_t z = tile_to_plane(p, next_item, local);
-            if (lane < kRecLanes) rec = reinterpret_cast<const uint4*>(table + z)[lane];
-        }
-        item = next_item;
+        const uint32_t cur_local = next.local;
+        next.item = item + stride;  // by position, unless the launch has a counter
         const PlaneRec& pl = *w.pl;
         uint32_t tyi = cur_local, txi = 0;  // (most planes are one segment wide: no division then)
         if (pl.tiles_x != 1u) { tyi = cur_local / pl.tiles_x; txi = cur_local - tyi * pl.tiles_x; }
@@ -1195,22 +1223,23 @@ __global__ void __launch_bounds__(kStagedThreads, kStagedCtasPerSm) staged_kerne
         const uint32_t ow = min(pl.tile_w, pl.dst_w - ox), nr = min(pl.tile_h, pl.dst_h - oy0);
         const bool f32 = p.chains[pl.chain].dst_format == FKB_PIX_F32C3;
         if (pl.kclass == KCLASS_POINT) {
-            if (!f32) ok = point_item<false, kPostGeneric>(p, w, ox, oy0, ow, nr, k4, lane);
+            if (!f32) ok = point_item<false, kPostGeneric>(p, w, ox, oy0, ow, nr, k4, lane, next);
             else switch (p.post_kind[pl.chain]) {
-                case 0: ok = point_item<true, 0>(p, w, ox, oy0, ow, nr, k4, lane); break;
-                case kPostMul: ok = point_item<true, kPostMul>(p, w, ox, oy0, ow, nr, k4, lane); break;
-                case kPostAdd: ok = point_item<true, kPostAdd>(p, w, ox, oy0, ow, nr, k4, lane); break;
-                case kPostMul | kPostAdd: ok = point_item<true, kPostMul | kPostAdd>(p, w, ox, oy0, ow, nr, k4, lane); break;
-                default: ok = point_item<true, kPostGeneric>(p, w, ox, oy0, ow, nr, k4, lane); break;
+                case 0: ok = point_item<true, 0>(p, w, ox, oy0, ow, nr, k4, lane, next); break;
+                case kPostMul: ok = point_item<true, kPostMul>(p, w, ox, oy0, ow, nr, k4, lane, next); break;
+                case kPostAdd: ok = point_item<true, kPostAdd>(p, w, ox, oy0, ow, nr, k4, lane, next); break;
+                case kPostMul | kPostAdd: ok = point_item<true, kPostMul | kPostAdd>(p, w, ox, oy0, ow, nr, k4, lane, next); break;
+                default: ok = point_item<true, kPostGeneric>(p, w, ox, oy0, ow, nr, k4, lane, next); break;
             }
         }
         else if (p.chains[pl.chain].src_format == FKB_PIX_U8C4) {  // (float destinations only: the host lowering sees to it)
-            ok = p.chains[pl.chain].write_kind != FKB_WRITE_PACKED ? resize_dispatch<true, true, true>(p, w, p.post_kind[pl.chain], ox, oy0, ow, nr, ph, lane)
-                                                                   : resize_dispatch<true, false, true>(p, w, p.post_kind[pl.chain], ox, oy0, ow, nr, ph, lane);
+            ok = p.chains[pl.chain].write_kind != FKB_WRITE_PACKED ? resize_dispatch<true, true, true>(p, w, p.post_kind[pl.chain], ox, oy0, ow, nr, ph, lane, next)
+                                                                   : resize_dispatch<true, false, true>(p, w, p.post_kind[pl.chain], ox, oy0, ow, nr, ph, lane, next);
         }
-        else if (p.chains[pl.chain].write_kind != FKB_WRITE_PACKED) ok = resize_dispatch<true, true>(p, w, p.post_kind[pl.chain], ox, oy0, ow, nr, ph, lane);
-        else ok = f32 ? resize_dispatch<true>(p, w, p.post_kind[pl.chain], ox, oy0, ow, nr, ph, lane)
-                      : resize_dispatch<false>(p, w, p.post_kind[pl.chain], ox, oy0, ow, nr, ph, lane);
+        else if (p.chains[pl.chain].write_kind != FKB_WRITE_PACKED) ok = resize_dispatch<true, true>(p, w, p.post_kind[pl.chain], ox, oy0, ow, nr, ph, lane, next);
+        else ok = f32 ? resize_dispatch<true>(p, w, p.post_kind[pl.chain], ox, oy0, ow, nr, ph, lane, next)
+                      : resize_dispatch<false>(p, w, p.post_kind[pl.chain], ox, oy0, ow, nr, ph, lane, next);
+        item = next.item;
     }
     if (lane == 0) bulk_wait_all();  // shared memory must stay valid until the last bulk store has read it
     if (dynamic && lane == 0) {

@@ -96,6 +96,8 @@ struct LaunchParams {
     const PlaneRec* table;    // device table, or null when `inline_planes` is used
     uint32_t n_planes;
     uint32_t n_tiles;
+    uint32_t n_split;         // the last n_split items of the staged kernel are dealt as two halves each (first rows, last rows):
+                              // n_tiles + n_split item numbers in all; the launch then ends behind half an item, not a whole one
     uint32_t tiles_per_plane;  // > 0 when every plane has the same shape; else PlaneRec::tile_base is searched
     int* status;
     uint32_t* work;            // staged_kernel: {next item, warps finished} for dynamic item claiming; null = items dealt round-robin

@@ -221,6 +221,7 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 //                            the joining of small pipelined planes to a general kernel with it, which the tests use to
 //                            drive small cases through the pipelined kernels);
 //   FKB_ROWS_PER_ITEM=n      output rows per item of the staged kernel (default: chosen from the launch size);
+//   FKB_SPLIT_ITEMS=0        the staged kernel's last items are dealt whole (default: in two halves, see lower());
 //   FKB_TEST_EXTRA_TX=n      test hook: the staged kernel's resize loads announce n bytes more than they deliver, so its
 //                            bounded waits run out and the launch ends with FKB_ERR_DEVICE_WAIT in the status word;
 //   FKB_WAIT_LIMIT_US=n      how long such a wait lasts before it gives up (default one second);
@@ -232,6 +233,7 @@ struct Tuning {
     uint64_t tiny_pixels = kTinyLaunchPixels;
     uint32_t rows_per_item = 0, test_extra_tx = 0, wait_limit_ns = 1000000000u;
     bool test_shrink_frame = false;
+    bool split_items = true;  // FKB_SPLIT_ITEMS=0: the staged kernel's last items are not dealt in halves
 };
 Tuning read_tuning() {
     Tuning t;
@@ -240,6 +242,7 @@ Tuning read_tuning() {
     if ((e = std::getenv("FKB_TINY_PIXELS")) && e[0]) t.tiny_pixels = std::strtoull(e, nullptr, 10);
     if ((e = std::getenv("FKB_ROWS_PER_ITEM")) && e[0]) t.rows_per_item = static_cast<uint32_t>(std::strtoul(e, nullptr, 10));
     if ((e = std::getenv("FKB_TEST_EXTRA_TX")) && e[0]) t.test_extra_tx = static_cast<uint32_t>(std::strtoul(e, nullptr, 10));
+    if ((e = std::getenv("FKB_SPLIT_ITEMS")) && e[0] == '0') t.split_items = false;
     if ((e = std::getenv("FKB_TEST_SHRINK_FRAME")) && e[0] == '1') t.test_shrink_frame = true;
     if ((e = std::getenv("FKB_WAIT_LIMIT_US")) && e[0]) t.wait_limit_ns = static_cast<uint32_t>(std::min<unsigned long>(std::strtoul(e, nullptr, 10), 4000000ul) * 1000ul);
     return t;
@@ -653,6 +656,14 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         L.lp.lut_swap |= (reorders & 1u) << c;
     }
     L.lp.n_tiles = n_tiles;
+    {
+        // A launch whose warps claim their items ends when the last claimed items do.  The last items — half as many as
+        // there are resident warps — are therefore dealt as two halves each (their first rows, their other rows): the end
+        // of the launch then waits for half an item, at the price of one more item set-up for those.  FKB_SPLIT_ITEMS=0
+        // switches it off.
+        const uint32_t resident = kStagedCtasPerSm * kStagedWarps * static_cast<uint32_t>(sms);
+        L.lp.n_split = (tune.split_items && n_tiles > 2u * resident) ? std::min(n_tiles - 2u * resident, resident / 2u) : 0u;
+    }
     L.lp.tiles_per_plane = (same_shape && first_count) ? first_count : 0;
     if (n_tiles) {
         L.staged_grid = std::min<uint32_t>(n_tiles, kStagedCtasPerSm * static_cast<uint32_t>(sms));
@@ -723,7 +734,7 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
 // would (measured: 128 planes of 224 x 224, 1.5 items per warp, 25.1 us by position against 27.7 us with claims, which
 // all arrive at the counter at once when the kernel starts).
 bool wants_work_counter(const Lowered& L) {
-    return L.staged_grid != 0 && L.lp.n_tiles > 2u * L.staged_grid * kStagedWarps;
+    return L.staged_grid != 0 && L.lp.n_tiles > 2u * L.staged_grid * kStagedWarps;  // (n_split is zero below that)
 }
 
 int run(const Lowered& L, const LaunchParams& lp, cudaStream_t stream) {

@@ -630,8 +630,9 @@ struct NextItem {
     const PlaneRec* table;
     uint32_t* work;    // the launch's counter, or null: every item is dealt by position
     uint32_t base;     // what is added to a claimed value: the number of items dealt by position
-    uint32_t item;     // the next item's number
-    uint32_t local;    // ... and its index among the items of its plane
+    uint32_t item;     // the next item's number (numbers run to n_tiles + n_split: the last n_split items have two each)
+    uint32_t local;    // ... its index among the items of its plane
+    uint32_t half;     // ... and which part of it the number stands for: 0 all rows, 1 the first half, 2 the rest
     uint32_t claim;    // (lane 0) what the counter returned
     bool pending;      // `item` is to be replaced by the claim
     uint4 rec;         // the next item's plane record, 16 bytes per lane
@@ -644,8 +645,12 @@ struct NextItem {
     __device__ __forceinline__ void fetch(const LaunchParams& p, uint32_t lane) {
         if (pending) item = base + __shfl_sync(0xffffffffu, claim, 0);
         pending = false;
-        if (item < p.n_tiles) {
-            const uint32_t z = tile_to_plane(p, item, local);
+        if (item < p.n_tiles + p.n_split) {
+            const uint32_t n_whole = p.n_tiles - p.n_split;
+            uint32_t real = item;
+            half = 0u;
+            if (item >= n_whole) { real = n_whole + ((item - n_whole) >> 1); half = 1u + ((item - n_whole) & 1u); }
+            const uint32_t z = tile_to_plane(p, real, local);
             if (lane < kRecLanes) rec = reinterpret_cast<const uint4*>(table + z)[lane];
         }
     }
@@ -1207,20 +1212,32 @@ __global__ void __launch_bounds__(kStagedThreads, kStagedCtasPerSm) staged_kerne
     next.table = plane_table(p);
     next.work = p.work;
     next.base = stride;
-    next.item = first; next.local = 0; next.claim = 0; next.pending = false;
+    next.item = first; next.local = 0; next.half = 0; next.claim = 0; next.pending = false;
     next.rec = make_uint4(0, 0, 0, 0);
     next.fetch(p, lane);  // the first item: its record's latency is paid once, at the start
-    for (uint32_t item = first; item < p.n_tiles && ok;) {
+    const uint32_t n_items = p.n_tiles + p.n_split;
+    for (uint32_t item = first; item < n_items && ok;) {
         __syncwarp();
         if (lane < kRecLanes) reinterpret_cast<uint4*>(smem_raw + w.base + 64)[lane] = next.rec;
         __syncwarp();
-        const uint32_t cur_local = next.local;
+        const uint32_t cur_local = next.local, cur_half = next.half;
         next.item = item + stride;  // by position, unless the launch has a counter
         const PlaneRec& pl = *w.pl;
         uint32_t tyi = cur_local, txi = 0;  // (most planes are one segment wide: no division then)
         if (pl.tiles_x != 1u) { tyi = cur_local / pl.tiles_x; txi = cur_local - tyi * pl.tiles_x; }
-        const uint32_t ox = txi * pl.tile_w, oy0 = tyi * pl.tile_h;
-        const uint32_t ow = min(pl.tile_w, pl.dst_w - ox), nr = min(pl.tile_h, pl.dst_h - oy0);
+        const uint32_t ox = txi * pl.tile_w, ow = min(pl.tile_w, pl.dst_w - ox);
+        uint32_t oy0 = tyi * pl.tile_h, nr = min(pl.tile_h, pl.dst_h - oy0);
+        if (cur_half) {
+            const uint32_t head = (nr + 1u) >> 1;  // rows of the first half
+            if (cur_half == 1u) nr = head;
+            else { oy0 += head; nr -= head; }
+            if (nr == 0u) {  // (an item of one row has no second half; the next item is still to be found)
+                next.claim_now(lane);
+                next.fetch(p, lane);
+                item = next.item;
+                continue;
+            }
+        }
         const bool f32 = p.chains[pl.chain].dst_format == FKB_PIX_F32C3;
         if (pl.kclass == KCLASS_POINT) {
             if (!f32) ok = point_item<false, kPostGeneric>(p, w, ox, oy0, ow, nr, k4, lane, next);

@@ -348,16 +348,19 @@ bool rgb_kernel_takes(const fkb_chain_desc& ch, const PlaneRec& r) {
     return x >= 0 && y >= 0 && x + r.crop_w <= static_cast<int64_t>(r.src_w) && y + r.crop_h <= static_cast<int64_t>(r.src_h);
 }
 
-// Output rows a warp processes per item.  An item costs a set-up (about as much as one row) and, inside an item, the
-// source rows of the row after next are already in flight, so longer items run better; shorter ones balance better
-// (warps claim them from a counter) and leave a shorter tail when the launch ends.  Measured on crop-resize launches of
-// 64 to 2048 planes of 224 x 224: eight rows per item are the best or within 1 % of it at every size (2048 planes:
-// 6 rows +3 %, 12 rows +2 %, 16 rows +8 %, 32 rows +25 %).  A launch too small to give every resident warp eight rows
-// gets items of just the length that spreads its rows over all warps in one round.
+// Output rows a warp processes per item.  An item costs a set-up (about as much as a row and a half), and inside an
+// item the source rows of the rows after next are already in flight, so longer items run better; shorter ones balance
+// better (warps claim them from a counter, the next one a few rows before the current one ends) and leave a shorter
+// tail when the launch ends.  Measured on crop-resize launches of 224 x 224 planes (rows per warp in brackets): 2048
+// planes (194) 12 rows per item 242 us, 8: 255, 10: 245, 16: 245, 24: 251; 1024 planes (97) 12: 126, 8: 132, 16: 127;
+// 512 planes (48) 12: 68.3, 8: 70.5, 20: 72; 256 planes (24) 10: 39.1, 8: 40.0, 12: 41.3, 14: 46.6; 128 planes (12): items
+// of 13 or 14 rows, one per warp, 24-25 us, against 25.7-26.3 us for 6 to 8 rows.  So: a launch too small to give every
+// resident warp sixteen rows gets items of just the length that spreads its rows over all warps in one round; up to
+// forty rows per warp items have ten rows, beyond that twelve.
 uint32_t rows_per_item(uint64_t row_segments, uint32_t resident_warps) {
-    constexpr uint32_t kRows = 8;
-    if (row_segments >= static_cast<uint64_t>(kRows) * resident_warps) return kRows;
-    return static_cast<uint32_t>(std::max<uint64_t>((row_segments + resident_warps - 1) / resident_warps, 1));
+    if (row_segments < 16ull * resident_warps)
+        return static_cast<uint32_t>(std::max<uint64_t>((row_segments + resident_warps - 1) / resident_warps, 1));
+    return row_segments < 40ull * resident_warps ? 10u : 12u;
 }
 
 // Shape of the ops that follow the read / the interpolation: bit 0 Mul, bit 1 Add or Sub, bit 2 SaturateCast when the

@@ -354,13 +354,14 @@ bool rgb_kernel_takes(const fkb_chain_desc& ch, const PlaneRec& r) {
 // tail when the launch ends.  Measured on crop-resize launches of 224 x 224 planes (rows per warp in brackets): 2048
 // planes (194) 12 rows per item 242 us, 8: 255, 10: 245, 16: 245, 24: 251; 1024 planes (97) 12: 126, 8: 132, 16: 127;
 // 512 planes (48) 12: 68.3, 8: 70.5, 20: 72; 256 planes (24) 10: 39.1, 8: 40.0, 12: 41.3, 14: 46.6; 128 planes (12): items
-// of 13 or 14 rows, one per warp, 24-25 us, against 25.7-26.3 us for 6 to 8 rows.  So: a launch too small to give every
+// of 13 or 14 rows, one per warp, 24-25 us, against 25.7-26.3 us for 6 to 8 rows; 192 planes (18): 8 rows 31.0 us, 10 rows
+// 33.8 us (fewer than two items per warp, which are then dealt by position).  So: a launch too small to give every
 // resident warp sixteen rows gets items of just the length that spreads its rows over all warps in one round; up to
-// forty rows per warp items have ten rows, beyond that twelve.
+// twenty-one rows per warp items have eight rows (enough items for the counter), up to forty ten, beyond that twelve.
 uint32_t rows_per_item(uint64_t row_segments, uint32_t resident_warps) {
     if (row_segments < 16ull * resident_warps)
         return static_cast<uint32_t>(std::max<uint64_t>((row_segments + resident_warps - 1) / resident_warps, 1));
-    return row_segments < 40ull * resident_warps ? 10u : 12u;
+    return row_segments < 21ull * resident_warps ? 8u : row_segments < 40ull * resident_warps ? 10u : 12u;
 }
 
 // Shape of the ops that follow the read / the interpolation: bit 0 Mul, bit 1 Add or Sub, bit 2 SaturateCast when the

@@ -213,7 +213,7 @@ __device__ __forceinline__ bool bulk_range_ok(const void* a, uint32_t bytes, con
 // keep the compiler from moving instructions across them, so this build runs slower than the product; what it gives is
 // the split.  In the product build all of this compiles to nothing.
 enum : int {
-    kPhaseWait = 0,      // shuffles + waiting for the row's source rows to land
+    kPhaseWait = 0,      // shuffles + waiting for the row's source rows to land (+ the claim and look-up of the next item on two rows)
     kPhaseCompute = 1,   // taps, arithmetic, stores into the row buffer, proxy fence, warp sync
     kPhaseStore = 2,     // issuing the bulk store(s) of the row
     kPhaseCommit = 3,    // closing the bulk group

@@ -316,6 +316,15 @@ def test_more_planes_than_a_grid_dimension_holds():
     check(wl, force_gather=True)
 
 
+@pytest.mark.parametrize("dst", [(32, 1), (40, 2), (33, 3)])
+def test_thousands_of_planes_of_one_to_three_rows(dst):
+    # items of one, two and three rows, claimed from the counter; the last ones are dealt as two halves, and the second
+    # half of a one-row item is empty
+    wl = W.batched_crop_resize(n_frames=6, crops_per_frame=1000, w=320, h=240, dst=dst, crop_range=(2, 60))
+    check(wl)
+    check(wl, use_plan=True)
+
+
 def test_back_to_back_launches_on_side_streams():
     from fusedkernellibrary_b200 import runtime
     wls = [W.batched_crop_resize(n_frames=2, crops_per_frame=20, w=320, h=240, dst=(64, 64), seed=s) for s in range(3)]

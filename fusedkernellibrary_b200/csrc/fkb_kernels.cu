@@ -1196,7 +1196,6 @@ __global__ void __launch_bounds__(kStagedThreads, kStagedCtasPerSm) staged_kerne
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncwarp();
-    pdl_wait();  // nothing above touches global memory
     const uint32_t warps_per_cta = blockDim.x >> 5;
     // Items are dealt in two ways.  By position, item i runs on warp (i / gridDim.x) % warps_per_cta of CTA i % gridDim.x
     // (a small launch spreads over all SMs).  With a work counter (launches of more than two items per warp), a warp takes
@@ -1214,7 +1213,11 @@ __global__ void __launch_bounds__(kStagedThreads, kStagedCtasPerSm) staged_kerne
     next.base = stride;
     next.item = first; next.local = 0; next.half = 0; next.claim = 0; next.pending = false;
     next.rec = make_uint4(0, 0, 0, 0);
-    next.fetch(p, lane);  // the first item: its record's latency is paid once, at the start
+    // The first item's record is requested before the wait for the kernel before this one: the plane table is written by
+    // the host (kernel parameters, a plan's table, or an upload that this launch follows in stream order), never by a
+    // kernel, so reading it needs no ordering against one; everything else this kernel reads or writes comes after the wait.
+    next.fetch(p, lane);
+    pdl_wait();
     const uint32_t n_items = p.n_tiles + p.n_split;
     for (uint32_t item = first; item < n_items && ok;) {
         __syncwarp();

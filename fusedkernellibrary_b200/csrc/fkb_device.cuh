@@ -177,7 +177,8 @@ __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wa
 // Programmatic dependent launch.  pdl_signal() lets the next kernel of the stream (if it was launched with programmatic
 // stream serialisation allowed) be set up while this grid still runs; pdl_wait() returns once the grid before this one
 // has completed and its writes are visible (at once when this launch has no such dependency).  Every kernel calls
-// pdl_signal() first and pdl_wait() before its first access to global memory.
+// pdl_signal() first and pdl_wait() before it reads a source, writes a destination or touches a counter; plane records,
+// which only the host writes, may be read ahead of it.
 __device__ __forceinline__ void pdl_signal() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 // make this thread's shared-memory writes visible to the async (bulk-copy) proxy

@@ -245,8 +245,9 @@ int fkb_validate(const fkb_chain_desc* chains, uint32_t n_chains,
  * Ordering: the usual stream order.  The kernels of launches of 200 000 output pixels and more are submitted with
  * programmatic stream serialisation allowed, so that the GPU may set such a kernel up while an earlier kernel of this
  * library is still running; every kernel waits for the completion (and the visibility of the writes) of the kernel
- * before it in the stream before it touches global memory, so a launch may consume what the previous launch or any
- * other earlier work in the stream produced.  FKB_PDL=0 in the environment switches the attribute off. */
+ * before it in the stream before it reads a source or writes a destination (only plane records, which the host writes,
+ * may be read earlier), so a launch may consume what the previous launch or any other earlier work in the stream
+ * produced.  FKB_PDL=0 in the environment switches the attribute off. */
 int fkb_launch_transform(const fkb_chain_desc* chain, const fkb_plane_desc* planes,
                          uint32_t n_planes, void* cuda_stream);
 

@@ -541,6 +541,22 @@ def shard_by_plane(wl: Workload, rank: int, world: int) -> Workload:
                     extra={**wl.extra, "global_planes": mine})
 
 
+def combine(parts) -> Workload:
+    """One divergent launch out of several single-chain workloads: chain c is the chain of parts[c], its planes follow
+    those of the chains before it (the order in which a divergent launch of the reference lists its sequences); sources
+    and output buffers are kept apart."""
+    chains, sources, out_sizes, planes = [], [], [], []
+    for c, wl in enumerate(parts):
+        assert len(wl.chains) == 1
+        s0, o0 = len(sources), len(out_sizes)
+        chains.append(wl.chains[0])
+        sources += list(wl.sources)
+        out_sizes += list(wl.out_sizes)
+        planes += [PlaneSpec(**{**p.__dict__, "src": p.src + s0, "dst": p.dst + o0, "chain": c}) for p in wl.planes]
+    return Workload("combined_" + "_".join(wl.name for wl in parts), chains, sources, out_sizes, planes,
+                    f"divergent launch of {len(parts)} chains")
+
+
 CONFIGS = {
     "readme_crops": readme_crops,
     "vertical_fusion": vertical_fusion,

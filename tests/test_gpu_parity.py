@@ -149,6 +149,16 @@ def test_random_launches(seed):
         check(wl, force_gather=True)
 
 
+@pytest.mark.parametrize("base", range(0, 60, 3))
+def test_random_divergent_launches(base):
+    # three random chains in one divergent launch, with uneven numbers of planes: the lowering deals the planes chain by
+    # chain in turn, every plane must still land where its descriptor says
+    wl = W.combine([W.random_workload(base + i) for i in range(3)])
+    check(wl)
+    check(wl, force_gather=True)
+    check(wl, use_plan=True)
+
+
 def test_tiny_launch_routing():
     # default behaviour: launches of fewer than 100 000 output pixels run through the general kernel
     for wl in [W.readme_crops(), W.vertical_fusion(w=200, h=100), W.divergent_planes(n_per_seq=1, w=128, h=72)]:
@@ -568,7 +578,7 @@ def test_self_checking_build_finds_nothing_on_the_parity_cases():
     lib = fkb_build.build_debug()
     env = dict(os.environ, FKB_LIBRARY=lib)
     r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(ROOT, "tests", "test_gpu_parity.py"), "-m", "gpu", "-x", "-q",
-                        "-k", "configurations_small or golden_fixtures or random_launches or edge_shapes or border_reader_modes"],
+                        "-k", "configurations_small or golden_fixtures or random_launches or random_divergent or edge_shapes or border_reader_modes"],
                        capture_output=True, text=True, timeout=1200, env=env, cwd=ROOT)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
 

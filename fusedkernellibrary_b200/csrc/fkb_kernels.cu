@@ -523,6 +523,9 @@ __global__ void __launch_bounds__(256) rgba_kernel(const __grid_constant__ Launc
                 }
             }
         }
+        // A SaturateCast that ends the chain of a byte destination leaves its results as 2^23 + n, the integer in the low
+        // byte, ready to be packed (the same rounding as the step itself: clamp, then one addition that rounds to even).
+        bool biased = false;
 #pragma unroll
         for (int i = 0; i < N; ++i) {
             const uint32_t kind = (k.kinds >> (2 * i)) & 3u;
@@ -532,16 +535,31 @@ __global__ void __launch_bounds__(256) rgba_kernel(const __grid_constant__ Launc
             } else if (kind == 1u) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c) v[c] = f2{__fdiv_rn(v[c].x, k.m[i][c]), __fdiv_rn(v[c].y, k.m[i][c])};
+            } else if (i == N - 1 && !k.f32) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    v[c] = add2(f2{fminf(fmaxf(v[c].x, 0.f), 255.f), fminf(fmaxf(v[c].y, 0.f), 255.f)}, f2{kMagic, kMagic});
+                biased = true;
             } else {
 #pragma unroll
                 for (int c = 0; c < 4; ++c) v[c] = f2{sat_u8_as_float(v[c].x), sat_u8_as_float(v[c].y)};
             }
         }
+        // the channel order of the destination: as computed, red and blue exchanged, or (never produced by the host's
+        // flattening so far) any other permutation
+        constexpr uint32_t kAsIs = 0u | (1u << 2) | (2u << 4) | (3u << 6), kSwapped = 2u | (1u << 2) | (0u << 4) | (3u << 6);
         f2 o[4];
+        if (k.perm == kAsIs) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            const uint32_t from = (k.perm >> (2 * c)) & 3u;
-            o[c] = from == 0u ? v[0] : from == 1u ? v[1] : from == 2u ? v[2] : v[3];
+            for (int c = 0; c < 4; ++c) o[c] = v[c];
+        } else if (k.perm == kSwapped) {
+            o[0] = v[2]; o[1] = v[1]; o[2] = v[0]; o[3] = v[3];
+        } else {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const uint32_t from = (k.perm >> (2 * c)) & 3u;
+                o[c] = from == 0u ? v[0] : from == 1u ? v[1] : from == 2u ? v[2] : v[3];
+            }
         }
         uint8_t* row = pl.dst + static_cast<size_t>(y) * pl.dst_pitch;
         if (k.f32) {
@@ -549,9 +567,15 @@ __global__ void __launch_bounds__(256) rgba_kernel(const __grid_constant__ Launc
             q[0] = make_float4(o[0].x, o[1].x, o[2].x, o[3].x);
             if (has_b) q[1] = make_float4(o[0].y, o[1].y, o[2].y, o[3].y);
         } else {
-            // (the values are integers in [0, 255] held exactly: the chain ended in a SaturateCast)
-            const uint32_t wa = u8_of_exact(o[0].x) | (u8_of_exact(o[1].x) << 8) | (u8_of_exact(o[2].x) << 16) | (u8_of_exact(o[3].x) << 24);
-            const uint32_t wb = u8_of_exact(o[0].y) | (u8_of_exact(o[1].y) << 8) | (u8_of_exact(o[2].y) << 16) | (u8_of_exact(o[3].y) << 24);
+            // (the values are integers in [0, 255] held exactly, or already 2^23 + n: the low byte of the sum is the byte)
+            uint32_t ba[4], bb[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const f2 t = biased ? o[c] : add2(o[c], f2{kMagic, kMagic});
+                ba[c] = __float_as_uint(t.x); bb[c] = __float_as_uint(t.y);
+            }
+            const uint32_t wa = __byte_perm(__byte_perm(ba[0], ba[1], 0x0040u), __byte_perm(ba[2], ba[3], 0x0040u), 0x5410u);
+            const uint32_t wb = __byte_perm(__byte_perm(bb[0], bb[1], 0x0040u), __byte_perm(bb[2], bb[3], 0x0040u), 0x5410u);
             uint32_t* q = reinterpret_cast<uint32_t*>(row + static_cast<size_t>(xa) * 4);
             if (has_b && (reinterpret_cast<uintptr_t>(q) & 7u) == 0) *reinterpret_cast<uint2*>(q) = make_uint2(wa, wb);
             else { q[0] = wa; if (has_b) q[1] = wb; }

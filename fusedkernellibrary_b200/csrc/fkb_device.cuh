@@ -41,7 +41,9 @@ struct __align__(16) PlaneRec {
     uint32_t lut_base;          // LUT units of all earlier planes (monotone over the table, searched by lut_kernel)
     float bg_w;                 // four-channel chains: the fourth channel of bg and of the per-plane operands
     float params_w[FKB_MAX_PLANE_PARAMS];
-    uint32_t spare_[3];
+    uint32_t all_background;    // a plane of a resampling chain whose every pixel is `bg` put through the ops behind the
+                                // interpolation (a conditional batch read's plane beyond the used ones): no source is read
+    uint32_t spare_[2];
 };
 static_assert(sizeof(PlaneRec) == 224, "layout is mirrored by the host lowering");
 // byte offset of channel c of a planar destination

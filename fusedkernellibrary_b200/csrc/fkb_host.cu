@@ -576,8 +576,28 @@ int lower(const fkb_chain_desc* chains, uint32_t n_chains, const fkb_plane_desc*
         std::memcpy(r.params_w, s.params_w, sizeof(r.params_w));
         if (s.chain & FKB_PLANE_DEFAULT) {  // the kernels know such a plane by its null source; the general kernels fill it
             r.src = r.src_chroma = nullptr;
-            const uint32_t df = chains[r.chain].dst_format;
+            const fkb_chain_desc& ch = chains[r.chain];
+            const uint32_t df = ch.dst_format;
             r.kclass = (df == FKB_PIX_U8C4 || df == FKB_PIX_F32C4) ? KCLASS_GATHER4 : KCLASS_GATHER;
+            // Under a Resize such a plane is `bg` put through the ops behind the interpolation, pixel for pixel: what the
+            // pipelined kernel writes for a plane without a single pixel inside its resized image.  Where a plane of this
+            // chain with a source would take that kernel (asked of classify() with a stand-in source), this one does too,
+            // as an all-background plane; the launch then needs no second kernel for it.
+            if (ch.geometry != FKB_GEOM_NONE && !tune.force_gather && ch.src_format == FKB_PIX_U8C3) {
+                PlaneRec probe = r;
+                probe.src = reinterpret_cast<const uint8_t*>(uintptr_t{4096});  // (never read: classify() looks at its alignment only)
+                probe.src_pitch = 16; probe.src_w = probe.src_h = 1;
+                probe.crop_x = probe.crop_y = 0; probe.crop_w = probe.crop_h = 1;
+                probe.fx = probe.fy = 1.f; probe.x1 = probe.y1 = 0; probe.x2 = probe.y2 = 0;
+                classify(ch, probe, tune);
+                if (probe.kclass == KCLASS_RESIZE) {
+                    r.kclass = KCLASS_RESIZE;
+                    r.tile_w = std::min(r.dst_w, kMaxTileW); r.tiles_x = (r.dst_w + r.tile_w - 1) / r.tile_w;
+                    r.all_background = 1u;
+                    r.crop_x = r.crop_y = 0; r.crop_w = r.crop_h = 1; r.src_pitch = 16; r.fx = r.fy = 1.f;
+                    r.x1 = 0; r.x2 = -1; r.y1 = 0; r.y2 = -1;
+                }
+            }
         } else {
             classify(chains[r.chain], r, tune);
         }

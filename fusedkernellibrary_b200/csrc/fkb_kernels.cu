@@ -890,7 +890,8 @@ __device__ __forceinline__ bool resize_item(const LaunchParams& p, const WarpSli
     constexpr uint32_t DEAD = PLANAR ? kMaxTileW * 4u : kOutRowBytes;          // where columns that do not exist are stored
     const PlaneRec& pl = *w.pl;
     const fkb_chain_desc& ch = p.chains[pl.chain];
-    const bool par = ch.geometry >= FKB_GEOM_RESIZE_PRESERVE_AR;
+    // (an all-background plane carries an empty rectangle x1..x2, whatever the chain's geometry)
+    const bool par = ch.geometry >= FKB_GEOM_RESIZE_PRESERVE_AR || pl.all_background != 0u;
     const int X1 = par ? pl.x1 : 0, Y1 = par ? pl.y1 : 0;
     const int X2 = par ? pl.x2 : static_cast<int>(pl.dst_w) - 1, Y2 = par ? pl.y2 : static_cast<int>(pl.dst_h) - 1;
     const int crop_w = pl.crop_w, crop_h = pl.crop_h;

@@ -99,6 +99,7 @@ SMALL = {
     "split_planes_f32": lambda: W.split_planes(),
     "split_planes_u8": lambda: W.split_planes(f32=False, dst=(333, 77)),
     "conditional_resize": lambda: W.conditional_resize(),
+    "conditional_resize_large": lambda: W.conditional_resize(used=6, w=1920, h=1080, dst=(640, 360)),  # default planes as all-background planes
     "conditional_pointwise": lambda: W.conditional_pointwise(),
 }
 

@@ -336,6 +336,15 @@ def test_thousands_of_planes_of_one_to_three_rows(dst):
     check(wl, use_plan=True)
 
 
+@pytest.mark.parametrize("frames,crops,dst", [(3, 70, (100, 37)), (5, 64, (224, 224)), (9, 50, (57, 113)), (2, 400, (33, 21)),
+                                              (16, 32, (224, 224)), (7, 33, (300, 41))])
+def test_mid_size_batches_of_odd_shapes(frames, crops, dst):
+    # launches of a few items per warp: items claimed from the counter, the last ones in halves, rows per item by size
+    wl = W.batched_crop_resize(n_frames=frames, crops_per_frame=crops, w=640, h=360, dst=dst, crop_range=(2, 300))
+    check(wl)
+    check(wl, use_plan=True)
+
+
 def test_back_to_back_launches_on_side_streams():
     from fusedkernellibrary_b200 import runtime
     wls = [W.batched_crop_resize(n_frames=2, crops_per_frame=20, w=320, h=240, dst=(64, 64), seed=s) for s in range(3)]
